@@ -1,0 +1,288 @@
+/*
+ * qoracle.c -- CPU restatement of the affine group-quantized inference path.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is the checker the CUDA library is
+ * compared against (tests/, the smoke check and the cpu_baseline leg of the
+ * benchmark).  Nothing in the shipped library links, loads or calls it.
+ *
+ * What it restates (paths are relative to the mlx-serve source tree):
+ *   - packed layout, unpack, dequantize : tests/dsv4_imatrix.py:107-163
+ *     (pack_bits / unpack_bits / dequant_np), cross-checked by the unpack in
+ *     src/transformer.zig:20098-20109 and :4931-4937
+ *   - bf16 round-to-nearest-even        : tests/convert_dsv4_weights.py:154-162
+ *   - quantize (scale/bias selection)   : tests/dsv4_imatrix.py:169-183
+ *     (_mlx_minmax_sb) and the code derivation at :264
+ *   - quantized_matmul, both transposes : src/kv_quant.zig:968-1094 and the
+ *     ground-truth loops in src/transformer.zig:24735-24744
+ *   - gather_qmm                        : src/transformer.zig:24735-24744,
+ *     :24799-24808, call shapes :15007-15035 and :15091-15119
+ *   - decode attention over packed K/V  : src/kv_quant.zig:478-687, kernel
+ *     semantics src/transformer.zig:4890-5006, batch length mask :10216-10249
+ *
+ * The arithmetic itself lives in ml-explore/mlx v0.32.0 (an un-vendored
+ * submodule, lib/mlx-src, absent from the checkout).  Parity is therefore
+ * pinned to the reference's own Python restatement above: the golden vectors
+ * under tests/golden/ were produced by importing tests/dsv4_imatrix.py and this
+ * file must reproduce them bit for bit (tests/test_oracle_golden.py).
+ *
+ * Two definitions no reference test pins, fixed here and mirrored on the GPU:
+ *   dequantize: bf16_rne( fmul(float(q), float(scale)) + float(bias) ) with a
+ *               separate fp32 multiply and add (build with -ffp-contract=off);
+ *   quantize:   codes are derived from the UNROUNDED fp32 (scale, bias); the
+ *               stored scale/bias are those values rounded to bf16.
+ * Matmul/attention accumulate in fp32 in index order; the weight term is the
+ * fp32 value q*s+b (not rounded to bf16).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define QO_API __attribute__((visibility("default")))
+
+/* ---- bf16 <-> f32 (tests/convert_dsv4_weights.py:154-162) ---- */
+static inline float bf16_to_f32(uint16_t h) {
+  uint32_t u = ((uint32_t)h) << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+static inline uint16_t f32_to_bf16(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  uint32_t r = u + 0x7FFFu + ((u >> 16) & 1u);
+  return (uint16_t)(r >> 16);
+}
+
+QO_API void qo_f32_to_bf16(const float* x, uint16_t* out, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) out[i] = f32_to_bf16(x[i]);
+}
+QO_API void qo_bf16_to_f32(const uint16_t* x, float* out, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) out[i] = bf16_to_f32(x[i]);
+}
+QO_API int qo_num_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
+
+/* ---- pack / unpack, bits in {2,4,8} (tests/dsv4_imatrix.py:107-153) ----
+ * value i of a row sits in word i/(32/bits) at bit (i % (32/bits))*bits. */
+QO_API void qo_pack(const uint8_t* q, int64_t rows, int64_t d, int bits, uint32_t* out) {
+  const int vpw = 32 / bits;
+  const int64_t words = d / vpw;
+  for (int64_t r = 0; r < rows; ++r)
+    for (int64_t w = 0; w < words; ++w) {
+      uint32_t word = 0;
+      for (int k = 0; k < vpw; ++k) word |= ((uint32_t)q[r * d + w * vpw + k]) << (k * bits);
+      out[r * words + w] = word;
+    }
+}
+QO_API void qo_unpack(const uint32_t* w, int64_t rows, int64_t d, int bits, uint8_t* out) {
+  const int vpw = 32 / bits;
+  const int64_t words = d / vpw;
+  const uint32_t mask = (1u << bits) - 1u;
+  for (int64_t r = 0; r < rows; ++r)
+    for (int64_t i = 0; i < d; ++i)
+      out[r * d + i] = (uint8_t)((w[r * words + i / vpw] >> ((i % vpw) * bits)) & mask);
+}
+
+static inline float unpack1(const uint32_t* row, int64_t i, int bits) {
+  const int vpw = 32 / bits;
+  return (float)((row[i / vpw] >> ((i % vpw) * bits)) & ((1u << bits) - 1u));
+}
+
+/* ---- dequantize (tests/dsv4_imatrix.py:156-163) ----
+ * w[r,i] = float(q)*float(s[r,i/gs]) + float(b[r,i/gs]); fp32 out. */
+QO_API void qo_dequantize_f32(const uint32_t* w, const uint16_t* s, const uint16_t* b,
+                              int64_t rows, int64_t d, int gs, int bits, float* out) {
+  const int64_t words = d * bits / 32, groups = d / gs;
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r)
+    for (int64_t i = 0; i < d; ++i) {
+      const float sc = bf16_to_f32(s[r * groups + i / gs]);
+      const float bi = bf16_to_f32(b[r * groups + i / gs]);
+      const float prod = unpack1(w + r * words, i, bits) * sc; /* rounded fp32 product */
+      out[r * d + i] = prod + bi;
+    }
+}
+QO_API void qo_dequantize_bf16(const uint32_t* w, const uint16_t* s, const uint16_t* b,
+                               int64_t rows, int64_t d, int gs, int bits, uint16_t* out) {
+  const int64_t words = d * bits / 32, groups = d / gs;
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r)
+    for (int64_t i = 0; i < d; ++i) {
+      const float sc = bf16_to_f32(s[r * groups + i / gs]);
+      const float bi = bf16_to_f32(b[r * groups + i / gs]);
+      const float prod = unpack1(w + r * words, i, bits) * sc;
+      out[r * d + i] = f32_to_bf16(prod + bi);
+    }
+}
+
+/* ---- quantize (tests/dsv4_imatrix.py:169-183 and :264) ----
+ * x: fp32 (bf16 inputs are widened by the caller, exactly). */
+QO_API void qo_quantize(const float* x, int64_t rows, int64_t d, int gs, int bits,
+                        uint32_t* out_q, uint16_t* out_s, uint16_t* out_b) {
+  const int vpw = 32 / bits;
+  const int64_t words = d / vpw, groups = d / gs;
+  const float n_bins = (float)((1 << bits) - 1);
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r) {
+    for (int64_t w = 0; w < words; ++w) out_q[r * words + w] = 0;
+    for (int64_t g = 0; g < groups; ++g) {
+      const float* X = x + r * d + g * gs;
+      float xmin = X[0], xmax = X[0];
+      for (int j = 1; j < gs; ++j) {
+        xmin = fminf(xmin, X[j]);
+        xmax = fmaxf(xmax, X[j]);
+      }
+      const int mask = fabsf(xmin) > fabsf(xmax);
+      float scale = fmaxf((xmax - xmin) / n_bins, 1e-7f);
+      scale = mask ? scale : -scale;
+      const float edge = mask ? xmin : xmax;
+      const float q0 = rintf(edge / scale);
+      float bias = 0.0f;
+      if (q0 != 0.0f) {
+        scale = edge / q0;
+        bias = edge;
+      }
+      for (int j = 0; j < gs; ++j) {
+        float v = rintf((X[j] - bias) / scale);
+        v = fminf(fmaxf(v, 0.0f), n_bins);
+        const int64_t i = g * gs + j;
+        out_q[r * words + i / vpw] |= ((uint32_t)v) << ((i % vpw) * bits);
+      }
+      out_s[r * groups + g] = f32_to_bf16(scale);
+      out_b[r * groups + g] = f32_to_bf16(bias);
+    }
+  }
+}
+
+/* ---- quantized_matmul, transpose=true (src/kv_quant.zig:968-1036) ----
+ * y[m,n] = sum_k x[m,k] * What[n,k];  W packed [N, K*bits/32], s,b [N, K/gs]. */
+QO_API void qo_qmm_t(const float* x, const uint32_t* w, const uint16_t* s, const uint16_t* b,
+                     int64_t M, int64_t N, int64_t K, int gs, int bits, float* y) {
+  const int64_t words = K * bits / 32, groups = K / gs;
+#pragma omp parallel
+  {
+    float* wrow = (float*)malloc(sizeof(float) * (size_t)K);
+#pragma omp for schedule(static)
+    for (int64_t n = 0; n < N; ++n) {
+      for (int64_t k = 0; k < K; ++k) {
+        const float sc = bf16_to_f32(s[n * groups + k / gs]);
+        const float bi = bf16_to_f32(b[n * groups + k / gs]);
+        const float prod = unpack1(w + n * words, k, bits) * sc;
+        wrow[k] = prod + bi;
+      }
+      for (int64_t m = 0; m < M; ++m) {
+        float acc = 0.0f;
+        const float* xr = x + m * K;
+        for (int64_t k = 0; k < K; ++k) acc += xr[k] * wrow[k];
+        y[m * N + n] = acc;
+      }
+    }
+    free(wrow);
+  }
+}
+
+/* ---- quantized_matmul, transpose=false (src/kv_quant.zig:1038-1094) ----
+ * y[m,n] = sum_k x[m,k] * What[k,n];  W packed [K, N*bits/32], s,b [K, N/gs]
+ * (groups run along the output axis n). */
+QO_API void qo_qmm_n(const float* x, const uint32_t* w, const uint16_t* s, const uint16_t* b,
+                     int64_t M, int64_t N, int64_t K, int gs, int bits, float* y) {
+  const int64_t words = N * bits / 32, groups = N / gs;
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; ++m) {
+    for (int64_t n = 0; n < N; ++n) {
+      float acc = 0.0f;
+      for (int64_t k = 0; k < K; ++k) {
+        const float sc = bf16_to_f32(s[k * groups + n / gs]);
+        const float bi = bf16_to_f32(b[k * groups + n / gs]);
+        const float prod = unpack1(w + k * words, n, bits) * sc;
+        acc += x[m * K + k] * (prod + bi);
+      }
+      y[m * N + n] = acc;
+    }
+  }
+}
+
+/* ---- gather_qmm, transpose=true (src/transformer.zig:24735-24744, :24799-24808) ----
+ * For output batch element i: y[i, m, :] = x[lhs[i], m, :] . What[rhs[i]]^T.
+ * x: [XB, M, K]; bank w: [E, N, K*bits/32]; lhs/rhs: [I]. */
+QO_API void qo_gather_qmm_t(const float* x, const uint32_t* w, const uint16_t* s, const uint16_t* b,
+                            const int64_t* lhs, const int64_t* rhs, int64_t I, int64_t M,
+                            int64_t N, int64_t K, int gs, int bits, float* y) {
+  const int64_t words = K * bits / 32, groups = K / gs;
+#pragma omp parallel for schedule(dynamic, 1)
+  for (int64_t i = 0; i < I; ++i) {
+    const int64_t e = rhs[i];
+    qo_qmm_t(x + lhs[i] * M * K, w + e * N * words, s + e * N * groups, b + e * N * groups, M, N,
+             K, gs, bits, y + i * M * N);
+  }
+}
+
+/* ---- decode attention over a packed K/V cache ----
+ * (src/kv_quant.zig:478-687 semantics with Tq == 1; batch length mask
+ *  src/transformer.zig:10216-10249; kernel semantics :4890-5006)
+ * q: [B, Hq, D] fp32; K triple: kq [B,Hkv,T,D*bits/32], ks/kb [B,Hkv,T,D/gs];
+ * V triple likewise with Dv.  All addressed by explicit (batch, head, token)
+ * element strides because cache views are strided slices of capacity buffers
+ * (src/transformer.zig:3472-3495).  kv_lens[b] (may be NULL => T) masks
+ * positions >= len; mask (may be NULL) is an additive fp32 row [B, T].
+ * out: [B, Hq, Dv] fp32. */
+QO_API void qo_kv_decode_attention(
+    const float* q, const uint32_t* kq, const uint16_t* ks, const uint16_t* kb,
+    const uint32_t* vq, const uint16_t* vs, const uint16_t* vb, int64_t B, int64_t Hq,
+    int64_t Hkv, int64_t T, int64_t D, int64_t Dv, int gs, int bits,
+    const int64_t* kq_str, const int64_t* ksb_str, const int64_t* vq_str, const int64_t* vsb_str,
+    float scale, const int32_t* kv_lens, const float* mask, float* out) {
+  const int64_t gqa = Hq / Hkv;
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
+  for (int64_t bi = 0; bi < B; ++bi) {
+    for (int64_t h = 0; h < Hq; ++h) {
+      const int64_t hk = h / gqa;
+      const int64_t len = kv_lens ? (int64_t)kv_lens[bi] : T;
+      float* sc = (float*)malloc(sizeof(float) * (size_t)(T > 0 ? T : 1));
+      const float* qv = q + (bi * Hq + h) * D;
+      float mx = -INFINITY;
+      for (int64_t t = 0; t < len; ++t) {
+        const uint32_t* row = kq + bi * kq_str[0] + hk * kq_str[1] + t * kq_str[2];
+        const uint16_t* srow = ks + bi * ksb_str[0] + hk * ksb_str[1] + t * ksb_str[2];
+        const uint16_t* brow = kb + bi * ksb_str[0] + hk * ksb_str[1] + t * ksb_str[2];
+        float acc = 0.0f;
+        for (int64_t e = 0; e < D; ++e) {
+          const float prod = unpack1(row, e, bits) * bf16_to_f32(srow[e / gs]);
+          acc += qv[e] * (prod + bf16_to_f32(brow[e / gs]));
+        }
+        float v = acc * scale;
+        if (mask) v += mask[bi * T + t];
+        sc[t] = v;
+        if (v > mx) mx = v;
+      }
+      float* o = out + (bi * Hq + h) * Dv;
+      for (int64_t e = 0; e < Dv; ++e) o[e] = 0.0f;
+      float l = 0.0f;
+      if (mx == -INFINITY) mx = 0.0f; /* fully masked: weights all zero */
+      for (int64_t t = 0; t < len; ++t) {
+        const float p = expf(sc[t] - mx);
+        l += p;
+        const uint32_t* row = vq + bi * vq_str[0] + hk * vq_str[1] + t * vq_str[2];
+        const uint16_t* srow = vs + bi * vsb_str[0] + hk * vsb_str[1] + t * vsb_str[2];
+        const uint16_t* brow = vb + bi * vsb_str[0] + hk * vsb_str[1] + t * vsb_str[2];
+        for (int64_t e = 0; e < Dv; ++e) {
+          const float prod = unpack1(row, e, bits) * bf16_to_f32(srow[e / gs]);
+          o[e] += p * (prod + bf16_to_f32(brow[e / gs]));
+        }
+      }
+      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+      for (int64_t e = 0; e < Dv; ++e) o[e] *= inv;
+      free(sc);
+    }
+  }
+}
