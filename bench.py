@@ -1,0 +1,314 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantized-inference hot path on B200 (one process per GPU).
+
+Default workload (``--workload c2``): continuous-batching decode through the 7 affine 4-bit g64
+projections of a Llama-3-8B-shaped layer (q,o 4096->4096; k,v 4096->1024; gate,up 4096->14336;
+down 14336->4096) for M concurrent sequences per GPU.  A *step* is one pass of M token rows through
+``--layers`` distinct layers' weight sets (distinct so the working set, ~123 MB per layer, is far
+larger than the 126 MB L2 and every pass streams the weights from HBM).  The metric is decode
+tokens/s through one such layer: value = n_gpus * M * layers * steps / time.  Sequences are
+batch-sharded: every GPU holds a full weight replica and its own M rows; no communication.
+
+Synthetic data: weights ~N(0,0.02) quantized on the device with the library's own quantize, activations
+~N(0,1) bf16, seeded.  Every launch goes through the C ABI (libqb200.so) via ctypes; the timed region is
+a CUDA graph of those launches replayed ``--steps`` times between CUDA events.
+
+``--impl reference`` times the CPU restatement of the same path (oracle/, the stand-in for MLX's CPU
+backend, which is not in the reference checkout) on the host cores for the same metric.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "mlx-serve_b200"))
+
+LLAMA = [("q", 4096, 4096), ("k", 1024, 4096), ("v", 1024, 4096), ("o", 4096, 4096),
+         ("gate", 14336, 4096), ("up", 14336, 4096), ("down", 4096, 14336)]
+BITS, GS = 4, 64
+
+
+def layer_bytes(M, bits=BITS, gs=GS):
+    """Algorithmic bytes of one layer pass: packed weights + scales + biases + activations in + out."""
+    tot = 0
+    for _, n, k in LLAMA:
+        tot += n * k * bits // 8 + 2 * (n * (k // gs) * 2) + M * k * 2 + M * n * 2
+    return tot
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows, self.proc, self.idx = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx = float(r[2])
+                for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                                  ("sw_power_cap", 8)):
+                    if r[col].lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                continue
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_layer_pass(M, seed=0xC2, reps=None, budget_s=12.0):
+    """Oracle timing of one layer pass (7 projections) at M rows; returns (tokens/s, threads, sample text)."""
+    import numpy as np
+    from oracle import qoracle as qo
+    rng = np.random.default_rng(seed)
+    ws, xs = [], {}
+    for _, n, k in LLAMA:
+        q = rng.integers(0, 2 ** 32, size=(n, k * BITS // 32), dtype=np.uint32)
+        s = qo.f32_to_bf16((np.abs(rng.standard_normal((n, k // GS))) * 0.005 + 1e-3).astype(np.float32))
+        b = qo.f32_to_bf16((rng.standard_normal((n, k // GS)) * 0.04).astype(np.float32))
+        ws.append((q, s, b))
+        if k not in xs:
+            xs[k] = qo.bf16_round(rng.standard_normal((M, k)).astype(np.float32))
+
+    def one():
+        for (q, s, b), (_, n, k) in zip(ws, LLAMA):
+            qo.qmm(xs[k], q, s, b, GS, BITS)
+
+    one()  # warm
+    t0 = time.perf_counter()
+    one()
+    dt1 = time.perf_counter() - t0
+    n = reps if reps is not None else max(1, min(50, int(budget_s / max(dt1, 1e-6))))
+    t0 = time.perf_counter()
+    for _ in range(n):
+        one()
+    dt = (time.perf_counter() - t0) / n
+    return M / dt, qo.num_threads(), f"{n} passes of one layer (7 projections) at M={M}, weights of random codes", dt
+
+
+def run_reference(args):
+    """The reference arm: the CPU restatement of the path on the host cores, same metric."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    M = args.m
+    steps, warmup = args.steps, args.warmup
+    reps = max(1, warmup) + steps
+    import numpy as np  # noqa: F401
+    tps, threads, sample, dt = cpu_layer_pass(M, reps=None, budget_s=max(4.0, min(40.0, 2.0 * reps)))
+    out = {
+        "impl": "reference", "metric": "decode_tokens_per_s_llama3_8b_layer_q4g64", "value": tps, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "c2: Llama-3-8B layer, 7 projections, 4-bit g64, M=%d rows; CPU oracle port "
+                               "(MLX CPU backend absent from the reference checkout)" % M, "M_per_gpu": M},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(out))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=8, help="concurrent sequences (token rows) per GPU")
+    ap.add_argument("--layers", type=int, default=16, help="distinct layer weight sets rotated through per step")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", action="store_true", help="also report M in {1,8,32,128} (outside the timed steps)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    import qb200
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    qb200.lib()  # fail loudly if the library is not built
+
+    M, L = args.m, args.layers
+    g = torch.Generator(device=dev).manual_seed(0xC2 + rank)
+    layers = []
+    for _ in range(L):
+        ws = []
+        for _, n, k in LLAMA:
+            w = (torch.randn((n, k), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+            ws.append(qb200.quantize(w, GS, BITS))
+            del w
+        layers.append(ws)
+
+    def make_io(m):
+        xin = torch.randn((L, m, 4096 + 14336), device=dev, generator=g).to(torch.bfloat16)
+        nout = sum(n for _, n, _ in LLAMA)
+        yout = torch.empty((L, m, nout), dtype=torch.bfloat16, device=dev)
+        return xin, yout
+
+    def enqueue(xin, yout):
+        for li in range(L):
+            col = 0
+            for (name, n, k), (q, s, b) in zip(LLAMA, layers[li]):
+                x = xin[li, :, :4096] if k == 4096 else xin[li, :, 4096:]
+                qb200.quantized_matmul(x, q, s, b, True, GS, BITS, out=yout[li, :, col:col + n])
+                col += n
+
+    def build_graph(m):
+        xin, yout = make_io(m)
+        s = torch.cuda.Stream(device=dev)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            enqueue(xin, yout)  # sets kernel attributes, warms up
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            enqueue(xin, yout)
+        return gr, xin, yout
+
+    def time_graph(gr, steps, warmup):
+        for _ in range(warmup):
+            gr.replay()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            gr.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.barrier()
+            ms = float(t.item())
+        return ms
+
+    gr, xin, yout = build_graph(M)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = time_graph(gr, args.steps, max(args.warmup, 3))
+    ms_step = ms / args.steps
+    value = world * M * L * args.steps / (ms * 1e-3)
+
+    # end to end: host buffers in, host buffers out, copies inside the timed region
+    xin_h = torch.empty(xin.shape, dtype=xin.dtype, pin_memory=True).copy_(xin)
+    yout_h = torch.empty(yout.shape, dtype=yout.dtype, pin_memory=True)
+    for _ in range(3):
+        xin.copy_(xin_h, non_blocking=True); gr.replay(); yout_h.copy_(yout, non_blocking=True)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        xin.copy_(xin_h, non_blocking=True)
+        gr.replay()
+        yout_h.copy_(yout, non_blocking=True)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_e2e = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    e2e_value = world * M * L * args.steps / (ms_e2e * 1e-3)
+
+    sweep = None
+    if args.sweep:
+        sweep = {}
+        for m in (1, 8, 32, 128):
+            g2, _, _ = build_graph(m)
+            msw = time_graph(g2, args.steps, 3) / args.steps
+            sweep[str(m)] = {"ms_per_step": msw, "tokens_per_s": world * m * L / (msw * 1e-3),
+                             "hbm_gbs": L * layer_bytes(m) / (msw * 1e-3) / 1e9}
+            del g2
+
+    if rank == 0:
+        peak, which = peaks()
+        launches_per_call = (M + 31) // 32
+        achieved = L * layer_bytes(M) / (ms_step * 1e-3) / 1e9
+        out = {
+            "metric": "decode_tokens_per_s_llama3_8b_layer_q4g64", "value": value, "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "c2: continuous-batching decode through the 7 affine 4-bit g64 projections of a "
+                                   "Llama-3-8B-shaped layer", "M_per_gpu": M, "layers_per_step": L,
+                       "weights_bytes_per_step": L * (layer_bytes(0)), "l2": "inputs larger than L2 (%.0f MB of "
+                       "weights streamed per step)" % (L * layer_bytes(0) / 1e6), "parallelism": "batch-sharded x%d, "
+                       "weights replicated, no collective" % world},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": which, "frac_of_nominal_8TBs": achieved / 8000.0,
+                         "bytes_per_launch": layer_bytes(M) / 7.0, "kernel": "qmv_dense_kernel", "traffic": None},
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": xin.numel() * 2,
+                    "d2h_bytes_per_step": yout.numel() * 2, "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": args.steps * L * 7 * launches_per_call,
+            "clocks": clocks,
+        }
+        if sweep:
+            out["sweep_M"] = sweep
+        if not args.no_cpu_baseline:
+            tps, threads, sample, _ = cpu_layer_pass(M)
+            out["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

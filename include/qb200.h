@@ -1,0 +1,189 @@
+/*
+ * qb200.h -- C ABI of libqb200: MLX-format affine group-quantized inference
+ * operators for NVIDIA B200 (sm_100a).
+ *
+ * Every operator mirrors, argument for argument, the mlx-c entry point that
+ * mlx-serve binds in src/mlx.zig, so the Zig host code can call it in place of
+ * mlx-c for this path.  Differences that follow from leaving MLX's lazy graph:
+ *   - tensors are plain descriptors (device pointer, dtype, shape, element
+ *     strides) instead of refcounted mlx_array handles;
+ *   - results are caller-allocated: `res` must describe a buffer of the
+ *     operator's output shape and dtype (the `*_shape` helpers compute it);
+ *   - work is enqueued on the given cudaStream_t and is complete when the
+ *     stream is synchronised (MLX: when the graph is evaluated);
+ *   - status codes: 0 on success like mlx-c (src/mlx.zig:547-550), a
+ *     qb200_status value otherwise; the message goes to the error handler
+ *     (src/mlx.zig:396-397) and to qb200_last_error().
+ * Nothing here allocates or frees device memory.  No operator launches on
+ * invalid input, and none aborts the process.
+ *
+ * Packed layout (src/kv_quant.zig:102-106, tests/dsv4_imatrix.py:107-163):
+ *   value i of a row is in uint32 word i/(32/bits) at bit (i%(32/bits))*bits;
+ *   w = q*scale + bias, one bf16 (scale, bias) per group_size consecutive
+ *   values along the last axis.  W [..., rows, in*bits/32] uint32,
+ *   scales/biases [..., rows, in/group_size].
+ */
+#ifndef QB200_H
+#define QB200_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define QB200_API
+#else
+#define QB200_API __attribute__((visibility("default")))
+#endif
+
+#define QB200_MAX_DIMS 8
+
+/* Same numeric values as mlx_dtype (src/mlx.zig:20-35). */
+typedef enum qb200_dtype {
+  QB200_BOOL = 0,
+  QB200_UINT8 = 1,
+  QB200_UINT16 = 2,
+  QB200_UINT32 = 3,
+  QB200_UINT64 = 4,
+  QB200_INT8 = 5,
+  QB200_INT16 = 6,
+  QB200_INT32 = 7,
+  QB200_INT64 = 8,
+  QB200_FLOAT16 = 9,
+  QB200_FLOAT32 = 10,
+  QB200_FLOAT64 = 11,
+  QB200_BFLOAT16 = 12
+} qb200_dtype;
+
+typedef enum qb200_status {
+  QB200_OK = 0,
+  QB200_ERR_UNSUPPORTED = 1, /* valid request this library declines (caller falls through) */
+  QB200_ERR_BAD_SHAPE = 2,
+  QB200_ERR_BAD_STRIDE = 3,
+  QB200_ERR_BAD_DTYPE = 4,
+  QB200_ERR_BAD_ARG = 5,
+  QB200_ERR_CUDA = 6,
+  QB200_ERR_WORKSPACE = 7,
+  QB200_ERR_TIMEOUT = 8
+} qb200_status;
+
+/* Tensor descriptor.  `stride` is in ELEMENTS.  A tensor with data == NULL and
+ * ndim == 0 stands for mlx-c's empty handle (`mlx_array{ .ctx = null }`). */
+typedef struct qb200_tensor {
+  void* data;
+  int32_t dtype; /* qb200_dtype */
+  int32_t ndim;
+  int64_t shape[QB200_MAX_DIMS];
+  int64_t stride[QB200_MAX_DIMS];
+} qb200_tensor;
+
+/* mlx_optional_int / mlx_optional_dtype (src/mlx.zig:40-62, :313-316). */
+typedef struct qb200_optional_int {
+  int value;
+  bool has_value;
+} qb200_optional_int;
+typedef struct qb200_optional_dtype {
+  int value; /* qb200_dtype */
+  bool has_value;
+} qb200_optional_dtype;
+
+typedef void* qb200_stream; /* cudaStream_t */
+
+/* ---- error reporting (replaces mlx_set_error_handler, src/mlx.zig:396-397) ---- */
+typedef void (*qb200_error_handler_func)(const char* msg, void* data);
+QB200_API void qb200_set_error_handler(qb200_error_handler_func handler, void* data, void (*dtor)(void*));
+QB200_API const char* qb200_last_error(void); /* thread-local; "" when none */
+QB200_API const char* qb200_version(void);
+
+/* ---- mlx_quantized_matmul (src/mlx.zig:262) ----
+ * transpose_w = true : y[..., m, n] = sum_k x[..., m, k] * What[..., n, k]
+ *                      (w [..., N, K*bits/32], scales/biases [..., N, K/gs]);
+ * transpose_w = false: y[..., m, n] = sum_k x[..., m, k] * What[..., k, n]
+ *                      (w [..., K, N*bits/32], groups run along n;
+ *                      src/kv_quant.zig:657-660, :1038-1094).
+ * Leading dims of x and of (w, scales, biases) broadcast (src/kv_quant.zig:968-975).
+ * fp32 accumulate, res dtype == x dtype (bf16 or f32).  group_size defaults to
+ * 64 and bits to 4 when not given, as in MLX.  mode must be "affine". */
+QB200_API int qb200_quantized_matmul(qb200_tensor* res, const qb200_tensor* x, const qb200_tensor* w,
+                                     const qb200_tensor* scales, const qb200_tensor* biases, bool transpose_w,
+                                     qb200_optional_int group_size, qb200_optional_int bits, const char* mode,
+                                     qb200_stream s);
+/* Output shape of the call above: fills out_shape[0..*out_ndim). */
+QB200_API int qb200_quantized_matmul_shape(const qb200_tensor* x, const qb200_tensor* w, const qb200_tensor* scales,
+                                           bool transpose_w, qb200_optional_int group_size, qb200_optional_int bits,
+                                           int64_t* out_shape, int32_t* out_ndim);
+
+/* ---- mlx_gather_qmm (src/mlx.zig:265; caller src/transformer.zig:20763-20784) ----
+ * w [E, N, K*bits/32], scales/biases [E, N, K/gs]; x [*xb, M, K]; rhs_indices
+ * any int32/uint32/int64 tensor of shape I; lhs_indices empty or of shape I.
+ * res [*I, M, N]: res[i] = x[lhs(i)] . What[rhs[i]]^T, where lhs(i) is
+ * lhs_indices[i] into x's flattened batch dims, or, when lhs_indices is empty,
+ * the position obtained by broadcasting x's batch dims against I.
+ * sorted_indices is a performance hint and never changes values
+ * (src/transformer.zig:20772-20774).  transpose_w must be true (the only form
+ * the reference uses). */
+QB200_API int qb200_gather_qmm(qb200_tensor* res, const qb200_tensor* x, const qb200_tensor* w,
+                               const qb200_tensor* scales, const qb200_tensor* biases,
+                               const qb200_tensor* lhs_indices, const qb200_tensor* rhs_indices, bool transpose_w,
+                               qb200_optional_int group_size, qb200_optional_int bits, const char* mode,
+                               bool sorted_indices, qb200_stream s);
+
+/* ---- mlx_dequantize (src/mlx.zig:271; caller src/kv_quant.zig:407-430) ----
+ * res [..., in] = q*scale + bias, computed as a rounded fp32 product plus a
+ * rounded fp32 add, then cast to `dtype` (default: the dtype of scales).
+ * global_scale must be NULL/empty (non-affine modes are out of scope). */
+QB200_API int qb200_dequantize(qb200_tensor* res, const qb200_tensor* w, const qb200_tensor* scales,
+                               const qb200_tensor* biases, qb200_optional_int group_size, qb200_optional_int bits,
+                               const char* mode, const qb200_tensor* global_scale, qb200_optional_dtype dtype,
+                               qb200_stream s);
+
+/* ---- mlx_quantize (src/mlx.zig:275; caller src/kv_quant.zig:126-162) ----
+ * mlx-c returns the vector [q, scales, biases]; here the three results are
+ * separate caller-allocated tensors in that order.  w is bf16 or f32
+ * [..., D] with D % group_size == 0; scales/biases take w's dtype when w is
+ * bf16 and bf16 otherwise. */
+QB200_API int qb200_quantize(qb200_tensor* res_q, qb200_tensor* res_scales, qb200_tensor* res_biases,
+                             const qb200_tensor* w, qb200_optional_int group_size, qb200_optional_int bits,
+                             const char* mode, const qb200_tensor* global_scale, qb200_stream s);
+
+/* ---- decode attention read directly from the packed KV cache ----
+ * Replaces kv_quant.quantAttention (src/kv_quant.zig:478-488) and the packed
+ * decode kernel + merge (src/transformer.zig:5063-5070, :5204-5246) for
+ * T_q == 1, and extends them to a batch of sequences with per-sequence
+ * lengths, which the reference serves by dequantising, padding and masking
+ * (src/transformer.zig:9758-9792, :10216-10249).
+ *   q            [B, Hq, 1, D]  bf16 or f32
+ *   k_q/k_s/k_b  [B, Hkv, T, D*bits/32 | D/gs | D/gs]  strided cache views
+ *   v_q/v_s/v_b  [B, Hkv, T, Dv*bits/32 | Dv/gs | Dv/gs]
+ *   mask_mode    "" | "causal" (a no-op at T_q == 1) | "array"
+ *   mask_arr     additive row broadcastable to [B, 1, 1, T] in q's dtype or f32
+ *                ("array" only; empty otherwise)
+ *   kv_lens      empty, or int32 [B] on the device: positions >= kv_lens[b] are masked
+ *   res          [B, Hq, 1, Dv] in q's dtype
+ *   workspace    device scratch of at least qb200_kv_decode_attention_workspace_size bytes
+ */
+QB200_API int qb200_kv_decode_attention(qb200_tensor* res, const qb200_tensor* q, const qb200_tensor* k_q,
+                                        const qb200_tensor* k_scales, const qb200_tensor* k_biases,
+                                        const qb200_tensor* v_q, const qb200_tensor* v_scales,
+                                        const qb200_tensor* v_biases, int bits, int group_size, float scale,
+                                        const char* mask_mode, const qb200_tensor* mask_arr,
+                                        const qb200_tensor* kv_lens, void* workspace, size_t workspace_bytes,
+                                        qb200_stream s);
+QB200_API size_t qb200_kv_decode_attention_workspace_size(int64_t B, int64_t Hq, int64_t Hkv, int64_t T,
+                                                          int64_t Dv);
+
+/* ---- quantise new K/V rows into the cache in place ----
+ * Steps 2 and 5 of KVCache.updateAffine (src/transformer.zig:3224-3337):
+ * quantise dense [B, Hkv, S, D] and write the triple at token `offset` of the
+ * capacity buffers cache_q/cache_s/cache_b [B, Hkv, cap, *]. */
+QB200_API int qb200_kv_append(qb200_tensor* cache_q, qb200_tensor* cache_scales, qb200_tensor* cache_biases,
+                              const qb200_tensor* dense, int64_t offset, int bits, int group_size, qb200_stream s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QB200_H */

@@ -1,0 +1,591 @@
+// C ABI of libqb200: argument validation, shape inference and kernel dispatch.
+// Every entry point mirrors the mlx-c operator mlx-serve binds in src/mlx.zig
+// (see include/qb200.h for the line references).  Validation happens entirely
+// on the host before any CUDA call, so bad input never reaches a kernel.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "kernels.h"
+
+using namespace qb;
+
+namespace {
+
+thread_local std::string g_last_error;
+std::mutex g_handler_mu;
+qb200_error_handler_func g_handler = nullptr;
+void* g_handler_data = nullptr;
+void (*g_handler_dtor)(void*) = nullptr;
+
+int fail(int status, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  qb200_error_handler_func h;
+  void* d;
+  {
+    std::lock_guard<std::mutex> lk(g_handler_mu);
+    h = g_handler;
+    d = g_handler_data;
+  }
+  if (h) h(buf, d);
+  return status;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(QB200_ERR_CUDA, "%s: CUDA error %d (%s)", what, (int)e, cudaGetErrorString(e));
+}
+
+bool is_empty(const qb200_tensor* t) { return t == nullptr || (t->data == nullptr && t->ndim == 0); }
+
+int dtype_size(int dt) {
+  switch (dt) {
+    case QB200_BOOL: case QB200_UINT8: case QB200_INT8: return 1;
+    case QB200_UINT16: case QB200_INT16: case QB200_FLOAT16: case QB200_BFLOAT16: return 2;
+    case QB200_UINT32: case QB200_INT32: case QB200_FLOAT32: return 4;
+    case QB200_UINT64: case QB200_INT64: case QB200_FLOAT64: return 8;
+    default: return 0;
+  }
+}
+bool is_float_dtype(int dt) { return dt == QB200_BFLOAT16 || dt == QB200_FLOAT32 || dt == QB200_FLOAT16; }
+bool is_index_dtype(int dt) { return dt == QB200_INT32 || dt == QB200_UINT32 || dt == QB200_INT64; }
+
+// Basic descriptor sanity.  Returns 0 or a status (after recording the message).
+int check_tensor(const qb200_tensor* t, const char* name, int min_ndim) {
+  if (t == nullptr) return fail(QB200_ERR_BAD_ARG, "%s: null tensor", name);
+  if (t->ndim < min_ndim || t->ndim > QB200_MAX_DIMS)
+    return fail(QB200_ERR_BAD_SHAPE, "%s: ndim %d outside [%d, %d]", name, t->ndim, min_ndim, QB200_MAX_DIMS);
+  if (dtype_size(t->dtype) == 0) return fail(QB200_ERR_BAD_DTYPE, "%s: unknown dtype %d", name, t->dtype);
+  int64_t n = 1;
+  for (int d = 0; d < t->ndim; ++d) {
+    if (t->shape[d] < 0) return fail(QB200_ERR_BAD_SHAPE, "%s: negative extent in dim %d", name, d);
+    if (t->stride[d] < 0) return fail(QB200_ERR_BAD_STRIDE, "%s: negative stride in dim %d", name, d);
+    n *= t->shape[d];
+  }
+  if (n > 0 && t->data == nullptr) return fail(QB200_ERR_BAD_ARG, "%s: null data pointer", name);
+  if (t->ndim > 0 && t->shape[t->ndim - 1] > 1 && t->stride[t->ndim - 1] != 1)
+    return fail(QB200_ERR_BAD_STRIDE, "%s: last axis must be contiguous (stride %lld)", name,
+                (long long)t->stride[t->ndim - 1]);
+  return 0;
+}
+
+int64_t numel(const qb200_tensor* t) {
+  int64_t n = 1;
+  for (int d = 0; d < t->ndim; ++d) n *= t->shape[d];
+  return n;
+}
+
+bool fully_contiguous(const qb200_tensor* t) {
+  int64_t expect = 1;
+  for (int d = t->ndim - 1; d >= 0; --d) {
+    if (t->shape[d] != 1 && t->stride[d] != expect) return false;
+    expect *= t->shape[d];
+  }
+  return true;
+}
+
+int resolve_mode(const char* mode, qb200_optional_int group_size, qb200_optional_int bits, int* gs, int* nb) {
+  if (mode == nullptr || std::strcmp(mode, "affine") != 0)
+    return fail(QB200_ERR_UNSUPPORTED, "quantization mode '%s' is not served (only \"affine\")", mode ? mode : "(null)");
+  *gs = group_size.has_value ? group_size.value : 64;
+  *nb = bits.has_value ? bits.value : 4;
+  if (*nb != 2 && *nb != 4 && *nb != 8) return fail(QB200_ERR_UNSUPPORTED, "bits=%d is not served (2, 4, 8)", *nb);
+  if (*gs != 32 && *gs != 64 && *gs != 128)
+    return fail(QB200_ERR_UNSUPPORTED, "group_size=%d is not served (32, 64, 128)", *gs);
+  return 0;
+}
+
+// Rows of a tensor = all dims but the last.
+RowMap make_rowmap(const qb200_tensor* t) {
+  RowMap m;
+  m.nd = t->ndim - 1;
+  bool contig = true;
+  int64_t expect = t->ndim >= 2 ? t->stride[t->ndim - 2] : t->shape[t->ndim - 1];
+  m.row_pitch = expect;
+  for (int d = t->ndim - 2; d >= 0; --d) {
+    m.shape[d] = t->shape[d];
+    m.stride[d] = t->stride[d];
+    if (t->shape[d] != 1 && t->stride[d] != expect) contig = false;
+    expect *= t->shape[d];
+  }
+  for (int d = m.nd; d < kMaxLead; ++d) { m.shape[d] = 1; m.stride[d] = 0; }
+  if (m.nd == 0) m.row_pitch = 0;
+  m.contiguous = contig ? 1 : 0;
+  return m;
+}
+
+int64_t rows_of(const qb200_tensor* t) {
+  int64_t n = 1;
+  for (int d = 0; d < t->ndim - 1; ++d) n *= t->shape[d];
+  return n;
+}
+
+bool same_leading(const qb200_tensor* a, const qb200_tensor* b) {
+  if (a->ndim != b->ndim) return false;
+  for (int d = 0; d < a->ndim - 1; ++d)
+    if (a->shape[d] != b->shape[d]) return false;
+  return true;
+}
+bool same_strides(const qb200_tensor* a, const qb200_tensor* b) {
+  if (a->ndim != b->ndim) return false;
+  for (int d = 0; d < a->ndim; ++d)
+    if (a->shape[d] != 1 && a->stride[d] != b->stride[d]) return false;
+  return true;
+}
+
+struct QmmPlan {
+  int64_t M, N, K;
+  int nb;                     // batch dims
+  int64_t bshape[kMaxLead];
+  bool x_was_1d;
+};
+
+int plan_qmm(const qb200_tensor* x, const qb200_tensor* w, const qb200_tensor* scales, bool transpose, int gs,
+             int bits, QmmPlan* p) {
+  const int vpw = 32 / bits;
+  p->x_was_1d = x->ndim == 1;
+  const int xnd = x->ndim;
+  p->K = x->shape[xnd - 1];
+  p->M = p->x_was_1d ? 1 : x->shape[xnd - 2];
+  const int64_t wrows = w->shape[w->ndim - 2], wcols = w->shape[w->ndim - 1];
+  if (transpose) {
+    p->N = wrows;
+    if (wcols * vpw != p->K)
+      return fail(QB200_ERR_BAD_SHAPE, "quantized_matmul: x inner dim %lld != w cols %lld * %d", (long long)p->K,
+                  (long long)wcols, vpw);
+    if (p->K % gs != 0 || scales->shape[scales->ndim - 1] != p->K / gs)
+      return fail(QB200_ERR_BAD_SHAPE, "quantized_matmul: scales last dim %lld != K/group_size = %lld",
+                  (long long)scales->shape[scales->ndim - 1], (long long)(p->K / gs));
+  } else {
+    p->N = wcols * vpw;
+    if (wrows != p->K)
+      return fail(QB200_ERR_BAD_SHAPE, "quantized_matmul: x inner dim %lld != w rows %lld (transpose_w=false)",
+                  (long long)p->K, (long long)wrows);
+    if (p->N % gs != 0 || scales->shape[scales->ndim - 1] != p->N / gs)
+      return fail(QB200_ERR_BAD_SHAPE, "quantized_matmul: scales last dim %lld != N/group_size = %lld",
+                  (long long)scales->shape[scales->ndim - 1], (long long)(p->N / gs));
+  }
+  if (scales->shape[scales->ndim - 2] != wrows)
+    return fail(QB200_ERR_BAD_SHAPE, "quantized_matmul: scales rows %lld != w rows %lld",
+                (long long)scales->shape[scales->ndim - 2], (long long)wrows);
+  const int xb = p->x_was_1d ? 0 : xnd - 2, wb = w->ndim - 2;
+  p->nb = xb > wb ? xb : wb;
+  for (int d = 0; d < p->nb; ++d) {
+    const int xd = d - (p->nb - xb), wd = d - (p->nb - wb);
+    const int64_t xs = xd >= 0 ? x->shape[xd] : 1, ws = wd >= 0 ? w->shape[wd] : 1;
+    if (xs != ws && xs != 1 && ws != 1)
+      return fail(QB200_ERR_BAD_SHAPE, "quantized_matmul: batch dims do not broadcast (%lld vs %lld)", (long long)xs,
+                  (long long)ws);
+    p->bshape[d] = xs == 1 ? ws : xs;
+  }
+  return 0;
+}
+
+// Broadcast batch map of an operand whose last `inner` dims are the matrix.
+BatchMap make_batchmap(const qb200_tensor* t, int inner, const QmmPlan& p) {
+  BatchMap m;
+  m.nd = p.nb;
+  const int tb = t->ndim - inner;
+  for (int d = 0; d < kMaxLead; ++d) { m.shape[d] = 1; m.stride[d] = 0; }
+  for (int d = 0; d < p.nb; ++d) {
+    m.shape[d] = p.bshape[d];
+    const int td = d - (p.nb - tb);
+    m.stride[d] = (td >= 0 && t->shape[td] != 1) ? t->stride[td] : 0;
+  }
+  return m;
+}
+
+}  // namespace
+
+extern "C" {
+
+QB200_API void qb200_set_error_handler(qb200_error_handler_func handler, void* data, void (*dtor)(void*)) {
+  std::lock_guard<std::mutex> lk(g_handler_mu);
+  if (g_handler_dtor && g_handler_data) g_handler_dtor(g_handler_data);
+  g_handler = handler;
+  g_handler_data = data;
+  g_handler_dtor = dtor;
+}
+
+QB200_API const char* qb200_last_error(void) { return g_last_error.c_str(); }
+QB200_API const char* qb200_version(void) { return "qb200 0.1 (sm_100a)"; }
+
+QB200_API int qb200_quantized_matmul_shape(const qb200_tensor* x, const qb200_tensor* w, const qb200_tensor* scales,
+                                           bool transpose_w, qb200_optional_int group_size, qb200_optional_int bits,
+                                           int64_t* out_shape, int32_t* out_ndim) {
+  int gs, nb, st;
+  if ((st = resolve_mode("affine", group_size, bits, &gs, &nb))) return st;
+  if ((st = check_tensor(x, "x", 1)) || (st = check_tensor(w, "w", 2)) || (st = check_tensor(scales, "scales", 2)))
+    return st;
+  if (out_shape == nullptr || out_ndim == nullptr) return fail(QB200_ERR_BAD_ARG, "null output shape");
+  QmmPlan p;
+  if ((st = plan_qmm(x, w, scales, transpose_w, gs, nb, &p))) return st;
+  int n = 0;
+  for (int d = 0; d < p.nb; ++d) out_shape[n++] = p.bshape[d];
+  if (!p.x_was_1d) out_shape[n++] = p.M;
+  out_shape[n++] = p.N;
+  *out_ndim = n;
+  return QB200_OK;
+}
+
+QB200_API int qb200_quantized_matmul(qb200_tensor* res, const qb200_tensor* x, const qb200_tensor* w,
+                                     const qb200_tensor* scales, const qb200_tensor* biases, bool transpose_w,
+                                     qb200_optional_int group_size, qb200_optional_int bits, const char* mode,
+                                     qb200_stream s) {
+  int gs, nb, st;
+  if ((st = resolve_mode(mode, group_size, bits, &gs, &nb))) return st;
+  if (is_empty(biases)) return fail(QB200_ERR_UNSUPPORTED, "quantized_matmul: biases are required (affine mode)");
+  if ((st = check_tensor(res, "res", 1)) || (st = check_tensor(x, "x", 1)) || (st = check_tensor(w, "w", 2)) ||
+      (st = check_tensor(scales, "scales", 2)) || (st = check_tensor(biases, "biases", 2)))
+    return st;
+  if (w->dtype != QB200_UINT32) return fail(QB200_ERR_BAD_DTYPE, "quantized_matmul: w must be uint32");
+  if (!is_float_dtype(x->dtype)) return fail(QB200_ERR_BAD_DTYPE, "quantized_matmul: x must be bf16, f16 or f32");
+  if (scales->dtype != QB200_BFLOAT16 || biases->dtype != QB200_BFLOAT16)
+    return fail(QB200_ERR_UNSUPPORTED, "quantized_matmul: scales and biases must be bf16");
+  if (res->dtype != x->dtype) return fail(QB200_ERR_BAD_DTYPE, "quantized_matmul: res dtype must equal x dtype");
+  if (scales->ndim != w->ndim || !same_leading(scales, w) || !same_leading(biases, scales) ||
+      biases->shape[biases->ndim - 1] != scales->shape[scales->ndim - 1])
+    return fail(QB200_ERR_BAD_SHAPE, "quantized_matmul: w, scales and biases must share their leading shape");
+  if (!same_strides(scales, biases))
+    return fail(QB200_ERR_BAD_STRIDE, "quantized_matmul: scales and biases must have identical strides");
+  QmmPlan p;
+  if ((st = plan_qmm(x, w, scales, transpose_w, gs, nb, &p))) return st;
+  // expected result shape
+  int64_t eshape[QB200_MAX_DIMS];
+  int en = 0;
+  for (int d = 0; d < p.nb; ++d) eshape[en++] = p.bshape[d];
+  if (!p.x_was_1d) eshape[en++] = p.M;
+  eshape[en++] = p.N;
+  if (res->ndim != en) return fail(QB200_ERR_BAD_SHAPE, "quantized_matmul: res ndim %d, expected %d", res->ndim, en);
+  for (int d = 0; d < en; ++d)
+    if (res->shape[d] != eshape[d])
+      return fail(QB200_ERR_BAD_SHAPE, "quantized_matmul: res dim %d is %lld, expected %lld", d,
+                  (long long)res->shape[d], (long long)eshape[d]);
+
+  QmmArgs a;
+  a.x = x->data; a.w = (const uint32_t*)w->data; a.s = scales->data; a.b = biases->data; a.y = res->data;
+  a.x_dtype = x->dtype;
+  a.M = p.M; a.N = p.N; a.K = p.K;
+  a.ldx = p.x_was_1d ? p.K : x->stride[x->ndim - 2];
+  a.ldw = w->stride[w->ndim - 2];
+  a.lds = scales->stride[scales->ndim - 2];
+  a.ldy = p.x_was_1d ? p.N : res->stride[res->ndim - 2];
+  a.gs = gs; a.bits = nb; a.transpose = transpose_w;
+  a.nbatch = 1;
+  for (int d = 0; d < p.nb; ++d) a.nbatch *= p.bshape[d];
+  a.xb = make_batchmap(x, p.x_was_1d ? 1 : 2, p);
+  a.wb = make_batchmap(w, 2, p);
+  a.sb = make_batchmap(scales, 2, p);
+  a.yb = make_batchmap(res, p.x_was_1d ? 1 : 2, p);
+  if (a.M == 0 || a.N == 0 || a.nbatch == 0) return QB200_OK;
+  if (a.K == 0) return fail(QB200_ERR_BAD_SHAPE, "quantized_matmul: empty contraction axis");
+  cudaError_t e;
+  if (qmv_mma_supported(a)) e = launch_qmv_mma(a, (cudaStream_t)s);
+  else e = launch_qmm_generic(a, (cudaStream_t)s);
+  if (e != cudaSuccess) return cuda_fail(e, "quantized_matmul");
+  return QB200_OK;
+}
+
+QB200_API int qb200_gather_qmm(qb200_tensor* res, const qb200_tensor* x, const qb200_tensor* w,
+                               const qb200_tensor* scales, const qb200_tensor* biases,
+                               const qb200_tensor* lhs_indices, const qb200_tensor* rhs_indices, bool transpose_w,
+                               qb200_optional_int group_size, qb200_optional_int bits, const char* mode,
+                               bool sorted_indices, qb200_stream s) {
+  int gs, nb, st;
+  if ((st = resolve_mode(mode, group_size, bits, &gs, &nb))) return st;
+  if (!transpose_w) return fail(QB200_ERR_UNSUPPORTED, "gather_qmm: only transpose_w=true is served");
+  if (is_empty(biases)) return fail(QB200_ERR_UNSUPPORTED, "gather_qmm: biases are required (affine mode)");
+  if (is_empty(rhs_indices)) return fail(QB200_ERR_UNSUPPORTED, "gather_qmm: rhs_indices are required");
+  if ((st = check_tensor(res, "res", 2)) || (st = check_tensor(x, "x", 2)) || (st = check_tensor(w, "w", 3)) ||
+      (st = check_tensor(scales, "scales", 3)) || (st = check_tensor(biases, "biases", 3)) ||
+      (st = check_tensor(rhs_indices, "rhs_indices", 0)))
+    return st;
+  if (w->ndim != 3 || scales->ndim != 3 || biases->ndim != 3)
+    return fail(QB200_ERR_UNSUPPORTED, "gather_qmm: w, scales, biases must be [E, N, *]");
+  if (w->dtype != QB200_UINT32) return fail(QB200_ERR_BAD_DTYPE, "gather_qmm: w must be uint32");
+  if (!is_float_dtype(x->dtype)) return fail(QB200_ERR_BAD_DTYPE, "gather_qmm: x must be bf16, f16 or f32");
+  if (scales->dtype != QB200_BFLOAT16 || biases->dtype != QB200_BFLOAT16)
+    return fail(QB200_ERR_UNSUPPORTED, "gather_qmm: scales and biases must be bf16");
+  if (res->dtype != x->dtype) return fail(QB200_ERR_BAD_DTYPE, "gather_qmm: res dtype must equal x dtype");
+  if (!is_index_dtype(rhs_indices->dtype)) return fail(QB200_ERR_BAD_DTYPE, "gather_qmm: rhs_indices must be int32/uint32/int64");
+  // Operands reaching gather_qmm must be row-contiguous (mlx-serve docs/gotchas/engine-mlx.md:16-20);
+  // non-contiguous ones are rejected instead of being read wrongly.
+  if (!fully_contiguous(w) || !fully_contiguous(scales) || !fully_contiguous(biases))
+    return fail(QB200_ERR_BAD_STRIDE, "gather_qmm: w, scales and biases must be contiguous");
+  if (!fully_contiguous(x) || !fully_contiguous(res) || !fully_contiguous(rhs_indices))
+    return fail(QB200_ERR_BAD_STRIDE, "gather_qmm: x, res and indices must be contiguous");
+  const int vpw = 32 / nb;
+  const int64_t E = w->shape[0], N = w->shape[1], K = w->shape[2] * vpw;
+  const int64_t M = x->shape[x->ndim - 2];
+  if (x->shape[x->ndim - 1] != K)
+    return fail(QB200_ERR_BAD_SHAPE, "gather_qmm: x inner dim %lld != w cols %lld * %d",
+                (long long)x->shape[x->ndim - 1], (long long)w->shape[2], vpw);
+  if (K % gs != 0 || scales->shape[0] != E || scales->shape[1] != N || scales->shape[2] != K / gs ||
+      biases->shape[0] != E || biases->shape[1] != N || biases->shape[2] != K / gs)
+    return fail(QB200_ERR_BAD_SHAPE, "gather_qmm: scales/biases must be [E, N, K/group_size]");
+  const int ind = rhs_indices->ndim;
+  if (ind + 2 > QB200_MAX_DIMS) return fail(QB200_ERR_BAD_SHAPE, "gather_qmm: too many index dims");
+  if (res->ndim != ind + 2) return fail(QB200_ERR_BAD_SHAPE, "gather_qmm: res ndim %d, expected %d", res->ndim, ind + 2);
+  for (int d = 0; d < ind; ++d)
+    if (res->shape[d] != rhs_indices->shape[d])
+      return fail(QB200_ERR_BAD_SHAPE, "gather_qmm: res dim %d != index dim", d);
+  if (res->shape[ind] != M || res->shape[ind + 1] != N)
+    return fail(QB200_ERR_BAD_SHAPE, "gather_qmm: res inner dims must be [M=%lld, N=%lld]", (long long)M, (long long)N);
+
+  GatherArgs a;
+  a.x = x->data; a.w = (const uint32_t*)w->data; a.s = scales->data; a.b = biases->data; a.y = res->data;
+  a.x_dtype = x->dtype;
+  a.I = numel(rhs_indices);
+  a.M = M; a.N = N; a.K = K;
+  a.x_batch_stride = M * K;
+  a.XB = 1;
+  for (int d = 0; d < x->ndim - 2; ++d) a.XB *= x->shape[d];
+  a.w_expert_stride = N * w->shape[2];
+  a.s_expert_stride = N * (K / gs);
+  a.E = E;
+  a.rhs = rhs_indices->data; a.rhs_dtype = rhs_indices->dtype;
+  a.lhs = nullptr; a.lhs_dtype = QB200_INT32;
+  a.xbcast.nd = ind;
+  for (int d = 0; d < kMaxLead; ++d) { a.xbcast.shape[d] = 1; a.xbcast.stride[d] = 0; }
+  if (!is_empty(lhs_indices)) {
+    if ((st = check_tensor(lhs_indices, "lhs_indices", 0))) return st;
+    if (!is_index_dtype(lhs_indices->dtype)) return fail(QB200_ERR_BAD_DTYPE, "gather_qmm: lhs_indices must be int32/uint32/int64");
+    if (lhs_indices->ndim != ind || !fully_contiguous(lhs_indices))
+      return fail(QB200_ERR_BAD_SHAPE, "gather_qmm: lhs_indices must match rhs_indices and be contiguous");
+    for (int d = 0; d < ind; ++d)
+      if (lhs_indices->shape[d] != rhs_indices->shape[d])
+        return fail(QB200_ERR_BAD_SHAPE, "gather_qmm: lhs_indices shape != rhs_indices shape");
+    a.lhs = lhs_indices->data; a.lhs_dtype = lhs_indices->dtype;
+  } else {
+    // broadcast x's batch dims against the index shape
+    const int xbn = x->ndim - 2;
+    if (xbn > ind) return fail(QB200_ERR_BAD_SHAPE, "gather_qmm: x has more batch dims than the indices");
+    int64_t run = 1;
+    for (int d = ind - 1; d >= 0; --d) {
+      const int xd = d - (ind - xbn);
+      const int64_t xs = xd >= 0 ? x->shape[xd] : 1;
+      a.xbcast.shape[d] = rhs_indices->shape[d];
+      if (xs == 1) a.xbcast.stride[d] = 0;
+      else if (xs == rhs_indices->shape[d]) { a.xbcast.stride[d] = run; }
+      else return fail(QB200_ERR_BAD_SHAPE, "gather_qmm: x batch dim %lld does not broadcast against index dim %lld",
+                       (long long)xs, (long long)rhs_indices->shape[d]);
+      run *= xs;
+    }
+  }
+  a.gs = gs; a.bits = nb; a.sorted = sorted_indices;
+  if (a.I == 0 || M == 0 || N == 0) return QB200_OK;
+  if (K == 0) return fail(QB200_ERR_BAD_SHAPE, "gather_qmm: empty contraction axis");
+  cudaError_t e;
+  if (gather_mma_supported(a)) e = launch_gather_mma(a, (cudaStream_t)s);
+  else e = launch_gather_generic(a, (cudaStream_t)s);
+  if (e != cudaSuccess) return cuda_fail(e, "gather_qmm");
+  return QB200_OK;
+}
+
+QB200_API int qb200_dequantize(qb200_tensor* res, const qb200_tensor* w, const qb200_tensor* scales,
+                               const qb200_tensor* biases, qb200_optional_int group_size, qb200_optional_int bits,
+                               const char* mode, const qb200_tensor* global_scale, qb200_optional_dtype dtype,
+                               qb200_stream s) {
+  int gs, nb, st;
+  if ((st = resolve_mode(mode, group_size, bits, &gs, &nb))) return st;
+  if (!is_empty(global_scale)) return fail(QB200_ERR_UNSUPPORTED, "dequantize: global_scale belongs to non-affine modes");
+  if (is_empty(biases)) return fail(QB200_ERR_UNSUPPORTED, "dequantize: biases are required (affine mode)");
+  if ((st = check_tensor(res, "res", 1)) || (st = check_tensor(w, "w", 1)) || (st = check_tensor(scales, "scales", 1)) ||
+      (st = check_tensor(biases, "biases", 1)))
+    return st;
+  if (w->dtype != QB200_UINT32) return fail(QB200_ERR_BAD_DTYPE, "dequantize: w must be uint32");
+  if (!is_float_dtype(scales->dtype) || biases->dtype != scales->dtype)
+    return fail(QB200_ERR_BAD_DTYPE, "dequantize: scales/biases must share a float dtype");
+  const int out_dt = dtype.has_value ? dtype.value : scales->dtype;
+  if (!is_float_dtype(out_dt)) return fail(QB200_ERR_BAD_DTYPE, "dequantize: output dtype %d is not served", out_dt);
+  if (res->dtype != out_dt) return fail(QB200_ERR_BAD_DTYPE, "dequantize: res dtype %d != requested %d", res->dtype, out_dt);
+  const int64_t d = w->shape[w->ndim - 1] * (32 / nb);
+  if (d % gs != 0 || scales->shape[scales->ndim - 1] != d / gs)
+    return fail(QB200_ERR_BAD_SHAPE, "dequantize: scales last dim %lld != %lld / group_size",
+                (long long)scales->shape[scales->ndim - 1], (long long)d);
+  if (!same_leading(w, scales) || !same_leading(scales, biases) || !same_leading(w, res) ||
+      biases->shape[biases->ndim - 1] != scales->shape[scales->ndim - 1] || res->shape[res->ndim - 1] != d)
+    return fail(QB200_ERR_BAD_SHAPE, "dequantize: w/scales/biases/res shapes disagree");
+  if (!same_strides(scales, biases)) return fail(QB200_ERR_BAD_STRIDE, "dequantize: scales and biases must have identical strides");
+  DequantArgs a;
+  a.w = (const uint32_t*)w->data; a.s = scales->data; a.b = biases->data; a.out = res->data;
+  a.wmap = make_rowmap(w); a.sbmap = make_rowmap(scales); a.omap = make_rowmap(res);
+  a.rows = rows_of(w); a.d = d; a.gs = gs; a.bits = nb;
+  a.sb_dtype = scales->dtype; a.out_dtype = out_dt;
+  if (a.rows * d == 0) return QB200_OK;
+  cudaError_t e = launch_dequantize(a, (cudaStream_t)s);
+  if (e != cudaSuccess) return cuda_fail(e, "dequantize");
+  return QB200_OK;
+}
+
+static int quantize_impl(qb200_tensor* res_q, qb200_tensor* res_scales, qb200_tensor* res_biases, const qb200_tensor* w,
+                         int gs, int nb, qb200_stream s, const char* who) {
+  int st;
+  if ((st = check_tensor(res_q, "res_q", 1)) || (st = check_tensor(res_scales, "res_scales", 1)) ||
+      (st = check_tensor(res_biases, "res_biases", 1)) || (st = check_tensor(w, "w", 1)))
+    return st;
+  if (!is_float_dtype(w->dtype)) return fail(QB200_ERR_BAD_DTYPE, "%s: input must be bf16, f16 or f32", who);
+  if (res_q->dtype != QB200_UINT32) return fail(QB200_ERR_BAD_DTYPE, "%s: packed output must be uint32", who);
+  if (!is_float_dtype(res_scales->dtype) || res_biases->dtype != res_scales->dtype)
+    return fail(QB200_ERR_BAD_DTYPE, "%s: scales/biases must share a float dtype", who);
+  const int64_t d = w->shape[w->ndim - 1];
+  if (d % gs != 0) return fail(QB200_ERR_BAD_SHAPE, "%s: last dim %lld is not a multiple of group_size %d", who, (long long)d, gs);
+  if (!same_leading(w, res_q) || !same_leading(w, res_scales) || !same_leading(w, res_biases) ||
+      res_q->shape[res_q->ndim - 1] != d * nb / 32 || res_scales->shape[res_scales->ndim - 1] != d / gs ||
+      res_biases->shape[res_biases->ndim - 1] != d / gs)
+    return fail(QB200_ERR_BAD_SHAPE, "%s: outputs must be [..., D*bits/32] and [..., D/group_size]", who);
+  if (!same_strides(res_scales, res_biases)) return fail(QB200_ERR_BAD_STRIDE, "%s: scales and biases must have identical strides", who);
+  QuantArgs a;
+  a.x = w->data; a.q = (uint32_t*)res_q->data; a.s = res_scales->data; a.b = res_biases->data;
+  a.xmap = make_rowmap(w); a.qmap = make_rowmap(res_q); a.sbmap = make_rowmap(res_scales);
+  a.rows = rows_of(w); a.d = d; a.gs = gs; a.bits = nb;
+  a.x_dtype = w->dtype; a.sb_dtype = res_scales->dtype;
+  if (a.rows * d == 0) return QB200_OK;
+  cudaError_t e = launch_quantize(a, (cudaStream_t)s);
+  if (e != cudaSuccess) return cuda_fail(e, who);
+  return QB200_OK;
+}
+
+QB200_API int qb200_quantize(qb200_tensor* res_q, qb200_tensor* res_scales, qb200_tensor* res_biases,
+                             const qb200_tensor* w, qb200_optional_int group_size, qb200_optional_int bits,
+                             const char* mode, const qb200_tensor* global_scale, qb200_stream s) {
+  int gs, nb, st;
+  if ((st = resolve_mode(mode, group_size, bits, &gs, &nb))) return st;
+  if (!is_empty(global_scale)) return fail(QB200_ERR_UNSUPPORTED, "quantize: global_scale belongs to non-affine modes");
+  return quantize_impl(res_q, res_scales, res_biases, w, gs, nb, s, "quantize");
+}
+
+QB200_API int qb200_kv_append(qb200_tensor* cache_q, qb200_tensor* cache_scales, qb200_tensor* cache_biases,
+                              const qb200_tensor* dense, int64_t offset, int bits, int group_size, qb200_stream s) {
+  int gs, nb, st;
+  qb200_optional_int og = {group_size, true}, ob = {bits, true};
+  if ((st = resolve_mode("affine", og, ob, &gs, &nb))) return st;
+  if ((st = check_tensor(cache_q, "cache_q", 4)) || (st = check_tensor(cache_scales, "cache_scales", 4)) ||
+      (st = check_tensor(cache_biases, "cache_biases", 4)) || (st = check_tensor(dense, "dense", 4)))
+    return st;
+  if (cache_q->ndim != 4 || cache_scales->ndim != 4 || cache_biases->ndim != 4 || dense->ndim != 4)
+    return fail(QB200_ERR_BAD_SHAPE, "kv_append: tensors must be [B, Hkv, tokens, last]");
+  const int64_t S = dense->shape[2], cap = cache_q->shape[2];
+  if (offset < 0 || offset + S > cap || cache_scales->shape[2] != cap || cache_biases->shape[2] != cap)
+    return fail(QB200_ERR_BAD_SHAPE, "kv_append: offset %lld + %lld tokens exceeds capacity %lld", (long long)offset,
+                (long long)S, (long long)cap);
+  qb200_tensor vq = *cache_q, vs = *cache_scales, vb = *cache_biases;
+  vq.shape[2] = vs.shape[2] = vb.shape[2] = S;
+  vq.data = (char*)cache_q->data + offset * cache_q->stride[2] * 4;
+  vs.data = (char*)cache_scales->data + offset * cache_scales->stride[2] * dtype_size(cache_scales->dtype);
+  vb.data = (char*)cache_biases->data + offset * cache_biases->stride[2] * dtype_size(cache_biases->dtype);
+  return quantize_impl(&vq, &vs, &vb, dense, gs, nb, s, "kv_append");
+}
+
+QB200_API size_t qb200_kv_decode_attention_workspace_size(int64_t B, int64_t Hq, int64_t Hkv, int64_t T, int64_t Dv) {
+  return kv_attn_workspace_bytes(B, Hq, Hkv, T, Dv);
+}
+
+QB200_API int qb200_kv_decode_attention(qb200_tensor* res, const qb200_tensor* q, const qb200_tensor* k_q,
+                                        const qb200_tensor* k_scales, const qb200_tensor* k_biases,
+                                        const qb200_tensor* v_q, const qb200_tensor* v_scales,
+                                        const qb200_tensor* v_biases, int bits, int group_size, float scale,
+                                        const char* mask_mode, const qb200_tensor* mask_arr,
+                                        const qb200_tensor* kv_lens, void* workspace, size_t workspace_bytes,
+                                        qb200_stream s) {
+  int gs, nb, st;
+  qb200_optional_int og = {group_size, true}, ob = {bits, true};
+  if ((st = resolve_mode("affine", og, ob, &gs, &nb))) return st;
+  if (nb == 2) return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention: bits must be 4 or 8");
+  const qb200_tensor* ts[8] = {res, q, k_q, k_scales, k_biases, v_q, v_scales, v_biases};
+  const char* names[8] = {"res", "q", "k_q", "k_scales", "k_biases", "v_q", "v_scales", "v_biases"};
+  for (int i = 0; i < 8; ++i) {
+    if ((st = check_tensor(ts[i], names[i], 4))) return st;
+    if (ts[i]->ndim != 4) return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: %s must be 4-D", names[i]);
+  }
+  if (q->dtype != QB200_BFLOAT16 && q->dtype != QB200_FLOAT32)
+    return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention: q must be bf16 or f32");
+  if (res->dtype != q->dtype) return fail(QB200_ERR_BAD_DTYPE, "kv_decode_attention: res dtype must equal q dtype");
+  if (k_q->dtype != QB200_UINT32 || v_q->dtype != QB200_UINT32)
+    return fail(QB200_ERR_BAD_DTYPE, "kv_decode_attention: packed K/V must be uint32");
+  if (k_scales->dtype != QB200_BFLOAT16 || k_biases->dtype != QB200_BFLOAT16 || v_scales->dtype != QB200_BFLOAT16 ||
+      v_biases->dtype != QB200_BFLOAT16)
+    return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention: scales and biases must be bf16");
+  const int64_t B = q->shape[0], Hq = q->shape[1], Tq = q->shape[2], D = q->shape[3];
+  const int64_t Hkv = k_q->shape[1], T = k_q->shape[2];
+  const int vpw = 32 / nb;
+  const int64_t Dk = k_q->shape[3] * vpw, Dv = v_q->shape[3] * vpw;
+  // Decode width only, as qkvAttnDecodeKernel (mlx-serve src/transformer.zig:5077); wider queries are declined.
+  if (Tq != 1) return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention: T_q=%lld (only decode width 1 is served)", (long long)Tq);
+  if (Dk != D) return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: q head dim %lld != K head dim %lld", (long long)D, (long long)Dk);
+  if (Hkv <= 0 || Hq % Hkv != 0) return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: Hq %lld not a multiple of Hkv %lld", (long long)Hq, (long long)Hkv);
+  if (D % gs != 0 || Dv % gs != 0) return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: head dims must be multiples of group_size");
+  const int64_t kshape[4] = {B, Hkv, T, 0};
+  for (int i = 2; i < 8; ++i)
+    for (int d = 0; d < 3; ++d)
+      if (ts[i]->shape[d] != kshape[d])
+        return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: %s dim %d is %lld, expected %lld", names[i], d,
+                    (long long)ts[i]->shape[d], (long long)kshape[d]);
+  if (k_scales->shape[3] != D / gs || k_biases->shape[3] != D / gs || v_scales->shape[3] != Dv / gs ||
+      v_biases->shape[3] != Dv / gs)
+    return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: scales/biases last dim must be D/group_size");
+  if (!same_strides(k_scales, k_biases) || !same_strides(v_scales, v_biases))
+    return fail(QB200_ERR_BAD_STRIDE, "kv_decode_attention: scales and biases must have identical strides");
+  if (res->shape[0] != B || res->shape[1] != Hq || res->shape[2] != 1 || res->shape[3] != Dv)
+    return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: res must be [B, Hq, 1, Dv]");
+
+  KvAttnArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.q = q->data; a.out = res->data; a.q_dtype = q->dtype;
+  a.kq = (const uint32_t*)k_q->data; a.ks = k_scales->data; a.kb = k_biases->data;
+  a.vq = (const uint32_t*)v_q->data; a.vs = v_scales->data; a.vb = v_biases->data;
+  a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.T = T; a.D = D; a.Dv = Dv;
+  a.q_str[0] = q->stride[0]; a.q_str[1] = q->stride[1];
+  a.o_str[0] = res->stride[0]; a.o_str[1] = res->stride[1];
+  for (int d = 0; d < 3; ++d) {
+    a.kq_str[d] = k_q->stride[d]; a.ksb_str[d] = k_scales->stride[d];
+    a.vq_str[d] = v_q->stride[d]; a.vsb_str[d] = v_scales->stride[d];
+  }
+  a.gs = gs; a.bits = nb; a.scale = scale;
+  const char* mm = mask_mode ? mask_mode : "";
+  if (std::strcmp(mm, "array") == 0) {
+    if (is_empty(mask_arr)) return fail(QB200_ERR_BAD_ARG, "kv_decode_attention: mask_mode \"array\" needs mask_arr");
+    if ((st = check_tensor(mask_arr, "mask_arr", 1))) return st;
+    if (mask_arr->dtype != q->dtype && mask_arr->dtype != QB200_FLOAT32)
+      return fail(QB200_ERR_BAD_DTYPE, "kv_decode_attention: mask must be q's dtype or f32");
+    if (mask_arr->shape[mask_arr->ndim - 1] != T)
+      return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: mask last dim %lld != T %lld",
+                  (long long)mask_arr->shape[mask_arr->ndim - 1], (long long)T);
+    // additive row broadcastable to [B, 1, 1, T]: every dim but the last (and an optional batch dim) is 1
+    int64_t bstride = 0;
+    for (int d = 0; d < mask_arr->ndim - 1; ++d) {
+      if (mask_arr->shape[d] == 1) continue;
+      if (d == mask_arr->ndim - 4 && mask_arr->shape[d] == B) { bstride = mask_arr->stride[d]; continue; }
+      if (mask_arr->ndim < 4 && d == 0 && mask_arr->shape[d] == B && mask_arr->ndim == 2) { bstride = mask_arr->stride[d]; continue; }
+      return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention: mask must broadcast as [B|1, 1, 1, T]");
+    }
+    a.mask = mask_arr->data; a.mask_dtype = mask_arr->dtype; a.mask_bstride = bstride;
+  } else if (std::strcmp(mm, "") != 0 && std::strcmp(mm, "causal") != 0) {
+    return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention: mask_mode '%s' is not served", mm);
+  }
+  if (!is_empty(kv_lens)) {
+    if ((st = check_tensor(kv_lens, "kv_lens", 1))) return st;
+    if (kv_lens->dtype != QB200_INT32 || kv_lens->ndim != 1 || kv_lens->shape[0] != B)
+      return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: kv_lens must be int32 [B]");
+    a.kv_lens = (const int32_t*)kv_lens->data;
+  }
+  a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+  if (B == 0 || Hq == 0 || Dv == 0) return QB200_OK;
+  if (!kv_attn_supported(a))
+    return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention: geometry not served (D=%lld Dv=%lld gs=%d gqa=%lld)",
+                (long long)D, (long long)Dv, gs, (long long)(Hq / Hkv));
+  const size_t need = kv_attn_workspace_bytes(B, Hq, Hkv, T, Dv);
+  if (need > 0 && (workspace == nullptr || workspace_bytes < need))
+    return fail(QB200_ERR_WORKSPACE, "kv_decode_attention: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  cudaError_t e = launch_kv_attn(a, (cudaStream_t)s);
+  if (e != cudaSuccess) return cuda_fail(e, "kv_decode_attention");
+  return QB200_OK;
+}
+
+}  // extern "C"

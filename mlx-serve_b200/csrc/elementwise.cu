@@ -1,0 +1,180 @@
+// dequantize / quantize kernels (bit-exact against the CPU oracle).
+//
+// dequantize mirrors mlx_dequantize as used by kv_quant.dequantizeAffine
+// (mlx-serve src/kv_quant.zig:407-430): w = q*scale + bias with a rounded fp32
+// product and a rounded fp32 add (no FMA contraction), then one cast.
+// quantize mirrors mlx_quantize as used by kv_quant.quantizeAffine
+// (src/kv_quant.zig:126-162); the scale/bias rule is the one restated in
+// tests/dsv4_imatrix.py:169-183 and the codes follow :264.
+#include "kernels.h"
+
+namespace qb {
+
+namespace {
+
+template <typename T> struct DT;
+template <> struct DT<float> { static constexpr int v = QB200_FLOAT32; };
+template <> struct DT<__nv_bfloat16> { static constexpr int v = QB200_BFLOAT16; };
+template <> struct DT<__half> { static constexpr int v = QB200_FLOAT16; };
+
+template <int BITS, typename ST, typename OT>
+__global__ void __launch_bounds__(256) dequant_kernel(DequantArgs a, int64_t words_per_row, int64_t total_words) {
+  constexpr int VPW = 32 / BITS;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total_words) return;
+  const int64_t row = idx / words_per_row;
+  const int64_t wi = idx - row * words_per_row;
+  const uint32_t word = a.w[a.wmap.offset(row) + wi];
+  const int64_t g = (wi * VPW) / a.gs;
+  const int64_t sboff = a.sbmap.offset(row) + g;
+  const float sc = IO<ST>::load(a.s, sboff);
+  const float bi = IO<ST>::load(a.b, sboff);
+  const int64_t obase = a.omap.offset(row) + wi * VPW;
+  float v[VPW];
+#pragma unroll
+  for (int k = 0; k < VPW; ++k) {
+    const float q = (float)((word >> (k * BITS)) & ((1u << BITS) - 1u));
+    v[k] = __fadd_rn(__fmul_rn(q, sc), bi);
+  }
+  if constexpr (sizeof(OT) == 2 && VPW % 2 == 0) {
+    // packed 16-bit stores when the destination is suitably aligned
+    OT* op = (OT*)a.out + obase;
+    if ((((uintptr_t)op) & (VPW * 2 - 1)) == 0) {
+      uint32_t pk[VPW / 2];
+#pragma unroll
+      for (int k = 0; k < VPW / 2; ++k) {
+        OT lo, hi;
+        if constexpr (DT<OT>::v == QB200_BFLOAT16) { lo = __float2bfloat16_rn(v[2 * k]); hi = __float2bfloat16_rn(v[2 * k + 1]); }
+        else { lo = __float2half_rn(v[2 * k]); hi = __float2half_rn(v[2 * k + 1]); }
+        pk[k] = (uint32_t)(*(uint16_t*)&lo) | ((uint32_t)(*(uint16_t*)&hi) << 16);
+      }
+      if constexpr (VPW == 8) *(uint4*)op = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      else if constexpr (VPW == 4) *(uint2*)op = make_uint2(pk[0], pk[1]);
+      else {
+#pragma unroll
+        for (int k = 0; k < VPW / 2; ++k) ((uint32_t*)op)[k] = pk[k];
+      }
+      return;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VPW; ++k) IO<OT>::store(a.out, obase + k, v[k]);
+}
+
+template <int BITS, typename ST>
+cudaError_t dequant_dispatch_out(const DequantArgs& a, cudaStream_t st) {
+  const int64_t wpr = a.d * BITS / 32;
+  const int64_t total = a.rows * wpr;
+  if (total == 0) return cudaSuccess;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  switch (a.out_dtype) {
+    case QB200_BFLOAT16: dequant_kernel<BITS, ST, __nv_bfloat16><<<blocks, 256, 0, st>>>(a, wpr, total); break;
+    case QB200_FLOAT32: dequant_kernel<BITS, ST, float><<<blocks, 256, 0, st>>>(a, wpr, total); break;
+    case QB200_FLOAT16: dequant_kernel<BITS, ST, __half><<<blocks, 256, 0, st>>>(a, wpr, total); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+template <int BITS>
+cudaError_t dequant_dispatch_sb(const DequantArgs& a, cudaStream_t st) {
+  switch (a.sb_dtype) {
+    case QB200_BFLOAT16: return dequant_dispatch_out<BITS, __nv_bfloat16>(a, st);
+    case QB200_FLOAT32: return dequant_dispatch_out<BITS, float>(a, st);
+    case QB200_FLOAT16: return dequant_dispatch_out<BITS, __half>(a, st);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+// One thread per packed output word; the gs/VPW threads of a group are
+// consecutive lanes of one warp and share min/max through shuffles.
+template <int BITS, typename XT, typename ST>
+__global__ void __launch_bounds__(256) quant_kernel(QuantArgs a, int64_t words_per_row, int64_t total_words) {
+  constexpr int VPW = 32 / BITS;
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = idx < total_words;
+  if (!live) idx = total_words - 1;  // keep the warp converged for the shuffles
+  const int64_t row = idx / words_per_row;
+  const int64_t wi = idx - row * words_per_row;
+  const int64_t xbase = a.xmap.offset(row) + wi * VPW;
+  float v[VPW];
+#pragma unroll
+  for (int k = 0; k < VPW; ++k) v[k] = IO<XT>::load(a.x, xbase + k);
+  float xmin = v[0], xmax = v[0];
+#pragma unroll
+  for (int k = 1; k < VPW; ++k) { xmin = fminf(xmin, v[k]); xmax = fmaxf(xmax, v[k]); }
+  const int tpg = a.gs / VPW;  // threads per group: power of two, <= 32
+  for (int off = tpg >> 1; off > 0; off >>= 1) {
+    xmin = fminf(xmin, __shfl_xor_sync(0xffffffffu, xmin, off));
+    xmax = fmaxf(xmax, __shfl_xor_sync(0xffffffffu, xmax, off));
+  }
+  const float n_bins = (float)((1 << BITS) - 1);
+  const bool mask = fabsf(xmin) > fabsf(xmax);
+  float scale = fmaxf(__fdiv_rn(__fsub_rn(xmax, xmin), n_bins), 1e-7f);
+  scale = mask ? scale : -scale;
+  const float edge = mask ? xmin : xmax;
+  const float q0 = rintf(__fdiv_rn(edge, scale));
+  float bias = 0.0f;
+  if (q0 != 0.0f) { scale = __fdiv_rn(edge, q0); bias = edge; }
+  uint32_t word = 0;
+#pragma unroll
+  for (int k = 0; k < VPW; ++k) {
+    float c = rintf(__fdiv_rn(__fsub_rn(v[k], bias), scale));
+    c = fminf(fmaxf(c, 0.0f), n_bins);
+    word |= ((uint32_t)c) << (k * BITS);
+  }
+  if (!live) return;
+  a.q[a.qmap.offset(row) + wi] = word;
+  if ((wi % tpg) == 0) {
+    const int64_t sboff = a.sbmap.offset(row) + (wi * VPW) / a.gs;
+    IO<ST>::store(a.s, sboff, scale);
+    IO<ST>::store(a.b, sboff, bias);
+  }
+}
+
+template <int BITS, typename XT>
+cudaError_t quant_dispatch_sb(const QuantArgs& a, cudaStream_t st) {
+  const int64_t wpr = a.d * BITS / 32;
+  const int64_t total = a.rows * wpr;
+  if (total == 0) return cudaSuccess;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  switch (a.sb_dtype) {
+    case QB200_BFLOAT16: quant_kernel<BITS, XT, __nv_bfloat16><<<blocks, 256, 0, st>>>(a, wpr, total); break;
+    case QB200_FLOAT32: quant_kernel<BITS, XT, float><<<blocks, 256, 0, st>>>(a, wpr, total); break;
+    case QB200_FLOAT16: quant_kernel<BITS, XT, __half><<<blocks, 256, 0, st>>>(a, wpr, total); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+template <int BITS>
+cudaError_t quant_dispatch_x(const QuantArgs& a, cudaStream_t st) {
+  switch (a.x_dtype) {
+    case QB200_BFLOAT16: return quant_dispatch_sb<BITS, __nv_bfloat16>(a, st);
+    case QB200_FLOAT32: return quant_dispatch_sb<BITS, float>(a, st);
+    case QB200_FLOAT16: return quant_dispatch_sb<BITS, __half>(a, st);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_dequantize(const DequantArgs& a, cudaStream_t st) {
+  switch (a.bits) {
+    case 2: return dequant_dispatch_sb<2>(a, st);
+    case 4: return dequant_dispatch_sb<4>(a, st);
+    case 8: return dequant_dispatch_sb<8>(a, st);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+cudaError_t launch_quantize(const QuantArgs& a, cudaStream_t st) {
+  switch (a.bits) {
+    case 2: return quant_dispatch_x<2>(a, st);
+    case 4: return quant_dispatch_x<4>(a, st);
+    case 8: return quant_dispatch_x<8>(a, st);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace qb

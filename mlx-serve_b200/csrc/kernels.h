@@ -1,0 +1,83 @@
+// Internal launch interface between the C ABI (api.cu) and the kernels.
+// Every launcher returns a cudaError_t and never allocates.
+#pragma once
+#include "common.cuh"
+
+namespace qb {
+
+// ---- elementwise.cu ----
+struct DequantArgs {
+  const uint32_t* w; const void* s; const void* b; void* out;
+  RowMap wmap, sbmap, omap;   // row -> element offset for w, scales/biases, out
+  int64_t rows; int64_t d;    // logical row length (values)
+  int gs, bits;
+  int sb_dtype, out_dtype;    // qb200_dtype
+};
+cudaError_t launch_dequantize(const DequantArgs& a, cudaStream_t st);
+
+struct QuantArgs {
+  const void* x; uint32_t* q; void* s; void* b;
+  RowMap xmap, qmap, sbmap;
+  int64_t rows; int64_t d;
+  int gs, bits;
+  int x_dtype, sb_dtype;
+};
+cudaError_t launch_quantize(const QuantArgs& a, cudaStream_t st);
+
+// ---- qmm_generic.cu : any shape, CUDA cores (safety net + transpose=false) ----
+struct QmmArgs {
+  const void* x; const uint32_t* w; const void* s; const void* b; void* y;
+  int x_dtype;                 // bf16 / f32 / f16 (y has the same dtype)
+  int64_t M, N, K;
+  int64_t ldx, ldw, lds, ldy;  // row pitches in elements
+  int gs, bits;
+  bool transpose;
+  int64_t nbatch;
+  BatchMap xb, wb, sb, yb;
+};
+cudaError_t launch_qmm_generic(const QmmArgs& a, cudaStream_t st);
+
+// ---- qmv_mma.cu : small-M weight-streaming kernels (tensor-core dots, HBM-bound) ----
+bool qmv_mma_supported(const QmmArgs& a);
+cudaError_t launch_qmv_mma(const QmmArgs& a, cudaStream_t st);
+
+struct GatherArgs {
+  const void* x; const uint32_t* w; const void* s; const void* b; void* y;
+  int x_dtype;
+  int64_t I;                   // number of output batch elements
+  int64_t M, N, K;
+  int64_t x_batch_stride;      // elements between consecutive x batch entries ([XB, M, K] contiguous)
+  int64_t XB;                  // number of x batch entries
+  int64_t w_expert_stride, s_expert_stride;  // elements per expert
+  int64_t E;
+  const void* lhs; int lhs_dtype;   // may be null: lhs(i) = broadcast position
+  const void* rhs; int rhs_dtype;
+  // broadcast of x batch dims against the index shape when lhs == null:
+  BatchMap xbcast;             // index-space position -> x batch entry (stride in batch entries)
+  int gs, bits;
+  bool sorted;
+};
+bool gather_mma_supported(const GatherArgs& a);
+cudaError_t launch_gather_mma(const GatherArgs& a, cudaStream_t st);
+cudaError_t launch_gather_generic(const GatherArgs& a, cudaStream_t st);
+
+// ---- kv_attn.cu ----
+struct KvAttnArgs {
+  const void* q; void* out; int q_dtype;
+  const uint32_t* kq; const void* ks; const void* kb;
+  const uint32_t* vq; const void* vs; const void* vb;
+  int64_t B, Hq, Hkv, T, D, Dv;
+  int64_t q_str[2], o_str[2];          // (batch, head) strides in elements; last dim contiguous
+  int64_t kq_str[3], ksb_str[3];       // (batch, head, token)
+  int64_t vq_str[3], vsb_str[3];
+  int gs, bits;
+  float scale;
+  const int32_t* kv_lens;              // device, may be null
+  const void* mask; int mask_dtype; int64_t mask_bstride;  // additive row [B?, T], may be null
+  void* workspace; size_t workspace_bytes;
+};
+size_t kv_attn_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t T, int64_t Dv);
+bool kv_attn_supported(const KvAttnArgs& a);
+cudaError_t launch_kv_attn(const KvAttnArgs& a, cudaStream_t st);
+
+}  // namespace qb

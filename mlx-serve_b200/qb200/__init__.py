@@ -1,0 +1,224 @@
+"""ctypes binding of libqb200's C ABI (``include/qb200.h``).
+
+The functions keep the names, argument order and meaning of the mlx-c operators
+mlx-serve calls (src/mlx.zig:262, :265, :271, :275) and of the two KV-cache
+helpers built from them (src/kv_quant.zig:478-488, src/transformer.zig:3224-3337).
+Tensors are ``torch`` CUDA tensors used purely as device buffers: this module
+builds a ``qb200_tensor`` descriptor (pointer, dtype, shape, element strides)
+for each and calls the library on torch's current stream.  Outputs are
+allocated here with ``torch.empty`` because the library never allocates.
+
+There is no CPU or PyTorch fallback: if ``libqb200.so`` is missing or a call is
+declined, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB_PATH = os.path.join(_PKG, "libqb200.so")
+
+MAX_DIMS = 8
+
+# mlx_dtype values (src/mlx.zig:20-35)
+UINT32, INT32, INT64, FLOAT16, FLOAT32, BFLOAT16 = 3, 7, 8, 9, 10, 12
+_TORCH2Q = {
+    torch.uint8: 1, torch.int8: 5, torch.int16: 6, torch.int32: 7, torch.int64: 8,
+    torch.float16: 9, torch.float32: 10, torch.float64: 11, torch.bfloat16: 12, torch.bool: 0,
+}
+if hasattr(torch, "uint32"):
+    _TORCH2Q[torch.uint32] = 3
+if hasattr(torch, "uint16"):
+    _TORCH2Q[torch.uint16] = 2
+
+STATUS = {0: "OK", 1: "UNSUPPORTED", 2: "BAD_SHAPE", 3: "BAD_STRIDE", 4: "BAD_DTYPE", 5: "BAD_ARG", 6: "CUDA",
+          7: "WORKSPACE", 8: "TIMEOUT"}
+
+
+class Tensor(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("dtype", C.c_int32), ("ndim", C.c_int32),
+                ("shape", C.c_int64 * MAX_DIMS), ("stride", C.c_int64 * MAX_DIMS)]
+
+
+class OptInt(C.Structure):
+    _fields_ = [("value", C.c_int), ("has_value", C.c_bool)]
+
+
+class OptDtype(C.Structure):
+    _fields_ = [("value", C.c_int), ("has_value", C.c_bool)]
+
+
+class Qb200Error(RuntimeError):
+    def __init__(self, status: int, msg: str):
+        super().__init__(f"qb200 status {status} ({STATUS.get(status, '?')}): {msg}")
+        self.status = status
+
+
+_lib = None
+
+
+def lib():
+    """Load libqb200.so; fails loudly when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise FileNotFoundError(f"{LIB_PATH} is missing: build it with `make -C {_PKG}`")
+        L = C.CDLL(LIB_PATH)
+        TP = C.POINTER(Tensor)
+        L.qb200_last_error.restype = C.c_char_p
+        L.qb200_version.restype = C.c_char_p
+        L.qb200_quantized_matmul.argtypes = [TP, TP, TP, TP, TP, C.c_bool, OptInt, OptInt, C.c_char_p, C.c_void_p]
+        L.qb200_quantized_matmul_shape.argtypes = [TP, TP, TP, C.c_bool, OptInt, OptInt, C.POINTER(C.c_int64),
+                                                   C.POINTER(C.c_int32)]
+        L.qb200_gather_qmm.argtypes = [TP, TP, TP, TP, TP, TP, TP, C.c_bool, OptInt, OptInt, C.c_char_p, C.c_bool,
+                                       C.c_void_p]
+        L.qb200_dequantize.argtypes = [TP, TP, TP, TP, OptInt, OptInt, C.c_char_p, TP, OptDtype, C.c_void_p]
+        L.qb200_quantize.argtypes = [TP, TP, TP, TP, OptInt, OptInt, C.c_char_p, TP, C.c_void_p]
+        L.qb200_kv_append.argtypes = [TP, TP, TP, TP, C.c_int64, C.c_int, C.c_int, C.c_void_p]
+        L.qb200_kv_decode_attention.argtypes = [TP, TP, TP, TP, TP, TP, TP, TP, C.c_int, C.c_int, C.c_float,
+                                                C.c_char_p, TP, TP, C.c_void_p, C.c_size_t, C.c_void_p]
+        L.qb200_kv_decode_attention_workspace_size.restype = C.c_size_t
+        L.qb200_kv_decode_attention_workspace_size.argtypes = [C.c_int64] * 5
+        for name in ("qb200_quantized_matmul", "qb200_quantized_matmul_shape", "qb200_gather_qmm", "qb200_dequantize",
+                     "qb200_quantize", "qb200_kv_append", "qb200_kv_decode_attention"):
+            getattr(L, name).restype = C.c_int
+        _lib = L
+    return _lib
+
+
+def desc(t, dtype_override=None) -> Tensor:
+    """Descriptor of a torch tensor (or an empty handle for None)."""
+    d = Tensor()
+    if t is None:
+        d.data, d.dtype, d.ndim = None, 0, 0
+        return d
+    d.data = t.data_ptr() if t.numel() > 0 else None
+    d.dtype = dtype_override if dtype_override is not None else _TORCH2Q[t.dtype]
+    d.ndim = t.dim()
+    for i in range(t.dim()):
+        d.shape[i] = t.shape[i]
+        d.stride[i] = t.stride(i)
+    return d
+
+
+def raw_desc(ptr, dtype, shape, stride) -> Tensor:
+    d = Tensor()
+    d.data, d.dtype, d.ndim = ptr, dtype, len(shape)
+    for i, (s, st) in enumerate(zip(shape, stride)):
+        d.shape[i], d.stride[i] = s, st
+    return d
+
+
+def _packed(t):
+    """uint32 payloads are carried in int32 torch tensors."""
+    return desc(t, UINT32)
+
+
+def _opt(v):
+    return OptInt(0, False) if v is None else OptInt(int(v), True)
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def check(status: int):
+    if status != 0:
+        raise Qb200Error(status, lib().qb200_last_error().decode())
+
+
+def quantized_matmul(x, w, scales, biases, transpose=True, group_size=None, bits=None, mode="affine", out=None):
+    """mlx_quantized_matmul (src/mlx.zig:262).  Returns x's dtype, shape broadcast(batch) + [M, N]."""
+    L = lib()
+    dx, dw, ds, db = desc(x), _packed(w), desc(scales), desc(biases)
+    if out is None:
+        shp = (C.c_int64 * MAX_DIMS)()
+        nd = C.c_int32(0)
+        check(L.qb200_quantized_matmul_shape(C.byref(dx), C.byref(dw), C.byref(ds), transpose, _opt(group_size),
+                                             _opt(bits), shp, C.byref(nd)))
+        out = torch.empty([shp[i] for i in range(nd.value)], dtype=x.dtype, device=x.device)
+    do = desc(out)
+    check(L.qb200_quantized_matmul(C.byref(do), C.byref(dx), C.byref(dw), C.byref(ds), C.byref(db), transpose,
+                                   _opt(group_size), _opt(bits), mode.encode(), _stream()))
+    return out
+
+
+def gather_qmm(x, w, scales, biases, lhs_indices=None, rhs_indices=None, transpose=True, group_size=None, bits=None,
+               mode="affine", sorted_indices=False, out=None):
+    """mlx_gather_qmm (src/mlx.zig:265).  Output [*rhs_indices.shape, M, N]."""
+    L = lib()
+    if out is None:
+        M, N = x.shape[-2], w.shape[-2]
+        out = torch.empty(list(rhs_indices.shape) + [M, N], dtype=x.dtype, device=x.device)
+    do, dx, dw, ds, db = desc(out), desc(x), _packed(w), desc(scales), desc(biases)
+    dl, dr = desc(lhs_indices), desc(rhs_indices)
+    check(L.qb200_gather_qmm(C.byref(do), C.byref(dx), C.byref(dw), C.byref(ds), C.byref(db), C.byref(dl),
+                             C.byref(dr), transpose, _opt(group_size), _opt(bits), mode.encode(), sorted_indices,
+                             _stream()))
+    return out
+
+
+def dequantize(w, scales, biases, group_size=None, bits=None, mode="affine", dtype=None, out=None):
+    """mlx_dequantize (src/mlx.zig:271)."""
+    L = lib()
+    b = 4 if bits is None else bits
+    odt = scales.dtype if dtype is None else dtype
+    if out is None:
+        out = torch.empty(list(w.shape[:-1]) + [w.shape[-1] * 32 // b], dtype=odt, device=w.device)
+    do, dw, ds, db, dg = desc(out), _packed(w), desc(scales), desc(biases), desc(None)
+    od = OptDtype(0, False) if dtype is None else OptDtype(_TORCH2Q[dtype], True)
+    check(L.qb200_dequantize(C.byref(do), C.byref(dw), C.byref(ds), C.byref(db), _opt(group_size), _opt(bits),
+                             mode.encode(), C.byref(dg), od, _stream()))
+    return out
+
+
+def quantize(w, group_size=None, bits=None, mode="affine"):
+    """mlx_quantize (src/mlx.zig:275): returns (q, scales, biases); q is uint32 carried as int32."""
+    L = lib()
+    gs = 64 if group_size is None else group_size
+    b = 4 if bits is None else bits
+    q = torch.empty(list(w.shape[:-1]) + [w.shape[-1] * b // 32], dtype=torch.int32, device=w.device)
+    sdt = torch.bfloat16
+    s = torch.empty(list(w.shape[:-1]) + [w.shape[-1] // gs], dtype=sdt, device=w.device)
+    bi = torch.empty_like(s)
+    dq, ds, db, dw, dg = _packed(q), desc(s), desc(bi), desc(w), desc(None)
+    check(L.qb200_quantize(C.byref(dq), C.byref(ds), C.byref(db), C.byref(dw), _opt(group_size), _opt(bits),
+                           mode.encode(), C.byref(dg), _stream()))
+    return q, s, bi
+
+
+def kv_append(cache_q, cache_scales, cache_biases, dense, offset, bits, group_size):
+    """Quantise dense [B,Hkv,S,D] into the capacity buffers at token ``offset`` (updateAffine steps 2+5)."""
+    L = lib()
+    dq, ds, db, dd = _packed(cache_q), desc(cache_scales), desc(cache_biases), desc(dense)
+    check(L.qb200_kv_append(C.byref(dq), C.byref(ds), C.byref(db), C.byref(dd), int(offset), int(bits),
+                            int(group_size), _stream()))
+
+
+def kv_decode_attention_workspace_size(B, Hq, Hkv, T, Dv) -> int:
+    return int(lib().qb200_kv_decode_attention_workspace_size(B, Hq, Hkv, T, Dv))
+
+
+def kv_decode_attention(q, k_triple, v_triple, bits, group_size, scale, mask_mode="", mask=None, kv_lens=None,
+                        workspace=None, out=None):
+    """Decode attention over packed K/V views; q [B,Hq,1,D] -> [B,Hq,1,Dv] (quantAttention at T_q = 1)."""
+    L = lib()
+    kq, ks, kb = k_triple
+    vq, vs, vb = v_triple
+    B, Hq = q.shape[0], q.shape[1]
+    Hkv, T = kq.shape[1], kq.shape[2]
+    Dv = vq.shape[3] * 32 // bits
+    if out is None:
+        out = torch.empty((B, Hq, 1, Dv), dtype=q.dtype, device=q.device)
+    need = kv_decode_attention_workspace_size(B, Hq, Hkv, T, Dv)
+    if workspace is None:
+        workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+    args = [desc(out), desc(q), _packed(kq), desc(ks), desc(kb), _packed(vq), desc(vs), desc(vb)]
+    dm, dl = desc(mask), desc(kv_lens)
+    check(L.qb200_kv_decode_attention(*[C.byref(a) for a in args], int(bits), int(group_size), float(scale),
+                                      mask_mode.encode(), C.byref(dm), C.byref(dl),
+                                      C.c_void_p(workspace.data_ptr()), workspace.numel(), _stream()))
+    return out

@@ -1,0 +1,127 @@
+"""GPU parity of quantized_matmul through the C ABI against the CPU oracle.
+
+Gates (tests/util.py): fp32 activations -> max|d| <= 1e-2 * RMS(out) (the stated tolerance, with
+orders of magnitude to spare); bf16 activations -> within half a bf16 ulp + 2e-3*RMS of the oracle's
+unrounded fp32 result."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import qoracle as qo
+from util import dev_triple, gate_bf16, gate_f32, make_weight, rand_bf16, to_dev_bf16
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(x32, q, s, b, gs, bits, transpose=True):
+    import qb200
+    dq, ds, db = dev_triple(q, s, b)
+    ref = qo.qmm_batched(x32, q, s, b, gs, bits, transpose) if x32.ndim > 2 or q.ndim > 2 else qo.qmm(x32, q, s, b, gs, bits, transpose)
+    y32 = qb200.quantized_matmul(torch.from_numpy(x32).cuda(), dq, ds, db, transpose, gs, bits)
+    r32 = gate_f32(y32.cpu().numpy(), ref, "fp32 activations")
+    y16 = qb200.quantized_matmul(to_dev_bf16(qo.f32_to_bf16(x32)), dq, ds, db, transpose, gs, bits)
+    assert y16.dtype == torch.bfloat16 and tuple(y16.shape) == ref.shape
+    r16 = gate_bf16(y16.float().cpu().numpy(), ref, "bf16 activations")
+    return r32, r16
+
+
+def test_config1_qmv_4096x4096():
+    """BASELINE config 1: x [1,4096] ~N(0,1), W [4096,4096] ~N(0,0.02), 4-bit g64."""
+    rng = np.random.default_rng(0xC1)
+    q, s, b = make_weight(rng, (4096, 4096), 64, 4)
+    r32, _ = _run(rand_bf16(rng, (1, 4096)), q, s, b, 64, 4)
+    assert r32 < 1e-4  # hi/lo-split fp32 activations: far inside the 1e-2 gate
+
+
+LLAMA = {"q": (4096, 4096), "k": (1024, 4096), "gate": (14336, 4096), "down": (4096, 14336)}
+
+
+@pytest.mark.parametrize("proj", list(LLAMA))
+@pytest.mark.parametrize("M", [1, 8, 32])
+def test_config2_llama_projections(proj, M):
+    """BASELINE config 2: the Llama-3-8B layer shapes (v = k, o = q, up = gate) at decode widths."""
+    N, K = LLAMA[proj]
+    rng = np.random.default_rng(0xC2 + M + N)
+    q, s, b = make_weight(rng, (N, K), 64, 4)
+    _run(rand_bf16(rng, (M, K)), q, s, b, 64, 4)
+
+
+def test_config2_m128():
+    rng = np.random.default_rng(0xC2 + 128)
+    q, s, b = make_weight(rng, (4096, 4096), 64, 4)
+    _run(rand_bf16(rng, (128, 4096)), q, s, b, 64, 4)
+
+
+@pytest.mark.parametrize("bits,gs", [(8, 64), (4, 128), (8, 128), (4, 32), (8, 32), (2, 64)])
+@pytest.mark.parametrize("M", [1, 5])
+def test_other_widths_and_group_sizes(bits, gs, M):
+    rng = np.random.default_rng(bits * 100 + gs + M)
+    q, s, b = make_weight(rng, (1536, 2048), gs, bits)
+    _run(rand_bf16(rng, (M, 2048)), q, s, b, gs, bits)
+
+
+@pytest.mark.parametrize("N,K,M", [(24, 256, 1), (1000, 512, 3), (16, 256, 9), (520, 768, 2), (8, 64, 4), (40, 320, 2)])
+def test_ragged_shapes(N, K, M):
+    """Row counts that are not a multiple of the 16-row tile, minimum K, K that only the generic path serves."""
+    rng = np.random.default_rng(N + K + M)
+    q, s, b = make_weight(rng, (N, K), 64, 4)
+    _run(rand_bf16(rng, (M, K)), q, s, b, 64, 4)
+
+
+def test_reference_4d_broadcast_cases():
+    """src/kv_quant.zig:968-1094: [1,2,3,64] x [1,2,5,64]^T -> [1,2,3,5] and [1,2,3,5] x [1,2,5,64] -> [1,2,3,64]."""
+    rng = np.random.default_rng(11)
+    wf = rand_bf16(rng, (1, 2, 5, 64), 0.5)
+    q, s, b = qo.quantize(wf, 64, 4)
+    _run(rand_bf16(rng, (1, 2, 3, 64)), q, s, b, 64, 4, True)
+    _run(rand_bf16(rng, (1, 2, 3, 5)), q, s, b, 64, 4, False)
+
+
+@pytest.mark.parametrize("transpose", [True, False])
+def test_batch_broadcast_and_transpose_false_attention_shapes(transpose):
+    """quantAttention's two products (src/kv_quant.zig:528-533, :657-674): q [B,Hkv,g,D] . K^T and attn [B,Hkv,g,T] . V."""
+    rng = np.random.default_rng(12)
+    B, H, g, T, D = 2, 2, 4, 96, 128
+    kv = rand_bf16(rng, (B, H, T, D))
+    q, s, b = qo.quantize(kv, 64, 8)
+    x = rand_bf16(rng, (B, H, g, D) if transpose else (B, H, g, T), 0.3)
+    _run(x, q, s, b, 64, 8, transpose)
+    # weights shared across the batch (broadcast of w's leading dims)
+    _run(x, q[:1], s[:1], b[:1], 64, 8, transpose)
+
+
+def test_strided_operands_and_1d_x():
+    import qb200
+    rng = np.random.default_rng(13)
+    N, K = 512, 1024
+    q, s, b = make_weight(rng, (2 * N, K), 64, 4)
+    dq, ds, db = dev_triple(q, s, b)
+    xbig = rand_bf16(rng, (4, 2 * K))
+    xd = to_dev_bf16(qo.f32_to_bf16(xbig))
+    y = qb200.quantized_matmul(xd[:, K:], dq[::2], ds[::2], db[::2], True, 64, 4)
+    ref = qo.qmm(np.ascontiguousarray(xbig[:, K:]), q[::2], s[::2], b[::2], 64, 4)
+    gate_bf16(y.float().cpu().numpy(), ref, "strided")
+    y1 = qb200.quantized_matmul(xd[0, :K], dq[:N], ds[:N], db[:N], True, 64, 4)
+    assert tuple(y1.shape) == (N,)
+    gate_bf16(y1.float().cpu().numpy(), qo.qmm(xbig[:1, :K], q[:N], s[:N], b[:N], 64, 4)[0], "1-D x")
+
+
+def test_linearity_full_size_gate_proj():
+    """Size-independent property at full size (14336 x 4096, M=8, fp32 activations):
+    qmm(a*x1 + x2) == a*qmm(x1) + qmm(x2) up to accumulation noise, and scaling x by 2 doubles y exactly."""
+    import qb200
+    g = torch.Generator(device="cuda").manual_seed(99)
+    w = (torch.randn((14336, 4096), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    q, s, b = qb200.quantize(w, 64, 4)
+    x1 = torch.randn((8, 4096), device="cuda", generator=g).to(torch.bfloat16).float()
+    x2 = torch.randn((8, 4096), device="cuda", generator=g).to(torch.bfloat16).float()
+    y1 = qb200.quantized_matmul(x1, q, s, b, True, 64, 4)
+    y2 = qb200.quantized_matmul(x2, q, s, b, True, 64, 4)
+    y12 = qb200.quantized_matmul(0.5 * x1 + x2, q, s, b, True, 64, 4)
+    r = float(y12.pow(2).mean().sqrt())
+    assert float((y12 - (0.5 * y1 + y2)).abs().max()) <= 2e-4 * r
+    assert torch.equal(qb200.quantized_matmul(2 * x1, q, s, b, True, 64, 4), 2 * y1)
+    # and against dequantize + fp32 matmul of the same triple
+    wd = qb200.dequantize(q, s, b, 64, 4, dtype=torch.float32)
+    yref = x1.double() @ wd.double().t()
+    assert float((y1.double() - yref).abs().max()) <= 1e-4 * r
