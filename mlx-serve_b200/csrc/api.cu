@@ -286,7 +286,8 @@ QB200_API int qb200_quantized_matmul(qb200_tensor* res, const qb200_tensor* x, c
   if (a.M == 0 || a.N == 0 || a.nbatch == 0) return QB200_OK;
   if (a.K == 0) return fail(QB200_ERR_BAD_SHAPE, "quantized_matmul: empty contraction axis");
   cudaError_t e;
-  if (qmv_mma_supported(a)) e = launch_qmv_mma(a, (cudaStream_t)s);
+  if (qmv_stream_supported(a)) e = launch_qmv_stream(a, (cudaStream_t)s);
+  else if (qmv_mma_supported(a)) e = launch_qmv_mma(a, (cudaStream_t)s);
   else e = launch_qmm_generic(a, (cudaStream_t)s);
   if (e != cudaSuccess) return cuda_fail(e, "quantized_matmul");
   return QB200_OK;

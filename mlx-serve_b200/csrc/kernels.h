@@ -41,6 +41,10 @@ cudaError_t launch_qmm_generic(const QmmArgs& a, cudaStream_t st);
 bool qmv_mma_supported(const QmmArgs& a);
 cudaError_t launch_qmv_mma(const QmmArgs& a, cudaStream_t st);
 
+// ---- qmv_stream.cu : persistent cp.async-ring weight-streaming kernel (decode widths) ----
+bool qmv_stream_supported(const QmmArgs& a);
+cudaError_t launch_qmv_stream(const QmmArgs& a, cudaStream_t st);
+
 struct GatherArgs {
   const void* x; const uint32_t* w; const void* s; const void* b; void* y;
   int x_dtype;

@@ -76,8 +76,9 @@ def test_round_trip_property_full_size():
         assert not torch.isnan(d).any()
         step = s.float().abs().repeat_interleave(64, dim=-1)
         err = (d - x.float()).abs()
-        # half a step plus the bf16 rounding of scale/bias (relative 2^-8 of the value range)
-        bound = 0.5 * step + (2.0 ** -8) * (x.float().abs() + step * (2 ** bits))
+        # the snapped grid can clip the far end of the range by up to one step; plus the bf16 rounding of
+        # scale/bias (relative 2^-8 of the value range)
+        bound = 1.0 * step + (2.0 ** -8) * (x.float().abs() + step * (2 ** bits))
         assert bool((err <= bound).all())
         assert int(q.view(torch.int32).ne(0).sum()) > 0
 
