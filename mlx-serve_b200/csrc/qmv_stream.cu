@@ -1,32 +1,37 @@
-// Persistent weight-streaming quantized matmul for decode widths (M <= 32):
-// y[M, N] = x[M, K] . What[N, K]^T, 4/8-bit affine codes, fp32 accumulate.
+// Persistent weight-streaming quantized matmul for decode widths (M <= 16 per
+// launch): y[M, N] = x[M, K] . What[N, K]^T, 4/8-bit affine codes.
 //
 // Replaces mlx_quantized_matmul(transpose=true) as called by qmatmulBits
 // (mlx-serve src/transformer.zig:20894-20983) at decode widths and the small-M
 // verify lanes (src/transformer.zig:1317-1453).
 //
-// The kernel is HBM-bound by construction, so it is organised around keeping
-// bytes in flight rather than around the math:
-//  * one persistent CTA per SM (16 warps = two groups of 8); every warp owns a
+// The kernel is HBM-bound by construction, so it is organised around (a)
+// keeping bytes in flight and (b) spending as few issue slots per packed byte
+// as possible -- a first version that expanded codes to bf16 for
+// mma.sync.bf16 was measured instruction-bound (INT pipe) at 27% of HBM peak.
+//  * One persistent CTA per SM (16 warps = two groups of 8).  Every warp owns a
 //    private ring of cp.async (LDGSTS, 128-bit per lane) stages in shared
-//    memory, each stage = 16 weight rows x 128 contiguous bytes plus their
-//    scales and biases, so ~100 KiB of packed weights are in flight per SM
-//    independent of register pressure; no thread ever waits on another warp
-//    for data (cp.async.wait_group + __syncwarp only), so there is no
-//    barrier-protocol that could hang;
-//  * activations are staged once per CTA (per 4096-wide K pass) in MMA
-//    fragment order; a group's 8 warps split K for one 16-row tile and reduce
-//    through shared memory behind a named barrier, double-buffered so the
-//    weight stream never drains;
-//  * codes are expanded in registers (LOP3 magic number for 4-bit, PRMT into an
-//    fp32 mantissa for 8-bit) to exact bf16 integers and contracted with
-//    mma.sync.m16n8k16; scale and bias are applied per 64-wide group to the
-//    fp32 accumulators:  y += s*(sum (c+q) x) + (b - c s)*(sum x), c = 128 or 0,
-//    so the weight term q*s+b keeps fp32 precision;
-//  * fp32 activations ride as bf16 hi + lo halves in two token slots.
+//    memory; a stage is 16 weight rows x 128 contiguous bytes plus their scales
+//    and biases, so ~100 KiB of packed weights are in flight per SM regardless
+//    of register pressure.  A warp only ever waits on its own copies
+//    (cp.async.wait_group + __syncwarp), so no cross-warp protocol can hang.
+//  * Integer tensor cores do the dots exactly: the packed codes are the u8 A
+//    operand of mma.sync.m16n8k32.s32.u8.s8 (4-bit: two ANDs and one shift per
+//    8 codes; 8-bit: the packed word as is), the activations are the s8 B
+//    operand.  Each activation is converted once per CTA to a 15-bit
+//    fixed-point value sharing one power-of-two scale per (token, 64-wide
+//    group), v = rn(x * 2^(14-E)), split into two 7/8-bit planes
+//    v = 128*p0 + p1 that occupy two columns of the n8 tile.  sum_k q*v is
+//    therefore exact in s32; the only rounding is that of v (2^-15 of the
+//    group's largest |x|: exact for bf16 inputs within 2^-7 of the group
+//    maximum, and below fp32 accumulation noise otherwise).
+//  * Per 64-wide group the s32 sums are combined (128*acc0 + acc1), converted
+//    once to fp32 and scaled:  y += (s 2^(E-14)) * sum(q v) + b * 2^(E-14) * sum(v).
+//    The weight term q*s+b is never rounded to bf16.
+//  * A group's 8 warps split K for one 16-row tile and reduce through shared
+//    memory behind a named barrier, double-buffered so the stream never drains.
 // Nothing is written to global scratch; the only global writes are y.
 #include "kernels.h"
-#include "qmv_frag.cuh"
 
 namespace qb {
 namespace {
@@ -37,8 +42,10 @@ constexpr int kThreads = kWarpsPerGroup * kGroups * 32;
 constexpr int kStages = 4;          // cp.async ring depth per warp
 constexpr int kStageW = 2048;       // 16 rows x 128 B of packed codes
 constexpr int kStageBytes = kStageW + 256;  // + 16 rows x (scales, biases)
+constexpr int kTokPerTile = 4;      // tokens per n8 tile (two planes each)
+constexpr int kMaxTok = 16;         // tokens per launch
 
-__host__ __device__ constexpr int kc_for(int nt) { return 4096 / nt; }
+__host__ __device__ constexpr int kc_for(int nt) { return nt <= 2 ? 4096 : 1024; }
 
 struct StreamK {
   const void* x; const uint32_t* w; const uint16_t* s; const uint16_t* b; void* y;
@@ -51,17 +58,14 @@ struct StreamK {
   int ntl_max;        // max tiles per group (sizes the multi-pass accumulator)
 };
 
-__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
-  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src));
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
 }
-__device__ __forceinline__ void cp_async8(void* dst, const void* src) {
-  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(d), "l"(src));
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src));
 }
-__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
-  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src));
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src));
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
@@ -70,11 +74,38 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 __device__ __forceinline__ void group_barrier(int grp) {
   asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "n"(kWarpsPerGroup * 32) : "memory");
 }
+// D(16x8,s32) += A(16x32,u8,row) * B(32x8,s8,col)
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
 // 16-byte chunk swizzle inside a 128-byte stage row so that the fragment reads
 // (64-bit per lane at 4 bits, 128-bit at 8 bits) are bank-conflict free.
 template <int BITS> __device__ __forceinline__ int swz(int row) {
   return BITS == 4 ? 2 * (row & 3) : 4 * (row & 1);
+}
+
+// A lane owns 16 consecutive K values of a group, 8 per MMA.  Offset (0..7)
+// inside those 8 of the byte that sits in operand register h (0: k-slots 4t..,
+// 1: k-slots 16+4t..), byte i.  4-bit words split into even and odd nibbles;
+// 8-bit words are in order.
+template <int BITS> __device__ __forceinline__ int kslot8(int h, int i) {
+  return BITS == 4 ? 2 * i + h : 4 * h + i;
+}
+
+// Fixed-point value of one activation: v = clamp(rn(x * up)), |v| < 2^14.
+__device__ __forceinline__ int fix15(float x, float up) {
+  int v = __float2int_rn(x * up);
+  v = v > 16383 ? 16383 : v;
+  v = v < -16383 ? -16383 : v;
+  return v;
+}
+__device__ __forceinline__ uint32_t plane_byte(int v, int plane) {
+  return plane == 0 ? (uint32_t)((v >> 7) & 0xFF) : (uint32_t)(v & 127);
 }
 
 // Position of a warp in its stream of (pass, local tile, K unit) items.
@@ -104,9 +135,8 @@ struct ItemIter {
 template <int BITS, int NT, bool M1>
 __global__ void __launch_bounds__(kThreads, 1) qmv_stream_kernel(StreamK p) {
   extern __shared__ __align__(128) unsigned char smem[];
-  constexpr int U = WReg<BITS>::U;            // 64-wide groups per unit
+  constexpr int U = BITS == 4 ? 4 : 2;        // 64-wide groups per unit
   constexpr int CK = 64 * U;                  // K values per unit (128 bytes per row)
-  constexpr int SLOTS = M1 ? 1 : 8 * NT;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int grp = warp / kWarpsPerGroup, ks = warp % kWarpsPerGroup;
@@ -115,40 +145,53 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_stream_kernel(StreamK p) {
   // ---- shared memory carve-up ----
   const int kc = p.kc;
   unsigned char* sp = smem;
-  unsigned char* ring = sp;                   sp += (size_t)kGroups * kWarpsPerGroup * kStages * kStageBytes;
-  uint2* xfrag = (uint2*)sp;                  sp += M1 ? (size_t)(kc / 16) * 4 * 8 : (size_t)(kc / 16) * NT * 32 * 8;
-  float* xsum = (float*)sp;                   sp += (size_t)(kc / 64) * SLOTS * 4;
-  float* red = (float*)sp;                    sp += (size_t)kGroups * 2 * kWarpsPerGroup * NT * 128 * 4;
-  float* yacc = (float*)sp;                   // [kGroups][ntl_max][NT*128], only when npass > 1
+  unsigned char* ring = sp;    sp += (size_t)kGroups * kWarpsPerGroup * kStages * kStageBytes;
+  uint2* xfrag = (uint2*)sp;   sp += M1 ? (size_t)(kc / 32) * 8 * 8 : (size_t)(kc / 32) * NT * 32 * 8;
+  float* gsc = (float*)sp;     sp += M1 ? (size_t)(kc / 64) * 8 : (size_t)(kc / 64) * NT * kTokPerTile * 8;  // (2^(E-14), 2^(E-14)*sum v)
+  float* red = (float*)sp;     sp += (size_t)kGroups * 2 * kWarpsPerGroup * NT * 64 * 4;
+  float* yacc = (float*)sp;    // [kGroups][ntl_max][NT*64], only when npass > 1
 
-  unsigned char* my_ring = ring + (size_t)warp * kStages * kStageBytes;
+  const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring + (size_t)warp * kStages * kStageBytes);
+  const unsigned char* my_ring_p = ring + (size_t)warp * kStages * kStageBytes;
   const int ntl = ggrp < p.ntiles ? (p.ntiles - ggrp + p.total_groups - 1) / p.total_groups : 0;
   const int ut = p.K / CK, upk = kc / CK;
 
-  // ---- producer: cp.async one item (16 rows x 128 B + scales/biases) into a ring stage ----
-  auto issue = [&](const ItemIter& it, int stage) {
-    unsigned char* st = my_ring + stage * kStageBytes;
-    const int tile = ggrp + it.tl * p.total_groups;
-    const int64_t k0 = (int64_t)it.pass * kc + (int64_t)it.u * CK;
-    const int chunk = lane & 7;
+  // ---- producer state: per-lane source pointers of the current tile ----
+  const int chunk = lane & 7;
+  const unsigned char* wsrc[4];
+  const uint16_t* sbsrc;
+  uint32_t wdst[4];
+  uint32_t sbdst;
+  int prod_tile = -1;
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int row = (lane >> 3) + 4 * r;
-      int n = tile * 16 + row;
+  for (int r = 0; r < 4; ++r) {
+    const int row = (lane >> 3) + 4 * r;
+    wdst[r] = row * 128 + ((chunk ^ swz<BITS>(row)) << 4);
+  }
+  sbdst = kStageW + (lane >> 4) * 128 + (lane & 15) * 8;
+
+  auto issue = [&](const ItemIter& it, int stage) {
+    const int tile = ggrp + it.tl * p.total_groups;
+    if (tile != prod_tile) {
+      prod_tile = tile;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        int n = tile * 16 + (lane >> 3) + 4 * r;
+        n = n < p.N ? n : p.N - 1;
+        wsrc[r] = (const unsigned char*)(p.w + (int64_t)n * p.ldw) + chunk * 16;
+      }
+      int n = tile * 16 + (lane & 15);
       n = n < p.N ? n : p.N - 1;
-      const unsigned char* src = (const unsigned char*)(p.w + (int64_t)n * p.ldw) + k0 * BITS / 8 + chunk * 16;
-      cp_async16(st + row * 128 + ((chunk ^ swz<BITS>(row)) << 4), src);
+      sbsrc = ((lane >> 4) ? p.b : p.s) + (int64_t)n * p.lds;
     }
-    {
-      const int row = lane & 15;
-      int n = tile * 16 + row;
-      n = n < p.N ? n : p.N - 1;
-      const uint16_t* base = (lane >> 4) ? p.b : p.s;
-      const uint16_t* src = base + (int64_t)n * p.lds + ((k0 >> 6) >> p.gshift);
-      unsigned char* dst = st + kStageW + (lane >> 4) * 128 + row * 8;
-      if (BITS == 4 && p.gshift == 0) cp_async8(dst, src);
-      else cp_async4(dst, src);
-    }
+    const uint32_t st = my_ring + stage * kStageBytes;
+    const int k0 = it.pass * kc + it.u * CK;
+    const int woff = k0 * BITS / 8;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) cp_async16(st + wdst[r], wsrc[r] + woff);
+    const uint16_t* ssrc = sbsrc + ((k0 >> 6) >> p.gshift);
+    if (BITS == 4 && p.gshift == 0) cp_async8(st + sbdst, ssrc);
+    else cp_async4(st + sbdst, ssrc);
   };
 
   ItemIter prod;
@@ -161,8 +204,6 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_stream_kernel(StreamK p) {
     ++issued;
   }
 
-  const int tok_per_tile = p.x_f32 ? 4 : 8;
-  const int esz = p.x_f32 ? 4 : 2;
   int consumed = 0;
   int red_buf = 0;
 
@@ -170,90 +211,112 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_stream_kernel(StreamK p) {
     const int k_base = pass * kc;
     const int klen = (p.K - k_base) < kc ? (p.K - k_base) : kc;
     if (pass > 0) __syncthreads();
-    // ---- stage activations of this pass in fragment order ----
-    if constexpr (M1) {
-      const int nitems = klen / 16;
-      for (int base = 0; base < nitems; base += kThreads) {
+    // ---- stage this pass's activations as s8 planes in B-fragment order ----
+    // One thread converts 8 consecutive K values of one token; the 8 lanes that cover a 64-wide
+    // group agree on the group's power-of-two scale (|x| * up < 2^14) through shuffles.
+    {
+      const int cpt = klen >> 3;                         // 8-value chunks per token
+      const int slots = M1 ? 1 : NT * kTokPerTile;
+      const int total = slots * cpt;
+      constexpr int PF = 4;  // chunks fetched per thread before any is converted (loads in flight together)
+      for (int base0 = 0; base0 < total; base0 += kThreads * PF) {
+       uint4 raw[PF][2];
+#pragma unroll
+       for (int q = 0; q < PF; ++q) {
+        const int it = base0 + q * kThreads + tid;
+        raw[q][0] = make_uint4(0u, 0u, 0u, 0u);
+        raw[q][1] = make_uint4(0u, 0u, 0u, 0u);
+        if (it < total) {
+          const int m = it / cpt, c = it - m * cpt;
+          if (m < p.M) {
+            const int64_t off = (int64_t)m * p.ldx + k_base + c * 8;
+            if (!p.x_f32) {
+              const uint16_t* px = (const uint16_t*)p.x + off;
+              if ((((uintptr_t)px) & 15) == 0) {
+                raw[q][0] = *(const uint4*)px;
+              } else {
+                uint32_t r[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) r[j] = (uint32_t)px[2 * j] | ((uint32_t)px[2 * j + 1] << 16);
+                raw[q][0] = make_uint4(r[0], r[1], r[2], r[3]);
+              }
+            } else {
+              const float* px = (const float*)p.x + off;
+              if ((((uintptr_t)px) & 15) == 0) {
+                raw[q][0] = *(const uint4*)px;
+                raw[q][1] = *(const uint4*)(px + 4);
+              } else {
+                raw[q][0] = make_uint4(__float_as_uint(px[0]), __float_as_uint(px[1]), __float_as_uint(px[2]), __float_as_uint(px[3]));
+                raw[q][1] = make_uint4(__float_as_uint(px[4]), __float_as_uint(px[5]), __float_as_uint(px[6]), __float_as_uint(px[7]));
+              }
+            }
+          }
+        }
+       }
+#pragma unroll
+       for (int q = 0; q < PF; ++q) {
+        const int base = base0 + q * kThreads;
+        if (base >= total) break;
         const int it = base + tid;
-        const bool ok = it < nitems;
-        float v[16];
-        if (ok) {
-          const uint16_t* px = (const uint16_t*)p.x + k_base + it * 16;
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = bf16_bits_to_f32(px[j]);
+        const bool ok = it < total;
+        const int m = ok ? it / cpt : 0;
+        const int c = ok ? it - m * cpt : 0;             // chunk index inside the pass
+        float f[8];
+        if (!p.x_f32) {
+          const uint4 a = raw[q][0];
+          f[0] = bf16lo(a.x); f[1] = bf16hi(a.x); f[2] = bf16lo(a.y); f[3] = bf16hi(a.y);
+          f[4] = bf16lo(a.z); f[5] = bf16hi(a.z); f[6] = bf16lo(a.w); f[7] = bf16hi(a.w);
         } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          const uint4 a = raw[q][0], b2 = raw[q][1];
+          f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
+          f[4] = __uint_as_float(b2.x); f[5] = __uint_as_float(b2.y); f[6] = __uint_as_float(b2.z); f[7] = __uint_as_float(b2.w);
         }
-        float sum = 0.f;
+        float mx = 0.f;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) sum += v[j];
+        for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(f[j]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        int e = (int)((__float_as_uint(mx) >> 23) & 0xFF) - 127 + 1;  // mx < 2^e
+        e = e < -100 ? -100 : (e > 110 ? 110 : e);
+        const float up = __uint_as_float((uint32_t)(127 + 14 - e) << 23);
+        const float down = __uint_as_float((uint32_t)(127 + e - 14) << 23);
+        int v[8];
+        int sum = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { v[j] = fix15(f[j], up); sum += v[j]; }
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
         if (ok) {
-          const int gi = it >> 2, tt = it & 3;
-          if (tt == 0) xsum[gi] = sum;
+          const int gi = c >> 3, tt = (c >> 1) & 3, jm = c & 1;  // 64-group, lane quarter, MMA of the group
+          const int nt = m / kTokPerTile, ml = m - nt * kTokPerTile;
+          if ((c & 7) == 0) {
+            float* gs = M1 ? gsc + gi * 2 : gsc + ((gi * NT + nt) * kTokPerTile + ml) * 2;
+            gs[0] = down;
+            gs[1] = down * (float)sum;
+          }
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint2 f;
-            f.x = pack_bf16x2(v[kperm<BITS>(i, 0)], v[kperm<BITS>(i, 1)]);
-            f.y = pack_bf16x2(v[kperm<BITS>(i, 2)], v[kperm<BITS>(i, 3)]);
-            xfrag[(gi * 4 + i) * 4 + tt] = f;
+          for (int pl = 0; pl < 2; ++pl) {
+            uint2 o;
+            o.x = plane_byte(v[kslot8<BITS>(0, 0)], pl) | (plane_byte(v[kslot8<BITS>(0, 1)], pl) << 8) |
+                  (plane_byte(v[kslot8<BITS>(0, 2)], pl) << 16) | (plane_byte(v[kslot8<BITS>(0, 3)], pl) << 24);
+            o.y = plane_byte(v[kslot8<BITS>(1, 0)], pl) | (plane_byte(v[kslot8<BITS>(1, 1)], pl) << 8) |
+                  (plane_byte(v[kslot8<BITS>(1, 2)], pl) << 16) | (plane_byte(v[kslot8<BITS>(1, 3)], pl) << 24);
+            if (M1) xfrag[(gi * 2 + jm) * 8 + pl * 4 + tt] = o;
+            else xfrag[((gi * 2 + jm) * NT + nt) * 32 + (2 * ml + pl) * 4 + tt] = o;
           }
         }
-      }
-    } else {
-      const int ngroups = klen >> 6;
-      for (int item = warp; item < ngroups * NT; item += kThreads / 32) {
-        const int gi = item / NT, nt = item - gi * NT;
-        const int m = nt * tok_per_tile + (p.x_f32 ? (g & 3) : g);
-        float v[16];
-        if (m >= p.M) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = 0.f;
-        } else if (!p.x_f32) {
-          const uint16_t* px = (const uint16_t*)p.x + (int64_t)m * p.ldx + k_base + gi * 64 + 16 * t;
-          if ((((uintptr_t)px) & 15) == 0) {
-            const uint4 a = *(const uint4*)px, c = *(const uint4*)(px + 8);
-            const uint32_t r[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
-#pragma unroll
-            for (int j = 0; j < 8; ++j) { v[2 * j] = bf16lo(r[j]); v[2 * j + 1] = bf16hi(r[j]); }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = bf16_bits_to_f32(px[j]);
-          }
-        } else {
-          const float* px = (const float*)p.x + (int64_t)m * p.ldx + k_base + gi * 64 + 16 * t;
-          const bool lo_half = g >= 4;
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float f = px[j];
-            const float hi = bf16_bits_to_f32(f32_to_bf16_bits(f));
-            v[j] = lo_half ? bf16_bits_to_f32(f32_to_bf16_bits(f - hi)) : hi;
-          }
-        }
-        float sum = 0.f;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) sum += v[j];
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        if (t == 0) xsum[(gi * NT + nt) * 8 + g] = sum;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint2 f;
-          f.x = pack_bf16x2(v[kperm<BITS>(i, 0)], v[kperm<BITS>(i, 1)]);
-          f.y = pack_bf16x2(v[kperm<BITS>(i, 2)], v[kperm<BITS>(i, 3)]);
-          xfrag[((gi * 4 + i) * NT + nt) * 32 + lane] = f;
-        }
+       }
       }
     }
     __syncthreads();
 
     const int upt = (ut - pass * upk) < upk ? (ut - pass * upk) : upk;
     for (int tl = 0; tl < ntl; ++tl) {
-      float tot[NT][4];
+      float tot[NT][2];
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = tot[nt][2] = tot[nt][3] = 0.f;
+      for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = 0.f;
 
       for (int u = ks; u < upt; u += kWarpsPerGroup) {
         // keep the ring full, then wait for this item's bytes
@@ -262,116 +325,107 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_stream_kernel(StreamK p) {
         ++issued;
         cp_async_wait<kStages - 1>();
         __syncwarp();
-        const unsigned char* st = my_ring + (consumed % kStages) * kStageBytes;
+        const unsigned char* st = my_ring_p + (consumed % kStages) * kStageBytes;
         ++consumed;
 
-        float s_lo[U], s_hi[U], b_lo[U], b_hi[U];
+        // scales / biases of rows g and g+8 for the unit's U groups (bf16 pairs)
+        uint32_t sl[2], sh[2], bl[2], bh[2];
         {
           const unsigned char* sb = st + kStageW;
           if (BITS == 4 && p.gshift == 0) {
             const uint2 a = *(const uint2*)(sb + g * 8), c = *(const uint2*)(sb + (g + 8) * 8);
             const uint2 d = *(const uint2*)(sb + 128 + g * 8), e = *(const uint2*)(sb + 128 + (g + 8) * 8);
-            const uint32_t ra[2] = {a.x, a.y}, rc[2] = {c.x, c.y}, rd[2] = {d.x, d.y}, re[2] = {e.x, e.y};
-#pragma unroll
-            for (int j = 0; j < U; ++j) {
-              s_lo[j] = (j & 1) ? bf16hi(ra[(j >> 1) & 1]) : bf16lo(ra[(j >> 1) & 1]);
-              s_hi[j] = (j & 1) ? bf16hi(rc[(j >> 1) & 1]) : bf16lo(rc[(j >> 1) & 1]);
-              b_lo[j] = (j & 1) ? bf16hi(rd[(j >> 1) & 1]) : bf16lo(rd[(j >> 1) & 1]);
-              b_hi[j] = (j & 1) ? bf16hi(re[(j >> 1) & 1]) : bf16lo(re[(j >> 1) & 1]);
-            }
+            sl[0] = a.x; sl[1] = a.y; sh[0] = c.x; sh[1] = c.y;
+            bl[0] = d.x; bl[1] = d.y; bh[0] = e.x; bh[1] = e.y;
           } else {
-            // U values at stride (1 >> gshift): 4-bit g128 -> 2 distinct, 8-bit g64 -> 2 distinct
             const uint32_t a = *(const uint32_t*)(sb + g * 8), c = *(const uint32_t*)(sb + (g + 8) * 8);
             const uint32_t d = *(const uint32_t*)(sb + 128 + g * 8), e = *(const uint32_t*)(sb + 128 + (g + 8) * 8);
-#pragma unroll
-            for (int j = 0; j < U; ++j) {
-              const int idx = BITS == 4 ? (j >> 1) : j;  // 4-bit reaches here only with group size 128
-              s_lo[j] = idx ? bf16hi(a) : bf16lo(a);
-              s_hi[j] = idx ? bf16hi(c) : bf16lo(c);
-              b_lo[j] = idx ? bf16hi(d) : bf16lo(d);
-              b_hi[j] = idx ? bf16hi(e) : bf16lo(e);
+            if (BITS == 4) {  // group size 128: each value serves two 64-wide groups
+              sl[0] = __byte_perm(a, a, 0x1010); sl[1] = __byte_perm(a, a, 0x3232);
+              sh[0] = __byte_perm(c, c, 0x1010); sh[1] = __byte_perm(c, c, 0x3232);
+              bl[0] = __byte_perm(d, d, 0x1010); bl[1] = __byte_perm(d, d, 0x3232);
+              bh[0] = __byte_perm(e, e, 0x1010); bh[1] = __byte_perm(e, e, 0x3232);
+            } else {
+              sl[0] = a; sh[0] = c; bl[0] = d; bh[0] = e;
+              sl[1] = sh[1] = bl[1] = bh[1] = 0;
             }
           }
         }
         const int gl0 = u * U;  // first 64-group of this unit inside the staged pass
 #pragma unroll
         for (int j = 0; j < U; ++j) {
-          typename WReg<BITS>::T wl, wh;
+          uint32_t a0[2], a1[2], a2[2], a3[2];  // [mma]: row g lo, row g+8 lo, row g hi, row g+8 hi
           if constexpr (BITS == 4) {
             const int c = 2 * j + (t >> 1), off = (t & 1) * 8;
-            wl = *(const uint2*)(st + g * 128 + ((c ^ swz<4>(g)) << 4) + off);
-            wh = *(const uint2*)(st + (g + 8) * 128 + ((c ^ swz<4>(g + 8)) << 4) + off);
+            const uint2 wl = *(const uint2*)(st + g * 128 + ((c ^ swz<4>(g)) << 4) + off);
+            const uint2 wh = *(const uint2*)(st + (g + 8) * 128 + ((c ^ swz<4>(g + 8)) << 4) + off);
+            a0[0] = wl.x & 0x0F0F0F0Fu; a2[0] = __umulhi(wl.x, 1u << 28) & 0x0F0F0F0Fu;
+            a0[1] = wl.y & 0x0F0F0F0Fu; a2[1] = __umulhi(wl.y, 1u << 28) & 0x0F0F0F0Fu;
+            a1[0] = wh.x & 0x0F0F0F0Fu; a3[0] = __umulhi(wh.x, 1u << 28) & 0x0F0F0F0Fu;
+            a1[1] = wh.y & 0x0F0F0F0Fu; a3[1] = __umulhi(wh.y, 1u << 28) & 0x0F0F0F0Fu;
           } else {
             const int c = 4 * j + t;
-            wl = *(const uint4*)(st + g * 128 + ((c ^ swz<8>(g)) << 4));
-            wh = *(const uint4*)(st + (g + 8) * 128 + ((c ^ swz<8>(g + 8)) << 4));
+            const uint4 wl = *(const uint4*)(st + g * 128 + ((c ^ swz<8>(g)) << 4));
+            const uint4 wh = *(const uint4*)(st + (g + 8) * 128 + ((c ^ swz<8>(g + 8)) << 4));
+            a0[0] = wl.x; a2[0] = wl.y; a0[1] = wl.z; a2[1] = wl.w;
+            a1[0] = wh.x; a3[0] = wh.y; a1[1] = wh.z; a3[1] = wh.w;
           }
-          float acc[NT][4];
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
           const int gl = gl0 + j;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t a[4];
-            expand<BITS>(wl, i, a[0], a[2]);
-            expand<BITS>(wh, i, a[1], a[3]);
-            if constexpr (M1) {
-              uint2 bf = make_uint2(0u, 0u);
-              if (g == 0) bf = xfrag[(gl * 4 + i) * 4 + t];
-              mma_bf16_16816(acc[0], a, bf.x, bf.y);
-            } else {
-#pragma unroll
-              for (int nt = 0; nt < NT; ++nt) {
-                const uint2 bf = xfrag[((gl * 4 + i) * NT + nt) * 32 + lane];
-                mma_bf16_16816(acc[nt], a, bf.x, bf.y);
-              }
-            }
-          }
-          const float sl = s_lo[j], sh = s_hi[j];
-          const float bl = fmaf(-code_base<BITS>(), sl, b_lo[j]);
-          const float bh = fmaf(-code_base<BITS>(), sh, b_hi[j]);
+          const float s_lo = (j & 1) ? bf16hi(sl[j >> 1]) : bf16lo(sl[j >> 1]);
+          const float s_hi = (j & 1) ? bf16hi(sh[j >> 1]) : bf16lo(sh[j >> 1]);
+          const float b_lo = (j & 1) ? bf16hi(bl[j >> 1]) : bf16lo(bl[j >> 1]);
+          const float b_hi = (j & 1) ? bf16hi(bh[j >> 1]) : bf16lo(bh[j >> 1]);
           if constexpr (M1) {
-            const float xs = xsum[gl];
-            tot[0][0] += fmaf(sl, acc[0][0], bl * xs);
-            tot[0][2] += fmaf(sh, acc[0][2], bh * xs);
+            int acc[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              uint2 bf = make_uint2(0u, 0u);
+              if (g < 2) bf = xfrag[(gl * 2 + i) * 8 + g * 4 + t];
+              mma_u8s8(acc, a0[i], a1[i], a2[i], a3[i], bf.x, bf.y);
+            }
+            const float2 gs = *(const float2*)&gsc[gl * 2];
+            const float f_lo = (float)(acc[0] * 128 + acc[1]), f_hi = (float)(acc[2] * 128 + acc[3]);
+            tot[0][0] = fmaf(s_lo * gs.x, f_lo, fmaf(b_lo, gs.y, tot[0][0]));
+            tot[0][1] = fmaf(s_hi * gs.x, f_hi, fmaf(b_hi, gs.y, tot[0][1]));
           } else {
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-              const float2 xs = *(const float2*)&xsum[(gl * NT + nt) * 8 + 2 * t];
-              tot[nt][0] += fmaf(sl, acc[nt][0], bl * xs.x);
-              tot[nt][1] += fmaf(sl, acc[nt][1], bl * xs.y);
-              tot[nt][2] += fmaf(sh, acc[nt][2], bh * xs.x);
-              tot[nt][3] += fmaf(sh, acc[nt][3], bh * xs.y);
+              int acc[4] = {0, 0, 0, 0};
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                const uint2 bf = xfrag[((gl * 2 + i) * NT + nt) * 32 + lane];
+                mma_u8s8(acc, a0[i], a1[i], a2[i], a3[i], bf.x, bf.y);
+              }
+              const float2 gs = *(const float2*)&gsc[((gl * NT + nt) * kTokPerTile + t) * 2];
+              const float f_lo = (float)(acc[0] * 128 + acc[1]), f_hi = (float)(acc[2] * 128 + acc[3]);
+              tot[nt][0] = fmaf(s_lo * gs.x, f_lo, fmaf(b_lo, gs.y, tot[nt][0]));
+              tot[nt][1] = fmaf(s_hi * gs.x, f_hi, fmaf(b_hi, gs.y, tot[nt][1]));
             }
           }
         }
         __syncwarp();
       }
 
-      // ---- reduce the group's 8 K-slices for this tile ----
-      float* rb = red + ((size_t)(grp * 2 + red_buf) * kWarpsPerGroup) * NT * 128;
+      // ---- reduce the group's 8 K-slices for this tile: red[buf][ks][nt][row 16][token 4] ----
+      float* rb = red + ((size_t)(grp * 2 + red_buf) * kWarpsPerGroup) * NT * 64;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        float* base = rb + ((size_t)ks * NT + nt) * 128;
-        *(float2*)&base[g * 8 + 2 * t] = make_float2(tot[nt][0], tot[nt][1]);
-        *(float2*)&base[(g + 8) * 8 + 2 * t] = make_float2(tot[nt][2], tot[nt][3]);
+        float* base = rb + ((size_t)ks * NT + nt) * 64;
+        base[g * 4 + t] = tot[nt][0];
+        base[(g + 8) * 4 + t] = tot[nt][1];
       }
       group_barrier(grp);
       const int tile = ggrp + tl * p.total_groups;
       const int gt = tid - grp * (kWarpsPerGroup * 32);  // thread index inside the group
-      const int ncols = M1 ? 1 : NT * tok_per_tile;
+      const int ncols = M1 ? 1 : NT * kTokPerTile;
       for (int o = gt; o < 16 * ncols; o += kWarpsPerGroup * 32) {
         const int row = o & 15, col = o >> 4;
-        const int nt = M1 ? 0 : col / tok_per_tile, c = M1 ? 0 : col - nt * tok_per_tile;
+        const int nt = col / kTokPerTile, c = col - nt * kTokPerTile;
         float v = 0.f;
 #pragma unroll
-        for (int k = 0; k < kWarpsPerGroup; ++k) {
-          const float* base = rb + ((size_t)k * NT + nt) * 128;
-          v += base[row * 8 + c];
-          if (!M1 && p.x_f32) v += base[row * 8 + c + 4];
-        }
+        for (int k = 0; k < kWarpsPerGroup; ++k) v += rb[((size_t)k * NT + nt) * 64 + row * 4 + c];
         if (p.npass > 1) {
-          float* ya = yacc + ((size_t)(grp * p.ntl_max + tl) * NT * 128) + col * 16 + row;
+          float* ya = yacc + ((size_t)(grp * p.ntl_max + tl) * NT * 64) + col * 16 + row;
           if (pass > 0) v += *ya;
           if (pass + 1 < p.npass) { *ya = v; continue; }
         }
@@ -385,10 +439,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_stream_kernel(StreamK p) {
     }
   }
   cp_async_wait<0>();
-  (void)esz;
 }
-
-struct LaunchCfg { int grid; size_t smem; int ntl_max; int total_groups; };
 
 int sm_count() {
   static int cached[64] = {};
@@ -416,21 +467,19 @@ bool plan_stream(StreamK& p, int NT, bool M1, int* grid_out, size_t* smem_out) {
   p.kc = p.K < kc_for(NT) ? p.K : kc_for(NT);
   if (M1) p.kc = p.K;
   p.npass = (p.K + p.kc - 1) / p.kc;
-  const int slots = M1 ? 1 : 8 * NT;
   size_t smem = (size_t)kGroups * kWarpsPerGroup * kStages * kStageBytes;
-  smem += M1 ? (size_t)(p.kc / 16) * 32 : (size_t)(p.kc / 16) * NT * 256;
-  smem += (size_t)(p.kc / 64) * slots * 4;
-  smem += (size_t)kGroups * 2 * kWarpsPerGroup * NT * 512;
-  if (p.npass > 1) smem += (size_t)kGroups * p.ntl_max * NT * 512;
+  smem += M1 ? (size_t)(p.kc / 32) * 64 : (size_t)(p.kc / 32) * NT * 256;
+  smem += M1 ? (size_t)(p.kc / 64) * 8 : (size_t)(p.kc / 64) * NT * kTokPerTile * 8;
+  smem += (size_t)kGroups * 2 * kWarpsPerGroup * NT * 256;
+  if (p.npass > 1) smem += (size_t)kGroups * p.ntl_max * NT * 256;
   *grid_out = grid;
   *smem_out = smem;
   return smem <= 227 * 1024;
 }
 
 void pick_inst(const StreamK& p, int* NT, bool* M1) {
-  const int tok = p.x_f32 ? 4 : 8;
-  const int nt = (p.M + tok - 1) / tok;
-  *M1 = (p.M == 1 && !p.x_f32 && p.K <= 32768);
+  const int nt = (p.M + kTokPerTile - 1) / kTokPerTile;
+  *M1 = (p.M == 1 && p.K <= 65536);
   *NT = nt <= 1 ? 1 : (nt <= 2 ? 2 : 4);
 }
 
@@ -477,8 +526,7 @@ bool qmv_stream_supported(const QmmArgs& a) {
   if (a.gs == 128 && (a.lds % 2) != 0) return false;
   StreamK p;
   p.N = (int)a.N; p.K = (int)a.K; p.x_f32 = a.x_dtype == QB200_FLOAT32;
-  const int tok = p.x_f32 ? 4 : 8;
-  p.M = (int)(a.M < 4 * tok ? a.M : 4 * tok);
+  p.M = (int)(a.M < kMaxTok ? a.M : kMaxTok);
   int nt, grid; bool m1; size_t smem;
   pick_inst(p, &nt, &m1);
   if (!plan_stream(p, nt, m1, &grid, &smem)) return false;
@@ -493,12 +541,11 @@ cudaError_t launch_qmv_stream(const QmmArgs& a, cudaStream_t st) {
   p.gshift = a.gs == 128 ? 1 : 0;
   p.x_f32 = a.x_dtype == QB200_FLOAT32;
   const int esz = p.x_f32 ? 4 : 2;
-  const int tok = p.x_f32 ? 4 : 8;
-  const int64_t block = 4 * tok;  // wider M re-streams the weights once per token block
-  for (int64_t m0 = 0; m0 < a.M; m0 += block) {
+  // wider M re-streams the weights once per block of kMaxTok tokens
+  for (int64_t m0 = 0; m0 < a.M; m0 += kMaxTok) {
     p.x = (const char*)a.x + (a.xb.offset(0) + m0 * a.ldx) * esz;
     p.y = (char*)a.y + (a.yb.offset(0) + m0 * a.ldy) * esz;
-    p.M = (int)((a.M - m0) < block ? (a.M - m0) : block);
+    p.M = (int)((a.M - m0) < kMaxTok ? (a.M - m0) : kMaxTok);
     cudaError_t e = a.bits == 4 ? launch_bits<4>(p, st) : launch_bits<8>(p, st);
     if (e != cudaSuccess) return e;
   }
