@@ -158,6 +158,7 @@ def main():
     ap.add_argument("--layers", type=int, default=16, help="distinct layer weight sets rotated through per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="also report M in {1,8,32,128} (outside the timed steps)")
+    ap.add_argument("--micro", action="store_true", help="per-projection timings (us per launch, GB/s) and exit")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -235,6 +236,30 @@ def main():
             dist.barrier()
             ms = float(t.item())
         return ms
+
+    if args.micro:
+        res = {}
+        for m in (1, 8):
+            for name, n, k in [LLAMA[0], LLAMA[1], LLAMA[4], LLAMA[6]]:
+                idx = [i for i, (nm, _, _) in enumerate(LLAMA) if nm == name][0]
+                x = torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16)
+                y = torch.empty((L, m, n), dtype=torch.bfloat16, device=dev)
+
+                def run():
+                    for li in range(L):
+                        q, s, b = layers[li][idx]
+                        qb200.quantized_matmul(x, q, s, b, True, GS, BITS, out=y[li])
+                run()
+                torch.cuda.synchronize()
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr):
+                    run()
+                ms = time_graph(gr, args.steps, 3) / args.steps
+                by = n * k * BITS // 8 + 4 * n * (k // GS) + 2 * m * (n + k)
+                res[f"{name}_M{m}"] = {"us_per_launch": ms * 1e3 / L, "GBps": by * L / (ms * 1e-3) / 1e9}
+        if rank == 0:
+            print(json.dumps(res))
+        return
 
     gr, xin, yout = build_graph(M)
     sampler = ClockSampler(local)

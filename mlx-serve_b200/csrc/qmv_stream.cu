@@ -37,9 +37,12 @@ namespace qb {
 namespace {
 
 constexpr int kWarpsPerGroup = 8;   // K split inside a group
-constexpr int kGroups = 2;          // groups (independent tile lists) per CTA
-constexpr int kThreads = kWarpsPerGroup * kGroups * 32;
-constexpr int kStages = 4;          // cp.async ring depth per warp
+// Groups (independent tile lists) per CTA.  The single-token kernel keeps its shared memory under half an
+// SM (one group, two CTAs per SM) so that, with programmatic dependent launch, a CTA of the next kernel in the
+// stream can start filling its weight ring while the previous kernel is still running on the same SM.
+__host__ __device__ constexpr int groups_for(bool m1) { return m1 ? 1 : 2; }
+__host__ __device__ constexpr int rt_for(int nt, bool m1) { return m1 ? 2 : 4 / nt; }  // tiles reduced per barrier
+__host__ __device__ constexpr int stages_for(int nt) { return nt == 1 ? 4 : 3; }  // cp.async ring depth per warp
 constexpr int kStageW = 2048;       // 16 rows x 128 B of packed codes
 constexpr int kStageBytes = kStageW + 256;  // + 16 rows x (scales, biases)
 constexpr int kTokPerTile = 4;      // tokens per n8 tile (two planes each)
@@ -98,11 +101,10 @@ template <int BITS> __device__ __forceinline__ int kslot8(int h, int i) {
 }
 
 // Fixed-point value of one activation: v = clamp(rn(x * up)), |v| < 2^14.
+// Round-to-nearest through the fp32 magic number 1.5*2^23 (one FMA, one integer subtract).
 __device__ __forceinline__ int fix15(float x, float up) {
-  int v = __float2int_rn(x * up);
-  v = v > 16383 ? 16383 : v;
-  v = v < -16383 ? -16383 : v;
-  return v;
+  const int v = __float_as_int(fmaf(x, up, 12582912.f)) - 0x4B400000;
+  return v > 16383 ? 16383 : v;  // fp32 inputs may round up to 2^14; -2^14 still fits the high plane
 }
 __device__ __forceinline__ uint32_t plane_byte(int v, int plane) {
   return plane == 0 ? (uint32_t)((v >> 7) & 0xFF) : (uint32_t)(v & 127);
@@ -133,10 +135,14 @@ struct ItemIter {
 };
 
 template <int BITS, int NT, bool M1>
-__global__ void __launch_bounds__(kThreads, 1) qmv_stream_kernel(StreamK p) {
+__global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 : 1) qmv_stream_kernel(StreamK p) {
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int U = BITS == 4 ? 4 : 2;        // 64-wide groups per unit
   constexpr int CK = 64 * U;                  // K values per unit (128 bytes per row)
+  constexpr int kStages = stages_for(NT);
+  constexpr int RT = rt_for(NT, M1);          // tiles reduced per group barrier
+  constexpr int kGroups = groups_for(M1);
+  constexpr int kThreads = kWarpsPerGroup * kGroups * 32;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int grp = warp / kWarpsPerGroup, ks = warp % kWarpsPerGroup;
@@ -148,8 +154,10 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_stream_kernel(StreamK p) {
   unsigned char* ring = sp;    sp += (size_t)kGroups * kWarpsPerGroup * kStages * kStageBytes;
   uint2* xfrag = (uint2*)sp;   sp += M1 ? (size_t)(kc / 32) * 8 * 8 : (size_t)(kc / 32) * NT * 32 * 8;
   float* gsc = (float*)sp;     sp += M1 ? (size_t)(kc / 64) * 8 : (size_t)(kc / 64) * NT * kTokPerTile * 8;  // (2^(E-14), 2^(E-14)*sum v)
-  float* red = (float*)sp;     sp += (size_t)kGroups * 2 * kWarpsPerGroup * NT * 64 * 4;
+  float* red = (float*)sp;     sp += (size_t)kGroups * 2 * RT * kWarpsPerGroup * NT * 64 * 4;
+  const uint2* zero8 = (const uint2*)sp; sp += 16;  // an all-zero B fragment for the unused columns
   float* yacc = (float*)sp;    // [kGroups][ntl_max][NT*64], only when npass > 1
+  if (threadIdx.x == 0) *(uint2*)zero8 = make_uint2(0u, 0u);
 
   const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring + (size_t)warp * kStages * kStageBytes);
   const unsigned char* my_ring_p = ring + (size_t)warp * kStages * kStageBytes;
@@ -194,6 +202,14 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_stream_kernel(StreamK p) {
     else cp_async4(st + sbdst, ssrc);
   };
 
+  // per-lane byte offsets of the fragment reads of row g (row g+8 is +1024: same swizzle)
+  int frag_off[U];
+#pragma unroll
+  for (int j = 0; j < U; ++j) {
+    if (BITS == 4) frag_off[j] = g * 128 + (((2 * j + (t >> 1)) ^ swz<4>(g)) << 4) + (t & 1) * 8;
+    else frag_off[j] = g * 128 + (((4 * j + t) ^ swz<8>(g)) << 4);
+  }
+
   ItemIter prod;
   prod.init(ks, ntl, p.npass, upk, ut);
   int issued = 0;
@@ -203,6 +219,11 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_stream_kernel(StreamK p) {
     cp_async_commit();
     ++issued;
   }
+
+  // Let the next grid in the stream begin launching, then wait for the previous grid to complete (and
+  // its writes to be visible) before reading activations or writing outputs.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   int consumed = 0;
   int red_buf = 0;
@@ -313,7 +334,11 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_stream_kernel(StreamK p) {
     __syncthreads();
 
     const int upt = (ut - pass * upk) < upk ? (ut - pass * upk) : upk;
-    for (int tl = 0; tl < ntl; ++tl) {
+    for (int tl0 = 0; tl0 < ntl; tl0 += RT) {
+     const int rcnt = (ntl - tl0) < RT ? (ntl - tl0) : RT;
+     float* rb = red + ((size_t)(grp * 2 + red_buf) * RT * kWarpsPerGroup) * NT * 64;
+     for (int r = 0; r < rcnt; ++r) {
+
       float tot[NT][2];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = 0.f;
@@ -356,17 +381,15 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_stream_kernel(StreamK p) {
         for (int j = 0; j < U; ++j) {
           uint32_t a0[2], a1[2], a2[2], a3[2];  // [mma]: row g lo, row g+8 lo, row g hi, row g+8 hi
           if constexpr (BITS == 4) {
-            const int c = 2 * j + (t >> 1), off = (t & 1) * 8;
-            const uint2 wl = *(const uint2*)(st + g * 128 + ((c ^ swz<4>(g)) << 4) + off);
-            const uint2 wh = *(const uint2*)(st + (g + 8) * 128 + ((c ^ swz<4>(g + 8)) << 4) + off);
-            a0[0] = wl.x & 0x0F0F0F0Fu; a2[0] = __umulhi(wl.x, 1u << 28) & 0x0F0F0F0Fu;
-            a0[1] = wl.y & 0x0F0F0F0Fu; a2[1] = __umulhi(wl.y, 1u << 28) & 0x0F0F0F0Fu;
-            a1[0] = wh.x & 0x0F0F0F0Fu; a3[0] = __umulhi(wh.x, 1u << 28) & 0x0F0F0F0Fu;
-            a1[1] = wh.y & 0x0F0F0F0Fu; a3[1] = __umulhi(wh.y, 1u << 28) & 0x0F0F0F0Fu;
+            const uint2 wl = *(const uint2*)(st + frag_off[j]);
+            const uint2 wh = *(const uint2*)(st + frag_off[j] + 1024);
+            a0[0] = wl.x & 0x0F0F0F0Fu; a2[0] = (wl.x >> 4) & 0x0F0F0F0Fu;
+            a0[1] = wl.y & 0x0F0F0F0Fu; a2[1] = (wl.y >> 4) & 0x0F0F0F0Fu;
+            a1[0] = wh.x & 0x0F0F0F0Fu; a3[0] = (wh.x >> 4) & 0x0F0F0F0Fu;
+            a1[1] = wh.y & 0x0F0F0F0Fu; a3[1] = (wh.y >> 4) & 0x0F0F0F0Fu;
           } else {
-            const int c = 4 * j + t;
-            const uint4 wl = *(const uint4*)(st + g * 128 + ((c ^ swz<8>(g)) << 4));
-            const uint4 wh = *(const uint4*)(st + (g + 8) * 128 + ((c ^ swz<8>(g + 8)) << 4));
+            const uint4 wl = *(const uint4*)(st + frag_off[j]);
+            const uint4 wh = *(const uint4*)(st + frag_off[j] + 1024);
             a0[0] = wl.x; a2[0] = wl.y; a0[1] = wl.z; a2[1] = wl.w;
             a1[0] = wh.x; a3[0] = wh.y; a1[1] = wh.z; a3[1] = wh.w;
           }
@@ -379,8 +402,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_stream_kernel(StreamK p) {
             int acc[4] = {0, 0, 0, 0};
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-              uint2 bf = make_uint2(0u, 0u);
-              if (g < 2) bf = xfrag[(gl * 2 + i) * 8 + g * 4 + t];
+              const uint2 bf = *(g < 2 ? &xfrag[(gl * 2 + i) * 8 + g * 4 + t] : zero8);
               mma_u8s8(acc, a0[i], a1[i], a2[i], a3[i], bf.x, bf.y);
             }
             const float2 gs = *(const float2*)&gsc[gl * 2];
@@ -406,24 +428,27 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_stream_kernel(StreamK p) {
         __syncwarp();
       }
 
-      // ---- reduce the group's 8 K-slices for this tile: red[buf][ks][nt][row 16][token 4] ----
-      float* rb = red + ((size_t)(grp * 2 + red_buf) * kWarpsPerGroup) * NT * 64;
+      // partial sums of this tile: red[buf][r][ks][nt][row 16][token 4]
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        float* base = rb + ((size_t)ks * NT + nt) * 64;
+        float* base = rb + (((size_t)r * kWarpsPerGroup + ks) * NT + nt) * 64;
         base[g * 4 + t] = tot[nt][0];
         base[(g + 8) * 4 + t] = tot[nt][1];
       }
-      group_barrier(grp);
-      const int tile = ggrp + tl * p.total_groups;
-      const int gt = tid - grp * (kWarpsPerGroup * 32);  // thread index inside the group
-      const int ncols = M1 ? 1 : NT * kTokPerTile;
-      for (int o = gt; o < 16 * ncols; o += kWarpsPerGroup * 32) {
-        const int row = o & 15, col = o >> 4;
+     }
+     // ---- one barrier per round: reduce the group's 8 K-slices of up to RT tiles ----
+     group_barrier(grp);
+     const int gt = tid - grp * (kWarpsPerGroup * 32);  // thread index inside the group
+     const int ncols = M1 ? 1 : NT * kTokPerTile;
+     for (int o = gt; o < rcnt * 16 * ncols; o += kWarpsPerGroup * 32) {
+        const int row = o & 15, rc = o >> 4;
+        const int r = rc / ncols, col = rc - r * ncols;
         const int nt = col / kTokPerTile, c = col - nt * kTokPerTile;
+        const int tl = tl0 + r;
+        const int tile = ggrp + tl * p.total_groups;
         float v = 0.f;
 #pragma unroll
-        for (int k = 0; k < kWarpsPerGroup; ++k) v += rb[((size_t)k * NT + nt) * 64 + row * 4 + c];
+        for (int k = 0; k < kWarpsPerGroup; ++k) v += rb[(((size_t)r * kWarpsPerGroup + k) * NT + nt) * 64 + row * 4 + c];
         if (p.npass > 1) {
           float* ya = yacc + ((size_t)(grp * p.ntl_max + tl) * NT * 64) + col * 16 + row;
           if (pass > 0) v += *ya;
@@ -434,8 +459,8 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_stream_kernel(StreamK p) {
           if (p.x_f32) ((float*)p.y)[(int64_t)col * p.ldy + n] = v;
           else ((uint16_t*)p.y)[(int64_t)col * p.ldy + n] = f32_to_bf16_bits(v);
         }
-      }
-      red_buf ^= 1;
+     }
+     red_buf ^= 1;
     }
   }
   cp_async_wait<0>();
@@ -456,10 +481,10 @@ int sm_count() {
 
 // Grid, K passes and shared-memory footprint of one instantiation; false when it does not fit.
 bool plan_stream(StreamK& p, int NT, bool M1, int* grid_out, size_t* smem_out) {
-  const int nsm = sm_count();
+  const int nsm = sm_count() * (M1 ? 2 : 1);  // CTA slots
+  const int kGroups = groups_for(M1);
   const int ntiles = (p.N + 15) / 16;
-  const int per = (ntiles + kGroups * nsm - 1) / (kGroups * nsm);
-  const int total_groups = (ntiles + per - 1) / per;
+  const int total_groups = ntiles < kGroups * nsm ? ntiles : kGroups * nsm;
   const int grid = (total_groups + kGroups - 1) / kGroups;
   p.ntiles = ntiles;
   p.total_groups = grid * kGroups;
@@ -467,14 +492,15 @@ bool plan_stream(StreamK& p, int NT, bool M1, int* grid_out, size_t* smem_out) {
   p.kc = p.K < kc_for(NT) ? p.K : kc_for(NT);
   if (M1) p.kc = p.K;
   p.npass = (p.K + p.kc - 1) / p.kc;
-  size_t smem = (size_t)kGroups * kWarpsPerGroup * kStages * kStageBytes;
+  size_t smem = (size_t)kGroups * kWarpsPerGroup * stages_for(NT) * kStageBytes;
   smem += M1 ? (size_t)(p.kc / 32) * 64 : (size_t)(p.kc / 32) * NT * 256;
   smem += M1 ? (size_t)(p.kc / 64) * 8 : (size_t)(p.kc / 64) * NT * kTokPerTile * 8;
-  smem += (size_t)kGroups * 2 * kWarpsPerGroup * NT * 256;
+  smem += (size_t)kGroups * 2 * rt_for(NT, M1) * kWarpsPerGroup * NT * 256;
+  smem += 16;
   if (p.npass > 1) smem += (size_t)kGroups * p.ntl_max * NT * 256;
   *grid_out = grid;
   *smem_out = smem;
-  return smem <= 227 * 1024;
+  return smem <= (M1 ? 113 : 227) * 1024;
 }
 
 void pick_inst(const StreamK& p, int* NT, bool* M1) {
@@ -497,8 +523,19 @@ cudaError_t launch_inst(StreamK p, cudaStream_t st) {
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
   }
-  kern<<<grid, kThreads, smem, st>>>(p);
-  return cudaGetLastError();
+  // Programmatic dependent launch: this grid may start (and prefetch weights, which no kernel writes)
+  // before the previous grid in the stream has finished; it waits for that grid before touching x or y.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kWarpsPerGroup * groups_for(M1) * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 template <int BITS>
