@@ -112,7 +112,18 @@ QB200_API int qb200_quantized_matmul(qb200_tensor* res, const qb200_tensor* x, c
                                      const qb200_tensor* scales, const qb200_tensor* biases, bool transpose_w,
                                      qb200_optional_int group_size, qb200_optional_int bits, const char* mode,
                                      qb200_stream s);
-/* Output shape of the call above: fills out_shape[0..*out_ndim). */
+/* Several weight matrices applied to the SAME activations in one call: res[i] = x . What_i^T.
+ * Same result as `count` calls of qb200_quantized_matmul; at decode widths the matrices share one
+ * kernel launch and one staging of x.  It serves the call sites where the reference issues
+ * back-to-back mlx_quantized_matmul calls on one input: q, k, v (src/transformer.zig:9202-9207,
+ * :9658, :9688) and gate, up (src/transformer.zig:9452-9454, :9852-9858); MLX's lazy graph leaves
+ * their scheduling to the runtime, an eager ABI has to be told. */
+QB200_API int qb200_quantized_matmul_batch(qb200_tensor* const* res, const qb200_tensor* x,
+                                           const qb200_tensor* const* w, const qb200_tensor* const* scales,
+                                           const qb200_tensor* const* biases, int count, bool transpose_w,
+                                           qb200_optional_int group_size, qb200_optional_int bits, const char* mode,
+                                           qb200_stream s);
+/* Output shape of qb200_quantized_matmul: fills out_shape[0..*out_ndim). */
 QB200_API int qb200_quantized_matmul_shape(const qb200_tensor* x, const qb200_tensor* w, const qb200_tensor* scales,
                                            bool transpose_w, qb200_optional_int group_size, qb200_optional_int bits,
                                            int64_t* out_shape, int32_t* out_ndim);

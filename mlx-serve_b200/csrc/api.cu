@@ -234,10 +234,11 @@ QB200_API int qb200_quantized_matmul_shape(const qb200_tensor* x, const qb200_te
   return QB200_OK;
 }
 
-QB200_API int qb200_quantized_matmul(qb200_tensor* res, const qb200_tensor* x, const qb200_tensor* w,
-                                     const qb200_tensor* scales, const qb200_tensor* biases, bool transpose_w,
-                                     qb200_optional_int group_size, qb200_optional_int bits, const char* mode,
-                                     qb200_stream s) {
+// Validates one quantized_matmul request and fills the kernel arguments.  *empty is set when the
+// result has no elements (nothing to launch).
+static int prepare_qmm(qb200_tensor* res, const qb200_tensor* x, const qb200_tensor* w, const qb200_tensor* scales,
+                       const qb200_tensor* biases, bool transpose_w, qb200_optional_int group_size,
+                       qb200_optional_int bits, const char* mode, QmmArgs* out, bool* empty) {
   int gs, nb, st;
   if ((st = resolve_mode(mode, group_size, bits, &gs, &nb))) return st;
   if (is_empty(biases)) return fail(QB200_ERR_UNSUPPORTED, "quantized_matmul: biases are required (affine mode)");
@@ -268,7 +269,7 @@ QB200_API int qb200_quantized_matmul(qb200_tensor* res, const qb200_tensor* x, c
       return fail(QB200_ERR_BAD_SHAPE, "quantized_matmul: res dim %d is %lld, expected %lld", d,
                   (long long)res->shape[d], (long long)eshape[d]);
 
-  QmmArgs a;
+  QmmArgs& a = *out;
   a.x = x->data; a.w = (const uint32_t*)w->data; a.s = scales->data; a.b = biases->data; a.y = res->data;
   a.x_dtype = x->dtype;
   a.M = p.M; a.N = p.N; a.K = p.K;
@@ -283,13 +284,59 @@ QB200_API int qb200_quantized_matmul(qb200_tensor* res, const qb200_tensor* x, c
   a.wb = make_batchmap(w, 2, p);
   a.sb = make_batchmap(scales, 2, p);
   a.yb = make_batchmap(res, p.x_was_1d ? 1 : 2, p);
-  if (a.M == 0 || a.N == 0 || a.nbatch == 0) return QB200_OK;
-  if (a.K == 0) return fail(QB200_ERR_BAD_SHAPE, "quantized_matmul: empty contraction axis");
-  cudaError_t e;
-  if (qmv_stream_supported(a)) e = launch_qmv_stream(a, (cudaStream_t)s);
-  else if (qmv_mma_supported(a)) e = launch_qmv_mma(a, (cudaStream_t)s);
-  else e = launch_qmm_generic(a, (cudaStream_t)s);
+  *empty = (a.M == 0 || a.N == 0 || a.nbatch == 0);
+  if (!*empty && a.K == 0) return fail(QB200_ERR_BAD_SHAPE, "quantized_matmul: empty contraction axis");
+  return QB200_OK;
+}
+
+static cudaError_t dispatch_qmm(const QmmArgs& a, cudaStream_t s) {
+  if (qmv_stream_supported(a)) return launch_qmv_stream(a, s);
+  if (qmv_mma_supported(a)) return launch_qmv_mma(a, s);
+  return launch_qmm_generic(a, s);
+}
+
+QB200_API int qb200_quantized_matmul(qb200_tensor* res, const qb200_tensor* x, const qb200_tensor* w,
+                                     const qb200_tensor* scales, const qb200_tensor* biases, bool transpose_w,
+                                     qb200_optional_int group_size, qb200_optional_int bits, const char* mode,
+                                     qb200_stream s) {
+  QmmArgs a;
+  bool empty = false;
+  int st = prepare_qmm(res, x, w, scales, biases, transpose_w, group_size, bits, mode, &a, &empty);
+  if (st) return st;
+  if (empty) return QB200_OK;
+  cudaError_t e = dispatch_qmm(a, (cudaStream_t)s);
   if (e != cudaSuccess) return cuda_fail(e, "quantized_matmul");
+  return QB200_OK;
+}
+
+QB200_API int qb200_quantized_matmul_batch(qb200_tensor* const* res, const qb200_tensor* x,
+                                           const qb200_tensor* const* w, const qb200_tensor* const* scales,
+                                           const qb200_tensor* const* biases, int count, bool transpose_w,
+                                           qb200_optional_int group_size, qb200_optional_int bits, const char* mode,
+                                           qb200_stream s) {
+  if (count < 0 || (count > 0 && (!res || !w || !scales || !biases)))
+    return fail(QB200_ERR_BAD_ARG, "quantized_matmul_batch: null operand list");
+  constexpr int kChunk = 4;
+  for (int i0 = 0; i0 < count; i0 += kChunk) {
+    const int n = count - i0 < kChunk ? count - i0 : kChunk;
+    QmmArgs a[kChunk];
+    bool empty[kChunk];
+    bool fuse = n > 1;
+    for (int i = 0; i < n; ++i) {
+      int st = prepare_qmm(res[i0 + i], x, w[i0 + i], scales[i0 + i], biases[i0 + i], transpose_w, group_size, bits,
+                           mode, &a[i], &empty[i]);
+      if (st) return st;
+      fuse = fuse && !empty[i] && qmv_stream_supported(a[i]) && a[i].K == a[0].K;
+    }
+    cudaError_t e = cudaSuccess;
+    if (fuse) {
+      e = launch_qmv_stream_multi(a, n, (cudaStream_t)s);
+    } else {
+      for (int i = 0; i < n && e == cudaSuccess; ++i)
+        if (!empty[i]) e = dispatch_qmm(a[i], (cudaStream_t)s);
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "quantized_matmul_batch");
+  }
   return QB200_OK;
 }
 

@@ -44,6 +44,7 @@ cudaError_t launch_qmv_mma(const QmmArgs& a, cudaStream_t st);
 // ---- qmv_stream.cu : persistent cp.async-ring weight-streaming kernel (decode widths) ----
 bool qmv_stream_supported(const QmmArgs& a);
 cudaError_t launch_qmv_stream(const QmmArgs& a, cudaStream_t st);
+cudaError_t launch_qmv_stream_multi(const QmmArgs* a, int count, cudaStream_t st);  // same x, <= 4 matrices
 
 struct GatherArgs {
   const void* x; const uint32_t* w; const void* s; const void* b; void* y;

@@ -50,10 +50,17 @@ constexpr int kMaxTok = 16;         // tokens per launch
 
 __host__ __device__ constexpr int kc_for(int nt) { return nt <= 2 ? 4096 : 1024; }
 
+constexpr int kMaxMat = 4;          // weight matrices served by one launch (same activations)
+
 struct StreamK {
-  const void* x; const uint32_t* w; const uint16_t* s; const uint16_t* b; void* y;
-  int M, N, K;
-  int64_t ldx, ldw, lds, ldy;
+  const void* x;
+  const uint32_t* w[kMaxMat]; const uint16_t* s[kMaxMat]; const uint16_t* b[kMaxMat]; void* y[kMaxMat];
+  int N[kMaxMat];
+  int64_t ldw[kMaxMat], lds[kMaxMat], ldy[kMaxMat];
+  int tile0[kMaxMat + 1];  // first 16-row tile of each matrix in the launch-wide tile numbering
+  int nmat;
+  int M, K;
+  int64_t ldx;
   int gshift, x_f32;
   int total_groups;   // groups over the whole grid (tile t belongs to group t % total_groups)
   int ntiles;
@@ -108,6 +115,17 @@ __device__ __forceinline__ int fix15(float x, float up) {
 }
 __device__ __forceinline__ uint32_t plane_byte(int v, int plane) {
   return plane == 0 ? (uint32_t)((v >> 7) & 0xFF) : (uint32_t)(v & 127);
+}
+
+// Kernel parameters are indexed with constant subscripts only (a dynamic subscript would force a
+// local-memory copy of the parameter block).
+#define QB_SEL4(arr, i) ((i) == 0 ? (arr)[0] : ((i) == 1 ? (arr)[1] : ((i) == 2 ? (arr)[2] : (arr)[3])))
+__device__ __forceinline__ int mat_of_tile(const StreamK& p, int tile) {
+  int mi = 0;
+  if (p.nmat > 1 && tile >= p.tile0[1]) mi = 1;
+  if (p.nmat > 2 && tile >= p.tile0[2]) mi = 2;
+  if (p.nmat > 3 && tile >= p.tile0[3]) mi = 3;
+  return mi;
 }
 
 // Position of a warp in its stream of (pass, local tile, K unit) items.
@@ -182,15 +200,19 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
     const int tile = ggrp + it.tl * p.total_groups;
     if (tile != prod_tile) {
       prod_tile = tile;
+      const int mi = mat_of_tile(p, tile);
+      const int row0 = (tile - QB_SEL4(p.tile0, mi)) * 16, nrows = QB_SEL4(p.N, mi);
+      const uint32_t* wm = QB_SEL4(p.w, mi);
+      const int64_t ldw = QB_SEL4(p.ldw, mi), lds = QB_SEL4(p.lds, mi);
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
-        int n = tile * 16 + (lane >> 3) + 4 * r;
-        n = n < p.N ? n : p.N - 1;
-        wsrc[r] = (const unsigned char*)(p.w + (int64_t)n * p.ldw) + chunk * 16;
+        int n = row0 + (lane >> 3) + 4 * r;
+        n = n < nrows ? n : nrows - 1;
+        wsrc[r] = (const unsigned char*)(wm + (int64_t)n * ldw) + chunk * 16;
       }
-      int n = tile * 16 + (lane & 15);
-      n = n < p.N ? n : p.N - 1;
-      sbsrc = ((lane >> 4) ? p.b : p.s) + (int64_t)n * p.lds;
+      int n = row0 + (lane & 15);
+      n = n < nrows ? n : nrows - 1;
+      sbsrc = ((lane >> 4) ? QB_SEL4(p.b, mi) : QB_SEL4(p.s, mi)) + (int64_t)n * lds;
     }
     const uint32_t st = my_ring + stage * kStageBytes;
     const int k0 = it.pass * kc + it.u * CK;
@@ -454,10 +476,13 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
           if (pass > 0) v += *ya;
           if (pass + 1 < p.npass) { *ya = v; continue; }
         }
-        const int n = tile * 16 + row;
-        if (n < p.N && col < p.M) {
-          if (p.x_f32) ((float*)p.y)[(int64_t)col * p.ldy + n] = v;
-          else ((uint16_t*)p.y)[(int64_t)col * p.ldy + n] = f32_to_bf16_bits(v);
+        const int mi = mat_of_tile(p, tile);
+        const int n = (tile - QB_SEL4(p.tile0, mi)) * 16 + row;
+        if (n < QB_SEL4(p.N, mi) && col < p.M) {
+          void* ym = QB_SEL4(p.y, mi);
+          const int64_t ldy = QB_SEL4(p.ldy, mi);
+          if (p.x_f32) ((float*)ym)[(int64_t)col * ldy + n] = v;
+          else ((uint16_t*)ym)[(int64_t)col * ldy + n] = f32_to_bf16_bits(v);
         }
      }
      red_buf ^= 1;
@@ -483,7 +508,9 @@ int sm_count() {
 bool plan_stream(StreamK& p, int NT, bool M1, int* grid_out, size_t* smem_out) {
   const int nsm = sm_count() * (M1 ? 2 : 1);  // CTA slots
   const int kGroups = groups_for(M1);
-  const int ntiles = (p.N + 15) / 16;
+  int ntiles = 0;
+  for (int i = 0; i < p.nmat; ++i) { p.tile0[i] = ntiles; ntiles += (p.N[i] + 15) / 16; }
+  for (int i = p.nmat; i <= kMaxMat; ++i) p.tile0[i] = ntiles;
   const int total_groups = ntiles < kGroups * nsm ? ntiles : kGroups * nsm;
   const int grid = (total_groups + kGroups - 1) / kGroups;
   p.ntiles = ntiles;
@@ -562,7 +589,7 @@ bool qmv_stream_supported(const QmmArgs& a) {
   if (a.gs == 64 && a.lds % 4 != 0) return false;
   if (a.gs == 128 && (a.lds % 2) != 0) return false;
   StreamK p;
-  p.N = (int)a.N; p.K = (int)a.K; p.x_f32 = a.x_dtype == QB200_FLOAT32;
+  p.nmat = 1; p.N[0] = (int)a.N; p.K = (int)a.K; p.x_f32 = a.x_dtype == QB200_FLOAT32;
   p.M = (int)(a.M < kMaxTok ? a.M : kMaxTok);
   int nt, grid; bool m1; size_t smem;
   pick_inst(p, &nt, &m1);
@@ -570,23 +597,38 @@ bool qmv_stream_supported(const QmmArgs& a) {
   return true;
 }
 
-cudaError_t launch_qmv_stream(const QmmArgs& a, cudaStream_t st) {
+// `count` (<= 4) weight matrices applied to the same activations in one launch.  Every entry must
+// have passed qmv_stream_supported and share x, M, K, dtype, bits and group size with the first.
+cudaError_t launch_qmv_stream_multi(const QmmArgs* a, int count, cudaStream_t st) {
   StreamK p;
-  p.w = a.w + a.wb.offset(0); p.s = (const uint16_t*)a.s + a.sb.offset(0); p.b = (const uint16_t*)a.b + a.sb.offset(0);
-  p.N = (int)a.N; p.K = (int)a.K;
-  p.ldx = a.ldx; p.ldw = a.ldw; p.lds = a.lds; p.ldy = a.ldy;
-  p.gshift = a.gs == 128 ? 1 : 0;
-  p.x_f32 = a.x_dtype == QB200_FLOAT32;
+  p.nmat = count;
+  for (int i = 0; i < kMaxMat; ++i) {
+    const QmmArgs& q = a[i < count ? i : 0];
+    p.w[i] = q.w + q.wb.offset(0);
+    p.s[i] = (const uint16_t*)q.s + q.sb.offset(0);
+    p.b[i] = (const uint16_t*)q.b + q.sb.offset(0);
+    p.N[i] = i < count ? (int)q.N : 0;
+    p.ldw[i] = q.ldw; p.lds[i] = q.lds; p.ldy[i] = q.ldy;
+  }
+  p.K = (int)a[0].K;
+  p.ldx = a[0].ldx;
+  p.gshift = a[0].gs == 128 ? 1 : 0;
+  p.x_f32 = a[0].x_dtype == QB200_FLOAT32;
   const int esz = p.x_f32 ? 4 : 2;
   // wider M re-streams the weights once per block of kMaxTok tokens
-  for (int64_t m0 = 0; m0 < a.M; m0 += kMaxTok) {
-    p.x = (const char*)a.x + (a.xb.offset(0) + m0 * a.ldx) * esz;
-    p.y = (char*)a.y + (a.yb.offset(0) + m0 * a.ldy) * esz;
-    p.M = (int)((a.M - m0) < kMaxTok ? (a.M - m0) : kMaxTok);
-    cudaError_t e = a.bits == 4 ? launch_bits<4>(p, st) : launch_bits<8>(p, st);
+  for (int64_t m0 = 0; m0 < a[0].M; m0 += kMaxTok) {
+    p.x = (const char*)a[0].x + (a[0].xb.offset(0) + m0 * a[0].ldx) * esz;
+    for (int i = 0; i < kMaxMat; ++i) {
+      const QmmArgs& q = a[i < count ? i : 0];
+      p.y[i] = (char*)q.y + (q.yb.offset(0) + m0 * q.ldy) * esz;
+    }
+    p.M = (int)((a[0].M - m0) < kMaxTok ? (a[0].M - m0) : kMaxTok);
+    cudaError_t e = a[0].bits == 4 ? launch_bits<4>(p, st) : launch_bits<8>(p, st);
     if (e != cudaSuccess) return e;
   }
   return cudaSuccess;
 }
+
+cudaError_t launch_qmv_stream(const QmmArgs& a, cudaStream_t st) { return launch_qmv_stream_multi(&a, 1, st); }
 
 }  // namespace qb

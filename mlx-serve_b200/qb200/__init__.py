@@ -73,6 +73,8 @@ def lib():
         L.qb200_quantized_matmul.argtypes = [TP, TP, TP, TP, TP, C.c_bool, OptInt, OptInt, C.c_char_p, C.c_void_p]
         L.qb200_quantized_matmul_shape.argtypes = [TP, TP, TP, C.c_bool, OptInt, OptInt, C.POINTER(C.c_int64),
                                                    C.POINTER(C.c_int32)]
+        L.qb200_quantized_matmul_batch.argtypes = [C.POINTER(TP), TP, C.POINTER(TP), C.POINTER(TP), C.POINTER(TP),
+                                                   C.c_int, C.c_bool, OptInt, OptInt, C.c_char_p, C.c_void_p]
         L.qb200_gather_qmm.argtypes = [TP, TP, TP, TP, TP, TP, TP, C.c_bool, OptInt, OptInt, C.c_char_p, C.c_bool,
                                        C.c_void_p]
         L.qb200_dequantize.argtypes = [TP, TP, TP, TP, OptInt, OptInt, C.c_char_p, TP, OptDtype, C.c_void_p]
@@ -82,7 +84,7 @@ def lib():
                                                 C.c_char_p, TP, TP, C.c_void_p, C.c_size_t, C.c_void_p]
         L.qb200_kv_decode_attention_workspace_size.restype = C.c_size_t
         L.qb200_kv_decode_attention_workspace_size.argtypes = [C.c_int64] * 5
-        for name in ("qb200_quantized_matmul", "qb200_quantized_matmul_shape", "qb200_gather_qmm", "qb200_dequantize",
+        for name in ("qb200_quantized_matmul", "qb200_quantized_matmul_batch", "qb200_quantized_matmul_shape", "qb200_gather_qmm", "qb200_dequantize",
                      "qb200_quantize", "qb200_kv_append", "qb200_kv_decode_attention"):
             getattr(L, name).restype = C.c_int
         _lib = L
@@ -144,6 +146,20 @@ def quantized_matmul(x, w, scales, biases, transpose=True, group_size=None, bits
     check(L.qb200_quantized_matmul(C.byref(do), C.byref(dx), C.byref(dw), C.byref(ds), C.byref(db), transpose,
                                    _opt(group_size), _opt(bits), mode.encode(), _stream()))
     return out
+
+
+def quantized_matmul_batch(x, triples, outs, transpose=True, group_size=None, bits=None, mode="affine"):
+    """Several (w, scales, biases) triples applied to the same x in one call; ``outs`` are preallocated."""
+    L = lib()
+    n = len(triples)
+    TP = C.POINTER(Tensor)
+    keep = [desc(x)] + [desc(o) for o in outs] + [_packed(t[0]) for t in triples] + \
+           [desc(t[1]) for t in triples] + [desc(t[2]) for t in triples]
+    arr = lambda lst: (TP * n)(*[C.pointer(d) for d in lst])
+    check(L.qb200_quantized_matmul_batch(arr(keep[1:1 + n]), C.byref(keep[0]), arr(keep[1 + n:1 + 2 * n]),
+                                         arr(keep[1 + 2 * n:1 + 3 * n]), arr(keep[1 + 3 * n:1 + 4 * n]), n, transpose,
+                                         _opt(group_size), _opt(bits), mode.encode(), _stream()))
+    return outs
 
 
 def gather_qmm(x, w, scales, biases, lhs_indices=None, rhs_indices=None, transpose=True, group_size=None, bits=None,

@@ -126,3 +126,18 @@ def test_linearity_full_size_gate_proj():
     wd = qb200.dequantize(q, s, b, 64, 4, dtype=torch.float32)
     yref = x1.double() @ wd.double().t()
     assert float((y1.double() - yref).abs().max()) <= 2e-4 * r
+
+
+@pytest.mark.parametrize("M", [1, 8])
+def test_batch_entry_matches_single_calls(M):
+    """q, k, v on one input through qb200_quantized_matmul_batch: bit-identical to three single calls."""
+    import qb200
+    rng = np.random.default_rng(21 + M)
+    K = 4096
+    x = to_dev_bf16(qo.f32_to_bf16(rand_bf16(rng, (M, K))))
+    triples = [dev_triple(*make_weight(rng, (n, K), 64, 4)) for n in (4096, 1024, 1000)]
+    single = [qb200.quantized_matmul(x, *t, True, 64, 4) for t in triples]
+    outs = [torch.empty_like(s) for s in single]
+    qb200.quantized_matmul_batch(x, triples, outs, True, 64, 4)
+    for a, b in zip(single, outs):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
