@@ -159,6 +159,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="also report M in {1,8,32,128} (outside the timed steps)")
     ap.add_argument("--no-batch", action="store_true", help="seven separate calls per layer instead of four")
+    ap.add_argument("--micro-kv", action="store_true", help="decode attention over the packed KV cache (config 5) and exit")
     ap.add_argument("--micro", action="store_true", help="per-projection timings (us per launch, GB/s) and exit")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -179,7 +180,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     qb200.lib()  # fail loudly if the library is not built
 
-    M, L = args.m, args.layers
+    M, L = args.m, (0 if args.micro_kv else args.layers)
     g = torch.Generator(device=dev).manual_seed(0xC2 + rank)
     layers = []
     for _ in range(L):
@@ -249,6 +250,43 @@ def main():
             dist.barrier()
             ms = float(t.item())
         return ms
+
+    if args.micro_kv:
+        res = {}
+        B, Hq, Hkv, D = 16, 32, 8, 128
+        for T in (4096, 32768):
+            for bits in (4, 8):
+                ncache = 4 if T == 4096 else 1   # rotate caches so every call streams from HBM (126 MB L2)
+                cap = T + 256                    # views of a larger capacity buffer: head stride != T * last
+                caches = []
+                for _ in range(ncache):
+                    k = torch.randn((B, Hkv, cap, D), device=dev, generator=g).to(torch.bfloat16)
+                    kt = qb200.quantize(k, 64, bits)
+                    k.normal_(generator=g)
+                    vt = qb200.quantize(k, 64, bits)
+                    del k
+                    caches.append(([t_[:, :, :T] for t_ in kt], [t_[:, :, :T] for t_ in vt]))
+                q = torch.randn((B, Hq, 1, D), device=dev, generator=g).to(torch.bfloat16)
+                out = torch.empty_like(q)
+                ws = torch.empty(qb200.kv_decode_attention_workspace_size(B, Hq, Hkv, T, D), dtype=torch.uint8, device=dev)
+                reps = 8
+
+                def run():
+                    for i in range(reps):
+                        kt, vt = caches[i % ncache]
+                        qb200.kv_decode_attention(q, kt, vt, bits, 64, D ** -0.5, workspace=ws, out=out)
+                run()
+                torch.cuda.synchronize()
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr):
+                    run()
+                ms = time_graph(gr, args.steps, 3) / args.steps / reps
+                by = B * Hkv * T * 2 * (D * bits // 8 + 8) + 2 * B * Hq * D * 2
+                res[f"T{T}_b{bits}"] = {"us_per_call": ms * 1e3, "GBps": by / (ms * 1e-3) / 1e9, "bytes": by}
+                del caches
+        if rank == 0:
+            print(json.dumps(res))
+        return
 
     if args.micro:
         res = {}

@@ -19,7 +19,7 @@ constexpr float kNegBig = -1e30f;  // clamp for fully masked blocks (src/transfo
 
 struct SplitPlan {
   int nsplit;
-  int64_t tokens_per_split;  // multiple of 64
+  int64_t tokens_per_split;  // multiple of 128
 };
 
 // Deterministic in (B, Hkv, T) so that the workspace query and the launch agree.
@@ -31,8 +31,8 @@ __host__ SplitPlan plan_splits(int64_t B, int64_t Hkv, int64_t T) {
   if (ns > max_ns) ns = max_ns;
   if (ns < 1) ns = 1;
   int64_t tps = (T + ns - 1) / ns;
-  tps = (tps + 63) / 64 * 64;
-  if (tps < 64) tps = 64;
+  tps = (tps + 127) / 128 * 128;
+  if (tps < 128) tps = 128;
   ns = (T + tps - 1) / tps;
   if (ns < 1) ns = 1;
   p.nsplit = (int)ns;
@@ -210,6 +210,10 @@ __global__ void kv_merge(KvK p) {
 
 }  // namespace
 
+bool kv_fast_supported(const KvAttnArgs& a);
+cudaError_t launch_kv_fast(const KvAttnArgs& a, int nsplit, int64_t tps, float* pm, float* pl, float* po,
+                           cudaStream_t st);
+
 size_t kv_attn_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t T, int64_t Dv) {
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || T <= 0 || Dv <= 0) return 0;
   const SplitPlan sp = plan_splits(B, Hkv, T);
@@ -237,12 +241,17 @@ cudaError_t launch_kv_attn(const KvAttnArgs& a, cudaStream_t st) {
   p.part_m = ws;
   p.part_l = ws + a.B * a.Hq * sp.nsplit;
   p.part_o = ws + 2 * a.B * a.Hq * sp.nsplit;
-  const int nwarp = 4;
-  const size_t smem = (size_t)(p.gqa * a.D + 2 * nwarp * p.gqa + nwarp * p.gqa * a.Dv) * sizeof(float);
-  dim3 grid((unsigned)sp.nsplit, (unsigned)a.Hkv, (unsigned)a.B);
-  if (a.bits == 4) kv_split_generic<4><<<grid, nwarp * 32, smem, st>>>(p);
-  else kv_split_generic<8><<<grid, nwarp * 32, smem, st>>>(p);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e;
+  if (kv_fast_supported(a)) {
+    e = launch_kv_fast(a, sp.nsplit, sp.tokens_per_split, p.part_m, p.part_l, p.part_o, st);
+  } else {
+    const int nwarp = 4;
+    const size_t smem = (size_t)(p.gqa * a.D + 2 * nwarp * p.gqa + nwarp * p.gqa * a.Dv) * sizeof(float);
+    dim3 grid((unsigned)sp.nsplit, (unsigned)a.Hkv, (unsigned)a.B);
+    if (a.bits == 4) kv_split_generic<4><<<grid, nwarp * 32, smem, st>>>(p);
+    else kv_split_generic<8><<<grid, nwarp * 32, smem, st>>>(p);
+    e = cudaGetLastError();
+  }
   if (e != cudaSuccess) return e;
   dim3 mgrid((unsigned)a.Hq, (unsigned)a.B, 1);
   kv_merge<<<mgrid, 128, 0, st>>>(p);

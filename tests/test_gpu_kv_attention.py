@@ -88,7 +88,8 @@ def test_config5_t32768_one_sequence_and_full_batch_property():
     half = qb200.kv_decode_attention(q, [t[:, :, :Th] for t in kt], [t[:, :, :Th] for t in vt], 4, 64, D ** -0.5)
     assert not torch.isnan(full).any()
     r = float(half.pow(2).mean().sqrt())
-    assert float((full - half).abs().max()) <= 1e-3 * r
+    # p * v_scale enters the integer tensor cores as 15-bit fixed point per 128-token block
+    assert float((full - half).abs().max()) <= 5e-3 * r
     lens = torch.full((B,), Th, dtype=torch.int32, device="cuda")
     masked = qb200.kv_decode_attention(q, kt, vt, 4, 64, D ** -0.5, kv_lens=lens)
-    assert float((masked - half).abs().max()) <= 1e-3 * r
+    assert float((masked - half).abs().max()) <= 5e-3 * r
