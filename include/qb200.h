@@ -98,6 +98,9 @@ typedef void (*qb200_error_handler_func)(const char* msg, void* data);
 QB200_API void qb200_set_error_handler(qb200_error_handler_func handler, void* data, void (*dtor)(void*));
 QB200_API const char* qb200_last_error(void); /* thread-local; "" when none */
 QB200_API const char* qb200_version(void);
+/* Diagnostic without a reference counterpart: 0, or the code of the bounded barrier wait that
+ * expired inside the tensor-core prefill kernel (synchronises the device). */
+QB200_API int qb200_debug_tc_status(void);
 
 /* ---- mlx_quantized_matmul (src/mlx.zig:262) ----
  * transpose_w = true : y[..., m, n] = sum_k x[..., m, k] * What[..., n, k]

@@ -215,6 +215,7 @@ QB200_API void qb200_set_error_handler(qb200_error_handler_func handler, void* d
 
 QB200_API const char* qb200_last_error(void) { return g_last_error.c_str(); }
 QB200_API const char* qb200_version(void) { return "qb200 0.1 (sm_100a)"; }
+QB200_API int qb200_debug_tc_status(void) { return qmm_tc_error_code(); }
 
 QB200_API int qb200_quantized_matmul_shape(const qb200_tensor* x, const qb200_tensor* w, const qb200_tensor* scales,
                                            bool transpose_w, qb200_optional_int group_size, qb200_optional_int bits,
@@ -290,6 +291,8 @@ static int prepare_qmm(qb200_tensor* res, const qb200_tensor* x, const qb200_ten
 }
 
 static cudaError_t dispatch_qmm(const QmmArgs& a, cudaStream_t s) {
+  // decode widths stream the weights once through the integer-MMA kernel; wider inputs go to tcgen05
+  if (a.M > 16 && qmm_tc_supported(a)) return launch_qmm_tc(a, s);
   if (qmv_stream_supported(a)) return launch_qmv_stream(a, s);
   if (qmv_mma_supported(a)) return launch_qmv_mma(a, s);
   return launch_qmm_generic(a, s);

@@ -46,6 +46,11 @@ bool qmv_stream_supported(const QmmArgs& a);
 cudaError_t launch_qmv_stream(const QmmArgs& a, cudaStream_t st);
 cudaError_t launch_qmv_stream_multi(const QmmArgs* a, int count, cudaStream_t st);  // same x, <= 4 matrices
 
+// ---- qmm_tc.cu : prefill widths on tcgen05 (dequantise into the swizzled smem operand, TMEM accumulate) ----
+bool qmm_tc_supported(const QmmArgs& a);
+cudaError_t launch_qmm_tc(const QmmArgs& a, cudaStream_t st);
+int qmm_tc_error_code();  // 0, or the code of a bounded wait that expired in the last failing launch
+
 struct GatherArgs {
   const void* x; const uint32_t* w; const void* s; const void* b; void* y;
   int x_dtype;

@@ -191,6 +191,34 @@ QO_API void qo_qmm_t(const float* x, const uint32_t* w, const uint16_t* s, const
   }
 }
 
+/* ---- quantized_matmul through the dense prefill route (src/transformer.zig:20987-21011) ----
+ * prefillDqGemm dequantises W to a bf16 [N, K] transient and runs a dense GEMM: the weight
+ * term is rounded to bf16 before the dot; accumulation stays fp32. */
+QO_API void qo_qmm_t_bf16w(const float* x, const uint32_t* w, const uint16_t* s, const uint16_t* b,
+                           int64_t M, int64_t N, int64_t K, int gs, int bits, float* y) {
+  const int64_t words = K * bits / 32, groups = K / gs;
+#pragma omp parallel
+  {
+    float* wrow = (float*)malloc(sizeof(float) * (size_t)K);
+#pragma omp for schedule(static)
+    for (int64_t n = 0; n < N; ++n) {
+      for (int64_t k = 0; k < K; ++k) {
+        const float sc = bf16_to_f32(s[n * groups + k / gs]);
+        const float bi = bf16_to_f32(b[n * groups + k / gs]);
+        const float prod = unpack1(w + n * words, k, bits) * sc;
+        wrow[k] = bf16_to_f32(f32_to_bf16(prod + bi));
+      }
+      for (int64_t m = 0; m < M; ++m) {
+        float acc = 0.0f;
+        const float* xr = x + m * K;
+        for (int64_t k = 0; k < K; ++k) acc += xr[k] * wrow[k];
+        y[m * N + n] = acc;
+      }
+    }
+    free(wrow);
+  }
+}
+
 /* ---- quantized_matmul, transpose=false (src/kv_quant.zig:1038-1094) ----
  * y[m,n] = sum_k x[m,k] * What[k,n];  W packed [K, N*bits/32], s,b [K, N/gs]
  * (groups run along the output axis n). */

@@ -117,14 +117,17 @@ def quantize(x, gs: int, bits: int):
     return q, s, b
 
 
-def qmm(x, w, s, b, gs: int, bits: int, transpose: bool = True) -> np.ndarray:
-    """2-D quantized matmul in fp32.  transpose=True: w is [N, K*bits/32]."""
+def qmm(x, w, s, b, gs: int, bits: int, transpose: bool = True, bf16_weights: bool = False) -> np.ndarray:
+    """2-D quantized matmul in fp32.  transpose=True: w is [N, K*bits/32].
+
+    ``bf16_weights`` rounds the dequantised weight to bf16 before the dot, as the reference's dense
+    prefill route does (src/transformer.zig:20987-21011)."""
     x, w, s, b = _c(x, np.float32), _c(w, np.uint32), _c(s, np.uint16), _c(b, np.uint16)
     M, K = x.shape
     if transpose:
         N = w.shape[0]
         assert w.shape[1] * 32 // bits == K
-        fn = lib().qo_qmm_t
+        fn = lib().qo_qmm_t_bf16w if bf16_weights else lib().qo_qmm_t
     else:
         N = w.shape[1] * 32 // bits
         assert w.shape[0] == K

@@ -21,7 +21,15 @@ def _run(x32, q, s, b, gs, bits, transpose=True):
     r32 = gate_f32(y32.cpu().numpy(), ref, "fp32 activations")
     y16 = qb200.quantized_matmul(to_dev_bf16(qo.f32_to_bf16(x32)), dq, ds, db, transpose, gs, bits)
     assert y16.dtype == torch.bfloat16 and tuple(y16.shape) == ref.shape
-    r16 = gate_bf16(y16.float().cpu().numpy(), ref, "bf16 activations")
+    if transpose and x32.ndim == 2 and q.ndim == 2 and x32.shape[0] > 16:
+        # prefill widths take the dense route's semantics: the weight term is rounded to bf16 once
+        # (src/transformer.zig:20987-21011).  Tight gate against that definition, and the stated
+        # 1e-2 * RMS tolerance (plus the output's own half ulp) against the fp32-weight oracle.
+        ref_w16 = qo.qmm(x32, q, s, b, gs, bits, True, bf16_weights=True)
+        r16 = gate_bf16(y16.float().cpu().numpy(), ref_w16, "bf16 activations, bf16 weight term")
+        gate_bf16(y16.float().cpu().numpy(), ref, "bf16 activations vs fp32 weight term", slack=1e-2)
+    else:
+        r16 = gate_bf16(y16.float().cpu().numpy(), ref, "bf16 activations")
     return r32, r16
 
 
@@ -141,3 +149,41 @@ def test_batch_entry_matches_single_calls(M):
     qb200.quantized_matmul_batch(x, triples, outs, True, 64, 4)
     for a, b in zip(single, outs):
         assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+@pytest.mark.parametrize("bits,gs", [(4, 64), (8, 64), (4, 128)])
+@pytest.mark.parametrize("M,N,K", [(512, 1024, 4096), (300, 1000, 1024), (17, 128, 64), (2048, 256, 2048)])
+def test_config4_prefill_shapes(bits, gs, M, N, K):
+    """BASELINE config 4 (dense prefill qmm) at oracle-sized shapes, incl. ragged M and N and the minimum K."""
+    import qb200
+    if K % gs:
+        pytest.skip("K not a multiple of the group size")
+    rng = np.random.default_rng(M + N + K + bits + gs)
+    q, s, b = make_weight(rng, (N, K), gs, bits)
+    _run(rand_bf16(rng, (M, K)), q, s, b, gs, bits)
+    assert qb200.lib().qb200_debug_tc_status() == 0
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_config4_full_size_vs_dequantize_plus_fp32_matmul(bits):
+    """BASELINE config 4 at full size (x [2048,4096], W [14336,4096]): the fused kernel against the route it replaces,
+    dequantize to bf16 + a plain fp32 matmul (torch, TF32 off)."""
+    import qb200
+    g = torch.Generator(device="cuda").manual_seed(0xC4)
+    w = (torch.randn((14336, 4096), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    q, s, b = qb200.quantize(w, 64, bits)
+    x = torch.randn((2048, 4096), device="cuda", generator=g).to(torch.bfloat16)
+    y = qb200.quantized_matmul(x, q, s, b, True, 64, bits)
+    assert qb200.lib().qb200_debug_tc_status() == 0
+    wd = qb200.dequantize(q, s, b, 64, bits, dtype=torch.bfloat16)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        ref = x.float() @ wd.float().t()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    assert not torch.isnan(y).any()
+    r = float(ref.pow(2).mean().sqrt())
+    d = (y.float() - ref).abs()
+    ulp = torch.pow(2.0, torch.floor(torch.log2(ref.abs().clamp_min(1e-30))) - 7)
+    assert bool((d <= 0.5 * ulp * (1 + 1e-6) + 1e-3 * r).all())
