@@ -160,6 +160,7 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="also report M in {1,8,32,128} (outside the timed steps)")
     ap.add_argument("--no-batch", action="store_true", help="seven separate calls per layer instead of four")
     ap.add_argument("--micro-kv", action="store_true", help="decode attention over the packed KV cache (config 5) and exit")
+    ap.add_argument("--micro-prefill", action="store_true", help="dense prefill qmm (config 4) and exit")
     ap.add_argument("--micro", action="store_true", help="per-projection timings (us per launch, GB/s) and exit")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -180,7 +181,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     qb200.lib()  # fail loudly if the library is not built
 
-    M, L = args.m, (0 if args.micro_kv else args.layers)
+    M, L = args.m, (0 if (args.micro_kv or args.micro_prefill) else args.layers)
     g = torch.Generator(device=dev).manual_seed(0xC2 + rank)
     layers = []
     for _ in range(L):
@@ -250,6 +251,34 @@ def main():
             dist.barrier()
             ms = float(t.item())
         return ms
+
+    if args.micro_prefill:
+        res = {}
+        Mp, Np, Kp = 2048, 14336, 4096
+        x = torch.randn((Mp, Kp), device=dev, generator=g).to(torch.bfloat16)
+        for bits in (4, 8):
+            ws = []
+            for _ in range(4):  # rotate weight sets (4 x 33-62 MB) and outputs
+                w = (torch.randn((Np, Kp), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+                ws.append(qb200.quantize(w, 64, bits))
+                del w
+            y = torch.empty((4, Mp, Np), dtype=torch.bfloat16, device=dev)
+
+            def run():
+                for i in range(4):
+                    qb200.quantized_matmul(x, *ws[i], True, 64, bits, out=y[i])
+            run()
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                run()
+            ms = time_graph(gr, args.steps, 3) / args.steps / 4
+            res[f"b{bits}"] = {"ms_per_call": ms, "TFLOPs": 2.0 * Mp * Np * Kp / (ms * 1e-3) / 1e12,
+                               "tc_status": qb200.lib().qb200_debug_tc_status()}
+            del ws, y
+        if rank == 0:
+            print(json.dumps(res))
+        return
 
     if args.micro_kv:
         res = {}

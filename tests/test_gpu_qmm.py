@@ -21,7 +21,7 @@ def _run(x32, q, s, b, gs, bits, transpose=True):
     r32 = gate_f32(y32.cpu().numpy(), ref, "fp32 activations")
     y16 = qb200.quantized_matmul(to_dev_bf16(qo.f32_to_bf16(x32)), dq, ds, db, transpose, gs, bits)
     assert y16.dtype == torch.bfloat16 and tuple(y16.shape) == ref.shape
-    if transpose and x32.ndim == 2 and q.ndim == 2 and x32.shape[0] > 16:
+    if transpose and x32.ndim == 2 and q.ndim == 2 and x32.shape[0] >= 64:
         # prefill widths take the dense route's semantics: the weight term is rounded to bf16 once
         # (src/transformer.zig:20987-21011).  Tight gate against that definition, and the stated
         # 1e-2 * RMS tolerance (plus the output's own half ulp) against the fp32-weight oracle.
