@@ -160,6 +160,7 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="also report M in {1,8,32,128} (outside the timed steps)")
     ap.add_argument("--no-batch", action="store_true", help="seven separate calls per layer instead of four")
     ap.add_argument("--micro-kv", action="store_true", help="decode attention over the packed KV cache (config 5) and exit")
+    ap.add_argument("--micro-moe", action="store_true", help="routed-MoE gather_qmm decode (config 3, 64 tokens) and exit")
     ap.add_argument("--micro-prefill", action="store_true", help="dense prefill qmm (config 4) and exit")
     ap.add_argument("--micro", action="store_true", help="per-projection timings (us per launch, GB/s) and exit")
     args = ap.parse_args()
@@ -181,7 +182,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     qb200.lib()  # fail loudly if the library is not built
 
-    M, L = args.m, (0 if (args.micro_kv or args.micro_prefill) else args.layers)
+    M, L = args.m, (0 if (args.micro_kv or args.micro_prefill or args.micro_moe) else args.layers)
     g = torch.Generator(device=dev).manual_seed(0xC2 + rank)
     layers = []
     for _ in range(L):
@@ -251,6 +252,42 @@ def main():
             dist.barrier()
             ms = float(t.item())
         return ms
+
+    if args.micro_moe:
+        E, H, I, T, topk = 128, 2048, 768, 64, 8
+        banks = {}
+        for name, (n, k) in (("gate", (I, H)), ("up", (I, H)), ("down", (H, I))):
+            w = (torch.randn((E, n, k), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+            banks[name] = qb200.quantize(w, 64, 4)
+            del w
+        logits = torch.randn((T, E), device=dev, generator=g)
+        inds = torch.topk(torch.softmax(logits, -1), topk, dim=-1).indices.reshape(-1)
+        order = torch.argsort(inds, stable=True)
+        sorted_inds = inds[order].to(torch.int32).contiguous()
+        xtok = torch.randn((T, H), device=dev, generator=g).to(torch.bfloat16)
+        x_rep = xtok[order // topk].reshape(T * topk, 1, H).contiguous()
+        act = torch.randn((T * topk, 1, I), device=dev, generator=g).to(torch.bfloat16)
+        yg = torch.empty((T * topk, 1, I), dtype=torch.bfloat16, device=dev)
+        yu = torch.empty_like(yg)
+        yd = torch.empty((T * topk, 1, H), dtype=torch.bfloat16, device=dev)
+        uniq = int(torch.unique(sorted_inds).numel())
+
+        def run():
+            qb200.gather_qmm(x_rep, *banks["gate"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yg)
+            qb200.gather_qmm(x_rep, *banks["up"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yu)
+            qb200.gather_qmm(act, *banks["down"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yd)
+        run()
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            run()
+        ms = time_graph(gr, args.steps, 3) / args.steps
+        per_expert = 786432 + 2 * 49152
+        by = 3 * uniq * per_expert + T * topk * 2 * (2 * (H + I) + (I + H))
+        if rank == 0:
+            print(json.dumps({"us_per_block": ms * 1e3, "unique_experts": uniq, "bytes": by,
+                              "GBps": by / (ms * 1e-3) / 1e9}))
+        return
 
     if args.micro_prefill:
         res = {}

@@ -1,0 +1,446 @@
+// Routed-MoE gather_qmm at decode widths: res[i] = x[lhs(i)] . What[rhs[i]]^T.
+//
+// Replaces mlx_gather_qmm as called by gatherExpertMm (mlx-serve
+// src/transformer.zig:20763-20784) for both call shapes of moeMLP2 -- rows
+// sorted by expert ([N,1,D] + rhs [N], src/transformer.zig:15007-15035) and the
+// stock decode shape (x [B,S,1,1,D] + rhs [B,S,K], src/transformer.zig:15091-15119)
+// -- and, like the reference's single-token gatherQmv kernels
+// (src/transformer.zig:20046-20109), it reads each routed expert's packed bank
+// in place, once.
+//
+// Decomposition (HBM-bound, one pass over every expert that is hit):
+//  * a persistent grid (one CTA of 16 warps per SM).  Every CTA derives the same
+//    ascending list of experts that occur in rhs, then takes (expert, share of
+//    the expert's 16-row tiles) work items round-robin.  With few active experts
+//    the tiles of one expert are spread over many CTAs; with many, a CTA sweeps
+//    whole experts.
+//  * for its expert the CTA collects the output rows routed to it (any order in
+//    rhs works; `sorted_indices` is never needed for correctness), stages their
+//    activations as two s8 fixed-point planes per row (8 rows per sweep), and
+//    each warp owns whole 16-row tiles: it streams the tile's K range through a
+//    private cp.async ring, multiplies on the integer tensor cores
+//    (mma.m16n8k32.u8.s8, codes as the A operand) and stores its 16 x rows
+//    results straight from registers.  No cross-warp reduction, no barriers in
+//    the streaming loop, nothing written to global scratch.
+// Arithmetic is that of the dense streaming kernel: exact s32 dots of codes with
+// 15-bit fixed-point activations, scale and bias applied per 64-wide group in
+// fp32; the weight term q*s+b is never rounded to bf16.
+#include "kernels.h"
+
+namespace qb {
+namespace {
+
+constexpr int kWarps = 16;
+constexpr int kThreads = kWarps * 32;
+constexpr int kStages = 3;
+constexpr int kStageW = 2048;                 // 16 rows x 128 B of packed codes
+constexpr int kStageBytes = kStageW + 256;    // + scales, biases
+constexpr int kRowsPerSweep = 8;              // two n8 tiles of (4 rows x 2 planes)
+constexpr int kMaxExperts = 1024;
+constexpr int kMaxRows = 2048;                // rows of one expert kept in shared memory
+
+struct GK {
+  const void* x; const uint32_t* w; const uint16_t* s; const uint16_t* b; void* y;
+  const void* rhs; const void* lhs;
+  int rhs_i64, lhs_i64;
+  BatchMap xbcast;
+  int64_t I, E, XB, xstride, wes, ses;
+  int N, K, gshift, x_f32;
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <int BITS> __device__ __forceinline__ int swz(int row) { return BITS == 4 ? 2 * (row & 3) : 4 * (row & 1); }
+template <int BITS> __device__ __forceinline__ int kslot8(int h, int i) { return BITS == 4 ? 2 * i + h : 4 * h + i; }
+__device__ __forceinline__ int fix15(float x, float up) {
+  const int v = __float_as_int(fmaf(x, up, 12582912.f)) - 0x4B400000;
+  return v > 16383 ? 16383 : v;
+}
+__device__ __forceinline__ uint32_t plane_byte(int v, int plane) {
+  return plane == 0 ? (uint32_t)((v >> 7) & 0xFF) : (uint32_t)(v & 127);
+}
+__device__ __forceinline__ long long load_index(const void* p, int is64, int64_t i) {
+  return is64 ? ((const long long*)p)[i] : (long long)((const uint32_t*)p)[i];
+}
+
+
+template <int BITS>
+__global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int U = BITS == 4 ? 4 : 2;   // 64-wide groups per unit
+  constexpr int CK = 64 * U;             // K values per unit (128 bytes per row)
+  constexpr int NT = 2;
+  __shared__ int s_act[kMaxExperts];            // ascending list of the experts that occur in rhs
+  __shared__ unsigned s_flags[kMaxExperts / 32];
+  __shared__ int s_nact, s_nrows;
+  __shared__ int s_rows[kMaxRows];              // output rows routed to the current expert
+  __shared__ long long s_xi[kRowsPerSweep];     // activation row of each slot (-1: empty)
+  __shared__ int s_orow[kRowsPerSweep];         // output row of each slot (-1: empty)
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  unsigned char* sp = smem;
+  unsigned char* ring = sp;    sp += (size_t)kWarps * kStages * kStageBytes;
+  uint2* xfrag = (uint2*)sp;   sp += (size_t)(p.K / 32) * NT * 32 * 8;
+  float* gsc = (float*)sp;     // [(group*NT + nt)*4 + row][2]: (2^(E-14), 2^(E-14) * sum v)
+  const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring + (size_t)warp * kStages * kStageBytes);
+  const unsigned char* my_ring_p = ring + (size_t)warp * kStages * kStageBytes;
+
+  // The indices (and activations) may come from the previous kernel in the stream.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // ---- every CTA derives the same ascending list of active experts ----
+  for (int i = tid; i < kMaxExperts / 32; i += kThreads) s_flags[i] = 0u;
+  __syncthreads();
+  for (int64_t i = tid; i < p.I; i += kThreads) {
+    const long long e = load_index(p.rhs, p.rhs_i64, i);
+    if (e >= 0 && e < p.E) atomicOr(&s_flags[e >> 5], 1u << (e & 31));
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int base = 0;
+    const int nwords = (int)((p.E + 31) / 32);
+    for (int wd = 0; wd < nwords; ++wd) {
+      const unsigned word = s_flags[wd];
+      if ((word >> lane) & 1u) s_act[base + __popc(word & ((1u << lane) - 1u))] = wd * 32 + lane;
+      base += __popc(word);
+    }
+    if (lane == 0) s_nact = base;
+  }
+  __syncthreads();
+  const int nact = s_nact;
+  if (nact == 0) return;
+  const int tiles_n = (p.N + 15) / 16;
+  int parts = (int)gridDim.x / nact;
+  parts = parts < 1 ? 1 : (parts > tiles_n ? tiles_n : parts);
+  const int per = (tiles_n + parts - 1) / parts;
+  const int nitems = nact * parts;
+  const int ut = p.K / CK;
+
+  // per-lane constants of the ring
+  const int chunk = lane & 7;
+  uint32_t wdst[4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int row = (lane >> 3) + 4 * r;
+    wdst[r] = row * 128 + ((chunk ^ swz<BITS>(row)) << 4);
+  }
+  const uint32_t sbdst = kStageW + (lane >> 4) * 128 + (lane & 15) * 8;
+  int frag_off[U];
+#pragma unroll
+  for (int j = 0; j < U; ++j) {
+    if (BITS == 4) frag_off[j] = g * 128 + (((2 * j + (t >> 1)) ^ swz<4>(g)) << 4) + (t & 1) * 8;
+    else frag_off[j] = g * 128 + (((4 * j + t) ^ swz<8>(g)) << 4);
+  }
+
+  for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+    const int e = s_act[item / parts], part = item % parts;
+    const int t0 = part * per;
+    const int t1 = (t0 + per) < tiles_n ? (t0 + per) : tiles_n;
+    const uint32_t* wexp = p.w + (int64_t)e * p.wes;
+    const uint16_t* sexp = p.s + (int64_t)e * p.ses;
+    const uint16_t* bexp = p.b + (int64_t)e * p.ses;
+    const int64_t ldw = (int64_t)p.K * BITS / 32, lds = p.K >> (6 + p.gshift);
+
+    // ---- the output rows routed to this expert (order is irrelevant: rows are independent) ----
+    __syncthreads();
+    if (tid == 0) s_nrows = 0;
+    __syncthreads();
+    for (int64_t i = tid; i < p.I; i += kThreads)
+      if (load_index(p.rhs, p.rhs_i64, i) == (long long)e) {
+        const int pos = atomicAdd(&s_nrows, 1);
+        if (pos < kMaxRows) s_rows[pos] = (int)i;
+      }
+    __syncthreads();
+    const int nrows = s_nrows < kMaxRows ? s_nrows : kMaxRows;
+
+    for (int r0 = 0; r0 < nrows; r0 += kRowsPerSweep) {
+      __syncthreads();  // previous sweep has finished with xfrag / slots
+      if (tid < kRowsPerSweep) {
+        long long xi = -1;
+        int orow = -1;
+        if (r0 + tid < nrows) {
+          orow = s_rows[r0 + tid];
+          xi = p.lhs ? load_index(p.lhs, p.lhs_i64, orow) : (long long)p.xbcast.offset(orow);
+          if (xi < 0 || xi >= p.XB) { xi = -1; orow = -1; }
+        }
+        s_xi[tid] = xi;
+        s_orow[tid] = orow;
+      }
+      __syncthreads();
+      const int nte = (nrows - r0) > 4 ? 2 : 1;  // n8 tiles in use
+      // ---- stage the rows' activations as s8 planes in B-fragment order (one thread: 8 K values) ----
+      {
+        const int cpt = p.K >> 3;
+        const int total = nte * 4 * cpt;
+        for (int base = 0; base < total; base += kThreads) {
+          const int it = base + tid;
+          const bool ok = it < total;
+          const int m = ok ? it / cpt : 0;
+          const int c = ok ? it - m * cpt : 0;
+          float f[8];
+          const long long xi = ok ? s_xi[m] : -1;
+          if (xi >= 0) {
+            const int64_t off = xi * p.xstride + (int64_t)c * 8;
+            if (!p.x_f32) {
+              const uint4 a = *(const uint4*)((const uint16_t*)p.x + off);
+              f[0] = bf16lo(a.x); f[1] = bf16hi(a.x); f[2] = bf16lo(a.y); f[3] = bf16hi(a.y);
+              f[4] = bf16lo(a.z); f[5] = bf16hi(a.z); f[6] = bf16lo(a.w); f[7] = bf16hi(a.w);
+            } else {
+              const float4 a = *(const float4*)((const float*)p.x + off), b2 = *(const float4*)((const float*)p.x + off + 4);
+              f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b2.x; f[5] = b2.y; f[6] = b2.z; f[7] = b2.w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = 0.f;
+          }
+          float mx = 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(f[j]));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+          int ex = (int)((__float_as_uint(mx) >> 23) & 0xFF) - 127 + 1;  // mx < 2^ex
+          ex = ex < -100 ? -100 : (ex > 110 ? 110 : ex);
+          const float up = __uint_as_float((uint32_t)(127 + 14 - ex) << 23);
+          const float down = __uint_as_float((uint32_t)(127 + ex - 14) << 23);
+          int v[8], sum = 0;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { v[j] = fix15(f[j], up); sum += v[j]; }
+          sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+          if (ok) {
+            const int gi = c >> 3, tt = (c >> 1) & 3, jm = c & 1;
+            const int nt = m >> 2, ml = m & 3;
+            if ((c & 7) == 0) {
+              float* gs = gsc + ((gi * NT + nt) * 4 + ml) * 2;
+              gs[0] = down;
+              gs[1] = down * (float)sum;
+            }
+#pragma unroll
+            for (int pl = 0; pl < 2; ++pl) {
+              uint2 o;
+              o.x = plane_byte(v[kslot8<BITS>(0, 0)], pl) | (plane_byte(v[kslot8<BITS>(0, 1)], pl) << 8) |
+                    (plane_byte(v[kslot8<BITS>(0, 2)], pl) << 16) | (plane_byte(v[kslot8<BITS>(0, 3)], pl) << 24);
+              o.y = plane_byte(v[kslot8<BITS>(1, 0)], pl) | (plane_byte(v[kslot8<BITS>(1, 1)], pl) << 8) |
+                    (plane_byte(v[kslot8<BITS>(1, 2)], pl) << 16) | (plane_byte(v[kslot8<BITS>(1, 3)], pl) << 24);
+              xfrag[((gi * 2 + jm) * NT + nt) * 32 + (2 * ml + pl) * 4 + tt] = o;
+            }
+          }
+        }
+      }
+      __syncthreads();
+      // ---- each warp owns whole 16-row tiles of the CTA's share ----
+      {
+        const int first = t0 + warp;
+        const int my_tiles = first < t1 ? (t1 - first + kWarps - 1) / kWarps : 0;
+        const int total = my_tiles * ut;
+        int issued = 0, consumed = 0, ptile = 0, pu = 0;  // producer position: (tile index, unit)
+        auto issue = [&](int stage) {
+          const int tile = first + ptile * kWarps;
+          const uint32_t st = my_ring + stage * kStageBytes;
+          const int64_t woff = (int64_t)pu * 128;
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            int n = tile * 16 + (lane >> 3) + 4 * r;
+            n = n < p.N ? n : p.N - 1;
+            cp_async16(st + wdst[r], (const unsigned char*)(wexp + (int64_t)n * ldw) + woff + chunk * 16);
+          }
+          int n = tile * 16 + (lane & 15);
+          n = n < p.N ? n : p.N - 1;
+          const uint16_t* ssrc = ((lane >> 4) ? bexp : sexp) + (int64_t)n * lds + ((pu * U) >> p.gshift);
+          if (BITS == 4 && p.gshift == 0) cp_async8(st + sbdst, ssrc);
+          else cp_async4(st + sbdst, ssrc);
+          if (++pu == ut) { pu = 0; ++ptile; }
+        };
+#pragma unroll
+        for (int i = 0; i < kStages - 1; ++i) {
+          if (issued < total) issue(issued % kStages);
+          cp_async_commit();
+          ++issued;
+        }
+        for (int ti = 0; ti < my_tiles; ++ti) {
+          float tot[NT][2];
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = 0.f;
+          for (int u = 0; u < ut; ++u) {
+            if (issued < total) issue(issued % kStages);
+            cp_async_commit();
+            ++issued;
+            cp_async_wait<kStages - 1>();
+            __syncwarp();
+            const unsigned char* st = my_ring_p + (consumed % kStages) * kStageBytes;
+            ++consumed;
+            uint32_t sl[2], sh[2], bl[2], bh[2];
+            {
+              const unsigned char* sb = st + kStageW;
+              if (BITS == 4 && p.gshift == 0) {
+                const uint2 a = *(const uint2*)(sb + g * 8), c = *(const uint2*)(sb + (g + 8) * 8);
+                const uint2 d = *(const uint2*)(sb + 128 + g * 8), e2 = *(const uint2*)(sb + 128 + (g + 8) * 8);
+                sl[0] = a.x; sl[1] = a.y; sh[0] = c.x; sh[1] = c.y;
+                bl[0] = d.x; bl[1] = d.y; bh[0] = e2.x; bh[1] = e2.y;
+              } else {
+                const uint32_t a = *(const uint32_t*)(sb + g * 8), c = *(const uint32_t*)(sb + (g + 8) * 8);
+                const uint32_t d = *(const uint32_t*)(sb + 128 + g * 8), e2 = *(const uint32_t*)(sb + 128 + (g + 8) * 8);
+                if (BITS == 4) {  // group size 128: each value serves two 64-wide groups
+                  sl[0] = __byte_perm(a, a, 0x1010); sl[1] = __byte_perm(a, a, 0x3232);
+                  sh[0] = __byte_perm(c, c, 0x1010); sh[1] = __byte_perm(c, c, 0x3232);
+                  bl[0] = __byte_perm(d, d, 0x1010); bl[1] = __byte_perm(d, d, 0x3232);
+                  bh[0] = __byte_perm(e2, e2, 0x1010); bh[1] = __byte_perm(e2, e2, 0x3232);
+                } else {
+                  sl[0] = a; sh[0] = c; bl[0] = d; bh[0] = e2;
+                  sl[1] = sh[1] = bl[1] = bh[1] = 0;
+                }
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < U; ++j) {
+              uint32_t a0[2], a1[2], a2[2], a3[2];
+              if constexpr (BITS == 4) {
+                const uint2 wl = *(const uint2*)(st + frag_off[j]);
+                const uint2 wh = *(const uint2*)(st + frag_off[j] + 1024);
+                a0[0] = wl.x & 0x0F0F0F0Fu; a2[0] = (wl.x >> 4) & 0x0F0F0F0Fu;
+                a0[1] = wl.y & 0x0F0F0F0Fu; a2[1] = (wl.y >> 4) & 0x0F0F0F0Fu;
+                a1[0] = wh.x & 0x0F0F0F0Fu; a3[0] = (wh.x >> 4) & 0x0F0F0F0Fu;
+                a1[1] = wh.y & 0x0F0F0F0Fu; a3[1] = (wh.y >> 4) & 0x0F0F0F0Fu;
+              } else {
+                const uint4 wl = *(const uint4*)(st + frag_off[j]);
+                const uint4 wh = *(const uint4*)(st + frag_off[j] + 1024);
+                a0[0] = wl.x; a2[0] = wl.y; a0[1] = wl.z; a2[1] = wl.w;
+                a1[0] = wh.x; a3[0] = wh.y; a1[1] = wh.z; a3[1] = wh.w;
+              }
+              const int gl = u * U + j;
+              const float s_lo = (j & 1) ? bf16hi(sl[j >> 1]) : bf16lo(sl[j >> 1]);
+              const float s_hi = (j & 1) ? bf16hi(sh[j >> 1]) : bf16lo(sh[j >> 1]);
+              const float b_lo = (j & 1) ? bf16hi(bl[j >> 1]) : bf16lo(bl[j >> 1]);
+              const float b_hi = (j & 1) ? bf16hi(bh[j >> 1]) : bf16lo(bh[j >> 1]);
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) {
+                if (nt < nte) {
+                  int acc[4] = {0, 0, 0, 0};
+#pragma unroll
+                  for (int i = 0; i < 2; ++i) {
+                    const uint2 bf = xfrag[((gl * 2 + i) * NT + nt) * 32 + lane];
+                    mma_u8s8(acc, a0[i], a1[i], a2[i], a3[i], bf.x, bf.y);
+                  }
+                  const float2 gs = *(const float2*)&gsc[((gl * NT + nt) * 4 + t) * 2];
+                  const float f_lo = (float)(acc[0] * 128 + acc[1]), f_hi = (float)(acc[2] * 128 + acc[3]);
+                  tot[nt][0] = fmaf(s_lo * gs.x, f_lo, fmaf(b_lo, gs.y, tot[nt][0]));
+                  tot[nt][1] = fmaf(s_hi * gs.x, f_hi, fmaf(b_hi, gs.y, tot[nt][1]));
+                }
+              }
+            }
+            __syncwarp();
+          }
+          // ---- store the tile: lane (g, t) holds weight rows g, g+8 for the row in slot nt*4 + t ----
+          const int n_lo = (first + ti * kWarps) * 16 + g;
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const int orow = s_orow[nt * 4 + t];
+            if (nt < nte && orow >= 0) {
+              const int64_t o = (int64_t)orow * p.N;
+              if (p.x_f32) {
+                if (n_lo < p.N) ((float*)p.y)[o + n_lo] = tot[nt][0];
+                if (n_lo + 8 < p.N) ((float*)p.y)[o + n_lo + 8] = tot[nt][1];
+              } else {
+                if (n_lo < p.N) ((uint16_t*)p.y)[o + n_lo] = f32_to_bf16_bits(tot[nt][0]);
+                if (n_lo + 8 < p.N) ((uint16_t*)p.y)[o + n_lo + 8] = f32_to_bf16_bits(tot[nt][1]);
+              }
+            }
+          }
+        }
+        cp_async_wait<0>();
+      }
+    }
+  }
+}
+
+int sm_count_g() {
+  static int cached[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+size_t smem_bytes(int K) {
+  return (size_t)kWarps * kStages * kStageBytes + (size_t)(K / 32) * 2 * 256 + (size_t)(K / 64) * 2 * 4 * 8 + 64;
+}
+
+}  // namespace
+
+bool gather_stream_supported(const GatherArgs& a) {
+  if (!((a.bits == 4 && (a.gs == 64 || a.gs == 128)) || (a.bits == 8 && a.gs == 64))) return false;
+  if (a.x_dtype != QB200_BFLOAT16 && a.x_dtype != QB200_FLOAT32) return false;
+  if (a.M != 1 || a.K % 256 != 0 || a.K <= 0 || a.K > 4096) return false;
+  if (a.N <= 0 || a.N > (1 << 24) || a.I <= 0 || a.I > kMaxRows || a.E > kMaxExperts) return false;
+  if ((((uintptr_t)a.w) & 15) != 0 || (a.w_expert_stride * 4) % 16 != 0) return false;
+  if ((((uintptr_t)a.s) & 7) != 0 || (((uintptr_t)a.b) & 7) != 0 || (a.s_expert_stride * 2) % 8 != 0) return false;
+  if (a.gs == 64 && (a.K / 64) % 4 != 0) return false;
+  if (a.gs == 128 && (a.K / 128) % 2 != 0) return false;
+  if ((((uintptr_t)a.x) & 15) != 0 || (a.x_batch_stride * (a.x_dtype == QB200_FLOAT32 ? 4 : 2)) % 16 != 0) return false;
+  if (a.rhs_dtype != QB200_INT64 && a.rhs_dtype != QB200_INT32 && a.rhs_dtype != QB200_UINT32) return false;
+  if (a.lhs && a.lhs_dtype != QB200_INT64 && a.lhs_dtype != QB200_INT32 && a.lhs_dtype != QB200_UINT32) return false;
+  return smem_bytes((int)a.K) + 14 * 1024 <= 227 * 1024;
+}
+
+cudaError_t launch_gather_stream(const GatherArgs& a, cudaStream_t st) {
+  GK p;
+  p.x = a.x; p.w = a.w; p.s = (const uint16_t*)a.s; p.b = (const uint16_t*)a.b; p.y = a.y;
+  p.rhs = a.rhs; p.lhs = a.lhs;
+  p.rhs_i64 = a.rhs_dtype == QB200_INT64; p.lhs_i64 = a.lhs_dtype == QB200_INT64;
+  p.xbcast = a.xbcast;
+  p.I = a.I; p.E = a.E; p.XB = a.XB; p.xstride = a.x_batch_stride;
+  p.wes = a.w_expert_stride; p.ses = a.s_expert_stride;
+  p.N = (int)a.N; p.K = (int)a.K; p.gshift = a.gs == 128 ? 1 : 0; p.x_f32 = a.x_dtype == QB200_FLOAT32;
+  const size_t smem = smem_bytes(p.K);
+  static bool done[2][64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int bi = a.bits == 4 ? 0 : 1;
+  if (dev < 0 || dev >= 64 || !done[bi][dev]) {
+    cudaError_t e = a.bits == 4
+        ? cudaFuncSetAttribute(gather_stream_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+        : cudaFuncSetAttribute(gather_stream_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) done[bi][dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(sm_count_g());
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (a.bits == 4) return cudaLaunchKernelEx(&cfg, gather_stream_kernel<4>, p);
+  return cudaLaunchKernelEx(&cfg, gather_stream_kernel<8>, p);
+}
+
+}  // namespace qb

@@ -70,6 +70,8 @@ struct GatherArgs {
 bool gather_mma_supported(const GatherArgs& a);
 cudaError_t launch_gather_mma(const GatherArgs& a, cudaStream_t st);
 cudaError_t launch_gather_generic(const GatherArgs& a, cudaStream_t st);
+bool gather_stream_supported(const GatherArgs& a);   // qmv_stream.cu: persistent streaming kernel, gather form
+cudaError_t launch_gather_stream(const GatherArgs& a, cudaStream_t st);
 
 // ---- kv_attn.cu ----
 struct KvAttnArgs {

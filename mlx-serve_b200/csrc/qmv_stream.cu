@@ -527,7 +527,7 @@ bool plan_stream(StreamK& p, int NT, bool M1, int* grid_out, size_t* smem_out) {
   if (p.npass > 1) smem += (size_t)kGroups * p.ntl_max * NT * 256;
   *grid_out = grid;
   *smem_out = smem;
-  return smem <= (M1 ? 113 : 227) * 1024;
+  return smem <= (size_t)(M1 ? 113 : 227) * 1024;
 }
 
 void pick_inst(const StreamK& p, int* NT, bool* M1) {
