@@ -1,0 +1,46 @@
+//! Zig externs for libqb200 (include/qb200.h).  Text only: Zig is not installed where this
+//! library is built, so this file has not been compiled; it restates the C declarations one
+//! for one, next to the mlx-c externs of mlx-serve's src/mlx.zig that they replace.
+const std = @import("std");
+
+pub const MAX_DIMS = 8;
+
+/// qb200_tensor: device pointer + dtype (same numbers as mlx_dtype, src/mlx.zig:20-35) + shape
+/// and strides in elements.  `.{}` (null data, ndim 0) stands for mlx-c's empty handle.
+pub const Tensor = extern struct {
+    data: ?*anyopaque = null,
+    dtype: i32 = 0,
+    ndim: i32 = 0,
+    shape: [MAX_DIMS]i64 = [_]i64{0} ** MAX_DIMS,
+    stride: [MAX_DIMS]i64 = [_]i64{0} ** MAX_DIMS,
+};
+pub const OptionalInt = extern struct { value: c_int = 0, has_value: bool = false };
+pub const OptionalDtype = extern struct { value: c_int = 0, has_value: bool = false };
+pub const Stream = ?*anyopaque; // cudaStream_t
+
+pub const ErrorHandler = ?*const fn ([*:0]const u8, ?*anyopaque) callconv(.c) void;
+pub extern "c" fn qb200_set_error_handler(handler: ErrorHandler, data: ?*anyopaque, dtor: ?*const fn (?*anyopaque) callconv(.c) void) void;
+pub extern "c" fn qb200_last_error() [*:0]const u8;
+
+// replaces mlx_quantized_matmul (src/mlx.zig:262)
+pub extern "c" fn qb200_quantized_matmul(res: *Tensor, x: *const Tensor, w: *const Tensor, scales: *const Tensor, biases: *const Tensor, transpose_w: bool, group_size: OptionalInt, bits: OptionalInt, mode: [*:0]const u8, s: Stream) c_int;
+pub extern "c" fn qb200_quantized_matmul_batch(res: [*]const *Tensor, x: *const Tensor, w: [*]const *const Tensor, scales: [*]const *const Tensor, biases: [*]const *const Tensor, count: c_int, transpose_w: bool, group_size: OptionalInt, bits: OptionalInt, mode: [*:0]const u8, s: Stream) c_int;
+pub extern "c" fn qb200_quantized_matmul_shape(x: *const Tensor, w: *const Tensor, scales: *const Tensor, transpose_w: bool, group_size: OptionalInt, bits: OptionalInt, out_shape: [*]i64, out_ndim: *i32) c_int;
+// replaces mlx_gather_qmm (src/mlx.zig:265)
+pub extern "c" fn qb200_gather_qmm(res: *Tensor, x: *const Tensor, w: *const Tensor, scales: *const Tensor, biases: *const Tensor, lhs_indices: *const Tensor, rhs_indices: *const Tensor, transpose_w: bool, group_size: OptionalInt, bits: OptionalInt, mode: [*:0]const u8, sorted_indices: bool, s: Stream) c_int;
+// replaces mlx_dequantize (src/mlx.zig:271)
+pub extern "c" fn qb200_dequantize(res: *Tensor, w: *const Tensor, scales: *const Tensor, biases: *const Tensor, group_size: OptionalInt, bits: OptionalInt, mode: [*:0]const u8, global_scale: *const Tensor, dtype: OptionalDtype, s: Stream) c_int;
+// replaces mlx_quantize (src/mlx.zig:275); results in mlx-c's vector order [q, scales, biases]
+pub extern "c" fn qb200_quantize(res_q: *Tensor, res_scales: *Tensor, res_biases: *Tensor, w: *const Tensor, group_size: OptionalInt, bits: OptionalInt, mode: [*:0]const u8, global_scale: *const Tensor, s: Stream) c_int;
+// replaces kv_quant.quantAttention / qkvAttnDecodeKernel + qkvMergePartials at T_q = 1
+pub extern "c" fn qb200_kv_decode_attention(res: *Tensor, q: *const Tensor, k_q: *const Tensor, k_scales: *const Tensor, k_biases: *const Tensor, v_q: *const Tensor, v_scales: *const Tensor, v_biases: *const Tensor, bits: c_int, group_size: c_int, scale: f32, mask_mode: [*:0]const u8, mask_arr: *const Tensor, kv_lens: *const Tensor, workspace: ?*anyopaque, workspace_bytes: usize, s: Stream) c_int;
+pub extern "c" fn qb200_kv_decode_attention_workspace_size(B: i64, Hq: i64, Hkv: i64, T: i64, Dv: i64) usize;
+// replaces steps 2 and 5 of KVCache.updateAffine (src/transformer.zig:3224-3337)
+pub extern "c" fn qb200_kv_append(cache_q: *Tensor, cache_scales: *Tensor, cache_biases: *Tensor, dense: *const Tensor, offset: i64, bits: c_int, group_size: c_int, s: Stream) c_int;
+
+/// Same convention as mlx.check (src/mlx.zig:547-550): 0 is success.  UNSUPPORTED (1) means
+/// "declined": the caller keeps its existing mlx-c path for that call.
+pub fn check(ret: c_int) !void {
+    if (ret == 1) return error.Qb200Declined;
+    if (ret != 0) return error.Qb200Error;
+}
