@@ -190,6 +190,26 @@ QB200_API int qb200_kv_decode_attention(qb200_tensor* res, const qb200_tensor* q
 QB200_API size_t qb200_kv_decode_attention_workspace_size(int64_t B, int64_t Hq, int64_t Hkv, int64_t T,
                                                           int64_t Dv);
 
+/* ---- the same attention for callers that cannot allocate device memory ----
+ * No counterpart in the reference (MLX allocates its own temporaries).  Identical arguments and
+ * results to qb200_kv_decode_attention minus the workspace: the split-KV partials go to an 8 MiB
+ * array built into the library (qb200_kv_decode_attention_noalloc_max_scratch() bytes, held on
+ * every GPU that loads the library until the process exits).  Shapes whose partials do not fit are
+ * rejected with QB200_ERR_WORKSPACE before anything is launched.  The call itself allocates and
+ * frees nothing.  The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress); make that first call outside any stream capture.  All calls on a device
+ * share the one array and its contents are whatever the last call left there (each call overwrites
+ * every entry it later reads, so nothing needs clearing); two calls whose kernels overlap on the
+ * GPU -- different streams, or one stream per thread -- race on it and must be serialised by the
+ * caller. */
+QB200_API int qb200_kv_decode_attention_noalloc(qb200_tensor* res, const qb200_tensor* q, const qb200_tensor* k_q,
+                                                const qb200_tensor* k_scales, const qb200_tensor* k_biases,
+                                                const qb200_tensor* v_q, const qb200_tensor* v_scales,
+                                                const qb200_tensor* v_biases, int bits, int group_size, float scale,
+                                                const char* mask_mode, const qb200_tensor* mask_arr,
+                                                const qb200_tensor* kv_lens, qb200_stream s);
+QB200_API size_t qb200_kv_decode_attention_noalloc_max_scratch(void);
+
 /* ---- quantise new K/V rows into the cache in place ----
  * Steps 2 and 5 of KVCache.updateAffine (src/transformer.zig:3224-3337):
  * quantise dense [B, Hkv, S, D] and write the triple at token `offset` of the

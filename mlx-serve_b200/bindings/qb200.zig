@@ -35,6 +35,9 @@ pub extern "c" fn qb200_quantize(res_q: *Tensor, res_scales: *Tensor, res_biases
 // replaces kv_quant.quantAttention / qkvAttnDecodeKernel + qkvMergePartials at T_q = 1
 pub extern "c" fn qb200_kv_decode_attention(res: *Tensor, q: *const Tensor, k_q: *const Tensor, k_scales: *const Tensor, k_biases: *const Tensor, v_q: *const Tensor, v_scales: *const Tensor, v_biases: *const Tensor, bits: c_int, group_size: c_int, scale: f32, mask_mode: [*:0]const u8, mask_arr: *const Tensor, kv_lens: *const Tensor, workspace: ?*anyopaque, workspace_bytes: usize, s: Stream) c_int;
 pub extern "c" fn qb200_kv_decode_attention_workspace_size(B: i64, Hq: i64, Hkv: i64, T: i64, Dv: i64) usize;
+// no counterpart in mlx-c: the same attention with scratch from an 8 MiB array inside the library
+pub extern "c" fn qb200_kv_decode_attention_noalloc(res: *Tensor, q: *const Tensor, k_q: *const Tensor, k_scales: *const Tensor, k_biases: *const Tensor, v_q: *const Tensor, v_scales: *const Tensor, v_biases: *const Tensor, bits: c_int, group_size: c_int, scale: f32, mask_mode: [*:0]const u8, mask_arr: *const Tensor, kv_lens: *const Tensor, s: Stream) c_int;
+pub extern "c" fn qb200_kv_decode_attention_noalloc_max_scratch() usize;
 // replaces steps 2 and 5 of KVCache.updateAffine (src/transformer.zig:3224-3337)
 pub extern "c" fn qb200_kv_append(cache_q: *Tensor, cache_scales: *Tensor, cache_biases: *Tensor, dense: *const Tensor, offset: i64, bits: c_int, group_size: c_int, s: Stream) c_int;
 

@@ -203,6 +203,11 @@ BatchMap make_batchmap(const qb200_tensor* t, int inner, const QmmPlan& p) {
 
 }  // namespace
 
+namespace qb {
+// Records an error message and notifies the handler, for entry points that live in other files.
+int report_error(int status, const char* msg) { return fail(status, "%s", msg); }
+}  // namespace qb
+
 extern "C" {
 
 QB200_API void qb200_set_error_handler(qb200_error_handler_func handler, void* data, void (*dtor)(void*)) {

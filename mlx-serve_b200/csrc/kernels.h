@@ -5,6 +5,8 @@
 
 namespace qb {
 
+int report_error(int status, const char* msg);  // api.cu: last-error string + handler
+
 // ---- elementwise.cu ----
 struct DequantArgs {
   const uint32_t* w; const void* s; const void* b; void* out;

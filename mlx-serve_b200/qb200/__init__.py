@@ -82,6 +82,10 @@ def lib():
         L.qb200_kv_append.argtypes = [TP, TP, TP, TP, C.c_int64, C.c_int, C.c_int, C.c_void_p]
         L.qb200_kv_decode_attention.argtypes = [TP, TP, TP, TP, TP, TP, TP, TP, C.c_int, C.c_int, C.c_float,
                                                 C.c_char_p, TP, TP, C.c_void_p, C.c_size_t, C.c_void_p]
+        L.qb200_kv_decode_attention_noalloc.argtypes = [TP, TP, TP, TP, TP, TP, TP, TP, C.c_int, C.c_int, C.c_float,
+                                                        C.c_char_p, TP, TP, C.c_void_p]
+        L.qb200_kv_decode_attention_noalloc.restype = C.c_int
+        L.qb200_kv_decode_attention_noalloc_max_scratch.restype = C.c_size_t
         L.qb200_kv_decode_attention_workspace_size.restype = C.c_size_t
         L.qb200_kv_decode_attention_workspace_size.argtypes = [C.c_int64] * 5
         for name in ("qb200_quantized_matmul", "qb200_quantized_matmul_batch", "qb200_quantized_matmul_shape", "qb200_gather_qmm", "qb200_dequantize",
@@ -237,4 +241,17 @@ def kv_decode_attention(q, k_triple, v_triple, bits, group_size, scale, mask_mod
     check(L.qb200_kv_decode_attention(*[C.byref(a) for a in args], int(bits), int(group_size), float(scale),
                                       mask_mode.encode(), C.byref(dm), C.byref(dl),
                                       C.c_void_p(workspace.data_ptr()), workspace.numel(), _stream()))
+    return out
+
+
+def kv_decode_attention_noalloc(q, k_triple, v_triple, bits, group_size, scale, out, mask_mode="", mask=None,
+                                kv_lens=None):
+    """kv_decode_attention for callers that cannot allocate: scratch comes from the array built into the library.
+    ``out`` must be preallocated; nothing is allocated on the device by this call."""
+    L = lib()
+    args = [desc(out), desc(q), _packed(k_triple[0]), desc(k_triple[1]), desc(k_triple[2]), _packed(v_triple[0]),
+            desc(v_triple[1]), desc(v_triple[2])]
+    dm, dl = desc(mask), desc(kv_lens)
+    check(L.qb200_kv_decode_attention_noalloc(*[C.byref(a) for a in args], int(bits), int(group_size), float(scale),
+                                              mask_mode.encode(), C.byref(dm), C.byref(dl), _stream()))
     return out
