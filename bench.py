@@ -161,6 +161,8 @@ def main():
     ap.add_argument("--no-batch", action="store_true", help="seven separate calls per layer instead of four")
     ap.add_argument("--micro-kv", action="store_true", help="decode attention over the packed KV cache (config 5) and exit")
     ap.add_argument("--micro-moe", action="store_true", help="routed-MoE gather_qmm decode (config 3, 64 tokens) and exit")
+    ap.add_argument("--micro-moe-ep", action="store_true",
+                    help="expert-parallel MoE block (config 3, 64 tokens per GPU) over all ranks and exit")
     ap.add_argument("--micro-prefill", action="store_true", help="dense prefill qmm (config 4) and exit")
     ap.add_argument("--micro", action="store_true", help="per-projection timings (us per launch, GB/s) and exit")
     args = ap.parse_args()
@@ -182,7 +184,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     qb200.lib()  # fail loudly if the library is not built
 
-    M, L = args.m, (0 if (args.micro_kv or args.micro_prefill or args.micro_moe) else args.layers)
+    M, L = args.m, (0 if (args.micro_kv or args.micro_prefill or args.micro_moe or args.micro_moe_ep) else args.layers)
     g = torch.Generator(device=dev).manual_seed(0xC2 + rank)
     layers = []
     for _ in range(L):
@@ -252,6 +254,42 @@ def main():
             dist.barrier()
             ms = float(t.item())
         return ms
+
+    if args.micro_moe_ep:
+        from qb200 import ep
+        E, H, I, T, topk = 128, 2048, 768, 64, 8
+        per = E // world
+        banks = {}
+        for name, (n, k) in (("gate", (I, H)), ("up", (I, H)), ("down", (H, I))):
+            w = (torch.randn((per, n, k), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+            banks[name] = qb200.quantize(w, 64, 4)
+            del w
+        fn = ep.default_expert_fn(banks)
+        xtok = torch.randn((T, H), device=dev, generator=g).to(torch.bfloat16)
+        inds, wts = ep.route(torch.randn((T, E), device=dev, generator=g), topk)
+        for _ in range(3):
+            out = ep.moe_block_ep(xtok, inds, wts, E, fn)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            out = ep.moe_block_ep(xtok, inds, wts, E, fn)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        if world > 1:
+            tt = torch.tensor([ms], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt.item())
+        if rank == 0:
+            print(json.dumps({"ms_per_block": ms, "tokens_per_s": world * T / (ms * 1e-3), "n_gpus": world,
+                              "experts_per_gpu": per, "nan": bool(torch.isnan(out).any())}))
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
 
     if args.micro_moe:
         E, H, I, T, topk = 128, 2048, 768, 64, 8
