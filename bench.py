@@ -41,6 +41,12 @@ def layer_bytes(M, bits=BITS, gs=GS):
     return tot
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the same launches, from the ncu
+# capture summarised in profiles/qmv_stream_c2_decode.md: (14.263 + 9.545) MB measured for the q/k/v and o launches
+# at M=8 against 14.156 + 0.164 + 9.437 + 0.131 MB algorithmic.  Traffic scales with the bytes a launch streams.
+NCU_TRAFFIC_OVER_ALGORITHMIC = 23.808 / 23.888
+
+
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -473,7 +479,10 @@ def main():
                        "weights replicated, no collective" % world},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": which, "frac_of_nominal_8TBs": achieved / 8000.0,
-                         "bytes_per_launch": layer_bytes(M) / (7.0 if args.no_batch else 4.0), "kernel": "qmv_stream_kernel", "traffic": None},
+                         "bytes_per_launch": layer_bytes(M) / (7.0 if args.no_batch else 4.0), "kernel": "qmv_stream_kernel",
+                         "traffic": NCU_TRAFFIC_OVER_ALGORITHMIC * layer_bytes(M) / (7.0 if args.no_batch else 4.0),
+                         "traffic_source": "ncu dram__bytes_read+write of the q/k/v and o launches (2-layer capture), "
+                                           "scaled by algorithmic bytes to the average launch"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": xin.numel() * 2,
                     "d2h_bytes_per_step": yout.numel() * 2, "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": args.steps * L * (7 if args.no_batch else 4) * launches_per_call,
