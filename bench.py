@@ -304,33 +304,51 @@ def main():
             w = (torch.randn((E, n, k), device=dev, generator=g) * 0.02).to(torch.bfloat16)
             banks[name] = qb200.quantize(w, 64, 4)
             del w
-        logits = torch.randn((T, E), device=dev, generator=g)
-        inds = torch.topk(torch.softmax(logits, -1), topk, dim=-1).indices.reshape(-1)
-        order = torch.argsort(inds, stable=True)
-        sorted_inds = inds[order].to(torch.int32).contiguous()
-        xtok = torch.randn((T, H), device=dev, generator=g).to(torch.bfloat16)
-        x_rep = xtok[order // topk].reshape(T * topk, 1, H).contiguous()
-        act = torch.randn((T * topk, 1, I), device=dev, generator=g).to(torch.bfloat16)
-        yg = torch.empty((T * topk, 1, I), dtype=torch.bfloat16, device=dev)
-        yu = torch.empty_like(yg)
-        yd = torch.empty((T * topk, 1, H), dtype=torch.bfloat16, device=dev)
-        uniq = int(torch.unique(sorted_inds).numel())
-
-        def run():
-            qb200.gather_qmm(x_rep, *banks["gate"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yg)
-            qb200.gather_qmm(x_rep, *banks["up"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yu)
-            qb200.gather_qmm(act, *banks["down"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yd)
-        run()
-        torch.cuda.synchronize()
-        gr = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(gr):
-            run()
-        ms = time_graph(gr, args.steps, 3) / args.steps
         per_expert = 786432 + 2 * 49152
-        by = 3 * uniq * per_expert + T * topk * 2 * (2 * (H + I) + (I + H))
+        res = {}
+
+        def block(T, inds):
+            """Buffers and the three gather_qmm calls of one MoE block for T tokens routed to `inds` [T*topk]."""
+            order = torch.argsort(inds, stable=True)
+            sorted_inds = inds[order].to(torch.int32).contiguous()
+            xtok = torch.randn((T, H), device=dev, generator=g).to(torch.bfloat16)
+            x_rep = xtok[order // topk].reshape(T * topk, 1, H).contiguous()
+            act = torch.randn((T * topk, 1, I), device=dev, generator=g).to(torch.bfloat16)
+            yg = torch.empty((T * topk, 1, I), dtype=torch.bfloat16, device=dev)
+            yu = torch.empty_like(yg)
+            yd = torch.empty((T * topk, 1, H), dtype=torch.bfloat16, device=dev)
+
+            def run():
+                qb200.gather_qmm(x_rep, *banks["gate"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yg)
+                qb200.gather_qmm(x_rep, *banks["up"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yu)
+                qb200.gather_qmm(act, *banks["down"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yd)
+            return run, int(torch.unique(sorted_inds).numel())
+
+        # 64 tokens: one block touches (nearly) every expert, 340 MB of banks > L2.
+        # 1 token: 16 blocks in the graph, each routed to a disjoint set of 8 experts, so the replay still
+        # streams all 128 experts from HBM instead of re-reading 21 MB from L2.
+        for T in (64, 1):
+            if T == 64:
+                logits = torch.randn((T, E), device=dev, generator=g)
+                runs = [block(T, torch.topk(torch.softmax(logits, -1), topk, dim=-1).indices.reshape(-1))]
+            else:
+                perm = torch.randperm(E, device=dev, generator=g)
+                runs = [block(T, perm[i * topk:(i + 1) * topk]) for i in range(E // topk)]
+            for r, _ in runs:
+                r()
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                for r, _ in runs:
+                    r()
+            ms = time_graph(gr, args.steps, 3) / args.steps / len(runs)
+            uniq = runs[0][1]
+            by = 3 * uniq * per_expert + T * topk * 2 * (2 * (H + I) + (I + H))
+            res[f"tokens{T}"] = {"us_per_block": ms * 1e3, "unique_experts": uniq, "bytes": by,
+                                 "GBps": by / (ms * 1e-3) / 1e9}
+            del gr
         if rank == 0:
-            print(json.dumps({"us_per_block": ms * 1e3, "unique_experts": uniq, "bytes": by,
-                              "GBps": by / (ms * 1e-3) / 1e9}))
+            print(json.dumps(res))
         return
 
     if args.micro_prefill:

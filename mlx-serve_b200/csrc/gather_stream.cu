@@ -10,12 +10,14 @@
 //
 // Decomposition (HBM-bound, one pass over every expert that is hit):
 //  * a persistent grid (one CTA of 16 warps per SM).  Every CTA derives the same
-//    ascending list of experts that occur in rhs, then takes (expert, share of
-//    the expert's 16-row tiles) work items round-robin.  With few active experts
-//    the tiles of one expert are spread over many CTAs; with many, a CTA sweeps
-//    whole experts.
-//  * for its expert the CTA collects the output rows routed to it (any order in
-//    rhs works; `sorted_indices` is never needed for correctness), stages their
+//    per-expert row counts from rhs.  An expert with c rows costs ceil(c/8)
+//    sweeps over its N/16 row tiles; the (expert, sweep, tile) triples are
+//    numbered in that order and CTA i takes the i-th equal share of the
+//    numbering, so every SM streams the same number of tiles however the
+//    router spread the rows.
+//  * for each (expert, sweep) segment of its share the CTA looks up the sweep's
+//    output rows (in ascending order of their position in rhs, so that all CTAs
+//    agree; `sorted_indices` is never needed for correctness), stages their
 //    activations as two s8 fixed-point planes per row (8 rows per sweep), and
 //    each warp owns whole 16-row tiles: it streams the tile's K range through a
 //    private cp.async ring, multiplies on the integer tensor cores
@@ -88,10 +90,9 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
   constexpr int U = BITS == 4 ? 4 : 2;   // 64-wide groups per unit
   constexpr int CK = 64 * U;             // K values per unit (128 bytes per row)
   constexpr int NT = 2;
-  __shared__ int s_act[kMaxExperts];            // ascending list of the experts that occur in rhs
-  __shared__ unsigned s_flags[kMaxExperts / 32];
-  __shared__ int s_nact, s_nrows;
-  __shared__ int s_rows[kMaxRows];              // output rows routed to the current expert
+  __shared__ int s_cum[kMaxExperts + 1];        // tiles of work before expert e (exclusive prefix), [E] = total
+  __shared__ int s_cnt[kMaxExperts];            // rows routed to expert e
+  __shared__ unsigned short s_rhs[kMaxRows];    // expert of every output row (0xFFFF: out of range)
   __shared__ long long s_xi[kRowsPerSweep];     // activation row of each slot (-1: empty)
   __shared__ int s_orow[kRowsPerSweep];         // output row of each slot (-1: empty)
 
@@ -99,7 +100,8 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
   unsigned char* sp = smem;
   unsigned char* ring = sp;    sp += (size_t)kWarps * kStages * kStageBytes;
   uint2* xfrag = (uint2*)sp;   sp += (size_t)(p.K / 32) * NT * 32 * 8;
-  float* gsc = (float*)sp;     // [(group*NT + nt)*4 + row][2]: (2^(E-14), 2^(E-14) * sum v)
+  float* gsc = (float*)sp;     sp += (size_t)(p.K / 64) * NT * 4 * 8;  // [(group*NT + nt)*4 + row][2]: (2^(E-14), 2^(E-14) * sum v)
+  float* red = (float*)sp;     // [warp][nt][2][lane]: partial sums of warps that share a tile's K range
   const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring + (size_t)warp * kStages * kStageBytes);
   const unsigned char* my_ring_p = ring + (size_t)warp * kStages * kStageBytes;
 
@@ -107,32 +109,53 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  // ---- every CTA derives the same ascending list of active experts ----
-  for (int i = tid; i < kMaxExperts / 32; i += kThreads) s_flags[i] = 0u;
+  // ---- every CTA derives the same per-expert row counts and the prefix of their cost in tiles ----
+  const int E = (int)p.E, I = (int)p.I;
+  const int tiles_n = (p.N + 15) / 16;
+  for (int i = tid; i < E; i += kThreads) s_cnt[i] = 0;
   __syncthreads();
-  for (int64_t i = tid; i < p.I; i += kThreads) {
+  for (int i = tid; i < I; i += kThreads) {
     const long long e = load_index(p.rhs, p.rhs_i64, i);
-    if (e >= 0 && e < p.E) atomicOr(&s_flags[e >> 5], 1u << (e & 31));
+    const bool in = e >= 0 && e < p.E;
+    s_rhs[i] = in ? (unsigned short)e : (unsigned short)0xFFFF;
+    if (in) atomicAdd(&s_cnt[(int)e], 1);
   }
   __syncthreads();
   if (warp == 0) {
     int base = 0;
-    const int nwords = (int)((p.E + 31) / 32);
-    for (int wd = 0; wd < nwords; ++wd) {
-      const unsigned word = s_flags[wd];
-      if ((word >> lane) & 1u) s_act[base + __popc(word & ((1u << lane) - 1u))] = wd * 32 + lane;
-      base += __popc(word);
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      const int cost = e < E ? ((s_cnt[e] + kRowsPerSweep - 1) / kRowsPerSweep) * tiles_n : 0;
+      int inc = cost;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += o;
+      }
+      if (e < E) s_cum[e] = base + inc - cost;
+      base += __shfl_sync(0xffffffffu, inc, 31);
     }
-    if (lane == 0) s_nact = base;
+    if (lane == 0) s_cum[E] = base;
   }
   __syncthreads();
-  const int nact = s_nact;
-  if (nact == 0) return;
-  const int tiles_n = (p.N + 15) / 16;
-  int parts = (int)gridDim.x / nact;
-  parts = parts < 1 ? 1 : (parts > tiles_n ? tiles_n : parts);
-  const int per = (tiles_n + parts - 1) / parts;
-  const int nitems = nact * parts;
+  const int W = s_cum[E];
+  if (W == 0) return;
+  // This CTA's share [lo, hi) of the numbering.  With many (expert, sweep) segments: equal shares, which
+  // may straddle two segments.  With few (single-token decode): every segment is cut into the same number
+  // of chunks so that no CTA pays the per-segment set-up twice.
+  int lo, hi;
+  const int nseg = W / tiles_n;
+  if (nseg * 2 <= (int)gridDim.x) {
+    const int cps = (int)gridDim.x / nseg;                 // chunks per segment
+    const int c = (tiles_n + cps - 1) / cps;               // tiles per chunk
+    const int seg = blockIdx.x / cps, ch = blockIdx.x - seg * cps;
+    if (seg >= nseg || ch * c >= tiles_n) return;
+    lo = seg * tiles_n + ch * c;
+    hi = (ch + 1) * c < tiles_n ? lo + c : (seg + 1) * tiles_n;
+  } else {
+    lo = (int)((long long)W * blockIdx.x / gridDim.x);
+    hi = (int)((long long)W * (blockIdx.x + 1) / gridDim.x);
+  }
   const int ut = p.K / CK;
 
   // per-lane constants of the ring
@@ -151,39 +174,84 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
     else frag_off[j] = g * 128 + (((4 * j + t) ^ swz<8>(g)) << 4);
   }
 
-  for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
-    const int e = s_act[item / parts], part = item % parts;
-    const int t0 = part * per;
-    const int t1 = (t0 + per) < tiles_n ? (t0 + per) : tiles_n;
+  int e = 0;
+  {  // first expert whose share of the numbering reaches past lo (s_cum is non-decreasing)
+    int a = 0, b = E;  // invariant: s_cum[a] <= lo < s_cum[b]
+    while (b - a > 1) {
+      const int m = (a + b) >> 1;
+      if (s_cum[m] <= lo) a = m; else b = m;
+    }
+    e = a;
+  }
+  for (int pos = lo; pos < hi;) {
+    while (s_cum[e + 1] <= pos) ++e;           // skips experts without rows
+    const int off = pos - s_cum[e];
+    const int sweep = off / tiles_n, t0 = off - sweep * tiles_n;
+    const int t1 = (t0 + (hi - pos)) < tiles_n ? (t0 + (hi - pos)) : tiles_n;
+    pos += t1 - t0;
     const uint32_t* wexp = p.w + (int64_t)e * p.wes;
     const uint16_t* sexp = p.s + (int64_t)e * p.ses;
     const uint16_t* bexp = p.b + (int64_t)e * p.ses;
     const int64_t ldw = (int64_t)p.K * BITS / 32, lds = p.K >> (6 + p.gshift);
+    const int r0 = sweep * kRowsPerSweep;
+    const int nrows = s_cnt[e];
 
-    // ---- the output rows routed to this expert (order is irrelevant: rows are independent) ----
-    __syncthreads();
-    if (tid == 0) s_nrows = 0;
-    __syncthreads();
-    for (int64_t i = tid; i < p.I; i += kThreads)
-      if (load_index(p.rhs, p.rhs_i64, i) == (long long)e) {
-        const int pos = atomicAdd(&s_nrows, 1);
-        if (pos < kMaxRows) s_rows[pos] = (int)i;
+    // ---- start streaming this warp's weights right away: they do not depend on the activations ----
+    const int seg_tiles = t1 - t0;
+    int ksplit = 1;
+    while (ksplit * 2 * seg_tiles <= kWarps && ksplit * 2 <= ut) ksplit *= 2;
+    const int kp = warp % ksplit;
+    const int first = ksplit == 1 ? t0 + warp : t0 + warp / ksplit;
+    const int my_tiles = first < t1 ? (ksplit == 1 ? (t1 - first + kWarps - 1) / kWarps : 1) : 0;
+    const int nu = (ut - kp + ksplit - 1) / ksplit;   // units of one tile handled by this warp
+    const int total = my_tiles * nu;
+    int issued = 0, consumed = 0, ptile = 0, pu = kp;  // producer position: (tile index, unit)
+    auto issue = [&](int stage) {
+      const int tile = first + ptile * kWarps;
+      const uint32_t st = my_ring + stage * kStageBytes;
+      const int64_t woff = (int64_t)pu * 128;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        int n = tile * 16 + (lane >> 3) + 4 * r;
+        n = n < p.N ? n : p.N - 1;
+        cp_async16(st + wdst[r], (const unsigned char*)(wexp + (int64_t)n * ldw) + woff + chunk * 16);
       }
-    __syncthreads();
-    const int nrows = s_nrows < kMaxRows ? s_nrows : kMaxRows;
+      int n = tile * 16 + (lane & 15);
+      n = n < p.N ? n : p.N - 1;
+      const uint16_t* ssrc = ((lane >> 4) ? bexp : sexp) + (int64_t)n * lds + ((pu * U) >> p.gshift);
+      if (BITS == 4 && p.gshift == 0) cp_async8(st + sbdst, ssrc);
+      else cp_async4(st + sbdst, ssrc);
+      pu += ksplit;
+      if (pu >= ut) { pu = kp; ++ptile; }
+    };
+#pragma unroll
+    for (int i = 0; i < kStages - 1; ++i) {
+      if (issued < total) issue(issued % kStages);
+      cp_async_commit();
+      ++issued;
+    }
 
-    for (int r0 = 0; r0 < nrows; r0 += kRowsPerSweep) {
-      __syncthreads();  // previous sweep has finished with xfrag / slots
-      if (tid < kRowsPerSweep) {
-        long long xi = -1;
-        int orow = -1;
-        if (r0 + tid < nrows) {
-          orow = s_rows[r0 + tid];
-          xi = p.lhs ? load_index(p.lhs, p.lhs_i64, orow) : (long long)p.xbcast.offset(orow);
-          if (xi < 0 || xi >= p.XB) { xi = -1; orow = -1; }
+    {
+      __syncthreads();  // previous segment has finished with xfrag / slots
+      // ---- rows r0 .. r0+7 of this expert in ascending rhs position ----
+      if (warp == 0) {
+        if (lane < kRowsPerSweep) { s_xi[lane] = -1; s_orow[lane] = -1; }
+        __syncwarp();
+        int seen = 0;
+        for (int i0 = 0; i0 < I && seen < r0 + kRowsPerSweep; i0 += 32) {
+          const int i = i0 + lane;
+          const bool hit = i < I && s_rhs[i] == (unsigned short)e;
+          const unsigned bal = __ballot_sync(0xffffffffu, hit);
+          const int rank = seen + __popc(bal & ((1u << lane) - 1u));
+          if (hit && rank >= r0 && rank < r0 + kRowsPerSweep) {
+            long long xi = p.lhs ? load_index(p.lhs, p.lhs_i64, i) : (long long)p.xbcast.offset(i);
+            int orow = i;
+            if (xi < 0 || xi >= p.XB) { xi = -1; orow = -1; }
+            s_xi[rank - r0] = xi;
+            s_orow[rank - r0] = orow;
+          }
+          seen += __popc(bal);
         }
-        s_xi[tid] = xi;
-        s_orow[tid] = orow;
       }
       __syncthreads();
       const int nte = (nrows - r0) > 4 ? 2 : 1;  // n8 tiles in use
@@ -249,40 +317,34 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
         }
       }
       __syncthreads();
-      // ---- each warp owns whole 16-row tiles of the CTA's share ----
-      {
-        const int first = t0 + warp;
-        const int my_tiles = first < t1 ? (t1 - first + kWarps - 1) / kWarps : 0;
-        const int total = my_tiles * ut;
-        int issued = 0, consumed = 0, ptile = 0, pu = 0;  // producer position: (tile index, unit)
-        auto issue = [&](int stage) {
-          const int tile = first + ptile * kWarps;
-          const uint32_t st = my_ring + stage * kStageBytes;
-          const int64_t woff = (int64_t)pu * 128;
+      // lane (g, t) holds weight rows g, g+8 of a tile for the row in slot nt*4 + t
+      auto store_tile = [&](int tile, const float (&tot)[NT][2]) {
+        const int n_lo = tile * 16 + g;
 #pragma unroll
-          for (int r = 0; r < 4; ++r) {
-            int n = tile * 16 + (lane >> 3) + 4 * r;
-            n = n < p.N ? n : p.N - 1;
-            cp_async16(st + wdst[r], (const unsigned char*)(wexp + (int64_t)n * ldw) + woff + chunk * 16);
+        for (int nt = 0; nt < NT; ++nt) {
+          const int orow = s_orow[nt * 4 + t];
+          if (nt < nte && orow >= 0) {
+            const int64_t o = (int64_t)orow * p.N;
+            if (p.x_f32) {
+              if (n_lo < p.N) ((float*)p.y)[o + n_lo] = tot[nt][0];
+              if (n_lo + 8 < p.N) ((float*)p.y)[o + n_lo + 8] = tot[nt][1];
+            } else {
+              if (n_lo < p.N) ((uint16_t*)p.y)[o + n_lo] = f32_to_bf16_bits(tot[nt][0]);
+              if (n_lo + 8 < p.N) ((uint16_t*)p.y)[o + n_lo + 8] = f32_to_bf16_bits(tot[nt][1]);
+            }
           }
-          int n = tile * 16 + (lane & 15);
-          n = n < p.N ? n : p.N - 1;
-          const uint16_t* ssrc = ((lane >> 4) ? bexp : sexp) + (int64_t)n * lds + ((pu * U) >> p.gshift);
-          if (BITS == 4 && p.gshift == 0) cp_async8(st + sbdst, ssrc);
-          else cp_async4(st + sbdst, ssrc);
-          if (++pu == ut) { pu = 0; ++ptile; }
-        };
-#pragma unroll
-        for (int i = 0; i < kStages - 1; ++i) {
-          if (issued < total) issue(issued % kStages);
-          cp_async_commit();
-          ++issued;
         }
+      };
+      // ---- each warp owns whole 16-row tiles of the segment; when the segment has fewer tiles than
+      //      the CTA has warps, `ksplit` warps share a tile's K range and reduce through shared memory ----
+      {
+        float tot[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = 0.f;
         for (int ti = 0; ti < my_tiles; ++ti) {
-          float tot[NT][2];
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = 0.f;
-          for (int u = 0; u < ut; ++u) {
+          for (int u = kp; u < ut; u += ksplit) {
             if (issued < total) issue(issued % kStages);
             cp_async_commit();
             ++issued;
@@ -351,24 +413,23 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
             }
             __syncwarp();
           }
-          // ---- store the tile: lane (g, t) holds weight rows g, g+8 for the row in slot nt*4 + t ----
-          const int n_lo = (first + ti * kWarps) * 16 + g;
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {
-            const int orow = s_orow[nt * 4 + t];
-            if (nt < nte && orow >= 0) {
-              const int64_t o = (int64_t)orow * p.N;
-              if (p.x_f32) {
-                if (n_lo < p.N) ((float*)p.y)[o + n_lo] = tot[nt][0];
-                if (n_lo + 8 < p.N) ((float*)p.y)[o + n_lo + 8] = tot[nt][1];
-              } else {
-                if (n_lo < p.N) ((uint16_t*)p.y)[o + n_lo] = f32_to_bf16_bits(tot[nt][0]);
-                if (n_lo + 8 < p.N) ((uint16_t*)p.y)[o + n_lo + 8] = f32_to_bf16_bits(tot[nt][1]);
-              }
-            }
-          }
+          if (ksplit == 1) store_tile(first + ti * kWarps, tot);
         }
         cp_async_wait<0>();
+        if (ksplit > 1) {   // uniform over the CTA: every warp reaches both barriers
+          float* mine = red + (size_t)warp * (NT * 2 * 32);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) { mine[(nt * 2 + 0) * 32 + lane] = tot[nt][0]; mine[(nt * 2 + 1) * 32 + lane] = tot[nt][1]; }
+          __syncthreads();
+          if (kp == 0 && my_tiles > 0) {
+            for (int k = 1; k < ksplit; ++k) {
+              const float* o = red + (size_t)(warp + k) * (NT * 2 * 32);
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) { tot[nt][0] += o[(nt * 2 + 0) * 32 + lane]; tot[nt][1] += o[(nt * 2 + 1) * 32 + lane]; }
+            }
+            store_tile(first, tot);
+          }
+        }
       }
     }
   }
@@ -388,7 +449,7 @@ int sm_count_g() {
 }
 
 size_t smem_bytes(int K) {
-  return (size_t)kWarps * kStages * kStageBytes + (size_t)(K / 32) * 2 * 256 + (size_t)(K / 64) * 2 * 4 * 8 + 64;
+  return (size_t)kWarps * kStages * kStageBytes + (size_t)(K / 32) * 2 * 256 + (size_t)(K / 64) * 2 * 4 * 8 + (size_t)kWarps * 2 * 2 * 32 * 4 + 64;
 }
 
 }  // namespace
@@ -405,7 +466,7 @@ bool gather_stream_supported(const GatherArgs& a) {
   if ((((uintptr_t)a.x) & 15) != 0 || (a.x_batch_stride * (a.x_dtype == QB200_FLOAT32 ? 4 : 2)) % 16 != 0) return false;
   if (a.rhs_dtype != QB200_INT64 && a.rhs_dtype != QB200_INT32 && a.rhs_dtype != QB200_UINT32) return false;
   if (a.lhs && a.lhs_dtype != QB200_INT64 && a.lhs_dtype != QB200_INT32 && a.lhs_dtype != QB200_UINT32) return false;
-  return smem_bytes((int)a.K) + 14 * 1024 <= 227 * 1024;
+  return smem_bytes((int)a.K) + 14 * 1024 <= 227 * 1024;  // + static shared memory
 }
 
 cudaError_t launch_gather_stream(const GatherArgs& a, cudaStream_t st) {

@@ -7,21 +7,35 @@
 // (src/transformer.zig:20894-20983).  The weight term is rounded to bf16 once,
 // exactly as that route's dequantised transient is (src/transformer.zig:20872-20873);
 // accumulation is fp32 in tensor memory.  No [N, K] transient ever reaches HBM:
-// each CTA dequantises the 128 x 64 weight tile it is about to multiply
-// straight into the swizzled shared-memory operand.
+// each CTA dequantises the weight tile it is about to multiply straight into the
+// swizzled shared-memory operand.
 //
-// CTA tile: 256 tokens x 128 weight rows, K in steps of 64.
-//   warp 4 lane 0 : TMA producer -- two 128x64 bf16 boxes of x per stage
-//                   (cp.async.bulk.tensor.2d, SWIZZLE_128B, no multicast), then
-//                   the single-thread tcgen05.mma issuer (M=128, N=128, K=16 x4,
-//                   two accumulators of 128 columns in TMEM) and tcgen05.commit.
-//   warps 0-3     : one thread per weight row: packed codes -> exact bf16
-//                   integers (byte shuffles) -> one bf16 FMA with the group's
-//                   scale and bias -> the K-major SWIZZLE_128B operand row;
-//                   after the main loop the same warps drain TMEM
-//                   (tcgen05.ld 32x32b) and store bf16 rows of y.
+// Persistent, warp-specialised CTAs (one per SM) walk the output tiles of
+// 256 tokens x BN weight rows (BN <= 128, chosen per problem so that the last
+// wave of tiles is full), K in steps of 64 through a 4-stage ring:
+//   warps 0-15 : dequantisers in two groups of 8 warps that take alternate
+//                k-blocks (a warp's per-k-block latency -- barrier wait, byte
+//                shuffles, proxy fence -- is what bounds this role, so two
+//                k-blocks are always being converted side by side).  Two threads
+//                per weight row: packed codes -> exact bf16 integers (byte
+//                shuffles) -> one bf16 FMA with the group's scale and bias ->
+//                the K-major SWIZZLE_128B operand row.  The packed codes come
+//                from a shared-memory ring that TMA fills (below); scales and
+//                biases are fetched eight k-groups at a time, one window ahead.
+//   warps 16-19: epilogue: tcgen05.ld of a finished accumulator, bf16 rows of y.
+//                Tensor memory holds two accumulator sets (2 x 2 x 128 columns),
+//                so the epilogue of tile i overlaps the main loop of tile i+1.
+//   warp 20    : TMA producer -- two 128x64 bf16 boxes of x per stage
+//                (cp.async.bulk.tensor.2d, SWIZZLE_128B, no multicast).
+//   warp 21    : TMA producer for the packed codes: 128 bytes of each of the
+//                tile's BN weight rows per copy (SWIZZLE_128B, no multicast),
+//                double-buffered.  Per-lane global loads of the codes would
+//                touch 32 cache lines per instruction and saturate the L1 data
+//                path that the tensor core's operand reads share.
+//   warp 22    : the single-thread tcgen05.mma issuer (M=128, N=BN, K=16 x4 per
+//                stage and accumulator) and its tcgen05.commit arrivals.
 // Every mbarrier wait is bounded: on expiry the kernel records an error code,
-// leaves its loops, frees its tensor memory and returns.
+// every role leaves its loops, the CTA frees its tensor memory and returns.
 #include <cuda.h>
 
 #include "kernels.h"
@@ -29,11 +43,16 @@
 namespace qb {
 namespace {
 
-constexpr int BM = 256, BN = 128, BK = 64, STAGES = 4;
-constexpr int kDequantThreads = 128;
-constexpr int kThreads = kDequantThreads + 32;
+constexpr int BM = 256, BN_MAX = 128, BK = 64, STAGES = 4;
+constexpr int kDequantGroups = 2;                   // group g converts the k-blocks with (index % 2) == g
+constexpr int kDequantWarps = 8 * kDequantGroups, kEpiWarps = 4;
+constexpr int kDequantThreads = 256;                 // threads that fill one stage: two per weight row
+constexpr int kEpiWarp0 = kDequantWarps;            // warps 16..19: warp % 4 = TMEM lane quarter
+constexpr int kTmaWarp = kEpiWarp0 + kEpiWarps, kWTmaWarp = kTmaWarp + 1, kMmaWarp = kWTmaWarp + 1;
+constexpr int kThreads = (kMmaWarp + 1) * 32;
 constexpr int A_STAGE_BYTES = BM * BK * 2;   // two 128-row boxes
-constexpr int B_STAGE_BYTES = BN * BK * 2;
+constexpr int B_STAGE_BYTES = BN_MAX * BK * 2;
+constexpr int RAW_BYTES = BN_MAX * 128;      // one super-block of packed codes: 128 bytes of every weight row
 constexpr uint32_t kSpinLimit = 1u << 24;
 
 __device__ int g_tc_error = 0;  // 0 = ok; otherwise the code of the wait that expired
@@ -43,6 +62,9 @@ struct TcK {
   int M, N, K;
   int64_t ldw, lds, ldy;
   int gshift;   // scale column = (k / 64) >> gshift
+  int BN;       // weight rows per tile (multiple of 16, <= 128)
+  int tiles_m, ntiles;
+  int sb_vec;   // scales / biases can be fetched 8 at a time (16-byte aligned rows, whole windows)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -86,13 +108,13 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
   d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
   return d;
 }
-// bf16 x bf16 -> f32, A and B K-major, M = 128, N = 128
-__device__ __forceinline__ uint32_t make_idesc() {
+// bf16 x bf16 -> f32, A and B K-major, M = 128, N = bn
+__device__ __forceinline__ uint32_t make_idesc(int bn) {
   uint32_t d = 0;
   d |= 1u << 4;                  // c format f32
   d |= 1u << 7;                  // a format bf16
   d |= 1u << 10;                 // b format bf16
-  d |= (uint32_t)(BN >> 3) << 17;
+  d |= (uint32_t)(bn >> 3) << 17;
   d |= (uint32_t)(128 >> 4) << 24;
   return d;
 }
@@ -118,17 +140,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr));
 }
 
-// 64 codes of one weight row -> 64 bf16 values q*s+b (one rounding), written as the 128-byte row
-// `r` of a K-major SWIZZLE_128B tile (16-byte chunk c lands at chunk c ^ (r & 7)).
+// 32 codes (half of a k-block) of one weight row -> 32 bf16 values q*s+b (one rounding), written as
+// chunks 4h..4h+3 of the 128-byte row `r` of a K-major SWIZZLE_128B tile (16-byte chunk c lands at
+// chunk c ^ (r & 7)).
 template <int BITS>
-__device__ __forceinline__ void dequant_row(const uint32_t* codes, uint32_t sb2, uint32_t bb2, unsigned char* tile, int r) {
+__device__ __forceinline__ void dequant_half(const uint32_t* codes, uint32_t sb2, uint32_t bb2, unsigned char* tile, int r,
+                                             int h) {
   // sb2 / bb2: the group's scale / bias replicated in both bf16 lanes
   const __nv_bfloat162 s2 = *(const __nv_bfloat162*)&sb2, b2 = *(const __nv_bfloat162*)&bb2;
   unsigned char* row = tile + r * 128;
+  const int xr = ((4 * h) ^ (r & 7)) << 4;   // chunk (4h + c) ^ (r & 7) = ((4h) ^ (r & 7)) ^ c for c < 4
   if constexpr (BITS == 4) {
     const __nv_bfloat162 c128 = __float2bfloat162_rn(128.f);
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {  // one packed word = 8 values = one 16-byte chunk of bf16
+    for (int c = 0; c < 4; ++c) {  // one packed word = 8 values = one 16-byte chunk of bf16
       const uint32_t w = codes[c];
       // bytes (q1q0, q3q2, q5q4, q7q6) -> bytes q0,q1,q2,q3 and q4,q5,q6,q7 in order
       const uint32_t lo = __byte_perm(w, 0, 0x4140), hi = __byte_perm(w, 0, 0x4342);
@@ -146,53 +171,58 @@ __device__ __forceinline__ void dequant_row(const uint32_t* codes, uint32_t sb2,
         v = __hfma2(v, s2, b2);       // q*s + b, rounded once
         o[j] = *(uint32_t*)&v;
       }
-      *(uint4*)(row + ((c ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+      *(uint4*)(row + (xr ^ (c << 4))) = make_uint4(o[0], o[1], o[2], o[3]);
     }
   } else {
     const float sf = bf16lo(sb2), bf = bf16lo(bb2);
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {  // two packed words = 8 values
+    for (int c = 0; c < 4; ++c) {  // two packed words = 8 values
       uint32_t o[4];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const uint32_t w = codes[2 * c + h];
+      for (int q = 0; q < 2; ++q) {
+        const uint32_t w = codes[2 * c + q];
         const float f0 = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540)) - 8388608.f;
         const float f1 = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7541)) - 8388608.f;
         const float f2 = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7542)) - 8388608.f;
         const float f3 = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7543)) - 8388608.f;
-        o[2 * h] = pack_bf16x2(fmaf(f0, sf, bf), fmaf(f1, sf, bf));
-        o[2 * h + 1] = pack_bf16x2(fmaf(f2, sf, bf), fmaf(f3, sf, bf));
+        o[2 * q] = pack_bf16x2(fmaf(f0, sf, bf), fmaf(f1, sf, bf));
+        o[2 * q + 1] = pack_bf16x2(fmaf(f2, sf, bf), fmaf(f3, sf, bf));
       }
-      *(uint4*)(row + ((c ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+      *(uint4*)(row + (xr ^ (c << 4))) = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
 }
 
 template <int BITS>
-__global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_constant__ CUtensorMap xmap, TcK p) {
+__global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, TcK p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // 1024-byte alignment for the swizzled tiles
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* a_tiles = smem;                                   // [STAGES][2][128 x 64 bf16]
-  unsigned char* b_tiles = smem + STAGES * A_STAGE_BYTES;          // [STAGES][128 x 64 bf16]
-  uint64_t* bars = (uint64_t*)(b_tiles + STAGES * B_STAGE_BYTES);  // full_a[S], full_b[S], empty[S], acc
-  uint64_t* full_a = bars, *full_b = bars + STAGES, *empty = bars + 2 * STAGES, *acc_bar = bars + 3 * STAGES;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 3 * STAGES + 1);
-  __shared__ int s_fail;
+  unsigned char* b_tiles = smem + STAGES * A_STAGE_BYTES;          // [STAGES][BN x 64 bf16]
+  unsigned char* raw = b_tiles + STAGES * B_STAGE_BYTES;           // [2][BN x 128 B of packed codes]
+  uint64_t* bars = (uint64_t*)(raw + 2 * RAW_BYTES);
+  uint64_t* full_a = bars, *full_b = bars + STAGES, *empty = bars + 2 * STAGES;
+  uint64_t* acc_full = bars + 3 * STAGES, *acc_empty = bars + 3 * STAGES + 2;
+  uint64_t* raw_full = bars + 3 * STAGES + 4, *raw_empty = bars + 3 * STAGES + 6;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 3 * STAGES + 8);
+  volatile int& s_fail = *(volatile int*)(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int nkb = p.K / BK;
-  constexpr int WPK = BK * BITS / 32;  // packed words per row per k-block
+  const int BN = p.BN;
+  constexpr int WPH = (BK / 2) * BITS / 32;  // packed words per half row per k-block (4 or 8)
+  constexpr int KPS = 128 * 8 / (BK * BITS);  // k-blocks per 128-byte super-block of codes (4 or 2)
 
   if (tid == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full_a[i], 1); mbar_init(&full_b[i], kDequantThreads); mbar_init(&empty[i], 1); }
-    mbar_init(acc_bar, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], kEpiWarps * 32); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], kDequantWarps * 32); }
     s_fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) {  // tensor-memory allocation: 256 columns (two 128x128 fp32 accumulators)
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u));
+  if (warp == kMmaWarp) {  // tensor memory: 512 columns = two sets of two 128x128 fp32 accumulators
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -200,124 +230,200 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  // Tile t of this CTA's list: token block t % tiles_m (fastest, so that CTAs running side by side
+  // share a weight tile through L2), weight block t / tiles_m.
+  if (warp == kTmaWarp) {
     if (lane == 0) {
-      // ---------------- TMA producer + MMA issuer (one thread) ----------------
-      const uint32_t idesc = make_idesc();
-      const bool two_halves = m0 + 128 < p.M;  // the second 128 token rows hold real tokens
-      int fail = 0;
-      // prologue: fill the pipeline
-      int loaded = 0;
-      for (; loaded < STAGES && loaded < nkb; ++loaded) {
-        mbar_expect_tx(&full_a[loaded], A_STAGE_BYTES);
-        const uint32_t dst = smem_u32(a_tiles + loaded * A_STAGE_BYTES);
-        tma_load_2d(dst, &xmap, &full_a[loaded], loaded * BK, m0);
-        tma_load_2d(dst + 128 * BK * 2, &xmap, &full_a[loaded], loaded * BK, m0 + 128);
-      }
-      for (int kb = 0; kb < nkb && !fail; ++kb) {
-        const int st = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        if (!mbar_wait(&full_a[st], ph)) { fail = 1; break; }
-        if (!mbar_wait(&full_b[st], ph)) { fail = 2; break; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = smem_u32(a_tiles + st * A_STAGE_BYTES), b_addr = smem_u32(b_tiles + st * B_STAGE_BYTES);
-#pragma unroll
-        for (int k16 = 0; k16 < BK / 16; ++k16) {
-          const uint64_t bd = make_desc(b_addr + k16 * 32);
-          const uint32_t accum = (kb > 0 || k16 > 0) ? 1u : 0u;
-          umma(tmem_base, make_desc(a_addr + k16 * 32), bd, idesc, accum);
-          if (two_halves) umma(tmem_base + 128, make_desc(a_addr + 128 * BK * 2 + k16 * 32), bd, idesc, accum);
-        }
-        umma_commit(&empty[st]);  // frees this stage once the MMAs above have read it
-        // refill the stage of the PREVIOUS k-block (its MMAs finish while the ones just issued are queued)
-        if (kb >= 1 && loaded < nkb) {
-          const int ls = (kb - 1) % STAGES;
-          if (!mbar_wait(&empty[ls], ((kb - 1) / STAGES) & 1)) { fail = 3; break; }
-          mbar_expect_tx(&full_a[ls], A_STAGE_BYTES);
-          const uint32_t dst = smem_u32(a_tiles + ls * A_STAGE_BYTES);
-          tma_load_2d(dst, &xmap, &full_a[ls], loaded * BK, m0);
-          tma_load_2d(dst + 128 * BK * 2, &xmap, &full_a[ls], loaded * BK, m0 + 128);
-          ++loaded;
+      // ---------------- TMA producer (one thread) ----------------
+      int it = 0, fail = 0;
+      for (int tile = blockIdx.x; tile < p.ntiles && !fail && !s_fail; tile += gridDim.x) {
+        const int m0 = (tile % p.tiles_m) * BM;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int st = it % STAGES;
+          if (it >= STAGES && !mbar_wait(&empty[st], ((it / STAGES) - 1) & 1)) { fail = 3; break; }
+          mbar_expect_tx(&full_a[st], A_STAGE_BYTES);
+          const uint32_t dst = smem_u32(a_tiles + st * A_STAGE_BYTES);
+          tma_load_2d(dst, &xmap, &full_a[st], kb * BK, m0);
+          tma_load_2d(dst + 128 * BK * 2, &xmap, &full_a[st], kb * BK, m0 + 128);
         }
       }
-      umma_commit(acc_bar);
       if (fail) { s_fail = fail; atomicExch(&g_tc_error, fail); }
     }
-  } else {
-    // ---------------- dequant producers: thread = weight row ----------------
-    const int r = tid;
-    int n = n0 + r;
-    n = n < p.N ? n : p.N - 1;
-    const uint32_t* wrow = p.w + (int64_t)n * p.ldw;
-    const uint16_t* srow = p.s + (int64_t)n * p.lds;
-    const uint16_t* brow = p.b + (int64_t)n * p.lds;
-    uint32_t codes[WPK], ncodes[WPK];
-    uint32_t sc = 0, bi = 0, nsc = 0, nbi = 0;
-    auto fetch = [&](int kb, uint32_t (&c)[WPK], uint32_t& s2, uint32_t& b2) {
-      const uint4* src = (const uint4*)(wrow + (int64_t)kb * WPK);
-#pragma unroll
-      for (int i = 0; i < WPK / 4; ++i) {
-        const uint4 v = __ldg(src + i);
-        c[4 * i] = v.x; c[4 * i + 1] = v.y; c[4 * i + 2] = v.z; c[4 * i + 3] = v.w;
+  } else if (warp == kWTmaWarp) {
+    if (lane == 0) {
+      // ---------------- TMA producer of the packed codes (one thread) ----------------
+      const int sb_per_tile = nkb / KPS;
+      int sbk = 0, fail = 0;
+      for (int tile = blockIdx.x; tile < p.ntiles && !fail && !s_fail; tile += gridDim.x) {
+        const int n0 = (tile / p.tiles_m) * BN;
+        for (int sbl = 0; sbl < sb_per_tile; ++sbl, ++sbk) {
+          const int buf = sbk & 1;
+          if (sbk >= 2 && !mbar_wait(&raw_empty[buf], ((sbk >> 1) - 1) & 1)) { fail = 7; break; }
+          mbar_expect_tx(&raw_full[buf], (uint32_t)BN * 128u);
+          tma_load_2d(smem_u32(raw + buf * RAW_BYTES), &wmap, &raw_full[buf], sbl * 32, n0);
+        }
       }
-      const uint32_t sv = __ldg(srow + (kb >> p.gshift)), bv = __ldg(brow + (kb >> p.gshift));
-      s2 = sv | (sv << 16);
-      b2 = bv | (bv << 16);
+      if (fail) { s_fail = fail; atomicExch(&g_tc_error, fail); }
+    }
+  } else if (warp == kMmaWarp) {
+    if (lane == 0) {
+      // ---------------- MMA issuer (one thread) ----------------
+      const uint32_t idesc = make_idesc(BN);
+      const uint64_t adesc0 = make_desc(smem_u32(a_tiles)), bdesc0 = make_desc(smem_u32(b_tiles));
+      int it = 0, fail = 0, ti = 0;
+      for (int tile = blockIdx.x; tile < p.ntiles && !fail && !s_fail; tile += gridDim.x, ++ti) {
+        const int m0 = (tile % p.tiles_m) * BM;
+        const bool two_halves = m0 + 128 < p.M;  // the second 128 token rows hold real tokens
+        const int buf = ti & 1;
+        if (ti >= 2 && !mbar_wait(&acc_empty[buf], ((ti >> 1) - 1) & 1)) { fail = 6; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t d0 = tmem_base + buf * 256;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int st = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full_a[st], ph)) { fail = 1; break; }
+          if (!mbar_wait(&full_b[st], ph)) { fail = 2; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          // descriptors of the stage: the start-address field counts 16-byte units, so a K step of
+          // 16 values (32 bytes) adds 2 and the second 128-row box of x adds 16 KiB / 16
+          const uint64_t ad0 = adesc0 + (uint64_t)(st * (A_STAGE_BYTES >> 4)), bd0 = bdesc0 + (uint64_t)(st * (B_STAGE_BYTES >> 4));
+#pragma unroll
+          for (int k16 = 0; k16 < BK / 16; ++k16) {
+            const uint32_t accum = (kb > 0 || k16 > 0) ? 1u : 0u;
+            umma(d0, ad0 + 2 * k16, bd0 + 2 * k16, idesc, accum);
+            if (two_halves) umma(d0 + 128, ad0 + ((128 * BK * 2) >> 4) + 2 * k16, bd0 + 2 * k16, idesc, accum);
+          }
+          umma_commit(&empty[st]);  // frees this stage (A and B) once the MMAs above have read it
+        }
+        if (fail) break;
+        umma_commit(&acc_full[buf]);
+      }
+      if (fail) { s_fail = fail; atomicExch(&g_tc_error, fail); }
+    }
+  } else if (warp < kDequantWarps) {
+    // ---------------- dequant producers: two threads per weight row, two groups ----------------
+    const int grp = warp >> 3, wg = warp & 7;
+    const int r = (wg & 3) * 32 + lane, h = wg >> 2;
+    const bool active = r < BN;
+    const int ntl = (p.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;  // tiles of this CTA
+    const int total_it = ntl * nkb;
+    // Scales and biases of this thread's row: windows of 8 values (8 << gshift k-blocks), the next
+    // window prefetched while the current one is used.  f_* is the prefetch cursor (tile, k-block).
+    const int WL = 8 << p.gshift;
+    uint4 s_cur = make_uint4(0, 0, 0, 0), b_cur = s_cur, s_nxt = s_cur, b_nxt = s_cur;
+    int f_tl = 0, f_kb = 0;
+    auto row_of = [&](int tl) {
+      const int tile = blockIdx.x + tl * gridDim.x;
+      const int n = (tile / p.tiles_m) * BN + r;
+      return n < p.N ? n : p.N - 1;
     };
-    if (nkb > 0) fetch(0, codes, sc, bi);
+    auto prefetch_window = [&]() {
+      if (f_kb >= nkb) { f_kb = 0; ++f_tl; }
+      if (active && f_tl < ntl) {
+        const int64_t off = (int64_t)row_of(f_tl) * p.lds + (f_kb >> p.gshift);
+        s_nxt = __ldg((const uint4*)(p.s + off));
+        b_nxt = __ldg((const uint4*)(p.b + off));
+      }
+      f_kb += WL;
+    };
+    if (p.sb_vec) prefetch_window();
     bool ok = true;
-    for (int kb = 0; kb < nkb; ++kb) {
-      const int st = kb % STAGES;
-      if (kb + 1 < nkb) fetch(kb + 1, ncodes, nsc, nbi);
-      if (kb >= STAGES && ok) ok = mbar_wait(&empty[st], ((kb / STAGES) - 1) & 1);
-      if (!ok) break;
-      dequant_row<BITS>(codes, sc, bi, b_tiles + st * B_STAGE_BYTES, r);
+    for (int it = grp; it < total_it; it += kDequantGroups) {
+      const int st = it % STAGES;
+      const int tl = it / nkb, kb = it - tl * nkb;
+      const int sbk = it / KPS, kbl = it % KPS, buf = sbk & 1;   // nkb is a multiple of KPS
+      uint32_t sv2, bv2;
+      if (p.sb_vec) {
+        if ((kb & (WL - 1)) == grp) {   // this group's first k-block of a window
+          s_cur = s_nxt; b_cur = b_nxt;
+          prefetch_window();
+        }
+        const int e = (kb >> p.gshift) & 7;
+        const uint32_t sw = e < 4 ? (e < 2 ? s_cur.x : s_cur.y) : (e < 6 ? s_cur.z : s_cur.w);
+        const uint32_t bw = e < 4 ? (e < 2 ? b_cur.x : b_cur.y) : (e < 6 ? b_cur.z : b_cur.w);
+        sv2 = (e & 1) ? __byte_perm(sw, sw, 0x3232) : __byte_perm(sw, sw, 0x1010);
+        bv2 = (e & 1) ? __byte_perm(bw, bw, 0x3232) : __byte_perm(bw, bw, 0x1010);
+      } else {
+        const int64_t off = (int64_t)row_of(tl) * p.lds + (kb >> p.gshift);
+        const uint32_t sv = active ? __ldg(p.s + off) : 0u, bv = active ? __ldg(p.b + off) : 0u;
+        sv2 = sv | (sv << 16);
+        bv2 = bv | (bv << 16);
+      }
+      ok = mbar_wait(&raw_full[buf], (sbk >> 1) & 1);
+      if (!ok || s_fail) { ok = false; break; }
+      uint32_t c[WPH];
+      if (active) {
+        const unsigned char* rrow = raw + buf * RAW_BYTES + r * 128;
+#pragma unroll
+        for (int i = 0; i < WPH / 4; ++i) {
+          const int chunk = kbl * (2 * WPH / 4) + h * (WPH / 4) + i;
+          const uint4 v = *(const uint4*)(rrow + ((chunk ^ (r & 7)) << 4));
+          c[4 * i] = v.x; c[4 * i + 1] = v.y; c[4 * i + 2] = v.z; c[4 * i + 3] = v.w;
+        }
+      }
+      if (it >= STAGES) ok = mbar_wait(&empty[st], ((it / STAGES) - 1) & 1);
+      if (!ok || s_fail) { ok = false; break; }
+      if (active) dequant_half<BITS>(c, sv2, bv2, b_tiles + st * B_STAGE_BYTES, r, h);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> async proxy (UMMA)
       mbar_arrive(&full_b[st]);
-#pragma unroll
-      for (int i = 0; i < WPK; ++i) codes[i] = ncodes[i];
-      sc = nsc; bi = nbi;
+      // Release the codes buffer only now that the loaded words have been consumed: the arrival is not
+      // ordered behind a shared-memory load whose result no instruction has waited for yet, and the
+      // TMA refill must not overtake this thread's last read.
+      if (kbl + kDequantGroups >= KPS) mbar_arrive(&raw_empty[buf]);
     }
-    if (!ok) atomicExch(&g_tc_error, 4);
+    if (!ok && !s_fail) { s_fail = 4; atomicExch(&g_tc_error, 4); }
+  } else {
     // ---------------- epilogue: TMEM -> registers -> bf16 rows of y ----------------
-    bool acc_ok = ok && mbar_wait(acc_bar, 0);
-    if (!acc_ok) atomicExch(&g_tc_error, 5);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (acc_ok && s_fail == 0) {
+    const int q = warp & 3;   // TMEM lane quarter this warp may read
+    int ti = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, ++ti) {
+      const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
+      const int nend = (n0 + BN) < p.N ? (n0 + BN) : p.N;
+      const int buf = ti & 1;
+      ok = mbar_wait(&acc_full[buf], (ti >> 1) & 1);
+      if (!ok || s_fail) { ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
       for (int half = 0; half < 2; ++half) {
         if (half == 1 && m0 + 128 >= p.M) break;
-        const int m = m0 + half * 128 + warp * 32 + lane;  // TMEM lane = token row
+        const int m = m0 + half * 128 + q * 32 + lane;  // TMEM lane = token row
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
           uint32_t v[32];
-          tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + half * 128 + c0, v);
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + half * 128 + c0, v);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           if (m < p.M) {
             uint16_t* yrow = p.y + (int64_t)m * p.ldy + n0 + c0;
-            if (n0 + c0 + 32 <= p.N && (((uintptr_t)yrow) & 15) == 0) {
+            const int nvalid = nend - (n0 + c0);   // columns of this chunk inside the matrix and the tile
+            const bool aligned = (((uintptr_t)yrow) & 15) == 0;
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < 4; ++j) {
+              if (aligned && 8 * j + 8 <= nvalid) {
                 uint4 o;
                 o.x = pack_bf16x2(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1]));
                 o.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
                 o.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
                 o.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
                 *(uint4*)(yrow + 8 * j) = o;
+              } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                  if (8 * j + i < nvalid) yrow[8 * j + i] = f32_to_bf16_bits(__uint_as_float(v[8 * j + i]));
               }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (n0 + c0 + j < p.N) yrow[j] = f32_to_bf16_bits(__uint_as_float(v[j]));
             }
           }
         }
       }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(&acc_empty[buf]);  // this accumulator set may be overwritten
     }
+    if (!ok && !s_fail) { s_fail = 5; atomicExch(&g_tc_error, 5); }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 4) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u));
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u));
   }
 }
 
@@ -339,7 +445,35 @@ EncodeFn get_encode() {
   return fn;
 }
 
-constexpr size_t kSmemBytes = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + (3 * STAGES + 1) * 8 + 16 + 1024;
+constexpr size_t kSmemBytes = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 2 * RAW_BYTES + (3 * STAGES + 8) * 8 + 16 + 1024;
+
+int sm_count_tc() {
+  static int cached[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+// Weight rows per tile: the candidate whose tile count fills the last wave best
+// (time ~ waves x (rows per tile + a fixed per-tile cost)).
+int pick_bn(int64_t M, int64_t N, int nsm) {
+  const int64_t tiles_m = (M + BM - 1) / BM;
+  int best = BN_MAX;
+  int64_t best_cost = -1;
+  for (int bn = BN_MAX; bn >= 64; bn -= 16) {
+    const int64_t tiles = tiles_m * ((N + bn - 1) / bn);
+    const int64_t waves = (tiles + nsm - 1) / nsm;
+    const int64_t cost = waves * (bn + 12);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+  }
+  return best;
+}
 
 }  // namespace
 
@@ -348,7 +482,7 @@ bool qmm_tc_supported(const QmmArgs& a) {
   if (a.bits != 4 && a.bits != 8) return false;
   if (a.gs != 64 && a.gs != 128) return false;
   if (a.x_dtype != QB200_BFLOAT16) return false;
-  if (a.K % BK != 0 || a.K < BK || a.N < 1 || a.M < 1) return false;
+  if (a.K % 256 != 0 || a.K < 256 || a.N < 1 || a.M < 1) return false;   // whole 128-byte super-blocks of codes
   if (a.M > (1 << 24) || a.N > (1 << 24)) return false;
   if ((((uintptr_t)a.x) & 15) != 0 || (a.ldx * 2) % 16 != 0) return false;
   if ((((uintptr_t)a.w) & 15) != 0 || (a.ldw * 4) % 16 != 0) return false;
@@ -370,6 +504,20 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, cudaStream_t st) {
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
   TcK p;
+  const int nsm = sm_count_tc();
+  p.BN = pick_bn(a.M, a.N, nsm);
+  // packed codes as a [N][K * bits / 32] array of 32-bit words: 128 bytes of BN rows per copy
+  CUtensorMap wmap;
+  {
+    const cuuint64_t wdims[2] = {(cuuint64_t)(a.K * a.bits / 32), (cuuint64_t)a.N};
+    const cuuint64_t wstrides[1] = {(cuuint64_t)a.ldw * 4};
+    const cuuint32_t wbox[2] = {32, (cuuint32_t)p.BN};
+    const void* wptr = (const void*)(a.w + a.wb.offset(0));
+    r = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)wptr, wdims, wstrides, wbox, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  }
   p.w = a.w + a.wb.offset(0);
   p.s = (const uint16_t*)a.s + a.sb.offset(0);
   p.b = (const uint16_t*)a.b + a.sb.offset(0);
@@ -377,7 +525,10 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, cudaStream_t st) {
   p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
   p.ldw = a.ldw; p.lds = a.lds; p.ldy = a.ldy;
   p.gshift = a.gs == 128 ? 1 : 0;
-  dim3 grid((unsigned)((a.N + BN - 1) / BN), (unsigned)((a.M + BM - 1) / BM), 1);
+  p.sb_vec = (a.lds % 8 == 0) && ((((uintptr_t)p.s) | ((uintptr_t)p.b)) & 15) == 0 && (a.K % (512 << p.gshift)) == 0;
+  p.tiles_m = (int)((a.M + BM - 1) / BM);
+  p.ntiles = p.tiles_m * (int)((a.N + p.BN - 1) / p.BN);
+  dim3 grid((unsigned)(p.ntiles < nsm ? p.ntiles : nsm), 1, 1);
   static bool done[2][64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -389,8 +540,8 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, cudaStream_t st) {
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) done[bi][dev] = true;
   }
-  if (a.bits == 4) qmm_tc_kernel<4><<<grid, kThreads, kSmemBytes, st>>>(map, p);
-  else qmm_tc_kernel<8><<<grid, kThreads, kSmemBytes, st>>>(map, p);
+  if (a.bits == 4) qmm_tc_kernel<4><<<grid, kThreads, kSmemBytes, st>>>(map, wmap, p);
+  else qmm_tc_kernel<8><<<grid, kThreads, kSmemBytes, st>>>(map, wmap, p);
   return cudaGetLastError();
 }
 

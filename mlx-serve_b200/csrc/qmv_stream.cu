@@ -84,6 +84,23 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 __device__ __forceinline__ void group_barrier(int grp) {
   asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "n"(kWarpsPerGroup * 32) : "memory");
 }
+// Thread-block cluster helpers (distributed shared memory): the CTAs of a cluster split the conversion of
+// the activations and write every converted fragment into the shared memory of all of them.
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t cluster_size() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_v2(uint32_t addr, uint32_t x, uint32_t y) {
+  asm volatile("st.shared::cluster.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(x), "r"(y) : "memory");
+}
+// All threads of all CTAs of the cluster (a hardware barrier: no spinning in software).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // D(16x8,s32) += A(16x32,u8,row) * B(32x8,s8,col)
 __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
@@ -176,6 +193,9 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
   const uint2* zero8 = (const uint2*)sp; sp += 16;  // an all-zero B fragment for the unused columns
   float* yacc = (float*)sp;    // [kGroups][ntl_max][NT*64], only when npass > 1
   if (threadIdx.x == 0) *(uint2*)zero8 = make_uint2(0u, 0u);
+  // A CTA's shared memory may only be written by its cluster peers once it is running: arrive now, and
+  // wait for every peer's arrival just before the first remote store.
+  if constexpr (!M1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 
   const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring + (size_t)warp * kStages * kStageBytes);
   const unsigned char* my_ring_p = ring + (size_t)warp * kStages * kStageBytes;
@@ -246,6 +266,7 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
   // its writes to be visible) before reading activations or writing outputs.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  if constexpr (!M1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 
   int consumed = 0;
   int red_buf = 0;
@@ -253,7 +274,9 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
   for (int pass = 0; pass < p.npass; ++pass) {
     const int k_base = pass * kc;
     const int klen = (p.K - k_base) < kc ? (p.K - k_base) : kc;
-    if (pass > 0) __syncthreads();
+    if (pass > 0) {  // every reader of the previous pass's fragments (cluster-wide) is done
+      if constexpr (M1) __syncthreads(); else cluster_sync_all();
+    }
     // ---- stage this pass's activations as s8 planes in B-fragment order ----
     // One thread converts 8 consecutive K values of one token; the 8 lanes that cover a 64-wide
     // group agree on the group's power-of-two scale (|x| * up < 2^14) through shuffles.
@@ -262,11 +285,14 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
       const int slots = M1 ? 1 : NT * kTokPerTile;
       const int total = slots * cpt;
       constexpr int PF = 4;  // chunks fetched per thread before any is converted (loads in flight together)
-      for (int base0 = 0; base0 < total; base0 += kThreads * PF) {
+      // The CTAs of a cluster take interleaved blocks of kThreads chunks and broadcast what they convert.
+      const int CS = M1 ? 1 : (int)cluster_size(), crank = M1 ? 0 : (int)cluster_rank();
+      const uint32_t xfrag_s = (uint32_t)__cvta_generic_to_shared(xfrag), gsc_s = (uint32_t)__cvta_generic_to_shared(gsc);
+      for (int base0 = 0; base0 < total; base0 += kThreads * PF * CS) {
        uint4 raw[PF][2];
 #pragma unroll
        for (int q = 0; q < PF; ++q) {
-        const int it = base0 + q * kThreads + tid;
+        const int it = base0 + (q * CS + crank) * kThreads + tid;
         raw[q][0] = make_uint4(0u, 0u, 0u, 0u);
         raw[q][1] = make_uint4(0u, 0u, 0u, 0u);
         if (it < total) {
@@ -298,8 +324,8 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
        }
 #pragma unroll
        for (int q = 0; q < PF; ++q) {
-        const int base = base0 + q * kThreads;
-        if (base >= total) break;
+        const int base = base0 + (q * CS + crank) * kThreads;
+        if (base >= total) continue;
         const int it = base + tid;
         const bool ok = it < total;
         const int m = ok ? it / cpt : 0;
@@ -335,9 +361,14 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
           const int gi = c >> 3, tt = (c >> 1) & 3, jm = c & 1;  // 64-group, lane quarter, MMA of the group
           const int nt = m / kTokPerTile, ml = m - nt * kTokPerTile;
           if ((c & 7) == 0) {
-            float* gs = M1 ? gsc + gi * 2 : gsc + ((gi * NT + nt) * kTokPerTile + ml) * 2;
-            gs[0] = down;
-            gs[1] = down * (float)sum;
+            if constexpr (M1) {
+              gsc[gi * 2] = down;
+              gsc[gi * 2 + 1] = down * (float)sum;
+            } else {
+              const uint32_t a = gsc_s + (uint32_t)(((gi * NT + nt) * kTokPerTile + ml) * 2) * 4u;
+              for (int cr = 0; cr < CS; ++cr)
+                st_cluster_v2(map_to_rank(a, cr), __float_as_uint(down), __float_as_uint(down * (float)sum));
+            }
           }
 #pragma unroll
           for (int pl = 0; pl < 2; ++pl) {
@@ -346,14 +377,18 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
                   (plane_byte(v[kslot8<BITS>(0, 2)], pl) << 16) | (plane_byte(v[kslot8<BITS>(0, 3)], pl) << 24);
             o.y = plane_byte(v[kslot8<BITS>(1, 0)], pl) | (plane_byte(v[kslot8<BITS>(1, 1)], pl) << 8) |
                   (plane_byte(v[kslot8<BITS>(1, 2)], pl) << 16) | (plane_byte(v[kslot8<BITS>(1, 3)], pl) << 24);
-            if (M1) xfrag[(gi * 2 + jm) * 8 + pl * 4 + tt] = o;
-            else xfrag[((gi * 2 + jm) * NT + nt) * 32 + (2 * ml + pl) * 4 + tt] = o;
+            if constexpr (M1) {
+              xfrag[(gi * 2 + jm) * 8 + pl * 4 + tt] = o;
+            } else {
+              const uint32_t a = xfrag_s + (uint32_t)(((gi * 2 + jm) * NT + nt) * 32 + (2 * ml + pl) * 4 + tt) * 8u;
+              for (int cr = 0; cr < CS; ++cr) st_cluster_v2(map_to_rank(a, cr), o.x, o.y);
+            }
           }
         }
        }
       }
     }
-    __syncthreads();
+    if constexpr (M1) __syncthreads(); else cluster_sync_all();
 
     const int upt = (ut - pass * upk) < upk ? (ut - pass * upk) : upk;
     for (int tl0 = 0; tl0 < ntl; tl0 += RT) {
@@ -505,14 +540,16 @@ int sm_count() {
 }
 
 // Grid, K passes and shared-memory footprint of one instantiation; false when it does not fit.
-bool plan_stream(StreamK& p, int NT, bool M1, int* grid_out, size_t* smem_out) {
-  const int nsm = sm_count() * (M1 ? 2 : 1);  // CTA slots
+bool plan_stream(StreamK& p, int NT, bool M1, int* grid_out, size_t* smem_out, int cluster = 1, int max_ctas = 0) {
+  int nsm = sm_count() * (M1 ? 2 : 1);  // CTA slots
+  if (max_ctas > 0 && max_ctas < nsm) nsm = max_ctas;
   const int kGroups = groups_for(M1);
   int ntiles = 0;
   for (int i = 0; i < p.nmat; ++i) { p.tile0[i] = ntiles; ntiles += (p.N[i] + 15) / 16; }
   for (int i = p.nmat; i <= kMaxMat; ++i) p.tile0[i] = ntiles;
   const int total_groups = ntiles < kGroups * nsm ? ntiles : kGroups * nsm;
-  const int grid = (total_groups + kGroups - 1) / kGroups;
+  int grid = (total_groups + kGroups - 1) / kGroups;
+  grid = (grid + cluster - 1) / cluster * cluster;   // whole clusters; CTAs beyond the tiles only help staging
   p.ntiles = ntiles;
   p.total_groups = grid * kGroups;
   p.ntl_max = (ntiles + p.total_groups - 1) / p.total_groups;
@@ -538,18 +575,45 @@ void pick_inst(const StreamK& p, int* NT, bool* M1) {
 
 template <int BITS, int NT, bool M1>
 cudaError_t launch_inst(StreamK p, cudaStream_t st) {
-  int grid = 0;
-  size_t smem = 0;
-  if (!plan_stream(p, NT, M1, &grid, &smem)) return cudaErrorInvalidConfiguration;
   auto kern = qmv_stream_kernel<BITS, NT, M1>;
   static bool attr_done[64] = {};
+  static int cluster_of[64] = {}, max_ctas_of[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+  const bool cached = dev >= 0 && dev < 64;
+  if (!cached || !attr_done[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
-    if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    // Cluster size for the shared activation staging: the largest of 4, 2 whose co-resident clusters
+    // (at the full shared-memory footprint) still cover at least 97% of the SMs; 1 otherwise.
+    int cs = 1, ctas = sm_count();
+    if (!M1) {
+      for (int c = 4; c >= 2; c >>= 1) {
+        cudaLaunchConfig_t q = {};
+        q.gridDim = dim3((sm_count() / c) * c);
+        q.blockDim = dim3(kWarpsPerGroup * groups_for(M1) * 32);
+        q.dynamicSmemBytes = 227 * 1024;
+        cudaLaunchAttribute qa[1];
+        qa[0].id = cudaLaunchAttributeClusterDimension;
+        qa[0].val.clusterDim.x = c; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+        q.attrs = qa;
+        q.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &q) == cudaSuccess && n * c * 100 >= sm_count() * 97) {
+          cs = c;
+          ctas = n * c < sm_count() ? n * c : (sm_count() / c) * c;
+          break;
+        }
+        (void)cudaGetLastError();
+      }
+    }
+    if (cached) { cluster_of[dev] = cs; max_ctas_of[dev] = ctas; attr_done[dev] = true; }
+    else { cluster_of[0] = cs; max_ctas_of[0] = ctas; }
   }
+  const int cs = cluster_of[cached ? dev : 0], max_ctas = max_ctas_of[cached ? dev : 0];
+  int grid = 0;
+  size_t smem = 0;
+  if (!plan_stream(p, NT, M1, &grid, &smem, cs, M1 ? 0 : max_ctas)) return cudaErrorInvalidConfiguration;
   // Programmatic dependent launch: this grid may start (and prefetch weights, which no kernel writes)
   // before the previous grid in the stream has finished; it waits for that grid before touching x or y.
   cudaLaunchConfig_t cfg = {};
@@ -557,11 +621,13 @@ cudaError_t launch_inst(StreamK p, cudaStream_t st) {
   cfg.blockDim = dim3(kWarpsPerGroup * groups_for(M1) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = cs; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = (!M1 && cs > 1) ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, kern, p);
 }
 

@@ -156,9 +156,11 @@ def test_batch_entry_matches_single_calls(M):
 
 
 @pytest.mark.parametrize("bits,gs", [(4, 64), (8, 64), (4, 128)])
-@pytest.mark.parametrize("M,N,K", [(512, 1024, 4096), (300, 1000, 1024), (17, 128, 64), (2048, 256, 2048)])
+@pytest.mark.parametrize("M,N,K", [(512, 1024, 4096), (300, 1000, 1024), (17, 128, 64), (2048, 256, 2048),
+                                   (256, 640, 768), (1100, 208, 1536), (4096, 2560, 512)])
 def test_config4_prefill_shapes(bits, gs, M, N, K):
-    """BASELINE config 4 (dense prefill qmm) at oracle-sized shapes, incl. ragged M and N and the minimum K."""
+    """BASELINE config 4 (dense prefill qmm) at oracle-sized shapes, incl. ragged M and N, the minimum K, K that is
+    not a whole window of scales (768, 1536 at group size 128) and more tiles than SMs (several tiles per CTA)."""
     import qb200
     if K % gs:
         pytest.skip("K not a multiple of the group size")
