@@ -55,7 +55,21 @@ constexpr int B_STAGE_BYTES = BN_MAX * BK * 2;
 constexpr int RAW_BYTES = BN_MAX * 128;      // one super-block of packed codes: 128 bytes of every weight row
 constexpr uint32_t kSpinLimit = 1u << 24;
 
-__device__ int g_tc_error = 0;  // 0 = ok; otherwise the code of the wait that expired
+__device__ int g_tc_error = 0;
+
+// Optional cycle accounting of the roles (a build with -DQB_TC_PROFILE; not part of the library build).
+#ifdef QB_TC_PROFILE
+__device__ long long g_tc_prof[256][16];
+#define PROF_DECL long long pt0 = 0, pacc[6] = {0, 0, 0, 0, 0, 0}
+#define PROF_T0() pt0 = clock64()
+#define PROF_ADD(i) do { const long long t_ = clock64(); pacc[i] += t_ - pt0; pt0 = t_; } while (0)
+#define PROF_OUT(base) do { for (int i_ = 0; i_ < 6; ++i_) g_tc_prof[blockIdx.x][(base) + i_] = pacc[i_]; } while (0)
+#else
+#define PROF_DECL
+#define PROF_T0()
+#define PROF_ADD(i)
+#define PROF_OUT(base)
+#endif  // 0 = ok; otherwise the code of the wait that expired
 
 struct TcK {
   const uint32_t* w; const uint16_t* s; const uint16_t* b; uint16_t* y;
@@ -90,6 +104,25 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         : "r"(addr), "r"(parity)
         : "memory");
     if (done) return true;
+  }
+  return false;
+}
+// The same for waits that are off the critical path (producers running ahead, the epilogue waiting for a
+// whole tile): after a few polls the thread sleeps between polls, so that it does not take issue slots
+// from the warps that convert weights.  Still bounded: 2^22 polls of at least 100 ns.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t it = 0; it < (kSpinLimit >> 2); ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (it >= 4) __nanosleep(100);
   }
   return false;
 }
@@ -240,7 +273,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
         const int m0 = (tile % p.tiles_m) * BM;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int st = it % STAGES;
-          if (it >= STAGES && !mbar_wait(&empty[st], ((it / STAGES) - 1) & 1)) { fail = 3; break; }
+          if (it >= STAGES && !mbar_wait_relaxed(&empty[st], ((it / STAGES) - 1) & 1)) { fail = 3; break; }
           mbar_expect_tx(&full_a[st], A_STAGE_BYTES);
           const uint32_t dst = smem_u32(a_tiles + st * A_STAGE_BYTES);
           tma_load_2d(dst, &xmap, &full_a[st], kb * BK, m0);
@@ -258,7 +291,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
         const int n0 = (tile / p.tiles_m) * BN;
         for (int sbl = 0; sbl < sb_per_tile; ++sbl, ++sbk) {
           const int buf = sbk & 1;
-          if (sbk >= 2 && !mbar_wait(&raw_empty[buf], ((sbk >> 1) - 1) & 1)) { fail = 7; break; }
+          if (sbk >= 2 && !mbar_wait_relaxed(&raw_empty[buf], ((sbk >> 1) - 1) & 1)) { fail = 7; break; }
           mbar_expect_tx(&raw_full[buf], (uint32_t)BN * 128u);
           tma_load_2d(smem_u32(raw + buf * RAW_BYTES), &wmap, &raw_full[buf], sbl * 32, n0);
         }
@@ -271,18 +304,23 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       const uint32_t idesc = make_idesc(BN);
       const uint64_t adesc0 = make_desc(smem_u32(a_tiles)), bdesc0 = make_desc(smem_u32(b_tiles));
       int it = 0, fail = 0, ti = 0;
+      PROF_DECL;
+      PROF_T0();
       for (int tile = blockIdx.x; tile < p.ntiles && !fail && !s_fail; tile += gridDim.x, ++ti) {
         const int m0 = (tile % p.tiles_m) * BM;
         const bool two_halves = m0 + 128 < p.M;  // the second 128 token rows hold real tokens
         const int buf = ti & 1;
-        if (ti >= 2 && !mbar_wait(&acc_empty[buf], ((ti >> 1) - 1) & 1)) { fail = 6; break; }
+        if (ti >= 2 && !mbar_wait_relaxed(&acc_empty[buf], ((ti >> 1) - 1) & 1)) { fail = 6; break; }
+        PROF_ADD(0);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t d0 = tmem_base + buf * 256;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int st = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&full_a[st], ph)) { fail = 1; break; }
+          PROF_ADD(1);
           if (!mbar_wait(&full_b[st], ph)) { fail = 2; break; }
+          PROF_ADD(2);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           // descriptors of the stage: the start-address field counts 16-byte units, so a K step of
           // 16 values (32 bytes) adds 2 and the second 128-row box of x adds 16 KiB / 16
@@ -294,10 +332,12 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
             if (two_halves) umma(d0 + 128, ad0 + ((128 * BK * 2) >> 4) + 2 * k16, bd0 + 2 * k16, idesc, accum);
           }
           umma_commit(&empty[st]);  // frees this stage (A and B) once the MMAs above have read it
+          PROF_ADD(3);
         }
         if (fail) break;
         umma_commit(&acc_full[buf]);
       }
+      PROF_OUT(0);
       if (fail) { s_fail = fail; atomicExch(&g_tc_error, fail); }
     }
   } else if (warp < kDequantWarps) {
@@ -328,6 +368,8 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
     };
     if (p.sb_vec) prefetch_window();
     bool ok = true;
+    PROF_DECL;
+    PROF_T0();
     for (int it = grp; it < total_it; it += kDequantGroups) {
       const int st = it % STAGES;
       const int tl = it / nkb, kb = it - tl * nkb;
@@ -349,8 +391,10 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
         sv2 = sv | (sv << 16);
         bv2 = bv | (bv << 16);
       }
+      PROF_ADD(0);
       ok = mbar_wait(&raw_full[buf], (sbk >> 1) & 1);
       if (!ok || s_fail) { ok = false; break; }
+      PROF_ADD(1);
       uint32_t c[WPH];
       if (active) {
         const unsigned char* rrow = raw + buf * RAW_BYTES + r * 128;
@@ -363,14 +407,20 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       }
       if (it >= STAGES) ok = mbar_wait(&empty[st], ((it / STAGES) - 1) & 1);
       if (!ok || s_fail) { ok = false; break; }
+      PROF_ADD(2);
       if (active) dequant_half<BITS>(c, sv2, bv2, b_tiles + st * B_STAGE_BYTES, r, h);
+      PROF_ADD(3);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> async proxy (UMMA)
+      PROF_ADD(4);
       mbar_arrive(&full_b[st]);
       // Release the codes buffer only now that the loaded words have been consumed: the arrival is not
       // ordered behind a shared-memory load whose result no instruction has waited for yet, and the
       // TMA refill must not overtake this thread's last read.
       if (kbl + kDequantGroups >= KPS) mbar_arrive(&raw_empty[buf]);
     }
+#ifdef QB_TC_PROFILE
+    if (lane == 0 && wg == 0) { PROF_ADD(5); PROF_OUT(grp == 0 ? 4 : 10); }
+#endif
     if (!ok && !s_fail) { s_fail = 4; atomicExch(&g_tc_error, 4); }
   } else {
     // ---------------- epilogue: TMEM -> registers -> bf16 rows of y ----------------
@@ -381,7 +431,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
       const int nend = (n0 + BN) < p.N ? (n0 + BN) : p.N;
       const int buf = ti & 1;
-      ok = mbar_wait(&acc_full[buf], (ti >> 1) & 1);
+      ok = mbar_wait_relaxed(&acc_full[buf], (ti >> 1) & 1);
       if (!ok || s_fail) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
@@ -544,6 +594,12 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, cudaStream_t st) {
   else qmm_tc_kernel<8><<<grid, kThreads, kSmemBytes, st>>>(map, wmap, p);
   return cudaGetLastError();
 }
+
+#ifdef QB_TC_PROFILE
+extern "C" __attribute__((visibility("default"))) void qb200_debug_tc_profile(long long* out) {
+  cudaMemcpyFromSymbol(out, g_tc_prof, sizeof(long long) * 256 * 16);
+}
+#endif
 
 int qmm_tc_error_code() {
   int v = 0;

@@ -52,6 +52,17 @@ __host__ __device__ constexpr int kc_for(int nt) { return nt <= 2 ? 4096 : 1024;
 
 constexpr int kMaxMat = 4;          // weight matrices served by one launch (same activations)
 
+// Optional timeline of one launch (a build with -DQB_STREAM_PROFILE; not part of the library build):
+// nanosecond timestamps of thread 0 of every CTA at the phase boundaries
+// (0 start, 1 first ring stages issued, 2 previous grid complete, 3 activations staged, 4 end).
+#ifdef QB_STREAM_PROFILE
+__device__ unsigned long long g_stream_tl[512][8];
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define TL(i) do { if (threadIdx.x == 0 && blockIdx.x < 512) g_stream_tl[blockIdx.x][i] = gtime(); } while (0)
+#else
+#define TL(i)
+#endif
+
 struct StreamK {
   const void* x;
   const uint32_t* w[kMaxMat]; const uint16_t* s[kMaxMat]; const uint16_t* b[kMaxMat]; void* y[kMaxMat];
@@ -182,6 +193,7 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int grp = warp / kWarpsPerGroup, ks = warp % kWarpsPerGroup;
   const int ggrp = blockIdx.x * kGroups + grp;  // global group id
+  TL(0);
 
   // ---- shared memory carve-up ----
   const int kc = p.kc;
@@ -264,8 +276,10 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
 
   // Let the next grid in the stream begin launching, then wait for the previous grid to complete (and
   // its writes to be visible) before reading activations or writing outputs.
+  TL(1);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  TL(2);
   if constexpr (!M1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 
   int consumed = 0;
@@ -389,6 +403,7 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
       }
     }
     if constexpr (M1) __syncthreads(); else cluster_sync_all();
+    if (pass == 0) TL(3);
 
     const int upt = (ut - pass * upk) < upk ? (ut - pass * upk) : upk;
     for (int tl0 = 0; tl0 < ntl; tl0 += RT) {
@@ -524,7 +539,14 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
     }
   }
   cp_async_wait<0>();
+  TL(4);
 }
+
+#ifdef QB_STREAM_PROFILE
+extern "C" __attribute__((visibility("default"))) void qb200_debug_stream_timeline(unsigned long long* out) {
+  cudaMemcpyFromSymbol(out, g_stream_tl, sizeof(unsigned long long) * 512 * 8);
+}
+#endif
 
 int sm_count() {
   static int cached[64] = {};
