@@ -106,6 +106,11 @@ def cpu_layer_pass(M, seed=0xC2, reps=None, budget_s=12.0):
     """Oracle timing of one layer pass (7 projections) at M rows; returns (tokens/s, threads, sample text)."""
     import numpy as np
     from oracle import qoracle as qo
+    # all the host threads this process may use (torchrun exports OMP_NUM_THREADS=1)
+    try:
+        qo.set_num_threads(len(os.sched_getaffinity(0)))
+    except (AttributeError, OSError):
+        qo.set_num_threads(os.cpu_count() or 1)
     rng = np.random.default_rng(seed)
     ws, xs = [], {}
     for _, n, k in LLAMA:

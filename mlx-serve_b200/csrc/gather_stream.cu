@@ -27,6 +27,8 @@
 // Arithmetic is that of the dense streaming kernel: exact s32 dots of codes with
 // 15-bit fixed-point activations, scale and bias applied per 64-wide group in
 // fp32; the weight term q*s+b is never rounded to bf16.
+#include <type_traits>
+
 #include "kernels.h"
 
 namespace qb {
@@ -48,6 +50,7 @@ struct GK {
   BatchMap xbcast;
   int64_t I, E, XB, xstride, wes, ses;
   int N, K, gshift, x_f32;
+  int nsb;   // (expert, sweep) segments staged together: 2 when their fragments fit beside the ring, else 1
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -93,14 +96,14 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
   __shared__ int s_cum[kMaxExperts + 1];        // tiles of work before expert e (exclusive prefix), [E] = total
   __shared__ int s_cnt[kMaxExperts];            // rows routed to expert e
   __shared__ unsigned short s_rhs[kMaxRows];    // expert of every output row (0xFFFF: out of range)
-  __shared__ long long s_xi[kRowsPerSweep];     // activation row of each slot (-1: empty)
-  __shared__ int s_orow[kRowsPerSweep];         // output row of each slot (-1: empty)
+  __shared__ long long s_xi[2 * kRowsPerSweep]; // activation row of each slot of each staged segment (-1: empty)
+  __shared__ int s_orow[2 * kRowsPerSweep];     // output row of each slot (-1: empty)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   unsigned char* sp = smem;
   unsigned char* ring = sp;    sp += (size_t)kWarps * kStages * kStageBytes;
-  uint2* xfrag = (uint2*)sp;   sp += (size_t)(p.K / 32) * NT * 32 * 8;
-  float* gsc = (float*)sp;     sp += (size_t)(p.K / 64) * NT * 4 * 8;  // [(group*NT + nt)*4 + row][2]: (2^(E-14), 2^(E-14) * sum v)
+  uint2* xfrag = (uint2*)sp;   sp += (size_t)p.nsb * (p.K / 32) * NT * 32 * 8;   // per staged segment
+  float* gsc = (float*)sp;     sp += (size_t)p.nsb * (p.K / 64) * NT * 4 * 8;   // [(group*NT + nt)*4 + row][2]: (2^(E-14), 2^(E-14) * sum v)
   float* red = (float*)sp;     // [warp][nt][2][lane]: partial sums of warps that share a tile's K range
   const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring + (size_t)warp * kStages * kStageBytes);
   const unsigned char* my_ring_p = ring + (size_t)warp * kStages * kStageBytes;
@@ -183,42 +186,76 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
     }
     e = a;
   }
+  const int64_t ldw = (int64_t)p.K * BITS / 32, lds = p.K >> (6 + p.gshift);
+  const int xf_stride = (p.K / 32) * NT * 32;       // uint2 elements of one segment's fragments
+  const int gs_stride = (p.K / 64) * NT * 4 * 2;    // floats of one segment's group scales
   for (int pos = lo; pos < hi;) {
-    while (s_cum[e + 1] <= pos) ++e;           // skips experts without rows
-    const int off = pos - s_cum[e];
-    const int sweep = off / tiles_n, t0 = off - sweep * tiles_n;
-    const int t1 = (t0 + (hi - pos)) < tiles_n ? (t0 + (hi - pos)) : tiles_n;
-    pos += t1 - t0;
-    const uint32_t* wexp = p.w + (int64_t)e * p.wes;
-    const uint16_t* sexp = p.s + (int64_t)e * p.ses;
-    const uint16_t* bexp = p.b + (int64_t)e * p.ses;
-    const int64_t ldw = (int64_t)p.K * BITS / 32, lds = p.K >> (6 + p.gshift);
-    const int r0 = sweep * kRowsPerSweep;
-    const int nrows = s_cnt[e];
+    // ---- up to p.nsb consecutive (expert, sweep) segments of the share are staged together, so that the
+    //      weight stream does not drain at the boundary between two experts ----
+    int e0 = 0, r00 = 0, t00 = 0, nt0 = 0, e1 = 0, r01 = 0, t01 = 0, nt1 = 0;
+    {
+      while (s_cum[e + 1] <= pos) ++e;           // skips experts without rows
+      int off = pos - s_cum[e];
+      int sweep = off / tiles_n;
+      e0 = e; r00 = sweep * kRowsPerSweep; t00 = off - sweep * tiles_n;
+      nt0 = (t00 + (hi - pos)) < tiles_n ? (hi - pos) : tiles_n - t00;
+      pos += nt0;
+      if (p.nsb > 1 && pos < hi) {
+        while (s_cum[e + 1] <= pos) ++e;
+        off = pos - s_cum[e];
+        sweep = off / tiles_n;
+        e1 = e; r01 = sweep * kRowsPerSweep; t01 = off - sweep * tiles_n;
+        nt1 = (t01 + (hi - pos)) < tiles_n ? (hi - pos) : tiles_n - t01;
+        pos += nt1;
+      }
+    }
+    const int ntb = nt0 + nt1;                    // tiles of this batch, numbered j = 0 .. ntb-1
+    const uint32_t* wexp0 = p.w + (int64_t)e0 * p.wes;
+    const uint16_t* sexp0 = p.s + (int64_t)e0 * p.ses;
+    const uint16_t* bexp0 = p.b + (int64_t)e0 * p.ses;
+    const uint32_t* wexp1 = p.w + (int64_t)e1 * p.wes;
+    const uint16_t* sexp1 = p.s + (int64_t)e1 * p.ses;
+    const uint16_t* bexp1 = p.b + (int64_t)e1 * p.ses;
+    const int nte0 = (s_cnt[e0] - r00) > 4 ? 2 : 1;             // n8 tiles in use per segment
+    const int nte1 = nt1 > 0 && (s_cnt[e1] - r01) > 4 ? 2 : 1;
 
-    // ---- start streaming this warp's weights right away: they do not depend on the activations ----
-    const int seg_tiles = t1 - t0;
+    // ---- start streaming this warp's weights right away: they do not depend on the activations.
+    //      Each warp owns whole 16-row tiles; when the batch has fewer tiles than the CTA has warps,
+    //      `ksplit` warps share a tile's K range and reduce through shared memory ----
     int ksplit = 1;
-    while (ksplit * 2 * seg_tiles <= kWarps && ksplit * 2 <= ut) ksplit *= 2;
+    while (ksplit * 2 * ntb <= kWarps && ksplit * 2 <= ut) ksplit *= 2;
     const int kp = warp % ksplit;
-    const int first = ksplit == 1 ? t0 + warp : t0 + warp / ksplit;
-    const int my_tiles = first < t1 ? (ksplit == 1 ? (t1 - first + kWarps - 1) / kWarps : 1) : 0;
+    const int first = ksplit == 1 ? warp : warp / ksplit;
+    const int my_tiles = first < ntb ? (ksplit == 1 ? (ntb - first + kWarps - 1) / kWarps : 1) : 0;
     const int nu = (ut - kp + ksplit - 1) / ksplit;   // units of one tile handled by this warp
     const int total = my_tiles * nu;
     int issued = 0, consumed = 0, ptile = 0, pu = kp;  // producer position: (tile index, unit)
+    // per-lane source pointers of the producer's current tile (recomputed when the tile changes)
+    const unsigned char* wsrc[4] = {nullptr, nullptr, nullptr, nullptr};
+    const uint16_t* sbsrc = nullptr;
+    int cached_tile = -1;
     auto issue = [&](int stage) {
-      const int tile = first + ptile * kWarps;
-      const uint32_t st = my_ring + stage * kStageBytes;
-      const int64_t woff = (int64_t)pu * 128;
+      if (ptile != cached_tile) {
+        cached_tile = ptile;
+        const int j = first + ptile * kWarps;
+        const bool sg = j >= nt0;
+        const int tile = sg ? t01 + (j - nt0) : t00 + j;
+        const uint32_t* wexp = sg ? wexp1 : wexp0;
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        int n = tile * 16 + (lane >> 3) + 4 * r;
+        for (int r = 0; r < 4; ++r) {
+          int n = tile * 16 + (lane >> 3) + 4 * r;
+          n = n < p.N ? n : p.N - 1;
+          wsrc[r] = (const unsigned char*)(wexp + (int64_t)n * ldw) + chunk * 16;
+        }
+        int n = tile * 16 + (lane & 15);
         n = n < p.N ? n : p.N - 1;
-        cp_async16(st + wdst[r], (const unsigned char*)(wexp + (int64_t)n * ldw) + woff + chunk * 16);
+        sbsrc = ((lane >> 4) ? (sg ? bexp1 : bexp0) : (sg ? sexp1 : sexp0)) + (int64_t)n * lds;
       }
-      int n = tile * 16 + (lane & 15);
-      n = n < p.N ? n : p.N - 1;
-      const uint16_t* ssrc = ((lane >> 4) ? bexp : sexp) + (int64_t)n * lds + ((pu * U) >> p.gshift);
+      const uint32_t st = my_ring + stage * kStageBytes;
+      const int woff = pu * 128;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) cp_async16(st + wdst[r], wsrc[r] + woff);
+      const uint16_t* ssrc = sbsrc + ((pu * U) >> p.gshift);
       if (BITS == 4 && p.gshift == 0) cp_async8(st + sbdst, ssrc);
       else cp_async4(st + sbdst, ssrc);
       pu += ksplit;
@@ -231,204 +268,219 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
       ++issued;
     }
 
-    {
-      __syncthreads();  // previous segment has finished with xfrag / slots
-      // ---- rows r0 .. r0+7 of this expert in ascending rhs position ----
-      if (warp == 0) {
-        if (lane < kRowsPerSweep) { s_xi[lane] = -1; s_orow[lane] = -1; }
-        __syncwarp();
-        int seen = 0;
-        for (int i0 = 0; i0 < I && seen < r0 + kRowsPerSweep; i0 += 32) {
-          const int i = i0 + lane;
-          const bool hit = i < I && s_rhs[i] == (unsigned short)e;
-          const unsigned bal = __ballot_sync(0xffffffffu, hit);
-          const int rank = seen + __popc(bal & ((1u << lane) - 1u));
-          if (hit && rank >= r0 && rank < r0 + kRowsPerSweep) {
-            long long xi = p.lhs ? load_index(p.lhs, p.lhs_i64, i) : (long long)p.xbcast.offset(i);
-            int orow = i;
-            if (xi < 0 || xi >= p.XB) { xi = -1; orow = -1; }
-            s_xi[rank - r0] = xi;
-            s_orow[rank - r0] = orow;
-          }
-          seen += __popc(bal);
+    __syncthreads();  // the previous batch has finished with the fragments and the slots
+    // ---- rows r0 .. r0+7 of each segment's expert in ascending rhs position (one warp per segment) ----
+    if (warp < 2 && (warp == 0 || nt1 > 0)) {
+      const int es = warp ? e1 : e0, r0 = warp ? r01 : r00;
+      long long* xi_s = s_xi + warp * kRowsPerSweep;
+      int* orow_s = s_orow + warp * kRowsPerSweep;
+      if (lane < kRowsPerSweep) { xi_s[lane] = -1; orow_s[lane] = -1; }
+      __syncwarp();
+      int seen = 0;
+      for (int i0 = 0; i0 < I && seen < r0 + kRowsPerSweep; i0 += 32) {
+        const int i = i0 + lane;
+        const bool hit = i < I && s_rhs[i] == (unsigned short)es;
+        const unsigned bal = __ballot_sync(0xffffffffu, hit);
+        const int rank = seen + __popc(bal & ((1u << lane) - 1u));
+        if (hit && rank >= r0 && rank < r0 + kRowsPerSweep) {
+          long long xi = p.lhs ? load_index(p.lhs, p.lhs_i64, i) : (long long)p.xbcast.offset(i);
+          int orow = i;
+          if (xi < 0 || xi >= p.XB) { xi = -1; orow = -1; }
+          xi_s[rank - r0] = xi;
+          orow_s[rank - r0] = orow;
         }
+        seen += __popc(bal);
       }
-      __syncthreads();
-      const int nte = (nrows - r0) > 4 ? 2 : 1;  // n8 tiles in use
-      // ---- stage the rows' activations as s8 planes in B-fragment order (one thread: 8 K values) ----
-      {
-        const int cpt = p.K >> 3;
-        const int total = nte * 4 * cpt;
-        for (int base = 0; base < total; base += kThreads) {
-          const int it = base + tid;
-          const bool ok = it < total;
-          const int m = ok ? it / cpt : 0;
-          const int c = ok ? it - m * cpt : 0;
-          float f[8];
-          const long long xi = ok ? s_xi[m] : -1;
-          if (xi >= 0) {
-            const int64_t off = xi * p.xstride + (int64_t)c * 8;
-            if (!p.x_f32) {
-              const uint4 a = *(const uint4*)((const uint16_t*)p.x + off);
-              f[0] = bf16lo(a.x); f[1] = bf16hi(a.x); f[2] = bf16lo(a.y); f[3] = bf16hi(a.y);
-              f[4] = bf16lo(a.z); f[5] = bf16hi(a.z); f[6] = bf16lo(a.w); f[7] = bf16hi(a.w);
-            } else {
-              const float4 a = *(const float4*)((const float*)p.x + off), b2 = *(const float4*)((const float*)p.x + off + 4);
-              f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b2.x; f[5] = b2.y; f[6] = b2.z; f[7] = b2.w;
-            }
+    }
+    __syncthreads();
+    // ---- stage the rows' activations as s8 planes in B-fragment order (one thread: 8 K values) ----
+    for (int sg = 0; sg < (nt1 > 0 ? 2 : 1); ++sg) {
+      const int cpt = p.K >> 3;
+      const int items = (sg ? nte1 : nte0) * 4 * cpt;
+      uint2* xf = xfrag + sg * xf_stride;
+      float* gsb = gsc + sg * gs_stride;
+      const long long* xi_s = s_xi + sg * kRowsPerSweep;
+      for (int base = 0; base < items; base += kThreads) {
+        const int it = base + tid;
+        const bool ok = it < items;
+        const int m = ok ? it / cpt : 0;
+        const int c = ok ? it - m * cpt : 0;
+        float f[8];
+        const long long xi = ok ? xi_s[m] : -1;
+        if (xi >= 0) {
+          const int64_t off = xi * p.xstride + (int64_t)c * 8;
+          if (!p.x_f32) {
+            const uint4 a = *(const uint4*)((const uint16_t*)p.x + off);
+            f[0] = bf16lo(a.x); f[1] = bf16hi(a.x); f[2] = bf16lo(a.y); f[3] = bf16hi(a.y);
+            f[4] = bf16lo(a.z); f[5] = bf16hi(a.z); f[6] = bf16lo(a.w); f[7] = bf16hi(a.w);
           } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = 0.f;
+            const float4 a = *(const float4*)((const float*)p.x + off), b2 = *(const float4*)((const float*)p.x + off + 4);
+            f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b2.x; f[5] = b2.y; f[6] = b2.z; f[7] = b2.w;
           }
-          float mx = 0.f;
+        } else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(f[j]));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-          int ex = (int)((__float_as_uint(mx) >> 23) & 0xFF) - 127 + 1;  // mx < 2^ex
-          ex = ex < -100 ? -100 : (ex > 110 ? 110 : ex);
-          const float up = __uint_as_float((uint32_t)(127 + 14 - ex) << 23);
-          const float down = __uint_as_float((uint32_t)(127 + ex - 14) << 23);
-          int v[8], sum = 0;
+          for (int j = 0; j < 8; ++j) f[j] = 0.f;
+        }
+        float mx = 0.f;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) { v[j] = fix15(f[j], up); sum += v[j]; }
-          sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-          sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-          sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-          if (ok) {
-            const int gi = c >> 3, tt = (c >> 1) & 3, jm = c & 1;
-            const int nt = m >> 2, ml = m & 3;
-            if ((c & 7) == 0) {
-              float* gs = gsc + ((gi * NT + nt) * 4 + ml) * 2;
-              gs[0] = down;
-              gs[1] = down * (float)sum;
-            }
+        for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(f[j]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        int ex = (int)((__float_as_uint(mx) >> 23) & 0xFF) - 127 + 1;  // mx < 2^ex
+        ex = ex < -100 ? -100 : (ex > 110 ? 110 : ex);
+        const float up = __uint_as_float((uint32_t)(127 + 14 - ex) << 23);
+        const float down = __uint_as_float((uint32_t)(127 + ex - 14) << 23);
+        int v[8], sum = 0;
 #pragma unroll
-            for (int pl = 0; pl < 2; ++pl) {
-              uint2 o;
-              o.x = plane_byte(v[kslot8<BITS>(0, 0)], pl) | (plane_byte(v[kslot8<BITS>(0, 1)], pl) << 8) |
-                    (plane_byte(v[kslot8<BITS>(0, 2)], pl) << 16) | (plane_byte(v[kslot8<BITS>(0, 3)], pl) << 24);
-              o.y = plane_byte(v[kslot8<BITS>(1, 0)], pl) | (plane_byte(v[kslot8<BITS>(1, 1)], pl) << 8) |
-                    (plane_byte(v[kslot8<BITS>(1, 2)], pl) << 16) | (plane_byte(v[kslot8<BITS>(1, 3)], pl) << 24);
-              xfrag[((gi * 2 + jm) * NT + nt) * 32 + (2 * ml + pl) * 4 + tt] = o;
-            }
+        for (int j = 0; j < 8; ++j) { v[j] = fix15(f[j], up); sum += v[j]; }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        if (ok) {
+          const int gi = c >> 3, tt = (c >> 1) & 3, jm = c & 1;
+          const int nt = m >> 2, ml = m & 3;
+          if ((c & 7) == 0) {
+            float* gs = gsb + ((gi * NT + nt) * 4 + ml) * 2;
+            gs[0] = down;
+            gs[1] = down * (float)sum;
+          }
+#pragma unroll
+          for (int pl = 0; pl < 2; ++pl) {
+            uint2 o;
+            o.x = plane_byte(v[kslot8<BITS>(0, 0)], pl) | (plane_byte(v[kslot8<BITS>(0, 1)], pl) << 8) |
+                  (plane_byte(v[kslot8<BITS>(0, 2)], pl) << 16) | (plane_byte(v[kslot8<BITS>(0, 3)], pl) << 24);
+            o.y = plane_byte(v[kslot8<BITS>(1, 0)], pl) | (plane_byte(v[kslot8<BITS>(1, 1)], pl) << 8) |
+                  (plane_byte(v[kslot8<BITS>(1, 2)], pl) << 16) | (plane_byte(v[kslot8<BITS>(1, 3)], pl) << 24);
+            xf[((gi * 2 + jm) * NT + nt) * 32 + (2 * ml + pl) * 4 + tt] = o;
           }
         }
       }
-      __syncthreads();
-      // lane (g, t) holds weight rows g, g+8 of a tile for the row in slot nt*4 + t
-      auto store_tile = [&](int tile, const float (&tot)[NT][2]) {
-        const int n_lo = tile * 16 + g;
+    }
+    __syncthreads();
+    // lane (g, t) holds weight rows g, g+8 of a tile for the row in slot nt*4 + t of the tile's segment
+    auto store_tile = [&](int j, const float (&tot)[NT][2]) {
+      const bool sg = j >= nt0;
+      const int tile = sg ? t01 + (j - nt0) : t00 + j;
+      const int nte = sg ? nte1 : nte0;
+      const int n_lo = tile * 16 + g;
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const int orow = s_orow[nt * 4 + t];
-          if (nt < nte && orow >= 0) {
-            const int64_t o = (int64_t)orow * p.N;
-            if (p.x_f32) {
-              if (n_lo < p.N) ((float*)p.y)[o + n_lo] = tot[nt][0];
-              if (n_lo + 8 < p.N) ((float*)p.y)[o + n_lo + 8] = tot[nt][1];
-            } else {
-              if (n_lo < p.N) ((uint16_t*)p.y)[o + n_lo] = f32_to_bf16_bits(tot[nt][0]);
-              if (n_lo + 8 < p.N) ((uint16_t*)p.y)[o + n_lo + 8] = f32_to_bf16_bits(tot[nt][1]);
-            }
+      for (int nt = 0; nt < NT; ++nt) {
+        const int orow = s_orow[(sg ? kRowsPerSweep : 0) + nt * 4 + t];
+        if (nt < nte && orow >= 0) {
+          const int64_t o = (int64_t)orow * p.N;
+          if (p.x_f32) {
+            if (n_lo < p.N) ((float*)p.y)[o + n_lo] = tot[nt][0];
+            if (n_lo + 8 < p.N) ((float*)p.y)[o + n_lo + 8] = tot[nt][1];
+          } else {
+            if (n_lo < p.N) ((uint16_t*)p.y)[o + n_lo] = f32_to_bf16_bits(tot[nt][0]);
+            if (n_lo + 8 < p.N) ((uint16_t*)p.y)[o + n_lo + 8] = f32_to_bf16_bits(tot[nt][1]);
           }
         }
-      };
-      // ---- each warp owns whole 16-row tiles of the segment; when the segment has fewer tiles than
-      //      the CTA has warps, `ksplit` warps share a tile's K range and reduce through shared memory ----
-      {
-        float tot[NT][2];
+      }
+    };
+    {
+      float tot[NT][2];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = 0.f;
+      for (int ti = 0; ti < my_tiles; ++ti) {
+        const int j = first + ti * kWarps;
+        const bool sg = j >= nt0;
+        const int nte = sg ? nte1 : nte0;
+        const uint2* xf = xfrag + (sg ? xf_stride : 0);
+        const float* gsb = gsc + (sg ? gs_stride : 0);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = 0.f;
-        for (int ti = 0; ti < my_tiles; ++ti) {
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = 0.f;
-          for (int u = kp; u < ut; u += ksplit) {
-            if (issued < total) issue(issued % kStages);
-            cp_async_commit();
-            ++issued;
-            cp_async_wait<kStages - 1>();
-            __syncwarp();
-            const unsigned char* st = my_ring_p + (consumed % kStages) * kStageBytes;
-            ++consumed;
-            uint32_t sl[2], sh[2], bl[2], bh[2];
-            {
-              const unsigned char* sb = st + kStageW;
-              if (BITS == 4 && p.gshift == 0) {
-                const uint2 a = *(const uint2*)(sb + g * 8), c = *(const uint2*)(sb + (g + 8) * 8);
-                const uint2 d = *(const uint2*)(sb + 128 + g * 8), e2 = *(const uint2*)(sb + 128 + (g + 8) * 8);
-                sl[0] = a.x; sl[1] = a.y; sh[0] = c.x; sh[1] = c.y;
-                bl[0] = d.x; bl[1] = d.y; bh[0] = e2.x; bh[1] = e2.y;
+        // one ring stage (16 rows x 128 bytes of codes) against the staged rows; NTE n8 tiles in use
+        auto unit = [&](auto nte_c, const unsigned char* st, int u) {
+          constexpr int NTE = decltype(nte_c)::value;
+          uint32_t sl[2], sh[2], bl[2], bh[2];
+          {
+            const unsigned char* sb = st + kStageW;
+            if (BITS == 4 && p.gshift == 0) {
+              const uint2 a = *(const uint2*)(sb + g * 8), c = *(const uint2*)(sb + (g + 8) * 8);
+              const uint2 d = *(const uint2*)(sb + 128 + g * 8), e2 = *(const uint2*)(sb + 128 + (g + 8) * 8);
+              sl[0] = a.x; sl[1] = a.y; sh[0] = c.x; sh[1] = c.y;
+              bl[0] = d.x; bl[1] = d.y; bh[0] = e2.x; bh[1] = e2.y;
+            } else {
+              const uint32_t a = *(const uint32_t*)(sb + g * 8), c = *(const uint32_t*)(sb + (g + 8) * 8);
+              const uint32_t d = *(const uint32_t*)(sb + 128 + g * 8), e2 = *(const uint32_t*)(sb + 128 + (g + 8) * 8);
+              if (BITS == 4) {  // group size 128: each value serves two 64-wide groups
+                sl[0] = __byte_perm(a, a, 0x1010); sl[1] = __byte_perm(a, a, 0x3232);
+                sh[0] = __byte_perm(c, c, 0x1010); sh[1] = __byte_perm(c, c, 0x3232);
+                bl[0] = __byte_perm(d, d, 0x1010); bl[1] = __byte_perm(d, d, 0x3232);
+                bh[0] = __byte_perm(e2, e2, 0x1010); bh[1] = __byte_perm(e2, e2, 0x3232);
               } else {
-                const uint32_t a = *(const uint32_t*)(sb + g * 8), c = *(const uint32_t*)(sb + (g + 8) * 8);
-                const uint32_t d = *(const uint32_t*)(sb + 128 + g * 8), e2 = *(const uint32_t*)(sb + 128 + (g + 8) * 8);
-                if (BITS == 4) {  // group size 128: each value serves two 64-wide groups
-                  sl[0] = __byte_perm(a, a, 0x1010); sl[1] = __byte_perm(a, a, 0x3232);
-                  sh[0] = __byte_perm(c, c, 0x1010); sh[1] = __byte_perm(c, c, 0x3232);
-                  bl[0] = __byte_perm(d, d, 0x1010); bl[1] = __byte_perm(d, d, 0x3232);
-                  bh[0] = __byte_perm(e2, e2, 0x1010); bh[1] = __byte_perm(e2, e2, 0x3232);
-                } else {
-                  sl[0] = a; sh[0] = c; bl[0] = d; bh[0] = e2;
-                  sl[1] = sh[1] = bl[1] = bh[1] = 0;
-                }
+                sl[0] = a; sh[0] = c; bl[0] = d; bh[0] = e2;
+                sl[1] = sh[1] = bl[1] = bh[1] = 0;
               }
             }
-#pragma unroll
-            for (int j = 0; j < U; ++j) {
-              uint32_t a0[2], a1[2], a2[2], a3[2];
-              if constexpr (BITS == 4) {
-                const uint2 wl = *(const uint2*)(st + frag_off[j]);
-                const uint2 wh = *(const uint2*)(st + frag_off[j] + 1024);
-                a0[0] = wl.x & 0x0F0F0F0Fu; a2[0] = (wl.x >> 4) & 0x0F0F0F0Fu;
-                a0[1] = wl.y & 0x0F0F0F0Fu; a2[1] = (wl.y >> 4) & 0x0F0F0F0Fu;
-                a1[0] = wh.x & 0x0F0F0F0Fu; a3[0] = (wh.x >> 4) & 0x0F0F0F0Fu;
-                a1[1] = wh.y & 0x0F0F0F0Fu; a3[1] = (wh.y >> 4) & 0x0F0F0F0Fu;
-              } else {
-                const uint4 wl = *(const uint4*)(st + frag_off[j]);
-                const uint4 wh = *(const uint4*)(st + frag_off[j] + 1024);
-                a0[0] = wl.x; a2[0] = wl.y; a0[1] = wl.z; a2[1] = wl.w;
-                a1[0] = wh.x; a3[0] = wh.y; a1[1] = wh.z; a3[1] = wh.w;
-              }
-              const int gl = u * U + j;
-              const float s_lo = (j & 1) ? bf16hi(sl[j >> 1]) : bf16lo(sl[j >> 1]);
-              const float s_hi = (j & 1) ? bf16hi(sh[j >> 1]) : bf16lo(sh[j >> 1]);
-              const float b_lo = (j & 1) ? bf16hi(bl[j >> 1]) : bf16lo(bl[j >> 1]);
-              const float b_hi = (j & 1) ? bf16hi(bh[j >> 1]) : bf16lo(bh[j >> 1]);
-#pragma unroll
-              for (int nt = 0; nt < NT; ++nt) {
-                if (nt < nte) {
-                  int acc[4] = {0, 0, 0, 0};
-#pragma unroll
-                  for (int i = 0; i < 2; ++i) {
-                    const uint2 bf = xfrag[((gl * 2 + i) * NT + nt) * 32 + lane];
-                    mma_u8s8(acc, a0[i], a1[i], a2[i], a3[i], bf.x, bf.y);
-                  }
-                  const float2 gs = *(const float2*)&gsc[((gl * NT + nt) * 4 + t) * 2];
-                  const float f_lo = (float)(acc[0] * 128 + acc[1]), f_hi = (float)(acc[2] * 128 + acc[3]);
-                  tot[nt][0] = fmaf(s_lo * gs.x, f_lo, fmaf(b_lo, gs.y, tot[nt][0]));
-                  tot[nt][1] = fmaf(s_hi * gs.x, f_hi, fmaf(b_hi, gs.y, tot[nt][1]));
-                }
-              }
-            }
-            __syncwarp();
           }
-          if (ksplit == 1) store_tile(first + ti * kWarps, tot);
+#pragma unroll
+          for (int jj = 0; jj < U; ++jj) {
+            uint32_t a0[2], a1[2], a2[2], a3[2];
+            if constexpr (BITS == 4) {
+              const uint2 wl = *(const uint2*)(st + frag_off[jj]);
+              const uint2 wh = *(const uint2*)(st + frag_off[jj] + 1024);
+              a0[0] = wl.x & 0x0F0F0F0Fu; a2[0] = (wl.x >> 4) & 0x0F0F0F0Fu;
+              a0[1] = wl.y & 0x0F0F0F0Fu; a2[1] = (wl.y >> 4) & 0x0F0F0F0Fu;
+              a1[0] = wh.x & 0x0F0F0F0Fu; a3[0] = (wh.x >> 4) & 0x0F0F0F0Fu;
+              a1[1] = wh.y & 0x0F0F0F0Fu; a3[1] = (wh.y >> 4) & 0x0F0F0F0Fu;
+            } else {
+              const uint4 wl = *(const uint4*)(st + frag_off[jj]);
+              const uint4 wh = *(const uint4*)(st + frag_off[jj] + 1024);
+              a0[0] = wl.x; a2[0] = wl.y; a0[1] = wl.z; a2[1] = wl.w;
+              a1[0] = wh.x; a3[0] = wh.y; a1[1] = wh.z; a3[1] = wh.w;
+            }
+            const int gl = u * U + jj;
+            const float s_lo = (jj & 1) ? bf16hi(sl[jj >> 1]) : bf16lo(sl[jj >> 1]);
+            const float s_hi = (jj & 1) ? bf16hi(sh[jj >> 1]) : bf16lo(sh[jj >> 1]);
+            const float b_lo = (jj & 1) ? bf16hi(bl[jj >> 1]) : bf16lo(bl[jj >> 1]);
+            const float b_hi = (jj & 1) ? bf16hi(bh[jj >> 1]) : bf16lo(bh[jj >> 1]);
+#pragma unroll
+            for (int nt = 0; nt < NTE; ++nt) {
+              {
+                int acc[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                  const uint2 bf = xf[((gl * 2 + i) * NT + nt) * 32 + lane];
+                  mma_u8s8(acc, a0[i], a1[i], a2[i], a3[i], bf.x, bf.y);
+                }
+                const float2 gs = *(const float2*)&gsb[((gl * NT + nt) * 4 + t) * 2];
+                const float f_lo = (float)(acc[0] * 128 + acc[1]), f_hi = (float)(acc[2] * 128 + acc[3]);
+                tot[nt][0] = fmaf(s_lo * gs.x, f_lo, fmaf(b_lo, gs.y, tot[nt][0]));
+                tot[nt][1] = fmaf(s_hi * gs.x, f_hi, fmaf(b_hi, gs.y, tot[nt][1]));
+              }
+            }
+          }
+        };
+        for (int u = kp; u < ut; u += ksplit) {
+          if (issued < total) issue(issued % kStages);
+          cp_async_commit();
+          ++issued;
+          cp_async_wait<kStages - 1>();
+          __syncwarp();
+          const unsigned char* st = my_ring_p + (consumed % kStages) * kStageBytes;
+          ++consumed;
+          if (nte == 1) unit(std::integral_constant<int, 1>{}, st, u);
+          else unit(std::integral_constant<int, 2>{}, st, u);
+          __syncwarp();
         }
-        cp_async_wait<0>();
-        if (ksplit > 1) {   // uniform over the CTA: every warp reaches both barriers
-          float* mine = red + (size_t)warp * (NT * 2 * 32);
+        if (ksplit == 1) store_tile(j, tot);
+      }
+      cp_async_wait<0>();
+      if (ksplit > 1) {   // uniform over the CTA: every warp reaches the barrier
+        float* mine = red + (size_t)warp * (NT * 2 * 32);
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) { mine[(nt * 2 + 0) * 32 + lane] = tot[nt][0]; mine[(nt * 2 + 1) * 32 + lane] = tot[nt][1]; }
-          __syncthreads();
-          if (kp == 0 && my_tiles > 0) {
-            for (int k = 1; k < ksplit; ++k) {
-              const float* o = red + (size_t)(warp + k) * (NT * 2 * 32);
+        for (int nt = 0; nt < NT; ++nt) { mine[(nt * 2 + 0) * 32 + lane] = tot[nt][0]; mine[(nt * 2 + 1) * 32 + lane] = tot[nt][1]; }
+        __syncthreads();
+        if (kp == 0 && my_tiles > 0) {
+          for (int k = 1; k < ksplit; ++k) {
+            const float* o = red + (size_t)(warp + k) * (NT * 2 * 32);
 #pragma unroll
-              for (int nt = 0; nt < NT; ++nt) { tot[nt][0] += o[(nt * 2 + 0) * 32 + lane]; tot[nt][1] += o[(nt * 2 + 1) * 32 + lane]; }
-            }
-            store_tile(first, tot);
+            for (int nt = 0; nt < NT; ++nt) { tot[nt][0] += o[(nt * 2 + 0) * 32 + lane]; tot[nt][1] += o[(nt * 2 + 1) * 32 + lane]; }
           }
+          store_tile(first, tot);
         }
       }
     }
@@ -448,9 +500,12 @@ int sm_count_g() {
   return cached[dev];
 }
 
-size_t smem_bytes(int K) {
-  return (size_t)kWarps * kStages * kStageBytes + (size_t)(K / 32) * 2 * 256 + (size_t)(K / 64) * 2 * 4 * 8 + (size_t)kWarps * 2 * 2 * 32 * 4 + 64;
+constexpr size_t kStaticSmem = 14 * 1024;   // upper bound of the kernel's static shared arrays
+size_t smem_bytes(int K, int nsb) {
+  return (size_t)kWarps * kStages * kStageBytes + (size_t)nsb * ((size_t)(K / 32) * 2 * 256 + (size_t)(K / 64) * 2 * 4 * 8) +
+         (size_t)kWarps * 2 * 2 * 32 * 4 + 64;
 }
+int pick_nsb(int K) { return smem_bytes(K, 2) + kStaticSmem <= 227 * 1024 ? 2 : 1; }
 
 }  // namespace
 
@@ -466,7 +521,7 @@ bool gather_stream_supported(const GatherArgs& a) {
   if ((((uintptr_t)a.x) & 15) != 0 || (a.x_batch_stride * (a.x_dtype == QB200_FLOAT32 ? 4 : 2)) % 16 != 0) return false;
   if (a.rhs_dtype != QB200_INT64 && a.rhs_dtype != QB200_INT32 && a.rhs_dtype != QB200_UINT32) return false;
   if (a.lhs && a.lhs_dtype != QB200_INT64 && a.lhs_dtype != QB200_INT32 && a.lhs_dtype != QB200_UINT32) return false;
-  return smem_bytes((int)a.K) + 14 * 1024 <= 227 * 1024;  // + static shared memory
+  return smem_bytes((int)a.K, 1) + kStaticSmem <= 227 * 1024;
 }
 
 cudaError_t launch_gather_stream(const GatherArgs& a, cudaStream_t st) {
@@ -478,15 +533,16 @@ cudaError_t launch_gather_stream(const GatherArgs& a, cudaStream_t st) {
   p.I = a.I; p.E = a.E; p.XB = a.XB; p.xstride = a.x_batch_stride;
   p.wes = a.w_expert_stride; p.ses = a.s_expert_stride;
   p.N = (int)a.N; p.K = (int)a.K; p.gshift = a.gs == 128 ? 1 : 0; p.x_f32 = a.x_dtype == QB200_FLOAT32;
-  const size_t smem = smem_bytes(p.K);
+  p.nsb = pick_nsb(p.K);
+  const size_t smem = smem_bytes(p.K, p.nsb);
   static bool done[2][64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   const int bi = a.bits == 4 ? 0 : 1;
   if (dev < 0 || dev >= 64 || !done[bi][dev]) {
     cudaError_t e = a.bits == 4
-        ? cudaFuncSetAttribute(gather_stream_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
-        : cudaFuncSetAttribute(gather_stream_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        ? cudaFuncSetAttribute(gather_stream_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024 - kStaticSmem))
+        : cudaFuncSetAttribute(gather_stream_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024 - kStaticSmem));
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) done[bi][dev] = true;
   }

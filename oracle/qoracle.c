@@ -64,6 +64,14 @@ QO_API void qo_f32_to_bf16(const float* x, uint16_t* out, int64_t n) {
 QO_API void qo_bf16_to_f32(const uint16_t* x, float* out, int64_t n) {
   for (int64_t i = 0; i < n; ++i) out[i] = bf16_to_f32(x[i]);
 }
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; a timing run may ask for the host's cores back. */
+QO_API void qo_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
 QO_API int qo_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

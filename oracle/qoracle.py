@@ -51,6 +51,11 @@ def num_threads() -> int:
     return int(lib().qo_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    """Threads the OpenMP loops use from now on (launchers like torchrun export OMP_NUM_THREADS=1)."""
+    lib().qo_set_num_threads(int(n))
+
+
 def f32_to_bf16(x) -> np.ndarray:
     x = _c(x, np.float32)
     out = np.empty(x.shape, np.uint16)
