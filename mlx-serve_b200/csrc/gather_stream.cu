@@ -73,6 +73,14 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, 
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// The same with a zero C operand (no accumulator initialisation in registers).
+__device__ __forceinline__ void mma_u8s8_z(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                           uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
 template <int BITS> __device__ __forceinline__ int swz(int row) { return BITS == 4 ? 2 * (row & 3) : 4 * (row & 1); }
 template <int BITS> __device__ __forceinline__ int kslot8(int h, int i) { return BITS == 4 ? 2 * i + h : 4 * h + i; }
 __device__ __forceinline__ int fix15(float x, float up) {
@@ -394,6 +402,9 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
         // one ring stage (16 rows x 128 bytes of codes) against the staged rows; NTE n8 tiles in use
         auto unit = [&](auto nte_c, const unsigned char* st, int u) {
           constexpr int NTE = decltype(nte_c)::value;
+          // fragments and group scales of this unit's U groups: every offset below is a compile-time constant
+          const uint2* xb = xf + (size_t)(u * U * 2 * NT) * 32 + lane;
+          const float* gb = gsb + (size_t)(u * U * NT * 4 + t) * 2;
           uint32_t sl[2], sh[2], bl[2], bh[2];
           {
             const unsigned char* sb = st + kStageW;
@@ -432,40 +443,38 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
               a0[0] = wl.x; a2[0] = wl.y; a0[1] = wl.z; a2[1] = wl.w;
               a1[0] = wh.x; a3[0] = wh.y; a1[1] = wh.z; a3[1] = wh.w;
             }
-            const int gl = u * U + jj;
             const float s_lo = (jj & 1) ? bf16hi(sl[jj >> 1]) : bf16lo(sl[jj >> 1]);
             const float s_hi = (jj & 1) ? bf16hi(sh[jj >> 1]) : bf16lo(sh[jj >> 1]);
             const float b_lo = (jj & 1) ? bf16hi(bl[jj >> 1]) : bf16lo(bl[jj >> 1]);
             const float b_hi = (jj & 1) ? bf16hi(bh[jj >> 1]) : bf16lo(bh[jj >> 1]);
 #pragma unroll
             for (int nt = 0; nt < NTE; ++nt) {
-              {
-                int acc[4] = {0, 0, 0, 0};
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                  const uint2 bf = xf[((gl * 2 + i) * NT + nt) * 32 + lane];
-                  mma_u8s8(acc, a0[i], a1[i], a2[i], a3[i], bf.x, bf.y);
-                }
-                const float2 gs = *(const float2*)&gsb[((gl * NT + nt) * 4 + t) * 2];
-                const float f_lo = (float)(acc[0] * 128 + acc[1]), f_hi = (float)(acc[2] * 128 + acc[3]);
-                tot[nt][0] = fmaf(s_lo * gs.x, f_lo, fmaf(b_lo, gs.y, tot[nt][0]));
-                tot[nt][1] = fmaf(s_hi * gs.x, f_hi, fmaf(b_hi, gs.y, tot[nt][1]));
-              }
+              int acc[4];
+              const uint2 bf0 = xb[((jj * 2 + 0) * NT + nt) * 32], bf1 = xb[((jj * 2 + 1) * NT + nt) * 32];
+              mma_u8s8_z(acc, a0[0], a1[0], a2[0], a3[0], bf0.x, bf0.y);
+              mma_u8s8(acc, a0[1], a1[1], a2[1], a3[1], bf1.x, bf1.y);
+              const float2 gs = *(const float2*)&gb[(jj * NT + nt) * 8];
+              const float f_lo = (float)(acc[0] * 128 + acc[1]), f_hi = (float)(acc[2] * 128 + acc[3]);
+              tot[nt][0] = fmaf(s_lo * gs.x, f_lo, fmaf(b_lo, gs.y, tot[nt][0]));
+              tot[nt][1] = fmaf(s_hi * gs.x, f_hi, fmaf(b_hi, gs.y, tot[nt][1]));
             }
           }
         };
-        for (int u = kp; u < ut; u += ksplit) {
-          if (issued < total) issue(issued % kStages);
-          cp_async_commit();
-          ++issued;
-          cp_async_wait<kStages - 1>();
-          __syncwarp();
-          const unsigned char* st = my_ring_p + (consumed % kStages) * kStageBytes;
-          ++consumed;
-          if (nte == 1) unit(std::integral_constant<int, 1>{}, st, u);
-          else unit(std::integral_constant<int, 2>{}, st, u);
-          __syncwarp();
-        }
+        auto sweep_k = [&](auto nte_c) {
+          for (int u = kp; u < ut; u += ksplit) {
+            if (issued < total) issue(issued % kStages);
+            cp_async_commit();
+            ++issued;
+            cp_async_wait<kStages - 1>();
+            __syncwarp();
+            const unsigned char* st = my_ring_p + (consumed % kStages) * kStageBytes;
+            ++consumed;
+            unit(nte_c, st, u);
+            __syncwarp();
+          }
+        };
+        if (nte == 1) sweep_k(std::integral_constant<int, 1>{});
+        else sweep_k(std::integral_constant<int, 2>{});
         if (ksplit == 1) store_tile(j, tot);
       }
       cp_async_wait<0>();

@@ -30,6 +30,11 @@
 //    The weight term q*s+b is never rounded to bf16.
 //  * A group's 8 warps split K for one 16-row tile and reduce through shared
 //    memory behind a named barrier, double-buffered so the stream never drains.
+//  * Thread-block clusters (M > 1): the CTAs of a cluster either split the
+//    conversion of the activations and broadcast the fragments through
+//    distributed shared memory, or -- when K is too long for one staging pass --
+//    share their tiles and split K, each converting only its own range, with the
+//    partial sums added in rank 0 behind one cluster barrier per round.
 // Nothing is written to global scratch; the only global writes are y.
 #include "kernels.h"
 
@@ -77,6 +82,8 @@ struct StreamK {
   int ntiles;
   int npass, kc;      // K passes of kc values
   int ntl_max;        // max tiles per group (sizes the multi-pass accumulator)
+  int ksplit;         // > 1: the CTAs of a cluster share their tiles and split K (partial sums meet in rank 0)
+  int upc;            // K units per CTA in that mode
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -107,6 +114,9 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t saddr, uint32_t rank) {
 __device__ __forceinline__ void st_cluster_v2(uint32_t addr, uint32_t x, uint32_t y) {
   asm volatile("st.shared::cluster.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
 // All threads of all CTAs of the cluster (a hardware barrier: no spinning in software).
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -119,6 +129,15 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, 
       "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// The same with a zero C operand (no accumulator initialisation in registers).
+__device__ __forceinline__ void mma_u8s8_z(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                           uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
 // 16-byte chunk swizzle inside a 128-byte stage row so that the fragment reads
@@ -192,7 +211,11 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int grp = warp / kWarpsPerGroup, ks = warp % kWarpsPerGroup;
-  const int ggrp = blockIdx.x * kGroups + grp;  // global group id
+  // K-split mode (large K at M > 1): the CTAs of a cluster work on the same tiles, each on its own range of K,
+  // so each converts only its range of the activations, once; rank 0 adds the partial sums and stores.
+  const bool split = !M1 && p.ksplit > 1;
+  const int crank = M1 ? 0 : (int)cluster_rank();
+  const int ggrp = (split ? (int)blockIdx.x / p.ksplit : (int)blockIdx.x) * kGroups + grp;  // global group id
   TL(0);
 
   // ---- shared memory carve-up ----
@@ -202,9 +225,9 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
   uint2* xfrag = (uint2*)sp;   sp += M1 ? (size_t)(kc / 32) * 8 * 8 : (size_t)(kc / 32) * NT * 32 * 8;
   float* gsc = (float*)sp;     sp += M1 ? (size_t)(kc / 64) * 8 : (size_t)(kc / 64) * NT * kTokPerTile * 8;  // (2^(E-14), 2^(E-14)*sum v)
   float* red = (float*)sp;     sp += (size_t)kGroups * 2 * RT * kWarpsPerGroup * NT * 64 * 4;
-  const uint2* zero8 = (const uint2*)sp; sp += 16;  // an all-zero B fragment for the unused columns
+  sp += 16;
   float* yacc = (float*)sp;    // [kGroups][ntl_max][NT*64], only when npass > 1
-  if (threadIdx.x == 0) *(uint2*)zero8 = make_uint2(0u, 0u);
+  float* xred = (float*)sp;    // K-split mode (npass == 1): [2][ksplit - 1][kGroups][256] partial sums from the peers
   // A CTA's shared memory may only be written by its cluster peers once it is running: arrive now, and
   // wait for every peer's arrival just before the first remote store.
   if constexpr (!M1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -212,7 +235,9 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
   const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring + (size_t)warp * kStages * kStageBytes);
   const unsigned char* my_ring_p = ring + (size_t)warp * kStages * kStageBytes;
   const int ntl = ggrp < p.ntiles ? (p.ntiles - ggrp + p.total_groups - 1) / p.total_groups : 0;
-  const int ut = p.K / CK, upk = kc / CK;
+  const int k_lo = split ? crank * p.upc * CK : 0;                 // first K value of this CTA's range
+  const int k_cta = split ? (p.K - k_lo < p.upc * CK ? (p.K - k_lo > 0 ? p.K - k_lo : 0) : p.upc * CK) : p.K;
+  const int ut = k_cta / CK, upk = split ? (ut > 0 ? ut : 1) : kc / CK;
 
   // ---- producer state: per-lane source pointers of the current tile ----
   const int chunk = lane & 7;
@@ -247,7 +272,7 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
       sbsrc = ((lane >> 4) ? QB_SEL4(p.b, mi) : QB_SEL4(p.s, mi)) + (int64_t)n * lds;
     }
     const uint32_t st = my_ring + stage * kStageBytes;
-    const int k0 = it.pass * kc + it.u * CK;
+    const int k0 = k_lo + it.pass * kc + it.u * CK;
     const int woff = k0 * BITS / 8;
 #pragma unroll
     for (int r = 0; r < 4; ++r) cp_async16(st + wdst[r], wsrc[r] + woff);
@@ -286,8 +311,8 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
   int red_buf = 0;
 
   for (int pass = 0; pass < p.npass; ++pass) {
-    const int k_base = pass * kc;
-    const int klen = (p.K - k_base) < kc ? (p.K - k_base) : kc;
+    const int k_base = k_lo + pass * kc;
+    const int klen = split ? k_cta : ((p.K - k_base) < kc ? (p.K - k_base) : kc);
     if (pass > 0) {  // every reader of the previous pass's fragments (cluster-wide) is done
       if constexpr (M1) __syncthreads(); else cluster_sync_all();
     }
@@ -300,13 +325,14 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
       const int total = slots * cpt;
       constexpr int PF = 4;  // chunks fetched per thread before any is converted (loads in flight together)
       // The CTAs of a cluster take interleaved blocks of kThreads chunks and broadcast what they convert.
-      const int CS = M1 ? 1 : (int)cluster_size(), crank = M1 ? 0 : (int)cluster_rank();
+      // (K-split mode: every CTA converts its own K range for itself)
+      const int CS = (M1 || split) ? 1 : (int)cluster_size(), crank_b = (M1 || split) ? 0 : crank;
       const uint32_t xfrag_s = (uint32_t)__cvta_generic_to_shared(xfrag), gsc_s = (uint32_t)__cvta_generic_to_shared(gsc);
       for (int base0 = 0; base0 < total; base0 += kThreads * PF * CS) {
        uint4 raw[PF][2];
 #pragma unroll
        for (int q = 0; q < PF; ++q) {
-        const int it = base0 + (q * CS + crank) * kThreads + tid;
+        const int it = base0 + (q * CS + crank_b) * kThreads + tid;
         raw[q][0] = make_uint4(0u, 0u, 0u, 0u);
         raw[q][1] = make_uint4(0u, 0u, 0u, 0u);
         if (it < total) {
@@ -338,7 +364,7 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
        }
 #pragma unroll
        for (int q = 0; q < PF; ++q) {
-        const int base = base0 + (q * CS + crank) * kThreads;
+        const int base = base0 + (q * CS + crank_b) * kThreads;
         if (base >= total) continue;
         const int it = base + tid;
         const bool ok = it < total;
@@ -381,7 +407,7 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
             } else {
               const uint32_t a = gsc_s + (uint32_t)(((gi * NT + nt) * kTokPerTile + ml) * 2) * 4u;
               for (int cr = 0; cr < CS; ++cr)
-                st_cluster_v2(map_to_rank(a, cr), __float_as_uint(down), __float_as_uint(down * (float)sum));
+                st_cluster_v2(map_to_rank(a, split ? crank : cr), __float_as_uint(down), __float_as_uint(down * (float)sum));
             }
           }
 #pragma unroll
@@ -395,7 +421,7 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
               xfrag[(gi * 2 + jm) * 8 + pl * 4 + tt] = o;
             } else {
               const uint32_t a = xfrag_s + (uint32_t)(((gi * 2 + jm) * NT + nt) * 32 + (2 * ml + pl) * 4 + tt) * 8u;
-              for (int cr = 0; cr < CS; ++cr) st_cluster_v2(map_to_rank(a, cr), o.x, o.y);
+              for (int cr = 0; cr < CS; ++cr) st_cluster_v2(map_to_rank(a, split ? crank : cr), o.x, o.y);
             }
           }
         }
@@ -406,8 +432,9 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
     if (pass == 0) TL(3);
 
     const int upt = (ut - pass * upk) < upk ? (ut - pass * upk) : upk;
-    for (int tl0 = 0; tl0 < ntl; tl0 += RT) {
-     const int rcnt = (ntl - tl0) < RT ? (ntl - tl0) : RT;
+    const int ntl_rounds = split ? p.ntl_max : ntl;   // K-split: the same number of rounds in every group and CTA
+    for (int tl0 = 0; tl0 < ntl_rounds; tl0 += RT) {
+     const int rcnt = (ntl - tl0) < RT ? ((ntl - tl0) > 0 ? (ntl - tl0) : 0) : RT;
      float* rb = red + ((size_t)(grp * 2 + red_buf) * RT * kWarpsPerGroup) * NT * 64;
      for (int r = 0; r < rcnt; ++r) {
 
@@ -448,7 +475,12 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
             }
           }
         }
-        const int gl0 = u * U;  // first 64-group of this unit inside the staged pass
+        // Fragments and group scales of this unit's U groups; every offset below is a compile-time constant.
+        // Single token: only the two plane columns 0 and 1 of the n8 tile are read back (by the lanes
+        // with t == 0), so the lanes that feed columns 2..7 may load anything: they re-read columns 0/1.
+        const uint2* xb = M1 ? xfrag + (size_t)(u * U * 2) * 8 + (g & 1) * 4 + t
+                             : xfrag + (size_t)(u * U * 2 * NT) * 32 + lane;
+        const float* gb = M1 ? gsc + (size_t)(u * U) * 2 : gsc + (size_t)(u * U * NT * kTokPerTile + t) * 2;
 #pragma unroll
         for (int j = 0; j < U; ++j) {
           uint32_t a0[2], a1[2], a2[2], a3[2];  // [mma]: row g lo, row g+8 lo, row g hi, row g+8 hi
@@ -465,32 +497,27 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
             a0[0] = wl.x; a2[0] = wl.y; a0[1] = wl.z; a2[1] = wl.w;
             a1[0] = wh.x; a3[0] = wh.y; a1[1] = wh.z; a3[1] = wh.w;
           }
-          const int gl = gl0 + j;
           const float s_lo = (j & 1) ? bf16hi(sl[j >> 1]) : bf16lo(sl[j >> 1]);
           const float s_hi = (j & 1) ? bf16hi(sh[j >> 1]) : bf16lo(sh[j >> 1]);
           const float b_lo = (j & 1) ? bf16hi(bl[j >> 1]) : bf16lo(bl[j >> 1]);
           const float b_hi = (j & 1) ? bf16hi(bh[j >> 1]) : bf16lo(bh[j >> 1]);
           if constexpr (M1) {
-            int acc[4] = {0, 0, 0, 0};
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              const uint2 bf = *(g < 2 ? &xfrag[(gl * 2 + i) * 8 + g * 4 + t] : zero8);
-              mma_u8s8(acc, a0[i], a1[i], a2[i], a3[i], bf.x, bf.y);
-            }
-            const float2 gs = *(const float2*)&gsc[gl * 2];
+            int acc[4];
+            const uint2 bf0 = xb[(j * 2 + 0) * 8], bf1 = xb[(j * 2 + 1) * 8];
+            mma_u8s8_z(acc, a0[0], a1[0], a2[0], a3[0], bf0.x, bf0.y);
+            mma_u8s8(acc, a0[1], a1[1], a2[1], a3[1], bf1.x, bf1.y);
+            const float2 gs = *(const float2*)&gb[j * 2];
             const float f_lo = (float)(acc[0] * 128 + acc[1]), f_hi = (float)(acc[2] * 128 + acc[3]);
             tot[0][0] = fmaf(s_lo * gs.x, f_lo, fmaf(b_lo, gs.y, tot[0][0]));
             tot[0][1] = fmaf(s_hi * gs.x, f_hi, fmaf(b_hi, gs.y, tot[0][1]));
           } else {
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-              int acc[4] = {0, 0, 0, 0};
-#pragma unroll
-              for (int i = 0; i < 2; ++i) {
-                const uint2 bf = xfrag[((gl * 2 + i) * NT + nt) * 32 + lane];
-                mma_u8s8(acc, a0[i], a1[i], a2[i], a3[i], bf.x, bf.y);
-              }
-              const float2 gs = *(const float2*)&gsc[((gl * NT + nt) * kTokPerTile + t) * 2];
+              int acc[4];
+              const uint2 bf0 = xb[((j * 2 + 0) * NT + nt) * 32], bf1 = xb[((j * 2 + 1) * NT + nt) * 32];
+              mma_u8s8_z(acc, a0[0], a1[0], a2[0], a3[0], bf0.x, bf0.y);
+              mma_u8s8(acc, a0[1], a1[1], a2[1], a3[1], bf1.x, bf1.y);
+              const float2 gs = *(const float2*)&gb[(j * NT + nt) * kTokPerTile * 2];
               const float f_lo = (float)(acc[0] * 128 + acc[1]), f_hi = (float)(acc[2] * 128 + acc[3]);
               tot[nt][0] = fmaf(s_lo * gs.x, f_lo, fmaf(b_lo, gs.y, tot[nt][0]));
               tot[nt][1] = fmaf(s_hi * gs.x, f_hi, fmaf(b_hi, gs.y, tot[nt][1]));
@@ -512,6 +539,35 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
      group_barrier(grp);
      const int gt = tid - grp * (kWarpsPerGroup * 32);  // thread index inside the group
      const int ncols = M1 ? 1 : NT * kTokPerTile;
+     if (split) {
+       // RT * NT == 4, so a round has at most 256 outputs per group: one per thread
+       const int o = gt;
+       const int row = o & 15, rc = o >> 4;
+       const int r = rc / ncols, col = rc - r * ncols;
+       const int nt = col / kTokPerTile, c = col - nt * kTokPerTile;
+       const bool live = o < rcnt * 16 * ncols;
+       float v = 0.f;
+       if (live) {
+#pragma unroll
+         for (int k = 0; k < kWarpsPerGroup; ++k) v += rb[(((size_t)r * kWarpsPerGroup + k) * NT + nt) * 64 + row * 4 + c];
+       }
+       float* slot0 = xred + ((size_t)red_buf * (p.ksplit - 1) * kGroups + grp) * 256 + gt;  // peer 1's slot of this round
+       if (crank != 0)
+         st_cluster_f32(map_to_rank((uint32_t)__cvta_generic_to_shared(slot0 + (size_t)(crank - 1) * kGroups * 256), 0), v);
+       cluster_sync_all();
+       if (crank == 0 && live) {
+         for (int k = 0; k + 1 < p.ksplit; ++k) v += slot0[(size_t)k * kGroups * 256];
+         const int tile = ggrp + (tl0 + r) * p.total_groups;
+         const int mi = mat_of_tile(p, tile);
+         const int n = (tile - QB_SEL4(p.tile0, mi)) * 16 + row;
+         if (n < QB_SEL4(p.N, mi) && col < p.M) {
+           void* ym = QB_SEL4(p.y, mi);
+           const int64_t ldy = QB_SEL4(p.ldy, mi);
+           if (p.x_f32) ((float*)ym)[(int64_t)col * ldy + n] = v;
+           else ((uint16_t*)ym)[(int64_t)col * ldy + n] = f32_to_bf16_bits(v);
+         }
+       }
+     } else
      for (int o = gt; o < rcnt * 16 * ncols; o += kWarpsPerGroup * 32) {
         const int row = o & 15, rc = o >> 4;
         const int r = rc / ncols, col = rc - r * ncols;
@@ -562,30 +618,52 @@ int sm_count() {
 }
 
 // Grid, K passes and shared-memory footprint of one instantiation; false when it does not fit.
-bool plan_stream(StreamK& p, int NT, bool M1, int* grid_out, size_t* smem_out, int cluster = 1, int max_ctas = 0) {
+bool plan_stream(StreamK& p, int NT, bool M1, int* grid_out, size_t* smem_out, int* cluster_out = nullptr, int cluster = 1,
+                 int max_ctas = 0, int ck = 256, int split_cluster = 0, int split_ctas = 0) {
   int nsm = sm_count() * (M1 ? 2 : 1);  // CTA slots
   if (max_ctas > 0 && max_ctas < nsm) nsm = max_ctas;
   const int kGroups = groups_for(M1);
   int ntiles = 0;
   for (int i = 0; i < p.nmat; ++i) { p.tile0[i] = ntiles; ntiles += (p.N[i] + 15) / 16; }
   for (int i = p.nmat; i <= kMaxMat; ++i) p.tile0[i] = ntiles;
-  const int total_groups = ntiles < kGroups * nsm ? ntiles : kGroups * nsm;
-  int grid = (total_groups + kGroups - 1) / kGroups;
-  grid = (grid + cluster - 1) / cluster * cluster;   // whole clusters; CTAs beyond the tiles only help staging
   p.ntiles = ntiles;
-  p.total_groups = grid * kGroups;
+  p.ksplit = 1;
+  p.upc = 0;
+  // K-split across the cluster: when K does not fit one staging pass, but a cluster's share of it does
+  // and still gives every warp of a group at least one unit per tile.
+  if (!M1 && split_cluster > 1 && p.K > kc_for(NT)) {
+    const int ut = p.K / ck, upc = (ut + split_cluster - 1) / split_cluster;
+    if (upc * ck <= kc_for(NT) && upc >= kWarpsPerGroup) { p.ksplit = split_cluster; p.upc = upc; }
+  }
+  int grid;
+  if (p.ksplit > 1) {
+    cluster = split_cluster;
+    const int nclus = (split_ctas > 0 ? split_ctas : nsm) / cluster;
+    const int groups = ntiles < kGroups * nclus ? ntiles : kGroups * nclus;
+    const int used = (groups + kGroups - 1) / kGroups;
+    grid = used * cluster;
+    p.total_groups = used * kGroups;
+    p.kc = p.upc * ck;
+  } else {
+    const int total_groups = ntiles < kGroups * nsm ? ntiles : kGroups * nsm;
+    grid = (total_groups + kGroups - 1) / kGroups;
+    grid = (grid + cluster - 1) / cluster * cluster;   // whole clusters; CTAs beyond the tiles only help staging
+    p.total_groups = grid * kGroups;
+    p.kc = p.K < kc_for(NT) ? p.K : kc_for(NT);
+    if (M1) p.kc = p.K;
+  }
   p.ntl_max = (ntiles + p.total_groups - 1) / p.total_groups;
-  p.kc = p.K < kc_for(NT) ? p.K : kc_for(NT);
-  if (M1) p.kc = p.K;
-  p.npass = (p.K + p.kc - 1) / p.kc;
+  p.npass = p.ksplit > 1 ? 1 : (p.K + p.kc - 1) / p.kc;
   size_t smem = (size_t)kGroups * kWarpsPerGroup * stages_for(NT) * kStageBytes;
   smem += M1 ? (size_t)(p.kc / 32) * 64 : (size_t)(p.kc / 32) * NT * 256;
   smem += M1 ? (size_t)(p.kc / 64) * 8 : (size_t)(p.kc / 64) * NT * kTokPerTile * 8;
   smem += (size_t)kGroups * 2 * rt_for(NT, M1) * kWarpsPerGroup * NT * 256;
   smem += 16;
   if (p.npass > 1) smem += (size_t)kGroups * p.ntl_max * NT * 256;
+  if (p.ksplit > 1) smem += (size_t)2 * (p.ksplit - 1) * kGroups * 256 * 4;
   *grid_out = grid;
   *smem_out = smem;
+  if (cluster_out) *cluster_out = cluster;
   return smem <= (size_t)(M1 ? 113 : 227) * 1024;
 }
 
@@ -599,16 +677,17 @@ template <int BITS, int NT, bool M1>
 cudaError_t launch_inst(StreamK p, cudaStream_t st) {
   auto kern = qmv_stream_kernel<BITS, NT, M1>;
   static bool attr_done[64] = {};
-  static int cluster_of[64] = {}, max_ctas_of[64] = {};
+  static int cluster_of[64] = {}, max_ctas_of[64] = {}, split_cluster_of[64] = {}, split_ctas_of[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  const bool cached = dev >= 0 && dev < 64;
-  if (!cached || !attr_done[dev]) {
+  const int di = (dev >= 0 && dev < 64) ? dev : 0;
+  if (!attr_done[di] || di != dev) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
-    // Cluster size for the shared activation staging: the largest of 4, 2 whose co-resident clusters
-    // (at the full shared-memory footprint) still cover at least 97% of the SMs; 1 otherwise.
-    int cs = 1, ctas = sm_count();
+    // Cluster size for the shared activation staging: the largest of 4, 2 whose co-resident clusters (at the
+    // full shared-memory footprint) still cover at least 97% of the SMs; 1 otherwise.  The K-split mode
+    // needs 4 and accepts losing up to 15% of the SMs to cluster placement.
+    int cs = 1, ctas = sm_count(), scs = 0, sctas = 0;
     if (!M1) {
       for (int c = 4; c >= 2; c >>= 1) {
         cudaLaunchConfig_t q = {};
@@ -621,21 +700,22 @@ cudaError_t launch_inst(StreamK p, cudaStream_t st) {
         q.attrs = qa;
         q.numAttrs = 1;
         int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, kern, &q) == cudaSuccess && n * c * 100 >= sm_count() * 97) {
-          cs = c;
-          ctas = n * c < sm_count() ? n * c : (sm_count() / c) * c;
-          break;
-        }
-        (void)cudaGetLastError();
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &q) != cudaSuccess) { (void)cudaGetLastError(); continue; }
+        const int covered = n * c < sm_count() ? n * c : (sm_count() / c) * c;
+        if (c == 4 && covered * 100 >= sm_count() * 85) { scs = 4; sctas = covered; }
+        if (cs == 1 && covered * 100 >= sm_count() * 97) { cs = c; ctas = covered; }
       }
     }
-    if (cached) { cluster_of[dev] = cs; max_ctas_of[dev] = ctas; attr_done[dev] = true; }
-    else { cluster_of[0] = cs; max_ctas_of[0] = ctas; }
+    cluster_of[di] = cs; max_ctas_of[di] = ctas; split_cluster_of[di] = scs; split_ctas_of[di] = sctas;
+    attr_done[di] = true;
   }
-  const int cs = cluster_of[cached ? dev : 0], max_ctas = max_ctas_of[cached ? dev : 0];
+  int cs = cluster_of[di];
+  const int max_ctas = max_ctas_of[di];
   int grid = 0;
   size_t smem = 0;
-  if (!plan_stream(p, NT, M1, &grid, &smem, cs, M1 ? 0 : max_ctas)) return cudaErrorInvalidConfiguration;
+  if (!plan_stream(p, NT, M1, &grid, &smem, &cs, cs, M1 ? 0 : max_ctas, BITS == 4 ? 256 : 128, split_cluster_of[di],
+                   split_ctas_of[di]))
+    return cudaErrorInvalidConfiguration;
   // Programmatic dependent launch: this grid may start (and prefetch weights, which no kernel writes)
   // before the previous grid in the stream has finished; it waits for that grid before touching x or y.
   cudaLaunchConfig_t cfg = {};
