@@ -329,11 +329,12 @@ def main():
                 qb200.gather_qmm(act, *banks["down"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yd)
             return run, int(torch.unique(sorted_inds).numel())
 
-        # 64 tokens: one block touches (nearly) every expert, 340 MB of banks > L2.
+        # 64 tokens: one block touches (nearly) every expert, 340 MB of banks > L2.  4096 tokens (prefill): 32768
+        # routed rows, 256 per expert on average -- a grouped GEMM; reported in TFLOP/s as well.
         # 1 token: 16 blocks in the graph, each routed to a disjoint set of 8 experts, so the replay still
         # streams all 128 experts from HBM instead of re-reading 21 MB from L2.
-        for T in (64, 1):
-            if T == 64:
+        for T in (64, 1, 4096):
+            if T != 1:
                 logits = torch.randn((T, E), device=dev, generator=g)
                 runs = [block(T, torch.topk(torch.softmax(logits, -1), topk, dim=-1).indices.reshape(-1))]
             else:
@@ -350,7 +351,8 @@ def main():
             uniq = runs[0][1]
             by = 3 * uniq * per_expert + T * topk * 2 * (2 * (H + I) + (I + H))
             res[f"tokens{T}"] = {"us_per_block": ms * 1e3, "unique_experts": uniq, "bytes": by,
-                                 "GBps": by / (ms * 1e-3) / 1e9}
+                                 "GBps": by / (ms * 1e-3) / 1e9,
+                                 "TFLOPs": 2.0 * T * topk * 3 * H * I / (ms * 1e-3) / 1e12}
             del gr
         if rank == 0:
             print(json.dumps(res))

@@ -441,7 +441,12 @@ QB200_API int qb200_gather_qmm(qb200_tensor* res, const qb200_tensor* x, const q
   if (a.I == 0 || M == 0 || N == 0) return QB200_OK;
   if (K == 0) return fail(QB200_ERR_BAD_SHAPE, "gather_qmm: empty contraction axis");
   cudaError_t e;
-  if (gather_stream_supported(a)) e = launch_gather_stream(a, (cudaStream_t)s);
+  // Few rows per expert: stream every hit expert once.  Many sorted rows (MoE prefill): grouped GEMM on the
+  // tensor-core kernel, from 32 rows per expert on average.
+  const bool many = a.I >= 32 * a.E && a.I >= 1024;
+  if (many && gather_tc_supported(a)) e = launch_gather_tc(a, (cudaStream_t)s);
+  else if (gather_stream_supported(a)) e = launch_gather_stream(a, (cudaStream_t)s);
+  else if (gather_tc_supported(a) && a.I >= 1024) e = launch_gather_tc(a, (cudaStream_t)s);
   else if (gather_mma_supported(a)) e = launch_gather_mma(a, (cudaStream_t)s);
   else e = launch_gather_generic(a, (cudaStream_t)s);
   if (e != cudaSuccess) return cuda_fail(e, "gather_qmm");

@@ -52,6 +52,9 @@ cudaError_t launch_qmv_stream_multi(const QmmArgs* a, int count, cudaStream_t st
 bool qmm_tc_supported(const QmmArgs& a);
 cudaError_t launch_qmm_tc(const QmmArgs& a, cudaStream_t st);
 int qmm_tc_error_code();  // 0, or the code of a bounded wait that expired in the last failing launch
+struct GatherArgs;
+bool gather_tc_supported(const GatherArgs& a);   // rows sorted by expert, many rows: grouped GEMM on the same kernel
+cudaError_t launch_gather_tc(const GatherArgs& a, cudaStream_t st);
 
 struct GatherArgs {
   const void* x; const uint32_t* w; const void* s; const void* b; void* y;

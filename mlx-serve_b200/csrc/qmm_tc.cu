@@ -43,7 +43,10 @@
 namespace qb {
 namespace {
 
-constexpr int BM = 256, BN_MAX = 128, BK = 64, STAGES = 4;
+constexpr int BM = 256, BN_MAX = 128, BK = 64;
+// ring depth: the grouped (routed-expert) form gives one stage's room to its row-offset tables
+__host__ __device__ constexpr int stages_of(bool grouped) { return grouped ? 3 : 4; }
+constexpr int kMaxGroupExperts = 1024;
 constexpr int kDequantGroups = 2;                   // group g converts the k-blocks with (index % 2) == g
 constexpr int kDequantWarps = 8 * kDequantGroups, kEpiWarps = 4;
 constexpr int kDequantThreads = 256;                 // threads that fill one stage: two per weight row
@@ -79,6 +82,15 @@ struct TcK {
   int BN;       // weight rows per tile (multiple of 16, <= 128)
   int tiles_m, ntiles;
   int sb_vec;   // scales / biases can be fetched 8 at a time (16-byte aligned rows, whole windows)
+  // grouped form (gather_qmm with rows sorted by expert): M = routed rows, N = rows of ONE expert's matrix,
+  // w/s/b are the banks [E][N][.] seen as one matrix of E*N rows, rhs[i] = expert of row i (ascending)
+  const void* rhs; int rhs_i64; int E;
+};
+
+struct TileCoord {
+  int row0, row_end;     // token rows [row0, min(row0 + 256, row_end)) of x / y
+  int n0, nend;          // output columns [n0, nend) of y
+  int wrow0, wrow_last;  // first weight row of the tile in the (stacked) weight matrix; last row that may be read
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -226,11 +238,12 @@ __device__ __forceinline__ void dequant_half(const uint32_t* codes, uint32_t sb2
   }
 }
 
-template <int BITS>
+template <int BITS, bool GROUPED>
 __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, TcK p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // 1024-byte alignment for the swizzled tiles
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int STAGES = stages_of(GROUPED);
   unsigned char* a_tiles = smem;                                   // [STAGES][2][128 x 64 bf16]
   unsigned char* b_tiles = smem + STAGES * A_STAGE_BYTES;          // [STAGES][BN x 64 bf16]
   unsigned char* raw = b_tiles + STAGES * B_STAGE_BYTES;           // [2][BN x 128 B of packed codes]
@@ -240,6 +253,9 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
   uint64_t* raw_full = bars + 3 * STAGES + 4, *raw_empty = bars + 3 * STAGES + 6;
   uint32_t* tmem_slot = (uint32_t*)(bars + 3 * STAGES + 8);
   volatile int& s_fail = *(volatile int*)(tmem_slot + 1);
+  // grouped form: first routed row of every expert and the prefix of their tile counts
+  int* s_off = (int*)(tmem_slot + 4);               // [E + 1]
+  int* s_tcum = s_off + (kMaxGroupExperts + 1);     // [E + 1]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nkb = p.K / BK;
@@ -263,14 +279,77 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
-  // Tile t of this CTA's list: token block t % tiles_m (fastest, so that CTAs running side by side
-  // share a weight tile through L2), weight block t / tiles_m.
+  const int tiles_nn = (p.N + BN - 1) / BN;   // weight-row blocks of one matrix
+  int ntiles = p.ntiles;
+  if constexpr (GROUPED) {
+    // rhs is ascending: expert e owns rows [lower_bound(e), lower_bound(e + 1)); each expert contributes
+    // ceil(rows / 256) * tiles_nn tiles.  Every CTA builds the same tables.
+    for (int e = tid; e <= p.E; e += kThreads) {
+      int lo = 0, hi = p.M;   // first index whose expert is >= e
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        const long long v = p.rhs_i64 ? ((const long long*)p.rhs)[mid] : (long long)((const int*)p.rhs)[mid];
+        if (v < e) lo = mid + 1; else hi = mid;
+      }
+      s_off[e] = lo;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      int base = 0;
+      for (int e0 = 0; e0 < p.E; e0 += 32) {
+        const int e = e0 + lane;
+        const int cnt = e < p.E ? s_off[e + 1] - s_off[e] : 0;
+        const int nt = ((cnt + BM - 1) / BM) * tiles_nn;
+        int inc = nt;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int o = __shfl_up_sync(0xffffffffu, inc, d);
+          if (lane >= d) inc += o;
+        }
+        if (e < p.E) s_tcum[e] = base + inc - nt;
+        base += __shfl_sync(0xffffffffu, inc, 31);
+      }
+      if (lane == 0) s_tcum[p.E] = base;
+    }
+    __syncthreads();
+    ntiles = s_tcum[p.E];
+  }
+  // Tile t -> coordinates.  Dense: token block t % tiles_m (fastest, so that CTAs running side by side share
+  // a weight tile through L2), weight block t / tiles_m.  Grouped: the expert whose tile range holds t, then
+  // the same order inside the expert.
+  auto coords = [&](int tile) {
+    TileCoord c;
+    if constexpr (GROUPED) {
+      int a = 0, b = p.E;   // s_tcum[a] <= tile < s_tcum[b]
+      while (b - a > 1) {
+        const int m = (a + b) >> 1;
+        if (s_tcum[m] <= tile) a = m; else b = m;
+      }
+      const int local = tile - s_tcum[a];
+      const int rows = s_off[a + 1] - s_off[a], tm = (rows + BM - 1) / BM;
+      const int nb = local / tm, mb = local - nb * tm;
+      c.row0 = s_off[a] + mb * BM;
+      c.row_end = s_off[a + 1];
+      c.n0 = nb * BN;
+      c.nend = (c.n0 + BN) < p.N ? (c.n0 + BN) : p.N;
+      c.wrow0 = a * p.N + c.n0;
+      c.wrow_last = a * p.N + p.N - 1;
+    } else {
+      c.row0 = (tile % p.tiles_m) * BM;
+      c.row_end = p.M;
+      c.n0 = (tile / p.tiles_m) * BN;
+      c.nend = (c.n0 + BN) < p.N ? (c.n0 + BN) : p.N;
+      c.wrow0 = c.n0;
+      c.wrow_last = p.N - 1;
+    }
+    return c;
+  };
   if (warp == kTmaWarp) {
     if (lane == 0) {
       // ---------------- TMA producer (one thread) ----------------
       int it = 0, fail = 0;
-      for (int tile = blockIdx.x; tile < p.ntiles && !fail && !s_fail; tile += gridDim.x) {
-        const int m0 = (tile % p.tiles_m) * BM;
+      for (int tile = blockIdx.x; tile < ntiles && !fail && !s_fail; tile += gridDim.x) {
+        const int m0 = coords(tile).row0;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int st = it % STAGES;
           if (it >= STAGES && !mbar_wait_relaxed(&empty[st], ((it / STAGES) - 1) & 1)) { fail = 3; break; }
@@ -287,8 +366,8 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       // ---------------- TMA producer of the packed codes (one thread) ----------------
       const int sb_per_tile = nkb / KPS;
       int sbk = 0, fail = 0;
-      for (int tile = blockIdx.x; tile < p.ntiles && !fail && !s_fail; tile += gridDim.x) {
-        const int n0 = (tile / p.tiles_m) * BN;
+      for (int tile = blockIdx.x; tile < ntiles && !fail && !s_fail; tile += gridDim.x) {
+        const int n0 = coords(tile).wrow0;
         for (int sbl = 0; sbl < sb_per_tile; ++sbl, ++sbk) {
           const int buf = sbk & 1;
           if (sbk >= 2 && !mbar_wait_relaxed(&raw_empty[buf], ((sbk >> 1) - 1) & 1)) { fail = 7; break; }
@@ -306,9 +385,9 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       int it = 0, fail = 0, ti = 0;
       PROF_DECL;
       PROF_T0();
-      for (int tile = blockIdx.x; tile < p.ntiles && !fail && !s_fail; tile += gridDim.x, ++ti) {
-        const int m0 = (tile % p.tiles_m) * BM;
-        const bool two_halves = m0 + 128 < p.M;  // the second 128 token rows hold real tokens
+      for (int tile = blockIdx.x; tile < ntiles && !fail && !s_fail; tile += gridDim.x, ++ti) {
+        const TileCoord tc = coords(tile);
+        const bool two_halves = tc.row0 + 128 < tc.row_end;  // the second 128 token rows hold real tokens
         const int buf = ti & 1;
         if (ti >= 2 && !mbar_wait_relaxed(&acc_empty[buf], ((ti >> 1) - 1) & 1)) { fail = 6; break; }
         PROF_ADD(0);
@@ -345,7 +424,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
     const int grp = warp >> 3, wg = warp & 7;
     const int r = (wg & 3) * 32 + lane, h = wg >> 2;
     const bool active = r < BN;
-    const int ntl = (p.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;  // tiles of this CTA
+    const int ntl = ntiles > (int)blockIdx.x ? (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;  // tiles of this CTA
     const int total_it = ntl * nkb;
     // Scales and biases of this thread's row: windows of 8 values (8 << gshift k-blocks), the next
     // window prefetched while the current one is used.  f_* is the prefetch cursor (tile, k-block).
@@ -354,8 +433,9 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
     int f_tl = 0, f_kb = 0;
     auto row_of = [&](int tl) {
       const int tile = blockIdx.x + tl * gridDim.x;
-      const int n = (tile / p.tiles_m) * BN + r;
-      return n < p.N ? n : p.N - 1;
+      const TileCoord tc = coords(tile);
+      const int n = tc.wrow0 + r;
+      return n < tc.wrow_last ? n : tc.wrow_last;
     };
     auto prefetch_window = [&]() {
       if (f_kb >= nkb) { f_kb = 0; ++f_tl; }
@@ -427,23 +507,23 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
     const int q = warp & 3;   // TMEM lane quarter this warp may read
     int ti = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, ++ti) {
-      const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
-      const int nend = (n0 + BN) < p.N ? (n0 + BN) : p.N;
+    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++ti) {
+      const TileCoord tc = coords(tile);
+      const int m0 = tc.row0, n0 = tc.n0, nend = tc.nend, mend = tc.row_end;
       const int buf = ti & 1;
       ok = mbar_wait_relaxed(&acc_full[buf], (ti >> 1) & 1);
       if (!ok || s_fail) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
       for (int half = 0; half < 2; ++half) {
-        if (half == 1 && m0 + 128 >= p.M) break;
+        if (half == 1 && m0 + 128 >= mend) break;
         const int m = m0 + half * 128 + q * 32 + lane;  // TMEM lane = token row
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
           uint32_t v[32];
           tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + half * 128 + c0, v);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          if (m < p.M) {
+          if (m < mend) {
             uint16_t* yrow = p.y + (int64_t)m * p.ldy + n0 + c0;
             const int nvalid = nend - (n0 + c0);   // columns of this chunk inside the matrix and the tile
             const bool aligned = (((uintptr_t)yrow) & 15) == 0;
@@ -495,7 +575,10 @@ EncodeFn get_encode() {
   return fn;
 }
 
-constexpr size_t kSmemBytes = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 2 * RAW_BYTES + (3 * STAGES + 8) * 8 + 16 + 1024;
+constexpr size_t smem_bytes_tc(bool grouped) {
+  return (size_t)stages_of(grouped) * (A_STAGE_BYTES + B_STAGE_BYTES) + 2 * RAW_BYTES + (3 * stages_of(grouped) + 8) * 8 + 16 +
+         (grouped ? (size_t)2 * (kMaxGroupExperts + 1) * 4 : 0) + 1024;
+}
 
 int sm_count_tc() {
   static int cached[64] = {};
@@ -540,7 +623,34 @@ bool qmm_tc_supported(const QmmArgs& a) {
   return true;
 }
 
-cudaError_t launch_qmm_tc(const QmmArgs& a, cudaStream_t st) {
+namespace {
+
+// One launch of either form.  x: [M rows][K] bf16 with row pitch ldx; weights: `wrows` rows (N for the dense
+// form, E * N stacked expert rows for the grouped form) with pitches ldw / lds.
+struct TcLaunch {
+  const void* x; int64_t M, K, ldx;
+  const uint32_t* w; const uint16_t* s; const uint16_t* b; int64_t wrows, N, ldw, lds;
+  uint16_t* y; int64_t ldy;
+  int bits, gs;
+  const void* rhs; int rhs_i64; int E;   // grouped form only
+};
+
+template <int BITS, bool GROUPED>
+cudaError_t launch_tc_inst(const CUtensorMap& xmap, const CUtensorMap& wmap, const TcK& p, dim3 grid, cudaStream_t st) {
+  static bool done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  constexpr size_t smem = smem_bytes_tc(GROUPED);
+  if (dev < 0 || dev >= 64 || !done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(qmm_tc_kernel<BITS, GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) done[dev] = true;
+  }
+  qmm_tc_kernel<BITS, GROUPED><<<grid, kThreads, smem, st>>>(xmap, wmap, p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_tc(const TcLaunch& a, bool grouped, cudaStream_t st) {
   EncodeFn enc = get_encode();
   if (!enc) return cudaErrorNotSupported;
   CUtensorMap map;
@@ -548,51 +658,83 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, cudaStream_t st) {
   const cuuint64_t strides[1] = {(cuuint64_t)a.ldx * 2};
   const cuuint32_t box[2] = {BK, 128};
   const cuuint32_t estr[2] = {1, 1};
-  const void* xptr = (const char*)a.x + a.xb.offset(0) * 2;
-  CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)xptr, dims, strides, box, estr,
+  CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)a.x, dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
   TcK p;
   const int nsm = sm_count_tc();
-  p.BN = pick_bn(a.M, a.N, nsm);
-  // packed codes as a [N][K * bits / 32] array of 32-bit words: 128 bytes of BN rows per copy
+  // the grouped form does not know its tile count on the host: full-width tiles
+  p.BN = grouped ? (a.N >= BN_MAX ? BN_MAX : (int)((a.N + 15) / 16 * 16)) : pick_bn(a.M, a.N, nsm);
+  // packed codes as a [rows][K * bits / 32] array of 32-bit words: 128 bytes of BN rows per copy
   CUtensorMap wmap;
   {
-    const cuuint64_t wdims[2] = {(cuuint64_t)(a.K * a.bits / 32), (cuuint64_t)a.N};
+    const cuuint64_t wdims[2] = {(cuuint64_t)(a.K * a.bits / 32), (cuuint64_t)a.wrows};
     const cuuint64_t wstrides[1] = {(cuuint64_t)a.ldw * 4};
     const cuuint32_t wbox[2] = {32, (cuuint32_t)p.BN};
-    const void* wptr = (const void*)(a.w + a.wb.offset(0));
-    r = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)wptr, wdims, wstrides, wbox, estr,
+    r = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)a.w, wdims, wstrides, wbox, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
   }
-  p.w = a.w + a.wb.offset(0);
-  p.s = (const uint16_t*)a.s + a.sb.offset(0);
-  p.b = (const uint16_t*)a.b + a.sb.offset(0);
-  p.y = (uint16_t*)a.y + a.yb.offset(0);
+  p.w = a.w; p.s = a.s; p.b = a.b; p.y = a.y;
   p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
   p.ldw = a.ldw; p.lds = a.lds; p.ldy = a.ldy;
   p.gshift = a.gs == 128 ? 1 : 0;
   p.sb_vec = (a.lds % 8 == 0) && ((((uintptr_t)p.s) | ((uintptr_t)p.b)) & 15) == 0 && (a.K % (512 << p.gshift)) == 0;
   p.tiles_m = (int)((a.M + BM - 1) / BM);
-  p.ntiles = p.tiles_m * (int)((a.N + p.BN - 1) / p.BN);
-  dim3 grid((unsigned)(p.ntiles < nsm ? p.ntiles : nsm), 1, 1);
-  static bool done[2][64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  const int bi = a.bits == 4 ? 0 : 1;
-  if (dev < 0 || dev >= 64 || !done[bi][dev]) {
-    cudaError_t e = a.bits == 4
-        ? cudaFuncSetAttribute(qmm_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes)
-        : cudaFuncSetAttribute(qmm_tc_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-    if (e != cudaSuccess) return e;
-    if (dev >= 0 && dev < 64) done[bi][dev] = true;
-  }
-  if (a.bits == 4) qmm_tc_kernel<4><<<grid, kThreads, kSmemBytes, st>>>(map, wmap, p);
-  else qmm_tc_kernel<8><<<grid, kThreads, kSmemBytes, st>>>(map, wmap, p);
-  return cudaGetLastError();
+  p.ntiles = p.tiles_m * (int)((a.N + p.BN - 1) / p.BN);   // dense form; the grouped form counts on the device
+  p.rhs = a.rhs; p.rhs_i64 = a.rhs_i64; p.E = a.E;
+  dim3 grid((unsigned)((!grouped && p.ntiles < nsm) ? p.ntiles : nsm), 1, 1);
+  if (grouped) return a.bits == 4 ? launch_tc_inst<4, true>(map, wmap, p, grid, st) : launch_tc_inst<8, true>(map, wmap, p, grid, st);
+  return a.bits == 4 ? launch_tc_inst<4, false>(map, wmap, p, grid, st) : launch_tc_inst<8, false>(map, wmap, p, grid, st);
+}
+
+}  // namespace
+
+cudaError_t launch_qmm_tc(const QmmArgs& a, cudaStream_t st) {
+  TcLaunch l;
+  l.x = (const char*)a.x + a.xb.offset(0) * 2; l.M = a.M; l.K = a.K; l.ldx = a.ldx;
+  l.w = a.w + a.wb.offset(0);
+  l.s = (const uint16_t*)a.s + a.sb.offset(0);
+  l.b = (const uint16_t*)a.b + a.sb.offset(0);
+  l.wrows = a.N; l.N = a.N; l.ldw = a.ldw; l.lds = a.lds;
+  l.y = (uint16_t*)a.y + a.yb.offset(0); l.ldy = a.ldy;
+  l.bits = a.bits; l.gs = a.gs;
+  l.rhs = nullptr; l.rhs_i64 = 0; l.E = 0;
+  return launch_tc(l, false, st);
+}
+
+// gather_qmm with the rows sorted by expert (the reference's prefill MoE path: x [I, 1, K] already gathered,
+// rhs [I] ascending, mlx-serve src/transformer.zig:15007-15035) as a grouped GEMM: every expert's run of rows
+// is a dense problem against that expert's matrix.
+bool gather_tc_supported(const GatherArgs& a) {
+  if (!a.sorted || a.lhs != nullptr || a.M != 1) return false;
+  if (a.XB != a.I) return false;                       // one activation row per output row, in order
+  for (int d = 0; d < a.xbcast.nd; ++d)
+    if (a.xbcast.shape[d] != 1 && a.xbcast.stride[d] == 0) return false;   // no broadcast of x
+  if (a.bits != 4 && a.bits != 8) return false;
+  if (a.gs != 64 && a.gs != 128) return false;
+  if (a.x_dtype != QB200_BFLOAT16) return false;
+  if (a.K % 256 != 0 || a.K < 256 || a.N < 16 || a.I < 1 || a.I > (1 << 24) || a.E < 1 || a.E > kMaxGroupExperts) return false;
+  if (a.E * a.N > (int64_t)1 << 30) return false;
+  if ((((uintptr_t)a.x) & 15) != 0 || (a.K * 2) % 16 != 0) return false;
+  if ((((uintptr_t)a.w) & 15) != 0 || (a.K * a.bits / 8) % 16 != 0) return false;
+  if (a.w_expert_stride != a.N * (a.K * a.bits / 32) || a.s_expert_stride != a.N * (a.K / a.gs)) return false;
+  if (a.rhs_dtype != QB200_INT64 && a.rhs_dtype != QB200_INT32 && a.rhs_dtype != QB200_UINT32) return false;
+  if (get_encode() == nullptr) return false;
+  return true;
+}
+
+cudaError_t launch_gather_tc(const GatherArgs& a, cudaStream_t st) {
+  TcLaunch l;
+  l.x = a.x; l.M = a.I; l.K = a.K; l.ldx = a.K;
+  l.w = a.w; l.s = (const uint16_t*)a.s; l.b = (const uint16_t*)a.b;
+  l.wrows = a.E * a.N; l.N = a.N; l.ldw = a.K * a.bits / 32; l.lds = a.K / a.gs;
+  l.y = (uint16_t*)a.y; l.ldy = a.N;
+  l.bits = a.bits; l.gs = a.gs;
+  l.rhs = a.rhs; l.rhs_i64 = a.rhs_dtype == QB200_INT64; l.E = (int)a.E;
+  return launch_tc(l, true, st);
 }
 
 #ifdef QB_TC_PROFILE

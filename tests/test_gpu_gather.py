@@ -102,3 +102,37 @@ def test_other_geometries_and_ragged_tail(bits, gs, K):
     gate_bf16(y.float().cpu().numpy(), ref, "ragged")
     y32 = qb200.gather_qmm(torch.from_numpy(x).cuda(), dq, ds, db, None, torch.from_numpy(inds).cuda(), True, gs, bits)
     gate_f32(y32.cpu().numpy(), ref, "ragged fp32")
+
+
+@pytest.mark.parametrize("bits,gs,N,K", [(4, 64, 256, 512), (8, 64, 200, 768), (4, 128, 768, 1024)])
+def test_config3_prefill_sorted_grouped(bits, gs, N, K):
+    """BASELINE config 3, prefill form: thousands of routed rows sorted by expert, x already gathered ([I, 1, K]),
+    which the library serves as a grouped GEMM on the tensor-core kernel.  Uneven runs per expert, including an
+    expert without rows, one with a single row and runs that are not multiples of the 256-row tile.  The weight
+    term is rounded to bf16 once on that route (as in the dense prefill route), so the reference is built from
+    the oracle's bf16 dequantisation."""
+    import qb200
+    E = 8
+    counts = [0, 1, 300, 1000, 257, 2, 2000, 536]
+    I = sum(counts)
+    rng = np.random.default_rng(N + K + bits)
+    q, s, b = make_weight(rng, (E, N, K), gs, bits)
+    dq, ds, db = dev_triple(q, s, b)
+    rhs = np.repeat(np.arange(E, dtype=np.int32), counts)
+    x = rand_bf16(rng, (I, 1, K))
+    wd = qo.bf16_to_f32(qo.dequantize(q, s, b, gs, bits, out_bf16=True)).astype(np.float64)
+    ref = np.empty((I, 1, N), np.float32)
+    pos = 0
+    for e, c in enumerate(counts):
+        if c:
+            ref[pos:pos + c, 0] = (x[pos:pos + c, 0].astype(np.float64) @ wd[e].T).astype(np.float32)
+        pos += c
+    y = qb200.gather_qmm(to_dev_bf16(qo.f32_to_bf16(x)), dq, ds, db, None, torch.from_numpy(rhs).cuda(), True, gs, bits,
+                         sorted_indices=True)
+    assert qb200.lib().qb200_debug_tc_status() == 0
+    assert tuple(y.shape) == (I, 1, N)
+    gate_bf16(y.float().cpu().numpy(), ref, "grouped prefill gather", slack=2e-3)
+    # int64 indices take the same route
+    y64 = qb200.gather_qmm(to_dev_bf16(qo.f32_to_bf16(x)), dq, ds, db, None, torch.from_numpy(rhs.astype(np.int64)).cuda(),
+                           True, gs, bits, sorted_indices=True)
+    assert torch.equal(y64.view(torch.int16), y.view(torch.int16))
