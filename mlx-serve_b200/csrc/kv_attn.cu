@@ -23,20 +23,30 @@ struct SplitPlan {
 };
 
 // Deterministic in (B, Hkv, T) so that the workspace query and the launch agree.
+// A split is served by one CTA of 8 warps that take its 128-token blocks round-robin.  The plan minimises
+//   waves of CTAs over the GPU x (blocks per warp + a fixed per-CTA cost of ~0.7 block times)
+// summed over the two residencies the fast kernel has (one CTA per SM at 8 bits, two at 4 bits; the bit
+// width is not an input here because the workspace query does not know it).
 __host__ SplitPlan plan_splits(int64_t B, int64_t Hkv, int64_t T) {
   SplitPlan p;
-  const int64_t ctas_wanted = 148 * 4;
-  int64_t ns = (ctas_wanted + B * Hkv - 1) / (B * Hkv);
-  const int64_t max_ns = (T + 255) / 256;  // at least 256 tokens per split
-  if (ns > max_ns) ns = max_ns;
-  if (ns < 1) ns = 1;
-  int64_t tps = (T + ns - 1) / ns;
-  tps = (tps + 127) / 128 * 128;
-  if (tps < 128) tps = 128;
-  ns = (T + tps - 1) / tps;
-  if (ns < 1) ns = 1;
-  p.nsplit = (int)ns;
-  p.tokens_per_split = tps;
+  const int64_t pairs = B * Hkv > 0 ? B * Hkv : 1;
+  int64_t max_ns = (T + 255) / 256;  // at least 256 tokens per split
+  if (max_ns < 1) max_ns = 1;
+  if (max_ns > 1024) max_ns = 1024;
+  double best = -1.0;
+  int64_t best_ns = 1, best_tps = 128;
+  for (int64_t ns = 1; ns <= max_ns; ++ns) {
+    int64_t tps = (T + ns - 1) / ns;
+    tps = (tps + 127) / 128 * 128;
+    if (tps < 128) tps = 128;
+    const int64_t ns_eff = (T + tps - 1) / tps > 0 ? (T + tps - 1) / tps : 1;
+    const double per_cta = (double)((tps / 128 + 7) / 8) + 0.7;
+    double cost = 0.0;
+    for (int slots = 148; slots <= 296; slots += 148) cost += (double)((pairs * ns_eff + slots - 1) / slots) * per_cta;
+    if (best < 0.0 || cost < best - 1e-9) { best = cost; best_ns = ns_eff; best_tps = tps; }
+  }
+  p.nsplit = (int)best_ns;
+  p.tokens_per_split = best_tps;
   return p;
 }
 

@@ -372,10 +372,20 @@ __global__ void __launch_bounds__(kWarps * 32, BITS == 4 ? 2 : 1) kv_fast_kernel
     }
     emax[0] = __reduce_max_sync(0xffffffffu, emax[0]);
     emax[1] = __reduce_max_sync(0xffffffffu, emax[1]);
+    // the largest weight of the block for head t (long, flat contexts have p << 1: without this the
+    // fixed-point grid would be sized for p = 1 and keep only a few bits of p * v_scale)
+    int pexp = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) pexp = max(pexp, (int)((__float_as_uint(sc[i]) >> 23) & 0xFF));
+    pexp = max(pexp, __shfl_xor_sync(0xffffffffu, pexp, 4));
+    pexp = max(pexp, __shfl_xor_sync(0xffffffffu, pexp, 8));
+    pexp = max(pexp, __shfl_xor_sync(0xffffffffu, pexp, 16));
+    // (per head: lane (g, t) builds and reads back only head t's columns, so up/down may differ by t)
+    const int ep = pexp - 126 < 0 ? pexp - 126 : 0;   // p < 2^ep (p <= 1 always)
     float up[2], down[2];
 #pragma unroll
     for (int grp = 0; grp < 2; ++grp) {
-      int e = emax[grp] - 127 + 1;  // |v_scale| < 2^e and p <= 1
+      int e = emax[grp] - 127 + 1 + ep;  // |v_scale| < 2^(e - ep) and p < 2^ep
       e = e < -100 ? -100 : (e > 110 ? 110 : e);
       up[grp] = __uint_as_float((uint32_t)(127 + 14 - e) << 23);
       down[grp] = __uint_as_float((uint32_t)(127 + e - 14) << 23);
