@@ -11,8 +11,13 @@
 // swizzled shared-memory operand.
 //
 // Persistent, warp-specialised CTAs (one per SM) walk the output tiles of
-// 256 tokens x BN weight rows (BN <= 128, chosen per problem so that the last
-// wave of tiles is full), K in steps of 64 through a 4-stage ring:
+// 256 tokens x BN weight rows (BN chosen per problem so that the last wave of
+// tiles is full), K in steps of 64 through a 3- or 4-stage ring.  Two tile
+// forms: BN <= 128 with two accumulator sets in tensor memory (the epilogue of
+// tile i overlaps the main loop of tile i+1; used below 257 tokens and by the
+// grouped form), and BN <= 208 with one set (fewer shared-memory operand bytes
+// per MAC -- the resource that bounds this kernel -- at the price of an
+// epilogue that is not overlapped; used for wide prefill).  Roles:
 //   warps 0-15 : dequantisers in two groups of 8 warps that take alternate
 //                k-blocks (a warp's per-k-block latency -- barrier wait, byte
 //                shuffles, proxy fence -- is what bounds this role, so two
@@ -45,7 +50,12 @@ namespace {
 
 constexpr int BM = 256, BN_MAX = 128, BK = 64;
 // ring depth: the grouped (routed-expert) form gives one stage's room to its row-offset tables
-__host__ __device__ constexpr int stages_of(bool grouped) { return grouped ? 3 : 4; }
+__host__ __device__ constexpr int stages_of(bool grouped, bool wide = false) { return (grouped || wide) ? 3 : 4; }
+// The wide form multiplies one B tile of up to 208 weight rows per stage against both token halves: fewer
+// operand bytes per MAC through shared memory (the resource that bounds this kernel), at the price of a
+// single accumulator set in tensor memory (2 x 256 columns), i.e. an epilogue that is not overlapped.
+constexpr int BN_WIDE = 208;
+__host__ __device__ constexpr int bn_max_of(bool wide) { return wide ? BN_WIDE : BN_MAX; }
 constexpr int kMaxGroupExperts = 1024;
 constexpr int kDequantGroups = 2;                   // group g converts the k-blocks with (index % 2) == g
 constexpr int kDequantWarps = 8 * kDequantGroups, kEpiWarps = 4;
@@ -238,16 +248,19 @@ __device__ __forceinline__ void dequant_half(const uint32_t* codes, uint32_t sb2
   }
 }
 
-template <int BITS, bool GROUPED>
+template <int BITS, bool GROUPED, bool WIDE>
 __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, TcK p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  // 1024-byte alignment for the swizzled tiles
-  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  constexpr int STAGES = stages_of(GROUPED);
+  // 1024-byte alignment for the swizzled tiles.  The wide form has no room for the slack: the kernel has no
+  // static shared memory, so its dynamic window starts aligned; that is verified below.
+  unsigned char* smem = WIDE ? smem_raw : (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int STAGES = stages_of(GROUPED, WIDE);
+  constexpr int B_STAGE = bn_max_of(WIDE) * BK * 2, RAW_B = bn_max_of(WIDE) * 128;
+  constexpr int HALF_COLS = WIDE ? 256 : 128;      // tensor-memory columns between the two token halves
   unsigned char* a_tiles = smem;                                   // [STAGES][2][128 x 64 bf16]
   unsigned char* b_tiles = smem + STAGES * A_STAGE_BYTES;          // [STAGES][BN x 64 bf16]
-  unsigned char* raw = b_tiles + STAGES * B_STAGE_BYTES;           // [2][BN x 128 B of packed codes]
-  uint64_t* bars = (uint64_t*)(raw + 2 * RAW_BYTES);
+  unsigned char* raw = b_tiles + STAGES * B_STAGE;                 // [2][BN x 128 B of packed codes]
+  uint64_t* bars = (uint64_t*)(raw + 2 * RAW_B);
   uint64_t* full_a = bars, *full_b = bars + STAGES, *empty = bars + 2 * STAGES;
   uint64_t* acc_full = bars + 3 * STAGES, *acc_empty = bars + 3 * STAGES + 2;
   uint64_t* raw_full = bars + 3 * STAGES + 4, *raw_empty = bars + 3 * STAGES + 6;
@@ -267,7 +280,8 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full_a[i], 1); mbar_init(&full_b[i], kDequantThreads); mbar_init(&empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], kEpiWarps * 32); }
     for (int i = 0; i < 2; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], kDequantWarps * 32); }
-    s_fail = 0;
+    s_fail = (WIDE && (smem_u32(smem) & 1023u) != 0) ? 8 : 0;   // misaligned window: every role leaves at once
+    if (s_fail) atomicExch(&g_tc_error, 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kMmaWarp) {  // tensor memory: 512 columns = two sets of two 128x128 fp32 accumulators
@@ -372,7 +386,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
           const int buf = sbk & 1;
           if (sbk >= 2 && !mbar_wait_relaxed(&raw_empty[buf], ((sbk >> 1) - 1) & 1)) { fail = 7; break; }
           mbar_expect_tx(&raw_full[buf], (uint32_t)BN * 128u);
-          tma_load_2d(smem_u32(raw + buf * RAW_BYTES), &wmap, &raw_full[buf], sbl * 32, n0);
+          tma_load_2d(smem_u32(raw + buf * RAW_B), &wmap, &raw_full[buf], sbl * 32, n0);
         }
       }
       if (fail) { s_fail = fail; atomicExch(&g_tc_error, fail); }
@@ -388,11 +402,13 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       for (int tile = blockIdx.x; tile < ntiles && !fail && !s_fail; tile += gridDim.x, ++ti) {
         const TileCoord tc = coords(tile);
         const bool two_halves = tc.row0 + 128 < tc.row_end;  // the second 128 token rows hold real tokens
-        const int buf = ti & 1;
-        if (ti >= 2 && !mbar_wait_relaxed(&acc_empty[buf], ((ti >> 1) - 1) & 1)) { fail = 6; break; }
+        // dense form: two accumulator sets used alternately; wide form: one set, reused by every tile
+        const int buf = WIDE ? 0 : ti & 1;
+        const int use = WIDE ? ti : ti >> 1;     // how many times this set was used before
+        if (use >= 1 && !mbar_wait_relaxed(&acc_empty[buf], (use - 1) & 1)) { fail = 6; break; }
         PROF_ADD(0);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t d0 = tmem_base + buf * 256;
+        const uint32_t d0 = tmem_base + buf * 256;   // (buf is 0 in the wide form)
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int st = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -403,12 +419,12 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           // descriptors of the stage: the start-address field counts 16-byte units, so a K step of
           // 16 values (32 bytes) adds 2 and the second 128-row box of x adds 16 KiB / 16
-          const uint64_t ad0 = adesc0 + (uint64_t)(st * (A_STAGE_BYTES >> 4)), bd0 = bdesc0 + (uint64_t)(st * (B_STAGE_BYTES >> 4));
+          const uint64_t ad0 = adesc0 + (uint64_t)(st * (A_STAGE_BYTES >> 4)), bd0 = bdesc0 + (uint64_t)(st * (B_STAGE >> 4));
 #pragma unroll
           for (int k16 = 0; k16 < BK / 16; ++k16) {
             const uint32_t accum = (kb > 0 || k16 > 0) ? 1u : 0u;
             umma(d0, ad0 + 2 * k16, bd0 + 2 * k16, idesc, accum);
-            if (two_halves) umma(d0 + 128, ad0 + ((128 * BK * 2) >> 4) + 2 * k16, bd0 + 2 * k16, idesc, accum);
+            if (two_halves) umma(d0 + HALF_COLS, ad0 + ((128 * BK * 2) >> 4) + 2 * k16, bd0 + 2 * k16, idesc, accum);
           }
           umma_commit(&empty[st]);  // frees this stage (A and B) once the MMAs above have read it
           PROF_ADD(3);
@@ -422,7 +438,8 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
   } else if (warp < kDequantWarps) {
     // ---------------- dequant producers: two threads per weight row, two groups ----------------
     const int grp = warp >> 3, wg = warp & 7;
-    const int r = (wg & 3) * 32 + lane, h = wg >> 2;
+    // dense form: two threads per weight row (h = half of the 64-wide k-block); wide form: one thread per row
+    const int r = WIDE ? wg * 32 + lane : (wg & 3) * 32 + lane, h = WIDE ? 0 : wg >> 2;
     const bool active = r < BN;
     const int ntl = ntiles > (int)blockIdx.x ? (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;  // tiles of this CTA
     const int total_it = ntl * nkb;
@@ -475,20 +492,26 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       ok = mbar_wait(&raw_full[buf], (sbk >> 1) & 1);
       if (!ok || s_fail) { ok = false; break; }
       PROF_ADD(1);
-      uint32_t c[WPH];
+      constexpr int NH = WIDE ? 2 : 1;   // halves of the k-block this thread converts
+      uint32_t c[NH][WPH];
       if (active) {
-        const unsigned char* rrow = raw + buf * RAW_BYTES + r * 128;
+        const unsigned char* rrow = raw + buf * RAW_B + r * 128;
 #pragma unroll
-        for (int i = 0; i < WPH / 4; ++i) {
-          const int chunk = kbl * (2 * WPH / 4) + h * (WPH / 4) + i;
-          const uint4 v = *(const uint4*)(rrow + ((chunk ^ (r & 7)) << 4));
-          c[4 * i] = v.x; c[4 * i + 1] = v.y; c[4 * i + 2] = v.z; c[4 * i + 3] = v.w;
-        }
+        for (int hh = 0; hh < NH; ++hh)
+#pragma unroll
+          for (int i = 0; i < WPH / 4; ++i) {
+            const int chunk = kbl * (2 * WPH / 4) + (h + hh) * (WPH / 4) + i;
+            const uint4 v = *(const uint4*)(rrow + ((chunk ^ (r & 7)) << 4));
+            c[hh][4 * i] = v.x; c[hh][4 * i + 1] = v.y; c[hh][4 * i + 2] = v.z; c[hh][4 * i + 3] = v.w;
+          }
       }
       if (it >= STAGES) ok = mbar_wait(&empty[st], ((it / STAGES) - 1) & 1);
       if (!ok || s_fail) { ok = false; break; }
       PROF_ADD(2);
-      if (active) dequant_half<BITS>(c, sv2, bv2, b_tiles + st * B_STAGE_BYTES, r, h);
+      if (active) {
+#pragma unroll
+        for (int hh = 0; hh < NH; ++hh) dequant_half<BITS>(c[hh], sv2, bv2, b_tiles + st * B_STAGE, r, h + hh);
+      }
       PROF_ADD(3);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> async proxy (UMMA)
       PROF_ADD(4);
@@ -510,8 +533,8 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++ti) {
       const TileCoord tc = coords(tile);
       const int m0 = tc.row0, n0 = tc.n0, nend = tc.nend, mend = tc.row_end;
-      const int buf = ti & 1;
-      ok = mbar_wait_relaxed(&acc_full[buf], (ti >> 1) & 1);
+      const int buf = WIDE ? 0 : ti & 1;
+      ok = mbar_wait_relaxed(&acc_full[buf], (WIDE ? ti : ti >> 1) & 1);
       if (!ok || s_fail) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
@@ -521,7 +544,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
           uint32_t v[32];
-          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + half * 128 + c0, v);
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + half * HALF_COLS + c0, v);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           if (m < mend) {
             uint16_t* yrow = p.y + (int64_t)m * p.ldy + n0 + c0;
@@ -575,10 +598,13 @@ EncodeFn get_encode() {
   return fn;
 }
 
-constexpr size_t smem_bytes_tc(bool grouped) {
-  return (size_t)stages_of(grouped) * (A_STAGE_BYTES + B_STAGE_BYTES) + 2 * RAW_BYTES + (3 * stages_of(grouped) + 8) * 8 + 16 +
-         (grouped ? (size_t)2 * (kMaxGroupExperts + 1) * 4 : 0) + 1024;
+constexpr size_t smem_bytes_tc(bool grouped, bool wide) {
+  return (size_t)stages_of(grouped, wide) * (A_STAGE_BYTES + bn_max_of(wide) * BK * 2) + (size_t)2 * bn_max_of(wide) * 128 +
+         (3 * stages_of(grouped, wide) + 8) * 8 + 16 + (grouped ? (size_t)2 * (kMaxGroupExperts + 1) * 4 : 0) +
+         (wide ? 0 : 1024);
 }
+static_assert(smem_bytes_tc(false, true) <= 227 * 1024, "wide form does not fit in shared memory");
+static_assert(smem_bytes_tc(false, false) <= 227 * 1024 && smem_bytes_tc(true, false) <= 227 * 1024, "shared memory");
 
 int sm_count_tc() {
   static int cached[64] = {};
@@ -595,11 +621,11 @@ int sm_count_tc() {
 
 // Weight rows per tile: the candidate whose tile count fills the last wave best
 // (time ~ waves x (rows per tile + a fixed per-tile cost)).
-int pick_bn(int64_t M, int64_t N, int nsm) {
+int pick_bn(int64_t M, int64_t N, int nsm, int bn_max = BN_MAX) {
   const int64_t tiles_m = (M + BM - 1) / BM;
-  int best = BN_MAX;
+  int best = bn_max;
   int64_t best_cost = -1;
-  for (int bn = BN_MAX; bn >= 64; bn -= 16) {
+  for (int bn = bn_max; bn >= 64; bn -= 16) {
     const int64_t tiles = tiles_m * ((N + bn - 1) / bn);
     const int64_t waves = (tiles + nsm - 1) / nsm;
     const int64_t cost = waves * (bn + 12);
@@ -635,18 +661,18 @@ struct TcLaunch {
   const void* rhs; int rhs_i64; int E;   // grouped form only
 };
 
-template <int BITS, bool GROUPED>
+template <int BITS, bool GROUPED, bool WIDE>
 cudaError_t launch_tc_inst(const CUtensorMap& xmap, const CUtensorMap& wmap, const TcK& p, dim3 grid, cudaStream_t st) {
   static bool done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  constexpr size_t smem = smem_bytes_tc(GROUPED);
+  constexpr size_t smem = smem_bytes_tc(GROUPED, WIDE);
   if (dev < 0 || dev >= 64 || !done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(qmm_tc_kernel<BITS, GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(qmm_tc_kernel<BITS, GROUPED, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) done[dev] = true;
   }
-  qmm_tc_kernel<BITS, GROUPED><<<grid, kThreads, smem, st>>>(xmap, wmap, p);
+  qmm_tc_kernel<BITS, GROUPED, WIDE><<<grid, kThreads, smem, st>>>(xmap, wmap, p);
   return cudaGetLastError();
 }
 
@@ -664,8 +690,10 @@ cudaError_t launch_tc(const TcLaunch& a, bool grouped, cudaStream_t st) {
   if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
   TcK p;
   const int nsm = sm_count_tc();
-  // the grouped form does not know its tile count on the host: full-width tiles
-  p.BN = grouped ? (a.N >= BN_MAX ? BN_MAX : (int)((a.N + 15) / 16 * 16)) : pick_bn(a.M, a.N, nsm);
+  // Wide tiles when both 128-token halves of a tile are in use and there are enough weight rows to fill the GPU
+  // with them; the grouped form does not know its tile count on the host and takes full-width dense tiles.
+  const bool wide = !grouped && a.M > 256 && a.N >= 1024;
+  p.BN = grouped ? (a.N >= BN_MAX ? BN_MAX : (int)((a.N + 15) / 16 * 16)) : pick_bn(a.M, a.N, nsm, bn_max_of(wide));
   // packed codes as a [rows][K * bits / 32] array of 32-bit words: 128 bytes of BN rows per copy
   CUtensorMap wmap;
   {
@@ -686,8 +714,9 @@ cudaError_t launch_tc(const TcLaunch& a, bool grouped, cudaStream_t st) {
   p.ntiles = p.tiles_m * (int)((a.N + p.BN - 1) / p.BN);   // dense form; the grouped form counts on the device
   p.rhs = a.rhs; p.rhs_i64 = a.rhs_i64; p.E = a.E;
   dim3 grid((unsigned)((!grouped && p.ntiles < nsm) ? p.ntiles : nsm), 1, 1);
-  if (grouped) return a.bits == 4 ? launch_tc_inst<4, true>(map, wmap, p, grid, st) : launch_tc_inst<8, true>(map, wmap, p, grid, st);
-  return a.bits == 4 ? launch_tc_inst<4, false>(map, wmap, p, grid, st) : launch_tc_inst<8, false>(map, wmap, p, grid, st);
+  if (grouped) return a.bits == 4 ? launch_tc_inst<4, true, false>(map, wmap, p, grid, st) : launch_tc_inst<8, true, false>(map, wmap, p, grid, st);
+  if (wide) return a.bits == 4 ? launch_tc_inst<4, false, true>(map, wmap, p, grid, st) : launch_tc_inst<8, false, true>(map, wmap, p, grid, st);
+  return a.bits == 4 ? launch_tc_inst<4, false, false>(map, wmap, p, grid, st) : launch_tc_inst<8, false, false>(map, wmap, p, grid, st);
 }
 
 }  // namespace
