@@ -298,9 +298,9 @@ static int prepare_qmm(qb200_tensor* res, const qb200_tensor* x, const qb200_ten
 static cudaError_t dispatch_qmm(const QmmArgs& a, cudaStream_t s) {
   // decode widths stream the weights once through the integer-MMA kernel; wider inputs go to tcgen05
   // (a 128-row weight tile per CTA leaves most SMs idle below ~64 tokens, where re-streaming the weights
-  // per 16-token block through the streaming kernel is still cheaper)
+  // per 8-token block through the streaming kernel is still cheaper)
   if (a.M >= 64 && qmm_tc_supported(a)) return launch_qmm_tc(a, s);
-  if (a.M > 16 && !qmv_stream_supported(a) && qmm_tc_supported(a)) return launch_qmm_tc(a, s);
+  if (a.M > 8 && !qmv_stream_supported(a) && qmm_tc_supported(a)) return launch_qmm_tc(a, s);
   if (qmv_stream_supported(a)) return launch_qmv_stream(a, s);
   if (qmv_mma_supported(a)) return launch_qmv_mma(a, s);
   return launch_qmm_generic(a, s);

@@ -619,16 +619,17 @@ int sm_count_tc() {
   return cached[dev];
 }
 
-// Weight rows per tile: the candidate whose tile count fills the last wave best
-// (time ~ waves x (rows per tile + a fixed per-tile cost)).
+// Weight rows per tile: the candidate whose tile count fills the last wave best.  Time per tile ~ rows + 40:
+// the activation traffic of a k-block through shared memory does not shrink with the tile, so narrow tiles
+// only pay when they put otherwise idle SMs to work (few weight rows, long K, few tokens).
 int pick_bn(int64_t M, int64_t N, int nsm, int bn_max = BN_MAX) {
   const int64_t tiles_m = (M + BM - 1) / BM;
   int best = bn_max;
   int64_t best_cost = -1;
-  for (int bn = bn_max; bn >= 64; bn -= 16) {
+  for (int bn = bn_max; bn >= 32; bn -= 16) {
     const int64_t tiles = tiles_m * ((N + bn - 1) / bn);
     const int64_t waves = (tiles + nsm - 1) / nsm;
-    const int64_t cost = waves * (bn + 12);
+    const int64_t cost = waves * (bn + 40);
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
   }
   return best;

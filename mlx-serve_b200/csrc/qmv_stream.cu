@@ -1,4 +1,4 @@
-// Persistent weight-streaming quantized matmul for decode widths (M <= 16 per
+// Persistent weight-streaming quantized matmul for decode widths (M <= 8 per
 // launch): y[M, N] = x[M, K] . What[N, K]^T, 4/8-bit affine codes.
 //
 // Replaces mlx_quantized_matmul(transpose=true) as called by qmatmulBits
@@ -51,7 +51,9 @@ __host__ __device__ constexpr int stages_for(int nt) { return nt == 1 ? 4 : 3; }
 constexpr int kStageW = 2048;       // 16 rows x 128 B of packed codes
 constexpr int kStageBytes = kStageW + 256;  // + 16 rows x (scales, biases)
 constexpr int kTokPerTile = 4;      // tokens per n8 tile (two planes each)
-constexpr int kMaxTok = 16;         // tokens per launch
+constexpr int kMaxTok = 8;          // tokens per launch (two n8 tiles of 4 tokens x 2 planes); wider M in 8-token blocks:
+                                    // a 16-token instantiation needed four staging passes over K = 4096 and was
+                                    // measured slower than two 8-token launches
 
 __host__ __device__ constexpr int kc_for(int nt) { return nt <= 2 ? 4096 : 1024; }
 
@@ -670,7 +672,7 @@ bool plan_stream(StreamK& p, int NT, bool M1, int* grid_out, size_t* smem_out, i
 void pick_inst(const StreamK& p, int* NT, bool* M1) {
   const int nt = (p.M + kTokPerTile - 1) / kTokPerTile;
   *M1 = (p.M == 1 && p.K <= 65536);
-  *NT = nt <= 1 ? 1 : (nt <= 2 ? 2 : 4);
+  *NT = nt <= 1 ? 1 : 2;
 }
 
 template <int BITS, int NT, bool M1>
@@ -739,8 +741,7 @@ cudaError_t launch_bits(const StreamK& p, cudaStream_t st) {
   pick_inst(p, &nt, &m1);
   if (m1) return launch_inst<BITS, 1, true>(p, st);
   if (nt == 1) return launch_inst<BITS, 1, false>(p, st);
-  if (nt == 2) return launch_inst<BITS, 2, false>(p, st);
-  return launch_inst<BITS, 4, false>(p, st);
+  return launch_inst<BITS, 2, false>(p, st);
 }
 
 }  // namespace
