@@ -42,9 +42,10 @@ def layer_bytes(M, bits=BITS, gs=GS):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the same launches, from the ncu
-# capture summarised in profiles/qmv_stream_c2_decode.md: (14.263 + 9.545) MB measured for the q/k/v and o launches
-# at M=8 against 14.156 + 0.164 + 9.437 + 0.131 MB algorithmic.  Traffic scales with the bytes a launch streams.
-NCU_TRAFFIC_OVER_ALGORITHMIC = 23.808 / 23.888
+# capture summarised in profiles/qmv_stream_c2_decode.md: 14.30 + 9.58 + 66.88 + 33.34 MB measured for the four
+# launches of a layer at M=8 (q/k/v, o, gate/up, down) against 124.0 MB algorithmic.  Traffic scales with the
+# bytes a launch streams.
+NCU_TRAFFIC_OVER_ALGORITHMIC = 124.10 / 123.99
 
 
 def peaks():
@@ -508,8 +509,8 @@ def main():
                          "peak_source": which, "frac_of_nominal_8TBs": achieved / 8000.0,
                          "bytes_per_launch": layer_bytes(M) / (7.0 if args.no_batch else 4.0), "kernel": "qmv_stream_kernel",
                          "traffic": NCU_TRAFFIC_OVER_ALGORITHMIC * layer_bytes(M) / (7.0 if args.no_batch else 4.0),
-                         "traffic_source": "ncu dram__bytes_read+write of the q/k/v and o launches (2-layer capture), "
-                                           "scaled by algorithmic bytes to the average launch"},
+                         "traffic_source": "ncu dram__bytes_read+write of the four launches of one layer (2-layer "
+                                           "capture), scaled by algorithmic bytes to the average launch"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": xin.numel() * 2,
                     "d2h_bytes_per_step": yout.numel() * 2, "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": args.steps * L * launches_per_layer,
