@@ -295,11 +295,13 @@ static int prepare_qmm(qb200_tensor* res, const qb200_tensor* x, const qb200_ten
   return QB200_OK;
 }
 
+// Tokens from which the tensor-core kernel (split-K over a cluster when the problem has few tiles) beats
+// re-streaming the weights once per 8 tokens: measured break-even on the C2 layer is ~30 tokens.
+constexpr int64_t kTcMinTokens = 32;
+
 static cudaError_t dispatch_qmm(const QmmArgs& a, cudaStream_t s) {
-  // decode widths stream the weights once through the integer-MMA kernel; wider inputs go to tcgen05
-  // (a 128-row weight tile per CTA leaves most SMs idle below ~64 tokens, where re-streaming the weights
-  // per 8-token block through the streaming kernel is still cheaper)
-  if (a.M >= 64 && qmm_tc_supported(a)) return launch_qmm_tc(a, s);
+  // decode widths stream the weights once per 8 tokens through the integer-MMA kernel; wider inputs go to tcgen05
+  if (a.M >= kTcMinTokens && qmm_tc_supported(a)) return launch_qmm_tc(a, s);
   if (a.M > 8 && !qmv_stream_supported(a) && qmm_tc_supported(a)) return launch_qmm_tc(a, s);
   if (qmv_stream_supported(a)) return launch_qmv_stream(a, s);
   if (qmv_mma_supported(a)) return launch_qmv_mma(a, s);
@@ -337,7 +339,8 @@ QB200_API int qb200_quantized_matmul_batch(qb200_tensor* const* res, const qb200
       int st = prepare_qmm(res[i0 + i], x, w[i0 + i], scales[i0 + i], biases[i0 + i], transpose_w, group_size, bits,
                            mode, &a[i], &empty[i]);
       if (st) return st;
-      fuse = fuse && !empty[i] && qmv_stream_supported(a[i]) && a[i].K == a[0].K;
+      // (from kTcMinTokens tokens the tensor-core kernel serves each matrix: same rule as dispatch_qmm)
+      fuse = fuse && !empty[i] && !(a[i].M >= kTcMinTokens && qmm_tc_supported(a[i])) && qmv_stream_supported(a[i]) && a[i].K == a[0].K;
     }
     cudaError_t e = cudaSuccess;
     if (fuse) {

@@ -95,6 +95,9 @@ struct TcK {
   // grouped form (gather_qmm with rows sorted by expert): M = routed rows, N = rows of ONE expert's matrix,
   // w/s/b are the banks [E][N][.] seen as one matrix of E*N rows, rhs[i] = expert of row i (ascending)
   const void* rhs; int rhs_i64; int E;
+  // split-K form (few tokens, few tiles): the `ksplit` CTAs of a cluster share one tile, each multiplies its own
+  // K range, and rank 0 adds the partial accumulators it receives through distributed shared memory
+  int ksplit;
 };
 
 struct TileCoord {
@@ -152,6 +155,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                ::"r"(dst), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
                : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank_tc() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_tc() {   // all threads of all CTAs of the cluster (hardware barrier)
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t rank, float4 v) {
+  uint32_t ra;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(addr), "r"(rank));
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(ra), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 // K-major, SWIZZLE_128B operand descriptor: rows of 128 bytes, 8-row atoms 1024 bytes apart.
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
@@ -271,7 +283,12 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
   int* s_tcum = s_off + (kMaxGroupExperts + 1);     // [E + 1]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int nkb = p.K / BK;
+  constexpr bool CAN_SPLIT = !GROUPED && !WIDE;
+  const int S = CAN_SPLIT ? p.ksplit : 1;                  // CTAs per tile (cluster size)
+  const int crank = S > 1 ? (int)cluster_rank_tc() : 0;
+  const int nkb = p.K / BK / S;                            // k-blocks of this CTA
+  const int kb0 = crank * nkb;                             // its first k-block
+  const int tile0 = (int)blockIdx.x / S, tstride = (int)gridDim.x / S;
   const int BN = p.BN;
   constexpr int WPH = (BK / 2) * BITS / 32;  // packed words per half row per k-block (4 or 8)
   constexpr int KPS = 128 * 8 / (BK * BITS);  // k-blocks per 128-byte super-block of codes (4 or 2)
@@ -362,15 +379,17 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
     if (lane == 0) {
       // ---------------- TMA producer (one thread) ----------------
       int it = 0, fail = 0;
-      for (int tile = blockIdx.x; tile < ntiles && !fail && !s_fail; tile += gridDim.x) {
-        const int m0 = coords(tile).row0;
+      for (int tile = tile0; tile < ntiles && !fail && !s_fail; tile += tstride) {
+        const TileCoord tc = coords(tile);
+        const int m0 = tc.row0;
+        const bool two = m0 + 128 < tc.row_end;   // the second 128-row box holds real tokens (else it is not multiplied)
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int st = it % STAGES;
           if (it >= STAGES && !mbar_wait_relaxed(&empty[st], ((it / STAGES) - 1) & 1)) { fail = 3; break; }
-          mbar_expect_tx(&full_a[st], A_STAGE_BYTES);
+          mbar_expect_tx(&full_a[st], two ? A_STAGE_BYTES : A_STAGE_BYTES / 2);
           const uint32_t dst = smem_u32(a_tiles + st * A_STAGE_BYTES);
-          tma_load_2d(dst, &xmap, &full_a[st], kb * BK, m0);
-          tma_load_2d(dst + 128 * BK * 2, &xmap, &full_a[st], kb * BK, m0 + 128);
+          tma_load_2d(dst, &xmap, &full_a[st], (kb0 + kb) * BK, m0);
+          if (two) tma_load_2d(dst + 128 * BK * 2, &xmap, &full_a[st], (kb0 + kb) * BK, m0 + 128);
         }
       }
       if (fail) { s_fail = fail; atomicExch(&g_tc_error, fail); }
@@ -380,13 +399,13 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       // ---------------- TMA producer of the packed codes (one thread) ----------------
       const int sb_per_tile = nkb / KPS;
       int sbk = 0, fail = 0;
-      for (int tile = blockIdx.x; tile < ntiles && !fail && !s_fail; tile += gridDim.x) {
+      for (int tile = tile0; tile < ntiles && !fail && !s_fail; tile += tstride) {
         const int n0 = coords(tile).wrow0;
         for (int sbl = 0; sbl < sb_per_tile; ++sbl, ++sbk) {
           const int buf = sbk & 1;
           if (sbk >= 2 && !mbar_wait_relaxed(&raw_empty[buf], ((sbk >> 1) - 1) & 1)) { fail = 7; break; }
           mbar_expect_tx(&raw_full[buf], (uint32_t)BN * 128u);
-          tma_load_2d(smem_u32(raw + buf * RAW_B), &wmap, &raw_full[buf], sbl * 32, n0);
+          tma_load_2d(smem_u32(raw + buf * RAW_B), &wmap, &raw_full[buf], (kb0 / KPS + sbl) * 32, n0);
         }
       }
       if (fail) { s_fail = fail; atomicExch(&g_tc_error, fail); }
@@ -399,7 +418,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       int it = 0, fail = 0, ti = 0;
       PROF_DECL;
       PROF_T0();
-      for (int tile = blockIdx.x; tile < ntiles && !fail && !s_fail; tile += gridDim.x, ++ti) {
+      for (int tile = tile0; tile < ntiles && !fail && !s_fail; tile += tstride, ++ti) {
         const TileCoord tc = coords(tile);
         const bool two_halves = tc.row0 + 128 < tc.row_end;  // the second 128 token rows hold real tokens
         // dense form: two accumulator sets used alternately; wide form: one set, reused by every tile
@@ -441,7 +460,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
     // dense form: two threads per weight row (h = half of the 64-wide k-block); wide form: one thread per row
     const int r = WIDE ? wg * 32 + lane : (wg & 3) * 32 + lane, h = WIDE ? 0 : wg >> 2;
     const bool active = r < BN;
-    const int ntl = ntiles > (int)blockIdx.x ? (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;  // tiles of this CTA
+    const int ntl = ntiles > tile0 ? (ntiles - tile0 + tstride - 1) / tstride : 0;  // tiles of this CTA
     const int total_it = ntl * nkb;
     // Scales and biases of this thread's row: windows of 8 values (8 << gshift k-blocks), the next
     // window prefetched while the current one is used.  f_* is the prefetch cursor (tile, k-block).
@@ -449,7 +468,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
     uint4 s_cur = make_uint4(0, 0, 0, 0), b_cur = s_cur, s_nxt = s_cur, b_nxt = s_cur;
     int f_tl = 0, f_kb = 0;
     auto row_of = [&](int tl) {
-      const int tile = blockIdx.x + tl * gridDim.x;
+      const int tile = tile0 + tl * tstride;
       const TileCoord tc = coords(tile);
       const int n = tc.wrow0 + r;
       return n < tc.wrow_last ? n : tc.wrow_last;
@@ -457,7 +476,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
     auto prefetch_window = [&]() {
       if (f_kb >= nkb) { f_kb = 0; ++f_tl; }
       if (active && f_tl < ntl) {
-        const int64_t off = (int64_t)row_of(f_tl) * p.lds + (f_kb >> p.gshift);
+        const int64_t off = (int64_t)row_of(f_tl) * p.lds + ((kb0 + f_kb) >> p.gshift);
         s_nxt = __ldg((const uint4*)(p.s + off));
         b_nxt = __ldg((const uint4*)(p.b + off));
       }
@@ -477,13 +496,13 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
           s_cur = s_nxt; b_cur = b_nxt;
           prefetch_window();
         }
-        const int e = (kb >> p.gshift) & 7;
+        const int e = ((kb0 + kb) >> p.gshift) & 7;
         const uint32_t sw = e < 4 ? (e < 2 ? s_cur.x : s_cur.y) : (e < 6 ? s_cur.z : s_cur.w);
         const uint32_t bw = e < 4 ? (e < 2 ? b_cur.x : b_cur.y) : (e < 6 ? b_cur.z : b_cur.w);
         sv2 = (e & 1) ? __byte_perm(sw, sw, 0x3232) : __byte_perm(sw, sw, 0x1010);
         bv2 = (e & 1) ? __byte_perm(bw, bw, 0x3232) : __byte_perm(bw, bw, 0x1010);
       } else {
-        const int64_t off = (int64_t)row_of(tl) * p.lds + (kb >> p.gshift);
+        const int64_t off = (int64_t)row_of(tl) * p.lds + ((kb0 + kb) >> p.gshift);
         const uint32_t sv = active ? __ldg(p.s + off) : 0u, bv = active ? __ldg(p.b + off) : 0u;
         sv2 = sv | (sv << 16);
         bv2 = bv | (bv << 16);
@@ -530,13 +549,14 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
     const int q = warp & 3;   // TMEM lane quarter this warp may read
     int ti = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++ti) {
+    for (int tile = tile0; tile < ntiles && ok; tile += tstride, ++ti) {
       const TileCoord tc = coords(tile);
       const int m0 = tc.row0, n0 = tc.n0, nend = tc.nend, mend = tc.row_end;
       const int buf = WIDE ? 0 : ti & 1;
       ok = mbar_wait_relaxed(&acc_full[buf], (WIDE ? ti : ti >> 1) & 1);
       if (!ok || s_fail) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (S > 1) break;   // split-K: one tile per cluster; the partial accumulators are exchanged below
 #pragma unroll 1
       for (int half = 0; half < 2; ++half) {
         if (half == 1 && m0 + 128 >= mend) break;
@@ -573,6 +593,76 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
     }
     if (!ok && !s_fail) { s_fail = 5; atomicExch(&g_tc_error, 5); }
   }
+  if constexpr (CAN_SPLIT) {
+    if (S > 1) {
+      // Every role of every CTA of the cluster has left its loops (the epilogue warps after their own CTA's
+      // accumulator was complete), so the pipeline buffers of rank 0 are free: ranks 1.. write their fp32
+      // partial tiles there (rows padded by 16 bytes against bank conflicts), rank 0 adds them to its own
+      // accumulator and stores.  Tokens <= 128 on this form: one 128-lane half.
+      const bool epi = warp >= kEpiWarp0 && warp < kEpiWarp0 + kEpiWarps;
+      const int q = warp & 3;
+      const int pitch = (BN + 31) / 32 * 32 * 4 + 16;      // bytes per partial row: whole 32-column chunks + padding
+      const bool have_tile = tile0 < ntiles && !s_fail;
+      cluster_sync_tc();
+      if (epi && crank != 0 && have_tile) {
+        const uint32_t dst0 = smem_u32(smem) + (uint32_t)((crank - 1) * 128 * pitch + (q * 32 + lane) * pitch);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            st_cluster_v4(dst0 + (uint32_t)(c0 + 4 * j) * 4u, 0u,
+                          make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                                      __uint_as_float(v[4 * j + 3])));
+        }
+      }
+      cluster_sync_tc();
+      if (epi && crank == 0 && have_tile) {
+        const TileCoord tc = coords(tile0);
+        const int m = tc.row0 + q * 32 + lane;
+        const unsigned char* src0 = smem + (size_t)(q * 32 + lane) * pitch;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          for (int k = 0; k + 1 < S; ++k) {
+            const float4* pr = (const float4*)(src0 + (size_t)k * 128 * pitch + (size_t)c0 * 4);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 a = pr[j];
+              f[4 * j] += a.x; f[4 * j + 1] += a.y; f[4 * j + 2] += a.z; f[4 * j + 3] += a.w;
+            }
+          }
+          if (m < tc.row_end) {
+            uint16_t* yrow = p.y + (int64_t)m * p.ldy + tc.n0 + c0;
+            const int nvalid = tc.nend - (tc.n0 + c0);
+            const bool aligned = (((uintptr_t)yrow) & 15) == 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (aligned && 8 * j + 8 <= nvalid) {
+                uint4 o;
+                o.x = pack_bf16x2(f[8 * j], f[8 * j + 1]);
+                o.y = pack_bf16x2(f[8 * j + 2], f[8 * j + 3]);
+                o.z = pack_bf16x2(f[8 * j + 4], f[8 * j + 5]);
+                o.w = pack_bf16x2(f[8 * j + 6], f[8 * j + 7]);
+                *(uint4*)(yrow + 8 * j) = o;
+              } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                  if (8 * j + i < nvalid) yrow[8 * j + i] = f32_to_bf16_bits(f[8 * j + i]);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == kMmaWarp) {
@@ -605,6 +695,8 @@ constexpr size_t smem_bytes_tc(bool grouped, bool wide) {
 }
 static_assert(smem_bytes_tc(false, true) <= 227 * 1024, "wide form does not fit in shared memory");
 static_assert(smem_bytes_tc(false, false) <= 227 * 1024 && smem_bytes_tc(true, false) <= 227 * 1024, "shared memory");
+
+constexpr size_t STAGES_DENSE_BYTES = (size_t)stages_of(false) * (A_STAGE_BYTES + B_STAGE_BYTES) + 2 * RAW_BYTES;  // pipeline buffers reused by the exchange
 
 int sm_count_tc() {
   static int cached[64] = {};
@@ -663,7 +755,8 @@ struct TcLaunch {
 };
 
 template <int BITS, bool GROUPED, bool WIDE>
-cudaError_t launch_tc_inst(const CUtensorMap& xmap, const CUtensorMap& wmap, const TcK& p, dim3 grid, cudaStream_t st) {
+cudaError_t launch_tc_inst(const CUtensorMap& xmap, const CUtensorMap& wmap, const TcK& p, dim3 grid, cudaStream_t st,
+                           int cluster = 1) {
   static bool done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -673,8 +766,51 @@ cudaError_t launch_tc_inst(const CUtensorMap& xmap, const CUtensorMap& wmap, con
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) done[dev] = true;
   }
+  if (cluster > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, qmm_tc_kernel<BITS, GROUPED, WIDE>, xmap, wmap, p);
+  }
   qmm_tc_kernel<BITS, GROUPED, WIDE><<<grid, kThreads, smem, st>>>(xmap, wmap, p);
   return cudaGetLastError();
+}
+
+// CTAs that clusters of `cluster` CTAs of the dense form can keep resident at once (cluster placement is per GPC,
+// so this is less than the SM count for clusters of 4).
+template <int BITS>
+int split_capacity(int cluster) {
+  static int cached[64][5] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev][cluster] == 0) {
+    constexpr size_t smem = smem_bytes_tc(false, false);
+    int n = 0;
+    cudaLaunchConfig_t q = {};
+    q.gridDim = dim3((unsigned)(sm_count_tc() / cluster * cluster));
+    q.blockDim = dim3(kThreads);
+    q.dynamicSmemBytes = smem;
+    cudaLaunchAttribute qa[1];
+    qa[0].id = cudaLaunchAttributeClusterDimension;
+    qa[0].val.clusterDim.x = cluster; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+    q.attrs = qa;
+    q.numAttrs = 1;
+    if (cudaFuncSetAttribute(qmm_tc_kernel<BITS, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&n, qmm_tc_kernel<BITS, false, false>, &q) != cudaSuccess) {
+      (void)cudaGetLastError();
+      n = 0;
+    }
+    cached[dev][cluster] = n > 0 ? n * cluster : -1;
+  }
+  return cached[dev][cluster] > 0 ? cached[dev][cluster] : 0;
 }
 
 cudaError_t launch_tc(const TcLaunch& a, bool grouped, cudaStream_t st) {
@@ -695,6 +831,28 @@ cudaError_t launch_tc(const TcLaunch& a, bool grouped, cudaStream_t st) {
   // with them; the grouped form does not know its tile count on the host and takes full-width dense tiles.
   const bool wide = !grouped && a.M > 256 && a.N >= 1024;
   p.BN = grouped ? (a.N >= BN_MAX ? BN_MAX : (int)((a.N + 15) / 16 * 16)) : pick_bn(a.M, a.N, nsm, bn_max_of(wide));
+  // Split-K over a cluster when a few-token problem has too few tiles to occupy the GPU: with one tile per CTA
+  // the time is the number of k-blocks a CTA walks (plus ~6 k-block times for the exchange), whatever the tile
+  // width, so K is cut in 4 or 2 and the tile is made just wide enough for tiles x ranks to fit the SMs.
+  p.ksplit = 1;
+  if (!grouped && !wide && a.M <= 128) {
+    const int gshift = a.gs == 128 ? 1 : 0;
+    const int nkb_all = (int)(a.K / BK);
+    const int64_t plain_tiles = (a.N + p.BN - 1) / p.BN;
+    const int64_t plain_cost = ((plain_tiles + nsm - 1) / nsm) * nkb_all;
+    for (int sp = 4; sp >= 2; sp >>= 1) {
+      if (nkb_all % (sp * (8 << gshift)) != 0 || nkb_all / sp < 8) continue;   // whole scale windows per rank
+      const int cap = a.bits == 4 ? split_capacity<4>(sp) : split_capacity<8>(sp);   // resident CTAs in clusters of sp
+      const int max_tiles = cap / sp;
+      if (max_tiles < 1) continue;
+      int bn = (int)((a.N + max_tiles - 1) / max_tiles);
+      bn = (bn + 15) / 16 * 16;
+      if (bn < 32) bn = 32;
+      if (bn > BN_MAX || (a.N + bn - 1) / bn > max_tiles) continue;
+      if ((size_t)(sp - 1) * 128 * ((bn + 31) / 32 * 32 * 4 + 16) > (size_t)STAGES_DENSE_BYTES) continue;
+      if (nkb_all / sp + 6 < plain_cost) { p.ksplit = sp; p.BN = bn; break; }
+    }
+  }
   // packed codes as a [rows][K * bits / 32] array of 32-bit words: 128 bytes of BN rows per copy
   CUtensorMap wmap;
   {
@@ -715,6 +873,11 @@ cudaError_t launch_tc(const TcLaunch& a, bool grouped, cudaStream_t st) {
   p.ntiles = p.tiles_m * (int)((a.N + p.BN - 1) / p.BN);   // dense form; the grouped form counts on the device
   p.rhs = a.rhs; p.rhs_i64 = a.rhs_i64; p.E = a.E;
   dim3 grid((unsigned)((!grouped && p.ntiles < nsm) ? p.ntiles : nsm), 1, 1);
+  if (p.ksplit > 1) {
+    grid = dim3((unsigned)(p.ntiles * p.ksplit), 1, 1);   // one tile per cluster
+    return a.bits == 4 ? launch_tc_inst<4, false, false>(map, wmap, p, grid, st, p.ksplit)
+                       : launch_tc_inst<8, false, false>(map, wmap, p, grid, st, p.ksplit);
+  }
   if (grouped) return a.bits == 4 ? launch_tc_inst<4, true, false>(map, wmap, p, grid, st) : launch_tc_inst<8, true, false>(map, wmap, p, grid, st);
   if (wide) return a.bits == 4 ? launch_tc_inst<4, false, true>(map, wmap, p, grid, st) : launch_tc_inst<8, false, true>(map, wmap, p, grid, st);
   return a.bits == 4 ? launch_tc_inst<4, false, false>(map, wmap, p, grid, st) : launch_tc_inst<8, false, false>(map, wmap, p, grid, st);

@@ -193,3 +193,15 @@ def test_config4_full_size_vs_dequantize_plus_fp32_matmul(bits):
     d = (y.float() - ref).abs()
     ulp = torch.pow(2.0, torch.floor(torch.log2(ref.abs().clamp_min(1e-30))) - 7)
     assert bool((d <= 0.5 * ulp * (1 + 1e-6) + 1e-3 * r).all())
+
+
+@pytest.mark.parametrize("bits,gs", [(4, 64), (8, 64), (4, 128)])
+@pytest.mark.parametrize("M,N,K", [(128, 4096, 4096), (64, 1024, 4096), (100, 1000, 2048), (128, 512, 14336)])
+def test_few_token_split_k_shapes(bits, gs, M, N, K):
+    """64..128 tokens against few weight rows: the tensor-core kernel cuts K over the CTAs of a cluster and adds
+    the partial accumulators in rank 0 (C2's M = 128 projections: q/o 4096x4096, k/v 1024x4096, down K = 14336)."""
+    import qb200
+    rng = np.random.default_rng(M + N + K + bits + gs)
+    q, s, b = make_weight(rng, (N, K), gs, bits)
+    _run(rand_bf16(rng, (M, K)), q, s, b, gs, bits)
+    assert qb200.lib().qb200_debug_tc_status() == 0
