@@ -480,6 +480,15 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     e2e_value = world * M * L * args.steps / (ms_e2e * 1e-3)
 
+    # The single-token line of the same workload (the shape BASELINE's bandwidth target is stated for) is cheap
+    # and always reported next to the batch-decode headline.
+    qmv_m1 = None
+    if M != 1 and L > 0:
+        g1, _, _ = build_graph(1)
+        ms1 = time_graph(g1, args.steps, 3) / args.steps
+        qmv_m1 = {"ms_per_step": ms1, "tokens_per_s": world * L / (ms1 * 1e-3), "hbm_gbs": L * layer_bytes(1) / (ms1 * 1e-3) / 1e9}
+        del g1
+
     sweep = None
     if args.sweep:
         sweep = {}
@@ -516,6 +525,9 @@ def main():
             "gpu_launches": args.steps * L * launches_per_layer,
             "clocks": clocks,
         }
+        if qmv_m1:
+            qmv_m1["frac_of_peak"] = qmv_m1["hbm_gbs"] / peak
+            out["qmv_m1"] = qmv_m1
         if sweep:
             out["sweep_M"] = sweep
         if not args.no_cpu_baseline:
