@@ -13,6 +13,11 @@ Here the experts are partitioned over the ranks of a process group -- rank r own
     -> combine all-to-all back to the row's owner
     -> owner applies the router weights and sums over the top-k.
 
+Two exchange plans: ``moe_block_ep`` sends exactly the routed rows (the per-destination counts are exchanged
+first, which costs a host synchronisation: right for prefill-sized inputs) and ``moe_block_ep_padded`` sends
+fixed-size blocks (every rank may receive all of a peer's T*k rows; unused slots carry expert id -1, which
+gather_qmm skips), so that nothing on the host waits for the device: right for decode-sized inputs.
+
 ``torch.distributed`` (NCCL on GPUs, gloo in the CPU tests) is only the plumbing; the expert math is
 ``expert_fn``, by default the library's gather_qmm through the C ABI.  The rows a rank receives are a
 concatenation of sorted runs, one per source rank, which gather_qmm accepts as is (it never relies on the
@@ -95,5 +100,56 @@ def moe_block_ep(x: torch.Tensor, inds: torch.Tensor, weights: torch.Tensor, num
     w_sorted = weights.reshape(-1)[order]
     contrib = (d_back.float() * w_sorted.float().unsqueeze(1)).to(x.dtype).float()
     out = torch.zeros((T, x.shape[1]), dtype=torch.float32, device=x.device)
+    out.index_add_(0, src_tok, contrib)
+    return out.to(x.dtype)
+
+
+def moe_block_ep_padded(x: torch.Tensor, inds: torch.Tensor, weights: torch.Tensor, num_experts: int, expert_fn,
+                        group=None) -> torch.Tensor:
+    """The same block with fixed-size exchange buffers and no host synchronisation.
+
+    Every rank sends each peer a block of T*k row slots (rows for that peer first, in expert order; the rest
+    empty with expert id -1) and gets blocks of the same size back, so all collectives have static shapes and
+    the whole block can be enqueued (or captured in a CUDA graph) without reading anything back.
+    ``expert_fn`` must leave rows whose local expert id is negative alone (the library's gather_qmm does).
+    """
+    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    rank = dist.get_rank(group) if world > 1 else 0
+    T, k = inds.shape
+    R, H = T * k, x.shape[1]
+    per_rank = (num_experts + world - 1) // world
+    dev = x.device
+    flat = inds.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    sorted_e = flat[order]
+    src_tok = torch.div(order, k, rounding_mode="floor")
+    dest = torch.div(sorted_e, per_rank, rounding_mode="floor")           # ascending
+    starts = torch.searchsorted(dest, torch.arange(world, device=dev, dtype=dest.dtype))
+    pos = torch.arange(R, device=dev) - starts[dest]                      # slot inside the destination's block
+    send_rows = x.new_zeros((world, R, H))
+    send_rows[dest, pos] = x[src_tok]
+    send_ids = torch.full((world, R), -1, dtype=torch.int64, device=dev)
+    send_ids[dest, pos] = sorted_e - dest * per_rank
+    if world > 1:
+        rows_in = torch.empty_like(send_rows)
+        ids_in = torch.empty_like(send_ids)
+        dist.all_to_all_single(rows_in, send_rows, group=group)
+        dist.all_to_all_single(ids_in, send_ids, group=group)
+    else:
+        rows_in, ids_in = send_rows, send_ids
+    rows_in = rows_in.reshape(world * R, H)
+    ids_in = ids_in.reshape(world * R)
+    g = expert_fn("gate", rows_in, ids_in)
+    u = expert_fn("up", rows_in, ids_in)
+    d = expert_fn("down", swiglu(g, u), ids_in).reshape(world, R, H)
+    if world > 1:
+        d_back = torch.empty_like(d)
+        dist.all_to_all_single(d_back, d.contiguous(), group=group)
+    else:
+        d_back = d
+    picked = d_back[dest, pos]                                            # [R, H]: the routed rows, in sorted order
+    w_sorted = weights.reshape(-1)[order]
+    contrib = (picked.float() * w_sorted.float().unsqueeze(1)).to(x.dtype).float()
+    out = torch.zeros((T, H), dtype=torch.float32, device=dev)
     out.index_add_(0, src_tok, contrib)
     return out.to(x.dtype)

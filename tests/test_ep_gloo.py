@@ -35,8 +35,12 @@ def _oracle_fn(banks, lo, hi):
 
     def fn(name, rows, local_ids):
         q, s, b = (a[lo:hi] for a in banks[name])
+        ids = local_ids.numpy()
+        live = np.nonzero(ids >= 0)[0]          # empty slots of the padded exchange carry -1 and stay untouched
         x = rows.float().numpy().reshape(rows.shape[0], 1, rows.shape[1])
-        y = qo.gather_qmm(x, q, s, b, np.arange(rows.shape[0]), local_ids.numpy(), 64, 4)[:, 0, :]
+        y = np.full((rows.shape[0], q.shape[1]), np.nan, np.float32)
+        if live.size:
+            y[live] = qo.gather_qmm(x[live], q, s, b, np.arange(live.size), ids[live], 64, 4)[:, 0, :]
         return torch.from_numpy(y).to(torch.bfloat16)
     return fn
 
@@ -57,8 +61,10 @@ def _worker(rank, world, port, ret):
         per = E // world
         x, logits = _inputs(rank)
         inds, w = ep.route(logits, K_TOP)
-        out = ep.moe_block_ep(x, inds, w, E, _oracle_fn(banks, rank * per, (rank + 1) * per))
+        fn = _oracle_fn(banks, rank * per, (rank + 1) * per)
+        out = ep.moe_block_ep(x, inds, w, E, fn)
         ret[rank] = out.float().numpy()
+        ret[world + rank] = ep.moe_block_ep_padded(x, inds, w, E, fn).float().numpy()
     finally:
         dist.destroy_process_group()
 
@@ -76,6 +82,9 @@ def test_two_rank_exchange_matches_single_process():
         ref = ep.moe_block_ep(x, inds, w, E, _oracle_fn(banks, 0, E)).float().numpy()
         assert not np.isnan(ret[rank]).any()
         assert np.array_equal(ret[rank], ref), "the exchange must not change any value"
+        assert not np.isnan(ret[world + rank]).any(), "an empty slot of the padded exchange leaked into the result"
+        assert np.array_equal(ret[world + rank], ref), "the padded exchange must not change any value"
+        assert np.array_equal(ep.moe_block_ep_padded(x, inds, w, E, _oracle_fn(banks, 0, E)).float().numpy(), ref)
 
 
 def test_route_renormalises_and_orders():

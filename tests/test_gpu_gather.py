@@ -136,3 +136,23 @@ def test_config3_prefill_sorted_grouped(bits, gs, N, K):
     y64 = qb200.gather_qmm(to_dev_bf16(qo.f32_to_bf16(x)), dq, ds, db, None, torch.from_numpy(rhs.astype(np.int64)).cuda(),
                            True, gs, bits, sorted_indices=True)
     assert torch.equal(y64.view(torch.int16), y.view(torch.int16))
+
+
+def test_moe_block_padded_exchange_plan_matches_exact_plan_on_one_gpu():
+    """The two exchange plans of the expert-parallel block (exact counts / fixed-size blocks whose empty slots carry
+    expert id -1) give identical outputs through the CUDA gather_qmm, which must skip the empty slots."""
+    from qb200 import ep
+    import qb200
+    E, H, I, T, k = 16, 512, 256, 24, 4
+    g = torch.Generator(device="cuda").manual_seed(7)
+    banks = {}
+    for name, (n, kk) in (("gate", (I, H)), ("up", (I, H)), ("down", (H, I))):
+        w = (torch.randn((E, n, kk), device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+        banks[name] = qb200.quantize(w, 64, 4)
+    fn = ep.default_expert_fn(banks)
+    x = torch.randn((T, H), device="cuda", generator=g).to(torch.bfloat16)
+    inds, w = ep.route(torch.randn((T, E), device="cuda", generator=g), k)
+    a = ep.moe_block_ep(x, inds, w, E, fn)
+    b = ep.moe_block_ep_padded(x, inds, w, E, fn)
+    assert not torch.isnan(a).any() and not torch.isnan(b).any()
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
