@@ -54,8 +54,8 @@ __host__ __device__ constexpr int stages_of(bool grouped, bool wide = false) { r
 // The wide form multiplies one B tile of up to 208 weight rows per stage against both token halves: fewer
 // operand bytes per MAC through shared memory (the resource that bounds this kernel), at the price of a
 // single accumulator set in tensor memory (2 x 256 columns), i.e. an epilogue that is not overlapped.
-constexpr int BN_WIDE = 208;
-__host__ __device__ constexpr int bn_max_of(bool wide) { return wide ? BN_WIDE : BN_MAX; }
+constexpr int BN_WIDE = 208, BN_WIDE_GROUPED = 192;   // the grouped form keeps 8 KiB for its tables
+__host__ __device__ constexpr int bn_max_of(bool wide, bool grouped = false) { return wide ? (grouped ? BN_WIDE_GROUPED : BN_WIDE) : BN_MAX; }
 constexpr int kMaxGroupExperts = 1024;
 constexpr int kDequantGroups = 2;                   // group g converts the k-blocks with (index % 2) == g
 constexpr int kDequantWarps = 8 * kDequantGroups, kEpiWarps = 4;
@@ -267,7 +267,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
   // static shared memory, so its dynamic window starts aligned; that is verified below.
   unsigned char* smem = WIDE ? smem_raw : (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int STAGES = stages_of(GROUPED, WIDE);
-  constexpr int B_STAGE = bn_max_of(WIDE) * BK * 2, RAW_B = bn_max_of(WIDE) * 128;
+  constexpr int B_STAGE = bn_max_of(WIDE, GROUPED) * BK * 2, RAW_B = bn_max_of(WIDE, GROUPED) * 128;
   constexpr int HALF_COLS = WIDE ? 256 : 128;      // tensor-memory columns between the two token halves
   unsigned char* a_tiles = smem;                                   // [STAGES][2][128 x 64 bf16]
   unsigned char* b_tiles = smem + STAGES * A_STAGE_BYTES;          // [STAGES][BN x 64 bf16]
@@ -598,64 +598,71 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       // Every role of every CTA of the cluster has left its loops (the epilogue warps after their own CTA's
       // accumulator was complete), so the pipeline buffers of rank 0 are free: ranks 1.. write their fp32
       // partial tiles there (rows padded by 16 bytes against bank conflicts), rank 0 adds them to its own
-      // accumulator and stores.  Tokens <= 128 on this form: one 128-lane half.
+      // accumulator and stores, one or two 128-token halves.
       const bool epi = warp >= kEpiWarp0 && warp < kEpiWarp0 + kEpiWarps;
       const int q = warp & 3;
       const int pitch = (BN + 31) / 32 * 32 * 4 + 16;      // bytes per partial row: whole 32-column chunks + padding
       const bool have_tile = tile0 < ntiles && !s_fail;
+      const TileCoord tc = coords(have_tile ? tile0 : 0);
+      const int nhalf = tc.row0 + 128 < tc.row_end ? 2 : 1;   // token halves in use (the host keeps the buffer in bounds)
       cluster_sync_tc();
       if (epi && crank != 0 && have_tile) {
-        const uint32_t dst0 = smem_u32(smem) + (uint32_t)((crank - 1) * 128 * pitch + (q * 32 + lane) * pitch);
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        for (int half = 0; half < nhalf; ++half) {
+          const uint32_t dst0 = smem_u32(smem) + (uint32_t)(((crank - 1) * nhalf * 128 + half * 128 + q * 32 + lane) * pitch);
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + half * HALF_COLS + c0, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            st_cluster_v4(dst0 + (uint32_t)(c0 + 4 * j) * 4u, 0u,
-                          make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
-                                      __uint_as_float(v[4 * j + 3])));
+            for (int j = 0; j < 8; ++j)
+              st_cluster_v4(dst0 + (uint32_t)(c0 + 4 * j) * 4u, 0u,
+                            make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                                        __uint_as_float(v[4 * j + 3])));
+          }
         }
       }
       cluster_sync_tc();
       if (epi && crank == 0 && have_tile) {
-        const TileCoord tc = coords(tile0);
-        const int m = tc.row0 + q * 32 + lane;
-        const unsigned char* src0 = smem + (size_t)(q * 32 + lane) * pitch;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          float f[32];
+        for (int half = 0; half < nhalf; ++half) {
+          const int m = tc.row0 + half * 128 + q * 32 + lane;
+          const unsigned char* src0 = smem + (size_t)(half * 128 + q * 32 + lane) * pitch;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + half * HALF_COLS + c0, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            float f[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-          for (int k = 0; k + 1 < S; ++k) {
-            const float4* pr = (const float4*)(src0 + (size_t)k * 128 * pitch + (size_t)c0 * 4);
+            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+            for (int k = 0; k + 1 < S; ++k) {
+              const float4* pr = (const float4*)(src0 + (size_t)k * nhalf * 128 * pitch + (size_t)c0 * 4);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float4 a = pr[j];
-              f[4 * j] += a.x; f[4 * j + 1] += a.y; f[4 * j + 2] += a.z; f[4 * j + 3] += a.w;
+              for (int j = 0; j < 8; ++j) {
+                const float4 a = pr[j];
+                f[4 * j] += a.x; f[4 * j + 1] += a.y; f[4 * j + 2] += a.z; f[4 * j + 3] += a.w;
+              }
             }
-          }
-          if (m < tc.row_end) {
-            uint16_t* yrow = p.y + (int64_t)m * p.ldy + tc.n0 + c0;
-            const int nvalid = tc.nend - (tc.n0 + c0);
-            const bool aligned = (((uintptr_t)yrow) & 15) == 0;
+            if (m < tc.row_end) {
+              uint16_t* yrow = p.y + (int64_t)m * p.ldy + tc.n0 + c0;
+              const int nvalid = tc.nend - (tc.n0 + c0);
+              const bool aligned = (((uintptr_t)yrow) & 15) == 0;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (aligned && 8 * j + 8 <= nvalid) {
-                uint4 o;
-                o.x = pack_bf16x2(f[8 * j], f[8 * j + 1]);
-                o.y = pack_bf16x2(f[8 * j + 2], f[8 * j + 3]);
-                o.z = pack_bf16x2(f[8 * j + 4], f[8 * j + 5]);
-                o.w = pack_bf16x2(f[8 * j + 6], f[8 * j + 7]);
-                *(uint4*)(yrow + 8 * j) = o;
-              } else {
+              for (int j = 0; j < 4; ++j) {
+                if (aligned && 8 * j + 8 <= nvalid) {
+                  uint4 o;
+                  o.x = pack_bf16x2(f[8 * j], f[8 * j + 1]);
+                  o.y = pack_bf16x2(f[8 * j + 2], f[8 * j + 3]);
+                  o.z = pack_bf16x2(f[8 * j + 4], f[8 * j + 5]);
+                  o.w = pack_bf16x2(f[8 * j + 6], f[8 * j + 7]);
+                  *(uint4*)(yrow + 8 * j) = o;
+                } else {
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                  if (8 * j + i < nvalid) yrow[8 * j + i] = f32_to_bf16_bits(f[8 * j + i]);
+                  for (int i = 0; i < 8; ++i)
+                    if (8 * j + i < nvalid) yrow[8 * j + i] = f32_to_bf16_bits(f[8 * j + i]);
+                }
               }
             }
           }
@@ -689,11 +696,11 @@ EncodeFn get_encode() {
 }
 
 constexpr size_t smem_bytes_tc(bool grouped, bool wide) {
-  return (size_t)stages_of(grouped, wide) * (A_STAGE_BYTES + bn_max_of(wide) * BK * 2) + (size_t)2 * bn_max_of(wide) * 128 +
+  return (size_t)stages_of(grouped, wide) * (A_STAGE_BYTES + bn_max_of(wide, grouped) * BK * 2) + (size_t)2 * bn_max_of(wide, grouped) * 128 +
          (3 * stages_of(grouped, wide) + 8) * 8 + 16 + (grouped ? (size_t)2 * (kMaxGroupExperts + 1) * 4 : 0) +
          (wide ? 0 : 1024);
 }
-static_assert(smem_bytes_tc(false, true) <= 227 * 1024, "wide form does not fit in shared memory");
+static_assert(smem_bytes_tc(false, true) <= 227 * 1024 && smem_bytes_tc(true, true) <= 227 * 1024, "wide form does not fit in shared memory");
 static_assert(smem_bytes_tc(false, false) <= 227 * 1024 && smem_bytes_tc(true, false) <= 227 * 1024, "shared memory");
 
 constexpr size_t STAGES_DENSE_BYTES = (size_t)stages_of(false) * (A_STAGE_BYTES + B_STAGE_BYTES) + 2 * RAW_BYTES;  // pipeline buffers reused by the exchange
@@ -829,13 +836,28 @@ cudaError_t launch_tc(const TcLaunch& a, bool grouped, cudaStream_t st) {
   const int nsm = sm_count_tc();
   // Wide tiles when both 128-token halves of a tile are in use and there are enough weight rows to fill the GPU
   // with them; the grouped form does not know its tile count on the host and takes full-width dense tiles.
-  const bool wide = !grouped && a.M > 256 && a.N >= 1024;
-  p.BN = grouped ? (a.N >= BN_MAX ? BN_MAX : (int)((a.N + 15) / 16 * 16)) : pick_bn(a.M, a.N, nsm, bn_max_of(wide));
+  // (grouped: many rows per expert on average, so that most tiles have both halves)
+  const bool wide = grouped ? (a.M >= 192 * (int64_t)a.E && a.N >= 256) : (a.M > 256 && a.N >= 1024);
+  if (grouped) {
+    // tile width with the best product of (rows used / rows multiplied) and the width's own efficiency
+    // (time per tile ~ width + 40, as in pick_bn)
+    const int cap = bn_max_of(wide, true);
+    int best = cap;
+    double best_score = -1.0;
+    for (int bn = cap; bn >= 64; bn -= 16) {
+      const double used = (double)a.N / (double)((a.N + bn - 1) / bn * bn);
+      const double score = used * bn / (bn + 40.0);
+      if (score > best_score) { best_score = score; best = bn; }
+    }
+    p.BN = a.N >= 64 ? best : (int)((a.N + 15) / 16 * 16);
+  } else {
+    p.BN = pick_bn(a.M, a.N, nsm, bn_max_of(wide));
+  }
   // Split-K over a cluster when a few-token problem has too few tiles to occupy the GPU: with one tile per CTA
   // the time is the number of k-blocks a CTA walks (plus ~6 k-block times for the exchange), whatever the tile
   // width, so K is cut in 4 or 2 and the tile is made just wide enough for tiles x ranks to fit the SMs.
   p.ksplit = 1;
-  if (!grouped && !wide && a.M <= 128) {
+  if (!grouped && !wide && a.M <= 256) {
     const int gshift = a.gs == 128 ? 1 : 0;
     const int nkb_all = (int)(a.K / BK);
     const int64_t plain_tiles = (a.N + p.BN - 1) / p.BN;
@@ -849,7 +871,7 @@ cudaError_t launch_tc(const TcLaunch& a, bool grouped, cudaStream_t st) {
       bn = (bn + 15) / 16 * 16;
       if (bn < 32) bn = 32;
       if (bn > BN_MAX || (a.N + bn - 1) / bn > max_tiles) continue;
-      if ((size_t)(sp - 1) * 128 * ((bn + 31) / 32 * 32 * 4 + 16) > (size_t)STAGES_DENSE_BYTES) continue;
+      if ((size_t)(sp - 1) * (a.M > 128 ? 256 : 128) * ((bn + 31) / 32 * 32 * 4 + 16) > (size_t)STAGES_DENSE_BYTES) continue;   // exchange buffer
       if (nkb_all / sp + 6 < plain_cost) { p.ksplit = sp; p.BN = bn; break; }
     }
   }
@@ -878,6 +900,7 @@ cudaError_t launch_tc(const TcLaunch& a, bool grouped, cudaStream_t st) {
     return a.bits == 4 ? launch_tc_inst<4, false, false>(map, wmap, p, grid, st, p.ksplit)
                        : launch_tc_inst<8, false, false>(map, wmap, p, grid, st, p.ksplit);
   }
+  if (grouped && wide) return a.bits == 4 ? launch_tc_inst<4, true, true>(map, wmap, p, grid, st) : launch_tc_inst<8, true, true>(map, wmap, p, grid, st);
   if (grouped) return a.bits == 4 ? launch_tc_inst<4, true, false>(map, wmap, p, grid, st) : launch_tc_inst<8, true, false>(map, wmap, p, grid, st);
   if (wide) return a.bits == 4 ? launch_tc_inst<4, false, true>(map, wmap, p, grid, st) : launch_tc_inst<8, false, true>(map, wmap, p, grid, st);
   return a.bits == 4 ? launch_tc_inst<4, false, false>(map, wmap, p, grid, st) : launch_tc_inst<8, false, false>(map, wmap, p, grid, st);

@@ -196,9 +196,10 @@ def test_config4_full_size_vs_dequantize_plus_fp32_matmul(bits):
 
 
 @pytest.mark.parametrize("bits,gs", [(4, 64), (8, 64), (4, 128)])
-@pytest.mark.parametrize("M,N,K", [(128, 4096, 4096), (64, 1024, 4096), (100, 1000, 2048), (128, 512, 14336)])
+@pytest.mark.parametrize("M,N,K", [(128, 4096, 4096), (64, 1024, 4096), (100, 1000, 2048), (128, 512, 14336),
+                                   (256, 4096, 4096), (200, 1024, 2048)])
 def test_few_token_split_k_shapes(bits, gs, M, N, K):
-    """64..128 tokens against few weight rows: the tensor-core kernel cuts K over the CTAs of a cluster and adds
+    """32..256 tokens against few weight rows: the tensor-core kernel cuts K over the CTAs of a cluster and adds
     the partial accumulators in rank 0 (C2's M = 128 projections: q/o 4096x4096, k/v 1024x4096, down K = 14336)."""
     import qb200
     rng = np.random.default_rng(M + N + K + bits + gs)
