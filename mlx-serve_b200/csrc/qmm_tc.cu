@@ -439,11 +439,19 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
           // descriptors of the stage: the start-address field counts 16-byte units, so a K step of
           // 16 values (32 bytes) adds 2 and the second 128-row box of x adds 16 KiB / 16
           const uint64_t ad0 = adesc0 + (uint64_t)(st * (A_STAGE_BYTES >> 4)), bd0 = bdesc0 + (uint64_t)(st * (B_STAGE >> 4));
+          // A tile without a second token half keeps two partial sums over K, in the columns the second
+          // half would use (odd K steps go there; the epilogue adds them): consecutive MMAs into ONE
+          // accumulator wait ~100 cycles on each other, two independent chains hide that.
 #pragma unroll
           for (int k16 = 0; k16 < BK / 16; ++k16) {
-            const uint32_t accum = (kb > 0 || k16 > 0) ? 1u : 0u;
-            umma(d0, ad0 + 2 * k16, bd0 + 2 * k16, idesc, accum);
-            if (two_halves) umma(d0 + HALF_COLS, ad0 + ((128 * BK * 2) >> 4) + 2 * k16, bd0 + 2 * k16, idesc, accum);
+            if (two_halves) {
+              const uint32_t accum = (kb > 0 || k16 > 0) ? 1u : 0u;
+              umma(d0, ad0 + 2 * k16, bd0 + 2 * k16, idesc, accum);
+              umma(d0 + HALF_COLS, ad0 + ((128 * BK * 2) >> 4) + 2 * k16, bd0 + 2 * k16, idesc, accum);
+            } else {
+              const uint32_t accum = (kb > 0 || k16 > 1) ? 1u : 0u;
+              umma(d0 + (k16 & 1) * HALF_COLS, ad0 + 2 * k16, bd0 + 2 * k16, idesc, accum);
+            }
           }
           umma_commit(&empty[st]);  // frees this stage (A and B) once the MMAs above have read it
           PROF_ADD(3);
@@ -552,6 +560,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
     for (int tile = tile0; tile < ntiles && ok; tile += tstride, ++ti) {
       const TileCoord tc = coords(tile);
       const int m0 = tc.row0, n0 = tc.n0, nend = tc.nend, mend = tc.row_end;
+      const bool ksum = m0 + 128 >= mend;   // (same test as the MMA issuer's two_halves)
       const int buf = WIDE ? 0 : ti & 1;
       ok = mbar_wait_relaxed(&acc_full[buf], (WIDE ? ti : ti >> 1) & 1);
       if (!ok || s_fail) { ok = false; break; }
@@ -566,6 +575,13 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
           uint32_t v[32];
           tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + half * HALF_COLS + c0, v);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (ksum) {   // single-half tile: the other half's columns hold the second partial sum over K
+            uint32_t w[32];
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + HALF_COLS + c0, w);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(w[j]));
+          }
           if (m < mend) {
             uint16_t* yrow = p.y + (int64_t)m * p.ldy + n0 + c0;
             const int nvalid = nend - (n0 + c0);   // columns of this chunk inside the matrix and the tile
@@ -615,6 +631,13 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
             uint32_t v[32];
             tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + half * HALF_COLS + c0, v);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (nhalf == 1) {   // second partial sum over K
+              uint32_t w[32];
+              tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + HALF_COLS + c0, w);
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(w[j]));
+            }
 #pragma unroll
             for (int j = 0; j < 8; ++j)
               st_cluster_v4(dst0 + (uint32_t)(c0 + 4 * j) * 4u, 0u,
@@ -637,6 +660,12 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
             float f[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+            if (nhalf == 1) {   // second partial sum over K
+              tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + HALF_COLS + c0, v);
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+              for (int j = 0; j < 32; ++j) f[j] += __uint_as_float(v[j]);
+            }
             for (int k = 0; k + 1 < S; ++k) {
               const float4* pr = (const float4*)(src0 + (size_t)k * nhalf * 128 * pitch + (size_t)c0 * 4);
 #pragma unroll

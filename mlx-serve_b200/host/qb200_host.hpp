@@ -1,0 +1,159 @@
+// C++ host-side mirror of the wrappers through which mlx-serve's Zig code reaches the quantized-inference
+// path, on top of libqb200's C ABI (include/qb200.h).  Same names, argument meaning and error behaviour as the
+// reference's wrappers, so that a call site reads the same after the switch:
+//
+//   quantizeAffine / dequantizeAffine        src/kv_quant.zig:126-162, :407-430
+//   QuantizedKV, quantAttention              src/kv_quant.zig:102-124, :478-687
+//   qmatmulBits                              src/transformer.zig:20894-20983
+//   gatherExpertMm                           src/transformer.zig:20763-20784
+//   KVCacheEntry, KVCache::updateAffine      src/transformer.zig:2777-2858, :3224-3337
+//
+// Differences that follow from the eager ABI: arrays are caller-owned device buffers described by `Array`
+// (no refcounted handles), results are allocated by the caller, and every call takes the CUDA stream (as the ABI's `qb200_stream`, a `cudaStream_t`).  A
+// request the library declines surfaces as `Declined` (the reference's wrappers treat a declined fast lane as
+// fall-through, src/transformer.zig:20463-20475); every other failure as `Error` with the library's message.
+// Header only; needs nothing but the C ABI.
+#pragma once
+#include <cstdint>
+#include <initializer_list>
+#include <stdexcept>
+#include <string>
+
+#include "qb200.h"
+
+namespace qb200h {
+
+struct Error : std::runtime_error {
+  int status;
+  Error(int st, const std::string& msg) : std::runtime_error(msg), status(st) {}
+};
+struct Declined : Error {
+  using Error::Error;
+};
+
+// 0 -> ok; QB200_ERR_UNSUPPORTED (1) -> Declined; anything else -> Error (src/mlx.zig:547-550 maps non-zero to
+// error.MlxError).
+inline void check(int rc) {
+  if (rc == 0) return;
+  const char* m = qb200_last_error();
+  if (rc == 1) throw Declined(rc, m ? m : "declined");
+  throw Error(rc, m ? m : "qb200 error");
+}
+
+// A device buffer seen as a tensor: the caller owns `data`.
+struct Array {
+  qb200_tensor t{};
+  Array() = default;
+  // contiguous row-major view
+  Array(void* data, qb200_dtype dtype, std::initializer_list<int64_t> shape) {
+    t.data = data;
+    t.dtype = dtype;
+    t.ndim = (int32_t)shape.size();
+    int i = 0;
+    for (int64_t d : shape) t.shape[i++] = d;
+    int64_t run = 1;
+    for (int d = t.ndim - 1; d >= 0; --d) { t.stride[d] = run; run *= t.shape[d]; }
+  }
+  bool empty() const { return t.data == nullptr; }
+  int64_t dim(int i) const { return t.shape[i < 0 ? t.ndim + i : i]; }
+  // view of `len` entries starting at `start` along axis `axis` (strides kept: cache views are strided slices,
+  // src/transformer.zig:3472-3495)
+  Array slice(int axis, int64_t start, int64_t len, size_t elem_bytes) const {
+    Array r = *this;
+    r.t.data = (char*)t.data + (size_t)(start * t.stride[axis]) * elem_bytes;
+    r.t.shape[axis] = len;
+    return r;
+  }
+};
+
+inline qb200_optional_int some(int v) { return qb200_optional_int{v, true}; }
+
+// One quantized weight (or expert bank): the triple the loader keeps per tensor (src/transformer.zig:18085).
+struct QWeight {
+  Array q, scales, biases;
+  int group_size = 64, bits = 4;
+};
+
+// kv_quant.QuantizedKV (src/kv_quant.zig:102-124): packed codes + scales + biases, quantised along the last axis.
+struct QuantizedKV {
+  Array q, scales, biases;
+  int group_size = 64, bits = 4;
+};
+
+// quantizeAffine (src/kv_quant.zig:126-162): x [..., D] -> triple, all three caller-allocated.
+inline void quantizeAffine(QuantizedKV& out, const Array& x, qb200_stream s) {
+  check(qb200_quantize(&out.q.t, &out.scales.t, &out.biases.t, &x.t, some(out.group_size), some(out.bits), "affine",
+                       nullptr, s));
+}
+
+// dequantizeAffine (src/kv_quant.zig:407-430): triple -> dense [..., D] in res's dtype.
+inline void dequantizeAffine(Array& res, const QuantizedKV& kv, qb200_stream s) {
+  qb200_optional_dtype dt{(qb200_dtype)res.t.dtype, true};
+  check(qb200_dequantize(&res.t, &kv.q.t, &kv.scales.t, &kv.biases.t, some(kv.group_size), some(kv.bits), "affine", nullptr,
+                         dt, s));
+}
+
+// qmatmulBits (src/transformer.zig:20894-20983): res = x . dequant(w)^T.
+inline void qmatmulBits(Array& res, const Array& x, const QWeight& w, qb200_stream s) {
+  check(qb200_quantized_matmul(&res.t, &x.t, &w.q.t, &w.scales.t, &w.biases.t, true, some(w.group_size), some(w.bits),
+                               "affine", s));
+}
+
+// The projections that share their input (q,k,v / gate,up: src/transformer.zig:9202-9207, :9452-9454) in one call.
+inline void qmatmulBitsBatch(Array* const* res, const Array& x, const QWeight* const* w, int count, qb200_stream s) {
+  if (count < 1 || count > 8) throw Error(2, "qmatmulBitsBatch: count must be 1..8");
+  qb200_tensor* r[8];
+  const qb200_tensor *q[8], *sc[8], *bi[8];
+  for (int i = 0; i < count; ++i) { r[i] = &res[i]->t; q[i] = &w[i]->q.t; sc[i] = &w[i]->scales.t; bi[i] = &w[i]->biases.t; }
+  check(qb200_quantized_matmul_batch(r, &x.t, q, sc, bi, count, true, some(w[0]->group_size), some(w[0]->bits), "affine",
+                                     s));
+}
+
+// gatherExpertMm (src/transformer.zig:20763-20784): res[i] = x[lhs(i)] . dequant(bank[rhs[i]])^T; lhs may be null.
+inline void gatherExpertMm(Array& res, const Array& x, const QWeight& bank, const Array* lhs_indices, const Array& rhs_indices,
+                           bool sorted_indices, qb200_stream s) {
+  check(qb200_gather_qmm(&res.t, &x.t, &bank.q.t, &bank.scales.t, &bank.biases.t, lhs_indices ? &lhs_indices->t : nullptr,
+                         &rhs_indices.t, true, some(bank.group_size), some(bank.bits), "affine", sorted_indices,
+                         s));
+}
+
+// KVCacheEntry (src/transformer.zig:2777-2858): six capacity buffers [B, Hkv, cap, *] per layer and the fill level.
+struct KVCacheEntry {
+  QuantizedKV keys, values;   // capacity buffers
+  int64_t offset = 0;         // tokens stored so far
+  int64_t capacity() const { return keys.q.dim(2); }
+  // views of the first `offset` tokens, with the capacity buffers' strides
+  QuantizedKV view(const QuantizedKV& c) const {
+    QuantizedKV v = c;
+    v.q = c.q.slice(2, 0, offset, 4);
+    v.scales = c.scales.slice(2, 0, offset, 2);
+    v.biases = c.biases.slice(2, 0, offset, 2);
+    return v;
+  }
+};
+
+// KVCache.updateAffine (src/transformer.zig:3224-3337): quantise the new K and V rows [B, Hkv, S, D] and write
+// them at `offset`; the caller grows the capacity buffers (the reference grows them by 25 %, :3116-3146).
+inline void updateAffine(KVCacheEntry& e, const Array& k_new, const Array& v_new, qb200_stream s) {
+  const int64_t S = k_new.dim(2);
+  if (e.offset + S > e.capacity()) throw Error(2, "updateAffine: capacity exceeded; grow the cache first");
+  check(qb200_kv_append(&e.keys.q.t, &e.keys.scales.t, &e.keys.biases.t, &k_new.t, e.offset, e.keys.bits, e.keys.group_size,
+                        s));
+  check(qb200_kv_append(&e.values.q.t, &e.values.scales.t, &e.values.biases.t, &v_new.t, e.offset, e.values.bits,
+                        e.values.group_size, s));
+  e.offset += S;
+}
+
+// quantAttention (src/kv_quant.zig:478-687) for T_q == 1: out [B, Hq, 1, Dv] = softmax(q K^T * scale) V over the
+// packed cache views.  `mask` is an optional additive row (mask mode "array"), `kv_lens` optional int32 [B].
+inline size_t quantAttentionWorkspace(int64_t B, int64_t Hq, int64_t Hkv, int64_t T, int64_t Dv) {
+  return qb200_kv_decode_attention_workspace_size(B, Hq, Hkv, T, Dv);
+}
+inline void quantAttention(Array& out, const Array& q, const QuantizedKV& k, const QuantizedKV& v, float scale, const Array* mask,
+                           const Array* kv_lens, void* workspace, size_t workspace_bytes, qb200_stream s) {
+  check(qb200_kv_decode_attention(&out.t, &q.t, &k.q.t, &k.scales.t, &k.biases.t, &v.q.t, &v.scales.t, &v.biases.t, k.bits,
+                                  k.group_size, scale, mask ? "array" : "", mask ? &mask->t : nullptr,
+                                  kv_lens ? &kv_lens->t : nullptr, workspace, workspace_bytes, s));
+}
+
+}  // namespace qb200h
