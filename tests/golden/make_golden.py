@@ -2,7 +2,7 @@
 """Generate the golden vectors in this folder from the reference's own code.
 
 Run in a checkout that has the mlx-serve tree available (its path is the first
-argument, default ``/root/reference``).  It imports the reference's numpy
+argument, default: the checkout next to this build).  It imports the reference's numpy
 restatement of MLX's affine quantization, ``tests/dsv4_imatrix.py``
 (pack_bits / unpack_bits / dequant_np / _mlx_minmax_sb, and the code
 derivation ``clip(rint((X - b) / s), 0, n)`` at :264) together with the bf16
@@ -23,7 +23,7 @@ import warnings
 
 import numpy as np
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "..", "reference")
 sys.path.insert(0, os.path.join(REF, "tests"))
 with warnings.catch_warnings():
     warnings.simplefilter("ignore")
