@@ -36,6 +36,7 @@
 //    share their tiles and split K, each converting only its own range, with the
 //    partial sums added in rank 0 behind one cluster barrier per round.
 // Nothing is written to global scratch; the only global writes are y.
+#include <type_traits>
 #include "kernels.h"
 
 namespace qb {
@@ -177,30 +178,6 @@ __device__ __forceinline__ int mat_of_tile(const StreamK& p, int tile) {
   return mi;
 }
 
-// Position of a warp in its stream of (pass, local tile, K unit) items.
-struct ItemIter {
-  int pass, tl, u;
-  int ks, ntl, npass, upk, ut;  // ut: units per tile over all of K; upk: units per full pass
-  __device__ __forceinline__ int upt(int p) const {
-    const int left = ut - p * upk;
-    return left < upk ? left : upk;
-  }
-  __device__ __forceinline__ void normalize() {
-    while (pass < npass && u >= upt(pass)) {
-      u = ks;
-      if (++tl >= ntl) { tl = 0; ++pass; }
-    }
-  }
-  __device__ __forceinline__ void init(int ks_, int ntl_, int npass_, int upk_, int ut_) {
-    ks = ks_; ntl = ntl_; npass = npass_; upk = upk_; ut = ut_;
-    pass = 0; tl = 0; u = ks;
-    if (ntl <= 0) pass = npass;
-    normalize();
-  }
-  __device__ __forceinline__ bool valid() const { return pass < npass; }
-  __device__ __forceinline__ void next() { u += kWarpsPerGroup; normalize(); }
-};
-
 template <int BITS, int NT, bool M1>
 __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 : 1) qmv_stream_kernel(StreamK p) {
   extern __shared__ __align__(128) unsigned char smem[];
@@ -241,46 +218,78 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
   const int k_cta = split ? (p.K - k_lo < p.upc * CK ? (p.K - k_lo > 0 ? p.K - k_lo : 0) : p.upc * CK) : p.K;
   const int ut = k_cta / CK, upk = split ? (ut > 0 ? ut : 1) : kc / CK;
 
-  // ---- producer state: per-lane source pointers of the current tile ----
+  // ---- producer: this warp's stream of (pass, local tile, K unit) items ----
+  // A lane copies 16 bytes of four rows of a stage (rows lane/8 + 4r) and one scale or bias entry.  The source
+  // pointers move by constants from unit to unit and from a tile to the group's next tile; only a change of
+  // matrix, a last partial tile or a new K pass recomputes them (setup()).
   const int chunk = lane & 7;
-  const unsigned char* wsrc[4];
-  const uint16_t* sbsrc;
   uint32_t wdst[4];
-  uint32_t sbdst;
-  int prod_tile = -1;
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
     const int row = (lane >> 3) + 4 * r;
-    wdst[r] = row * 128 + ((chunk ^ swz<BITS>(row)) << 4);
+    wdst[r] = my_ring + row * 128 + ((chunk ^ swz<BITS>(row)) << 4);
   }
-  sbdst = kStageW + (lane >> 4) * 128 + (lane & 15) * 8;
+  const uint32_t sbdst = my_ring + kStageW + (lane & 15) * 16 + (lane >> 4) * 8;   // per row: scales | biases
+  const int sbstep = (kWarpsPerGroup * U) >> p.gshift;   // scale entries between two units of this warp
+  const unsigned char* wp = nullptr;   // row slot 0 of the next item
+  const uint16_t* sbp = nullptr;       // scale (lanes 0-15) or bias (16-31) of the next item
+  uint32_t roff[3] = {0u, 0u, 0u};     // byte offsets of row slots 1..3 from slot 0
+  int64_t tstep_w = 0, tstep_sb = 0;   // from behind a tile's last unit to the next tile's first
+  int p_tile = 0, p_fast_end = 0;      // current tile; the group's next tile below p_fast_end is a constant step away
+  int p_tl = 0, p_pass = 0, p_j = 0, p_nu = 0;
+  uint32_t p_off = 0;                  // byte offset of the stage the next item goes to
 
-  auto issue = [&](const ItemIter& it, int stage) {
-    const int tile = ggrp + it.tl * p.total_groups;
-    if (tile != prod_tile) {
-      prod_tile = tile;
-      const int mi = mat_of_tile(p, tile);
-      const int row0 = (tile - QB_SEL4(p.tile0, mi)) * 16, nrows = QB_SEL4(p.N, mi);
-      const uint32_t* wm = QB_SEL4(p.w, mi);
-      const int64_t ldw = QB_SEL4(p.ldw, mi), lds = QB_SEL4(p.lds, mi);
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        int n = row0 + (lane >> 3) + 4 * r;
-        n = n < nrows ? n : nrows - 1;
-        wsrc[r] = (const unsigned char*)(wm + (int64_t)n * ldw) + chunk * 16;
-      }
-      int n = row0 + (lane & 15);
-      n = n < nrows ? n : nrows - 1;
-      sbsrc = ((lane >> 4) ? QB_SEL4(p.b, mi) : QB_SEL4(p.s, mi)) + (int64_t)n * lds;
+  auto setup = [&]() {
+    for (;;) {
+      if (p_pass >= p.npass || ntl <= 0) { p_pass = p.npass; p_tl = ntl; return; }   // stream exhausted
+      const int left = ut - p_pass * upk, upt_p = left < upk ? left : upk;
+      p_nu = upt_p > ks ? (upt_p - ks + kWarpsPerGroup - 1) / kWarpsPerGroup : 0;
+      if (p_nu > 0) break;
+      ++p_pass;   // this warp has no unit in this pass
     }
-    const uint32_t st = my_ring + stage * kStageBytes;
-    const int k0 = k_lo + it.pass * kc + it.u * CK;
-    const int woff = k0 * BITS / 8;
+    p_tile = ggrp + p_tl * p.total_groups;
+    const int mi = mat_of_tile(p, p_tile);
+    const int t0 = QB_SEL4(p.tile0, mi), nrows = QB_SEL4(p.N, mi);
+    const int row0 = (p_tile - t0) * 16;
+    const int64_t ldw = QB_SEL4(p.ldw, mi), lds = QB_SEL4(p.lds, mi);
+    const int k0 = k_lo + p_pass * kc + ks * CK;
+    int n0 = row0 + (lane >> 3);
+    n0 = n0 < nrows ? n0 : nrows - 1;
+    wp = (const unsigned char*)(QB_SEL4(p.w, mi) + (int64_t)n0 * ldw) + chunk * 16 + k0 * BITS / 8;
 #pragma unroll
-    for (int r = 0; r < 4; ++r) cp_async16(st + wdst[r], wsrc[r] + woff);
-    const uint16_t* ssrc = sbsrc + ((k0 >> 6) >> p.gshift);
-    if (BITS == 4 && p.gshift == 0) cp_async8(st + sbdst, ssrc);
-    else cp_async4(st + sbdst, ssrc);
+    for (int r = 1; r < 4; ++r) {
+      int n = row0 + (lane >> 3) + 4 * r;
+      n = n < nrows ? n : nrows - 1;
+      roff[r - 1] = (uint32_t)((n - n0) * (int)ldw * 4);
+    }
+    int ns = row0 + (lane & 15);
+    ns = ns < nrows ? ns : nrows - 1;
+    sbp = ((lane >> 4) ? QB_SEL4(p.b, mi) : QB_SEL4(p.s, mi)) + (int64_t)ns * lds + ((k0 >> 6) >> p.gshift);
+    tstep_w = (int64_t)p.total_groups * 16 * ldw * 4 - (int64_t)p_nu * (kWarpsPerGroup * 128);
+    tstep_sb = (int64_t)p.total_groups * 16 * lds - (int64_t)p_nu * sbstep;
+    p_fast_end = t0 + nrows / 16;
+  };
+  auto prod_valid = [&]() { return p_tl < ntl; };
+  // copy the next item into its stage and step to the one after it
+  auto issue = [&]() {
+    cp_async16(wdst[0] + p_off, wp);
+    cp_async16(wdst[1] + p_off, wp + roff[0]);
+    cp_async16(wdst[2] + p_off, wp + roff[1]);
+    cp_async16(wdst[3] + p_off, wp + roff[2]);
+    if (BITS == 4 && p.gshift == 0) cp_async8(sbdst + p_off, sbp);
+    else cp_async4(sbdst + p_off, sbp);
+    p_off = p_off + kStageBytes == kStages * kStageBytes ? 0u : p_off + kStageBytes;
+    wp += kWarpsPerGroup * 128;
+    sbp += sbstep;
+    if (++p_j == p_nu) {
+      p_j = 0;
+      ++p_tl;
+      p_tile += p.total_groups;
+      wp += tstep_w;
+      sbp += tstep_sb;
+      if (p_tl >= ntl) { p_tl = 0; ++p_pass; setup(); }
+      else if (p_tile >= p_fast_end) setup();
+    }
   };
 
   // per-lane byte offsets of the fragment reads of row g (row g+8 is +1024: same swizzle)
@@ -291,14 +300,11 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
     else frag_off[j] = g * 128 + (((4 * j + t) ^ swz<8>(g)) << 4);
   }
 
-  ItemIter prod;
-  prod.init(ks, ntl, p.npass, upk, ut);
-  int issued = 0;
+  setup();
 #pragma unroll
   for (int i = 0; i < kStages - 1; ++i) {
-    if (prod.valid()) { issue(prod, issued % kStages); prod.next(); }
+    if (prod_valid()) issue();
     cp_async_commit();
-    ++issued;
   }
 
   // Let the next grid in the stream begin launching, then wait for the previous grid to complete (and
@@ -309,7 +315,7 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
   TL(2);
   if constexpr (!M1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 
-  int consumed = 0;
+  uint32_t c_off = 0;   // byte offset of the stage the next unit is read from
   int red_buf = 0;
 
   for (int pass = 0; pass < p.npass; ++pass) {
@@ -320,65 +326,58 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
     }
     // ---- stage this pass's activations as s8 planes in B-fragment order ----
     // One thread converts 8 consecutive K values of one token; the 8 lanes that cover a 64-wide
-    // group agree on the group's power-of-two scale (|x| * up < 2^14) through shuffles.
+    // group agree on the group's power-of-two scale (|x| * up < 2^14) through shuffles.  The conversion
+    // v = rn(x * up) is one FMA onto 1.5 * 2^23: the low 16 bits of the sum's bit pattern are v in two's
+    // complement, so the planes are cut out of pairs of values packed into one word.
     {
       const int cpt = klen >> 3;                         // 8-value chunks per token
-      const int slots = M1 ? 1 : NT * kTokPerTile;
-      const int total = slots * cpt;
-      constexpr int PF = 4;  // chunks fetched per thread before any is converted (loads in flight together)
-      // The CTAs of a cluster take interleaved blocks of kThreads chunks and broadcast what they convert.
-      // (K-split mode: every CTA converts its own K range for itself)
+      constexpr int PF = (M1 || NT == 2) ? 4 : 2;  // chunks fetched per thread before any is converted (loads in flight together)
+      const bool al16 = ((((uintptr_t)p.x) | (uintptr_t)(p.ldx * (p.x_f32 ? 4 : 2))) & 15) == 0;  // k_base * element size is
+      // The CTAs of a cluster take the tokens in turn and write what they convert into the shared memory of
+      // all of them (K-split mode: every CTA converts its own K range of every token for itself).
       const int CS = (M1 || split) ? 1 : (int)cluster_size(), crank_b = (M1 || split) ? 0 : crank;
-      const uint32_t xfrag_s = (uint32_t)__cvta_generic_to_shared(xfrag), gsc_s = (uint32_t)__cvta_generic_to_shared(gsc);
-      for (int base0 = 0; base0 < total; base0 += kThreads * PF * CS) {
-       uint4 raw[PF][2];
+      uint32_t xdst[4] = {0u, 0u, 0u, 0u}, gdelta = 0u;   // a peer's gsc is the same distance behind its xfrag
+      if constexpr (!M1) {
+        const uint32_t xfrag_s = (uint32_t)__cvta_generic_to_shared(xfrag), gsc_s = (uint32_t)__cvta_generic_to_shared(gsc);
 #pragma unroll
-       for (int q = 0; q < PF; ++q) {
-        const int it = base0 + (q * CS + crank_b) * kThreads + tid;
-        raw[q][0] = make_uint4(0u, 0u, 0u, 0u);
-        raw[q][1] = make_uint4(0u, 0u, 0u, 0u);
-        if (it < total) {
-          const int m = it / cpt, c = it - m * cpt;
-          if (m < p.M) {
-            const int64_t off = (int64_t)m * p.ldx + k_base + c * 8;
-            if (!p.x_f32) {
-              const uint16_t* px = (const uint16_t*)p.x + off;
-              if ((((uintptr_t)px) & 15) == 0) {
-                raw[q][0] = *(const uint4*)px;
-              } else {
-                uint32_t r[4];
+        for (int cr = 0; cr < 4; ++cr) {
+          const uint32_t rk = split ? (uint32_t)crank : (uint32_t)(cr < CS ? cr : 0);
+          xdst[cr] = map_to_rank(xfrag_s, rk);
+        }
+        gdelta = gsc_s - xfrag_s;
+      }
+      auto load = [&](auto f32tag, int m, int c, uint4& r0, uint4& r1) {
+        constexpr bool F32 = decltype(f32tag)::value;
+        const int64_t off = (int64_t)m * p.ldx + k_base + c * 8;
+        if constexpr (!F32) {
+          const uint16_t* px = (const uint16_t*)p.x + off;
+          if (al16) {
+            r0 = *(const uint4*)px;
+          } else {
+            uint32_t r[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) r[j] = (uint32_t)px[2 * j] | ((uint32_t)px[2 * j + 1] << 16);
-                raw[q][0] = make_uint4(r[0], r[1], r[2], r[3]);
-              }
-            } else {
-              const float* px = (const float*)p.x + off;
-              if ((((uintptr_t)px) & 15) == 0) {
-                raw[q][0] = *(const uint4*)px;
-                raw[q][1] = *(const uint4*)(px + 4);
-              } else {
-                raw[q][0] = make_uint4(__float_as_uint(px[0]), __float_as_uint(px[1]), __float_as_uint(px[2]), __float_as_uint(px[3]));
-                raw[q][1] = make_uint4(__float_as_uint(px[4]), __float_as_uint(px[5]), __float_as_uint(px[6]), __float_as_uint(px[7]));
-              }
-            }
+            for (int j = 0; j < 4; ++j) r[j] = (uint32_t)px[2 * j] | ((uint32_t)px[2 * j + 1] << 16);
+            r0 = make_uint4(r[0], r[1], r[2], r[3]);
+          }
+        } else {
+          const float* px = (const float*)p.x + off;
+          if (al16) {
+            r0 = *(const uint4*)px;
+            r1 = *(const uint4*)(px + 4);
+          } else {
+            r0 = make_uint4(__float_as_uint(px[0]), __float_as_uint(px[1]), __float_as_uint(px[2]), __float_as_uint(px[3]));
+            r1 = make_uint4(__float_as_uint(px[4]), __float_as_uint(px[5]), __float_as_uint(px[6]), __float_as_uint(px[7]));
           }
         }
-       }
-#pragma unroll
-       for (int q = 0; q < PF; ++q) {
-        const int base = base0 + (q * CS + crank_b) * kThreads;
-        if (base >= total) continue;
-        const int it = base + tid;
-        const bool ok = it < total;
-        const int m = ok ? it / cpt : 0;
-        const int c = ok ? it - m * cpt : 0;             // chunk index inside the pass
+      };
+      // every lane of the warp calls this (shuffles); `ok` gates the stores
+      auto convert = [&](auto f32tag, const uint4& a, const uint4& b2, int c, int m, bool ok) {
+        constexpr bool F32 = decltype(f32tag)::value;
         float f[8];
-        if (!p.x_f32) {
-          const uint4 a = raw[q][0];
+        if constexpr (!F32) {
           f[0] = bf16lo(a.x); f[1] = bf16hi(a.x); f[2] = bf16lo(a.y); f[3] = bf16hi(a.y);
           f[4] = bf16lo(a.z); f[5] = bf16hi(a.z); f[6] = bf16lo(a.w); f[7] = bf16hi(a.w);
         } else {
-          const uint4 a = raw[q][0], b2 = raw[q][1];
           f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
           f[4] = __uint_as_float(b2.x); f[5] = __uint_as_float(b2.y); f[6] = __uint_as_float(b2.z); f[7] = __uint_as_float(b2.w);
         }
@@ -392,43 +391,87 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
         e = e < -100 ? -100 : (e > 110 ? 110 : e);
         const float up = __uint_as_float((uint32_t)(127 + 14 - e) << 23);
         const float down = __uint_as_float((uint32_t)(127 + e - 14) << 23);
-        int v[8];
-        int sum = 0;
+        uint32_t w[8];   // bit patterns of 1.5 * 2^23 + v: 0x4B400000 + v
+        uint32_t isum = 0;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { v[j] = fix15(f[j], up); sum += v[j]; }
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-        if (ok) {
-          const int gi = c >> 3, tt = (c >> 1) & 3, jm = c & 1;  // 64-group, lane quarter, MMA of the group
+        for (int j = 0; j < 8; ++j) {
+          float r = fmaf(f[j], up, 12582912.f);
+          if constexpr (F32) r = fminf(r, 12599295.f);   // fp32 inputs may round up to 2^14: v <= 16383 (-2^14 fits the high plane)
+          w[j] = __float_as_uint(r);
+          isum += w[j];
+        }
+        isum += __shfl_xor_sync(0xffffffffu, isum, 1);
+        isum += __shfl_xor_sync(0xffffffffu, isum, 2);
+        isum += __shfl_xor_sync(0xffffffffu, isum, 4);
+        const int sum = (int)(isum - 0xD0000000u);   // 64 values: 64 * 0x4B400000 mod 2^32
+        if (!ok) return;
+        uint32_t o[2][2];   // [plane][operand register]
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t p0 = __byte_perm(w[kslot8<BITS>(h, 0)], w[kslot8<BITS>(h, 1)], 0x5410);   // two 16-bit values
+          const uint32_t p1 = __byte_perm(w[kslot8<BITS>(h, 2)], w[kslot8<BITS>(h, 3)], 0x5410);
+          o[0][h] = __byte_perm((p0 >> 7) & 0x00FF00FFu, (p1 >> 7) & 0x00FF00FFu, 0x6420);   // (v >> 7) & 0xFF
+          o[1][h] = __byte_perm(p0 & 0x007F007Fu, p1 & 0x007F007Fu, 0x6420);                 // v & 127
+        }
+        const int gi = c >> 3, tt = (c >> 1) & 3, jm = c & 1;  // 64-group, lane quarter, MMA of the group
+        if constexpr (M1) {
+          if ((c & 7) == 0) *(float2*)&gsc[gi * 2] = make_float2(down, down * (float)sum);
+          uint2* d = xfrag + (gi * 8 + tt) * 2 + jm;   // 16 bytes per (group, column, lane quarter): both MMAs' operands
+          d[0] = make_uint2(o[0][0], o[0][1]);
+          d[8] = make_uint2(o[1][0], o[1][1]);
+        } else {
           const int nt = m / kTokPerTile, ml = m - nt * kTokPerTile;
-          if ((c & 7) == 0) {
-            if constexpr (M1) {
-              gsc[gi * 2] = down;
-              gsc[gi * 2 + 1] = down * (float)sum;
-            } else {
-              const uint32_t a = gsc_s + (uint32_t)(((gi * NT + nt) * kTokPerTile + ml) * 2) * 4u;
-              for (int cr = 0; cr < CS; ++cr)
-                st_cluster_v2(map_to_rank(a, split ? crank : cr), __float_as_uint(down), __float_as_uint(down * (float)sum));
-            }
-          }
+          const uint32_t xo = (uint32_t)((gi * NT + nt) * 32 + 2 * ml * 4 + tt) * 16u + (uint32_t)jm * 8u;
+          const uint32_t go = (uint32_t)(((gi * kTokPerTile + ml) * NT + nt) * 2) * 4u;
 #pragma unroll
-          for (int pl = 0; pl < 2; ++pl) {
-            uint2 o;
-            o.x = plane_byte(v[kslot8<BITS>(0, 0)], pl) | (plane_byte(v[kslot8<BITS>(0, 1)], pl) << 8) |
-                  (plane_byte(v[kslot8<BITS>(0, 2)], pl) << 16) | (plane_byte(v[kslot8<BITS>(0, 3)], pl) << 24);
-            o.y = plane_byte(v[kslot8<BITS>(1, 0)], pl) | (plane_byte(v[kslot8<BITS>(1, 1)], pl) << 8) |
-                  (plane_byte(v[kslot8<BITS>(1, 2)], pl) << 16) | (plane_byte(v[kslot8<BITS>(1, 3)], pl) << 24);
-            if constexpr (M1) {
-              xfrag[(gi * 2 + jm) * 8 + pl * 4 + tt] = o;
-            } else {
-              const uint32_t a = xfrag_s + (uint32_t)(((gi * 2 + jm) * NT + nt) * 32 + (2 * ml + pl) * 4 + tt) * 8u;
-              for (int cr = 0; cr < CS; ++cr) st_cluster_v2(map_to_rank(a, split ? crank : cr), o.x, o.y);
+          for (int cr = 0; cr < 4; ++cr) {
+            if (cr < CS) {
+              st_cluster_v2(xdst[cr] + xo, o[0][0], o[0][1]);
+              st_cluster_v2(xdst[cr] + xo + 64u, o[1][0], o[1][1]);
+              if ((c & 7) == 0) st_cluster_v2(xdst[cr] + gdelta + go, __float_as_uint(down), __float_as_uint(down * (float)sum));
             }
           }
         }
-       }
-      }
+      };
+      auto stage_all = [&](auto f32tag) {
+        if constexpr (M1) {
+          for (int c0 = 0; c0 < cpt; c0 += kThreads * PF) {
+            uint4 raw[PF][2];
+#pragma unroll
+            for (int q = 0; q < PF; ++q) {
+              const int c = c0 + q * kThreads + tid;
+              raw[q][0] = raw[q][1] = make_uint4(0u, 0u, 0u, 0u);
+              if (c < cpt) load(f32tag, 0, c, raw[q][0], raw[q][1]);
+            }
+#pragma unroll
+            for (int q = 0; q < PF; ++q) {
+              if (c0 + q * kThreads >= cpt) continue;
+              const int c = c0 + q * kThreads + tid;
+              convert(f32tag, raw[q][0], raw[q][1], c, 0, c < cpt);
+            }
+          }
+        } else {
+          for (int c0 = 0; c0 < cpt; c0 += kThreads) {
+            const int c = c0 + tid;
+            for (int m0 = crank_b; m0 < p.M; m0 += PF * CS) {
+              uint4 raw[PF][2];
+#pragma unroll
+              for (int q = 0; q < PF; ++q) {
+                const int m = m0 + q * CS;
+                raw[q][0] = raw[q][1] = make_uint4(0u, 0u, 0u, 0u);
+                if (m < p.M && c < cpt) load(f32tag, m, c, raw[q][0], raw[q][1]);
+              }
+#pragma unroll
+              for (int q = 0; q < PF; ++q) {
+                const int m = m0 + q * CS;
+                if (m >= p.M) continue;
+                convert(f32tag, raw[q][0], raw[q][1], c, m, c < cpt);
+              }
+            }
+          }
+        }
+      };
+      if (p.x_f32) stage_all(std::true_type{}); else stage_all(std::false_type{});
     }
     if constexpr (M1) __syncthreads(); else cluster_sync_all();
     if (pass == 0) TL(3);
@@ -446,43 +489,44 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
 
       for (int u = ks; u < upt; u += kWarpsPerGroup) {
         // keep the ring full, then wait for this item's bytes
-        if (prod.valid()) { issue(prod, issued % kStages); prod.next(); }
+        if (prod_valid()) issue();
         cp_async_commit();
-        ++issued;
         cp_async_wait<kStages - 1>();
         __syncwarp();
-        const unsigned char* st = my_ring_p + (consumed % kStages) * kStageBytes;
-        ++consumed;
+        const unsigned char* st = my_ring_p + c_off;
+        c_off = c_off + kStageBytes == kStages * kStageBytes ? 0u : c_off + kStageBytes;
 
-        // scales / biases of rows g and g+8 for the unit's U groups (bf16 pairs)
+        // scales / biases of rows g and g+8 for the unit's U groups (bf16 pairs): 16 bytes per row
         uint32_t sl[2], sh[2], bl[2], bh[2];
         {
-          const unsigned char* sb = st + kStageW;
+          const uint4 lo = *(const uint4*)(st + kStageW + g * 16), hi = *(const uint4*)(st + kStageW + (g + 8) * 16);
           if (BITS == 4 && p.gshift == 0) {
-            const uint2 a = *(const uint2*)(sb + g * 8), c = *(const uint2*)(sb + (g + 8) * 8);
-            const uint2 d = *(const uint2*)(sb + 128 + g * 8), e = *(const uint2*)(sb + 128 + (g + 8) * 8);
-            sl[0] = a.x; sl[1] = a.y; sh[0] = c.x; sh[1] = c.y;
-            bl[0] = d.x; bl[1] = d.y; bh[0] = e.x; bh[1] = e.y;
+            sl[0] = lo.x; sl[1] = lo.y; sh[0] = hi.x; sh[1] = hi.y;
+            bl[0] = lo.z; bl[1] = lo.w; bh[0] = hi.z; bh[1] = hi.w;
+          } else if (BITS == 4) {  // group size 128: each value serves two 64-wide groups
+            sl[0] = __byte_perm(lo.x, lo.x, 0x1010); sl[1] = __byte_perm(lo.x, lo.x, 0x3232);
+            sh[0] = __byte_perm(hi.x, hi.x, 0x1010); sh[1] = __byte_perm(hi.x, hi.x, 0x3232);
+            bl[0] = __byte_perm(lo.z, lo.z, 0x1010); bl[1] = __byte_perm(lo.z, lo.z, 0x3232);
+            bh[0] = __byte_perm(hi.z, hi.z, 0x1010); bh[1] = __byte_perm(hi.z, hi.z, 0x3232);
           } else {
-            const uint32_t a = *(const uint32_t*)(sb + g * 8), c = *(const uint32_t*)(sb + (g + 8) * 8);
-            const uint32_t d = *(const uint32_t*)(sb + 128 + g * 8), e = *(const uint32_t*)(sb + 128 + (g + 8) * 8);
-            if (BITS == 4) {  // group size 128: each value serves two 64-wide groups
-              sl[0] = __byte_perm(a, a, 0x1010); sl[1] = __byte_perm(a, a, 0x3232);
-              sh[0] = __byte_perm(c, c, 0x1010); sh[1] = __byte_perm(c, c, 0x3232);
-              bl[0] = __byte_perm(d, d, 0x1010); bl[1] = __byte_perm(d, d, 0x3232);
-              bh[0] = __byte_perm(e, e, 0x1010); bh[1] = __byte_perm(e, e, 0x3232);
-            } else {
-              sl[0] = a; sh[0] = c; bl[0] = d; bh[0] = e;
-              sl[1] = sh[1] = bl[1] = bh[1] = 0;
-            }
+            sl[0] = lo.x; sh[0] = hi.x; bl[0] = lo.z; bh[0] = hi.z;
+            sl[1] = sh[1] = bl[1] = bh[1] = 0;
           }
         }
         // Fragments and group scales of this unit's U groups; every offset below is a compile-time constant.
         // Single token: only the two plane columns 0 and 1 of the n8 tile are read back (by the lanes
         // with t == 0), so the lanes that feed columns 2..7 may load anything: they re-read columns 0/1.
-        const uint2* xb = M1 ? xfrag + (size_t)(u * U * 2) * 8 + (g & 1) * 4 + t
-                             : xfrag + (size_t)(u * U * 2 * NT) * 32 + lane;
-        const float* gb = M1 ? gsc + (size_t)(u * U) * 2 : gsc + (size_t)(u * U * NT * kTokPerTile + t) * 2;
+        const uint4* xb = M1 ? (const uint4*)xfrag + (size_t)(u * U) * 8 + (g & 1) * 4 + t
+                             : (const uint4*)xfrag + (size_t)(u * U * NT) * 32 + lane;
+        const float* gb = M1 ? gsc + (size_t)(u * U) * 2 : gsc + (size_t)((u * U * kTokPerTile + t) * NT) * 2;
+        float2 gs1[U];   // single token: the unit's group scales, two groups per load
+        if constexpr (M1) {
+#pragma unroll
+          for (int j = 0; j < U; j += 2) {
+            const float4 v = *(const float4*)&gb[j * 2];
+            gs1[j] = make_float2(v.x, v.y); gs1[j + 1] = make_float2(v.z, v.w);
+          }
+        }
 #pragma unroll
         for (int j = 0; j < U; ++j) {
           uint32_t a0[2], a1[2], a2[2], a3[2];  // [mma]: row g lo, row g+8 lo, row g hi, row g+8 hi
@@ -505,21 +549,28 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
           const float b_hi = (j & 1) ? bf16hi(bh[j >> 1]) : bf16lo(bh[j >> 1]);
           if constexpr (M1) {
             int acc[4];
-            const uint2 bf0 = xb[(j * 2 + 0) * 8], bf1 = xb[(j * 2 + 1) * 8];
-            mma_u8s8_z(acc, a0[0], a1[0], a2[0], a3[0], bf0.x, bf0.y);
-            mma_u8s8(acc, a0[1], a1[1], a2[1], a3[1], bf1.x, bf1.y);
-            const float2 gs = *(const float2*)&gb[j * 2];
+            const uint4 bf = xb[j * 8];
+            mma_u8s8_z(acc, a0[0], a1[0], a2[0], a3[0], bf.x, bf.y);
+            mma_u8s8(acc, a0[1], a1[1], a2[1], a3[1], bf.z, bf.w);
+            const float2 gs = gs1[j];
             const float f_lo = (float)(acc[0] * 128 + acc[1]), f_hi = (float)(acc[2] * 128 + acc[3]);
             tot[0][0] = fmaf(s_lo * gs.x, f_lo, fmaf(b_lo, gs.y, tot[0][0]));
             tot[0][1] = fmaf(s_hi * gs.x, f_hi, fmaf(b_hi, gs.y, tot[0][1]));
           } else {
+            float2 gsn[NT];   // this lane's token of every tile
+            if constexpr (NT == 2) {
+              const float4 v = *(const float4*)&gb[j * kTokPerTile * NT * 2];
+              gsn[0] = make_float2(v.x, v.y); gsn[NT - 1] = make_float2(v.z, v.w);
+            } else {
+              gsn[0] = *(const float2*)&gb[j * kTokPerTile * NT * 2];
+            }
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
               int acc[4];
-              const uint2 bf0 = xb[((j * 2 + 0) * NT + nt) * 32], bf1 = xb[((j * 2 + 1) * NT + nt) * 32];
-              mma_u8s8_z(acc, a0[0], a1[0], a2[0], a3[0], bf0.x, bf0.y);
-              mma_u8s8(acc, a0[1], a1[1], a2[1], a3[1], bf1.x, bf1.y);
-              const float2 gs = *(const float2*)&gb[(j * NT + nt) * kTokPerTile * 2];
+              const uint4 bf = xb[(j * NT + nt) * 32];
+              mma_u8s8_z(acc, a0[0], a1[0], a2[0], a3[0], bf.x, bf.y);
+              mma_u8s8(acc, a0[1], a1[1], a2[1], a3[1], bf.z, bf.w);
+              const float2 gs = gsn[nt];
               const float f_lo = (float)(acc[0] * 128 + acc[1]), f_hi = (float)(acc[2] * 128 + acc[3]);
               tot[nt][0] = fmaf(s_lo * gs.x, f_lo, fmaf(b_lo, gs.y, tot[nt][0]));
               tot[nt][1] = fmaf(s_hi * gs.x, f_hi, fmaf(b_hi, gs.y, tot[nt][1]));
