@@ -83,13 +83,6 @@ __device__ __forceinline__ void mma_u8s8_z(int (&d)[4], uint32_t a0, uint32_t a1
 }
 template <int BITS> __device__ __forceinline__ int swz(int row) { return BITS == 4 ? 2 * (row & 3) : 4 * (row & 1); }
 template <int BITS> __device__ __forceinline__ int kslot8(int h, int i) { return BITS == 4 ? 2 * i + h : 4 * h + i; }
-__device__ __forceinline__ int fix15(float x, float up) {
-  const int v = __float_as_int(fmaf(x, up, 12582912.f)) - 0x4B400000;
-  return v > 16383 ? 16383 : v;
-}
-__device__ __forceinline__ uint32_t plane_byte(int v, int plane) {
-  return plane == 0 ? (uint32_t)((v >> 7) & 0xFF) : (uint32_t)(v & 127);
-}
 __device__ __forceinline__ long long load_index(const void* p, int is64, int64_t i) {
   return is64 ? ((const long long*)p)[i] : (long long)((const uint32_t*)p)[i];
 }
@@ -177,7 +170,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
     const int row = (lane >> 3) + 4 * r;
     wdst[r] = row * 128 + ((chunk ^ swz<BITS>(row)) << 4);
   }
-  const uint32_t sbdst = kStageW + (lane >> 4) * 128 + (lane & 15) * 8;
+  const uint32_t sbdst = kStageW + (lane & 15) * 16 + (lane >> 4) * 8;   // per row: scales | biases
   int frag_off[U];
 #pragma unroll
   for (int j = 0; j < U; ++j) {
@@ -237,12 +230,13 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
     const int my_tiles = first < ntb ? (ksplit == 1 ? (ntb - first + kWarps - 1) / kWarps : 1) : 0;
     const int nu = (ut - kp + ksplit - 1) / ksplit;   // units of one tile handled by this warp
     const int total = my_tiles * nu;
-    int issued = 0, consumed = 0, ptile = 0, pu = kp;  // producer position: (tile index, unit)
+    int issued = 0, ptile = 0, pu = kp;  // producer position: (tile index, unit)
+    uint32_t p_off = 0, c_off = 0;       // byte offsets of the stages the next item is copied to / read from
     // per-lane source pointers of the producer's current tile (recomputed when the tile changes)
     const unsigned char* wsrc[4] = {nullptr, nullptr, nullptr, nullptr};
     const uint16_t* sbsrc = nullptr;
     int cached_tile = -1;
-    auto issue = [&](int stage) {
+    auto issue = [&]() {
       if (ptile != cached_tile) {
         cached_tile = ptile;
         const int j = first + ptile * kWarps;
@@ -259,7 +253,8 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
         n = n < p.N ? n : p.N - 1;
         sbsrc = ((lane >> 4) ? (sg ? bexp1 : bexp0) : (sg ? sexp1 : sexp0)) + (int64_t)n * lds;
       }
-      const uint32_t st = my_ring + stage * kStageBytes;
+      const uint32_t st = my_ring + p_off;
+      p_off = p_off + kStageBytes == kStages * kStageBytes ? 0u : p_off + kStageBytes;
       const int woff = pu * 128;
 #pragma unroll
       for (int r = 0; r < 4; ++r) cp_async16(st + wdst[r], wsrc[r] + woff);
@@ -271,7 +266,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
     };
 #pragma unroll
     for (int i = 0; i < kStages - 1; ++i) {
-      if (issued < total) issue(issued % kStages);
+      if (issued < total) issue();
       cp_async_commit();
       ++issued;
     }
@@ -302,66 +297,86 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
     }
     __syncthreads();
     // ---- stage the rows' activations as s8 planes in B-fragment order (one thread: 8 K values) ----
+    // v = rn(x * up) is one FMA onto 1.5 * 2^23 (the low 16 bits of the sum's bit pattern are v in two's
+    // complement); the two planes are cut out of pairs of values packed into one word.
+    // thread -> (row of the pass, 8-value chunk); K <= 4096, so one pass covers every chunk of a row
+    const int st_cpt = p.K >> 3;
+    const int st_rpp = kThreads / st_cpt;               // rows converted per pass
+    const int st_mr = tid / st_cpt, st_cr = tid - st_mr * st_cpt;
     for (int sg = 0; sg < (nt1 > 0 ? 2 : 1); ++sg) {
-      const int cpt = p.K >> 3;
-      const int items = (sg ? nte1 : nte0) * 4 * cpt;
+      const int nrows = (sg ? nte1 : nte0) * 4;
       uint2* xf = xfrag + sg * xf_stride;
       float* gsb = gsc + sg * gs_stride;
       const long long* xi_s = s_xi + sg * kRowsPerSweep;
-      for (int base = 0; base < items; base += kThreads) {
-        const int it = base + tid;
-        const bool ok = it < items;
-        const int m = ok ? it / cpt : 0;
-        const int c = ok ? it - m * cpt : 0;
-        float f[8];
-        const long long xi = ok ? xi_s[m] : -1;
-        if (xi >= 0) {
-          const int64_t off = xi * p.xstride + (int64_t)c * 8;
+      constexpr int PF = 2;   // rows fetched per thread before any is converted
+      for (int mb = 0; mb < nrows; mb += PF * st_rpp) {
+        uint4 raw[PF][2];
+        bool okq[PF];
+#pragma unroll
+        for (int q = 0; q < PF; ++q) {
+          const int m = mb + q * st_rpp + st_mr;
+          okq[q] = st_mr < st_rpp && m < nrows;
+          raw[q][0] = raw[q][1] = make_uint4(0u, 0u, 0u, 0u);
+          const long long xi = okq[q] ? xi_s[m] : -1;
+          if (xi >= 0) {
+            const int64_t off = xi * p.xstride + (int64_t)st_cr * 8;
+            if (!p.x_f32) {
+              raw[q][0] = *(const uint4*)((const uint16_t*)p.x + off);
+            } else {
+              raw[q][0] = *(const uint4*)((const float*)p.x + off);
+              raw[q][1] = *(const uint4*)((const float*)p.x + off + 4);
+            }
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < PF; ++q) {
+          if (mb + q * st_rpp >= nrows) continue;
+          const int m = mb + q * st_rpp + st_mr, c = st_cr;
+          float f[8];
+          const uint4 a = raw[q][0], b2 = raw[q][1];
           if (!p.x_f32) {
-            const uint4 a = *(const uint4*)((const uint16_t*)p.x + off);
             f[0] = bf16lo(a.x); f[1] = bf16hi(a.x); f[2] = bf16lo(a.y); f[3] = bf16hi(a.y);
             f[4] = bf16lo(a.z); f[5] = bf16hi(a.z); f[6] = bf16lo(a.w); f[7] = bf16hi(a.w);
           } else {
-            const float4 a = *(const float4*)((const float*)p.x + off), b2 = *(const float4*)((const float*)p.x + off + 4);
-            f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b2.x; f[5] = b2.y; f[6] = b2.z; f[7] = b2.w;
+            f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
+            f[4] = __uint_as_float(b2.x); f[5] = __uint_as_float(b2.y); f[6] = __uint_as_float(b2.z); f[7] = __uint_as_float(b2.w);
           }
-        } else {
+          float mx = 0.f;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) f[j] = 0.f;
-        }
-        float mx = 0.f;
+          for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(f[j]));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+          int ex = (int)((__float_as_uint(mx) >> 23) & 0xFF) - 127 + 1;  // mx < 2^ex
+          ex = ex < -100 ? -100 : (ex > 110 ? 110 : ex);
+          const float up = __uint_as_float((uint32_t)(127 + 14 - ex) << 23);
+          const float down = __uint_as_float((uint32_t)(127 + ex - 14) << 23);
+          uint32_t w[8], isum = 0;   // bit patterns 0x4B400000 + v
 #pragma unroll
-        for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(f[j]));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-        int ex = (int)((__float_as_uint(mx) >> 23) & 0xFF) - 127 + 1;  // mx < 2^ex
-        ex = ex < -100 ? -100 : (ex > 110 ? 110 : ex);
-        const float up = __uint_as_float((uint32_t)(127 + 14 - ex) << 23);
-        const float down = __uint_as_float((uint32_t)(127 + ex - 14) << 23);
-        int v[8], sum = 0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { v[j] = fix15(f[j], up); sum += v[j]; }
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-        if (ok) {
+          for (int j = 0; j < 8; ++j) {
+            w[j] = __float_as_uint(fminf(fmaf(f[j], up, 12582912.f), 12599295.f));   // v <= 16383 (fp32 inputs may round up to 2^14)
+            isum += w[j];
+          }
+          isum += __shfl_xor_sync(0xffffffffu, isum, 1);
+          isum += __shfl_xor_sync(0xffffffffu, isum, 2);
+          isum += __shfl_xor_sync(0xffffffffu, isum, 4);
+          const int sum = (int)(isum - 0xD0000000u);   // 64 values: 64 * 0x4B400000 mod 2^32
+          if (!okq[q]) continue;
           const int gi = c >> 3, tt = (c >> 1) & 3, jm = c & 1;
           const int nt = m >> 2, ml = m & 3;
-          if ((c & 7) == 0) {
-            float* gs = gsb + ((gi * NT + nt) * 4 + ml) * 2;
-            gs[0] = down;
-            gs[1] = down * (float)sum;
-          }
+          if ((c & 7) == 0) *(float2*)&gsb[((gi * 4 + ml) * NT + nt) * 2] = make_float2(down, down * (float)sum);
+          uint32_t o[2][2];   // [plane][operand register]
 #pragma unroll
-          for (int pl = 0; pl < 2; ++pl) {
-            uint2 o;
-            o.x = plane_byte(v[kslot8<BITS>(0, 0)], pl) | (plane_byte(v[kslot8<BITS>(0, 1)], pl) << 8) |
-                  (plane_byte(v[kslot8<BITS>(0, 2)], pl) << 16) | (plane_byte(v[kslot8<BITS>(0, 3)], pl) << 24);
-            o.y = plane_byte(v[kslot8<BITS>(1, 0)], pl) | (plane_byte(v[kslot8<BITS>(1, 1)], pl) << 8) |
-                  (plane_byte(v[kslot8<BITS>(1, 2)], pl) << 16) | (plane_byte(v[kslot8<BITS>(1, 3)], pl) << 24);
-            xf[((gi * 2 + jm) * NT + nt) * 32 + (2 * ml + pl) * 4 + tt] = o;
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t p0 = __byte_perm(w[kslot8<BITS>(h, 0)], w[kslot8<BITS>(h, 1)], 0x5410);   // two 16-bit values
+            const uint32_t p1 = __byte_perm(w[kslot8<BITS>(h, 2)], w[kslot8<BITS>(h, 3)], 0x5410);
+            o[0][h] = __byte_perm((p0 >> 7) & 0x00FF00FFu, (p1 >> 7) & 0x00FF00FFu, 0x6420);   // (v >> 7) & 0xFF
+            o[1][h] = __byte_perm(p0 & 0x007F007Fu, p1 & 0x007F007Fu, 0x6420);                 // v & 127
           }
+          // 16 bytes per (group, tile, column, lane quarter): the operands of both MMAs of the group
+          uint2* d = xf + (((gi * NT + nt) * 32 + 2 * ml * 4 + tt) * 2 + jm);
+          d[0] = make_uint2(o[0][0], o[0][1]);
+          d[8] = make_uint2(o[1][0], o[1][1]);
         }
       }
     }
@@ -403,28 +418,22 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
         auto unit = [&](auto nte_c, const unsigned char* st, int u) {
           constexpr int NTE = decltype(nte_c)::value;
           // fragments and group scales of this unit's U groups: every offset below is a compile-time constant
-          const uint2* xb = xf + (size_t)(u * U * 2 * NT) * 32 + lane;
-          const float* gb = gsb + (size_t)(u * U * NT * 4 + t) * 2;
+          const uint4* xb = (const uint4*)xf + (size_t)(u * U * NT) * 32 + lane;
+          const float* gb = gsb + (size_t)((u * U * 4 + t) * NT) * 2;
           uint32_t sl[2], sh[2], bl[2], bh[2];
           {
-            const unsigned char* sb = st + kStageW;
+            const uint4 lo = *(const uint4*)(st + kStageW + g * 16), hi = *(const uint4*)(st + kStageW + (g + 8) * 16);
             if (BITS == 4 && p.gshift == 0) {
-              const uint2 a = *(const uint2*)(sb + g * 8), c = *(const uint2*)(sb + (g + 8) * 8);
-              const uint2 d = *(const uint2*)(sb + 128 + g * 8), e2 = *(const uint2*)(sb + 128 + (g + 8) * 8);
-              sl[0] = a.x; sl[1] = a.y; sh[0] = c.x; sh[1] = c.y;
-              bl[0] = d.x; bl[1] = d.y; bh[0] = e2.x; bh[1] = e2.y;
+              sl[0] = lo.x; sl[1] = lo.y; sh[0] = hi.x; sh[1] = hi.y;
+              bl[0] = lo.z; bl[1] = lo.w; bh[0] = hi.z; bh[1] = hi.w;
+            } else if (BITS == 4) {  // group size 128: each value serves two 64-wide groups
+              sl[0] = __byte_perm(lo.x, lo.x, 0x1010); sl[1] = __byte_perm(lo.x, lo.x, 0x3232);
+              sh[0] = __byte_perm(hi.x, hi.x, 0x1010); sh[1] = __byte_perm(hi.x, hi.x, 0x3232);
+              bl[0] = __byte_perm(lo.z, lo.z, 0x1010); bl[1] = __byte_perm(lo.z, lo.z, 0x3232);
+              bh[0] = __byte_perm(hi.z, hi.z, 0x1010); bh[1] = __byte_perm(hi.z, hi.z, 0x3232);
             } else {
-              const uint32_t a = *(const uint32_t*)(sb + g * 8), c = *(const uint32_t*)(sb + (g + 8) * 8);
-              const uint32_t d = *(const uint32_t*)(sb + 128 + g * 8), e2 = *(const uint32_t*)(sb + 128 + (g + 8) * 8);
-              if (BITS == 4) {  // group size 128: each value serves two 64-wide groups
-                sl[0] = __byte_perm(a, a, 0x1010); sl[1] = __byte_perm(a, a, 0x3232);
-                sh[0] = __byte_perm(c, c, 0x1010); sh[1] = __byte_perm(c, c, 0x3232);
-                bl[0] = __byte_perm(d, d, 0x1010); bl[1] = __byte_perm(d, d, 0x3232);
-                bh[0] = __byte_perm(e2, e2, 0x1010); bh[1] = __byte_perm(e2, e2, 0x3232);
-              } else {
-                sl[0] = a; sh[0] = c; bl[0] = d; bh[0] = e2;
-                sl[1] = sh[1] = bl[1] = bh[1] = 0;
-              }
+              sl[0] = lo.x; sh[0] = hi.x; bl[0] = lo.z; bh[0] = hi.z;
+              sl[1] = sh[1] = bl[1] = bh[1] = 0;
             }
           }
 #pragma unroll
@@ -447,13 +456,20 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
             const float s_hi = (jj & 1) ? bf16hi(sh[jj >> 1]) : bf16lo(sh[jj >> 1]);
             const float b_lo = (jj & 1) ? bf16hi(bl[jj >> 1]) : bf16lo(bl[jj >> 1]);
             const float b_hi = (jj & 1) ? bf16hi(bh[jj >> 1]) : bf16lo(bh[jj >> 1]);
+            float2 gsn[NT];   // this lane's row of every n8 tile
+            if constexpr (NTE == 2) {
+              const float4 v = *(const float4*)&gb[jj * 4 * NT * 2];
+              gsn[0] = make_float2(v.x, v.y); gsn[1] = make_float2(v.z, v.w);
+            } else {
+              gsn[0] = *(const float2*)&gb[jj * 4 * NT * 2];
+            }
 #pragma unroll
             for (int nt = 0; nt < NTE; ++nt) {
               int acc[4];
-              const uint2 bf0 = xb[((jj * 2 + 0) * NT + nt) * 32], bf1 = xb[((jj * 2 + 1) * NT + nt) * 32];
-              mma_u8s8_z(acc, a0[0], a1[0], a2[0], a3[0], bf0.x, bf0.y);
-              mma_u8s8(acc, a0[1], a1[1], a2[1], a3[1], bf1.x, bf1.y);
-              const float2 gs = *(const float2*)&gb[(jj * NT + nt) * 8];
+              const uint4 bf = xb[(jj * NT + nt) * 32];
+              mma_u8s8_z(acc, a0[0], a1[0], a2[0], a3[0], bf.x, bf.y);
+              mma_u8s8(acc, a0[1], a1[1], a2[1], a3[1], bf.z, bf.w);
+              const float2 gs = gsn[nt];
               const float f_lo = (float)(acc[0] * 128 + acc[1]), f_hi = (float)(acc[2] * 128 + acc[3]);
               tot[nt][0] = fmaf(s_lo * gs.x, f_lo, fmaf(b_lo, gs.y, tot[nt][0]));
               tot[nt][1] = fmaf(s_hi * gs.x, f_hi, fmaf(b_hi, gs.y, tot[nt][1]));
@@ -462,13 +478,13 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
         };
         auto sweep_k = [&](auto nte_c) {
           for (int u = kp; u < ut; u += ksplit) {
-            if (issued < total) issue(issued % kStages);
+            if (issued < total) issue();
             cp_async_commit();
             ++issued;
             cp_async_wait<kStages - 1>();
             __syncwarp();
-            const unsigned char* st = my_ring_p + (consumed % kStages) * kStageBytes;
-            ++consumed;
+            const unsigned char* st = my_ring_p + c_off;
+            c_off = c_off + kStageBytes == kStages * kStageBytes ? 0u : c_off + kStageBytes;
             unit(nte_c, st, u);
             __syncwarp();
           }

@@ -62,7 +62,8 @@ constexpr int kMaxMat = 4;          // weight matrices served by one launch (sam
 
 // Optional timeline of one launch (a build with -DQB_STREAM_PROFILE; not part of the library build):
 // nanosecond timestamps of thread 0 of every CTA at the phase boundaries
-// (0 start, 1 first ring stages issued, 2 previous grid complete, 3 activations staged, 4 end).
+// (0 start, 5 shared memory carved up, 6 producer set up, 7 first stage issued, 1 ring filled,
+// 2 previous grid complete, 3 activations staged, 4 end).
 #ifdef QB_STREAM_PROFILE
 __device__ unsigned long long g_stream_tl[512][8];
 __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
@@ -157,16 +158,6 @@ template <int BITS> __device__ __forceinline__ int kslot8(int h, int i) {
   return BITS == 4 ? 2 * i + h : 4 * h + i;
 }
 
-// Fixed-point value of one activation: v = clamp(rn(x * up)), |v| < 2^14.
-// Round-to-nearest through the fp32 magic number 1.5*2^23 (one FMA, one integer subtract).
-__device__ __forceinline__ int fix15(float x, float up) {
-  const int v = __float_as_int(fmaf(x, up, 12582912.f)) - 0x4B400000;
-  return v > 16383 ? 16383 : v;  // fp32 inputs may round up to 2^14; -2^14 still fits the high plane
-}
-__device__ __forceinline__ uint32_t plane_byte(int v, int plane) {
-  return plane == 0 ? (uint32_t)((v >> 7) & 0xFF) : (uint32_t)(v & 127);
-}
-
 // Kernel parameters are indexed with constant subscripts only (a dynamic subscript would force a
 // local-memory copy of the parameter block).
 #define QB_SEL4(arr, i) ((i) == 0 ? (arr)[0] : ((i) == 1 ? (arr)[1] : ((i) == 2 ? (arr)[2] : (arr)[3])))
@@ -218,6 +209,7 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
   const int k_cta = split ? (p.K - k_lo < p.upc * CK ? (p.K - k_lo > 0 ? p.K - k_lo : 0) : p.upc * CK) : p.K;
   const int ut = k_cta / CK, upk = split ? (ut > 0 ? ut : 1) : kc / CK;
 
+  TL(5);
   // ---- producer: this warp's stream of (pass, local tile, K unit) items ----
   // A lane copies 16 bytes of four rows of a stage (rows lane/8 + 4r) and one scale or bias entry.  The source
   // pointers move by constants from unit to unit and from a tile to the group's next tile; only a change of
@@ -301,10 +293,12 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
   }
 
   setup();
+  TL(6);
 #pragma unroll
   for (int i = 0; i < kStages - 1; ++i) {
     if (prod_valid()) issue();
     cp_async_commit();
+    if (i == 0) TL(7);
   }
 
   // Let the next grid in the stream begin launching, then wait for the previous grid to complete (and
