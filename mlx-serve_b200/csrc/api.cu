@@ -296,8 +296,8 @@ static int prepare_qmm(qb200_tensor* res, const qb200_tensor* x, const qb200_ten
 }
 
 // Tokens from which the tensor-core kernel (split-K over a cluster when the problem has few tiles) beats
-// re-streaming the weights once per 8 tokens: measured break-even on the C2 layer is ~30 tokens.
-constexpr int64_t kTcMinTokens = 32;
+// re-streaming the weights once per 8 tokens: measured on the C2 layer, four 8-token passes (32 tokens) still win.
+constexpr int64_t kTcMinTokens = 33;
 
 static cudaError_t dispatch_qmm(const QmmArgs& a, cudaStream_t s) {
   // decode widths stream the weights once per 8 tokens through the integer-MMA kernel; wider inputs go to tcgen05

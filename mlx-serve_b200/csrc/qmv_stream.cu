@@ -53,8 +53,8 @@ constexpr int kStageW = 2048;       // 16 rows x 128 B of packed codes
 constexpr int kStageBytes = kStageW + 256;  // + 16 rows x (scales, biases)
 constexpr int kTokPerTile = 4;      // tokens per n8 tile (two planes each)
 constexpr int kMaxTok = 8;          // tokens per launch (two n8 tiles of 4 tokens x 2 planes); wider M in 8-token blocks:
-                                    // a 16-token instantiation needed four staging passes over K = 4096 and was
-                                    // measured slower than two 8-token launches
+                                    // a 16-token instantiation (K staged in two passes of 2048, partial sums kept in
+                                    // shared memory between them) was measured 15% slower than two 8-token launches
 
 __host__ __device__ constexpr int kc_for(int nt) { return nt <= 2 ? 4096 : 1024; }
 
@@ -63,9 +63,9 @@ constexpr int kMaxMat = 4;          // weight matrices served by one launch (sam
 // Optional timeline of one launch (a build with -DQB_STREAM_PROFILE; not part of the library build):
 // nanosecond timestamps of thread 0 of every CTA at the phase boundaries
 // (0 start, 5 shared memory carved up, 6 producer set up, 7 first stage issued, 1 ring filled,
-// 2 previous grid complete, 3 activations staged, 4 end).
+// 2 previous grid complete, 8 activations converted, 3 staged for every CTA of the cluster, 4 end).
 #ifdef QB_STREAM_PROFILE
-__device__ unsigned long long g_stream_tl[512][8];
+__device__ unsigned long long g_stream_tl[512][12];
 __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
 #define TL(i) do { if (threadIdx.x == 0 && blockIdx.x < 512) g_stream_tl[blockIdx.x][i] = gtime(); } while (0)
 #else
@@ -129,7 +129,7 @@ __device__ __forceinline__ void cluster_sync_all() {
 // D(16x8,s32) += A(16x32,u8,row) * B(32x8,s8,col)
 __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -138,7 +138,7 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, 
 // The same with a zero C operand (no accumulator initialisation in registers).
 __device__ __forceinline__ void mma_u8s8_z(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                            uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
       : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
@@ -467,6 +467,7 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
       };
       if (p.x_f32) stage_all(std::true_type{}); else stage_all(std::false_type{});
     }
+    if (pass == 0) TL(8);
     if constexpr (M1) __syncthreads(); else cluster_sync_all();
     if (pass == 0) TL(3);
 
@@ -647,7 +648,7 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
 
 #ifdef QB_STREAM_PROFILE
 extern "C" __attribute__((visibility("default"))) void qb200_debug_stream_timeline(unsigned long long* out) {
-  cudaMemcpyFromSymbol(out, g_stream_tl, sizeof(unsigned long long) * 512 * 8);
+  cudaMemcpyFromSymbol(out, g_stream_tl, sizeof(unsigned long long) * 512 * 12);
 }
 #endif
 

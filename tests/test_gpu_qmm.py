@@ -58,6 +58,17 @@ def test_config2_llama_projections(proj, M):
     _run(rand_bf16(rng, (M, K)), q, s, b, 64, 4)
 
 
+@pytest.mark.parametrize("bits,gs", [(4, 64), (8, 64), (4, 128)])
+@pytest.mark.parametrize("M,N,K", [(16, 4096, 4096), (9, 1024, 4096), (13, 1000, 2048), (16, 512, 14336), (24, 2048, 1024),
+                                   (31, 640, 4096), (16, 14336, 4096), (12, 256, 256)])
+def test_nine_to_thirty_two_tokens(bits, gs, M, N, K):
+    """9..32 tokens: the streaming kernel re-streams the weights once per block of 8 tokens (ragged last block, K staged
+    in passes or cut over a cluster for long K)."""
+    rng = np.random.default_rng(M * 7 + N + K + bits)
+    q, s, b = make_weight(rng, (N, K), gs, bits)
+    _run(rand_bf16(rng, (M, K)), q, s, b, gs, bits)
+
+
 def test_config2_m128():
     rng = np.random.default_rng(0xC2 + 128)
     q, s, b = make_weight(rng, (4096, 4096), 64, 4)
