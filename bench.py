@@ -521,9 +521,9 @@ def main():
 
     if rank == 0:
         peak, which = peaks()
-        # the streaming kernel serves 8 tokens per launch (fused q/k/v and gate/up: 4 launches per layer); from
+        # the streaming kernel serves 8 tokens per launch (fused q/k/v and gate/up: 4 launches per layer); above
         # 32 tokens the tensor-core kernel takes one launch per projection
-        launches_per_layer = 7 if M >= 32 else (7 if args.no_batch else 4) * ((M + 7) // 8)
+        launches_per_layer = 7 if M > 32 else (7 if args.no_batch else 4) * ((M + 7) // 8)
         achieved = L * layer_bytes(M) / (ms_step * 1e-3) / 1e9
         out = {
             "metric": "decode_tokens_per_s_llama3_8b_layer_q4g64", "value": value, "unit": "tokens/s",

@@ -200,7 +200,7 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
   float* xred = (float*)sp;    // K-split mode (npass == 1): [2][ksplit - 1][kGroups][256] partial sums from the peers
   // A CTA's shared memory may only be written by its cluster peers once it is running: arrive now, and
   // wait for every peer's arrival just before the first remote store.
-  if constexpr (!M1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  if constexpr (!M1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
   const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring + (size_t)warp * kStages * kStageBytes);
   const unsigned char* my_ring_p = ring + (size_t)warp * kStages * kStageBytes;
