@@ -50,7 +50,9 @@ namespace {
 
 constexpr int BM = 256, BN_MAX = 128, BK = 64;
 // ring depth: the grouped (routed-expert) form gives one stage's room to its row-offset tables
-__host__ __device__ constexpr int stages_of(bool grouped, bool wide = false) { return (grouped || wide) ? 3 : 4; }
+// (few-token form, at most 128 tokens: stages hold one 128-row box of x, so six of them fit where four did --
+// the k-loop is bound by the round trip of a stage there, not by any unit's throughput)
+__host__ __device__ constexpr int stages_of(bool grouped, bool wide = false, bool half = false) { return half ? 6 : ((grouped || wide) ? 3 : 4); }
 // The wide form multiplies one B tile of up to 208 weight rows per stage against both token halves: fewer
 // operand bytes per MAC through shared memory (the resource that bounds this kernel), at the price of a
 // single accumulator set in tensor memory (2 x 256 columns), i.e. an epilogue that is not overlapped.
@@ -185,16 +187,24 @@ __device__ __forceinline__ uint32_t make_idesc(int bn) {
   d |= (uint32_t)(128 >> 4) << 24;
   return d;
 }
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+// Both are executed by every lane of the issuing warp with the same operands (so that the compiler can keep
+// them in uniform registers and the loop around them stays convergent); only the lane with `issue` set
+// issues the instruction.
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum, uint32_t issue) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
+      "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum), "r"(0u)
+      "setp.ne.b32 q, %6, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum), "r"(0u), "r"(issue)
       : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+__device__ __forceinline__ void umma_commit(uint64_t* bar, uint32_t issue) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(smem_u32(bar)), "r"(issue) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -260,17 +270,18 @@ __device__ __forceinline__ void dequant_half(const uint32_t* codes, uint32_t sb2
   }
 }
 
-template <int BITS, bool GROUPED, bool WIDE>
+template <int BITS, bool GROUPED, bool WIDE, bool HALF = false>
 __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, TcK p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // 1024-byte alignment for the swizzled tiles.  The wide form has no room for the slack: the kernel has no
   // static shared memory, so its dynamic window starts aligned; that is verified below.
   unsigned char* smem = WIDE ? smem_raw : (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  constexpr int STAGES = stages_of(GROUPED, WIDE);
+  constexpr int STAGES = stages_of(GROUPED, WIDE, HALF);
+  constexpr int A_STAGE = HALF ? A_STAGE_BYTES / 2 : A_STAGE_BYTES;   // HALF: no tile has a second token half
   constexpr int B_STAGE = bn_max_of(WIDE, GROUPED) * BK * 2, RAW_B = bn_max_of(WIDE, GROUPED) * 128;
   constexpr int HALF_COLS = WIDE ? 256 : 128;      // tensor-memory columns between the two token halves
   unsigned char* a_tiles = smem;                                   // [STAGES][2][128 x 64 bf16]
-  unsigned char* b_tiles = smem + STAGES * A_STAGE_BYTES;          // [STAGES][BN x 64 bf16]
+  unsigned char* b_tiles = smem + STAGES * A_STAGE;                // [STAGES][BN x 64 bf16]
   unsigned char* raw = b_tiles + STAGES * B_STAGE;                 // [2][BN x 128 B of packed codes]
   uint64_t* bars = (uint64_t*)(raw + 2 * RAW_B);
   uint64_t* full_a = bars, *full_b = bars + STAGES, *empty = bars + 2 * STAGES;
@@ -387,7 +398,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
           const int st = it % STAGES;
           if (it >= STAGES && !mbar_wait_relaxed(&empty[st], ((it / STAGES) - 1) & 1)) { fail = 3; break; }
           mbar_expect_tx(&full_a[st], two ? A_STAGE_BYTES : A_STAGE_BYTES / 2);
-          const uint32_t dst = smem_u32(a_tiles + st * A_STAGE_BYTES);
+          const uint32_t dst = smem_u32(a_tiles + st * A_STAGE);
           tma_load_2d(dst, &xmap, &full_a[st], (kb0 + kb) * BK, m0);
           if (two) tma_load_2d(dst + 128 * BK * 2, &xmap, &full_a[st], (kb0 + kb) * BK, m0 + 128);
         }
@@ -411,8 +422,9 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       if (fail) { s_fail = fail; atomicExch(&g_tc_error, fail); }
     }
   } else if (warp == kMmaWarp) {
-    if (lane == 0) {
-      // ---------------- MMA issuer (one thread) ----------------
+    {
+      // ---------------- MMA issuer (the whole warp walks the loop, lane 0 issues) ----------------
+      const uint32_t lead = lane == 0 ? 1u : 0u;
       const uint32_t idesc = make_idesc(BN);
       const uint64_t adesc0 = make_desc(smem_u32(a_tiles)), bdesc0 = make_desc(smem_u32(b_tiles));
       int it = 0, fail = 0, ti = 0;
@@ -438,7 +450,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           // descriptors of the stage: the start-address field counts 16-byte units, so a K step of
           // 16 values (32 bytes) adds 2 and the second 128-row box of x adds 16 KiB / 16
-          const uint64_t ad0 = adesc0 + (uint64_t)(st * (A_STAGE_BYTES >> 4)), bd0 = bdesc0 + (uint64_t)(st * (B_STAGE >> 4));
+          const uint64_t ad0 = adesc0 + (uint64_t)(st * (A_STAGE >> 4)), bd0 = bdesc0 + (uint64_t)(st * (B_STAGE >> 4));
           // A tile without a second token half keeps two partial sums over K, in the columns the second
           // half would use (odd K steps go there; the epilogue adds them): consecutive MMAs into ONE
           // accumulator wait ~100 cycles on each other, two independent chains hide that.
@@ -446,21 +458,21 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
           for (int k16 = 0; k16 < BK / 16; ++k16) {
             if (two_halves) {
               const uint32_t accum = (kb > 0 || k16 > 0) ? 1u : 0u;
-              umma(d0, ad0 + 2 * k16, bd0 + 2 * k16, idesc, accum);
-              umma(d0 + HALF_COLS, ad0 + ((128 * BK * 2) >> 4) + 2 * k16, bd0 + 2 * k16, idesc, accum);
+              umma(d0, ad0 + 2 * k16, bd0 + 2 * k16, idesc, accum, lead);
+              umma(d0 + HALF_COLS, ad0 + ((128 * BK * 2) >> 4) + 2 * k16, bd0 + 2 * k16, idesc, accum, lead);
             } else {
               const uint32_t accum = (kb > 0 || k16 > 1) ? 1u : 0u;
-              umma(d0 + (k16 & 1) * HALF_COLS, ad0 + 2 * k16, bd0 + 2 * k16, idesc, accum);
+              umma(d0 + (k16 & 1) * HALF_COLS, ad0 + 2 * k16, bd0 + 2 * k16, idesc, accum, lead);
             }
           }
-          umma_commit(&empty[st]);  // frees this stage (A and B) once the MMAs above have read it
+          umma_commit(&empty[st], lead);  // frees this stage (A and B) once the MMAs above have read it
           PROF_ADD(3);
         }
         if (fail) break;
-        umma_commit(&acc_full[buf]);
+        umma_commit(&acc_full[buf], lead);
       }
-      PROF_OUT(0);
-      if (fail) { s_fail = fail; atomicExch(&g_tc_error, fail); }
+      if (lane == 0) PROF_OUT(0);
+      if (fail && lane == 0) { s_fail = fail; atomicExch(&g_tc_error, fail); }
     }
   } else if (warp < kDequantWarps) {
     // ---------------- dequant producers: two threads per weight row, two groups ----------------
@@ -724,13 +736,14 @@ EncodeFn get_encode() {
   return fn;
 }
 
-constexpr size_t smem_bytes_tc(bool grouped, bool wide) {
-  return (size_t)stages_of(grouped, wide) * (A_STAGE_BYTES + bn_max_of(wide, grouped) * BK * 2) + (size_t)2 * bn_max_of(wide, grouped) * 128 +
-         (3 * stages_of(grouped, wide) + 8) * 8 + 16 + (grouped ? (size_t)2 * (kMaxGroupExperts + 1) * 4 : 0) +
+constexpr size_t smem_bytes_tc(bool grouped, bool wide, bool half = false) {
+  return (size_t)stages_of(grouped, wide, half) * ((half ? A_STAGE_BYTES / 2 : A_STAGE_BYTES) + bn_max_of(wide, grouped) * BK * 2) +
+         (size_t)2 * bn_max_of(wide, grouped) * 128 + (3 * stages_of(grouped, wide, half) + 8) * 8 + 16 + (grouped ? (size_t)2 * (kMaxGroupExperts + 1) * 4 : 0) +
          (wide ? 0 : 1024);
 }
 static_assert(smem_bytes_tc(false, true) <= 227 * 1024 && smem_bytes_tc(true, true) <= 227 * 1024, "wide form does not fit in shared memory");
 static_assert(smem_bytes_tc(false, false) <= 227 * 1024 && smem_bytes_tc(true, false) <= 227 * 1024, "shared memory");
+static_assert(smem_bytes_tc(false, false, true) <= 227 * 1024, "few-token form does not fit in shared memory");
 
 constexpr size_t STAGES_DENSE_BYTES = (size_t)stages_of(false) * (A_STAGE_BYTES + B_STAGE_BYTES) + 2 * RAW_BYTES;  // pipeline buffers reused by the exchange
 
@@ -790,15 +803,15 @@ struct TcLaunch {
   const void* rhs; int rhs_i64; int E;   // grouped form only
 };
 
-template <int BITS, bool GROUPED, bool WIDE>
+template <int BITS, bool GROUPED, bool WIDE, bool HALF = false>
 cudaError_t launch_tc_inst(const CUtensorMap& xmap, const CUtensorMap& wmap, const TcK& p, dim3 grid, cudaStream_t st,
                            int cluster = 1) {
   static bool done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  constexpr size_t smem = smem_bytes_tc(GROUPED, WIDE);
+  constexpr size_t smem = smem_bytes_tc(GROUPED, WIDE, HALF);
   if (dev < 0 || dev >= 64 || !done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(qmm_tc_kernel<BITS, GROUPED, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(qmm_tc_kernel<BITS, GROUPED, WIDE, HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) done[dev] = true;
   }
@@ -813,9 +826,9 @@ cudaError_t launch_tc_inst(const CUtensorMap& xmap, const CUtensorMap& wmap, con
     attr[0].val.clusterDim.x = cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, qmm_tc_kernel<BITS, GROUPED, WIDE>, xmap, wmap, p);
+    return cudaLaunchKernelEx(&cfg, qmm_tc_kernel<BITS, GROUPED, WIDE, HALF>, xmap, wmap, p);
   }
-  qmm_tc_kernel<BITS, GROUPED, WIDE><<<grid, kThreads, smem, st>>>(xmap, wmap, p);
+  qmm_tc_kernel<BITS, GROUPED, WIDE, HALF><<<grid, kThreads, smem, st>>>(xmap, wmap, p);
   return cudaGetLastError();
 }
 
@@ -886,6 +899,7 @@ cudaError_t launch_tc(const TcLaunch& a, bool grouped, cudaStream_t st) {
   // the time is the number of k-blocks a CTA walks (plus ~6 k-block times for the exchange), whatever the tile
   // width, so K is cut in 4 or 2 and the tile is made just wide enough for tiles x ranks to fit the SMs.
   p.ksplit = 1;
+  const bool half = !grouped && !wide && a.M <= 128;   // no tile has a second token half: six stages of one x box
   if (!grouped && !wide && a.M <= 256) {
     const int gshift = a.gs == 128 ? 1 : 0;
     const int nkb_all = (int)(a.K / BK);
@@ -926,12 +940,15 @@ cudaError_t launch_tc(const TcLaunch& a, bool grouped, cudaStream_t st) {
   dim3 grid((unsigned)((!grouped && p.ntiles < nsm) ? p.ntiles : nsm), 1, 1);
   if (p.ksplit > 1) {
     grid = dim3((unsigned)(p.ntiles * p.ksplit), 1, 1);   // one tile per cluster
+    if (half) return a.bits == 4 ? launch_tc_inst<4, false, false, true>(map, wmap, p, grid, st, p.ksplit)
+                                 : launch_tc_inst<8, false, false, true>(map, wmap, p, grid, st, p.ksplit);
     return a.bits == 4 ? launch_tc_inst<4, false, false>(map, wmap, p, grid, st, p.ksplit)
                        : launch_tc_inst<8, false, false>(map, wmap, p, grid, st, p.ksplit);
   }
   if (grouped && wide) return a.bits == 4 ? launch_tc_inst<4, true, true>(map, wmap, p, grid, st) : launch_tc_inst<8, true, true>(map, wmap, p, grid, st);
   if (grouped) return a.bits == 4 ? launch_tc_inst<4, true, false>(map, wmap, p, grid, st) : launch_tc_inst<8, true, false>(map, wmap, p, grid, st);
   if (wide) return a.bits == 4 ? launch_tc_inst<4, false, true>(map, wmap, p, grid, st) : launch_tc_inst<8, false, true>(map, wmap, p, grid, st);
+  if (half) return a.bits == 4 ? launch_tc_inst<4, false, false, true>(map, wmap, p, grid, st) : launch_tc_inst<8, false, false, true>(map, wmap, p, grid, st);
   return a.bits == 4 ? launch_tc_inst<4, false, false>(map, wmap, p, grid, st) : launch_tc_inst<8, false, false>(map, wmap, p, grid, st);
 }
 
