@@ -298,24 +298,8 @@ def main():
                 dist.all_reduce(tt, op=dist.ReduceOp.MAX)
                 ms = float(tt.item())
             res[name] = {"ms_per_block": ms, "tokens_per_s": world * T / (ms * 1e-3), "nan": bool(torch.isnan(out).any())}
-        # The padded plan reads nothing back on the host, so the whole block (collectives included) can be one
-        # CUDA graph; the eager numbers above are dominated by the launch overhead of ~25 small framework kernels.
-        try:
-            side = torch.cuda.Stream(device=dev)
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                for _ in range(2):
-                    out = ep.moe_block_ep_padded(xtok, inds, wts, E, fn)
-            torch.cuda.current_stream().wait_stream(side)
-            torch.cuda.synchronize()
-            gr = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gr):
-                out = ep.moe_block_ep_padded(xtok, inds, wts, E, fn)
-            ms = time_graph(gr, args.steps, 3) / args.steps
-            res["padded_cuda_graph"] = {"ms_per_block": ms, "tokens_per_s": world * T / (ms * 1e-3),
-                                        "nan": bool(torch.isnan(out).any())}
-        except Exception as exc:  # graph capture of the collectives is not available in every build
-            res["padded_cuda_graph"] = {"unavailable": str(exc)[:200]}
+        # (Both plans are timed eagerly.  Capturing the padded plan's collectives into a CUDA graph did not return on
+        # a two-GPU box and is not attempted.)
         if rank == 0:
             print(json.dumps(res))
         if world > 1:
