@@ -113,6 +113,25 @@ def test_batch_broadcast_and_transpose_false_attention_shapes(transpose):
     _run(x, q[:1], s[:1], b[:1], 64, 8, transpose)
 
 
+@pytest.mark.parametrize("M", [1, 8])
+def test_fp32_activations_just_below_a_power_of_two(M):
+    """fp32 activations whose group maximum rounds up to 2^14 on the 15-bit fixed-point grid (the staging clamps them
+    to 16383), zeros, and a group of very small values next to a group of large ones."""
+    rng = np.random.default_rng(77 + M)
+    q, s, b = make_weight(rng, (512, 1024), 64, 4)
+    x = rng.standard_normal((M, 1024)).astype(np.float32)
+    x[:, 0:64] = np.nextafter(np.float32(2.0), np.float32(0.0))
+    x[:, 64:128] = -np.nextafter(np.float32(0.5), np.float32(0.0))
+    x[:, 128:192] = 0.0
+    x[:, 192:256] *= 1e-20
+    x[:, 256:320] *= 1e4
+    ref = qo.qmm(x, q, s, b, 64, 4, True)
+    import qb200
+    dq, ds, db = dev_triple(q, s, b)
+    y = qb200.quantized_matmul(torch.from_numpy(x).cuda(), dq, ds, db, True, 64, 4)
+    gate_f32(y.cpu().numpy(), ref, "fp32 activations at the clamp")
+
+
 def test_strided_operands_and_1d_x():
     import qb200
     rng = np.random.default_rng(13)
