@@ -317,7 +317,7 @@ def main():
         per_expert = 786432 + 2 * 49152
         res = {}
 
-        def block(T, inds):
+        def block(T, inds, fused=False):
             """Buffers and the three gather_qmm calls of one MoE block for T tokens routed to `inds` [T*topk]."""
             order = torch.argsort(inds, stable=True)
             sorted_inds = inds[order].to(torch.int32).contiguous()
@@ -329,6 +329,11 @@ def main():
             yd = torch.empty((T * topk, 1, H), dtype=torch.bfloat16, device=dev)
 
             def run():
+                if fused:   # gate and up in one launch with the SwiGLU epilogue, its result feeds the down projection
+                    qb200.gather_qmm_swiglu(x_rep, *banks["gate"], *banks["up"], None, sorted_inds, 64, 4,
+                                            sorted_indices=True, out=yg)
+                    qb200.gather_qmm(yg, *banks["down"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yd)
+                    return
                 qb200.gather_qmm(x_rep, *banks["gate"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yg)
                 qb200.gather_qmm(x_rep, *banks["up"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yu)
                 qb200.gather_qmm(act, *banks["down"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yd)
@@ -338,13 +343,13 @@ def main():
         # routed rows, 256 per expert on average -- a grouped GEMM; reported in TFLOP/s as well.
         # 1 token: 16 blocks in the graph, each routed to a disjoint set of 8 experts, so the replay still
         # streams all 128 experts from HBM instead of re-reading 21 MB from L2.
-        for T in (64, 1, 4096):
+        for T, fused in ((64, False), (1, False), (4096, False), (64, True), (1, True)):
             if T != 1:
                 logits = torch.randn((T, E), device=dev, generator=g)
-                runs = [block(T, torch.topk(torch.softmax(logits, -1), topk, dim=-1).indices.reshape(-1))]
+                runs = [block(T, torch.topk(torch.softmax(logits, -1), topk, dim=-1).indices.reshape(-1), fused)]
             else:
                 perm = torch.randperm(E, device=dev, generator=g)
-                runs = [block(T, perm[i * topk:(i + 1) * topk]) for i in range(E // topk)]
+                runs = [block(T, perm[i * topk:(i + 1) * topk], fused) for i in range(E // topk)]
             for r, _ in runs:
                 r()
             torch.cuda.synchronize()
@@ -355,7 +360,7 @@ def main():
             ms = time_graph(gr, args.steps, 3) / args.steps / len(runs)
             uniq = runs[0][1]
             by = 3 * uniq * per_expert + T * topk * 2 * (2 * (H + I) + (I + H))
-            res[f"tokens{T}"] = {"us_per_block": ms * 1e3, "unique_experts": uniq, "bytes": by,
+            res[f"tokens{T}" + ("_fused_gate_up_swiglu" if fused else "")] = {"us_per_block": ms * 1e3, "unique_experts": uniq, "bytes": by,
                                  "GBps": by / (ms * 1e-3) / 1e9,
                                  "TFLOPs": 2.0 * T * topk * 3 * H * I / (ms * 1e-3) / 1e12}
             del gr

@@ -146,6 +146,23 @@ QB200_API int qb200_gather_qmm(qb200_tensor* res, const qb200_tensor* x, const q
                                qb200_optional_int group_size, qb200_optional_int bits, const char* mode,
                                bool sorted_indices, qb200_stream s);
 
+/* ---- fused gate/up projection + SwiGLU of the routed-expert block ----
+ * res[i] = silu(x[lhs(i)] . Wgate[rhs[i]]^T) * (x[lhs(i)] . Wup[rhs[i]]^T), both banks of one shape, read once,
+ * with the activations staged once.  Replaces two gatherExpertMm calls and fusedSwiGLU in moeMLP2
+ * (src/transformer.zig:15007-15035, :19925-19931) and the single-token gatherQmvGateUp kernel
+ * (src/transformer.zig:20303-20396, :20145-20203).  Rounding points of the bf16 form are the reference's
+ * (src/transformer.zig:19842-19851): both projections rounded to bf16, the sigmoid of the rounded gate read from
+ * a table over all bf16 patterns, g*sig rounded, then *up rounded; fp32 inputs compute (g*sigmoid(g))*u in fp32.
+ * Served by the streaming kernel's shapes (at most 2048 index entries, K <= 4096 and a multiple of 256);
+ * anything else returns QB200_ERR_UNSUPPORTED and the caller keeps the unfused chain.  The first call on a
+ * device uploads the 128 KiB sigmoid table with a synchronous copy. */
+QB200_API int qb200_gather_qmm_swiglu(qb200_tensor* res, const qb200_tensor* x, const qb200_tensor* w_gate,
+                                      const qb200_tensor* scales_gate, const qb200_tensor* biases_gate,
+                                      const qb200_tensor* w_up, const qb200_tensor* scales_up,
+                                      const qb200_tensor* biases_up, const qb200_tensor* lhs_indices,
+                                      const qb200_tensor* rhs_indices, qb200_optional_int group_size,
+                                      qb200_optional_int bits, const char* mode, bool sorted_indices, qb200_stream s);
+
 /* ---- mlx_dequantize (src/mlx.zig:271; caller src/kv_quant.zig:407-430) ----
  * res [..., in] = q*scale + bias, computed as a rounded fp32 product plus a
  * rounded fp32 add, then cast to `dtype` (default: the dtype of scales).

@@ -354,11 +354,13 @@ QB200_API int qb200_quantized_matmul_batch(qb200_tensor* const* res, const qb200
   return QB200_OK;
 }
 
-QB200_API int qb200_gather_qmm(qb200_tensor* res, const qb200_tensor* x, const qb200_tensor* w,
-                               const qb200_tensor* scales, const qb200_tensor* biases,
-                               const qb200_tensor* lhs_indices, const qb200_tensor* rhs_indices, bool transpose_w,
-                               qb200_optional_int group_size, qb200_optional_int bits, const char* mode,
-                               bool sorted_indices, qb200_stream s) {
+// Validation and geometry of one gather_qmm call; *skip is set when there is nothing to compute.
+static int prepare_gather(qb200_tensor* res, const qb200_tensor* x, const qb200_tensor* w,
+                          const qb200_tensor* scales, const qb200_tensor* biases,
+                          const qb200_tensor* lhs_indices, const qb200_tensor* rhs_indices, bool transpose_w,
+                          qb200_optional_int group_size, qb200_optional_int bits, const char* mode,
+                          bool sorted_indices, GatherArgs* out, bool* skip) {
+  *skip = false;
   int gs, nb, st;
   if ((st = resolve_mode(mode, group_size, bits, &gs, &nb))) return st;
   if (!transpose_w) return fail(QB200_ERR_UNSUPPORTED, "gather_qmm: only transpose_w=true is served");
@@ -441,8 +443,22 @@ QB200_API int qb200_gather_qmm(qb200_tensor* res, const qb200_tensor* x, const q
     }
   }
   a.gs = gs; a.bits = nb; a.sorted = sorted_indices;
-  if (a.I == 0 || M == 0 || N == 0) return QB200_OK;
+  *out = a;
+  if (a.I == 0 || M == 0 || N == 0) { *skip = true; return QB200_OK; }
   if (K == 0) return fail(QB200_ERR_BAD_SHAPE, "gather_qmm: empty contraction axis");
+  return QB200_OK;
+}
+
+QB200_API int qb200_gather_qmm(qb200_tensor* res, const qb200_tensor* x, const qb200_tensor* w,
+                               const qb200_tensor* scales, const qb200_tensor* biases,
+                               const qb200_tensor* lhs_indices, const qb200_tensor* rhs_indices, bool transpose_w,
+                               qb200_optional_int group_size, qb200_optional_int bits, const char* mode,
+                               bool sorted_indices, qb200_stream s) {
+  GatherArgs a;
+  bool skip = false;
+  const int st = prepare_gather(res, x, w, scales, biases, lhs_indices, rhs_indices, transpose_w, group_size, bits, mode,
+                                sorted_indices, &a, &skip);
+  if (st || skip) return st;
   cudaError_t e;
   // Few rows per expert: stream every hit expert once.  Many sorted rows (MoE prefill): grouped GEMM on the
   // tensor-core kernel, from 32 rows per expert on average.
@@ -453,6 +469,43 @@ QB200_API int qb200_gather_qmm(qb200_tensor* res, const qb200_tensor* x, const q
   else if (gather_mma_supported(a)) e = launch_gather_mma(a, (cudaStream_t)s);
   else e = launch_gather_generic(a, (cudaStream_t)s);
   if (e != cudaSuccess) return cuda_fail(e, "gather_qmm");
+  return QB200_OK;
+}
+
+QB200_API int qb200_gather_qmm_swiglu(qb200_tensor* res, const qb200_tensor* x, const qb200_tensor* w_gate,
+                                      const qb200_tensor* scales_gate, const qb200_tensor* biases_gate,
+                                      const qb200_tensor* w_up, const qb200_tensor* scales_up,
+                                      const qb200_tensor* biases_up, const qb200_tensor* lhs_indices,
+                                      const qb200_tensor* rhs_indices, qb200_optional_int group_size,
+                                      qb200_optional_int bits, const char* mode, bool sorted_indices, qb200_stream s) {
+  GatherArgs a;
+  bool skip = false;
+  int st = prepare_gather(res, x, w_gate, scales_gate, biases_gate, lhs_indices, rhs_indices, true, group_size, bits, mode,
+                          sorted_indices, &a, &skip);
+  if (st) return st;
+  if ((st = check_tensor(w_up, "w_up", 3)) || (st = check_tensor(scales_up, "scales_up", 3)) ||
+      (st = check_tensor(biases_up, "biases_up", 3)))
+    return st;
+  if (w_up->dtype != QB200_UINT32 || scales_up->dtype != QB200_BFLOAT16 || biases_up->dtype != QB200_BFLOAT16)
+    return fail(QB200_ERR_BAD_DTYPE, "gather_qmm_swiglu: the up bank must be uint32 codes with bf16 scales and biases");
+  if (w_up->ndim != 3 || scales_up->ndim != 3 || biases_up->ndim != 3)
+    return fail(QB200_ERR_BAD_SHAPE, "gather_qmm_swiglu: the up bank must be [E, N, *]");
+  for (int d = 0; d < 3; ++d)
+    if (w_up->shape[d] != w_gate->shape[d] || scales_up->shape[d] != scales_gate->shape[d] ||
+        biases_up->shape[d] != biases_gate->shape[d])
+      return fail(QB200_ERR_BAD_SHAPE, "gather_qmm_swiglu: gate and up banks must have the same shape");
+  if (!fully_contiguous(w_up) || !fully_contiguous(scales_up) || !fully_contiguous(biases_up))
+    return fail(QB200_ERR_BAD_STRIDE, "gather_qmm_swiglu: w, scales and biases must be contiguous");
+  if (skip) return QB200_OK;
+  if (x->dtype != QB200_BFLOAT16 && x->dtype != QB200_FLOAT32)
+    return fail(QB200_ERR_UNSUPPORTED, "gather_qmm_swiglu: x must be bf16 or f32");
+  a.w2 = (const uint32_t*)w_up->data; a.s2 = scales_up->data; a.b2 = biases_up->data;
+  // Declined shapes leave the caller on the unfused chain (two gather_qmm calls and its own SwiGLU), as the
+  // reference's fused path does (src/transformer.zig:19925-19931).
+  if (!gather_stream_supported(a) || (((uintptr_t)a.w2) & 15) != 0 || (((uintptr_t)a.s2) & 7) != 0 || (((uintptr_t)a.b2) & 7) != 0)
+    return fail(QB200_ERR_UNSUPPORTED, "gather_qmm_swiglu: shape not served by the fused streaming kernel");
+  const cudaError_t e = launch_gather_stream(a, (cudaStream_t)s);
+  if (e != cudaSuccess) return cuda_fail(e, "gather_qmm_swiglu");
   return QB200_OK;
 }
 

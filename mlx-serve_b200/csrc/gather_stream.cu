@@ -27,6 +27,8 @@
 // Arithmetic is that of the dense streaming kernel: exact s32 dots of codes with
 // 15-bit fixed-point activations, scale and bias applied per 64-wide group in
 // fp32; the weight term q*s+b is never rounded to bf16.
+#include <cmath>
+#include <cstring>
 #include <type_traits>
 
 #include "kernels.h"
@@ -51,6 +53,9 @@ struct GK {
   int64_t I, E, XB, xstride, wes, ses;
   int N, K, gshift, x_f32;
   int nsb;   // (expert, sweep) segments staged together: 2 when their fragments fit beside the ring, else 1
+  // fused gate/up form: a second bank of the same geometry; y = silu(x . gate^T) * (x . up^T)
+  const uint32_t* w2; const uint16_t* s2; const uint16_t* b2;
+  const uint16_t* sigtab;   // sigmoid of every bf16 pattern, as bf16
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -88,7 +93,7 @@ __device__ __forceinline__ long long load_index(const void* p, int is64, int64_t
 }
 
 
-template <int BITS>
+template <int BITS, bool FUSED>
 __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int U = BITS == 4 ? 4 : 2;   // 64-wide groups per unit
@@ -188,6 +193,9 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
     e = a;
   }
   const int64_t ldw = (int64_t)p.K * BITS / 32, lds = p.K >> (6 + p.gshift);
+  // fused form: the second bank has the first one's geometry, so its stage sources are a constant away
+  const int64_t wdelta = FUSED ? (const unsigned char*)p.w2 - (const unsigned char*)p.w : 0;           // bytes
+  const int64_t sbdelta = FUSED ? ((lane >> 4) ? p.b2 - p.b : p.s2 - p.s) : 0;                          // entries
   const int xf_stride = (p.K / 32) * NT * 32;       // uint2 elements of one segment's fragments
   const int gs_stride = (p.K / 64) * NT * 4 * 2;    // floats of one segment's group scales
   for (int pos = lo; pos < hi;) {
@@ -229,8 +237,9 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
     const int first = ksplit == 1 ? warp : warp / ksplit;
     const int my_tiles = first < ntb ? (ksplit == 1 ? (ntb - first + kWarps - 1) / kWarps : 1) : 0;
     const int nu = (ut - kp + ksplit - 1) / ksplit;   // units of one tile handled by this warp
-    const int total = my_tiles * nu;
+    const int total = my_tiles * nu * (FUSED ? 2 : 1);   // fused form: every unit of both banks, first bank first
     int issued = 0, ptile = 0, pu = kp;  // producer position: (tile index, unit)
+    int pbank = 0;                       // fused form: bank of the next item
     uint32_t p_off = 0, c_off = 0;       // byte offsets of the stages the next item is copied to / read from
     // per-lane source pointers of the producer's current tile (recomputed when the tile changes)
     const unsigned char* wsrc[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -255,12 +264,13 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
       }
       const uint32_t st = my_ring + p_off;
       p_off = p_off + kStageBytes == kStages * kStageBytes ? 0u : p_off + kStageBytes;
-      const int woff = pu * 128;
+      const int64_t woff = (int64_t)pu * 128 + ((FUSED && pbank) ? wdelta : 0);
 #pragma unroll
       for (int r = 0; r < 4; ++r) cp_async16(st + wdst[r], wsrc[r] + woff);
-      const uint16_t* ssrc = sbsrc + ((pu * U) >> p.gshift);
+      const uint16_t* ssrc = sbsrc + ((pu * U) >> p.gshift) + ((FUSED && pbank) ? sbdelta : 0);
       if (BITS == 4 && p.gshift == 0) cp_async8(st + sbdst, ssrc);
       else cp_async4(st + sbdst, ssrc);
+      if (FUSED) { pbank ^= 1; if (pbank) return; }
       pu += ksplit;
       if (pu >= ut) { pu = kp; ++ptile; }
     };
@@ -382,7 +392,17 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
     }
     __syncthreads();
     // lane (g, t) holds weight rows g, g+8 of a tile for the row in slot nt*4 + t of the tile's segment
-    auto store_tile = [&](int j, const float (&tot)[NT][2]) {
+    // fused form: silu(gate) * up with the reference's rounding points (src/transformer.zig:19842-19851): the
+    // sigmoid of the rounded gate from the table of all bf16 patterns, each product rounded to the output type
+    auto swiglu16 = [&](float gate, float up) -> uint16_t {
+      const uint32_t g16 = f32_to_bf16_bits(gate);
+      const float gf = __uint_as_float(g16 << 16), sig = __uint_as_float((uint32_t)p.sigtab[g16] << 16);
+      const float act = __uint_as_float((uint32_t)f32_to_bf16_bits(gf * sig) << 16);
+      const float uf = __uint_as_float((uint32_t)f32_to_bf16_bits(up) << 16);
+      return f32_to_bf16_bits(act * uf);
+    };
+    auto swiglu32 = [&](float gate, float up) -> float { return (gate * (1.f / (1.f + expf(-gate)))) * up; };
+    auto store_tile = [&](int j, const float (&tot)[NT][2], const float (&tot2)[NT][2]) {
       const bool sg = j >= nt0;
       const int tile = sg ? t01 + (j - nt0) : t00 + j;
       const int nte = sg ? nte1 : nte0;
@@ -393,19 +413,19 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
         if (nt < nte && orow >= 0) {
           const int64_t o = (int64_t)orow * p.N;
           if (p.x_f32) {
-            if (n_lo < p.N) ((float*)p.y)[o + n_lo] = tot[nt][0];
-            if (n_lo + 8 < p.N) ((float*)p.y)[o + n_lo + 8] = tot[nt][1];
+            if (n_lo < p.N) ((float*)p.y)[o + n_lo] = FUSED ? swiglu32(tot[nt][0], tot2[nt][0]) : tot[nt][0];
+            if (n_lo + 8 < p.N) ((float*)p.y)[o + n_lo + 8] = FUSED ? swiglu32(tot[nt][1], tot2[nt][1]) : tot[nt][1];
           } else {
-            if (n_lo < p.N) ((uint16_t*)p.y)[o + n_lo] = f32_to_bf16_bits(tot[nt][0]);
-            if (n_lo + 8 < p.N) ((uint16_t*)p.y)[o + n_lo + 8] = f32_to_bf16_bits(tot[nt][1]);
+            if (n_lo < p.N) ((uint16_t*)p.y)[o + n_lo] = FUSED ? swiglu16(tot[nt][0], tot2[nt][0]) : f32_to_bf16_bits(tot[nt][0]);
+            if (n_lo + 8 < p.N) ((uint16_t*)p.y)[o + n_lo + 8] = FUSED ? swiglu16(tot[nt][1], tot2[nt][1]) : f32_to_bf16_bits(tot[nt][1]);
           }
         }
       }
     };
     {
-      float tot[NT][2];
+      float tot[NT][2], tot2[NT][2];   // tot2: the second bank's sums (fused form)
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = 0.f;
+      for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = tot2[nt][0] = tot2[nt][1] = 0.f;
       for (int ti = 0; ti < my_tiles; ++ti) {
         const int j = first + ti * kWarps;
         const bool sg = j >= nt0;
@@ -413,9 +433,9 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
         const uint2* xf = xfrag + (sg ? xf_stride : 0);
         const float* gsb = gsc + (sg ? gs_stride : 0);
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = 0.f;
+        for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = tot2[nt][0] = tot2[nt][1] = 0.f;
         // one ring stage (16 rows x 128 bytes of codes) against the staged rows; NTE n8 tiles in use
-        auto unit = [&](auto nte_c, const unsigned char* st, int u) {
+        auto unit = [&](auto nte_c, const unsigned char* st, int u, float (&tt)[NT][2]) {
           constexpr int NTE = decltype(nte_c)::value;
           // fragments and group scales of this unit's U groups: every offset below is a compile-time constant
           const uint4* xb = (const uint4*)xf + (size_t)(u * U * NT) * 32 + lane;
@@ -471,13 +491,13 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
               mma_u8s8(acc, a0[1], a1[1], a2[1], a3[1], bf.z, bf.w);
               const float2 gs = gsn[nt];
               const float f_lo = (float)(acc[0] * 128 + acc[1]), f_hi = (float)(acc[2] * 128 + acc[3]);
-              tot[nt][0] = fmaf(s_lo * gs.x, f_lo, fmaf(b_lo, gs.y, tot[nt][0]));
-              tot[nt][1] = fmaf(s_hi * gs.x, f_hi, fmaf(b_hi, gs.y, tot[nt][1]));
+              tt[nt][0] = fmaf(s_lo * gs.x, f_lo, fmaf(b_lo, gs.y, tt[nt][0]));
+              tt[nt][1] = fmaf(s_hi * gs.x, f_hi, fmaf(b_hi, gs.y, tt[nt][1]));
             }
           }
         };
         auto sweep_k = [&](auto nte_c) {
-          for (int u = kp; u < ut; u += ksplit) {
+          auto step = [&](int u, float (&tt)[NT][2]) {
             if (issued < total) issue();
             cp_async_commit();
             ++issued;
@@ -485,13 +505,17 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
             __syncwarp();
             const unsigned char* st = my_ring_p + c_off;
             c_off = c_off + kStageBytes == kStages * kStageBytes ? 0u : c_off + kStageBytes;
-            unit(nte_c, st, u);
+            unit(nte_c, st, u, tt);
             __syncwarp();
+          };
+          for (int u = kp; u < ut; u += ksplit) {
+            step(u, tot);
+            if constexpr (FUSED) step(u, tot2);   // the same unit of the second bank, against the same fragments
           }
         };
         if (nte == 1) sweep_k(std::integral_constant<int, 1>{});
         else sweep_k(std::integral_constant<int, 2>{});
-        if (ksplit == 1) store_tile(j, tot);
+        if (ksplit == 1) store_tile(j, tot, tot2);
       }
       cp_async_wait<0>();
       if (ksplit > 1) {   // uniform over the CTA: every warp reaches the barrier
@@ -505,11 +529,53 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) { tot[nt][0] += o[(nt * 2 + 0) * 32 + lane]; tot[nt][1] += o[(nt * 2 + 1) * 32 + lane]; }
           }
-          store_tile(first, tot);
         }
+        if constexpr (FUSED) {   // the second bank's sums through the same buffer
+          __syncthreads();
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) { mine[(nt * 2 + 0) * 32 + lane] = tot2[nt][0]; mine[(nt * 2 + 1) * 32 + lane] = tot2[nt][1]; }
+          __syncthreads();
+          if (kp == 0 && my_tiles > 0) {
+            for (int k = 1; k < ksplit; ++k) {
+              const float* o = red + (size_t)(warp + k) * (NT * 2 * 32);
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) { tot2[nt][0] += o[(nt * 2 + 0) * 32 + lane]; tot2[nt][1] += o[(nt * 2 + 1) * 32 + lane]; }
+            }
+          }
+        }
+        if (kp == 0 && my_tiles > 0) store_tile(first, tot, tot2);
       }
     }
   }
+}
+
+// sigmoid of every bf16 bit pattern, rounded to bf16 (the reference tabulates mlx_sigmoid the same way,
+// src/transformer.zig:19853-19885); filled from the host once per device.
+__device__ uint16_t g_sigtab[1 << 16];
+
+const uint16_t* sigmoid_table(cudaError_t* err) {
+  static const uint16_t* ptr[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) { *err = cudaErrorInvalidDevice; return nullptr; }
+  if (!ptr[dev]) {
+    static uint16_t host[1 << 16];
+    for (uint32_t i = 0; i < (1u << 16); ++i) {
+      uint32_t bits = i << 16;
+      float x;
+      memcpy(&x, &bits, 4);
+      const float sg = 1.0f / (1.0f + expf(-x));
+      uint32_t u;
+      memcpy(&u, &sg, 4);
+      host[i] = (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);   // round to nearest even
+    }
+    void* d = nullptr;
+    if ((*err = cudaGetSymbolAddress(&d, g_sigtab)) != cudaSuccess) return nullptr;
+    if ((*err = cudaMemcpy(d, host, sizeof(host), cudaMemcpyHostToDevice)) != cudaSuccess) return nullptr;
+    ptr[dev] = (const uint16_t*)d;
+  }
+  *err = cudaSuccess;
+  return ptr[dev];
 }
 
 int sm_count_g() {
@@ -559,15 +625,22 @@ cudaError_t launch_gather_stream(const GatherArgs& a, cudaStream_t st) {
   p.wes = a.w_expert_stride; p.ses = a.s_expert_stride;
   p.N = (int)a.N; p.K = (int)a.K; p.gshift = a.gs == 128 ? 1 : 0; p.x_f32 = a.x_dtype == QB200_FLOAT32;
   p.nsb = pick_nsb(p.K);
+  const bool fused = a.w2 != nullptr;
+  p.w2 = a.w2; p.s2 = (const uint16_t*)a.s2; p.b2 = (const uint16_t*)a.b2; p.sigtab = nullptr;
+  if (fused) {
+    cudaError_t te;
+    p.sigtab = sigmoid_table(&te);
+    if (!p.sigtab) return te;
+  }
   const size_t smem = smem_bytes(p.K, p.nsb);
-  static bool done[2][64] = {};
+  static bool done[4][64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  const int bi = a.bits == 4 ? 0 : 1;
+  const int bi = (a.bits == 4 ? 0 : 1) + (fused ? 2 : 0);
+  const void* kern = a.bits == 4 ? (fused ? (const void*)gather_stream_kernel<4, true> : (const void*)gather_stream_kernel<4, false>)
+                                 : (fused ? (const void*)gather_stream_kernel<8, true> : (const void*)gather_stream_kernel<8, false>);
   if (dev < 0 || dev >= 64 || !done[bi][dev]) {
-    cudaError_t e = a.bits == 4
-        ? cudaFuncSetAttribute(gather_stream_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024 - kStaticSmem))
-        : cudaFuncSetAttribute(gather_stream_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024 - kStaticSmem));
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024 - kStaticSmem));
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) done[bi][dev] = true;
   }
@@ -581,8 +654,12 @@ cudaError_t launch_gather_stream(const GatherArgs& a, cudaStream_t st) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (a.bits == 4) return cudaLaunchKernelEx(&cfg, gather_stream_kernel<4>, p);
-  return cudaLaunchKernelEx(&cfg, gather_stream_kernel<8>, p);
+  if (fused) {
+    if (a.bits == 4) return cudaLaunchKernelEx(&cfg, gather_stream_kernel<4, true>, p);
+    return cudaLaunchKernelEx(&cfg, gather_stream_kernel<8, true>, p);
+  }
+  if (a.bits == 4) return cudaLaunchKernelEx(&cfg, gather_stream_kernel<4, false>, p);
+  return cudaLaunchKernelEx(&cfg, gather_stream_kernel<8, false>, p);
 }
 
 }  // namespace qb

@@ -71,6 +71,8 @@ struct GatherArgs {
   BatchMap xbcast;             // index-space position -> x batch entry (stride in batch entries)
   int gs, bits;
   bool sorted;
+  // fused gate/up form (gather_stream only): a second bank of the same geometry, y = silu(x . w^T) * (x . w2^T)
+  const uint32_t* w2 = nullptr; const void* s2 = nullptr; const void* b2 = nullptr;
 };
 bool gather_mma_supported(const GatherArgs& a);
 cudaError_t launch_gather_mma(const GatherArgs& a, cudaStream_t st);

@@ -77,6 +77,7 @@ def lib():
                                                    C.c_int, C.c_bool, OptInt, OptInt, C.c_char_p, C.c_void_p]
         L.qb200_gather_qmm.argtypes = [TP, TP, TP, TP, TP, TP, TP, C.c_bool, OptInt, OptInt, C.c_char_p, C.c_bool,
                                        C.c_void_p]
+        L.qb200_gather_qmm_swiglu.argtypes = [TP] * 10 + [OptInt, OptInt, C.c_char_p, C.c_bool, C.c_void_p]
         L.qb200_dequantize.argtypes = [TP, TP, TP, TP, OptInt, OptInt, C.c_char_p, TP, OptDtype, C.c_void_p]
         L.qb200_quantize.argtypes = [TP, TP, TP, TP, OptInt, OptInt, C.c_char_p, TP, C.c_void_p]
         L.qb200_kv_append.argtypes = [TP, TP, TP, TP, C.c_int64, C.c_int, C.c_int, C.c_void_p]
@@ -88,7 +89,7 @@ def lib():
         L.qb200_kv_decode_attention_noalloc_max_scratch.restype = C.c_size_t
         L.qb200_kv_decode_attention_workspace_size.restype = C.c_size_t
         L.qb200_kv_decode_attention_workspace_size.argtypes = [C.c_int64] * 5
-        for name in ("qb200_quantized_matmul", "qb200_quantized_matmul_batch", "qb200_quantized_matmul_shape", "qb200_gather_qmm", "qb200_dequantize",
+        for name in ("qb200_quantized_matmul", "qb200_quantized_matmul_batch", "qb200_quantized_matmul_shape", "qb200_gather_qmm", "qb200_gather_qmm_swiglu", "qb200_dequantize",
                      "qb200_quantize", "qb200_kv_append", "qb200_kv_decode_attention"):
             getattr(L, name).restype = C.c_int
         _lib = L
@@ -178,6 +179,25 @@ def gather_qmm(x, w, scales, biases, lhs_indices=None, rhs_indices=None, transpo
     check(L.qb200_gather_qmm(C.byref(do), C.byref(dx), C.byref(dw), C.byref(ds), C.byref(db), C.byref(dl),
                              C.byref(dr), transpose, _opt(group_size), _opt(bits), mode.encode(), sorted_indices,
                              _stream()))
+    return out
+
+
+def gather_qmm_swiglu(x, w_gate, scales_gate, biases_gate, w_up, scales_up, biases_up, lhs_indices=None, rhs_indices=None,
+                      group_size=None, bits=None, mode="affine", sorted_indices=False, out=None):
+    """Fused gate/up projection + SwiGLU of the routed-expert block: silu(x . Wgate^T) * (x . Wup^T) per index entry
+    (moeMLP2's two gatherExpertMm calls and fusedSwiGLU, src/transformer.zig:15007-15035, :19925-19931).
+    Raises Qb200Error (status QB200_ERR_UNSUPPORTED) for shapes the fused kernel does not serve."""
+    L = lib()
+    if out is None:
+        M, N = x.shape[-2], w_gate.shape[-2]
+        out = torch.empty(list(rhs_indices.shape) + [M, N], dtype=x.dtype, device=x.device)
+    do, dx = desc(out), desc(x)
+    dg, dgs, dgb = _packed(w_gate), desc(scales_gate), desc(biases_gate)
+    du, dus, dub = _packed(w_up), desc(scales_up), desc(biases_up)
+    dl, dr = desc(lhs_indices), desc(rhs_indices)
+    check(L.qb200_gather_qmm_swiglu(C.byref(do), C.byref(dx), C.byref(dg), C.byref(dgs), C.byref(dgb), C.byref(du),
+                                    C.byref(dus), C.byref(dub), C.byref(dl), C.byref(dr), _opt(group_size), _opt(bits),
+                                    mode.encode(), sorted_indices, _stream()))
     return out
 
 

@@ -64,6 +64,26 @@ QO_API void qo_f32_to_bf16(const float* x, uint16_t* out, int64_t n) {
 QO_API void qo_bf16_to_f32(const uint16_t* x, float* out, int64_t n) {
   for (int64_t i = 0; i < n; ++i) out[i] = bf16_to_f32(x[i]);
 }
+
+/* ---- fused SwiGLU of the MoE block: y = silu(gate) * up, elementwise (src/transformer.zig:19842-19851) ----
+ * bf16 form: gate and up are first rounded to bf16 (they are the stored outputs of the two projections);
+ * sig = bf16(sigmoid(gate)) (the reference reads it from a table of mlx_sigmoid over all bf16 patterns,
+ * src/transformer.zig:19853-19885); act = bf16(gate * sig); y = bf16(act * up).
+ * Parity unpinned: the last bit of mlx_sigmoid itself is not pinned by any reference test; this restatement uses
+ * 1 / (1 + expf(-x)) in fp32. */
+QO_API void qo_swiglu_bf16(const float* gate, const float* up, uint16_t* out, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) {
+    const float g = bf16_to_f32(f32_to_bf16(gate[i]));
+    const float u = bf16_to_f32(f32_to_bf16(up[i]));
+    const float sig = bf16_to_f32(f32_to_bf16(1.0f / (1.0f + expf(-g))));
+    const float act = bf16_to_f32(f32_to_bf16(g * sig));
+    out[i] = f32_to_bf16(act * u);
+  }
+}
+/* fp32 form (the reference declines fp32 there and keeps the unfused chain): (g * sigmoid(g)) * u in fp32. */
+QO_API void qo_swiglu_f32(const float* gate, const float* up, float* out, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) out[i] = (gate[i] * (1.0f / (1.0f + expf(-gate[i])))) * up[i];
+}
 /* Launchers such as torchrun export OMP_NUM_THREADS=1; a timing run may ask for the host's cores back. */
 QO_API void qo_set_num_threads(int n) {
 #ifdef _OPENMP

@@ -161,6 +161,21 @@ def qmm_batched(x, w, s, b, gs: int, bits: int, transpose: bool = True) -> np.nd
     return out
 
 
+def swiglu_bf16(gate, up) -> np.ndarray:
+    """silu(gate) * up with the fused kernel's rounding points (bf16 inputs, sigmoid, product, product); bf16 bits."""
+    gate, up = _c(gate, np.float32), _c(up, np.float32)
+    out = np.empty(gate.shape, np.uint16)
+    lib().qo_swiglu_bf16(_p(gate, C.c_float), _p(up, C.c_float), _p(out, C.c_uint16), C.c_int64(gate.size))
+    return out
+
+
+def swiglu_f32(gate, up) -> np.ndarray:
+    gate, up = _c(gate, np.float32), _c(up, np.float32)
+    out = np.empty(gate.shape, np.float32)
+    lib().qo_swiglu_f32(_p(gate, C.c_float), _p(up, C.c_float), _p(out, C.c_float), C.c_int64(gate.size))
+    return out
+
+
 def gather_qmm(x, w, s, b, lhs, rhs, gs: int, bits: int) -> np.ndarray:
     """x [XB, M, K] fp32, bank [E, N, K*bits/32]; y[i] = x[lhs[i]] . What[rhs[i]]^T -> [I, M, N]."""
     x, w, s, b = _c(x, np.float32), _c(w, np.uint32), _c(s, np.uint16), _c(b, np.uint16)

@@ -156,3 +156,68 @@ def test_moe_block_padded_exchange_plan_matches_exact_plan_on_one_gpu():
     b = ep.moe_block_ep_padded(x, inds, w, E, fn)
     assert not torch.isnan(a).any() and not torch.isnan(b).any()
     assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+@pytest.mark.parametrize("T,bits,gs", [(64, 4, 64), (1, 4, 64), (5, 8, 64), (33, 4, 128)])
+def test_fused_gate_up_swiglu_matches_the_unfused_chain(T, bits, gs):
+    """qb200_gather_qmm_swiglu against (a) the library's own two gather_qmm results pushed through the oracle's
+    SwiGLU restatement -- bit for bit, since the fused kernel forms the same fp32 sums -- and (b) the full oracle
+    chain within the matmul gate.  T=1 takes the form in which several warps share a tile's K range."""
+    import qb200
+    E, H, I, k = 128, 2048, 768, 8
+    rng = np.random.default_rng(0xF1 + T + bits)
+    qg, sg, bg = make_weight(rng, (E, I, H), gs, bits)
+    qu, su, bu = make_weight(rng, (E, I, H), gs, bits)
+    dg, du = dev_triple(qg, sg, bg), dev_triple(qu, su, bu)
+    flat = _route(rng, T, E, k).reshape(-1)
+    order = np.argsort(flat, kind="stable")
+    sorted_inds = flat[order]
+    x = rand_bf16(rng, (T, H))
+    x_rep = x[order // k].reshape(T * k, 1, H)
+    idx = torch.from_numpy(sorted_inds).cuda()
+    x16 = to_dev_bf16(qo.f32_to_bf16(x_rep))
+    g16 = qb200.gather_qmm(x16, *dg, None, idx, True, gs, bits, sorted_indices=True)
+    u16 = qb200.gather_qmm(x16, *du, None, idx, True, gs, bits, sorted_indices=True)
+    want = qo.swiglu_bf16(g16.float().cpu().numpy(), u16.float().cpu().numpy())
+    y16 = qb200.gather_qmm_swiglu(x16, *dg, *du, None, idx, gs, bits, sorted_indices=True)
+    assert y16.dtype == torch.bfloat16 and tuple(y16.shape) == (T * k, 1, I)
+    got = y16.view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size} elements differ from the unfused chain"
+    # full oracle chain (fp32 activations): tolerance of the matmul gate on the product
+    rg = qo.gather_qmm(x_rep, qg, sg, bg, np.arange(T * k), sorted_inds, gs, bits)
+    ru = qo.gather_qmm(x_rep, qu, su, bu, np.arange(T * k), sorted_inds, gs, bits)
+    ref = qo.swiglu_f32(rg, ru)
+    y32 = qb200.gather_qmm_swiglu(torch.from_numpy(x_rep).cuda(), *dg, *du, None, idx, gs, bits, sorted_indices=True)
+    gate_f32(y32.cpu().numpy(), ref, "fused fp32")
+    # bf16 form against the fp32 chain: four bf16 roundings (gate, sigmoid, two products), 2^-9 relative each
+    d = np.abs(y16.float().cpu().numpy().astype(np.float64) - ref)
+    rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+    assert (d <= 2.0 ** -6 * np.abs(ref) + 1e-2 * rms).all()
+
+
+def test_fused_gate_up_swiglu_decode_shape_and_declined_shapes():
+    """The stock decode shape (x [B,S,1,1,D] broadcast against rhs [B,S,K], src/transformer.zig:15091-15119) and a
+    shape the fused kernel declines (the caller keeps the unfused chain)."""
+    import qb200
+    E, H, I, k = 16, 1024, 512, 4
+    rng = np.random.default_rng(0xF2)
+    qg, sg, bg = make_weight(rng, (E, I, H), 64, 4)
+    qu, su, bu = make_weight(rng, (E, I, H), 64, 4)
+    dg, du = dev_triple(qg, sg, bg), dev_triple(qu, su, bu)
+    inds = _route(rng, 3, E, k).reshape(1, 3, k)
+    x = rand_bf16(rng, (1, 3, 1, 1, H))
+    idx = torch.from_numpy(inds).cuda()
+    x16 = to_dev_bf16(qo.f32_to_bf16(x))
+    g16 = qb200.gather_qmm(x16, *dg, None, idx, True, 64, 4)
+    u16 = qb200.gather_qmm(x16, *du, None, idx, True, 64, 4)
+    want = qo.swiglu_bf16(g16.float().cpu().numpy(), u16.float().cpu().numpy())
+    y16 = qb200.gather_qmm_swiglu(x16, *dg, *du, None, idx, 64, 4)
+    assert tuple(y16.shape) == (1, 3, k, 1, I)
+    assert np.array_equal(y16.view(torch.int16).cpu().numpy().view(np.uint16), want)
+    # K = 320 is not a multiple of 256: declined, nothing written
+    q2, s2, b2 = make_weight(rng, (4, 32, 320), 64, 4)
+    d2 = dev_triple(q2, s2, b2)
+    x2 = to_dev_bf16(qo.f32_to_bf16(rand_bf16(rng, (2, 1, 320))))
+    with pytest.raises(qb200.Qb200Error) as ei:
+        qb200.gather_qmm_swiglu(x2, *d2, *d2, None, torch.tensor([0, 3], dtype=torch.int32).cuda(), 64, 4)
+    assert ei.value.status == 1

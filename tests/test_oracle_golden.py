@@ -149,3 +149,21 @@ def test_kv_decode_attention_vs_dense_float64(bits):
             p = np.exp(sc - sc.max())
             ref = (p / p.sum()) @ vd[bi, h // 4, :L]
             assert np.abs(out[bi, h] - ref).max() < 1e-4
+
+
+def test_swiglu_restatement_rounding_points():
+    """bf16 form: sigmoid, g*sig and act*up are each rounded to bf16 (src/transformer.zig:19842-19851); checked
+    against numpy in float64 with the same rounding points."""
+    rng = np.random.default_rng(5)
+    g = rng.standard_normal(4096).astype(np.float32) * 3
+    u = rng.standard_normal(4096).astype(np.float32)
+    got = qo.bf16_to_f32(qo.swiglu_bf16(g, u))
+    g16, u16 = qo.bf16_round(g), qo.bf16_round(u)
+    sig = qo.bf16_round((1.0 / (1.0 + np.exp(-g16.astype(np.float64)))).astype(np.float32))
+    act = qo.bf16_round(g16 * sig)
+    want = qo.bf16_round(act * u16)
+    assert (got != want).mean() < 1e-3            # float64 vs fp32 exp may flip a rounding at a tie
+    assert np.abs(got - want).max() <= np.abs(want).max() * 2.0 ** -7
+    f = qo.swiglu_f32(g, u)
+    assert np.allclose(f, g / (1 + np.exp(-g.astype(np.float64))) * u, rtol=1e-5, atol=1e-7)
+    assert qo.bf16_to_f32(qo.swiglu_bf16(np.zeros(4, np.float32), np.ones(4, np.float32))).tolist() == [0.0] * 4
