@@ -28,6 +28,9 @@ pub extern "c" fn qb200_quantized_matmul_batch(res: [*]const *Tensor, x: *const 
 pub extern "c" fn qb200_quantized_matmul_shape(x: *const Tensor, w: *const Tensor, scales: *const Tensor, transpose_w: bool, group_size: OptionalInt, bits: OptionalInt, out_shape: [*]i64, out_ndim: *i32) c_int;
 // replaces mlx_gather_qmm (src/mlx.zig:265)
 pub extern "c" fn qb200_gather_qmm(res: *Tensor, x: *const Tensor, w: *const Tensor, scales: *const Tensor, biases: *const Tensor, lhs_indices: *const Tensor, rhs_indices: *const Tensor, transpose_w: bool, group_size: OptionalInt, bits: OptionalInt, mode: [*:0]const u8, sorted_indices: bool, s: Stream) c_int;
+// replaces the two gatherExpertMm calls + fusedSwiGLU of moeMLP2 (src/transformer.zig:15007-15035, :19925-19931);
+// returns 1 (declined) for shapes it does not serve: keep the unfused chain then
+pub extern "c" fn qb200_gather_qmm_swiglu(res: *Tensor, x: *const Tensor, w_gate: *const Tensor, scales_gate: *const Tensor, biases_gate: *const Tensor, w_up: *const Tensor, scales_up: *const Tensor, biases_up: *const Tensor, lhs_indices: *const Tensor, rhs_indices: *const Tensor, group_size: OptionalInt, bits: OptionalInt, mode: [*:0]const u8, sorted_indices: bool, s: Stream) c_int;
 // replaces mlx_dequantize (src/mlx.zig:271)
 pub extern "c" fn qb200_dequantize(res: *Tensor, w: *const Tensor, scales: *const Tensor, biases: *const Tensor, group_size: OptionalInt, bits: OptionalInt, mode: [*:0]const u8, global_scale: *const Tensor, dtype: OptionalDtype, s: Stream) c_int;
 // replaces mlx_quantize (src/mlx.zig:275); results in mlx-c's vector order [q, scales, biases]

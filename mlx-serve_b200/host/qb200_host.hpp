@@ -6,6 +6,7 @@
 //   QuantizedKV, quantAttention              src/kv_quant.zig:102-124, :478-687
 //   qmatmulBits                              src/transformer.zig:20894-20983
 //   gatherExpertMm                           src/transformer.zig:20763-20784
+//   gatherExpertGateUpSwiGLU                 src/transformer.zig:15007-15035 with fusedSwiGLU, :19925-19931
 //   KVCacheEntry, KVCache::updateAffine      src/transformer.zig:2777-2858, :3224-3337
 //
 // Differences that follow from the eager ABI: arrays are caller-owned device buffers described by `Array`
@@ -115,6 +116,17 @@ inline void gatherExpertMm(Array& res, const Array& x, const QWeight& bank, cons
   check(qb200_gather_qmm(&res.t, &x.t, &bank.q.t, &bank.scales.t, &bank.biases.t, lhs_indices ? &lhs_indices->t : nullptr,
                          &rhs_indices.t, true, some(bank.group_size), some(bank.bits), "affine", sorted_indices,
                          s));
+}
+
+// The gate and up projections of the routed-expert block with fusedSwiGLU applied (src/transformer.zig:15007-15035,
+// :19925-19931): res[i] = silu(x[lhs(i)] . gate[rhs[i]]^T) * (x[lhs(i)] . up[rhs[i]]^T).  Throws Declined for shapes the
+// fused kernel does not serve; the caller then keeps two gatherExpertMm calls and its own SwiGLU, as the reference's
+// fusedSwiGLU returns null to its caller.
+inline void gatherExpertGateUpSwiGLU(Array& res, const Array& x, const QWeight& gate, const QWeight& up, const Array* lhs_indices,
+                                     const Array& rhs_indices, bool sorted_indices, qb200_stream s) {
+  check(qb200_gather_qmm_swiglu(&res.t, &x.t, &gate.q.t, &gate.scales.t, &gate.biases.t, &up.q.t, &up.scales.t, &up.biases.t,
+                                lhs_indices ? &lhs_indices->t : nullptr, &rhs_indices.t, some(gate.group_size), some(gate.bits),
+                                "affine", sorted_indices, s));
 }
 
 // KVCacheEntry (src/transformer.zig:2777-2858): six capacity buffers [B, Hkv, cap, *] per layer and the fill level.
