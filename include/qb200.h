@@ -163,6 +163,16 @@ QB200_API int qb200_gather_qmm_swiglu(qb200_tensor* res, const qb200_tensor* x, 
                                       const qb200_tensor* rhs_indices, qb200_optional_int group_size,
                                       qb200_optional_int bits, const char* mode, bool sorted_indices, qb200_stream s);
 
+/* ---- the tail of the routed-expert block: rows back to token order, times the scores, summed over top-k ----
+ * res[t, h] = sum_j round(y[inv_order[t*k + j], h] * scores[t, j]).  Replaces mlx_take_axis(inv_order) +
+ * mlx_multiply(norm_scores) + mlx_sum_axis(-2) of moeMLP2 (src/transformer.zig:15036-15042, :15127-15140).
+ * y [T*k, H] or [T*k, 1, H] in the order its rows were computed (sorted by expert), scores [.., T, k] and res
+ * [.., T, H] of y's dtype (bf16 or f32), inv_order [T*k] int32/int64 or empty (rows already in token order).
+ * bf16: each product is rounded to bf16, as the reference's multiply in the activation dtype is; the sum over k is
+ * kept in fp32, ascending k, rounded once (the accumulation type of mlx_sum_axis is not pinned by the reference). */
+QB200_API int qb200_moe_weighted_sum(qb200_tensor* res, const qb200_tensor* y, const qb200_tensor* scores,
+                                     const qb200_tensor* inv_order, qb200_stream s);
+
 /* ---- mlx_dequantize (src/mlx.zig:271; caller src/kv_quant.zig:407-430) ----
  * res [..., in] = q*scale + bias, computed as a rounded fp32 product plus a
  * rounded fp32 add, then cast to `dtype` (default: the dtype of scales).

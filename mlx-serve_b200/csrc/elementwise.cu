@@ -157,7 +157,63 @@ cudaError_t quant_dispatch_x(const QuantArgs& a, cudaStream_t st) {
   }
 }
 
+// One thread per 8 consecutive h of one token: the k rows are read 16 bytes at a time.  bf16: every product is
+// rounded to bf16 (the reference multiplies in the activation dtype, src/transformer.zig:15127-15140), the sum over
+// k runs in fp32 in ascending k and is rounded once.
+template <bool F32>
+__global__ void __launch_bounds__(256) moe_sum_kernel(MoeSumArgs a) {
+  const int64_t per_tok = a.H / 8;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= a.T * per_tok) return;
+  const int64_t t = i / per_tok, h0 = (i - t * per_tok) * 8;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  for (int64_t j = 0; j < a.topk; ++j) {
+    const int64_t e = t * a.topk + j;
+    int64_t row = e;
+    if (a.inv) row = a.inv_i64 ? ((const long long*)a.inv)[e] : (long long)((const int*)a.inv)[e];
+    if (row < 0 || row >= a.T * a.topk) continue;   // out-of-range entries contribute nothing
+    if (F32) {
+      const float sc = ((const float*)a.scores)[e];
+      const float4 v0 = *(const float4*)((const float*)a.y + row * a.H + h0), v1 = *(const float4*)((const float*)a.y + row * a.H + h0 + 4);
+      acc[0] += v0.x * sc; acc[1] += v0.y * sc; acc[2] += v0.z * sc; acc[3] += v0.w * sc;
+      acc[4] += v1.x * sc; acc[5] += v1.y * sc; acc[6] += v1.z * sc; acc[7] += v1.w * sc;
+    } else {
+      const float sc = __uint_as_float((uint32_t)((const uint16_t*)a.scores)[e] << 16);
+      const uint4 v = *(const uint4*)((const uint16_t*)a.y + row * a.H + h0);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        acc[2 * q] += __uint_as_float((uint32_t)f32_to_bf16_bits(bf16lo(w[q]) * sc) << 16);
+        acc[2 * q + 1] += __uint_as_float((uint32_t)f32_to_bf16_bits(bf16hi(w[q]) * sc) << 16);
+      }
+    }
+  }
+  if (F32) {
+    float* o = (float*)a.out + t * a.H + h0;
+    *(float4*)o = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *(float4*)(o + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  } else {
+    uint4 o;
+    o.x = (uint32_t)f32_to_bf16_bits(acc[0]) | ((uint32_t)f32_to_bf16_bits(acc[1]) << 16);
+    o.y = (uint32_t)f32_to_bf16_bits(acc[2]) | ((uint32_t)f32_to_bf16_bits(acc[3]) << 16);
+    o.z = (uint32_t)f32_to_bf16_bits(acc[4]) | ((uint32_t)f32_to_bf16_bits(acc[5]) << 16);
+    o.w = (uint32_t)f32_to_bf16_bits(acc[6]) | ((uint32_t)f32_to_bf16_bits(acc[7]) << 16);
+    *(uint4*)((uint16_t*)a.out + t * a.H + h0) = o;
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_moe_weighted_sum(const MoeSumArgs& a, cudaStream_t st) {
+  const int64_t n = a.T * (a.H / 8);
+  if (n <= 0) return cudaSuccess;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (a.dtype == QB200_FLOAT32) moe_sum_kernel<true><<<blocks, 256, 0, st>>>(a);
+  else moe_sum_kernel<false><<<blocks, 256, 0, st>>>(a);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_dequantize(const DequantArgs& a, cudaStream_t st) {
   switch (a.bits) {

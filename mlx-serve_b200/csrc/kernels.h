@@ -17,6 +17,16 @@ struct DequantArgs {
 };
 cudaError_t launch_dequantize(const DequantArgs& a, cudaStream_t st);
 
+// Score-weighted sum over the top-k axis of the routed-expert block, with the rows taken back from expert order:
+// out[t, h] = sum_j round(y[inv[t*k + j], h] * scores[t, j]).
+struct MoeSumArgs {
+  const void* y; const void* scores; const void* inv; void* out;
+  int inv_i64;            // inv may be null: row t*k + j
+  int64_t T, topk, H;
+  int dtype;              // QB200_BFLOAT16 or QB200_FLOAT32 (y, scores and out)
+};
+cudaError_t launch_moe_weighted_sum(const MoeSumArgs& a, cudaStream_t st);
+
 struct QuantArgs {
   const void* x; uint32_t* q; void* s; void* b;
   RowMap xmap, qmap, sbmap;

@@ -129,6 +129,12 @@ inline void gatherExpertGateUpSwiGLU(Array& res, const Array& x, const QWeight& 
                                 "affine", sorted_indices, s));
 }
 
+// The tail of moeMLP2 (src/transformer.zig:15036-15042, :15127-15140): rows of the down projection back to token
+// order, times norm_scores, summed over top-k.  inv_order may be null (rows already in token order).
+inline void moeWeightedSum(Array& res, const Array& down_sorted, const Array& norm_scores, const Array* inv_order, qb200_stream s) {
+  check(qb200_moe_weighted_sum(&res.t, &down_sorted.t, &norm_scores.t, inv_order ? &inv_order->t : nullptr, s));
+}
+
 // KVCacheEntry (src/transformer.zig:2777-2858): six capacity buffers [B, Hkv, cap, *] per layer and the fill level.
 struct KVCacheEntry {
   QuantizedKV keys, values;   // capacity buffers

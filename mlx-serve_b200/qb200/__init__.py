@@ -78,6 +78,7 @@ def lib():
         L.qb200_gather_qmm.argtypes = [TP, TP, TP, TP, TP, TP, TP, C.c_bool, OptInt, OptInt, C.c_char_p, C.c_bool,
                                        C.c_void_p]
         L.qb200_gather_qmm_swiglu.argtypes = [TP] * 10 + [OptInt, OptInt, C.c_char_p, C.c_bool, C.c_void_p]
+        L.qb200_moe_weighted_sum.argtypes = [TP, TP, TP, TP, C.c_void_p]
         L.qb200_dequantize.argtypes = [TP, TP, TP, TP, OptInt, OptInt, C.c_char_p, TP, OptDtype, C.c_void_p]
         L.qb200_quantize.argtypes = [TP, TP, TP, TP, OptInt, OptInt, C.c_char_p, TP, C.c_void_p]
         L.qb200_kv_append.argtypes = [TP, TP, TP, TP, C.c_int64, C.c_int, C.c_int, C.c_void_p]
@@ -89,7 +90,7 @@ def lib():
         L.qb200_kv_decode_attention_noalloc_max_scratch.restype = C.c_size_t
         L.qb200_kv_decode_attention_workspace_size.restype = C.c_size_t
         L.qb200_kv_decode_attention_workspace_size.argtypes = [C.c_int64] * 5
-        for name in ("qb200_quantized_matmul", "qb200_quantized_matmul_batch", "qb200_quantized_matmul_shape", "qb200_gather_qmm", "qb200_gather_qmm_swiglu", "qb200_dequantize",
+        for name in ("qb200_quantized_matmul", "qb200_quantized_matmul_batch", "qb200_quantized_matmul_shape", "qb200_gather_qmm", "qb200_gather_qmm_swiglu", "qb200_moe_weighted_sum", "qb200_dequantize",
                      "qb200_quantize", "qb200_kv_append", "qb200_kv_decode_attention"):
             getattr(L, name).restype = C.c_int
         _lib = L
@@ -198,6 +199,17 @@ def gather_qmm_swiglu(x, w_gate, scales_gate, biases_gate, w_up, scales_up, bias
     check(L.qb200_gather_qmm_swiglu(C.byref(do), C.byref(dx), C.byref(dg), C.byref(dgs), C.byref(dgb), C.byref(du),
                                     C.byref(dus), C.byref(dub), C.byref(dl), C.byref(dr), _opt(group_size), _opt(bits),
                                     mode.encode(), sorted_indices, _stream()))
+    return out
+
+
+def moe_weighted_sum(y, scores, inv_order=None, out=None):
+    """Rows back to token order, times the scores, summed over top-k (moeMLP2's take(inv_order) + multiply + sum,
+    src/transformer.zig:15036-15042, :15127-15140).  y [T*k, H] or [T*k, 1, H], scores [..., T, k] -> [..., T, H]."""
+    L = lib()
+    if out is None:
+        out = torch.empty(list(scores.shape[:-1]) + [y.shape[-1]], dtype=y.dtype, device=y.device)
+    check(L.qb200_moe_weighted_sum(C.byref(desc(out)), C.byref(desc(y)), C.byref(desc(scores)), C.byref(desc(inv_order)),
+                                   _stream()))
     return out
 
 

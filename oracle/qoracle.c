@@ -80,6 +80,24 @@ QO_API void qo_swiglu_bf16(const float* gate, const float* up, uint16_t* out, in
     out[i] = f32_to_bf16(act * u);
   }
 }
+/* ---- score-weighted sum over top-k with the rows taken back from expert order
+ * (src/transformer.zig:15036-15042, :15127-15140): out[t,h] = sum_j y[inv[t*k+j], h] * scores[t, j].
+ * bf16 form (as_bf16 != 0): y and scores are bf16 values, each product is rounded to bf16, fp32 sum in ascending j,
+ * one final rounding.  inv may be NULL (identity). */
+QO_API void qo_moe_weighted_sum(const float* y, const float* scores, const int64_t* inv, int64_t T, int64_t k, int64_t H,
+                                int as_bf16, float* out) {
+  for (int64_t t = 0; t < T; ++t)
+    for (int64_t h = 0; h < H; ++h) {
+      float acc = 0.0f;
+      for (int64_t j = 0; j < k; ++j) {
+        const int64_t row = inv ? inv[t * k + j] : t * k + j;
+        if (row < 0 || row >= T * k) continue;
+        const float p = y[row * H + h] * scores[t * k + j];
+        acc += as_bf16 ? bf16_to_f32(f32_to_bf16(p)) : p;
+      }
+      out[t * H + h] = as_bf16 ? bf16_to_f32(f32_to_bf16(acc)) : acc;
+    }
+}
 /* fp32 form (the reference declines fp32 there and keeps the unfused chain): (g * sigmoid(g)) * u in fp32. */
 QO_API void qo_swiglu_f32(const float* gate, const float* up, float* out, int64_t n) {
   for (int64_t i = 0; i < n; ++i) out[i] = (gate[i] * (1.0f / (1.0f + expf(-gate[i])))) * up[i];

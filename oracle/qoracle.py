@@ -176,6 +176,19 @@ def swiglu_f32(gate, up) -> np.ndarray:
     return out
 
 
+def moe_weighted_sum(y, scores, inv=None, as_bf16: bool = True) -> np.ndarray:
+    """out[t, h] = sum_j y[inv[t*k + j], h] * scores[t, j]; y [T*k, H], scores [T, k] (fp32 carriers of bf16 values when
+    as_bf16: products and the final sum are rounded to bf16)."""
+    y, scores = _c(y, np.float32), _c(scores, np.float32)
+    T, k = scores.shape
+    H = y.shape[-1]
+    out = np.empty((T, H), np.float32)
+    invp = None if inv is None else _p(_c(inv, np.int64), C.c_int64)
+    lib().qo_moe_weighted_sum(_p(y, C.c_float), _p(scores, C.c_float), invp, C.c_int64(T), C.c_int64(k), C.c_int64(H),
+                              C.c_int(1 if as_bf16 else 0), _p(out, C.c_float))
+    return out
+
+
 def gather_qmm(x, w, s, b, lhs, rhs, gs: int, bits: int) -> np.ndarray:
     """x [XB, M, K] fp32, bank [E, N, K*bits/32]; y[i] = x[lhs[i]] . What[rhs[i]]^T -> [I, M, N]."""
     x, w, s, b = _c(x, np.float32), _c(w, np.uint32), _c(s, np.uint16), _c(b, np.uint16)

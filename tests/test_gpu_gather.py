@@ -221,3 +221,58 @@ def test_fused_gate_up_swiglu_decode_shape_and_declined_shapes():
     with pytest.raises(qb200.Qb200Error) as ei:
         qb200.gather_qmm_swiglu(x2, *d2, *d2, None, torch.tensor([0, 3], dtype=torch.int32).cuda(), 64, 4)
     assert ei.value.status == 1
+
+
+@pytest.mark.parametrize("T,k,H", [(64, 8, 2048), (1, 8, 2048), (7, 2, 264)])
+def test_moe_weighted_sum_bit_exact(T, k, H):
+    """qb200_moe_weighted_sum against the oracle restatement: bit-exact in both dtypes, with and without inv_order."""
+    import qb200
+    rng = np.random.default_rng(T * 31 + k + H)
+    y = qo.bf16_round(rng.standard_normal((T * k, 1, H)).astype(np.float32))
+    sc = qo.bf16_round(rng.random((T, k)).astype(np.float32))
+    inv = rng.permutation(T * k).astype(np.int32)
+    for use_inv in (True, False):
+        want16 = qo.f32_to_bf16(qo.moe_weighted_sum(y.reshape(T * k, H), sc, inv if use_inv else None, as_bf16=True))
+        got16 = qb200.moe_weighted_sum(to_dev_bf16(qo.f32_to_bf16(y)), to_dev_bf16(qo.f32_to_bf16(sc)),
+                                       torch.from_numpy(inv).cuda() if use_inv else None)
+        assert tuple(got16.shape) == (T, H)
+        assert np.array_equal(got16.view(torch.int16).cpu().numpy().view(np.uint16), want16)
+        want32 = qo.moe_weighted_sum(y.reshape(T * k, H), sc, inv if use_inv else None, as_bf16=False)
+        got32 = qb200.moe_weighted_sum(torch.from_numpy(y).cuda(), torch.from_numpy(sc).cuda(),
+                                       torch.from_numpy(inv.astype(np.int64)).cuda() if use_inv else None)
+        assert np.array_equal(got32.cpu().numpy(), want32)
+
+
+def test_moe_block_fused_path_end_to_end():
+    """The routed-expert block of moeMLP2 (src/transformer.zig:14961-15043, :15127-15140) through the fused entries:
+    sort by expert, gate/up + SwiGLU, down, rows back to token order times the scores; against the oracle chain."""
+    import qb200
+    E, H, I, T, k = 32, 1024, 512, 16, 4
+    rng = np.random.default_rng(0xB10C)
+    banks = {n: make_weight(rng, (E, I, H) if n != "down" else (E, H, I), 64, 4) for n in ("gate", "up", "down")}
+    dev = {n: dev_triple(*banks[n]) for n in banks}
+    inds = _route(rng, T, E, k)
+    flat = inds.reshape(-1)
+    order = np.argsort(flat, kind="stable")
+    inv = np.argsort(order, kind="stable").astype(np.int32)
+    sorted_inds = flat[order]
+    scores = qo.bf16_round(rng.random((T, k)).astype(np.float32))
+    scores = qo.bf16_round(scores / scores.sum(-1, keepdims=True))
+    x = rand_bf16(rng, (T, H))
+    x_rep = x[order // k].reshape(T * k, 1, H)
+    # oracle chain with the same rounding points
+    g = qo.gather_qmm(x_rep, *banks["gate"], np.arange(T * k), sorted_inds, 64, 4)
+    u = qo.gather_qmm(x_rep, *banks["up"], np.arange(T * k), sorted_inds, 64, 4)
+    act = qo.bf16_to_f32(qo.swiglu_bf16(g, u))
+    d = qo.bf16_round(qo.gather_qmm(act.reshape(T * k, 1, I), *banks["down"], np.arange(T * k), sorted_inds, 64, 4))
+    ref = qo.moe_weighted_sum(d.reshape(T * k, H), scores, inv, as_bf16=True)
+    idx = torch.from_numpy(sorted_inds).cuda()
+    a16 = qb200.gather_qmm_swiglu(to_dev_bf16(qo.f32_to_bf16(x_rep)), *dev["gate"], *dev["up"], None, idx, 64, 4,
+                                  sorted_indices=True)
+    d16 = qb200.gather_qmm(a16, *dev["down"], None, idx, True, 64, 4, sorted_indices=True)
+    out = qb200.moe_weighted_sum(d16, to_dev_bf16(qo.f32_to_bf16(scores)), torch.from_numpy(inv).cuda())
+    got = out.float().cpu().numpy()
+    rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+    # bf16 roundings of the intermediate tensors can flip by one ulp where the oracle's and the kernels' fp32 sums
+    # differ in their last bits; the block's result stays within a few bf16 ulps
+    assert np.abs(got - ref).max() <= 2.0 ** -6 * np.abs(ref).max() + 1e-2 * rms

@@ -167,3 +167,24 @@ def test_swiglu_restatement_rounding_points():
     f = qo.swiglu_f32(g, u)
     assert np.allclose(f, g / (1 + np.exp(-g.astype(np.float64))) * u, rtol=1e-5, atol=1e-7)
     assert qo.bf16_to_f32(qo.swiglu_bf16(np.zeros(4, np.float32), np.ones(4, np.float32))).tolist() == [0.0] * 4
+
+
+def test_moe_weighted_sum_restatement():
+    """Inverse permutation + score-weighted sum over top-k against plain numpy (fp32 form) and with bf16 rounding
+    of every product (bf16 form)."""
+    rng = np.random.default_rng(6)
+    T, k, H = 5, 4, 16
+    y = qo.bf16_round(rng.standard_normal((T * k, H)).astype(np.float32))
+    sc = qo.bf16_round(rng.random((T, k)).astype(np.float32))
+    inv = rng.permutation(T * k).astype(np.int64)
+    f = qo.moe_weighted_sum(y, sc, inv, as_bf16=False)
+    want = np.zeros((T, H), np.float32)
+    for j in range(k):   # same order of additions
+        want = want + y[inv.reshape(T, k)[:, j]] * sc[:, j:j + 1]
+    assert np.array_equal(f, want)
+    b = qo.moe_weighted_sum(y, sc, inv, as_bf16=True)
+    wb = np.zeros((T, H), np.float32)
+    for j in range(k):
+        wb = wb + qo.bf16_round(y[inv.reshape(T, k)[:, j]] * sc[:, j:j + 1])
+    assert np.array_equal(b, qo.bf16_round(wb))
+    assert np.array_equal(qo.moe_weighted_sum(y, sc, None, as_bf16=False), qo.moe_weighted_sum(y, sc, np.arange(T * k), as_bf16=False))
