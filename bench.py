@@ -327,12 +327,16 @@ def main():
             yg = torch.empty((T * topk, 1, I), dtype=torch.bfloat16, device=dev)
             yu = torch.empty_like(yg)
             yd = torch.empty((T * topk, 1, H), dtype=torch.bfloat16, device=dev)
+            inv = torch.argsort(order).to(torch.int32).contiguous()
+            scores = torch.softmax(torch.randn((T, topk), device=dev, generator=g), -1).to(torch.bfloat16)
+            ysum = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
 
             def run():
                 if fused:   # gate and up in one launch with the SwiGLU epilogue, its result feeds the down projection
                     qb200.gather_qmm_swiglu(x_rep, *banks["gate"], *banks["up"], None, sorted_inds, 64, 4,
                                             sorted_indices=True, out=yg)
                     qb200.gather_qmm(yg, *banks["down"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yd)
+                    qb200.moe_weighted_sum(yd, scores, inv, out=ysum)   # back to token order, x scores, sum over top-k
                     return
                 qb200.gather_qmm(x_rep, *banks["gate"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yg)
                 qb200.gather_qmm(x_rep, *banks["up"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yu)
@@ -360,7 +364,7 @@ def main():
             ms = time_graph(gr, args.steps, 3) / args.steps / len(runs)
             uniq = runs[0][1]
             by = 3 * uniq * per_expert + T * topk * 2 * (2 * (H + I) + (I + H))
-            res[f"tokens{T}" + ("_fused_gate_up_swiglu" if fused else "")] = {"us_per_block": ms * 1e3, "unique_experts": uniq, "bytes": by,
+            res[f"tokens{T}" + ("_fused_block" if fused else "")] = {"us_per_block": ms * 1e3, "unique_experts": uniq, "bytes": by,
                                  "GBps": by / (ms * 1e-3) / 1e9,
                                  "TFLOPs": 2.0 * T * topk * 3 * H * I / (ms * 1e-3) / 1e12}
             del gr

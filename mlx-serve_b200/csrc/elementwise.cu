@@ -169,24 +169,49 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(MoeSumArgs a) {
   float acc[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-  for (int64_t j = 0; j < a.topk; ++j) {
-    const int64_t e = t * a.topk + j;
-    int64_t row = e;
-    if (a.inv) row = a.inv_i64 ? ((const long long*)a.inv)[e] : (long long)((const int*)a.inv)[e];
-    if (row < 0 || row >= a.T * a.topk) continue;   // out-of-range entries contribute nothing
-    if (F32) {
-      const float sc = ((const float*)a.scores)[e];
-      const float4 v0 = *(const float4*)((const float*)a.y + row * a.H + h0), v1 = *(const float4*)((const float*)a.y + row * a.H + h0 + 4);
-      acc[0] += v0.x * sc; acc[1] += v0.y * sc; acc[2] += v0.z * sc; acc[3] += v0.w * sc;
-      acc[4] += v1.x * sc; acc[5] += v1.y * sc; acc[6] += v1.z * sc; acc[7] += v1.w * sc;
-    } else {
-      const float sc = __uint_as_float((uint32_t)((const uint16_t*)a.scores)[e] << 16);
-      const uint4 v = *(const uint4*)((const uint16_t*)a.y + row * a.H + h0);
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  // top-k entries in batches of 8: first every index and score, then every row (independent loads in flight
+  // together), then the products in ascending j
+  for (int64_t j0 = 0; j0 < a.topk; j0 += 8) {
+    int64_t row[8];
+    float sc[8];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        acc[2 * q] += __uint_as_float((uint32_t)f32_to_bf16_bits(bf16lo(w[q]) * sc) << 16);
-        acc[2 * q + 1] += __uint_as_float((uint32_t)f32_to_bf16_bits(bf16hi(w[q]) * sc) << 16);
+    for (int q = 0; q < 8; ++q) {
+      const int64_t e = t * a.topk + j0 + q;
+      row[q] = -1;
+      sc[q] = 0.f;
+      if (j0 + q < a.topk) {
+        row[q] = a.inv ? (a.inv_i64 ? ((const long long*)a.inv)[e] : (long long)((const int*)a.inv)[e]) : e;
+        sc[q] = F32 ? ((const float*)a.scores)[e] : __uint_as_float((uint32_t)((const uint16_t*)a.scores)[e] << 16);
+        if (row[q] >= a.T * a.topk) row[q] = -1;   // out-of-range entries contribute nothing
+      }
+    }
+    uint4 v0[8], v1[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      v0[q] = v1[q] = make_uint4(0u, 0u, 0u, 0u);
+      if (row[q] >= 0) {
+        if (F32) {
+          v0[q] = *(const uint4*)((const float*)a.y + row[q] * a.H + h0);
+          v1[q] = *(const uint4*)((const float*)a.y + row[q] * a.H + h0 + 4);
+        } else {
+          v0[q] = *(const uint4*)((const uint16_t*)a.y + row[q] * a.H + h0);
+        }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      if (row[q] < 0) continue;
+      if (F32) {
+        const uint32_t w[8] = {v0[q].x, v0[q].y, v0[q].z, v0[q].w, v1[q].x, v1[q].y, v1[q].z, v1[q].w};
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[c] += __uint_as_float(w[c]) * sc[q];
+      } else {
+        const uint32_t w[4] = {v0[q].x, v0[q].y, v0[q].z, v0[q].w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          acc[2 * c] += __uint_as_float((uint32_t)f32_to_bf16_bits(bf16lo(w[c]) * sc[q]) << 16);
+          acc[2 * c + 1] += __uint_as_float((uint32_t)f32_to_bf16_bits(bf16hi(w[c]) * sc[q]) << 16);
+        }
       }
     }
   }
