@@ -519,7 +519,7 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     e2e_value = world * M * L * args.steps / (ms_e2e * 1e-3)
 
-    # The single-token line of the same workload (the shape BASELINE's bandwidth target is stated for) is cheap
+    # The single-token line of the same workload (the shape the bandwidth target is stated for) is cheap
     # and always reported next to the batch-decode headline.
     qmv_m1 = None
     if M != 1 and L > 0:

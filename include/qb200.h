@@ -155,7 +155,8 @@ QB200_API int qb200_gather_qmm(qb200_tensor* res, const qb200_tensor* x, const q
  * a table over all bf16 patterns, g*sig rounded, then *up rounded; fp32 inputs compute (g*sigmoid(g))*u in fp32.
  * Served by the streaming kernel's shapes (at most 2048 index entries, K <= 4096 and a multiple of 256);
  * anything else returns QB200_ERR_UNSUPPORTED and the caller keeps the unfused chain.  The first call on a
- * device uploads the 128 KiB sigmoid table with a synchronous copy. */
+ * device uploads the 128 KiB sigmoid table with a synchronous copy, so it must not happen while the stream is
+ * being captured into a CUDA graph (it fails with a CUDA error then; call once before capturing). */
 QB200_API int qb200_gather_qmm_swiglu(qb200_tensor* res, const qb200_tensor* x, const qb200_tensor* w_gate,
                                       const qb200_tensor* scales_gate, const qb200_tensor* biases_gate,
                                       const qb200_tensor* w_up, const qb200_tensor* scales_up,

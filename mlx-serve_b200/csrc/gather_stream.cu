@@ -553,12 +553,19 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
 // src/transformer.zig:19853-19885); filled from the host once per device.
 __device__ uint16_t g_sigtab[1 << 16];
 
-const uint16_t* sigmoid_table(cudaError_t* err) {
+const uint16_t* sigmoid_table(cudaStream_t st, cudaError_t* err) {
   static const uint16_t* ptr[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) { *err = cudaErrorInvalidDevice; return nullptr; }
   if (!ptr[dev]) {
+    // the upload is a synchronous copy: not possible while `st` is being captured into a graph (call once before)
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+      (void)cudaGetLastError();
+      *err = cudaErrorStreamCaptureUnsupported;
+      return nullptr;
+    }
     static uint16_t host[1 << 16];
     for (uint32_t i = 0; i < (1u << 16); ++i) {
       uint32_t bits = i << 16;
@@ -629,7 +636,7 @@ cudaError_t launch_gather_stream(const GatherArgs& a, cudaStream_t st) {
   p.w2 = a.w2; p.s2 = (const uint16_t*)a.s2; p.b2 = (const uint16_t*)a.b2; p.sigtab = nullptr;
   if (fused) {
     cudaError_t te;
-    p.sigtab = sigmoid_table(&te);
+    p.sigtab = sigmoid_table(st, &te);
     if (!p.sigtab) return te;
   }
   const size_t smem = smem_bytes(p.K, p.nsb);

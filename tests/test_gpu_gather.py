@@ -42,7 +42,7 @@ def test_reference_small_cases():
 
 @pytest.mark.parametrize("proj", ["gate", "down"])
 def test_config3_decode_sorted(proj):
-    """BASELINE config 3, decode: 64 tokens x top-8 of 128 experts, rows sorted by expert, x_rep = x[order // 8]."""
+    """Benchmark configuration 3, decode: 64 tokens x top-8 of 128 experts, rows sorted by expert, x_rep = x[order // 8]."""
     import qb200
     E, H, I, T, k = 128, 2048, 768, 64, 8
     N, K = (I, H) if proj == "gate" else (H, I)
@@ -106,7 +106,7 @@ def test_other_geometries_and_ragged_tail(bits, gs, K):
 
 @pytest.mark.parametrize("bits,gs,N,K", [(4, 64, 256, 512), (8, 64, 200, 768), (4, 128, 768, 1024)])
 def test_config3_prefill_sorted_grouped(bits, gs, N, K):
-    """BASELINE config 3, prefill form: thousands of routed rows sorted by expert, x already gathered ([I, 1, K]),
+    """Benchmark configuration 3, prefill form: thousands of routed rows sorted by expert, x already gathered ([I, 1, K]),
     which the library serves as a grouped GEMM on the tensor-core kernel.  Uneven runs per expert, including an
     expert without rows, one with a single row and runs that are not multiples of the 256-row tile.  The weight
     term is rounded to bf16 once on that route (as in the dense prefill route), so the reference is built from

@@ -66,7 +66,7 @@ def test_additive_mask_row_and_ragged_lengths(bits):
 
 @pytest.mark.parametrize("bits", [4, 8])
 def test_config5_t4096(bits):
-    """BASELINE config 5 at T=4096: B=16, Hq=32, Hkv=8, D=128, cap = next capacity so head stride != T*last."""
+    """Benchmark configuration 5 at T=4096: B=16, Hq=32, Hkv=8, D=128, cap = next capacity so head stride != T*last."""
     rng = np.random.default_rng(0xC5 + bits)
     _run(rng, 16, 32, 8, 4096, 128, bits, cap=4352)
 

@@ -38,7 +38,7 @@ def _run(x32, q, s, b, gs, bits, transpose=True):
 
 
 def test_config1_qmv_4096x4096():
-    """BASELINE config 1: x [1,4096] ~N(0,1), W [4096,4096] ~N(0,0.02), 4-bit g64."""
+    """Benchmark configuration 1: x [1,4096] ~N(0,1), W [4096,4096] ~N(0,0.02), 4-bit g64."""
     rng = np.random.default_rng(0xC1)
     q, s, b = make_weight(rng, (4096, 4096), 64, 4)
     r32, _ = _run(rand_bf16(rng, (1, 4096)), q, s, b, 64, 4)
@@ -51,7 +51,7 @@ LLAMA = {"q": (4096, 4096), "k": (1024, 4096), "gate": (14336, 4096), "down": (4
 @pytest.mark.parametrize("proj", list(LLAMA))
 @pytest.mark.parametrize("M", [1, 8, 32])
 def test_config2_llama_projections(proj, M):
-    """BASELINE config 2: the Llama-3-8B layer shapes (v = k, o = q, up = gate) at decode widths."""
+    """Benchmark configuration 2: the Llama-3-8B layer shapes (v = k, o = q, up = gate) at decode widths."""
     N, K = LLAMA[proj]
     rng = np.random.default_rng(0xC2 + M + N)
     q, s, b = make_weight(rng, (N, K), 64, 4)
@@ -189,7 +189,7 @@ def test_batch_entry_matches_single_calls(M):
 @pytest.mark.parametrize("M,N,K", [(512, 1024, 4096), (300, 1000, 1024), (17, 128, 64), (2048, 256, 2048),
                                    (256, 640, 768), (1100, 208, 1536), (4096, 2560, 512)])
 def test_config4_prefill_shapes(bits, gs, M, N, K):
-    """BASELINE config 4 (dense prefill qmm) at oracle-sized shapes, incl. ragged M and N, the minimum K, K that is
+    """Benchmark configuration 4 (dense prefill qmm) at oracle-sized shapes, incl. ragged M and N, the minimum K, K that is
     not a whole window of scales (768, 1536 at group size 128) and more tiles than SMs (several tiles per CTA)."""
     import qb200
     if K % gs:
@@ -202,7 +202,7 @@ def test_config4_prefill_shapes(bits, gs, M, N, K):
 
 @pytest.mark.parametrize("bits", [4, 8])
 def test_config4_full_size_vs_dequantize_plus_fp32_matmul(bits):
-    """BASELINE config 4 at full size (x [2048,4096], W [14336,4096]): the fused kernel against the route it replaces,
+    """Benchmark configuration 4 at full size (x [2048,4096], W [14336,4096]): the fused kernel against the route it replaces,
     dequantize to bf16 + a plain fp32 matmul (torch, TF32 off)."""
     import qb200
     g = torch.Generator(device="cuda").manual_seed(0xC4)
