@@ -24,6 +24,9 @@ void qo_qmm_t_bf16w(const float* x, const uint32_t* w, const uint16_t* s, const 
                     int64_t K, int gs, int bits, float* y);
 void qo_gather_qmm_t(const float* x, const uint32_t* w, const uint16_t* s, const uint16_t* b, const int64_t* lhs,
                      const int64_t* rhs, int64_t I, int64_t M, int64_t N, int64_t K, int gs, int bits, float* y);
+void qo_swiglu_bf16(const float* gate, const float* up, uint16_t* out, int64_t n);
+void qo_moe_weighted_sum(const float* y, const float* scores, const int64_t* inv, int64_t T, int64_t k, int64_t H, int as_bf16,
+                         float* out);
 void qo_kv_decode_attention(const float* q, const uint32_t* kq, const uint16_t* ks, const uint16_t* kb, const uint32_t* vq,
                             const uint16_t* vs, const uint16_t* vb, int64_t B, int64_t Hq, int64_t Hkv, int64_t T, int64_t D,
                             int64_t Dv, int gs, int bits, const int64_t* kq_str, const int64_t* ksb_str, const int64_t* vq_str,
@@ -150,6 +153,39 @@ int main(int argc, char** argv) {
       gatherExpertMm(dy, dx, qb_, nullptr, dr, true, stream);
       cudaDeviceSynchronize();
       ok = gate(f32_of(to_host((uint16_t*)dy.t.data, (size_t)(I * EN))), ref, 1e-2, "gatherExpertMm (sorted)") && ok;
+
+      // ---- the same rows through gate and up banks with fusedSwiGLU (src/transformer.zig:15007-15035, :19925-19931) ----
+      std::vector<float> bank2 = rand_bf16((size_t)(E * EN * K), 0.05f), ref2((size_t)(I * EN));
+      std::vector<uint32_t> uq(bq.size());
+      std::vector<uint16_t> us(bs.size()), ub(bs.size());
+      qo_quantize(bank2.data(), E * EN, K, gs, bits, uq.data(), us.data(), ub.data());
+      QWeight qu_;
+      qu_.q = Array(to_dev(uq), QB200_UINT32, {E, EN, K * bits / 32});
+      qu_.scales = Array(to_dev(us), QB200_BFLOAT16, {E, EN, K / gs});
+      qu_.biases = Array(to_dev(ub), QB200_BFLOAT16, {E, EN, K / gs});
+      qo_gather_qmm_t(x.data(), uq.data(), us.data(), ub.data(), lhs.data(), rhs.data(), I, 1, EN, K, gs, bits, ref2.data());
+      std::vector<uint16_t> act16((size_t)(I * EN));
+      qo_swiglu_bf16(ref.data(), ref2.data(), act16.data(), I * EN);
+      Array da(dev_alloc<uint16_t>((size_t)(I * EN)), QB200_BFLOAT16, {I, 1, EN});
+      gatherExpertGateUpSwiGLU(da, dx, qb_, qu_, nullptr, dr, true, stream);
+      cudaDeviceSynchronize();
+      ok = gate(f32_of(to_host((uint16_t*)da.t.data, (size_t)(I * EN))), f32_of(act16), 2e-2, "gatherExpertGateUpSwiGLU") && ok;
+
+      // ---- rows back to token order, times the scores, summed over top-k (src/transformer.zig:15036-15042, :15127-15140) ----
+      const int64_t T = 4, topk = 3;   // I = T * topk rows
+      std::vector<int64_t> inv = {5, 0, 9, 1, 6, 10, 2, 7, 11, 3, 4, 8};
+      std::vector<float> yrows = f32_of(to_host((uint16_t*)da.t.data, (size_t)(I * EN))), sc = rand_bf16((size_t)(T * topk), 1.0f);
+      std::vector<float> sref((size_t)(T * EN));
+      qo_moe_weighted_sum(yrows.data(), sc.data(), inv.data(), T, topk, EN, 1, sref.data());
+      Array dsc(to_dev(bf16_of(sc)), QB200_BFLOAT16, {T, topk}), dinv(to_dev(inv), QB200_INT64, {I});
+      Array dsum(dev_alloc<uint16_t>((size_t)(T * EN)), QB200_BFLOAT16, {T, EN});
+      moeWeightedSum(dsum, da, dsc, &dinv, stream);
+      cudaDeviceSynchronize();
+      std::vector<float> got = f32_of(to_host((uint16_t*)dsum.t.data, (size_t)(T * EN)));
+      bool exact = true;
+      for (size_t i = 0; i < got.size(); ++i) exact = exact && got[i] == sref[i];
+      std::printf("%s moeWeightedSum: bit-exact against the oracle\n", exact ? "ok  " : "FAIL");
+      ok = ok && exact;
     }
 
     // ---- KVCache.updateAffine + quantAttention over strided views (src/transformer.zig:3224-3337, src/kv_quant.zig:478-687) ----
