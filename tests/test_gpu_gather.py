@@ -276,3 +276,30 @@ def test_moe_block_fused_path_end_to_end():
     # bf16 roundings of the intermediate tensors can flip by one ulp where the oracle's and the kernels' fp32 sums
     # differ in their last bits; the block's result stays within a few bf16 ulps
     assert np.abs(got - ref).max() <= 2.0 ** -6 * np.abs(ref).max() + 1e-2 * rms
+
+
+def test_fused_gate_up_swiglu_long_k_explicit_lhs():
+    """K = 4096 (one expert segment staged at a time), explicit lhs_indices into a shared activation batch, unsorted
+    experts, an out-of-range expert id (its row is left untouched)."""
+    import qb200
+    E, H, I = 8, 4096, 72
+    rng = np.random.default_rng(0xF3)
+    qg, sg, bg = make_weight(rng, (E, I, H), 64, 4)
+    qu, su, bu = make_weight(rng, (E, I, H), 64, 4)
+    dg, du = dev_triple(qg, sg, bg), dev_triple(qu, su, bu)
+    x = rand_bf16(rng, (5, 1, H))
+    lhs = np.array([4, 0, 0, 3, 1, 2, 2, 4, 1], np.int32)
+    rhs = np.array([7, 2, 5, 2, 0, 7, 9, 1, 3], np.int32)   # 9 is out of range
+    x16 = to_dev_bf16(qo.f32_to_bf16(x))
+    li, ri = torch.from_numpy(lhs).cuda(), torch.from_numpy(rhs).cuda()
+    g16 = torch.full((9, 1, I), 3.0, dtype=torch.bfloat16, device="cuda")
+    u16 = g16.clone()
+    y16 = g16.clone()
+    qb200.gather_qmm(x16, *dg, li, ri, True, 64, 4, out=g16)
+    qb200.gather_qmm(x16, *du, li, ri, True, 64, 4, out=u16)
+    qb200.gather_qmm_swiglu(x16, *dg, *du, li, ri, 64, 4, out=y16)
+    want = qo.swiglu_bf16(g16.float().cpu().numpy(), u16.float().cpu().numpy())
+    got = y16.view(torch.int16).cpu().numpy().view(np.uint16)
+    keep = rhs < E
+    assert np.array_equal(got[keep], want[keep])
+    assert (y16[6].float() == 3.0).all()
