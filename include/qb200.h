@@ -164,6 +164,15 @@ QB200_API int qb200_gather_qmm_swiglu(qb200_tensor* res, const qb200_tensor* x, 
                                       const qb200_tensor* rhs_indices, qb200_optional_int group_size,
                                       qb200_optional_int bits, const char* mode, bool sorted_indices, qb200_stream s);
 
+/* ---- the router of the routed-expert block (moeRoutingChain, src/transformer.zig:17022-17063) ----
+ * logits [..., T, E] (bf16 or f32, E <= 1024) -> inds [..., T, k] int32: the k largest logits of each row, larger
+ * first, equal logits by lower index (the reference takes the set from mlx_argpartition, which leaves the order of the
+ * k open; scores and every later gather use the same order); norm_scores [..., T, k] of the logits' dtype:
+ * softmax over the row in fp32 rounded to that dtype, the k entries divided by their sum, sum and quotient each
+ * rounded to that dtype, as the chain of MLX ops (softmax, take_along_axis, sum, divide) rounds them. */
+QB200_API int qb200_moe_route(qb200_tensor* inds, qb200_tensor* norm_scores, const qb200_tensor* logits, int k,
+                              qb200_stream s);
+
 /* ---- the tail of the routed-expert block: rows back to token order, times the scores, summed over top-k ----
  * res[t, h] = sum_j round(y[inv_order[t*k + j], h] * scores[t, j]).  Replaces mlx_take_axis(inv_order) +
  * mlx_multiply(norm_scores) + mlx_sum_axis(-2) of moeMLP2 (src/transformer.zig:15036-15042, :15127-15140).

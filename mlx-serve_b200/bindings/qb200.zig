@@ -33,6 +33,8 @@ pub extern "c" fn qb200_gather_qmm(res: *Tensor, x: *const Tensor, w: *const Ten
 pub extern "c" fn qb200_gather_qmm_swiglu(res: *Tensor, x: *const Tensor, w_gate: *const Tensor, scales_gate: *const Tensor, biases_gate: *const Tensor, w_up: *const Tensor, scales_up: *const Tensor, biases_up: *const Tensor, lhs_indices: *const Tensor, rhs_indices: *const Tensor, group_size: OptionalInt, bits: OptionalInt, mode: [*:0]const u8, sorted_indices: bool, s: Stream) c_int;
 // replaces mlx_take_axis(inv_order) + mlx_multiply(norm_scores) + mlx_sum_axis(-2) at the end of moeMLP2 (src/transformer.zig:15036-15042, :15127-15140)
 pub extern "c" fn qb200_moe_weighted_sum(res: *Tensor, y: *const Tensor, scores: *const Tensor, inv_order: *const Tensor, s: Stream) c_int;
+// replaces moeRoutingChain (src/transformer.zig:17022-17063): argpartition, softmax, take_along_axis, sum, divide
+pub extern "c" fn qb200_moe_route(inds: *Tensor, norm_scores: *Tensor, logits: *const Tensor, k: c_int, s: Stream) c_int;
 // replaces mlx_dequantize (src/mlx.zig:271)
 pub extern "c" fn qb200_dequantize(res: *Tensor, w: *const Tensor, scales: *const Tensor, biases: *const Tensor, group_size: OptionalInt, bits: OptionalInt, mode: [*:0]const u8, global_scale: *const Tensor, dtype: OptionalDtype, s: Stream) c_int;
 // replaces mlx_quantize (src/mlx.zig:275); results in mlx-c's vector order [q, scales, biases]

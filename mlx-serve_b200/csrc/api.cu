@@ -509,6 +509,34 @@ QB200_API int qb200_gather_qmm_swiglu(qb200_tensor* res, const qb200_tensor* x, 
   return QB200_OK;
 }
 
+QB200_API int qb200_moe_route(qb200_tensor* inds, qb200_tensor* norm_scores, const qb200_tensor* logits, int k,
+                              qb200_stream s) {
+  int st;
+  if ((st = check_tensor(inds, "inds", 1)) || (st = check_tensor(norm_scores, "norm_scores", 1)) ||
+      (st = check_tensor(logits, "logits", 1)))
+    return st;
+  if (logits->dtype != QB200_BFLOAT16 && logits->dtype != QB200_FLOAT32)
+    return fail(QB200_ERR_UNSUPPORTED, "moe_route: logits must be bf16 or f32");
+  if (norm_scores->dtype != logits->dtype) return fail(QB200_ERR_BAD_DTYPE, "moe_route: norm_scores must have the logits' dtype");
+  if (inds->dtype != QB200_INT32 && inds->dtype != QB200_UINT32) return fail(QB200_ERR_BAD_DTYPE, "moe_route: inds must be int32/uint32");
+  if (!fully_contiguous(inds) || !fully_contiguous(norm_scores) || !fully_contiguous(logits))
+    return fail(QB200_ERR_BAD_STRIDE, "moe_route: tensors must be contiguous");
+  const int64_t E = logits->shape[logits->ndim - 1];
+  const int64_t T = E > 0 ? numel(logits) / E : 0;
+  if (k < 1 || k > 32 || k > E) return fail(QB200_ERR_UNSUPPORTED, "moe_route: k must be in 1..min(32, E)");
+  if (E > 1024) return fail(QB200_ERR_UNSUPPORTED, "moe_route: at most 1024 experts");
+  if (inds->shape[inds->ndim - 1] != k || norm_scores->shape[norm_scores->ndim - 1] != k || numel(inds) != T * k ||
+      numel(norm_scores) != T * k)
+    return fail(QB200_ERR_BAD_SHAPE, "moe_route: inds and norm_scores must be [..., T, k] for logits [..., T, E]");
+  MoeRouteArgs a;
+  a.logits = logits->data; a.inds = (int*)inds->data; a.scores = norm_scores->data;
+  a.T = T; a.E = (int)E; a.topk = k; a.dtype = logits->dtype;
+  if (T == 0) return QB200_OK;
+  const cudaError_t e = launch_moe_route(a, (cudaStream_t)s);
+  if (e != cudaSuccess) return cuda_fail(e, "moe_route");
+  return QB200_OK;
+}
+
 QB200_API int qb200_moe_weighted_sum(qb200_tensor* res, const qb200_tensor* y, const qb200_tensor* scores,
                                      const qb200_tensor* inv_order, qb200_stream s) {
   int st;

@@ -229,7 +229,78 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(MoeSumArgs a) {
   }
 }
 
+// One warp per row of logits (E <= 1024: up to 32 values per lane, column e in lane e % 32).  The k indices are
+// those of the largest logits, larger first, equal logits by lower index (the reference takes them from
+// mlx_argpartition, which leaves their order open; everything downstream is indexed alike, src/transformer.zig:17022-17063).
+// softmax in fp32 (precise), rounded to the logits' dtype as the reference's array is, then the k entries divided
+// by their sum, each step rounded to that dtype.
+template <bool F32>
+__global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= a.T) return;
+  constexpr int kPer = 32;
+  float v[kPer];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const int e = i * 32 + lane;
+    v[i] = -INFINITY;
+    if (e < a.E) {
+      v[i] = F32 ? ((const float*)a.logits)[row * a.E + e]
+                 : __uint_as_float((uint32_t)((const uint16_t*)a.logits)[row * a.E + e] << 16);
+      mx = fmaxf(mx, v[i]);
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < kPer; ++i)
+    if (i * 32 + lane < a.E) sum += expf(v[i] - mx);
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+  auto round_dt = [](float x) { return F32 ? x : __uint_as_float((uint32_t)f32_to_bf16_bits(x) << 16); };
+  float topw = 0.f, wsum = 0.f;   // lane j keeps the j-th selected probability
+  int topi = -1;
+  uint32_t taken = 0;             // bit i: this lane's value i was selected
+  for (int j = 0; j < a.topk; ++j) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+      const int e = i * 32 + lane;
+      if (e < a.E && !((taken >> i) & 1u) && (v[i] > bv || (v[i] == bv && e < bi))) { bv = v[i]; bi = e; }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, d);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, d);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (bi != 0x7fffffff && (bi & 31) == lane) taken |= 1u << (bi >> 5);
+    const float pr = bi != 0x7fffffff ? round_dt(expf(bv - mx) / sum) : 0.f;
+    wsum += pr;                   // every lane adds the same values in the same order
+    if (lane == j) { topw = pr; topi = bi != 0x7fffffff ? bi : 0; }
+  }
+  wsum = round_dt(wsum);
+  if (lane < a.topk) {
+    a.inds[row * a.topk + lane] = topi;
+    const float ns = round_dt(topw / wsum);
+    if (F32) ((float*)a.scores)[row * a.topk + lane] = ns;
+    else ((uint16_t*)a.scores)[row * a.topk + lane] = f32_to_bf16_bits(ns);
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_moe_route(const MoeRouteArgs& a, cudaStream_t st) {
+  if (a.T <= 0) return cudaSuccess;
+  const unsigned blocks = (unsigned)((a.T + 3) / 4);
+  if (a.dtype == QB200_FLOAT32) moe_route_kernel<true><<<blocks, 128, 0, st>>>(a);
+  else moe_route_kernel<false><<<blocks, 128, 0, st>>>(a);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_moe_weighted_sum(const MoeSumArgs& a, cudaStream_t st) {
   const int64_t n = a.T * (a.H / 8);

@@ -27,6 +27,15 @@ struct MoeSumArgs {
 };
 cudaError_t launch_moe_weighted_sum(const MoeSumArgs& a, cudaStream_t st);
 
+// Router of the routed-expert block: the k largest logits of every row, softmax over the row, the k probabilities
+// renormalised to sum to one.
+struct MoeRouteArgs {
+  const void* logits; int* inds; void* scores;
+  int64_t T; int E, topk;
+  int dtype;              // QB200_BFLOAT16 or QB200_FLOAT32 (logits and scores)
+};
+cudaError_t launch_moe_route(const MoeRouteArgs& a, cudaStream_t st);
+
 struct QuantArgs {
   const void* x; uint32_t* q; void* s; void* b;
   RowMap xmap, qmap, sbmap;

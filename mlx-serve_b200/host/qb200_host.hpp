@@ -129,6 +129,11 @@ inline void gatherExpertGateUpSwiGLU(Array& res, const Array& x, const QWeight& 
                                 "affine", sorted_indices, s));
 }
 
+// moeRoutingChain (src/transformer.zig:17022-17063): the k largest logits per row and their renormalised softmax scores.
+inline void moeRoutingChain(Array& inds, Array& norm_scores, const Array& router_logits, int k, qb200_stream s) {
+  check(qb200_moe_route(&inds.t, &norm_scores.t, &router_logits.t, k, s));
+}
+
 // The tail of moeMLP2 (src/transformer.zig:15036-15042, :15127-15140): rows of the down projection back to token
 // order, times norm_scores, summed over top-k.  inv_order may be null (rows already in token order).
 inline void moeWeightedSum(Array& res, const Array& down_sorted, const Array& norm_scores, const Array* inv_order, qb200_stream s) {

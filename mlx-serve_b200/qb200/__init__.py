@@ -79,6 +79,7 @@ def lib():
                                        C.c_void_p]
         L.qb200_gather_qmm_swiglu.argtypes = [TP] * 10 + [OptInt, OptInt, C.c_char_p, C.c_bool, C.c_void_p]
         L.qb200_moe_weighted_sum.argtypes = [TP, TP, TP, TP, C.c_void_p]
+        L.qb200_moe_route.argtypes = [TP, TP, TP, C.c_int, C.c_void_p]
         L.qb200_dequantize.argtypes = [TP, TP, TP, TP, OptInt, OptInt, C.c_char_p, TP, OptDtype, C.c_void_p]
         L.qb200_quantize.argtypes = [TP, TP, TP, TP, OptInt, OptInt, C.c_char_p, TP, C.c_void_p]
         L.qb200_kv_append.argtypes = [TP, TP, TP, TP, C.c_int64, C.c_int, C.c_int, C.c_void_p]
@@ -90,7 +91,7 @@ def lib():
         L.qb200_kv_decode_attention_noalloc_max_scratch.restype = C.c_size_t
         L.qb200_kv_decode_attention_workspace_size.restype = C.c_size_t
         L.qb200_kv_decode_attention_workspace_size.argtypes = [C.c_int64] * 5
-        for name in ("qb200_quantized_matmul", "qb200_quantized_matmul_batch", "qb200_quantized_matmul_shape", "qb200_gather_qmm", "qb200_gather_qmm_swiglu", "qb200_moe_weighted_sum", "qb200_dequantize",
+        for name in ("qb200_quantized_matmul", "qb200_quantized_matmul_batch", "qb200_quantized_matmul_shape", "qb200_gather_qmm", "qb200_gather_qmm_swiglu", "qb200_moe_weighted_sum", "qb200_moe_route", "qb200_dequantize",
                      "qb200_quantize", "qb200_kv_append", "qb200_kv_decode_attention"):
             getattr(L, name).restype = C.c_int
         _lib = L
@@ -200,6 +201,15 @@ def gather_qmm_swiglu(x, w_gate, scales_gate, biases_gate, w_up, scales_up, bias
                                     C.byref(dus), C.byref(dub), C.byref(dl), C.byref(dr), _opt(group_size), _opt(bits),
                                     mode.encode(), sorted_indices, _stream()))
     return out
+
+
+def moe_route(logits, k):
+    """moeRoutingChain (src/transformer.zig:17022-17063): (inds int32 [..., T, k], norm_scores [..., T, k])."""
+    L = lib()
+    inds = torch.empty(list(logits.shape[:-1]) + [k], dtype=torch.int32, device=logits.device)
+    scores = torch.empty(list(logits.shape[:-1]) + [k], dtype=logits.dtype, device=logits.device)
+    check(L.qb200_moe_route(C.byref(desc(inds)), C.byref(desc(scores)), C.byref(desc(logits)), int(k), _stream()))
+    return inds, scores
 
 
 def moe_weighted_sum(y, scores, inv_order=None, out=None):

@@ -80,6 +80,38 @@ QO_API void qo_swiglu_bf16(const float* gate, const float* up, uint16_t* out, in
     out[i] = f32_to_bf16(act * u);
   }
 }
+/* ---- router (src/transformer.zig:17022-17063): indices of the k largest logits (larger first, ties by lower
+ * index), softmax over the row in fp32 rounded to the logits' dtype, the k entries renormalised by their rounded sum.
+ * logits are fp32 carriers (bf16 values when as_bf16). */
+QO_API void qo_moe_route(const float* logits, int64_t T, int64_t E, int64_t k, int as_bf16, int32_t* inds, float* scores) {
+  unsigned char* taken = (unsigned char*)malloc((size_t)E);
+  for (int64_t t = 0; t < T; ++t) {
+    const float* x = logits + t * E;
+    float mx = -INFINITY, sum = 0.0f;
+    for (int64_t e = 0; e < E; ++e) mx = x[e] > mx ? x[e] : mx;
+    for (int64_t e = 0; e < E; ++e) sum += expf(x[e] - mx);
+    memset(taken, 0, (size_t)E);
+    float wsum = 0.0f;
+    for (int64_t j = 0; j < k; ++j) {
+      int64_t best = -1;
+      for (int64_t e = 0; e < E; ++e)
+        if (!taken[e] && (best < 0 || x[e] > x[best])) best = e;
+      taken[best] = 1;
+      inds[t * k + j] = (int32_t)best;
+      float pr = expf(x[best] - mx) / sum;
+      if (as_bf16) pr = bf16_to_f32(f32_to_bf16(pr));
+      scores[t * k + j] = pr;
+      wsum += pr;
+    }
+    if (as_bf16) wsum = bf16_to_f32(f32_to_bf16(wsum));
+    for (int64_t j = 0; j < k; ++j) {
+      const float ns = scores[t * k + j] / wsum;
+      scores[t * k + j] = as_bf16 ? bf16_to_f32(f32_to_bf16(ns)) : ns;
+    }
+  }
+  free(taken);
+}
+
 /* ---- score-weighted sum over top-k with the rows taken back from expert order
  * (src/transformer.zig:15036-15042, :15127-15140): out[t,h] = sum_j y[inv[t*k+j], h] * scores[t, j].
  * bf16 form (as_bf16 != 0): y and scores are bf16 values, each product is rounded to bf16, fp32 sum in ascending j,

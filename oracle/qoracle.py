@@ -176,6 +176,17 @@ def swiglu_f32(gate, up) -> np.ndarray:
     return out
 
 
+def moe_route(logits, k: int, as_bf16: bool = True):
+    """Router restatement: (inds [T, k] int32, norm_scores [T, k] fp32 carriers) for logits [T, E]."""
+    logits = _c(logits, np.float32)
+    T, E = logits.shape
+    inds = np.empty((T, k), np.int32)
+    scores = np.empty((T, k), np.float32)
+    lib().qo_moe_route(_p(logits, C.c_float), C.c_int64(T), C.c_int64(E), C.c_int64(k), C.c_int(1 if as_bf16 else 0),
+                       _p(inds, C.c_int32), _p(scores, C.c_float))
+    return inds, scores
+
+
 def moe_weighted_sum(y, scores, inv=None, as_bf16: bool = True) -> np.ndarray:
     """out[t, h] = sum_j y[inv[t*k + j], h] * scores[t, j]; y [T*k, H], scores [T, k] (fp32 carriers of bf16 values when
     as_bf16: products and the final sum are rounded to bf16)."""

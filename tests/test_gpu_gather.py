@@ -303,3 +303,25 @@ def test_fused_gate_up_swiglu_long_k_explicit_lhs():
     keep = rhs < E
     assert np.array_equal(got[keep], want[keep])
     assert (y16[6].float() == 3.0).all()
+
+
+@pytest.mark.parametrize("T,E,k", [(64, 128, 8), (1, 128, 8), (5, 1024, 6), (3, 40, 4)])
+def test_moe_route_matches_the_oracle(T, E, k):
+    """qb200_moe_route: the indices exactly (logits with ties included), the scores within one rounding step of the
+    logits' dtype (the kernel's expf and sum order differ from the oracle's in the last fp32 bits)."""
+    import qb200
+    rng = np.random.default_rng(T + E + k)
+    lg = qo.bf16_round(rng.standard_normal((T, E)).astype(np.float32) * 2)
+    lg[0, 3] = lg[0, E - 1] = lg[0].max() + 1      # a tie at the top
+    inds_ref, sc_ref = qo.moe_route(lg, k, as_bf16=True)
+    inds, sc = qb200.moe_route(to_dev_bf16(qo.f32_to_bf16(lg)), k)
+    assert inds.dtype == torch.int32 and tuple(inds.shape) == (T, k) and sc.dtype == torch.bfloat16
+    assert np.array_equal(inds.cpu().numpy(), inds_ref)
+    got = sc.float().cpu().numpy()
+    assert np.abs(got - sc_ref).max() <= 2.0 ** -7 * np.abs(sc_ref).max()
+    assert (got != sc_ref).mean() < 0.05
+    i32, s32 = qb200.moe_route(torch.from_numpy(lg).cuda(), k)
+    ir, sr = qo.moe_route(lg, k, as_bf16=False)
+    assert np.array_equal(i32.cpu().numpy(), ir)
+    assert np.allclose(s32.cpu().numpy(), sr, rtol=2e-6, atol=1e-9)
+    assert np.allclose(s32.cpu().numpy().sum(-1), 1.0, atol=1e-5)

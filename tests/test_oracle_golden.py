@@ -188,3 +188,21 @@ def test_moe_weighted_sum_restatement():
         wb = wb + qo.bf16_round(y[inv.reshape(T, k)[:, j]] * sc[:, j:j + 1])
     assert np.array_equal(b, qo.bf16_round(wb))
     assert np.array_equal(qo.moe_weighted_sum(y, sc, None, as_bf16=False), qo.moe_weighted_sum(y, sc, np.arange(T * k), as_bf16=False))
+
+
+def test_moe_route_restatement():
+    """Router: top-k by logit (ties by lower index), softmax, renormalised scores; against numpy."""
+    rng = np.random.default_rng(7)
+    T, E, k = 9, 128, 8
+    lg = qo.bf16_round(rng.standard_normal((T, E)).astype(np.float32))
+    lg[0, 5] = lg[0, 77] = 9.0            # a tie at the top: lower index first
+    inds, sc = qo.moe_route(lg, k, as_bf16=False)
+    assert inds[0, 0] == 5 and inds[0, 1] == 77
+    p = np.exp(lg.astype(np.float64) - lg.max(-1, keepdims=True)); p /= p.sum(-1, keepdims=True)
+    for t in range(T):
+        order = sorted(range(E), key=lambda e: (-lg[t, e], e))[:k]
+        assert inds[t].tolist() == order
+        w = p[t, order]
+        assert np.allclose(sc[t], w / w.sum(), rtol=1e-5)
+    _, sb = qo.moe_route(lg, k, as_bf16=True)
+    assert np.array_equal(sb, qo.bf16_round(sb)) and np.abs(sb - sc).max() < 2.0 ** -8
