@@ -166,10 +166,10 @@ QB200_API int qb200_gather_qmm_swiglu(qb200_tensor* res, const qb200_tensor* x, 
 
 /* ---- the router of the routed-expert block (moeRoutingChain, src/transformer.zig:17022-17063) ----
  * logits [..., T, E] (bf16 or f32, E <= 1024) -> inds [..., T, k] int32: the k largest logits of each row, larger
- * first, equal logits by lower index (the reference takes the set from mlx_argpartition, which leaves the order of the
- * k open; scores and every later gather use the same order); norm_scores [..., T, k] of the logits' dtype:
- * softmax over the row in fp32 rounded to that dtype, the k entries divided by their sum, sum and quotient each
- * rounded to that dtype, as the chain of MLX ops (softmax, take_along_axis, sum, divide) rounds them. */
+ * first, equal logits by lower index -- the order of the reference's one-kernel router (src/transformer.zig:17485-17500;
+ * the unfused chain takes the set from mlx_argpartition, which leaves the order open); norm_scores [..., T, k] of the
+ * logits' dtype: softmax over the row in fp32 rounded to that dtype, the k entries divided by their sum, the sum
+ * accumulated in that dtype in selection order (:17530-17534), the quotient rounded to it. */
 QB200_API int qb200_moe_route(qb200_tensor* inds, qb200_tensor* norm_scores, const qb200_tensor* logits, int k,
                               qb200_stream s);
 
@@ -178,8 +178,9 @@ QB200_API int qb200_moe_route(qb200_tensor* inds, qb200_tensor* norm_scores, con
  * mlx_multiply(norm_scores) + mlx_sum_axis(-2) of moeMLP2 (src/transformer.zig:15036-15042, :15127-15140).
  * y [T*k, H] or [T*k, 1, H] in the order its rows were computed (sorted by expert), scores [.., T, k] and res
  * [.., T, H] of y's dtype (bf16 or f32), inv_order [T*k] int32/int64 or empty (rows already in token order).
- * bf16: each product is rounded to bf16, as the reference's multiply in the activation dtype is; the sum over k is
- * kept in fp32, ascending k, rounded once (the accumulation type of mlx_sum_axis is not pinned by the reference). */
+ * bf16: each product is rounded to bf16, as the reference's multiply in the activation dtype is, and the sum over k
+ * is an ascending accumulate in bf16, rounded after every add: the reference's fused down+reduce kernel documents
+ * that as MLX's behaviour and replicates it (src/transformer.zig:20566-20571).  f32: plain fp32 sum. */
 QB200_API int qb200_moe_weighted_sum(qb200_tensor* res, const qb200_tensor* y, const qb200_tensor* scores,
                                      const qb200_tensor* inv_order, qb200_stream s);
 

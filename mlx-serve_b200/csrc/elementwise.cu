@@ -158,8 +158,10 @@ cudaError_t quant_dispatch_x(const QuantArgs& a, cudaStream_t st) {
 }
 
 // One thread per 8 consecutive h of one token: the k rows are read 16 bytes at a time.  bf16: every product is
-// rounded to bf16 (the reference multiplies in the activation dtype, src/transformer.zig:15127-15140), the sum over
-// k runs in fp32 in ascending k and is rounded once.
+// rounded to bf16 (the reference multiplies in the activation dtype, src/transformer.zig:15127-15140) and the sum
+// over k is an ascending accumulate in bf16, rounded after every add, which is how MLX reduces a bf16 row and what
+// the reference's fused down+reduce kernel replicates (src/transformer.zig:20566-20571).
+__device__ __forceinline__ float rbf(float x) { return __uint_as_float((uint32_t)f32_to_bf16_bits(x) << 16); }
 template <bool F32>
 __global__ void __launch_bounds__(256) moe_sum_kernel(MoeSumArgs a) {
   const int64_t per_tok = a.H / 8;
@@ -208,9 +210,9 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(MoeSumArgs a) {
       } else {
         const uint32_t w[4] = {v0[q].x, v0[q].y, v0[q].z, v0[q].w};
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          acc[2 * c] += __uint_as_float((uint32_t)f32_to_bf16_bits(bf16lo(w[c]) * sc[q]) << 16);
-          acc[2 * c + 1] += __uint_as_float((uint32_t)f32_to_bf16_bits(bf16hi(w[c]) * sc[q]) << 16);
+        for (int c = 0; c < 4; ++c) {   // product rounded to bf16, then a bf16 accumulate (rounded after every add)
+          acc[2 * c] = rbf(acc[2 * c] + rbf(bf16lo(w[c]) * sc[q]));
+          acc[2 * c + 1] = rbf(acc[2 * c + 1] + rbf(bf16hi(w[c]) * sc[q]));
         }
       }
     }
@@ -233,7 +235,8 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(MoeSumArgs a) {
 // those of the largest logits, larger first, equal logits by lower index (the reference takes them from
 // mlx_argpartition, which leaves their order open; everything downstream is indexed alike, src/transformer.zig:17022-17063).
 // softmax in fp32 (precise), rounded to the logits' dtype as the reference's array is, then the k entries divided
-// by their sum, each step rounded to that dtype.
+// by their sum (accumulated in that dtype, larger-first order), each step rounded to that dtype -- the order and the
+// accumulation are those of the reference's one-kernel router (src/transformer.zig:17485-17500, :17530-17534).
 template <bool F32>
 __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteArgs a) {
   const int lane = threadIdx.x & 31;
@@ -280,10 +283,10 @@ __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteArgs a) {
     }
     if (bi != 0x7fffffff && (bi & 31) == lane) taken |= 1u << (bi >> 5);
     const float pr = bi != 0x7fffffff ? round_dt(expf(bv - mx) / sum) : 0.f;
-    wsum += pr;                   // every lane adds the same values in the same order
+    wsum = round_dt(wsum + pr);   // ascending accumulate in the logits' dtype, rounded after every add
+                                  // (src/transformer.zig:17530-17534); every lane adds the same values
     if (lane == j) { topw = pr; topi = bi != 0x7fffffff ? bi : 0; }
   }
-  wsum = round_dt(wsum);
   if (lane < a.topk) {
     a.inds[row * a.topk + lane] = topi;
     const float ns = round_dt(topw / wsum);

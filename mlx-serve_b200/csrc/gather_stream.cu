@@ -401,7 +401,10 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
       const float uf = __uint_as_float((uint32_t)f32_to_bf16_bits(up) << 16);
       return f32_to_bf16_bits(act * uf);
     };
-    auto swiglu32 = [&](float gate, float up) -> float { return (gate * (1.f / (1.f + expf(-gate)))) * up; };
+    auto swiglu32 = [&](float gate, float up) -> float {
+      const float sy = 1.f / (1.f + expf(fabsf(gate)));
+      return (gate * (gate < 0.f ? sy : 1.f - sy)) * up;
+    };
     auto store_tile = [&](int j, const float (&tot)[NT][2], const float (&tot2)[NT][2]) {
       const bool sg = j >= nt0;
       const int tile = sg ? t01 + (j - nt0) : t00 + j;
@@ -571,7 +574,9 @@ const uint16_t* sigmoid_table(cudaStream_t st, cudaError_t* err) {
       uint32_t bits = i << 16;
       float x;
       memcpy(&x, &bits, 4);
-      const float sg = 1.0f / (1.0f + expf(-x));
+      // the two-sided form of MLX's Sigmoid, as the reference quotes it (src/transformer.zig:17566-17570)
+      const float sy = 1.0f / (1.0f + expf(fabsf(x)));
+      const float sg = x < 0.0f ? sy : 1.0f - sy;
       uint32_t u;
       memcpy(&u, &sg, 4);
       host[i] = (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);   // round to nearest even

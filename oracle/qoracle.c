@@ -70,18 +70,23 @@ QO_API void qo_bf16_to_f32(const uint16_t* x, float* out, int64_t n) {
  * sig = bf16(sigmoid(gate)) (the reference reads it from a table of mlx_sigmoid over all bf16 patterns,
  * src/transformer.zig:19853-19885); act = bf16(gate * sig); y = bf16(act * up).
  * Parity unpinned: the last bit of mlx_sigmoid itself is not pinned by any reference test; this restatement uses
- * 1 / (1 + expf(-x)) in fp32. */
+ * the two-sided form the reference quotes from MLX's Sigmoid (src/transformer.zig:17566-17570) in fp32. */
+static inline float sigmoid_f32(float x) {
+  const float sy = 1.0f / (1.0f + expf(fabsf(x)));
+  return x < 0.0f ? sy : 1.0f - sy;
+}
 QO_API void qo_swiglu_bf16(const float* gate, const float* up, uint16_t* out, int64_t n) {
   for (int64_t i = 0; i < n; ++i) {
     const float g = bf16_to_f32(f32_to_bf16(gate[i]));
     const float u = bf16_to_f32(f32_to_bf16(up[i]));
-    const float sig = bf16_to_f32(f32_to_bf16(1.0f / (1.0f + expf(-g))));
+    const float sig = bf16_to_f32(f32_to_bf16(sigmoid_f32(g)));
     const float act = bf16_to_f32(f32_to_bf16(g * sig));
     out[i] = f32_to_bf16(act * u);
   }
 }
 /* ---- router (src/transformer.zig:17022-17063): indices of the k largest logits (larger first, ties by lower
- * index), softmax over the row in fp32 rounded to the logits' dtype, the k entries renormalised by their rounded sum.
+ * index, as the reference's one-kernel router picks them, :17485-17500), softmax over the row in fp32 rounded to the
+ * logits' dtype, the k entries renormalised by their sum accumulated in that dtype.
  * logits are fp32 carriers (bf16 values when as_bf16). */
 QO_API void qo_moe_route(const float* logits, int64_t T, int64_t E, int64_t k, int as_bf16, int32_t* inds, float* scores) {
   unsigned char* taken = (unsigned char*)malloc((size_t)E);
@@ -101,9 +106,8 @@ QO_API void qo_moe_route(const float* logits, int64_t T, int64_t E, int64_t k, i
       float pr = expf(x[best] - mx) / sum;
       if (as_bf16) pr = bf16_to_f32(f32_to_bf16(pr));
       scores[t * k + j] = pr;
-      wsum += pr;
+      wsum = as_bf16 ? bf16_to_f32(f32_to_bf16(wsum + pr)) : wsum + pr;   /* accumulate in the input dtype (:17530-17534) */
     }
-    if (as_bf16) wsum = bf16_to_f32(f32_to_bf16(wsum));
     for (int64_t j = 0; j < k; ++j) {
       const float ns = scores[t * k + j] / wsum;
       scores[t * k + j] = as_bf16 ? bf16_to_f32(f32_to_bf16(ns)) : ns;
@@ -114,8 +118,9 @@ QO_API void qo_moe_route(const float* logits, int64_t T, int64_t E, int64_t k, i
 
 /* ---- score-weighted sum over top-k with the rows taken back from expert order
  * (src/transformer.zig:15036-15042, :15127-15140): out[t,h] = sum_j y[inv[t*k+j], h] * scores[t, j].
- * bf16 form (as_bf16 != 0): y and scores are bf16 values, each product is rounded to bf16, fp32 sum in ascending j,
- * one final rounding.  inv may be NULL (identity). */
+ * bf16 form (as_bf16 != 0): y and scores are bf16 values, each product is rounded to bf16 and added to a bf16
+ * accumulator in ascending j, rounded after every add (src/transformer.zig:20566-20571: "MLX's bf16 sum reduction
+ * accumulates in the input dtype").  inv may be NULL (identity). */
 QO_API void qo_moe_weighted_sum(const float* y, const float* scores, const int64_t* inv, int64_t T, int64_t k, int64_t H,
                                 int as_bf16, float* out) {
   for (int64_t t = 0; t < T; ++t)
@@ -125,14 +130,14 @@ QO_API void qo_moe_weighted_sum(const float* y, const float* scores, const int64
         const int64_t row = inv ? inv[t * k + j] : t * k + j;
         if (row < 0 || row >= T * k) continue;
         const float p = y[row * H + h] * scores[t * k + j];
-        acc += as_bf16 ? bf16_to_f32(f32_to_bf16(p)) : p;
+        acc = as_bf16 ? bf16_to_f32(f32_to_bf16(acc + bf16_to_f32(f32_to_bf16(p)))) : acc + p;
       }
-      out[t * H + h] = as_bf16 ? bf16_to_f32(f32_to_bf16(acc)) : acc;
+      out[t * H + h] = acc;
     }
 }
 /* fp32 form (the reference declines fp32 there and keeps the unfused chain): (g * sigmoid(g)) * u in fp32. */
 QO_API void qo_swiglu_f32(const float* gate, const float* up, float* out, int64_t n) {
-  for (int64_t i = 0; i < n; ++i) out[i] = (gate[i] * (1.0f / (1.0f + expf(-gate[i])))) * up[i];
+  for (int64_t i = 0; i < n; ++i) out[i] = (gate[i] * sigmoid_f32(gate[i])) * up[i];
 }
 /* Launchers such as torchrun export OMP_NUM_THREADS=1; a timing run may ask for the host's cores back. */
 QO_API void qo_set_num_threads(int n) {

@@ -171,7 +171,7 @@ def test_swiglu_restatement_rounding_points():
 
 def test_moe_weighted_sum_restatement():
     """Inverse permutation + score-weighted sum over top-k against plain numpy (fp32 form) and with bf16 rounding
-    of every product (bf16 form)."""
+    of every product and of the running sum (bf16 form)."""
     rng = np.random.default_rng(6)
     T, k, H = 5, 4, 16
     y = qo.bf16_round(rng.standard_normal((T * k, H)).astype(np.float32))
@@ -184,9 +184,9 @@ def test_moe_weighted_sum_restatement():
     assert np.array_equal(f, want)
     b = qo.moe_weighted_sum(y, sc, inv, as_bf16=True)
     wb = np.zeros((T, H), np.float32)
-    for j in range(k):
-        wb = wb + qo.bf16_round(y[inv.reshape(T, k)[:, j]] * sc[:, j:j + 1])
-    assert np.array_equal(b, qo.bf16_round(wb))
+    for j in range(k):   # bf16 accumulator: rounded after every add (src/transformer.zig:20566-20571)
+        wb = qo.bf16_round(wb + qo.bf16_round(y[inv.reshape(T, k)[:, j]] * sc[:, j:j + 1]))
+    assert np.array_equal(b, wb)
     assert np.array_equal(qo.moe_weighted_sum(y, sc, None, as_bf16=False), qo.moe_weighted_sum(y, sc, np.arange(T * k), as_bf16=False))
 
 
