@@ -335,6 +335,10 @@ def main():
                 if fused:   # gate and up in one launch with the SwiGLU epilogue, its result feeds the down projection
                     qb200.gather_qmm_swiglu(x_rep, *banks["gate"], *banks["up"], None, sorted_inds, 64, 4,
                                             sorted_indices=True, out=yg)
+                    if T == 1:   # single-token decode step: down projection, weighting and sum over top-k in one launch
+                        qb200.moe_down_reduce(yg.view(T, topk, I), *banks["down"], sorted_inds.view(T, topk), scores, 64, 4,
+                                              out=ysum)
+                        return
                     qb200.gather_qmm(yg, *banks["down"], None, sorted_inds, True, 64, 4, sorted_indices=True, out=yd)
                     qb200.moe_weighted_sum(yd, scores, inv, out=ysum)   # back to token order, x scores, sum over top-k
                     return

@@ -164,6 +164,19 @@ QB200_API int qb200_gather_qmm_swiglu(qb200_tensor* res, const qb200_tensor* x, 
                                       const qb200_tensor* rhs_indices, qb200_optional_int group_size,
                                       qb200_optional_int bits, const char* mode, bool sorted_indices, qb200_stream s);
 
+/* ---- down projection + router weighting + sum over top-k in one launch, for the single-token decode step ----
+ * res[t, n] = sum_j round(round(act[t, j, :] . Wdown[inds[t, j]][n, :]) * scores[t, j]), ascending j, every step
+ * rounded to the activation dtype.  Replaces gatherQmvDownReduce (src/transformer.zig:20559-20623, :20675-20761)
+ * with its rounding points: the per-slot dot product as the unfused gather_qmm would store it, the rounded product
+ * with the score, the ascending accumulate in the input dtype.  act [T, k, K] (or [T, k, 1, K]), w [E, N, K*bits/32]
+ * with scales/biases [E, N, K/gs], inds [T, k] int32/int64, scores [T, k] and res [T, N] of act's dtype (bf16/f32).
+ * Served for at most 4 tokens and 16 slots, K a multiple of 256; anything else returns QB200_ERR_UNSUPPORTED and the
+ * caller keeps qb200_gather_qmm + qb200_moe_weighted_sum (same values). */
+QB200_API int qb200_moe_down_reduce(qb200_tensor* res, const qb200_tensor* act, const qb200_tensor* w,
+                                    const qb200_tensor* scales, const qb200_tensor* biases, const qb200_tensor* inds,
+                                    const qb200_tensor* scores, qb200_optional_int group_size, qb200_optional_int bits,
+                                    const char* mode, qb200_stream s);
+
 /* ---- the router of the routed-expert block (moeRoutingChain, src/transformer.zig:17022-17063) ----
  * logits [..., T, E] (bf16 or f32, E <= 1024) -> inds [..., T, k] int32: the k largest logits of each row, larger
  * first, equal logits by lower index -- the order of the reference's one-kernel router (src/transformer.zig:17485-17500;

@@ -35,6 +35,8 @@ pub extern "c" fn qb200_gather_qmm_swiglu(res: *Tensor, x: *const Tensor, w_gate
 pub extern "c" fn qb200_moe_weighted_sum(res: *Tensor, y: *const Tensor, scores: *const Tensor, inv_order: *const Tensor, s: Stream) c_int;
 // replaces moeRoutingChain (src/transformer.zig:17022-17063): argpartition, softmax, take_along_axis, sum, divide
 pub extern "c" fn qb200_moe_route(inds: *Tensor, norm_scores: *Tensor, logits: *const Tensor, k: c_int, s: Stream) c_int;
+// replaces gatherQmvDownReduce (src/transformer.zig:20559-20623, :20675-20761); returns 1 (declined) beyond 4 tokens: keep qb200_gather_qmm + qb200_moe_weighted_sum then
+pub extern "c" fn qb200_moe_down_reduce(res: *Tensor, act: *const Tensor, w: *const Tensor, scales: *const Tensor, biases: *const Tensor, inds: *const Tensor, scores: *const Tensor, group_size: OptionalInt, bits: OptionalInt, mode: [*:0]const u8, s: Stream) c_int;
 // replaces mlx_dequantize (src/mlx.zig:271)
 pub extern "c" fn qb200_dequantize(res: *Tensor, w: *const Tensor, scales: *const Tensor, biases: *const Tensor, group_size: OptionalInt, bits: OptionalInt, mode: [*:0]const u8, global_scale: *const Tensor, dtype: OptionalDtype, s: Stream) c_int;
 // replaces mlx_quantize (src/mlx.zig:275); results in mlx-c's vector order [q, scales, biases]

@@ -509,6 +509,55 @@ QB200_API int qb200_gather_qmm_swiglu(qb200_tensor* res, const qb200_tensor* x, 
   return QB200_OK;
 }
 
+QB200_API int qb200_moe_down_reduce(qb200_tensor* res, const qb200_tensor* act, const qb200_tensor* w,
+                                    const qb200_tensor* scales, const qb200_tensor* biases, const qb200_tensor* inds,
+                                    const qb200_tensor* scores, qb200_optional_int group_size, qb200_optional_int bits,
+                                    const char* mode, qb200_stream s) {
+  int gs, nb, st;
+  if ((st = resolve_mode(mode, group_size, bits, &gs, &nb))) return st;
+  if ((st = check_tensor(res, "res", 1)) || (st = check_tensor(act, "act", 2)) || (st = check_tensor(w, "w", 3)) ||
+      (st = check_tensor(scales, "scales", 3)) || (st = check_tensor(biases, "biases", 3)) ||
+      (st = check_tensor(inds, "inds", 1)) || (st = check_tensor(scores, "scores", 1)))
+    return st;
+  if (w->ndim != 3 || scales->ndim != 3 || biases->ndim != 3)
+    return fail(QB200_ERR_UNSUPPORTED, "moe_down_reduce: w, scales, biases must be [E, N, *]");
+  if (w->dtype != QB200_UINT32 || scales->dtype != QB200_BFLOAT16 || biases->dtype != QB200_BFLOAT16)
+    return fail(QB200_ERR_BAD_DTYPE, "moe_down_reduce: w must be uint32 with bf16 scales and biases");
+  if (act->dtype != QB200_BFLOAT16 && act->dtype != QB200_FLOAT32)
+    return fail(QB200_ERR_UNSUPPORTED, "moe_down_reduce: act must be bf16 or f32");
+  if (res->dtype != act->dtype || scores->dtype != act->dtype)
+    return fail(QB200_ERR_BAD_DTYPE, "moe_down_reduce: act, scores and res must share a dtype");
+  if (!is_index_dtype(inds->dtype)) return fail(QB200_ERR_BAD_DTYPE, "moe_down_reduce: inds must be int32/uint32/int64");
+  if (!fully_contiguous(w) || !fully_contiguous(scales) || !fully_contiguous(biases) || !fully_contiguous(act) ||
+      !fully_contiguous(res) || !fully_contiguous(inds) || !fully_contiguous(scores))
+    return fail(QB200_ERR_BAD_STRIDE, "moe_down_reduce: tensors must be contiguous");
+  const int vpw = 32 / nb;
+  const int64_t E = w->shape[0], N = w->shape[1], K = w->shape[2] * vpw;
+  const int64_t topk = scores->shape[scores->ndim - 1];
+  const int64_t T = topk > 0 ? numel(scores) / topk : 0;
+  if (act->shape[act->ndim - 1] != K || numel(act) != T * topk * K)
+    return fail(QB200_ERR_BAD_SHAPE, "moe_down_reduce: act must be [T, k, K] (or [T, k, 1, K]) for scores [T, k]");
+  if (numel(inds) != T * topk) return fail(QB200_ERR_BAD_SHAPE, "moe_down_reduce: inds must be [T, k]");
+  if (K % gs != 0 || scales->shape[0] != E || scales->shape[1] != N || scales->shape[2] != K / gs ||
+      biases->shape[0] != E || biases->shape[1] != N || biases->shape[2] != K / gs)
+    return fail(QB200_ERR_BAD_SHAPE, "moe_down_reduce: scales/biases must be [E, N, K/group_size]");
+  if (res->shape[res->ndim - 1] != N || numel(res) != T * N)
+    return fail(QB200_ERR_BAD_SHAPE, "moe_down_reduce: res must be [T, N]");
+  if (T == 0 || N == 0) return QB200_OK;
+  MoeDownReduceArgs a;
+  a.act = act->data; a.w = (const uint32_t*)w->data; a.s = scales->data; a.b = biases->data; a.y = res->data;
+  a.inds = inds->data; a.scores = scores->data; a.inds_i64 = inds->dtype == QB200_INT64;
+  a.T = T; a.N = N; a.K = K; a.E = E; a.wes = N * w->shape[2]; a.ses = N * (K / gs);
+  a.topk = (int)topk; a.gs = gs; a.bits = nb; a.dtype = act->dtype;
+  // Every token streams its own k experts: meant for the single-token decode step (a few tokens at most); wider
+  // batches are declined and keep gather_qmm + moe_weighted_sum, which read each expert once for all its rows.
+  if (T > 4 || topk > 16 || !moe_down_reduce_supported(a))
+    return fail(QB200_ERR_UNSUPPORTED, "moe_down_reduce: shape not served by the fused kernel");
+  const cudaError_t e = launch_moe_down_reduce(a, (cudaStream_t)s);
+  if (e != cudaSuccess) return cuda_fail(e, "moe_down_reduce");
+  return QB200_OK;
+}
+
 QB200_API int qb200_moe_route(qb200_tensor* inds, qb200_tensor* norm_scores, const qb200_tensor* logits, int k,
                               qb200_stream s) {
   int st;

@@ -36,6 +36,17 @@ struct MoeRouteArgs {
 };
 cudaError_t launch_moe_route(const MoeRouteArgs& a, cudaStream_t st);
 
+// ---- moe_down_reduce.cu: down projection + router weighting + sum over top-k for a few tokens ----
+struct MoeDownReduceArgs {
+  const void* act; const uint32_t* w; const void* s; const void* b; void* y;
+  const void* inds; const void* scores;
+  int inds_i64;
+  int64_t T, N, K, E, wes, ses;
+  int topk, gs, bits, dtype;
+};
+bool moe_down_reduce_supported(const MoeDownReduceArgs& a);
+cudaError_t launch_moe_down_reduce(const MoeDownReduceArgs& a, cudaStream_t st);
+
 struct QuantArgs {
   const void* x; uint32_t* q; void* s; void* b;
   RowMap xmap, qmap, sbmap;

@@ -129,6 +129,14 @@ inline void gatherExpertGateUpSwiGLU(Array& res, const Array& x, const QWeight& 
                                 "affine", sorted_indices, s));
 }
 
+// gatherQmvDownReduce (src/transformer.zig:20559-20623, :20675-20761): the single-token tail of the routed-expert block,
+// res[t, n] = sum_j round(round(act[t, j] . down[inds[t, j]][n]) * scores[t, j]).  Throws Declined beyond a few tokens.
+inline void gatherQmvDownReduce(Array& res, const Array& act, const QWeight& down, const Array& inds, const Array& scores,
+                                qb200_stream s) {
+  check(qb200_moe_down_reduce(&res.t, &act.t, &down.q.t, &down.scales.t, &down.biases.t, &inds.t, &scores.t,
+                              some(down.group_size), some(down.bits), "affine", s));
+}
+
 // moeRoutingChain (src/transformer.zig:17022-17063): the k largest logits per row and their renormalised softmax scores.
 inline void moeRoutingChain(Array& inds, Array& norm_scores, const Array& router_logits, int k, qb200_stream s) {
   check(qb200_moe_route(&inds.t, &norm_scores.t, &router_logits.t, k, s));

@@ -80,6 +80,7 @@ def lib():
         L.qb200_gather_qmm_swiglu.argtypes = [TP] * 10 + [OptInt, OptInt, C.c_char_p, C.c_bool, C.c_void_p]
         L.qb200_moe_weighted_sum.argtypes = [TP, TP, TP, TP, C.c_void_p]
         L.qb200_moe_route.argtypes = [TP, TP, TP, C.c_int, C.c_void_p]
+        L.qb200_moe_down_reduce.argtypes = [TP] * 7 + [OptInt, OptInt, C.c_char_p, C.c_void_p]
         L.qb200_dequantize.argtypes = [TP, TP, TP, TP, OptInt, OptInt, C.c_char_p, TP, OptDtype, C.c_void_p]
         L.qb200_quantize.argtypes = [TP, TP, TP, TP, OptInt, OptInt, C.c_char_p, TP, C.c_void_p]
         L.qb200_kv_append.argtypes = [TP, TP, TP, TP, C.c_int64, C.c_int, C.c_int, C.c_void_p]
@@ -91,7 +92,7 @@ def lib():
         L.qb200_kv_decode_attention_noalloc_max_scratch.restype = C.c_size_t
         L.qb200_kv_decode_attention_workspace_size.restype = C.c_size_t
         L.qb200_kv_decode_attention_workspace_size.argtypes = [C.c_int64] * 5
-        for name in ("qb200_quantized_matmul", "qb200_quantized_matmul_batch", "qb200_quantized_matmul_shape", "qb200_gather_qmm", "qb200_gather_qmm_swiglu", "qb200_moe_weighted_sum", "qb200_moe_route", "qb200_dequantize",
+        for name in ("qb200_quantized_matmul", "qb200_quantized_matmul_batch", "qb200_quantized_matmul_shape", "qb200_gather_qmm", "qb200_gather_qmm_swiglu", "qb200_moe_weighted_sum", "qb200_moe_route", "qb200_moe_down_reduce", "qb200_dequantize",
                      "qb200_quantize", "qb200_kv_append", "qb200_kv_decode_attention"):
             getattr(L, name).restype = C.c_int
         _lib = L
@@ -200,6 +201,18 @@ def gather_qmm_swiglu(x, w_gate, scales_gate, biases_gate, w_up, scales_up, bias
     check(L.qb200_gather_qmm_swiglu(C.byref(do), C.byref(dx), C.byref(dg), C.byref(dgs), C.byref(dgb), C.byref(du),
                                     C.byref(dus), C.byref(dub), C.byref(dl), C.byref(dr), _opt(group_size), _opt(bits),
                                     mode.encode(), sorted_indices, _stream()))
+    return out
+
+
+def moe_down_reduce(act, w, scales, biases, inds, scores, group_size=None, bits=None, mode="affine", out=None):
+    """gatherQmvDownReduce (src/transformer.zig:20559-20623): down projection of every slot, times its score, summed
+    over top-k.  act [T, k, K], inds/scores [T, k] -> [T, N]."""
+    L = lib()
+    if out is None:
+        out = torch.empty(list(scores.shape[:-1]) + [w.shape[-2]], dtype=act.dtype, device=act.device)
+    check(L.qb200_moe_down_reduce(C.byref(desc(out)), C.byref(desc(act)), C.byref(_packed(w)), C.byref(desc(scales)),
+                                  C.byref(desc(biases)), C.byref(desc(inds)), C.byref(desc(scores)), _opt(group_size),
+                                  _opt(bits), mode.encode(), _stream()))
     return out
 
 

@@ -325,3 +325,55 @@ def test_moe_route_matches_the_oracle(T, E, k):
     assert np.array_equal(i32.cpu().numpy(), ir)
     assert np.allclose(s32.cpu().numpy(), sr, rtol=2e-6, atol=1e-9)
     assert np.allclose(s32.cpu().numpy().sum(-1), 1.0, atol=1e-5)
+
+
+@pytest.mark.parametrize("T,bits,gs,H,I", [(1, 4, 64, 2048, 768), (3, 8, 64, 512, 512), (2, 4, 128, 1000, 1024)])
+def test_moe_down_reduce_matches_the_unfused_tail(T, bits, gs, H, I):
+    """qb200_moe_down_reduce (the reference's gatherQmvDownReduce, src/transformer.zig:20559-20623) against the
+    library's own gather_qmm + moe_weighted_sum (same rounding points; the dot products may differ in their last fp32
+    bits where the unfused kernel splits K over warps) and against the oracle chain."""
+    import qb200
+    E, k = 32, 8
+    rng = np.random.default_rng(0xD0 + T + bits + H)
+    q, s, b = make_weight(rng, (E, H, I), gs, bits)
+    dw = dev_triple(q, s, b)
+    inds = _route(rng, T, E, k)
+    inds[0, 2] = E + 3 if T > 1 else inds[0, 2]          # an out-of-range expert contributes nothing
+    scores = qo.bf16_round(rng.random((T, k)).astype(np.float32))
+    act = rand_bf16(rng, (T, k, I))
+    a16 = to_dev_bf16(qo.f32_to_bf16(act))
+    s16 = to_dev_bf16(qo.f32_to_bf16(scores))
+    idx = torch.from_numpy(inds).cuda()
+    got = qb200.moe_down_reduce(a16, *dw, idx, s16, gs, bits)
+    assert got.dtype == torch.bfloat16 and tuple(got.shape) == (T, H)
+    # the unfused tail on the GPU (rows of out-of-range experts are left untouched by gather_qmm: start from zeros)
+    d16 = torch.zeros((T * k, 1, H), dtype=torch.bfloat16, device="cuda")
+    qb200.gather_qmm(a16.view(T * k, 1, I), *dw, None, idx.view(-1), True, gs, bits, out=d16)
+    want = qb200.moe_weighted_sum(d16, s16, None).float().cpu().numpy()
+    g = got.float().cpu().numpy()
+    assert (g != want).mean() < 0.02
+    assert np.abs(g - want).max() <= 2.0 ** -6 * np.abs(want).max()
+    # oracle chain
+    keep = (inds.reshape(-1) < E)
+    rows = qo.gather_qmm(act.reshape(T * k, 1, I), q, s, b, np.arange(T * k), np.where(keep, inds.reshape(-1), 0), gs, bits)
+    rows = qo.bf16_round(rows.reshape(T * k, H)) * keep[:, None]
+    ref = qo.moe_weighted_sum(rows, scores, None, as_bf16=True)
+    rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+    assert np.abs(g - ref).max() <= 2.0 ** -6 * np.abs(ref).max() + 1e-2 * rms
+    # fp32 form
+    g32 = qb200.moe_down_reduce(torch.from_numpy(act).cuda(), *dw, idx, torch.from_numpy(scores).cuda(), gs, bits)
+    rows32 = qo.gather_qmm(act.reshape(T * k, 1, I), q, s, b, np.arange(T * k), np.where(keep, inds.reshape(-1), 0), gs, bits)
+    ref32 = qo.moe_weighted_sum(rows32.reshape(T * k, H) * keep[:, None], scores, None, as_bf16=False)
+    gate_f32(g32.cpu().numpy(), ref32, "down+reduce fp32")
+
+
+def test_moe_down_reduce_declines_wide_batches():
+    import qb200
+    rng = np.random.default_rng(3)
+    q, s, b = make_weight(rng, (4, 64, 256), 64, 4)
+    dw = dev_triple(q, s, b)
+    act = to_dev_bf16(qo.f32_to_bf16(rand_bf16(rng, (8, 2, 256))))
+    sc = to_dev_bf16(qo.f32_to_bf16(rand_bf16(rng, (8, 2))))
+    with pytest.raises(qb200.Qb200Error) as ei:
+        qb200.moe_down_reduce(act, *dw, torch.zeros((8, 2), dtype=torch.int32, device="cuda"), sc, 64, 4)
+    assert ei.value.status == 1
