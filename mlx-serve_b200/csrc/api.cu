@@ -463,7 +463,9 @@ QB200_API int qb200_gather_qmm(qb200_tensor* res, const qb200_tensor* x, const q
   // Few rows per expert: stream every hit expert once.  Many sorted rows (MoE prefill): grouped GEMM on the
   // tensor-core kernel, from 32 rows per expert on average.
   const bool many = a.I >= 32 * a.E && a.I >= 1024;
-  if (many && gather_tc_supported(a)) e = launch_gather_tc(a, (cudaStream_t)s);
+  // Up to 16 rows (single-token decode: every row its own expert): a CTA per (row, 16 output rows).
+  if (gather_small_supported(a)) e = launch_gather_small(a, (cudaStream_t)s);
+  else if (many && gather_tc_supported(a)) e = launch_gather_tc(a, (cudaStream_t)s);
   else if (gather_stream_supported(a)) e = launch_gather_stream(a, (cudaStream_t)s);
   else if (gather_tc_supported(a) && a.I >= 1024) e = launch_gather_tc(a, (cudaStream_t)s);
   else if (gather_mma_supported(a)) e = launch_gather_mma(a, (cudaStream_t)s);
@@ -502,9 +504,10 @@ QB200_API int qb200_gather_qmm_swiglu(qb200_tensor* res, const qb200_tensor* x, 
   a.w2 = (const uint32_t*)w_up->data; a.s2 = scales_up->data; a.b2 = biases_up->data;
   // Declined shapes leave the caller on the unfused chain (two gather_qmm calls and its own SwiGLU), as the
   // reference's fused path does (src/transformer.zig:19925-19931).
-  if (!gather_stream_supported(a) || (((uintptr_t)a.w2) & 15) != 0 || (((uintptr_t)a.s2) & 7) != 0 || (((uintptr_t)a.b2) & 7) != 0)
+  const bool small = gather_small_supported(a);
+  if (!small && (!gather_stream_supported(a) || (((uintptr_t)a.w2) & 15) != 0 || (((uintptr_t)a.s2) & 7) != 0 || (((uintptr_t)a.b2) & 7) != 0))
     return fail(QB200_ERR_UNSUPPORTED, "gather_qmm_swiglu: shape not served by the fused streaming kernel");
-  const cudaError_t e = launch_gather_stream(a, (cudaStream_t)s);
+  const cudaError_t e = small ? launch_gather_small(a, (cudaStream_t)s) : launch_gather_stream(a, (cudaStream_t)s);
   if (e != cudaSuccess) return cuda_fail(e, "gather_qmm_swiglu");
   return QB200_OK;
 }

@@ -556,6 +556,8 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
 // src/transformer.zig:19853-19885); filled from the host once per device.
 __device__ uint16_t g_sigtab[1 << 16];
 
+}  // namespace
+
 const uint16_t* sigmoid_table(cudaStream_t st, cudaError_t* err) {
   static const uint16_t* ptr[64] = {};
   int dev = 0;
@@ -589,6 +591,8 @@ const uint16_t* sigmoid_table(cudaStream_t st, cudaError_t* err) {
   *err = cudaSuccess;
   return ptr[dev];
 }
+
+namespace {
 
 int sm_count_g() {
   static int cached[64] = {};

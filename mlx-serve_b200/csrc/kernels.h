@@ -107,6 +107,11 @@ struct GatherArgs {
 bool gather_mma_supported(const GatherArgs& a);
 cudaError_t launch_gather_mma(const GatherArgs& a, cudaStream_t st);
 cudaError_t launch_gather_generic(const GatherArgs& a, cudaStream_t st);
+// sigmoid of every bf16 bit pattern as bf16 (device table, uploaded on first use; null + *err when that fails)
+const uint16_t* sigmoid_table(cudaStream_t st, cudaError_t* err);
+// few rows, each with its own expert (single-token decode): a CTA per (row, 16 output rows), moe_down_reduce.cu
+bool gather_small_supported(const GatherArgs& a);
+cudaError_t launch_gather_small(const GatherArgs& a, cudaStream_t st);
 bool gather_stream_supported(const GatherArgs& a);   // qmv_stream.cu: persistent streaming kernel, gather form
 cudaError_t launch_gather_stream(const GatherArgs& a, cudaStream_t st);
 
