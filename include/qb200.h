@@ -101,6 +101,9 @@ QB200_API const char* qb200_version(void);
 /* Diagnostic without a reference counterpart: 0, or the code of the bounded barrier wait that
  * expired inside the tensor-core prefill kernel (synchronises the device). */
 QB200_API int qb200_debug_tc_status(void);
+/* Clears that code (it is sticky: once set it stays until cleared).  A host should read the status once per step
+ * after its stream synchronisation -- a non-zero code means a result of that step is incomplete -- and clear it. */
+QB200_API void qb200_debug_tc_reset(void);
 
 /* ---- mlx_quantized_matmul (src/mlx.zig:262) ----
  * transpose_w = true : y[..., m, n] = sum_k x[..., m, k] * What[..., n, k]
@@ -186,6 +189,20 @@ QB200_API int qb200_moe_down_reduce(qb200_tensor* res, const qb200_tensor* act, 
 QB200_API int qb200_moe_route(qb200_tensor* inds, qb200_tensor* norm_scores, const qb200_tensor* logits, int k,
                               qb200_stream s);
 
+/* ---- sort of the routed-expert block's index list by expert (moeMLP2, src/transformer.zig:14961-15006) ----
+ * inds [..., T, k] (int32/uint32/int64, flattened to n = T*k entries) -> all int32 [n], each optional (pass an
+ * empty tensor to skip it):
+ *   order        = argsort(flat_inds), stable: equal experts keep their original order (mlx_argsort_axis, :14972);
+ *   inv_order    = argsort(order) (:14975), the row of entry i after sorting;
+ *   sorted_inds  = flat_inds[order] (:14980), the rhs_indices of the three gather_qmm calls;
+ *   token_rows   = order / k (:14983-14987), the lhs_indices that stand for the x_rep gather (:14995-15005);
+ *   expert_offsets [num_experts + 1]: rows of expert e are [offsets[e], offsets[e+1]) (no counterpart in the
+ *                  reference; the expert-parallel exchange cuts the sorted list by it).
+ * One launch (a counting sort).  Index values outside [0, num_experts) sort behind every expert; num_experts <= 1024. */
+QB200_API int qb200_moe_sort_by_expert(qb200_tensor* order, qb200_tensor* inv_order, qb200_tensor* sorted_inds,
+                                       qb200_tensor* token_rows, qb200_tensor* expert_offsets, const qb200_tensor* inds,
+                                       int num_experts, qb200_stream s);
+
 /* ---- the tail of the routed-expert block: rows back to token order, times the scores, summed over top-k ----
  * res[t, h] = sum_j round(y[inv_order[t*k + j], h] * scores[t, j]).  Replaces mlx_take_axis(inv_order) +
  * mlx_multiply(norm_scores) + mlx_sum_axis(-2) of moeMLP2 (src/transformer.zig:15036-15042, :15127-15140).
@@ -240,6 +257,25 @@ QB200_API int qb200_kv_decode_attention(qb200_tensor* res, const qb200_tensor* q
                                         qb200_stream s);
 QB200_API size_t qb200_kv_decode_attention_workspace_size(int64_t B, int64_t Hq, int64_t Hkv, int64_t T,
                                                           int64_t Dv);
+
+/* ---- the same attention over a batch whose sequences own separate caches ----
+ * The reference's slots each hold a B = 1 cache with its own capacity and length (src/scheduler.zig:463-480); its
+ * batched decode dequantises every slot's cache, pads to the longest and concatenates before one attention call
+ * (forwardBatchedDecode, src/transformer.zig:9742-9792; padAndStackBatchedKV, :10165-10211; buildBatchedDecodeMask,
+ * :10216-10249).  Here the packed views are read in place: k_q[b] ... v_biases[b] are the six views of sequence b,
+ * each [1, Hkv, T_b, last] with its own strides and its own length T_b; q is [num_seqs, Hq, 1, D], res
+ * [num_seqs, Hq, 1, Dv].  mask_arr (mode "array") broadcasts to [num_seqs, 1, 1, T_max] with T_max the longest
+ * view; kv_lens, when given, further limits sequence b to its first kv_lens[b] positions.  The descriptors are read
+ * on the host during the call (they need not outlive it).  Workspace: qb200_kv_decode_attention_ptrs_workspace_size. */
+QB200_API int qb200_kv_decode_attention_ptrs(qb200_tensor* res, const qb200_tensor* q, const qb200_tensor* const* k_q,
+                                             const qb200_tensor* const* k_scales, const qb200_tensor* const* k_biases,
+                                             const qb200_tensor* const* v_q, const qb200_tensor* const* v_scales,
+                                             const qb200_tensor* const* v_biases, int num_seqs, int bits, int group_size,
+                                             float scale, const char* mask_mode, const qb200_tensor* mask_arr,
+                                             const qb200_tensor* kv_lens, void* workspace, size_t workspace_bytes,
+                                             qb200_stream s);
+QB200_API size_t qb200_kv_decode_attention_ptrs_workspace_size(int64_t num_seqs, int64_t Hq, int64_t Hkv, int64_t T_max,
+                                                               int64_t Dv);
 
 /* ---- the same attention for callers that cannot allocate device memory ----
  * No counterpart in the reference (MLX allocates its own temporaries).  Identical arguments and

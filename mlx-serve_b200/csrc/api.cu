@@ -221,6 +221,7 @@ QB200_API void qb200_set_error_handler(qb200_error_handler_func handler, void* d
 QB200_API const char* qb200_last_error(void) { return g_last_error.c_str(); }
 QB200_API const char* qb200_version(void) { return "qb200 0.1 (sm_100a)"; }
 QB200_API int qb200_debug_tc_status(void) { return qmm_tc_error_code(); }
+QB200_API void qb200_debug_tc_reset(void) { qmm_tc_error_reset(); }
 
 QB200_API int qb200_quantized_matmul_shape(const qb200_tensor* x, const qb200_tensor* w, const qb200_tensor* scales,
                                            bool transpose_w, qb200_optional_int group_size, qb200_optional_int bits,
@@ -589,6 +590,44 @@ QB200_API int qb200_moe_route(qb200_tensor* inds, qb200_tensor* norm_scores, con
   return QB200_OK;
 }
 
+QB200_API int qb200_moe_sort_by_expert(qb200_tensor* order, qb200_tensor* inv_order, qb200_tensor* sorted_inds,
+                                       qb200_tensor* token_rows, qb200_tensor* expert_offsets, const qb200_tensor* inds,
+                                       int num_experts, qb200_stream s) {
+  int st;
+  if ((st = check_tensor(inds, "inds", 1))) return st;
+  if (!is_index_dtype(inds->dtype)) return fail(QB200_ERR_BAD_DTYPE, "moe_sort_by_expert: inds must be int32/uint32/int64");
+  if (!fully_contiguous(inds)) return fail(QB200_ERR_BAD_STRIDE, "moe_sort_by_expert: inds must be contiguous");
+  if (num_experts < 1 || num_experts > 1024) return fail(QB200_ERR_UNSUPPORTED, "moe_sort_by_expert: 1..1024 experts are served");
+  const int64_t n = numel(inds), topk = inds->shape[inds->ndim - 1];
+  if (n >= (int64_t)1 << 24) return fail(QB200_ERR_UNSUPPORTED, "moe_sort_by_expert: at most 2^24 - 1 index entries");
+  MoeSortArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.inds = inds->data; a.inds_i64 = inds->dtype == QB200_INT64; a.n = n; a.E = num_experts; a.topk = (int)(topk > 0 ? topk : 1);
+  qb200_tensor* outs[4] = {order, inv_order, sorted_inds, token_rows};
+  const char* names[4] = {"order", "inv_order", "sorted_inds", "token_rows"};
+  int** dst[4] = {&a.order, &a.inv_order, &a.sorted_inds, &a.token_rows};
+  for (int i = 0; i < 4; ++i) {
+    if (is_empty(outs[i])) continue;
+    if ((st = check_tensor(outs[i], names[i], 1))) return st;
+    if (outs[i]->dtype != QB200_INT32 && outs[i]->dtype != QB200_UINT32)
+      return fail(QB200_ERR_BAD_DTYPE, "moe_sort_by_expert: %s must be int32/uint32", names[i]);
+    if (numel(outs[i]) != n || !fully_contiguous(outs[i]))
+      return fail(QB200_ERR_BAD_SHAPE, "moe_sort_by_expert: %s must hold one contiguous entry per index", names[i]);
+    *dst[i] = (int*)outs[i]->data;
+  }
+  if (!is_empty(expert_offsets)) {
+    if ((st = check_tensor(expert_offsets, "expert_offsets", 1))) return st;
+    if (expert_offsets->dtype != QB200_INT32 && expert_offsets->dtype != QB200_UINT32)
+      return fail(QB200_ERR_BAD_DTYPE, "moe_sort_by_expert: expert_offsets must be int32/uint32");
+    if (numel(expert_offsets) != (int64_t)num_experts + 1 || !fully_contiguous(expert_offsets))
+      return fail(QB200_ERR_BAD_SHAPE, "moe_sort_by_expert: expert_offsets must be [num_experts + 1]");
+    a.offsets = (int*)expert_offsets->data;
+  }
+  const cudaError_t e = launch_moe_sort(a, (cudaStream_t)s);
+  if (e != cudaSuccess) return cuda_fail(e, "moe_sort_by_expert");
+  return QB200_OK;
+}
+
 QB200_API int qb200_moe_weighted_sum(qb200_tensor* res, const qb200_tensor* y, const qb200_tensor* scores,
                                      const qb200_tensor* inv_order, qb200_stream s) {
   int st;
@@ -719,6 +758,40 @@ QB200_API int qb200_kv_append(qb200_tensor* cache_q, qb200_tensor* cache_scales,
   return quantize_impl(&vq, &vs, &vb, dense, gs, nb, s, "kv_append");
 }
 
+// Mask mode, additive mask row and per-sequence lengths of the decode attention entries (T = the longest view).
+static int parse_kv_mask(KvAttnArgs& a, const qb200_tensor* q, const char* mask_mode, const qb200_tensor* mask_arr,
+                         const qb200_tensor* kv_lens, int64_t B, int64_t T) {
+  int st;
+  const char* mm = mask_mode ? mask_mode : "";
+  if (std::strcmp(mm, "array") == 0) {
+    if (is_empty(mask_arr)) return fail(QB200_ERR_BAD_ARG, "kv_decode_attention: mask_mode \"array\" needs mask_arr");
+    if ((st = check_tensor(mask_arr, "mask_arr", 1))) return st;
+    if (mask_arr->dtype != q->dtype && mask_arr->dtype != QB200_FLOAT32)
+      return fail(QB200_ERR_BAD_DTYPE, "kv_decode_attention: mask must be q's dtype or f32");
+    if (mask_arr->shape[mask_arr->ndim - 1] != T)
+      return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: mask last dim %lld != T %lld",
+                  (long long)mask_arr->shape[mask_arr->ndim - 1], (long long)T);
+    // additive row broadcastable to [B, 1, 1, T]: every dim but the last (and an optional batch dim) is 1
+    int64_t bstride = 0;
+    for (int d = 0; d < mask_arr->ndim - 1; ++d) {
+      if (mask_arr->shape[d] == 1) continue;
+      if (d == mask_arr->ndim - 4 && mask_arr->shape[d] == B) { bstride = mask_arr->stride[d]; continue; }
+      if (mask_arr->ndim < 4 && d == 0 && mask_arr->shape[d] == B && mask_arr->ndim == 2) { bstride = mask_arr->stride[d]; continue; }
+      return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention: mask must broadcast as [B|1, 1, 1, T]");
+    }
+    a.mask = mask_arr->data; a.mask_dtype = mask_arr->dtype; a.mask_bstride = bstride;
+  } else if (std::strcmp(mm, "") != 0 && std::strcmp(mm, "causal") != 0) {
+    return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention: mask_mode '%s' is not served", mm);
+  }
+  if (!is_empty(kv_lens)) {
+    if ((st = check_tensor(kv_lens, "kv_lens", 1))) return st;
+    if (kv_lens->dtype != QB200_INT32 || kv_lens->ndim != 1 || kv_lens->shape[0] != B)
+      return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: kv_lens must be int32 [B]");
+    a.kv_lens = (const int32_t*)kv_lens->data;
+  }
+  return 0;
+}
+
 QB200_API size_t qb200_kv_decode_attention_workspace_size(int64_t B, int64_t Hq, int64_t Hkv, int64_t T, int64_t Dv) {
   return kv_attn_workspace_bytes(B, Hq, Hkv, T, Dv);
 }
@@ -784,43 +857,131 @@ QB200_API int qb200_kv_decode_attention(qb200_tensor* res, const qb200_tensor* q
     a.vq_str[d] = v_q->stride[d]; a.vsb_str[d] = v_scales->stride[d];
   }
   a.gs = gs; a.bits = nb; a.scale = scale;
-  const char* mm = mask_mode ? mask_mode : "";
-  if (std::strcmp(mm, "array") == 0) {
-    if (is_empty(mask_arr)) return fail(QB200_ERR_BAD_ARG, "kv_decode_attention: mask_mode \"array\" needs mask_arr");
-    if ((st = check_tensor(mask_arr, "mask_arr", 1))) return st;
-    if (mask_arr->dtype != q->dtype && mask_arr->dtype != QB200_FLOAT32)
-      return fail(QB200_ERR_BAD_DTYPE, "kv_decode_attention: mask must be q's dtype or f32");
-    if (mask_arr->shape[mask_arr->ndim - 1] != T)
-      return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: mask last dim %lld != T %lld",
-                  (long long)mask_arr->shape[mask_arr->ndim - 1], (long long)T);
-    // additive row broadcastable to [B, 1, 1, T]: every dim but the last (and an optional batch dim) is 1
-    int64_t bstride = 0;
-    for (int d = 0; d < mask_arr->ndim - 1; ++d) {
-      if (mask_arr->shape[d] == 1) continue;
-      if (d == mask_arr->ndim - 4 && mask_arr->shape[d] == B) { bstride = mask_arr->stride[d]; continue; }
-      if (mask_arr->ndim < 4 && d == 0 && mask_arr->shape[d] == B && mask_arr->ndim == 2) { bstride = mask_arr->stride[d]; continue; }
-      return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention: mask must broadcast as [B|1, 1, 1, T]");
-    }
-    a.mask = mask_arr->data; a.mask_dtype = mask_arr->dtype; a.mask_bstride = bstride;
-  } else if (std::strcmp(mm, "") != 0 && std::strcmp(mm, "causal") != 0) {
-    return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention: mask_mode '%s' is not served", mm);
-  }
-  if (!is_empty(kv_lens)) {
-    if ((st = check_tensor(kv_lens, "kv_lens", 1))) return st;
-    if (kv_lens->dtype != QB200_INT32 || kv_lens->ndim != 1 || kv_lens->shape[0] != B)
-      return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: kv_lens must be int32 [B]");
-    a.kv_lens = (const int32_t*)kv_lens->data;
-  }
+  if ((st = parse_kv_mask(a, q, mask_mode, mask_arr, kv_lens, B, T))) return st;
   a.workspace = workspace; a.workspace_bytes = workspace_bytes;
   if (B == 0 || Hq == 0 || Dv == 0) return QB200_OK;
+  // An empty cache view has no softmax to take; it is refused here, before the workspace check and before any
+  // launch, so that no kernel is ever planned for zero tokens.
+  if (T <= 0) return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: the cache view holds no tokens (T = %lld)", (long long)T);
   if (!kv_attn_supported(a))
     return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention: geometry not served (D=%lld Dv=%lld gs=%d gqa=%lld)",
                 (long long)D, (long long)Dv, gs, (long long)(Hq / Hkv));
   const size_t need = kv_attn_workspace_bytes(B, Hq, Hkv, T, Dv);
-  if (need > 0 && (workspace == nullptr || workspace_bytes < need))
+  if (need == 0 || workspace == nullptr || workspace_bytes < need)
     return fail(QB200_ERR_WORKSPACE, "kv_decode_attention: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
   cudaError_t e = launch_kv_attn(a, (cudaStream_t)s);
   if (e != cudaSuccess) return cuda_fail(e, "kv_decode_attention");
+  return QB200_OK;
+}
+
+QB200_API size_t qb200_kv_decode_attention_ptrs_workspace_size(int64_t num_seqs, int64_t Hq, int64_t Hkv, int64_t T_max,
+                                                               int64_t Dv) {
+  size_t need = 0;
+  for (int64_t b0 = 0; b0 < num_seqs; b0 += kMaxSeqPtrs) {
+    const int64_t nb = num_seqs - b0 < kMaxSeqPtrs ? num_seqs - b0 : kMaxSeqPtrs;
+    const size_t n = kv_attn_workspace_bytes(nb, Hq, Hkv, T_max, Dv);
+    need = n > need ? n : need;
+  }
+  return need;
+}
+
+QB200_API int qb200_kv_decode_attention_ptrs(qb200_tensor* res, const qb200_tensor* q, const qb200_tensor* const* k_q,
+                                             const qb200_tensor* const* k_scales, const qb200_tensor* const* k_biases,
+                                             const qb200_tensor* const* v_q, const qb200_tensor* const* v_scales,
+                                             const qb200_tensor* const* v_biases, int num_seqs, int bits, int group_size,
+                                             float scale, const char* mask_mode, const qb200_tensor* mask_arr,
+                                             const qb200_tensor* kv_lens, void* workspace, size_t workspace_bytes,
+                                             qb200_stream s) {
+  int gs, nb, st;
+  qb200_optional_int og = {group_size, true}, ob = {bits, true};
+  if ((st = resolve_mode("affine", og, ob, &gs, &nb))) return st;
+  if (nb == 2) return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention_ptrs: bits must be 4 or 8");
+  if ((st = check_tensor(res, "res", 4)) || (st = check_tensor(q, "q", 4))) return st;
+  if (res->ndim != 4 || q->ndim != 4) return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention_ptrs: q and res must be 4-D");
+  if (num_seqs < 0 || (num_seqs > 0 && (!k_q || !k_scales || !k_biases || !v_q || !v_scales || !v_biases)))
+    return fail(QB200_ERR_BAD_ARG, "kv_decode_attention_ptrs: null view list");
+  if (q->dtype != QB200_BFLOAT16 && q->dtype != QB200_FLOAT32)
+    return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention_ptrs: q must be bf16 or f32");
+  if (res->dtype != q->dtype) return fail(QB200_ERR_BAD_DTYPE, "kv_decode_attention_ptrs: res dtype must equal q dtype");
+  const int64_t B = q->shape[0], Hq = q->shape[1], Tq = q->shape[2], D = q->shape[3];
+  if (B != num_seqs) return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention_ptrs: q holds %lld sequences, %d views given", (long long)B, num_seqs);
+  if (Tq != 1) return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention_ptrs: T_q=%lld (only decode width 1 is served)", (long long)Tq);
+  if (B == 0) return QB200_OK;
+  const int vpw = 32 / nb;
+  int64_t Hkv = 0, Dv = 0, T_max = 0;
+  // every sequence: six 4-D views [1, Hkv, T_b, last] of its own capacity buffers
+  for (int64_t b = 0; b < B; ++b) {
+    const qb200_tensor* ts[6] = {k_q[b], k_scales[b], k_biases[b], v_q[b], v_scales[b], v_biases[b]};
+    const char* names[6] = {"k_q", "k_scales", "k_biases", "v_q", "v_scales", "v_biases"};
+    for (int i = 0; i < 6; ++i) {
+      if ((st = check_tensor(ts[i], names[i], 4))) return st;
+      if (ts[i]->ndim != 4 || ts[i]->shape[0] != 1)
+        return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention_ptrs: %s of sequence %lld must be [1, Hkv, T, last]", names[i], (long long)b);
+      if (ts[i]->dtype != ((i == 0 || i == 3) ? QB200_UINT32 : QB200_BFLOAT16))
+        return fail(QB200_ERR_BAD_DTYPE, "kv_decode_attention_ptrs: %s must be %s", names[i], (i == 0 || i == 3) ? "uint32" : "bf16");
+    }
+    if (b == 0) { Hkv = ts[0]->shape[1]; Dv = ts[3]->shape[3] * vpw; }
+    const int64_t T = ts[0]->shape[2];
+    for (int i = 0; i < 6; ++i)
+      if (ts[i]->shape[1] != Hkv || ts[i]->shape[2] != T)
+        return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention_ptrs: the six views of sequence %lld disagree on [Hkv, T]", (long long)b);
+    if (ts[0]->shape[3] * vpw != D || ts[3]->shape[3] * vpw != Dv || ts[1]->shape[3] != D / gs || ts[2]->shape[3] != D / gs ||
+        ts[4]->shape[3] != Dv / gs || ts[5]->shape[3] != Dv / gs)
+      return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention_ptrs: head dims of sequence %lld do not match q / group_size", (long long)b);
+    if (!same_strides(ts[1], ts[2]) || !same_strides(ts[4], ts[5]))
+      return fail(QB200_ERR_BAD_STRIDE, "kv_decode_attention_ptrs: scales and biases must have identical strides");
+    if (T <= 0) return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention_ptrs: the cache view of sequence %lld holds no tokens", (long long)b);
+    T_max = T > T_max ? T : T_max;
+  }
+  if (Hkv <= 0 || Hq % Hkv != 0) return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention_ptrs: Hq %lld not a multiple of Hkv %lld", (long long)Hq, (long long)Hkv);
+  if (D % gs != 0 || Dv % gs != 0) return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention_ptrs: head dims must be multiples of group_size");
+  if (res->shape[0] != B || res->shape[1] != Hq || res->shape[2] != 1 || res->shape[3] != Dv)
+    return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention_ptrs: res must be [B, Hq, 1, Dv]");
+
+  KvAttnArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.q_dtype = q->dtype;
+  a.Hq = Hq; a.Hkv = Hkv; a.T = T_max; a.D = D; a.Dv = Dv;
+  a.q_str[0] = q->stride[0]; a.q_str[1] = q->stride[1];
+  a.o_str[0] = res->stride[0]; a.o_str[1] = res->stride[1];
+  a.gs = gs; a.bits = nb; a.scale = scale;
+  if ((st = parse_kv_mask(a, q, mask_mode, mask_arr, kv_lens, B, T_max))) return st;
+  a.B = B < kMaxSeqPtrs ? B : kMaxSeqPtrs;
+  if (Hq == 0 || Dv == 0) return QB200_OK;
+  if (!kv_attn_supported(a))
+    return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention_ptrs: geometry not served (D=%lld Dv=%lld gs=%d gqa=%lld)",
+                (long long)D, (long long)Dv, gs, (long long)(Hq / Hkv));
+  const size_t need = qb200_kv_decode_attention_ptrs_workspace_size(B, Hq, Hkv, T_max, Dv);
+  if (need == 0 || workspace == nullptr || workspace_bytes < need)
+    return fail(QB200_ERR_WORKSPACE, "kv_decode_attention_ptrs: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+  const int esz = dtype_size(q->dtype);
+  const int msz = a.mask ? dtype_size(a.mask_dtype) : 0;
+  // at most kMaxSeqPtrs sequences per launch: their views travel as a kernel parameter
+  for (int64_t b0 = 0; b0 < B; b0 += kMaxSeqPtrs) {
+    KvSeqTable tab;
+    std::memset(&tab, 0, sizeof(tab));
+    const int64_t nbq = B - b0 < kMaxSeqPtrs ? B - b0 : kMaxSeqPtrs;
+    for (int64_t i = 0; i < nbq; ++i) {
+      KvSeq& e = tab.s[i];
+      const int64_t b = b0 + i;
+      e.kq = (const uint32_t*)k_q[b]->data; e.ks = k_scales[b]->data; e.kb = k_biases[b]->data;
+      e.vq = (const uint32_t*)v_q[b]->data; e.vs = v_scales[b]->data; e.vb = v_biases[b]->data;
+      for (int d = 0; d < 2; ++d) {
+        e.kq_str[d] = k_q[b]->stride[d + 1]; e.ksb_str[d] = k_scales[b]->stride[d + 1];
+        e.vq_str[d] = v_q[b]->stride[d + 1]; e.vsb_str[d] = v_scales[b]->stride[d + 1];
+      }
+      e.T = k_q[b]->shape[2];
+    }
+    KvAttnArgs c = a;
+    c.B = nbq;
+    c.q = (const char*)q->data + b0 * q->stride[0] * esz;
+    c.out = (char*)res->data + b0 * res->stride[0] * esz;
+    if (a.kv_lens) c.kv_lens = a.kv_lens + b0;
+    if (a.mask) c.mask = (const char*)a.mask + b0 * a.mask_bstride * msz;
+    const cudaError_t e = launch_kv_attn(c, (cudaStream_t)s, &tab);
+    if (e != cudaSuccess) return cuda_fail(e, "kv_decode_attention_ptrs");
+  }
   return QB200_OK;
 }
 

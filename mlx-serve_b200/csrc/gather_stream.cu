@@ -31,7 +31,10 @@
 #include <cstring>
 #include <type_traits>
 
+#include <mutex>
+
 #include "kernels.h"
+#include "stream_ptx.cuh"
 
 namespace qb {
 namespace {
@@ -58,36 +61,6 @@ struct GK {
   const uint16_t* sigtab;   // sigmoid of every bf16 pattern, as bf16
 };
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
-}
-__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src));
-}
-__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-  asm(
-      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-// The same with a zero C operand (no accumulator initialisation in registers).
-__device__ __forceinline__ void mma_u8s8_z(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                           uint32_t b1) {
-  asm(
-      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {0,0,0,0};"
-      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-template <int BITS> __device__ __forceinline__ int swz(int row) { return BITS == 4 ? 2 * (row & 3) : 4 * (row & 1); }
-template <int BITS> __device__ __forceinline__ int kslot8(int h, int i) { return BITS == 4 ? 2 * i + h : 4 * h + i; }
 __device__ __forceinline__ long long load_index(const void* p, int is64, int64_t i) {
   return is64 ? ((const long long*)p)[i] : (long long)((const uint32_t*)p)[i];
 }
@@ -173,14 +146,14 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
     const int row = (lane >> 3) + 4 * r;
-    wdst[r] = row * 128 + ((chunk ^ swz<BITS>(row)) << 4);
+    wdst[r] = row * 128 + ((chunk ^ swz_w<BITS>(row)) << 4);
   }
   const uint32_t sbdst = kStageW + (lane & 15) * 16 + (lane >> 4) * 8;   // per row: scales | biases
   int frag_off[U];
 #pragma unroll
   for (int j = 0; j < U; ++j) {
-    if (BITS == 4) frag_off[j] = g * 128 + (((2 * j + (t >> 1)) ^ swz<4>(g)) << 4) + (t & 1) * 8;
-    else frag_off[j] = g * 128 + (((4 * j + t) ^ swz<8>(g)) << 4);
+    if (BITS == 4) frag_off[j] = g * 128 + (((2 * j + (t >> 1)) ^ swz_w<4>(g)) << 4) + (t & 1) * 8;
+    else frag_off[j] = g * 128 + (((4 * j + t) ^ swz_w<8>(g)) << 4);
   }
 
   int e = 0;
@@ -353,14 +326,14 @@ __global__ void __launch_bounds__(kThreads, 1) gather_stream_kernel(GK p) {
           }
           float mx = 0.f;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(f[j]));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+          for (int j = 0; j < 8; ++j) mx = fmax_nan(mx, fabsf(f[j]));
+          mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+          mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+          mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
           int ex = (int)((__float_as_uint(mx) >> 23) & 0xFF) - 127 + 1;  // mx < 2^ex
           ex = ex < -100 ? -100 : (ex > 110 ? 110 : ex);
           const float up = __uint_as_float((uint32_t)(127 + 14 - ex) << 23);
-          const float down = __uint_as_float((uint32_t)(127 + ex - 14) << 23);
+          const float down = poison_if(nonfinite(mx), __uint_as_float((uint32_t)(127 + ex - 14) << 23));
           uint32_t w[8], isum = 0;   // bit patterns 0x4B400000 + v
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -563,6 +536,7 @@ const uint16_t* sigmoid_table(cudaStream_t st, cudaError_t* err) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) { *err = cudaErrorInvalidDevice; return nullptr; }
+  std::lock_guard<std::mutex> setup_lk(setup_mutex());   // the table and its host staging buffer are built once
   if (!ptr[dev]) {
     // the upload is a synchronous copy: not possible while `st` is being captured into a graph (call once before)
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
@@ -594,18 +568,6 @@ const uint16_t* sigmoid_table(cudaStream_t st, cudaError_t* err) {
 
 namespace {
 
-int sm_count_g() {
-  static int cached[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
-  }
-  return cached[dev];
-}
 
 constexpr size_t kStaticSmem = 14 * 1024;   // upper bound of the kernel's static shared arrays
 size_t smem_bytes(int K, int nsb) {
@@ -655,13 +617,16 @@ cudaError_t launch_gather_stream(const GatherArgs& a, cudaStream_t st) {
   const int bi = (a.bits == 4 ? 0 : 1) + (fused ? 2 : 0);
   const void* kern = a.bits == 4 ? (fused ? (const void*)gather_stream_kernel<4, true> : (const void*)gather_stream_kernel<4, false>)
                                  : (fused ? (const void*)gather_stream_kernel<8, true> : (const void*)gather_stream_kernel<8, false>);
+  {
+  std::lock_guard<std::mutex> setup_lk(setup_mutex());   // first use on a device, from any thread
   if (dev < 0 || dev >= 64 || !done[bi][dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024 - kStaticSmem));
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) done[bi][dev] = true;
   }
+  }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(sm_count_g());
+  cfg.gridDim = dim3(sm_count());
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;

@@ -1,11 +1,15 @@
 // Internal launch interface between the C ABI (api.cu) and the kernels.
 // Every launcher returns a cudaError_t and never allocates.
 #pragma once
+#include <mutex>
+
 #include "common.cuh"
 
 namespace qb {
 
 int report_error(int status, const char* msg);  // api.cu: last-error string + handler
+int sm_count();                                 // device.cu: SMs of the current device
+std::mutex& setup_mutex();                      // device.cu: guards every first-use-per-device set-up
 
 // ---- elementwise.cu ----
 struct DequantArgs {
@@ -35,6 +39,18 @@ struct MoeRouteArgs {
   int dtype;              // QB200_BFLOAT16 or QB200_FLOAT32 (logits and scores)
 };
 cudaError_t launch_moe_route(const MoeRouteArgs& a, cudaStream_t st);
+
+// Stable sort of the flattened top-k index list by expert (moe_sort.cu).  Every output may be null.
+struct MoeSortArgs {
+  const void* inds; int inds_i64;
+  int* order;        // [n]: order[p] = position in inds of the p-th entry in expert order
+  int* inv_order;    // [n]: inv_order[order[p]] = p
+  int* sorted_inds;  // [n]: inds[order[p]]
+  int* token_rows;   // [n]: order[p] / topk (the token a sorted row belongs to)
+  int* offsets;      // [E + 1]: rows of expert e are [offsets[e], offsets[e + 1])
+  int64_t n; int E; int topk;
+};
+cudaError_t launch_moe_sort(const MoeSortArgs& a, cudaStream_t st);
 
 // ---- moe_down_reduce.cu: down projection + router weighting + sum over top-k for a few tokens ----
 struct MoeDownReduceArgs {
@@ -81,6 +97,7 @@ cudaError_t launch_qmv_stream_multi(const QmmArgs* a, int count, cudaStream_t st
 // ---- qmm_tc.cu : prefill widths on tcgen05 (dequantise into the swizzled smem operand, TMEM accumulate) ----
 bool qmm_tc_supported(const QmmArgs& a);
 cudaError_t launch_qmm_tc(const QmmArgs& a, cudaStream_t st);
+void qmm_tc_error_reset();
 int qmm_tc_error_code();  // 0, or the code of a bounded wait that expired in the last failing launch
 struct GatherArgs;
 bool gather_tc_supported(const GatherArgs& a);   // rows sorted by expert, many rows: grouped GEMM on the same kernel
@@ -130,8 +147,21 @@ struct KvAttnArgs {
   const void* mask; int mask_dtype; int64_t mask_bstride;  // additive row [B?, T], may be null
   void* workspace; size_t workspace_bytes;
 };
+// Per-sequence cache views for a batch whose sequences own separate caches (the reference's slots each hold a
+// B = 1 cache with its own capacity, src/scheduler.zig:463-480): base pointers, (head, token) strides in
+// elements and the view's length.  The table travels as a kernel parameter.
+constexpr int kMaxSeqPtrs = 32;   // sequences per launch (the reference batches at most 32 slots, src/scheduler.zig:5147)
+struct KvSeq {
+  const uint32_t* kq; const void* ks; const void* kb;
+  const uint32_t* vq; const void* vs; const void* vb;
+  int64_t kq_str[2], ksb_str[2], vq_str[2], vsb_str[2];
+  int64_t T;
+};
+struct KvSeqTable { KvSeq s[kMaxSeqPtrs]; };
+struct KvNoTable {};
 size_t kv_attn_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t T, int64_t Dv);
 bool kv_attn_supported(const KvAttnArgs& a);
-cudaError_t launch_kv_attn(const KvAttnArgs& a, cudaStream_t st);
+bool kv_fast_supported(const KvAttnArgs& a, const KvSeqTable* seqs = nullptr);
+cudaError_t launch_kv_attn(const KvAttnArgs& a, cudaStream_t st, const KvSeqTable* seqs = nullptr);  // seqs: a.B <= kMaxSeqPtrs views, a.T their longest
 
 }  // namespace qb

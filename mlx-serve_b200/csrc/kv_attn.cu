@@ -9,6 +9,8 @@
 // unnormalised O) then the merge of src/transformer.zig:5194-5203.
 #include <math.h>
 
+#include <type_traits>
+
 #include "kernels.h"
 
 namespace qb {
@@ -29,6 +31,7 @@ struct SplitPlan {
 // width is not an input here because the workspace query does not know it).
 __host__ SplitPlan plan_splits(int64_t B, int64_t Hkv, int64_t T) {
   SplitPlan p;
+  const int nsm = sm_count();   // CTA slots: one CTA per SM at 8 bits, two at 4 bits
   const int64_t pairs = B * Hkv > 0 ? B * Hkv : 1;
   int64_t max_ns = (T + 255) / 256;  // at least 256 tokens per split
   if (max_ns < 1) max_ns = 1;
@@ -42,7 +45,7 @@ __host__ SplitPlan plan_splits(int64_t B, int64_t Hkv, int64_t T) {
     const int64_t ns_eff = (T + tps - 1) / tps > 0 ? (T + tps - 1) / tps : 1;
     const double per_cta = (double)((tps / 128 + 7) / 8) + 0.7;
     double cost = 0.0;
-    for (int slots = 148; slots <= 296; slots += 148) cost += (double)((pairs * ns_eff + slots - 1) / slots) * per_cta;
+    for (int slots = nsm; slots <= 2 * nsm; slots += nsm) cost += (double)((pairs * ns_eff + slots - 1) / slots) * per_cta;
     if (best < 0.0 || cost < best - 1e-9) { best = cost; best_ns = ns_eff; best_tps = tps; }
   }
   p.nsplit = (int)best_ns;
@@ -69,8 +72,9 @@ __device__ __forceinline__ float load_mask(const KvK& p, int64_t b, int64_t t) {
 
 // Generic CUDA-core path: any head dim that is a multiple of 32, any group
 // size, GQA <= 8.  One warp per token; lanes stride over the packed words.
-template <int BITS>
-__global__ void __launch_bounds__(128) kv_split_generic(KvK p) {
+template <int BITS, class TAB>
+__global__ void __launch_bounds__(128) kv_split_generic(KvK p, const __grid_constant__ TAB tab) {
+  constexpr bool PTRS = std::is_same<TAB, KvSeqTable>::value;
   constexpr int VPW = 32 / BITS;
   extern __shared__ float smem[];
   const KvAttnArgs& a = p.a;
@@ -89,8 +93,26 @@ __global__ void __launch_bounds__(128) kv_split_generic(KvK p) {
     qs[i] = a.q_dtype == QB200_FLOAT32 ? ((const float*)a.q)[off] : bf16_bits_to_f32(((const uint16_t*)a.q)[off]);
   }
   __syncthreads();
-  int64_t len = a.kv_lens ? (int64_t)a.kv_lens[b] : a.T;
-  if (len > a.T) len = a.T;
+  // this sequence's cache view: its own pointers and strides, or a slice of the batched tensors
+  const uint32_t* kq_b; const uint32_t* vq_b;
+  const uint16_t* ks_b; const uint16_t* kb_b; const uint16_t* vs_b; const uint16_t* vb_b;
+  int64_t kq_tok, ksb_tok, vq_tok, vsb_tok, T_seq;
+  if constexpr (PTRS) {
+    const KvSeq& q = tab.s[b];
+    kq_b = q.kq + hk * q.kq_str[0]; vq_b = q.vq + hk * q.vq_str[0];
+    ks_b = (const uint16_t*)q.ks + hk * q.ksb_str[0]; kb_b = (const uint16_t*)q.kb + hk * q.ksb_str[0];
+    vs_b = (const uint16_t*)q.vs + hk * q.vsb_str[0]; vb_b = (const uint16_t*)q.vb + hk * q.vsb_str[0];
+    kq_tok = q.kq_str[1]; ksb_tok = q.ksb_str[1]; vq_tok = q.vq_str[1]; vsb_tok = q.vsb_str[1];
+    T_seq = q.T;
+  } else {
+    kq_b = a.kq + b * a.kq_str[0] + hk * a.kq_str[1]; vq_b = a.vq + b * a.vq_str[0] + hk * a.vq_str[1];
+    ks_b = (const uint16_t*)a.ks + b * a.ksb_str[0] + hk * a.ksb_str[1]; kb_b = (const uint16_t*)a.kb + b * a.ksb_str[0] + hk * a.ksb_str[1];
+    vs_b = (const uint16_t*)a.vs + b * a.vsb_str[0] + hk * a.vsb_str[1]; vb_b = (const uint16_t*)a.vb + b * a.vsb_str[0] + hk * a.vsb_str[1];
+    kq_tok = a.kq_str[2]; ksb_tok = a.ksb_str[2]; vq_tok = a.vq_str[2]; vsb_tok = a.vsb_str[2];
+    T_seq = a.T;
+  }
+  int64_t len = a.kv_lens ? (int64_t)a.kv_lens[b] : T_seq;
+  if (len > T_seq) len = T_seq;
   const int64_t t0 = (int64_t)split * p.tps;
   int64_t t1 = t0 + p.tps;
   if (t1 > len) t1 = len;
@@ -108,9 +130,9 @@ __global__ void __launch_bounds__(128) kv_split_generic(KvK p) {
       for (int k = 0; k < VPW; ++k) o[h][j][k] = 0.f;
   }
   for (int64_t t = t0 + warp; t < t1; t += nwarp) {
-    const uint32_t* krow = a.kq + b * a.kq_str[0] + hk * a.kq_str[1] + t * a.kq_str[2];
-    const uint16_t* ksr = (const uint16_t*)a.ks + b * a.ksb_str[0] + hk * a.ksb_str[1] + t * a.ksb_str[2];
-    const uint16_t* kbr = (const uint16_t*)a.kb + b * a.ksb_str[0] + hk * a.ksb_str[1] + t * a.ksb_str[2];
+    const uint32_t* krow = kq_b + t * kq_tok;
+    const uint16_t* ksr = ks_b + t * ksb_tok;
+    const uint16_t* kbr = kb_b + t * ksb_tok;
     float dot[kMaxGqa];
 #pragma unroll
     for (int h = 0; h < kMaxGqa; ++h) dot[h] = 0.f;
@@ -147,9 +169,9 @@ __global__ void __launch_bounds__(128) kv_split_generic(KvK p) {
           for (int k = 0; k < VPW; ++k) o[h][j][k] *= alpha;
       }
     }
-    const uint32_t* vrow = a.vq + b * a.vq_str[0] + hk * a.vq_str[1] + t * a.vq_str[2];
-    const uint16_t* vsr = (const uint16_t*)a.vs + b * a.vsb_str[0] + hk * a.vsb_str[1] + t * a.vsb_str[2];
-    const uint16_t* vbr = (const uint16_t*)a.vb + b * a.vsb_str[0] + hk * a.vsb_str[1] + t * a.vsb_str[2];
+    const uint32_t* vrow = vq_b + t * vq_tok;
+    const uint16_t* vsr = vs_b + t * vsb_tok;
+    const uint16_t* vbr = vb_b + t * vsb_tok;
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const int w = lane + 32 * j;
@@ -220,9 +242,8 @@ __global__ void kv_merge(KvK p) {
 
 }  // namespace
 
-bool kv_fast_supported(const KvAttnArgs& a);
 cudaError_t launch_kv_fast(const KvAttnArgs& a, int nsplit, int64_t tps, float* pm, float* pl, float* po,
-                           cudaStream_t st);
+                           cudaStream_t st, const KvSeqTable* seqs);
 
 size_t kv_attn_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t T, int64_t Dv) {
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || T <= 0 || Dv <= 0) return 0;
@@ -240,10 +261,11 @@ bool kv_attn_supported(const KvAttnArgs& a) {
   return true;
 }
 
-cudaError_t launch_kv_attn(const KvAttnArgs& a, cudaStream_t st) {
+cudaError_t launch_kv_attn(const KvAttnArgs& a, cudaStream_t st, const KvSeqTable* seqs) {
   KvK p;
   p.a = a;
-  const SplitPlan sp = plan_splits(a.B, a.Hkv, a.T > 0 ? a.T : 1);
+  if (a.B <= 0 || a.Hq <= 0 || a.Hkv <= 0 || a.T <= 0 || a.Dv <= 0 || a.workspace == nullptr) return cudaErrorInvalidValue;
+  const SplitPlan sp = plan_splits(a.B, a.Hkv, a.T);
   p.nsplit = sp.nsplit;
   p.tps = sp.tokens_per_split;
   p.gqa = (int)(a.Hq / a.Hkv);
@@ -252,14 +274,19 @@ cudaError_t launch_kv_attn(const KvAttnArgs& a, cudaStream_t st) {
   p.part_l = ws + a.B * a.Hq * sp.nsplit;
   p.part_o = ws + 2 * a.B * a.Hq * sp.nsplit;
   cudaError_t e;
-  if (kv_fast_supported(a)) {
-    e = launch_kv_fast(a, sp.nsplit, sp.tokens_per_split, p.part_m, p.part_l, p.part_o, st);
+  if (kv_fast_supported(a, seqs)) {
+    e = launch_kv_fast(a, sp.nsplit, sp.tokens_per_split, p.part_m, p.part_l, p.part_o, st, seqs);
   } else {
     const int nwarp = 4;
     const size_t smem = (size_t)(p.gqa * a.D + 2 * nwarp * p.gqa + nwarp * p.gqa * a.Dv) * sizeof(float);
     dim3 grid((unsigned)sp.nsplit, (unsigned)a.Hkv, (unsigned)a.B);
-    if (a.bits == 4) kv_split_generic<4><<<grid, nwarp * 32, smem, st>>>(p);
-    else kv_split_generic<8><<<grid, nwarp * 32, smem, st>>>(p);
+    if (seqs) {
+      if (a.bits == 4) kv_split_generic<4, KvSeqTable><<<grid, nwarp * 32, smem, st>>>(p, *seqs);
+      else kv_split_generic<8, KvSeqTable><<<grid, nwarp * 32, smem, st>>>(p, *seqs);
+    } else {
+      if (a.bits == 4) kv_split_generic<4, KvNoTable><<<grid, nwarp * 32, smem, st>>>(p, KvNoTable{});
+      else kv_split_generic<8, KvNoTable><<<grid, nwarp * 32, smem, st>>>(p, KvNoTable{});
+    }
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) return e;

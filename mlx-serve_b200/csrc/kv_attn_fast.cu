@@ -25,7 +25,12 @@
 //    dim, contraction along tokens) otherwise makes expensive.  s32 sums are
 //    kept for a whole block and folded into fp32 once per block; the V bias
 //    term is a plain fp32 dot of p with the biases.
+#include <mutex>
+
+#include <type_traits>
+
 #include "kernels.h"
+#include "stream_ptx.cuh"
 
 namespace qb {
 namespace {
@@ -54,23 +59,6 @@ struct FastK {
   float* part_m; float* part_l; float* part_o;
 };
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
-}
-__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 // Two 16x16 byte matrices, transposed: lanes 0-15 give the row addresses of the first, 16-31 of the
 // second.  Lane (g, t) receives for each matrix: r0 = rows 4t..4t+3 of byte column g, r1 = of column g+8.
 __device__ __forceinline__ void ldmatrix_b8_trans_x2(uint32_t (&r)[4], uint32_t addr) {
@@ -86,7 +74,6 @@ template <int BITS> __device__ __forceinline__ int swz(int row) {
   if (BITS == 8) f ^= (row & 1) << 2;
   return f;
 }
-template <int BITS> __device__ __forceinline__ int kslot8(int h, int i) { return BITS == 4 ? 2 * i + h : 4 * h + i; }
 
 __device__ __forceinline__ int fix15(float x, float up) {
   const int v = __float_as_int(fmaf(x, up, 12582912.f)) - 0x4B400000;
@@ -101,8 +88,10 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-template <int BITS>
-__global__ void __launch_bounds__(kWarps * 32, BITS == 4 ? 2 : 1) kv_fast_kernel(FastK p) {
+// TAB = KvSeqTable: sequence b reads its own cache view from the table; KvNoTable: one strided [B, Hkv, T, .] tensor.
+template <int BITS, class TAB>
+__global__ void __launch_bounds__(kWarps * 32, BITS == 4 ? 2 : 1) kv_fast_kernel(FastK p, const __grid_constant__ TAB tab) {
+  constexpr bool PTRS = std::is_same<TAB, KvSeqTable>::value;
   using G = Geo<BITS>;
   extern __shared__ __align__(128) unsigned char smem[];
   const KvAttnArgs& a = p.a;
@@ -137,14 +126,14 @@ __global__ void __launch_bounds__(kWarps * 32, BITS == 4 ? 2 : 1) kv_fast_kernel
       }
       float mx = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(f[j]));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      for (int j = 0; j < 8; ++j) mx = fmax_nan(mx, fabsf(f[j]));
+      mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
       int e = (int)((__float_as_uint(mx) >> 23) & 0xFF) - 127 + 1;
       e = e < -100 ? -100 : (e > 110 ? 110 : e);
       const float up = __uint_as_float((uint32_t)(127 + 14 - e) << 23);
-      const float down = __uint_as_float((uint32_t)(127 + e - 14) << 23);
+      const float down = poison_if(nonfinite(mx), __uint_as_float((uint32_t)(127 + e - 14) << 23));
       int v[8], sum = 0;
 #pragma unroll
       for (int j = 0; j < 8; ++j) { v[j] = fix15(f[j], up); sum += v[j]; }
@@ -166,8 +155,30 @@ __global__ void __launch_bounds__(kWarps * 32, BITS == 4 ? 2 : 1) kv_fast_kernel
   }
   __syncthreads();
 
-  int64_t len = a.kv_lens ? (int64_t)a.kv_lens[b] : a.T;
-  len = len > a.T ? a.T : (len < 0 ? 0 : len);
+  // this sequence's cache view
+  const unsigned char* kq_base; const unsigned char* vq_base;
+  const uint16_t* ks_base; const uint16_t* kb_base; const uint16_t* vs_base; const uint16_t* vb_base;
+  int64_t kq_tok, ksb_tok, vq_tok, vsb_tok, T_seq;
+  if constexpr (PTRS) {
+    const KvSeq& q = tab.s[b];
+    kq_base = (const unsigned char*)(q.kq + hk * q.kq_str[0]);
+    vq_base = (const unsigned char*)(q.vq + hk * q.vq_str[0]);
+    ks_base = (const uint16_t*)q.ks + hk * q.ksb_str[0]; kb_base = (const uint16_t*)q.kb + hk * q.ksb_str[0];
+    vs_base = (const uint16_t*)q.vs + hk * q.vsb_str[0]; vb_base = (const uint16_t*)q.vb + hk * q.vsb_str[0];
+    kq_tok = q.kq_str[1]; ksb_tok = q.ksb_str[1]; vq_tok = q.vq_str[1]; vsb_tok = q.vsb_str[1];
+    T_seq = q.T;
+  } else {
+    kq_base = (const unsigned char*)(a.kq + b * a.kq_str[0] + hk * a.kq_str[1]);
+    vq_base = (const unsigned char*)(a.vq + b * a.vq_str[0] + hk * a.vq_str[1]);
+    ks_base = (const uint16_t*)a.ks + b * a.ksb_str[0] + hk * a.ksb_str[1];
+    kb_base = (const uint16_t*)a.kb + b * a.ksb_str[0] + hk * a.ksb_str[1];
+    vs_base = (const uint16_t*)a.vs + b * a.vsb_str[0] + hk * a.vsb_str[1];
+    vb_base = (const uint16_t*)a.vb + b * a.vsb_str[0] + hk * a.vsb_str[1];
+    kq_tok = a.kq_str[2]; ksb_tok = a.ksb_str[2]; vq_tok = a.vq_str[2]; vsb_tok = a.vsb_str[2];
+    T_seq = a.T;
+  }
+  int64_t len = a.kv_lens ? (int64_t)a.kv_lens[b] : T_seq;
+  len = len > T_seq ? T_seq : (len < 0 ? 0 : len);
   const int64_t t_begin = (int64_t)split * p.tps;
   int64_t t_end = t_begin + p.tps;
   t_end = t_end > len ? len : t_end;
@@ -175,13 +186,7 @@ __global__ void __launch_bounds__(kWarps * 32, BITS == 4 ? 2 : 1) kv_fast_kernel
   const int my_blocks = warp < nblocks ? (nblocks - warp + kWarps - 1) / kWarps : 0;
   const int my_items = my_blocks * 8;  // per block: 4 K chunks then 4 V chunks
 
-  const unsigned char* kq_base = (const unsigned char*)(a.kq + b * a.kq_str[0] + hk * a.kq_str[1]);
-  const unsigned char* vq_base = (const unsigned char*)(a.vq + b * a.vq_str[0] + hk * a.vq_str[1]);
-  const uint16_t* ks_base = (const uint16_t*)a.ks + b * a.ksb_str[0] + hk * a.ksb_str[1];
-  const uint16_t* kb_base = (const uint16_t*)a.kb + b * a.ksb_str[0] + hk * a.ksb_str[1];
-  const uint16_t* vs_base = (const uint16_t*)a.vs + b * a.vsb_str[0] + hk * a.vsb_str[1];
-  const uint16_t* vb_base = (const uint16_t*)a.vb + b * a.vsb_str[0] + hk * a.vsb_str[1];
-  const int64_t last_tok = a.T - 1;
+  const int64_t last_tok = T_seq > 0 ? T_seq - 1 : 0;
 
   const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring + (size_t)warp * G::STAGES * G::STAGE_BYTES);
   const unsigned char* my_ring_p = ring + (size_t)warp * G::STAGES * G::STAGE_BYTES;
@@ -193,7 +198,7 @@ __global__ void __launch_bounds__(kWarps * 32, BITS == 4 ? 2 : 1) kv_fast_kernel
     const int64_t tok0 = t_begin + (int64_t)blk * kBlockTok + ch * kChunk;
     const uint32_t st = my_ring + stage * G::STAGE_BYTES;
     const unsigned char* cbase = isv ? vq_base : kq_base;
-    const int64_t cstr = (isv ? a.vq_str[2] : a.kq_str[2]) * 4;  // bytes per token row
+    const int64_t cstr = (isv ? vq_tok : kq_tok) * 4;  // bytes per token row
     constexpr int RPI = 32 / G::CHUNKS;                          // rows covered per instruction
     const int cc = lane % G::CHUNKS, r0 = lane / G::CHUNKS;
 #pragma unroll
@@ -217,10 +222,10 @@ __global__ void __launch_bounds__(kWarps * 32, BITS == 4 ? 2 : 1) kv_fast_kernel
       int64_t tok = t_begin + (int64_t)blk * kBlockTok + ch * kChunk + lane;
       tok = tok > last_tok ? last_tok : tok;
       const uint32_t d = dst0 + ch * 128 + pos;
-      cp_async4(d, ks_base + tok * a.ksb_str[2]);
-      cp_async4(d + 512, kb_base + tok * a.ksb_str[2]);
-      cp_async4(d + 1024, vs_base + tok * a.vsb_str[2]);
-      cp_async4(d + 1536, vb_base + tok * a.vsb_str[2]);
+      cp_async4(d, ks_base + tok * ksb_tok);
+      cp_async4(d + 512, kb_base + tok * ksb_tok);
+      cp_async4(d + 1024, vs_base + tok * vsb_tok);
+      cp_async4(d + 1536, vb_base + tok * vsb_tok);
     }
   };
 
@@ -296,8 +301,8 @@ __global__ void __launch_bounds__(kWarps * 32, BITS == 4 ? 2 : 1) kv_fast_kernel
             a1[0] = wh.x; a3[0] = wh.y; a1[1] = wh.z; a3[1] = wh.w;
           }
           int acc[4] = {0, 0, 0, 0};
-          mma_u8s8(acc, a0[0], a1[0], a2[0], a3[0], qf[grp][0].x, qf[grp][0].y);
-          mma_u8s8(acc, a0[1], a1[1], a2[1], a3[1], qf[grp][1].x, qf[grp][1].y);
+          mma_u8s8_ordered(acc, a0[0], a1[0], a2[0], a3[0], qf[grp][0].x, qf[grp][0].y);
+          mma_u8s8_ordered(acc, a0[1], a1[1], a2[1], a3[1], qf[grp][1].x, qf[grp][1].y);
           const float2 qg = grp == 0 ? qg0 : qg1;
           const float f_lo = (float)(acc[0] * 128 + acc[1]), f_hi = (float)(acc[2] * 128 + acc[3]);
           // token j = 2*tile (row g) and 2*tile+1 (row g+8): scale/bias pair words sw[j], bw[j]; group = half
@@ -428,12 +433,12 @@ __global__ void __launch_bounds__(kWarps * 32, BITS == 4 ? 2 : 1) kv_fast_kernel
         const int grp = kb / (G::CHUNKS / 2);
         if constexpr (BITS == 4) {
           // byte column c holds head-dim values 32kb + 2c (low nibble) and 2c+1 (high nibble)
-          mma_u8s8(accv[2 * kb], r[0] & 0x0F0F0F0Fu, r[1] & 0x0F0F0F0Fu, r[2] & 0x0F0F0F0Fu, r[3] & 0x0F0F0F0Fu,
+          mma_u8s8_ordered(accv[2 * kb], r[0] & 0x0F0F0F0Fu, r[1] & 0x0F0F0F0Fu, r[2] & 0x0F0F0F0Fu, r[3] & 0x0F0F0F0Fu,
                    bfr[grp][0], bfr[grp][1]);
-          mma_u8s8(accv[2 * kb + 1], (r[0] >> 4) & 0x0F0F0F0Fu, (r[1] >> 4) & 0x0F0F0F0Fu, (r[2] >> 4) & 0x0F0F0F0Fu,
+          mma_u8s8_ordered(accv[2 * kb + 1], (r[0] >> 4) & 0x0F0F0F0Fu, (r[1] >> 4) & 0x0F0F0F0Fu, (r[2] >> 4) & 0x0F0F0F0Fu,
                    (r[3] >> 4) & 0x0F0F0F0Fu, bfr[grp][0], bfr[grp][1]);
         } else {
-          mma_u8s8(accv[kb], r[0], r[1], r[2], r[3], bfr[grp][0], bfr[grp][1]);
+          mma_u8s8_ordered(accv[kb], r[0], r[1], r[2], r[3], bfr[grp][0], bfr[grp][1]);
         }
       }
       __syncwarp();
@@ -495,7 +500,7 @@ __global__ void __launch_bounds__(kWarps * 32, BITS == 4 ? 2 : 1) kv_fast_kernel
 
 }  // namespace
 
-bool kv_fast_supported(const KvAttnArgs& a) {
+bool kv_fast_supported(const KvAttnArgs& a, const KvSeqTable* seqs) {
   if (a.bits != 4 && a.bits != 8) return false;
   if (a.D != kD || a.Dv != kD || a.gs != 64) return false;
   const int64_t gqa = a.Hq / a.Hkv;
@@ -503,6 +508,20 @@ bool kv_fast_supported(const KvAttnArgs& a) {
   if (a.q_dtype != QB200_BFLOAT16 && a.q_dtype != QB200_FLOAT32) return false;
   if (a.Hkv > 65535 || a.B > 65535 || a.T < 1) return false;
   // 16-byte aligned code rows, 4-byte aligned scale/bias rows
+  if (seqs) {
+    if (a.B > kMaxSeqPtrs) return false;
+    for (int64_t b = 0; b < a.B; ++b) {
+      const KvSeq& q = seqs->s[b];
+      if (q.T < 1) return false;
+      if ((((uintptr_t)q.kq) & 15) || (((uintptr_t)q.vq) & 15)) return false;
+      if ((((uintptr_t)q.ks) & 3) || (((uintptr_t)q.kb) & 3) || (((uintptr_t)q.vs) & 3) || (((uintptr_t)q.vb) & 3)) return false;
+      for (int d = 0; d < 2; ++d) {
+        if ((q.kq_str[d] * 4) % 16 != 0 || (q.vq_str[d] * 4) % 16 != 0) return false;
+        if ((q.ksb_str[d] * 2) % 4 != 0 || (q.vsb_str[d] * 2) % 4 != 0) return false;
+      }
+    }
+    return true;
+  }
   if ((((uintptr_t)a.kq) & 15) || (((uintptr_t)a.vq) & 15)) return false;
   for (int d = 0; d < 3; ++d) {
     if ((a.kq_str[d] * 4) % 16 != 0 || (a.vq_str[d] * 4) % 16 != 0) return false;
@@ -512,35 +531,34 @@ bool kv_fast_supported(const KvAttnArgs& a) {
   return true;
 }
 
+namespace {
+template <int BITS, class TAB>
+cudaError_t launch_fast_inst(const FastK& p, const TAB& tab, dim3 grid, cudaStream_t st) {
+  const size_t smem = (size_t)kWarps * (Geo<BITS>::STAGES * Geo<BITS>::STAGE_BYTES + Geo<BITS>::SB_BYTES) + 4 * 32 * 8 + 64;
+  static bool done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  {
+    std::lock_guard<std::mutex> setup_lk(setup_mutex());   // first use on a device, from any thread
+    if (dev < 0 || dev >= 64 || !done[dev]) {
+      const cudaError_t e = cudaFuncSetAttribute(kv_fast_kernel<BITS, TAB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      if (e != cudaSuccess) return e;
+      if (dev >= 0 && dev < 64) done[dev] = true;
+    }
+  }
+  kv_fast_kernel<BITS, TAB><<<grid, kWarps * 32, smem, st>>>(p, tab);
+  return cudaGetLastError();
+}
+}  // namespace
+
 cudaError_t launch_kv_fast(const KvAttnArgs& a, int nsplit, int64_t tps, float* pm, float* pl, float* po,
-                           cudaStream_t st) {
+                           cudaStream_t st, const KvSeqTable* seqs) {
   FastK p;
   p.a = a; p.nsplit = nsplit; p.tps = tps; p.gqa = (int)(a.Hq / a.Hkv);
   p.part_m = pm; p.part_l = pl; p.part_o = po;
-  dim3 grid((unsigned)nsplit, (unsigned)a.Hkv, (unsigned)a.B);
-  cudaError_t e;
-  if (a.bits == 4) {
-    const size_t smem = (size_t)kWarps * (Geo<4>::STAGES * Geo<4>::STAGE_BYTES + Geo<4>::SB_BYTES) + 4 * 32 * 8 + 64;
-    static bool done[64] = {};
-    int dev = 0; cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !done[dev]) {
-      e = cudaFuncSetAttribute(kv_fast_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-      if (e != cudaSuccess) return e;
-      if (dev >= 0 && dev < 64) done[dev] = true;
-    }
-    kv_fast_kernel<4><<<grid, kWarps * 32, smem, st>>>(p);
-  } else {
-    const size_t smem = (size_t)kWarps * (Geo<8>::STAGES * Geo<8>::STAGE_BYTES + Geo<8>::SB_BYTES) + 4 * 32 * 8 + 64;
-    static bool done[64] = {};
-    int dev = 0; cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !done[dev]) {
-      e = cudaFuncSetAttribute(kv_fast_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-      if (e != cudaSuccess) return e;
-      if (dev >= 0 && dev < 64) done[dev] = true;
-    }
-    kv_fast_kernel<8><<<grid, kWarps * 32, smem, st>>>(p);
-  }
-  return cudaGetLastError();
+  const dim3 grid((unsigned)nsplit, (unsigned)a.Hkv, (unsigned)a.B);
+  if (seqs) return a.bits == 4 ? launch_fast_inst<4, KvSeqTable>(p, *seqs, grid, st) : launch_fast_inst<8, KvSeqTable>(p, *seqs, grid, st);
+  return a.bits == 4 ? launch_fast_inst<4, KvNoTable>(p, KvNoTable{}, grid, st) : launch_fast_inst<8, KvNoTable>(p, KvNoTable{}, grid, st);
 }
 
 }  // namespace qb

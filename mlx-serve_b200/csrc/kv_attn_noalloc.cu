@@ -26,6 +26,7 @@ cudaError_t static_scratch_address(void** out) {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> setup_lk(qb::setup_mutex());
   if (addr[dev] == nullptr) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_kv_static_scratch);
@@ -56,6 +57,9 @@ QB200_API int qb200_kv_decode_attention_noalloc(qb200_tensor* res, const qb200_t
   const int64_t B = q->shape[0], Hq = q->shape[1], Hkv = k_q->shape[1], T = k_q->shape[2];
   const int64_t Dv = v_q->shape[3] * (32 / bits);
   const size_t need = qb200_kv_decode_attention_workspace_size(B, Hq, Hkv, T, Dv);
+  if (need == 0)   // an empty batch, head list or cache view: the main entry answers it (OK or a shape error) without a launch
+    return qb200_kv_decode_attention(res, q, k_q, k_scales, k_biases, v_q, v_scales, v_biases, bits, group_size, scale,
+                                     mask_mode, mask_arr, kv_lens, nullptr, 0, s);
   if (need > kStaticScratchBytes) {
     char msg[256];
     snprintf(msg, sizeof(msg),

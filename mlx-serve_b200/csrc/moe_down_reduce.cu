@@ -12,7 +12,10 @@
 // The k values per row meet in shared memory behind one barrier.
 #include <type_traits>
 
+#include <mutex>
+
 #include "kernels.h"
+#include "stream_ptx.cuh"
 
 namespace qb {
 namespace {
@@ -30,33 +33,6 @@ struct DRK {
   int N, K, topk, gshift, f32;
 };
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
-}
-__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src));
-}
-__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void mma_u8s8_z(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                           uint32_t b1) {
-  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {0,0,0,0};"
-      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-template <int BITS> __device__ __forceinline__ int swz(int row) { return BITS == 4 ? 2 * (row & 3) : 4 * (row & 1); }
-template <int BITS> __device__ __forceinline__ int kslot8(int h, int i) { return BITS == 4 ? 2 * i + h : 4 * h + i; }
 __device__ __forceinline__ float rdt(float x, bool f32) { return f32 ? x : __uint_as_float((uint32_t)f32_to_bf16_bits(x) << 16); }
 
 template <int BITS>
@@ -91,7 +67,7 @@ __global__ void __launch_bounds__(kMaxSlots * 32) moe_down_reduce_kernel(DRK p) 
     int n = tile * 16 + row;
     n = n < p.N ? n : p.N - 1;
     wsrc[r] = (const unsigned char*)(p.w + (live ? e : 0) * p.wes + (int64_t)n * ldw) + chunk * 16;
-    wdst[r] = my_ring + row * 128 + ((chunk ^ swz<BITS>(row)) << 4);
+    wdst[r] = my_ring + row * 128 + ((chunk ^ swz_w<BITS>(row)) << 4);
   }
   int ns = tile * 16 + (lane & 15);
   ns = ns < p.N ? ns : p.N - 1;
@@ -129,14 +105,14 @@ __global__ void __launch_bounds__(kMaxSlots * 32) moe_down_reduce_kernel(DRK p) 
     }
     float mx = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(f[j]));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+    for (int j = 0; j < 8; ++j) mx = fmax_nan(mx, fabsf(f[j]));
+    mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
     int ex = (int)((__float_as_uint(mx) >> 23) & 0xFF) - 127 + 1;  // mx < 2^ex
     ex = ex < -100 ? -100 : (ex > 110 ? 110 : ex);
     const float up = __uint_as_float((uint32_t)(127 + 14 - ex) << 23);
-    const float down = __uint_as_float((uint32_t)(127 + ex - 14) << 23);
+    const float down = poison_if(nonfinite(mx), __uint_as_float((uint32_t)(127 + ex - 14) << 23));
     uint32_t w[8], isum = 0;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -167,8 +143,8 @@ __global__ void __launch_bounds__(kMaxSlots * 32) moe_down_reduce_kernel(DRK p) 
   int frag_off[U];
 #pragma unroll
   for (int j = 0; j < U; ++j) {
-    if (BITS == 4) frag_off[j] = g * 128 + (((2 * j + (t >> 1)) ^ swz<4>(g)) << 4) + (t & 1) * 8;
-    else frag_off[j] = g * 128 + (((4 * j + t) ^ swz<8>(g)) << 4);
+    if (BITS == 4) frag_off[j] = g * 128 + (((2 * j + (t >> 1)) ^ swz_w<4>(g)) << 4) + (t & 1) * 8;
+    else frag_off[j] = g * 128 + (((4 * j + t) ^ swz_w<8>(g)) << 4);
   }
   float tot0 = 0.f, tot1 = 0.f;
   for (int u = 0; u < ut; ++u) {
@@ -308,7 +284,7 @@ __global__ void __launch_bounds__((FUSED ? 2 : 1) * kParts * 32) gather_small_ke
     int n = tile * 16 + row;
     n = n < p.N ? n : p.N - 1;
     wsrc[r] = (const unsigned char*)(wb + e * p.wes + (int64_t)n * ldw) + chunk * 16;
-    wdst[r] = my_ring + row * 128 + ((chunk ^ swz<BITS>(row)) << 4);
+    wdst[r] = my_ring + row * 128 + ((chunk ^ swz_w<BITS>(row)) << 4);
   }
   int ns = tile * 16 + (lane & 15);
   ns = ns < p.N ? ns : p.N - 1;
@@ -346,14 +322,14 @@ __global__ void __launch_bounds__((FUSED ? 2 : 1) * kParts * 32) gather_small_ke
     }
     float mx = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(f[j]));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+    for (int j = 0; j < 8; ++j) mx = fmax_nan(mx, fabsf(f[j]));
+    mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
     int ex = (int)((__float_as_uint(mx) >> 23) & 0xFF) - 127 + 1;  // mx < 2^ex
     ex = ex < -100 ? -100 : (ex > 110 ? 110 : ex);
     const float up = __uint_as_float((uint32_t)(127 + 14 - ex) << 23);
-    const float down = __uint_as_float((uint32_t)(127 + ex - 14) << 23);
+    const float down = poison_if(nonfinite(mx), __uint_as_float((uint32_t)(127 + ex - 14) << 23));
     uint32_t w[8], isum = 0;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -384,8 +360,8 @@ __global__ void __launch_bounds__((FUSED ? 2 : 1) * kParts * 32) gather_small_ke
   int frag_off[U];
 #pragma unroll
   for (int j = 0; j < U; ++j) {
-    if (BITS == 4) frag_off[j] = g * 128 + (((2 * j + (t >> 1)) ^ swz<4>(g)) << 4) + (t & 1) * 8;
-    else frag_off[j] = g * 128 + (((4 * j + t) ^ swz<8>(g)) << 4);
+    if (BITS == 4) frag_off[j] = g * 128 + (((2 * j + (t >> 1)) ^ swz_w<4>(g)) << 4) + (t & 1) * 8;
+    else frag_off[j] = g * 128 + (((4 * j + t) ^ swz_w<8>(g)) << 4);
   }
   float tot0 = 0.f, tot1 = 0.f;
   for (int k = 0; k < nu; ++k) {
@@ -511,10 +487,13 @@ cudaError_t launch_moe_down_reduce(const MoeDownReduceArgs& a, cudaStream_t st) 
   int dev = 0;
   cudaGetDevice(&dev);
   const int bi = a.bits == 4 ? 0 : 1;
+  {
+  std::lock_guard<std::mutex> setup_lk(setup_mutex());   // first use on a device, from any thread
   if (dev < 0 || dev >= 64 || !done[bi][dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) done[bi][dev] = true;
+  }
   }
   const dim3 grid((unsigned)((p.N + 15) / 16), (unsigned)a.T, 1);
   if (a.bits == 4) moe_down_reduce_kernel<4><<<grid, p.topk * 32, smem, st>>>(p);
@@ -565,10 +544,13 @@ cudaError_t launch_gather_small(const GatherArgs& a, cudaStream_t st) {
   static bool done[8][64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
+  {
+  std::lock_guard<std::mutex> setup_lk(setup_mutex());   // first use on a device, from any thread
   if (dev < 0 || dev >= 64 || !done[ki][dev]) {
     cudaError_t e = cudaFuncSetAttribute(kerns[ki], cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) done[ki][dev] = true;
+  }
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)((p.N + 15) / 16), (unsigned)a.I, 1);

@@ -43,6 +43,8 @@
 // every role leaves its loops, the CTA frees its tensor memory and returns.
 #include <cuda.h>
 
+#include <mutex>
+
 #include "kernels.h"
 
 namespace qb {
@@ -725,6 +727,7 @@ typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void
 EncodeFn get_encode() {
   static EncodeFn fn = nullptr;
   static bool tried = false;
+  std::lock_guard<std::mutex> setup_lk(setup_mutex());
   if (!tried) {
     tried = true;
     void* sym = nullptr;
@@ -747,18 +750,6 @@ static_assert(smem_bytes_tc(false, false, true) <= 227 * 1024, "few-token form d
 
 constexpr size_t STAGES_DENSE_BYTES = (size_t)stages_of(false) * (A_STAGE_BYTES + B_STAGE_BYTES) + 2 * RAW_BYTES;  // pipeline buffers reused by the exchange
 
-int sm_count_tc() {
-  static int cached[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
-  }
-  return cached[dev];
-}
 
 // Weight rows per tile: the candidate whose tile count fills the last wave best.  Time per tile ~ rows + 40:
 // the activation traffic of a k-block through shared memory does not shrink with the tile, so narrow tiles
@@ -810,10 +801,13 @@ cudaError_t launch_tc_inst(const CUtensorMap& xmap, const CUtensorMap& wmap, con
   int dev = 0;
   cudaGetDevice(&dev);
   constexpr size_t smem = smem_bytes_tc(GROUPED, WIDE, HALF);
+  {
+  std::lock_guard<std::mutex> setup_lk(setup_mutex());   // first use on a device, from any thread
   if (dev < 0 || dev >= 64 || !done[dev]) {
     cudaError_t e = cudaFuncSetAttribute(qmm_tc_kernel<BITS, GROUPED, WIDE, HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) done[dev] = true;
+  }
   }
   if (cluster > 1) {
     cudaLaunchConfig_t cfg = {};
@@ -840,11 +834,12 @@ int split_capacity(int cluster) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
+  std::lock_guard<std::mutex> setup_lk(setup_mutex());
   if (cached[dev][cluster] == 0) {
     constexpr size_t smem = smem_bytes_tc(false, false);
     int n = 0;
     cudaLaunchConfig_t q = {};
-    q.gridDim = dim3((unsigned)(sm_count_tc() / cluster * cluster));
+    q.gridDim = dim3((unsigned)(sm_count() / cluster * cluster));
     q.blockDim = dim3(kThreads);
     q.dynamicSmemBytes = smem;
     cudaLaunchAttribute qa[1];
@@ -875,7 +870,7 @@ cudaError_t launch_tc(const TcLaunch& a, bool grouped, cudaStream_t st) {
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
   TcK p;
-  const int nsm = sm_count_tc();
+  const int nsm = sm_count();
   // Wide tiles when both 128-token halves of a tile are in use and there are enough weight rows to fill the GPU
   // with them; the grouped form does not know its tile count on the host and takes full-width dense tiles.
   // (grouped: many rows per expert on average, so that most tiles have both halves)
@@ -1004,6 +999,11 @@ extern "C" __attribute__((visibility("default"))) void qb200_debug_tc_profile(lo
   cudaMemcpyFromSymbol(out, g_tc_prof, sizeof(long long) * 256 * 16);
 }
 #endif
+
+void qmm_tc_error_reset() {
+  const int zero = 0;
+  cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
+}
 
 int qmm_tc_error_code() {
   int v = 0;

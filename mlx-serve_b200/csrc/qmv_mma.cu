@@ -23,6 +23,8 @@
 //    nothing is written to global scratch.
 //  * fp32 activations are split into bf16 hi + lo halves that occupy two token
 //    slots of the same n-tile, so fp32 inputs keep ~16 significant bits.
+#include <mutex>
+
 #include "kernels.h"
 #include "qmv_frag.cuh"
 
@@ -302,10 +304,13 @@ cudaError_t launch_dense_inst(const DenseK& p, int64_t nbatch, cudaStream_t st) 
   static bool attr_done[64] = {};  // per instantiation and device; the call is idempotent
   int dev = 0;
   cudaGetDevice(&dev);
+  {
+  std::lock_guard<std::mutex> setup_lk(setup_mutex());   // first use on a device, from any thread
   if (dev < 0 || dev >= 64 || !attr_done[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
+  }
   }
   dim3 grid((unsigned)((p.N + ROWS - 1) / ROWS), 1, (unsigned)nbatch);
   kern<<<grid, kThreads, smem, st>>>(p);
@@ -443,10 +448,13 @@ cudaError_t launch_gather_inst(const GatherK& p, cudaStream_t st) {
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
+  {
+  std::lock_guard<std::mutex> setup_lk(setup_mutex());   // first use on a device, from any thread
   if (dev < 0 || dev >= 64 || !attr_done[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
+  }
   }
   const int tok = p.x_f32 ? 4 : 8;
   dim3 grid((unsigned)((p.N + ROWS - 1) / ROWS), (unsigned)((p.I + tok - 1) / tok), 1);

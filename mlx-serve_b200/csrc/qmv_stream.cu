@@ -38,6 +38,7 @@
 // Nothing is written to global scratch; the only global writes are y.
 #include <type_traits>
 #include "kernels.h"
+#include "stream_ptx.cuh"
 
 namespace qb {
 namespace {
@@ -90,74 +91,9 @@ struct StreamK {
   int upc;            // K units per CTA in that mode
 };
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
-}
-__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src));
-}
-__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
 __device__ __forceinline__ void group_barrier(int grp) {
   asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "n"(kWarpsPerGroup * 32) : "memory");
 }
-// Thread-block cluster helpers (distributed shared memory): the CTAs of a cluster split the conversion of
-// the activations and write every converted fragment into the shared memory of all of them.
-__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
-__device__ __forceinline__ uint32_t cluster_size() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t saddr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void st_cluster_v2(uint32_t addr, uint32_t x, uint32_t y) {
-  asm volatile("st.shared::cluster.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
-// All threads of all CTAs of the cluster (a hardware barrier: no spinning in software).
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-// D(16x8,s32) += A(16x32,u8,row) * B(32x8,s8,col)
-__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-  asm(
-      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// The same with a zero C operand (no accumulator initialisation in registers).
-__device__ __forceinline__ void mma_u8s8_z(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                           uint32_t b1) {
-  asm(
-      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {0,0,0,0};"
-      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// 16-byte chunk swizzle inside a 128-byte stage row so that the fragment reads
-// (64-bit per lane at 4 bits, 128-bit at 8 bits) are bank-conflict free.
-template <int BITS> __device__ __forceinline__ int swz(int row) {
-  return BITS == 4 ? 2 * (row & 3) : 4 * (row & 1);
-}
-
-// A lane owns 16 consecutive K values of a group, 8 per MMA.  Offset (0..7)
-// inside those 8 of the byte that sits in operand register h (0: k-slots 4t..,
-// 1: k-slots 16+4t..), byte i.  4-bit words split into even and odd nibbles;
-// 8-bit words are in order.
-template <int BITS> __device__ __forceinline__ int kslot8(int h, int i) {
-  return BITS == 4 ? 2 * i + h : 4 * h + i;
-}
-
 // Kernel parameters are indexed with constant subscripts only (a dynamic subscript would force a
 // local-memory copy of the parameter block).
 #define QB_SEL4(arr, i) ((i) == 0 ? (arr)[0] : ((i) == 1 ? (arr)[1] : ((i) == 2 ? (arr)[2] : (arr)[3])))
@@ -219,7 +155,7 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
     const int row = (lane >> 3) + 4 * r;
-    wdst[r] = my_ring + row * 128 + ((chunk ^ swz<BITS>(row)) << 4);
+    wdst[r] = my_ring + row * 128 + ((chunk ^ swz_w<BITS>(row)) << 4);
   }
   const uint32_t sbdst = my_ring + kStageW + (lane & 15) * 16 + (lane >> 4) * 8;   // per row: scales | biases
   const int sbstep = (kWarpsPerGroup * U) >> p.gshift;   // scale entries between two units of this warp
@@ -288,8 +224,8 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
   int frag_off[U];
 #pragma unroll
   for (int j = 0; j < U; ++j) {
-    if (BITS == 4) frag_off[j] = g * 128 + (((2 * j + (t >> 1)) ^ swz<4>(g)) << 4) + (t & 1) * 8;
-    else frag_off[j] = g * 128 + (((4 * j + t) ^ swz<8>(g)) << 4);
+    if (BITS == 4) frag_off[j] = g * 128 + (((2 * j + (t >> 1)) ^ swz_w<4>(g)) << 4) + (t & 1) * 8;
+    else frag_off[j] = g * 128 + (((4 * j + t) ^ swz_w<8>(g)) << 4);
   }
 
   setup();
@@ -377,14 +313,14 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
         }
         float mx = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(f[j]));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        for (int j = 0; j < 8; ++j) mx = fmax_nan(mx, fabsf(f[j]));
+        mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
         int e = (int)((__float_as_uint(mx) >> 23) & 0xFF) - 127 + 1;  // mx < 2^e
         e = e < -100 ? -100 : (e > 110 ? 110 : e);
         const float up = __uint_as_float((uint32_t)(127 + 14 - e) << 23);
-        const float down = __uint_as_float((uint32_t)(127 + e - 14) << 23);
+        const float down = poison_if(nonfinite(mx), __uint_as_float((uint32_t)(127 + e - 14) << 23));
         uint32_t w[8];   // bit patterns of 1.5 * 2^23 + v: 0x4B400000 + v
         uint32_t isum = 0;
 #pragma unroll
@@ -652,18 +588,6 @@ extern "C" __attribute__((visibility("default"))) void qb200_debug_stream_timeli
 }
 #endif
 
-int sm_count() {
-  static int cached[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
-  }
-  return cached[dev];
-}
 
 // Grid, K passes and shared-memory footprint of one instantiation; false when it does not fit.
 bool plan_stream(StreamK& p, int NT, bool M1, int* grid_out, size_t* smem_out, int* cluster_out = nullptr, int cluster = 1,
@@ -729,6 +653,7 @@ cudaError_t launch_inst(StreamK p, cudaStream_t st) {
   int dev = 0;
   cudaGetDevice(&dev);
   const int di = (dev >= 0 && dev < 64) ? dev : 0;
+  std::unique_lock<std::mutex> setup_lk(setup_mutex());   // first use on a device, from any thread
   if (!attr_done[di] || di != dev) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
@@ -759,10 +684,11 @@ cudaError_t launch_inst(StreamK p, cudaStream_t st) {
   }
   int cs = cluster_of[di];
   const int max_ctas = max_ctas_of[di];
+  const int split_cluster = split_cluster_of[di], split_ctas = split_ctas_of[di];
+  setup_lk.unlock();
   int grid = 0;
   size_t smem = 0;
-  if (!plan_stream(p, NT, M1, &grid, &smem, &cs, cs, M1 ? 0 : max_ctas, BITS == 4 ? 256 : 128, split_cluster_of[di],
-                   split_ctas_of[di]))
+  if (!plan_stream(p, NT, M1, &grid, &smem, &cs, cs, M1 ? 0 : max_ctas, BITS == 4 ? 256 : 128, split_cluster, split_ctas))
     return cudaErrorInvalidConfiguration;
   // Programmatic dependent launch: this grid may start (and prefetch weights, which no kernel writes)
   // before the previous grid in the stream has finished; it waits for that grid before touching x or y.

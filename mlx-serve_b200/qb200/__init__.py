@@ -86,6 +86,14 @@ def lib():
         L.qb200_kv_append.argtypes = [TP, TP, TP, TP, C.c_int64, C.c_int, C.c_int, C.c_void_p]
         L.qb200_kv_decode_attention.argtypes = [TP, TP, TP, TP, TP, TP, TP, TP, C.c_int, C.c_int, C.c_float,
                                                 C.c_char_p, TP, TP, C.c_void_p, C.c_size_t, C.c_void_p]
+        L.qb200_kv_decode_attention_ptrs.argtypes = [TP, TP] + [C.POINTER(TP)] * 6 + [C.c_int, C.c_int, C.c_int, C.c_float,
+                                                     C.c_char_p, TP, TP, C.c_void_p, C.c_size_t, C.c_void_p]
+        L.qb200_kv_decode_attention_ptrs.restype = C.c_int
+        L.qb200_kv_decode_attention_ptrs_workspace_size.restype = C.c_size_t
+        L.qb200_kv_decode_attention_ptrs_workspace_size.argtypes = [C.c_int64] * 5
+        L.qb200_moe_sort_by_expert.argtypes = [TP] * 6 + [C.c_int, C.c_void_p]
+        L.qb200_moe_sort_by_expert.restype = C.c_int
+        L.qb200_debug_tc_reset.restype = None
         L.qb200_kv_decode_attention_noalloc.argtypes = [TP, TP, TP, TP, TP, TP, TP, TP, C.c_int, C.c_int, C.c_float,
                                                         C.c_char_p, TP, TP, C.c_void_p]
         L.qb200_kv_decode_attention_noalloc.restype = C.c_int
@@ -310,3 +318,47 @@ def kv_decode_attention_noalloc(q, k_triple, v_triple, bits, group_size, scale, 
     check(L.qb200_kv_decode_attention_noalloc(*[C.byref(a) for a in args], int(bits), int(group_size), float(scale),
                                               mask_mode.encode(), C.byref(dm), C.byref(dl), _stream()))
     return out
+
+
+def kv_decode_attention_ptrs(q, k_triples, v_triples, bits, group_size, scale, mask_mode="", mask=None, kv_lens=None,
+                             workspace=None, out=None):
+    """Decode attention over a batch whose sequences own separate caches: ``k_triples[b]`` / ``v_triples[b]`` are the
+    (codes, scales, biases) views [1, Hkv, T_b, .] of sequence b (forwardBatchedDecode's per-slot caches,
+    src/transformer.zig:9742-9792).  q [B,Hq,1,D] -> [B,Hq,1,Dv]."""
+    L = lib()
+    B, Hq = q.shape[0], q.shape[1]
+    Hkv = k_triples[0][0].shape[1]
+    tmax = max(t[0].shape[2] for t in k_triples)
+    Dv = v_triples[0][0].shape[3] * 32 // bits
+    if out is None:
+        out = torch.empty((B, Hq, 1, Dv), dtype=q.dtype, device=q.device)
+    need = int(L.qb200_kv_decode_attention_ptrs_workspace_size(B, Hq, Hkv, tmax, Dv))
+    if workspace is None:
+        workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+    TP = C.POINTER(Tensor)
+    keep = []
+
+    def arr(items, packed):
+        ds = [(_packed(t) if packed else desc(t)) for t in items]
+        keep.append(ds)
+        return (TP * B)(*[C.pointer(d) for d in ds])
+    lists = [arr([t[0] for t in k_triples], True), arr([t[1] for t in k_triples], False), arr([t[2] for t in k_triples], False),
+             arr([t[0] for t in v_triples], True), arr([t[1] for t in v_triples], False), arr([t[2] for t in v_triples], False)]
+    do, dq, dm, dl = desc(out), desc(q), desc(mask), desc(kv_lens)
+    check(L.qb200_kv_decode_attention_ptrs(C.byref(do), C.byref(dq), *lists, int(B), int(bits), int(group_size),
+                                           float(scale), mask_mode.encode(), C.byref(dm), C.byref(dl),
+                                           C.c_void_p(workspace.data_ptr()), workspace.numel(), _stream()))
+    return out
+
+
+def moe_sort_by_expert(inds, num_experts, want_offsets=True):
+    """Stable sort of the flattened top-k index list by expert (moeMLP2, src/transformer.zig:14961-15006).
+    Returns (order, inv_order, sorted_inds, token_rows, expert_offsets), all int32."""
+    L = lib()
+    n = inds.numel()
+    mk = lambda m: torch.empty((m,), dtype=torch.int32, device=inds.device)
+    order, inv, sinds, rows = mk(n), mk(n), mk(n), mk(n)
+    offs = mk(num_experts + 1) if want_offsets else None
+    check(L.qb200_moe_sort_by_expert(C.byref(desc(order)), C.byref(desc(inv)), C.byref(desc(sinds)), C.byref(desc(rows)),
+                                     C.byref(desc(offs)), C.byref(desc(inds)), int(num_experts), _stream()))
+    return order, inv, sinds, rows, offs

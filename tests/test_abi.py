@@ -126,3 +126,20 @@ def test_kv_attention_declines_wide_queries_and_checks_workspace(q):
     r1 = _t(q, q.BFLOAT16, [B, Hq, 1, D])
     assert q.kv_decode_attention_workspace_size(B, Hq, Hkv, T, D) > 0
     assert fn(*args(r1, q1)) == 7  # workspace missing
+
+
+def test_kv_attention_refuses_an_empty_cache_view_before_any_launch(q):
+    """A cache view without tokens (offset 0) must not reach a kernel: both entries answer BAD_SHAPE on the host."""
+    B, Hq, Hkv, D = 2, 8, 2, 128
+    q1 = _t(q, q.BFLOAT16, [B, Hq, 1, D])
+    r1 = _t(q, q.BFLOAT16, [B, Hq, 1, D])
+    kq = _t(q, q.UINT32, [B, Hkv, 0, 16])
+    ks = _t(q, q.BFLOAT16, [B, Hkv, 0, 2])
+    e = q.desc(None)
+    common = [C.byref(r1), C.byref(q1), C.byref(kq), C.byref(ks), C.byref(ks), C.byref(kq), C.byref(ks), C.byref(ks),
+              4, 64, 0.088, b"", C.byref(e), C.byref(e)]
+    assert q.kv_decode_attention_workspace_size(B, Hq, Hkv, 0, D) == 0
+    assert q.lib().qb200_kv_decode_attention(*common, None, 0, None) == 2
+    assert q.lib().qb200_kv_decode_attention(*common, C.c_void_p(0x1000), 1 << 20, None) == 2
+    assert q.lib().qb200_kv_decode_attention_noalloc(*common, None) == 2
+    assert b"no tokens" in q.lib().qb200_last_error()

@@ -138,6 +138,86 @@ def test_config3_prefill_sorted_grouped(bits, gs, N, K):
     assert torch.equal(y64.view(torch.int16), y.view(torch.int16))
 
 
+@pytest.mark.parametrize("proj", ["gate", "down"])
+def test_config3_prefill_full_size_row_sample_against_the_oracle(proj):
+    """Benchmark configuration 3 at its prefill size: 128 experts, 4096 tokens x top-8 = 32768 rows sorted by expert
+    (the device sort entry produces the order), gate 2048->768 and down 768->2048, 4-bit g64.  The oracle is
+    row-independent, so a row sample is checked: the first two and last two rows of every expert's run."""
+    import qb200
+    from util import from_dev_bf16, from_dev_u32, half_ulp_fraction, record
+    E, T, k = 128, 4096, 8
+    N, K = (768, 2048) if proj == "gate" else (2048, 768)
+    g = torch.Generator(device="cuda").manual_seed(0xC3 + N)
+    w = (torch.randn((E, N, K), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    dq, ds, db = qb200.quantize(w, 64, 4)
+    del w
+    logits = torch.randn((T, E), device="cuda", generator=g)
+    inds, _ = qb200.moe_route(logits, k)
+    order, inv, sinds, rows, offs = qb200.moe_sort_by_expert(inds, E)
+    xtok = torch.randn((T, K), device="cuda", generator=g).to(torch.bfloat16)
+    x_rep = xtok[rows.long()].reshape(T * k, 1, K).contiguous()
+    y = qb200.gather_qmm(x_rep, dq, ds, db, None, sinds, True, 64, 4, sorted_indices=True)
+    torch.cuda.synchronize()
+    assert qb200.lib().qb200_debug_tc_status() == 0
+    assert tuple(y.shape) == (T * k, 1, N) and not torch.isnan(y).any()
+    o = offs.cpu().numpy()
+    sample = sorted({int(r) for e in range(E) for r in (o[e], o[e] + 1, o[e + 1] - 2, o[e + 1] - 1) if o[e] <= r < o[e + 1]})
+    sample = np.array(sample, np.int64)
+    hq, hs, hb = from_dev_u32(dq), from_dev_bf16(ds), from_dev_bf16(db)
+    xs = x_rep[torch.from_numpy(sample).cuda()].float().cpu().numpy()                 # [S, 1, K]
+    es = sinds.cpu().numpy()[sample]
+    ref_w16 = np.empty((len(sample), 1, N), np.float32)
+    for e in np.unique(es):
+        m = es == e
+        ref_w16[m, 0] = qo.qmm(np.ascontiguousarray(xs[m, 0]), hq[e], hs[e], hb[e], 64, 4, True, bf16_weights=True)
+    ref = qo.gather_qmm(xs, hq, hs, hb, np.arange(len(sample)), es, 64, 4)
+    got = y[torch.from_numpy(sample).cuda()].float().cpu().numpy()
+    # this many sorted rows per expert run on the grouped tensor-core form: weight term rounded to bf16 once
+    gate_bf16(got, ref_w16, "full-size prefill gather, bf16 weight term", slack=2e-3)
+    r16 = gate_bf16(got, ref, "full-size prefill gather vs fp32 weight term", slack=1e-2)
+    record(f"C3 prefill {proj} 128 experts x 32768 rows (sample of {len(sample)} rows)",
+           "bf16 activations vs oracle (unrounded fp32)", r16, half_ulp_fraction(got, ref), int(ref.size))
+    # the same rows through explicit lhs indices (no x_rep copy) on the first 2048 sorted rows, bit for bit
+    y_l = qb200.gather_qmm(xtok.view(T, 1, K), dq, ds, db, rows[:2048].contiguous(), sinds[:2048].contiguous(), True, 64, 4,
+                           sorted_indices=True)
+    y_r = qb200.gather_qmm(x_rep[:2048].contiguous(), dq, ds, db, None, sinds[:2048].contiguous(), True, 64, 4, sorted_indices=True)
+    assert torch.equal(y_l.view(torch.int16), y_r.view(torch.int16))
+
+
+def test_non_finite_activations_reach_the_output():
+    """An Inf or a NaN activation must not come out as a finite number: every output that depends on the group
+    holding it is non-finite, other tokens are untouched (MLX's quantized_matmul propagates them likewise)."""
+    import qb200
+    rng = np.random.default_rng(404)
+    q, s, b = make_weight(rng, (512, 1024), 64, 4)
+    dq, ds, db = dev_triple(q, s, b)
+    for M in (1, 8, 20):
+        x = rand_bf16(rng, (M, 1024))
+        clean = qb200.quantized_matmul(to_dev_bf16(qo.f32_to_bf16(x)), dq, ds, db, True, 64, 4).float().cpu().numpy()
+        x[0, 100] = np.inf
+        if M > 1:
+            x[M - 1, 700] = np.nan
+        for dev_x in (to_dev_bf16(qo.f32_to_bf16(x)), torch.from_numpy(x).cuda()):
+            y = qb200.quantized_matmul(dev_x, dq, ds, db, True, 64, 4).float().cpu().numpy()
+            assert not np.isfinite(y[0]).any()
+            if M > 1:
+                assert not np.isfinite(y[M - 1]).any()
+            if M > 2:
+                assert np.isfinite(y[1:M - 1]).all()
+        if M > 2:
+            y16 = qb200.quantized_matmul(to_dev_bf16(qo.f32_to_bf16(x)), dq, ds, db, True, 64, 4).float().cpu().numpy()
+            assert np.array_equal(y16[1:M - 1], clean[1:M - 1])
+    # gather form
+    E = 4
+    bq, bs, bb = make_weight(rng, (E, 256, 512), 64, 4)
+    inds = np.sort(rng.integers(0, E, 40)).astype(np.int32)
+    xr = rand_bf16(rng, (40, 1, 512))
+    xr[7, 0, 3] = np.nan
+    y = qb200.gather_qmm(to_dev_bf16(qo.f32_to_bf16(xr)), *dev_triple(bq, bs, bb), None, torch.from_numpy(inds).cuda(), True, 64, 4,
+                         sorted_indices=True).float().cpu().numpy()
+    assert not np.isfinite(y[7]).any() and np.isfinite(np.delete(y, 7, axis=0)).all()
+
+
 def test_moe_block_padded_exchange_plan_matches_exact_plan_on_one_gpu():
     """The two exchange plans of the expert-parallel block (exact counts / fixed-size blocks whose empty slots carry
     expert id -1) give identical outputs through the CUDA gather_qmm, which must skip the empty slots."""

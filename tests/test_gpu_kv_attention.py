@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from oracle import qoracle as qo
-from util import dev_triple, gate_bf16, gate_f32, rand_bf16, to_dev_bf16
+from util import dev_triple, from_dev_bf16, from_dev_u32, gate_bf16, gate_f32, half_ulp_fraction, rand_bf16, record, to_dev_bf16
 
 pytestmark = pytest.mark.gpu
 
@@ -93,3 +93,105 @@ def test_config5_t32768_one_sequence_and_full_batch_property():
     lens = torch.full((B,), Th, dtype=torch.int32, device="cuda")
     masked = qb200.kv_decode_attention(q, kt, vt, 4, 64, D ** -0.5, kv_lens=lens)
     assert float((masked - half).abs().max()) <= 5e-3 * r
+
+
+def _device_cache(g, B, Hkv, cap, D, bits):
+    """A packed cache made on the device with the library's quantize (bit-exact against the oracle's, see the
+    elementwise tests); the host copy of chosen sequences feeds the oracle."""
+    import qb200
+    k = torch.randn((B, Hkv, cap, D), device="cuda", generator=g).to(torch.bfloat16)
+    kt = qb200.quantize(k, 64, bits)
+    k.normal_(generator=g)
+    vt = qb200.quantize(k, 64, bits)
+    del k
+    return kt, vt
+
+
+def _host_seq(triple, b, T):
+    qd, sd, bd = (t[b:b + 1, :, :T].contiguous() for t in triple)
+    return from_dev_u32(qd), from_dev_bf16(sd), from_dev_bf16(bd)
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_config5_t32768_full_batch_ragged_lengths_two_sequences_against_the_oracle(bits):
+    """Benchmark configuration 5 at T=32768, both widths: the full batch of 16 sequences with ragged lengths runs on
+    the GPU, a full-length sequence and a ragged one are checked against the oracle."""
+    import qb200
+    g = torch.Generator(device="cuda").manual_seed(0xC5 + bits)
+    B, Hq, Hkv, T, D = 16, 32, 8, 32768, 128
+    kt, vt = _device_cache(g, B, Hkv, T + 256, D, bits)
+    kv, vv = [t[:, :, :T] for t in kt], [t[:, :, :T] for t in vt]
+    q = torch.randn((B, Hq, 1, D), device="cuda", generator=g).to(torch.bfloat16)
+    lens_np = np.full((B,), T, np.int32)
+    lens_np[5], lens_np[9], lens_np[12] = 20001, 1, 32767
+    lens = torch.from_numpy(lens_np).cuda()
+    out = qb200.kv_decode_attention(q, kv, vv, bits, 64, D ** -0.5, kv_lens=lens)
+    out32 = qb200.kv_decode_attention(q.float(), kv, vv, bits, 64, D ** -0.5, kv_lens=lens)
+    torch.cuda.synchronize()
+    assert not torch.isnan(out).any()
+    for b in (0, 5):
+        qh = q[b:b + 1, :, 0].float().cpu().numpy()
+        ref = qo.kv_decode_attention(qh, *_host_seq(kt, b, T), *_host_seq(vt, b, T), 64, bits, D ** -0.5,
+                                     kv_lens=lens_np[b:b + 1])
+        r32 = gate_f32(out32[b:b + 1, :, 0].cpu().numpy(), ref, f"fp32 q, sequence {b}")
+        got = out[b:b + 1, :, 0].float().cpu().numpy()
+        r16 = gate_bf16(got, ref, f"bf16 q, sequence {b}", slack=4e-3)
+        record(f"C5 T=32768 {bits}-bit, B=16 ragged, sequence {b}", "fp32 q vs oracle", r32, None, int(ref.size))
+        record(f"C5 T=32768 {bits}-bit, B=16 ragged, sequence {b}", "bf16 q vs oracle (unrounded fp32)", r16,
+               half_ulp_fraction(got, ref), int(ref.size))
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_sixteen_caches_of_different_capacity_through_the_pointer_form(bits):
+    """forwardBatchedDecode's situation (src/transformer.zig:9742-9792): every slot owns a B=1 cache with its own
+    capacity and offset.  Sixteen such caches through qb200_kv_decode_attention_ptrs against the oracle, sequence by
+    sequence, and against the single-tensor entry on the same data."""
+    import qb200
+    rng = np.random.default_rng(0xA14 + bits)
+    B, Hq, Hkv, D = 16, 32, 8, 128
+    lens = [int(x) for x in rng.integers(1, 1500, B)]
+    lens[0], lens[1], lens[2] = 1, 128, 1499
+    q = rand_bf16(rng, (B, Hq, D))
+    ktr, vtr, refs, hk, hv = [], [], [], [], []
+    for b in range(B):
+        cap = (lens[b] + 255) // 256 * 256 + 256 * int(rng.integers(0, 3))   # capacity grows in 256-token chunks
+        kt, vt = _cache(rng, 1, Hkv, cap, D, bits)
+        hk.append([a[:, :, :lens[b]] for a in kt])
+        hv.append([a[:, :, :lens[b]] for a in vt])
+        refs.append(qo.kv_decode_attention(q[b:b + 1], *hk[b], *hv[b], 64, bits, D ** -0.5))
+        ktr.append([t[:, :, :lens[b]] for t in dev_triple(*kt)])
+        vtr.append([t[:, :, :lens[b]] for t in dev_triple(*vt)])
+    ref = np.concatenate(refs, 0)
+    o32 = qb200.kv_decode_attention_ptrs(torch.from_numpy(q).cuda().view(B, Hq, 1, D), ktr, vtr, bits, 64, D ** -0.5)
+    r32 = gate_f32(o32.cpu().numpy().reshape(B, Hq, D), ref, "fp32 q, pointer form")
+    o16 = qb200.kv_decode_attention_ptrs(to_dev_bf16(qo.f32_to_bf16(q)).view(B, Hq, 1, D), ktr, vtr, bits, 64, D ** -0.5)
+    got = o16.float().cpu().numpy().reshape(B, Hq, D)
+    r16 = gate_bf16(got, ref, "bf16 q, pointer form", slack=4e-3)
+    record(f"a14 16 caches of different capacity, {bits}-bit", "fp32 q vs oracle", r32, None, int(ref.size))
+    record(f"a14 16 caches of different capacity, {bits}-bit", "bf16 q vs oracle (unrounded fp32)", r16,
+           half_ulp_fraction(got, ref), int(ref.size))
+    # kv_lens on top of the views' own lengths
+    cut = np.array([max(1, n // 2) for n in lens], np.int32)
+    o_cut = qb200.kv_decode_attention_ptrs(torch.from_numpy(q).cuda().view(B, Hq, 1, D), ktr, vtr, bits, 64, D ** -0.5,
+                                           kv_lens=torch.from_numpy(cut).cuda())
+    for b in (3, 7):
+        rb = qo.kv_decode_attention(q[b:b + 1], *hk[b], *hv[b], 64, bits, D ** -0.5, kv_lens=cut[b:b + 1])
+        gate_f32(o_cut[b:b + 1].cpu().numpy().reshape(1, Hq, D), rb, "pointer form with kv_lens")
+
+
+def test_pointer_form_other_head_dims_and_more_than_32_sequences():
+    """Geometries only the generic kernel serves (D=64, GQA 6:1) and a batch beyond one launch's table of 32 views."""
+    import qb200
+    rng = np.random.default_rng(0xA15)
+    for (B, Hq, Hkv, D, bits) in ((3, 12, 2, 64, 8), (40, 8, 2, 128, 4)):
+        lens = [int(x) for x in rng.integers(1, 300, B)]
+        q = rand_bf16(rng, (B, Hq, D))
+        ktr, vtr, refs = [], [], []
+        for b in range(B):
+            kt, vt = _cache(rng, 1, Hkv, lens[b] + 7, D, bits)
+            refs.append(qo.kv_decode_attention(q[b:b + 1], *[a[:, :, :lens[b]] for a in kt], *[a[:, :, :lens[b]] for a in vt],
+                                               64, bits, D ** -0.5))
+            ktr.append([t[:, :, :lens[b]] for t in dev_triple(*kt)])
+            vtr.append([t[:, :, :lens[b]] for t in dev_triple(*vt)])
+        o = qb200.kv_decode_attention_ptrs(torch.from_numpy(q).cuda().view(B, Hq, 1, D), ktr, vtr, bits, 64, D ** -0.5)
+        gate_f32(o.cpu().numpy().reshape(B, Hq, D), np.concatenate(refs, 0), f"pointer form D={D} B={B}")

@@ -36,11 +36,29 @@ def test_noalloc_matches_workspace_entry_on_two_calls_in_a_row():
         r = float(ref.float().pow(2).mean().sqrt())
         # same kernels, same split plan: the tolerance of the attention parity tests is far more than needed
         assert float((out.float() - ref.float()).abs().max()) <= 4e-3 * r + 1e-30
+        # and against the CPU oracle on the same packed cache (copied back to the host)
+        from oracle import qoracle as qo
+        from util import from_dev_bf16, from_dev_u32, gate_bf16
+        hk = [from_dev_u32(kt[0]), from_dev_bf16(kt[1]), from_dev_bf16(kt[2])]
+        hv = [from_dev_u32(vt[0]), from_dev_bf16(vt[1]), from_dev_bf16(vt[2])]
+        want = qo.kv_decode_attention(q[:, :, 0].float().cpu().numpy(), *hk, *hv, 64, bits, D ** -0.5,
+                                      kv_lens=lens.cpu().numpy())
+        gate_bf16(out[:, :, 0].float().cpu().numpy(), want, "no-allocation entry vs oracle", slack=4e-3)
         # second call in a row reuses the array that the first one left dirty
         out2 = torch.full_like(ref, float("nan"))
         qb200.kv_decode_attention_noalloc(q, kt, vt, bits, 64, D ** -0.5, out2, kv_lens=lens)
         torch.cuda.synchronize()
         assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
+
+
+def test_size_gate_agrees_with_the_plan_the_launch_uses():
+    """The refusal is decided from the same workspace query the launch plans with: for the shapes tested above it
+    must report a non-zero need that fits the built-in array (no kernel is launched here)."""
+    import qb200
+    cap = qb200.lib().qb200_kv_decode_attention_noalloc_max_scratch()
+    for (B, Hq, Hkv, T, D) in [(4, 32, 8, 3000, 128), (2, 8, 2, 777, 128), (1, 8, 2, 1, 128)]:
+        need = qb200.kv_decode_attention_workspace_size(B, Hq, Hkv, T, D)
+        assert 0 < need <= cap
 
 
 def test_noalloc_rejects_shapes_beyond_the_built_in_scratch():

@@ -1,4 +1,7 @@
 """Helpers shared by the GPU parity tests: seeded inputs, host<->device moves, comparison gates."""
+import json
+import os
+
 import numpy as np
 import torch
 
@@ -43,6 +46,27 @@ def rms(a):
 def bf16_ulp(v):
     a = np.maximum(np.abs(v.astype(np.float64)), 2.0 ** -126)
     return 2.0 ** (np.floor(np.log2(a)) - 7)
+
+
+_TABLE = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out", "parity_table.jsonl")
+
+
+def record(config: str, what: str, max_over_rms: float, frac_half_ulp=None, n=None):
+    """Append one row of the measured-tolerance table (literal max|delta|/RMS and, for bf16 outputs, the fraction of
+    outputs within half a bf16 ulp of the oracle's unrounded value).  Written only where the scratch folder exists."""
+    try:
+        os.makedirs(os.path.dirname(_TABLE), exist_ok=True)
+        with open(_TABLE, "a") as f:
+            f.write(json.dumps({"config": config, "what": what, "max_abs_delta_over_rms": max_over_rms,
+                                "frac_within_half_ulp": frac_half_ulp, "outputs": n}) + "\n")
+    except OSError:
+        pass
+
+
+def half_ulp_fraction(got_f32: np.ndarray, ref_f32: np.ndarray) -> float:
+    """Fraction of bf16 outputs that are the correctly rounded value of the oracle's fp32 result (or within half an ulp)."""
+    d = np.abs(got_f32.astype(np.float64) - ref_f32.astype(np.float64))
+    return float((d <= 0.5 * bf16_ulp(ref_f32) * (1 + 1e-6)).mean())
 
 
 def gate_f32(got: np.ndarray, ref: np.ndarray, what=""):
