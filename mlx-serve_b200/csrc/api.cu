@@ -4,6 +4,7 @@
 // on the host before any CUDA call, so bad input never reaches a kernel.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -220,8 +221,14 @@ QB200_API void qb200_set_error_handler(qb200_error_handler_func handler, void* d
 
 QB200_API const char* qb200_last_error(void) { return g_last_error.c_str(); }
 QB200_API const char* qb200_version(void) { return "qb200 0.1 (sm_100a)"; }
-QB200_API int qb200_debug_tc_status(void) { return qmm_tc_error_code(); }
-QB200_API void qb200_debug_tc_reset(void) { qmm_tc_error_reset(); }
+QB200_API int qb200_debug_tc_status(void) {
+  const int tc = qmm_tc_error_code();
+  return tc ? tc : qmv_wide_error_code();
+}
+QB200_API void qb200_debug_tc_reset(void) {
+  qmm_tc_error_reset();
+  qmv_wide_error_reset();
+}
 
 QB200_API int qb200_quantized_matmul_shape(const qb200_tensor* x, const qb200_tensor* w, const qb200_tensor* scales,
                                            bool transpose_w, qb200_optional_int group_size, qb200_optional_int bits,
@@ -296,13 +303,23 @@ static int prepare_qmm(qb200_tensor* res, const qb200_tensor* x, const qb200_ten
   return QB200_OK;
 }
 
-// Tokens from which the tensor-core kernel (split-K over a cluster when the problem has few tiles) beats
-// re-streaming the weights once per 8 tokens: measured on the C2 layer, four 8-token passes (32 tokens) still win.
-constexpr int64_t kTcMinTokens = 33;
+// Routing by token count.  Up to 8 tokens: the narrow streaming kernel (one launch).  9 .. 64 (bf16 activations): the
+// wide streaming kernel, which reads every packed word once for up to 64 tokens per pass (measured on the C2 layer:
+// 172 us at 64 tokens against 235 us for the tensor-core kernel; at 128 tokens the tensor-core kernel wins, 238 us
+// against 341).  Above that the tensor-core kernel.  QB200_WIDE_MAX_TOKENS in the environment moves the upper limit (0 turns the wide kernel off; a
+// diagnostic for measuring the crossover, read once).
+static int64_t wide_max_tokens() {
+  static const int64_t v = [] {
+    const char* e = getenv("QB200_WIDE_MAX_TOKENS");
+    return e ? (int64_t)atoll(e) : (int64_t)64;
+  }();
+  return v;
+}
+static bool takes_wide(const QmmArgs& a) { return a.M > 8 && a.M <= wide_max_tokens() && qmv_wide_supported(a); }
 
 static cudaError_t dispatch_qmm(const QmmArgs& a, cudaStream_t s) {
-  // decode widths stream the weights once per 8 tokens through the integer-MMA kernel; wider inputs go to tcgen05
-  if (a.M >= kTcMinTokens && qmm_tc_supported(a)) return launch_qmm_tc(a, s);
+  if (takes_wide(a)) return launch_qmv_wide(a, s);
+  if (a.M > wide_max_tokens() && a.M > 8 && qmm_tc_supported(a)) return launch_qmm_tc(a, s);
   if (a.M > 8 && !qmv_stream_supported(a) && qmm_tc_supported(a)) return launch_qmm_tc(a, s);
   if (qmv_stream_supported(a)) return launch_qmv_stream(a, s);
   if (qmv_mma_supported(a)) return launch_qmv_mma(a, s);
@@ -335,16 +352,19 @@ QB200_API int qb200_quantized_matmul_batch(qb200_tensor* const* res, const qb200
     const int n = count - i0 < kChunk ? count - i0 : kChunk;
     QmmArgs a[kChunk];
     bool empty[kChunk];
-    bool fuse = n > 1;
+    bool fuse = n > 1, wide = n > 1;
     for (int i = 0; i < n; ++i) {
       int st = prepare_qmm(res[i0 + i], x, w[i0 + i], scales[i0 + i], biases[i0 + i], transpose_w, group_size, bits,
                            mode, &a[i], &empty[i]);
       if (st) return st;
-      // (from kTcMinTokens tokens the tensor-core kernel serves each matrix: same rule as dispatch_qmm)
-      fuse = fuse && !empty[i] && !(a[i].M >= kTcMinTokens && qmm_tc_supported(a[i])) && qmv_stream_supported(a[i]) && a[i].K == a[0].K;
+      // the matrices share a launch where the single call would take a streaming kernel (same rule as dispatch_qmm)
+      wide = wide && !empty[i] && takes_wide(a[i]) && a[i].K == a[0].K;
+      fuse = fuse && !empty[i] && a[i].M <= 8 && qmv_stream_supported(a[i]) && a[i].K == a[0].K;
     }
     cudaError_t e = cudaSuccess;
-    if (fuse) {
+    if (wide) {
+      e = launch_qmv_wide_multi(a, n, (cudaStream_t)s);
+    } else if (fuse) {
       e = launch_qmv_stream_multi(a, n, (cudaStream_t)s);
     } else {
       for (int i = 0; i < n && e == cudaSuccess; ++i)

@@ -94,6 +94,13 @@ bool qmv_stream_supported(const QmmArgs& a);
 cudaError_t launch_qmv_stream(const QmmArgs& a, cudaStream_t st);
 cudaError_t launch_qmv_stream_multi(const QmmArgs* a, int count, cudaStream_t st);  // same x, <= 4 matrices
 
+// ---- qmv_wide.cu : 9..32 tokens per pass, every packed word read once (stream-K over a persistent grid) ----
+bool qmv_wide_supported(const QmmArgs& a);
+cudaError_t launch_qmv_wide(const QmmArgs& a, cudaStream_t st);
+cudaError_t launch_qmv_wide_multi(const QmmArgs* a, int count, cudaStream_t st);   // same x, <= 4 matrices
+int qmv_wide_error_code();    // 0, or the code of a bounded wait that expired
+void qmv_wide_error_reset();
+
 // ---- qmm_tc.cu : prefill widths on tcgen05 (dequantise into the swizzled smem operand, TMEM accumulate) ----
 bool qmm_tc_supported(const QmmArgs& a);
 cudaError_t launch_qmm_tc(const QmmArgs& a, cudaStream_t st);

@@ -38,11 +38,12 @@ def _run(x32, q, s, b, gs, bits, transpose=True, tag=None):
 
 
 def _tensor_core_route(M, K, bits, gs):
-    """The dispatch rule of qb200_quantized_matmul for bf16 activations: from 33 tokens the tcgen05 kernel (K a
-    multiple of 256, 4/8 bits, group 64/128); below that only where the streaming kernel does not serve the format."""
+    """The dispatch rule of qb200_quantized_matmul for bf16 activations: from 9 tokens a kernel that rounds the weight
+    term to bf16 once, as the reference's dense route does -- the wide streaming kernel (4/8 bits at group 64, 4 bits
+    at group 128, K a multiple of 256 up to 16384) or the tcgen05 kernel (K a multiple of 256, 4/8 bits, group
+    64/128); up to 8 tokens, and for other formats, the fp32 weight term."""
     tc_ok = K % 256 == 0 and bits in (4, 8) and gs in (64, 128)
-    stream_ok = K % 256 == 0 and (bits, gs) in ((4, 64), (4, 128), (8, 64))
-    return tc_ok and (M >= 33 or (M > 8 and not stream_ok))
+    return tc_ok and M > 8 and (M > 64 or K <= 16384 or (bits, gs) == (8, 128))
 
 
 def test_config1_qmv_4096x4096():
@@ -68,10 +69,11 @@ def test_config2_llama_projections(proj, M):
 
 @pytest.mark.parametrize("bits,gs", [(4, 64), (8, 64), (4, 128)])
 @pytest.mark.parametrize("M,N,K", [(16, 4096, 4096), (9, 1024, 4096), (13, 1000, 2048), (16, 512, 14336), (24, 2048, 1024),
-                                   (31, 640, 4096), (16, 14336, 4096), (12, 256, 256)])
-def test_nine_to_thirty_two_tokens(bits, gs, M, N, K):
-    """9..32 tokens: the streaming kernel re-streams the weights once per block of 8 tokens (ragged last block, K staged
-    in passes or cut over a cluster for long K)."""
+                                   (31, 640, 4096), (16, 14336, 4096), (12, 256, 256), (40, 1000, 2048), (64, 640, 4096),
+                                   (57, 4096, 1024), (33, 16, 512)])
+def test_nine_to_sixty_four_tokens(bits, gs, M, N, K):
+    """9..64 tokens: the wide streaming kernel reads the weights once per pass (16-, 32- and 64-token forms, ragged token
+    counts and row counts, K from one ring stage to the longest projection, work cut over the CTAs inside tile blocks)."""
     rng = np.random.default_rng(M * 7 + N + K + bits)
     q, s, b = make_weight(rng, (N, K), gs, bits)
     _run(rand_bf16(rng, (M, K)), q, s, b, gs, bits)
