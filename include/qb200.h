@@ -207,7 +207,9 @@ QB200_API int qb200_moe_sort_by_expert(qb200_tensor* order, qb200_tensor* inv_or
  * res[t, h] = sum_j round(y[inv_order[t*k + j], h] * scores[t, j]).  Replaces mlx_take_axis(inv_order) +
  * mlx_multiply(norm_scores) + mlx_sum_axis(-2) of moeMLP2 (src/transformer.zig:15036-15042, :15127-15140).
  * y [T*k, H] or [T*k, 1, H] in the order its rows were computed (sorted by expert), scores [.., T, k] and res
- * [.., T, H] of y's dtype (bf16 or f32), inv_order [T*k] int32/int64 or empty (rows already in token order).
+ * [.., T, H] of y's dtype (bf16 or f32), inv_order [T*k] int32/int64 or empty (rows already in token order).  With
+ * inv_order y may hold any number of rows (entries outside [0, rows) contribute nothing: the expert-parallel block
+ * picks its rows out of the returned exchange buffer this way).
  * bf16: each product is rounded to bf16, as the reference's multiply in the activation dtype is, and the sum over k
  * is an ascending accumulate in bf16, rounded after every add: the reference's fused down+reduce kernel documents
  * that as MLX's behaviour and replicates it (src/transformer.zig:20566-20571).  f32: plain fp32 sum. */

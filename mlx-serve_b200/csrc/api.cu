@@ -660,7 +660,7 @@ QB200_API int qb200_moe_weighted_sum(qb200_tensor* res, const qb200_tensor* y, c
     return fail(QB200_ERR_BAD_STRIDE, "moe_weighted_sum: y, scores and res must be contiguous");
   const int64_t H = y->shape[y->ndim - 1], topk = scores->shape[scores->ndim - 1];
   const int64_t R = H > 0 ? numel(y) / H : 0, T = topk > 0 ? numel(scores) / topk : 0;
-  if (res->shape[res->ndim - 1] != H || numel(res) != T * H || R != T * topk)
+  if (res->shape[res->ndim - 1] != H || numel(res) != T * H || (is_empty(inv_order) && R != T * topk))
     return fail(QB200_ERR_BAD_SHAPE, "moe_weighted_sum: y [T*k rows, H], scores [T, k], res [T, H] expected");
   if (H % 8 != 0) return fail(QB200_ERR_UNSUPPORTED, "moe_weighted_sum: H must be a multiple of 8");
   const int esz = y->dtype == QB200_FLOAT32 ? 4 : 2;
@@ -668,13 +668,13 @@ QB200_API int qb200_moe_weighted_sum(qb200_tensor* res, const qb200_tensor* y, c
     return fail(QB200_ERR_UNSUPPORTED, "moe_weighted_sum: rows must be 16-byte aligned");
   MoeSumArgs a;
   a.y = y->data; a.scores = scores->data; a.out = res->data; a.inv = nullptr; a.inv_i64 = 0;
-  a.T = T; a.topk = topk; a.H = H; a.dtype = y->dtype;
+  a.T = T; a.topk = topk; a.H = H; a.R = R; a.dtype = y->dtype;
   if (!is_empty(inv_order)) {
     if ((st = check_tensor(inv_order, "inv_order", 0))) return st;
     if (inv_order->dtype != QB200_INT32 && inv_order->dtype != QB200_UINT32 && inv_order->dtype != QB200_INT64)
       return fail(QB200_ERR_BAD_DTYPE, "moe_weighted_sum: inv_order must be int32/uint32/int64");
-    if (numel(inv_order) != R || !fully_contiguous(inv_order))
-      return fail(QB200_ERR_BAD_SHAPE, "moe_weighted_sum: inv_order must hold one contiguous entry per row of y");
+    if (numel(inv_order) != T * topk || !fully_contiguous(inv_order))
+      return fail(QB200_ERR_BAD_SHAPE, "moe_weighted_sum: inv_order must hold one contiguous entry per (token, slot)");
     a.inv = inv_order->data; a.inv_i64 = inv_order->dtype == QB200_INT64;
   }
   if (T == 0 || H == 0) return QB200_OK;

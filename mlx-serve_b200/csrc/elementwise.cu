@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(MoeSumArgs a) {
       if (j0 + q < a.topk) {
         row[q] = a.inv ? (a.inv_i64 ? ((const long long*)a.inv)[e] : (long long)((const int*)a.inv)[e]) : e;
         sc[q] = F32 ? ((const float*)a.scores)[e] : __uint_as_float((uint32_t)((const uint16_t*)a.scores)[e] << 16);
-        if (row[q] >= a.T * a.topk) row[q] = -1;   // out-of-range entries contribute nothing
+        if (row[q] >= a.R) row[q] = -1;   // out-of-range (and negative) entries contribute nothing
       }
     }
     uint4 v0[8], v1[8];

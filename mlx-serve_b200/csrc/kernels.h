@@ -27,6 +27,7 @@ struct MoeSumArgs {
   const void* y; const void* scores; const void* inv; void* out;
   int inv_i64;            // inv may be null: row t*k + j
   int64_t T, topk, H;
+  int64_t R;              // rows of y (T * topk unless inv picks rows out of a larger buffer)
   int dtype;              // QB200_BFLOAT16 or QB200_FLOAT32 (y, scores and out)
 };
 cudaError_t launch_moe_weighted_sum(const MoeSumArgs& a, cudaStream_t st);

@@ -1,155 +1,193 @@
-"""Expert-parallel routed-MoE block around gather_qmm (one process per GPU).
+"""Expert-parallel routed-expert block: binding of libqb200_ep.so and a host mirror of its exchange plan.
 
-mlx-serve runs its MoE layer on one device: route, sort rows by expert, three ``gather_qmm`` calls with a
-SwiGLU in between, un-permute, weight by the router scores and sum over the top-k
-(``moeMLP2``, src/transformer.zig:14961-15043 and :15127-15140; routing ``moeRoutingChain`` :17022-17063).
-Here the experts are partitioned over the ranks of a process group -- rank r owns experts
-[r*E/G, (r+1)*E/G) -- and the token rows are exchanged once each way:
+The product is the C entry ``qb200_moe_block_ep`` (include/qb200_ep.h): sort by expert, pack per destination
+rank, NCCL all-to-all of rows and expert ids, the library's fused gate/up + SwiGLU and down kernels on the local
+experts, all-to-all back, score-weighted sum -- rank r owns experts [r*E/world, (r+1)*E/world).  It stands for
+moeMLP2 (mlx-serve src/transformer.zig:14945-15140) run over several GPUs.
 
-    route locally -> sort rows by expert (rows for one destination rank are then contiguous)
-    -> all-to-all of per-destination row counts
-    -> dispatch all-to-all of the rows (and their expert ids)
-    -> local gather_qmm(gate), gather_qmm(up), SwiGLU, gather_qmm(down) on the owned experts
-    -> combine all-to-all back to the row's owner
-    -> owner applies the router weights and sums over the top-k.
-
-Two exchange plans: ``moe_block_ep`` sends exactly the routed rows (the per-destination counts are exchanged
-first, which costs a host synchronisation: right for prefill-sized inputs) and ``moe_block_ep_padded`` sends
-fixed-size blocks (every rank may receive all of a peer's T*k rows; unused slots carry expert id -1, which
-gather_qmm skips), so that nothing on the host waits for the device: right for decode-sized inputs.
-
-``torch.distributed`` (NCCL on GPUs, gloo in the CPU tests) is only the plumbing; the expert math is
-``expert_fn``, by default the library's gather_qmm through the C ABI.  The rows a rank receives are a
-concatenation of sorted runs, one per source rank, which gather_qmm accepts as is (it never relies on the
-order of the indices).
+``plan_pack`` / ``moe_block_ep_host`` restate the same plan on the host with numpy index arithmetic and
+``torch.distributed`` (any backend), the expert math supplied by the caller.  They exist for the CPU tests of the
+exchange logic (gloo ranks, expert math by the CPU oracle) and are not on any GPU path.
 """
 from __future__ import annotations
 
+import ctypes as C
+import os
+
+import numpy as np
 import torch
 import torch.distributed as dist
 
+from . import Tensor, _packed, check, desc, lib as core_lib
 
-def route(logits: torch.Tensor, k: int, dtype=torch.bfloat16):
-    """softmax -> top-k -> renormalise (src/transformer.zig:17022-17063).  Returns (inds [T,k] int64, w [T,k])."""
-    p = torch.softmax(logits.float(), dim=-1)
-    topv, topi = torch.topk(p, k, dim=-1)
-    w = (topv / topv.sum(dim=-1, keepdim=True)).to(dtype)
-    return topi, w
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+EP_LIB_PATH = os.path.join(_PKG, "libqb200_ep.so")
+_ep = None
 
 
-def swiglu(g: torch.Tensor, u: torch.Tensor) -> torch.Tensor:
-    """silu(g) * u with each op's result in the activation dtype (src/transformer.zig:20157-20159)."""
-    return (torch.nn.functional.silu(g.float()).to(g.dtype).float() * u.float()).to(g.dtype)
+def ep_lib():
+    """Load libqb200_ep.so (after the core library, which it links); fails loudly when it has not been built."""
+    global _ep
+    if _ep is None:
+        core_lib()
+        if not os.path.exists(EP_LIB_PATH):
+            raise FileNotFoundError(f"{EP_LIB_PATH} is missing: build it with `make -C {_PKG}`")
+        L = C.CDLL(EP_LIB_PATH)
+        TP = C.POINTER(Tensor)
+        L.qb200_ep_unique_id.argtypes = [C.c_void_p]
+        L.qb200_ep_comm_create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p]
+        L.qb200_ep_comm_destroy.argtypes = [C.c_void_p]
+        L.qb200_moe_block_ep_capacity.restype = C.c_int64
+        L.qb200_moe_block_ep_capacity.argtypes = [C.c_int64, C.c_int, C.c_int]
+        L.qb200_moe_block_ep_workspace_size.restype = C.c_size_t
+        L.qb200_moe_block_ep_workspace_size.argtypes = [C.c_int64, C.c_int, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_int64]
+        L.qb200_moe_block_ep.argtypes = [TP] * 13 + [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int64, C.c_int, C.c_int,
+                                                     C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+        for n in ("qb200_ep_unique_id", "qb200_ep_comm_create", "qb200_ep_comm_destroy", "qb200_moe_block_ep"):
+            getattr(L, n).restype = C.c_int
+        _ep = L
+    return _ep
 
 
-def default_expert_fn(banks, group_size=64, bits=4):
-    """expert_fn over local banks {'gate','up','down': (q, scales, biases)} using the CUDA library."""
-    import qb200
+def make_comm(world: int, rank: int, device):
+    """An NCCL communicator for the block, made with the NCCL the library links; the unique id travels over
+    torch.distributed (plumbing only)."""
+    L = ep_lib()
+    buf = torch.zeros(128, dtype=torch.uint8)
+    if rank == 0:
+        raw = (C.c_ubyte * 128)()
+        check(L.qb200_ep_unique_id(raw))
+        buf = torch.tensor(list(raw), dtype=torch.uint8)
+    if world > 1:
+        on = buf.to(device) if dist.get_backend() == "nccl" else buf
+        dist.broadcast(on, 0)
+        buf = on.cpu()
+    raw = (C.c_ubyte * 128)(*buf.tolist())
+    comm = C.c_void_p()
+    check(L.qb200_ep_comm_create(C.byref(comm), world, rank, raw))
+    return comm
 
-    def fn(name, rows, expert_ids):
-        q, s, b = banks[name]
-        out = qb200.gather_qmm(rows.unsqueeze(1).contiguous(), q, s, b, None, expert_ids.to(torch.int32).contiguous(),
-                               True, group_size, bits, sorted_indices=False)
-        return out.squeeze(1)
-    return fn
+
+def capacity(T: int, topk: int, world: int) -> int:
+    return int(ep_lib().qb200_moe_block_ep_capacity(T, topk, world))
 
 
-def _a2a(t: torch.Tensor, out_splits, in_splits, group):
-    out = t.new_empty((int(sum(out_splits)),) + tuple(t.shape[1:]))
-    dist.all_to_all_single(out, t.contiguous(), output_split_sizes=list(out_splits), input_split_sizes=list(in_splits),
-                           group=group)
-    return out
+class Block:
+    """Workspace, overflow counter and output of one expert-parallel block, allocated once and reused."""
+
+    def __init__(self, T, topk, H, I, E, world, rank, comm, banks, cap=None, group_size=64, bits=4, device="cuda"):
+        L = ep_lib()
+        self.T, self.topk, self.H, self.I, self.E, self.world, self.rank, self.comm = T, topk, H, I, E, world, rank, comm
+        self.cap = capacity(T, topk, world) if cap is None else cap
+        self.gs, self.bits = group_size, bits
+        need = int(L.qb200_moe_block_ep_workspace_size(T, topk, H, I, E, world, self.cap))
+        self.ws = torch.empty(need, dtype=torch.uint8, device=device)
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=device)
+        self.out = torch.empty((T, H), dtype=torch.bfloat16, device=device)
+        self.banks = banks   # {"gate": (q, s, b), "up": ..., "down": ...} of this rank's experts
+
+    def run(self, x, inds, scores):
+        L = ep_lib()
+        ds = [desc(self.out), desc(x), desc(inds), desc(scores)]
+        for name in ("gate", "up", "down"):
+            q, s, b = self.banks[name]
+            ds += [_packed(q), desc(s), desc(b)]
+        check(L.qb200_moe_block_ep(*[C.byref(d) for d in ds], self.E, self.world, self.rank, self.comm, self.cap, self.gs,
+                                   self.bits, C.c_void_p(self.overflow.data_ptr()), C.c_void_p(self.ws.data_ptr()),
+                                   self.ws.numel(), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return self.out
 
 
-def moe_block_ep(x: torch.Tensor, inds: torch.Tensor, weights: torch.Tensor, num_experts: int, expert_fn,
-                 group=None) -> torch.Tensor:
-    """One routed-MoE block for this rank's tokens x [T, H]; experts are spread over ``group``.
+# ---------------------------------------------------------------------------------------------------------------
+# Host mirror of the exchange plan (index arithmetic only), for the CPU tests.
 
-    ``expert_fn(name, rows [R, K], local_expert_ids [R]) -> [R, N]`` runs one projection on the owned experts.
-    With a single rank (or no initialised process group) the exchange degenerates to the identity.
-    """
-    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
-    rank = dist.get_rank(group) if world > 1 else 0
-    T, k = inds.shape
-    per_rank = (num_experts + world - 1) // world
+def plan_pack(inds: np.ndarray, E: int, world: int, cap: int):
+    """inds [T, k] -> (send_src [world, cap] position in the flattened index list or -1, send_e [world, cap] local
+    expert id or E/world for padding, back_row [T*k] row of the returned buffer or -1, overflow rows)."""
     flat = inds.reshape(-1)
-    order = torch.argsort(flat, stable=True)
-    sorted_e = flat[order]
-    src_tok = torch.div(order, k, rounding_mode="floor")
-    rows = x[src_tok]
-    if world > 1:
-        dest = torch.div(sorted_e, per_rank, rounding_mode="floor")
-        send_counts = torch.bincount(dest, minlength=world).to(torch.int64)
-        recv_counts = torch.empty_like(send_counts)
-        dist.all_to_all_single(recv_counts, send_counts, group=group)
-        send_l, recv_l = send_counts.tolist(), recv_counts.tolist()
-        rows_in = _a2a(rows, recv_l, send_l, group)
-        e_in = _a2a(sorted_e, recv_l, send_l, group)
-    else:
-        send_l = recv_l = None
-        rows_in, e_in = rows, sorted_e
-    local_e = e_in - rank * per_rank
-    if rows_in.shape[0] > 0:
-        g = expert_fn("gate", rows_in, local_e)
-        u = expert_fn("up", rows_in, local_e)
-        d = expert_fn("down", swiglu(g, u), local_e)
-    else:
-        d = rows_in.new_empty((0, x.shape[1]))
-    d_back = _a2a(d, send_l, recv_l, group) if world > 1 else d
-    # weight by the router score (product rounded to the activation dtype, src/transformer.zig:20567-20571)
-    w_sorted = weights.reshape(-1)[order]
-    contrib = (d_back.float() * w_sorted.float().unsqueeze(1)).to(x.dtype).float()
-    out = torch.zeros((T, x.shape[1]), dtype=torch.float32, device=x.device)
-    out.index_add_(0, src_tok, contrib)
-    return out.to(x.dtype)
+    n, El = flat.size, E // world
+    key = np.where((flat < 0) | (flat >= E), E, flat)
+    order = np.argsort(key, kind="stable")
+    inv = np.argsort(order, kind="stable")
+    offs = np.concatenate([[0], np.cumsum(np.bincount(key, minlength=E + 1)[:E])])
+    send_src = np.full((world, cap), -1, np.int64)
+    send_e = np.full((world, cap), El, np.int32)
+    overflow = 0
+    for r in range(world):
+        p0, p1 = offs[r * El], offs[(r + 1) * El]
+        m = min(p1 - p0, cap)
+        send_src[r, :m] = order[p0:p0 + m]
+        send_e[r, :m] = flat[order[p0:p0 + m]] - r * El
+        overflow += max(0, p1 - p0 - cap)
+    back_row = np.full(n, -1, np.int64)
+    for i in range(n):
+        e = flat[i]
+        if 0 <= e < E:
+            r = e // El
+            slot = inv[i] - offs[r * El]
+            if slot < cap:
+                back_row[i] = r * cap + slot
+    return send_src, send_e, back_row, int(overflow)
 
 
-def moe_block_ep_padded(x: torch.Tensor, inds: torch.Tensor, weights: torch.Tensor, num_experts: int, expert_fn,
-                        group=None) -> torch.Tensor:
-    """The same block with fixed-size exchange buffers and no host synchronisation.
-
-    Every rank sends each peer a block of T*k row slots (rows for that peer first, in expert order; the rest
-    empty with expert id -1) and gets blocks of the same size back, so all collectives have static shapes and
-    the whole block can be enqueued (or captured in a CUDA graph) without reading anything back.
-    ``expert_fn`` must leave rows whose local expert id is negative alone (the library's gather_qmm does).
-    """
-    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
-    rank = dist.get_rank(group) if world > 1 else 0
+def moe_block_ep_host(x: np.ndarray, inds: np.ndarray, scores: np.ndarray, E: int, cap: int, expert_fn, weighted_sum):
+    """The block over torch.distributed with the plan above.  ``expert_fn(rows [R, H], local_ids [R]) -> [R, H]``
+    computes gate/up + SwiGLU + down for rows whose id is in range and leaves the others alone;
+    ``weighted_sum(y [R, H], scores [T, k], rows [T*k]) -> [T, H]``.  A peer that does not show up makes the
+    all_to_all raise after the process group's timeout: the exchange has no other way to wait."""
+    world, rank = dist.get_world_size(), dist.get_rank()
     T, k = inds.shape
-    R, H = T * k, x.shape[1]
-    per_rank = (num_experts + world - 1) // world
-    dev = x.device
-    flat = inds.reshape(-1)
-    order = torch.argsort(flat, stable=True)
-    sorted_e = flat[order]
-    src_tok = torch.div(order, k, rounding_mode="floor")
-    dest = torch.div(sorted_e, per_rank, rounding_mode="floor")           # ascending
-    starts = torch.searchsorted(dest, torch.arange(world, device=dev, dtype=dest.dtype))
-    pos = torch.arange(R, device=dev) - starts[dest]                      # slot inside the destination's block
-    send_rows = x.new_zeros((world, R, H))
-    send_rows[dest, pos] = x[src_tok]
-    send_ids = torch.full((world, R), -1, dtype=torch.int64, device=dev)
-    send_ids[dest, pos] = sorted_e - dest * per_rank
+    H = x.shape[1]
+    src, send_e, back_row, overflow = plan_pack(inds, E, world, cap)
+    send_x = np.zeros((world, cap, H), np.float32)
+    live = src >= 0
+    send_x[live] = x[src[live] // k]
+    recv_x, recv_e = torch.empty((world, cap, H)), torch.empty((world, cap), dtype=torch.int32)
+    dist.all_to_all_single(recv_x, torch.from_numpy(send_x))
+    dist.all_to_all_single(recv_e, torch.from_numpy(send_e))
+    y = expert_fn(recv_x.numpy().reshape(world * cap, H), recv_e.numpy().reshape(-1))
+    back = torch.empty((world, cap, H))
+    dist.all_to_all_single(back, torch.from_numpy(np.ascontiguousarray(y, np.float32).reshape(world, cap, H)))
+    return weighted_sum(back.numpy().reshape(world * cap, H), scores, back_row), overflow
+
+
+# ---------------------------------------------------------------------------------------------------------------
+
+def bench_block(dev, g, world, rank, steps=20, T=64):
+    """Benchmark configuration 3, decode: 128 experts top-8, hidden 2048, expert width 768, 4-bit g64, T tokens per
+    GPU, experts sharded over the ranks.  Device time of the block (max over ranks), tokens/s of the whole job."""
+    from . import moe_route, quantize
+    E, H, I, topk = 128, 2048, 768, 8
+    per = E // world
+    banks = {}
+    for name, (n, k) in (("gate", (I, H)), ("up", (I, H)), ("down", (H, I))):
+        w = (torch.randn((per, n, k), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        banks[name] = quantize(w, 64, 4)
+        del w
+    comm = make_comm(world, rank, dev)
+    blk = Block(T, topk, H, I, E, world, rank, comm, banks, device=dev)
+    x = torch.randn((T, H), device=dev, generator=g).to(torch.bfloat16)
+    inds, scores = moe_route(torch.randn((T, E), device=dev, generator=g).to(torch.bfloat16), topk)
+    for _ in range(5):
+        out = blk.run(x, inds, scores)
+    torch.cuda.synchronize()
     if world > 1:
-        rows_in = torch.empty_like(send_rows)
-        ids_in = torch.empty_like(send_ids)
-        dist.all_to_all_single(rows_in, send_rows, group=group)
-        dist.all_to_all_single(ids_in, send_ids, group=group)
-    else:
-        rows_in, ids_in = send_rows, send_ids
-    rows_in = rows_in.reshape(world * R, H)
-    ids_in = ids_in.reshape(world * R)
-    g = expert_fn("gate", rows_in, ids_in)
-    u = expert_fn("up", rows_in, ids_in)
-    d = expert_fn("down", swiglu(g, u), ids_in).reshape(world, R, H)
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        out = blk.run(x, inds, scores)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
     if world > 1:
-        d_back = torch.empty_like(d)
-        dist.all_to_all_single(d_back, d.contiguous(), group=group)
-    else:
-        d_back = d
-    picked = d_back[dest, pos]                                            # [R, H]: the routed rows, in sorted order
-    w_sorted = weights.reshape(-1)[order]
-    contrib = (picked.float() * w_sorted.float().unsqueeze(1)).to(x.dtype).float()
-    out = torch.zeros((T, H), dtype=torch.float32, device=dev)
-    out.index_add_(0, src_tok, contrib)
-    return out.to(x.dtype)
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    res = {"n_gpus": world, "experts_per_gpu": per, "tokens_per_gpu": T, "capacity_rows_per_peer": blk.cap,
+           "us_per_block": ms * 1e3, "tokens_per_s": world * T / (ms * 1e-3), "overflow_rows": int(blk.overflow.item()),
+           "nan": bool(torch.isnan(out).any()),
+           "nvlink_bytes_per_gpu_per_block": 2 * (world - 1) * blk.cap * H * 2 + (world - 1) * blk.cap * 4,
+           "launches_per_block": "5 kernels (sort, pack, gate/up+SwiGLU, down, weighted sum) + 2 NCCL groups"}
+    ep_lib().qb200_ep_comm_destroy(comm)
+    return res

@@ -15,8 +15,8 @@ def q():
     return qb200
 
 
-def declared_symbols():
-    src = open(os.path.join(ROOT, "include", "qb200.h")).read()
+def declared_symbols(header="qb200.h"):
+    src = open(os.path.join(ROOT, "include", header)).read()
     return sorted(set(re.findall(r"QB200_API[^;(]*?\b(qb200_\w+)\s*\(", src)))
 
 
@@ -32,6 +32,19 @@ def test_library_exports_every_declared_symbol(q):
     for s in declared_symbols():
         assert hasattr(L, s), f"{s} declared in qb200.h but not exported"
     assert b"sm_100a" in L.qb200_version()
+
+
+def test_expert_parallel_library_exports_every_declared_symbol(q):
+    from qb200 import ep
+    L = ep.ep_lib()
+    syms = declared_symbols("qb200_ep.h")
+    assert "qb200_moe_block_ep" in syms and "qb200_ep_comm_create" in syms
+    for s in syms:
+        assert hasattr(L, s), f"{s} declared in qb200_ep.h but not exported"
+    # capacity rule: never more than T*k rows per peer, and world * capacity within the 2048 rows the local kernels serve
+    assert L.qb200_moe_block_ep_capacity(64, 8, 8) == 256 and L.qb200_moe_block_ep_capacity(64, 8, 2) == 512
+    assert L.qb200_moe_block_ep_capacity(4, 8, 2) == 32
+    assert L.qb200_moe_block_ep_workspace_size(64, 8, 2048, 768, 128, 8, 256) > 3 * 2048 * 2048 * 2
 
 
 def _t(q, dtype, shape, ptr=0x1000):

@@ -218,26 +218,6 @@ def test_non_finite_activations_reach_the_output():
     assert not np.isfinite(y[7]).any() and np.isfinite(np.delete(y, 7, axis=0)).all()
 
 
-def test_moe_block_padded_exchange_plan_matches_exact_plan_on_one_gpu():
-    """The two exchange plans of the expert-parallel block (exact counts / fixed-size blocks whose empty slots carry
-    expert id -1) give identical outputs through the CUDA gather_qmm, which must skip the empty slots."""
-    from qb200 import ep
-    import qb200
-    E, H, I, T, k = 16, 512, 256, 24, 4
-    g = torch.Generator(device="cuda").manual_seed(7)
-    banks = {}
-    for name, (n, kk) in (("gate", (I, H)), ("up", (I, H)), ("down", (H, I))):
-        w = (torch.randn((E, n, kk), device="cuda", generator=g) * 0.05).to(torch.bfloat16)
-        banks[name] = qb200.quantize(w, 64, 4)
-    fn = ep.default_expert_fn(banks)
-    x = torch.randn((T, H), device="cuda", generator=g).to(torch.bfloat16)
-    inds, w = ep.route(torch.randn((T, E), device="cuda", generator=g), k)
-    a = ep.moe_block_ep(x, inds, w, E, fn)
-    b = ep.moe_block_ep_padded(x, inds, w, E, fn)
-    assert not torch.isnan(a).any() and not torch.isnan(b).any()
-    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
-
-
 @pytest.mark.parametrize("T,bits,gs", [(64, 4, 64), (1, 4, 64), (5, 8, 64), (33, 4, 128)])
 def test_fused_gate_up_swiglu_matches_the_unfused_chain(T, bits, gs):
     """qb200_gather_qmm_swiglu against (a) the library's own two gather_qmm results pushed through the oracle's
