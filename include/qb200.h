@@ -90,6 +90,10 @@ typedef struct qb200_optional_dtype {
   int value; /* qb200_dtype */
   bool has_value;
 } qb200_optional_dtype;
+typedef struct qb200_optional_float {
+  float value;
+  bool has_value;
+} qb200_optional_float;
 
 typedef void* qb200_stream; /* cudaStream_t */
 
@@ -305,6 +309,36 @@ QB200_API size_t qb200_kv_decode_attention_noalloc_max_scratch(void);
  * capacity buffers cache_q/cache_s/cache_b [B, Hkv, cap, *]. */
 QB200_API int qb200_kv_append(qb200_tensor* cache_q, qb200_tensor* cache_scales, qb200_tensor* cache_biases,
                               const qb200_tensor* dense, int64_t offset, int bits, int group_size, qb200_stream s);
+
+/* ==== the small operators of the batched decode step around the path (forwardBatchedDecode,
+ * src/transformer.zig:9562-9924); bf16 activations, one launch each ==== */
+
+/* mlx_fast_rms_norm (src/mlx.zig:319; rmsNorm / rmsNormEps, src/transformer.zig:7770-7779):
+ * res[..., i] = round(weight[i] * round(x[..., i] * rsqrt(mean(x^2) + eps))), mean and first product in fp32. */
+QB200_API int qb200_rms_norm(qb200_tensor* res, const qb200_tensor* x, const qb200_tensor* weight, float eps, qb200_stream s);
+/* mlx_add followed by rmsNorm, as the decode step does after the attention and MLP projections
+ * (src/transformer.zig:9836-9843, :9856-9859): sum_res = round(a + b), norm_res = rms_norm(sum_res).  Either result
+ * may be empty (sum only at the end of the last layer; with b empty this is qb200_rms_norm). */
+QB200_API int qb200_add_rms_norm(qb200_tensor* sum_res, qb200_tensor* norm_res, const qb200_tensor* a, const qb200_tensor* b,
+                                 const qb200_tensor* weight, float eps, qb200_stream s);
+/* mlx_fast_rope_dynamic (src/mlx.zig:324; callers src/transformer.zig:9678, :9735): x [N, heads, 1, D], one position
+ * offsets[n] (int32, on the device) per sequence; element i of the first dims/2 pairs with i + dims/2, angle
+ * scale * offset * base^(-2i/dims); elements beyond dims pass through.  res may be x.  traditional must be false and
+ * freqs empty (a frequency table and the interleaved pairing are declined). */
+QB200_API int qb200_rope(qb200_tensor* res, const qb200_tensor* x, int dims, bool traditional, qb200_optional_float base,
+                         float scale, const qb200_tensor* offsets, const qb200_tensor* freqs, qb200_stream s);
+/* fusedSwiGLU of the dense MLP (computeGeglu, src/transformer.zig:8220-8243): silu(gate) * up with the rounding points
+ * of the reference's kernel (src/transformer.zig:19842-19851).  The first call on a device uploads the 128 KiB sigmoid
+ * table (call once before capturing a graph). */
+QB200_API int qb200_swiglu(qb200_tensor* res, const qb200_tensor* gate, const qb200_tensor* up, qb200_stream s);
+/* One new token per sequence into per-sequence packed caches: the per-slot KVCache.update loop of the batched decode
+ * (src/transformer.zig:9738-9756; updateAffine, :3224-3337) as one launch for K and V of every sequence.
+ * k_q[n] ... v_biases[n]: the capacity buffers [1, Hkv, cap_n, last] of sequence n; dense_k / dense_v
+ * [num_seqs, Hkv, 1, D]; offsets[n] (host array) = the token position to write in sequence n. */
+QB200_API int qb200_kv_append_seqs(qb200_tensor* const* k_q, qb200_tensor* const* k_scales, qb200_tensor* const* k_biases,
+                                   qb200_tensor* const* v_q, qb200_tensor* const* v_scales, qb200_tensor* const* v_biases,
+                                   const qb200_tensor* dense_k, const qb200_tensor* dense_v, const int64_t* offsets, int num_seqs,
+                                   int bits, int group_size, qb200_stream s);
 
 #ifdef __cplusplus
 }

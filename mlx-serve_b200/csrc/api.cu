@@ -8,6 +8,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "kernels.h"
 
@@ -1002,6 +1003,151 @@ QB200_API int qb200_kv_decode_attention_ptrs(qb200_tensor* res, const qb200_tens
     const cudaError_t e = launch_kv_attn(c, (cudaStream_t)s, &tab);
     if (e != cudaSuccess) return cuda_fail(e, "kv_decode_attention_ptrs");
   }
+  return QB200_OK;
+}
+
+// ---- the small operators of the batched decode step (bf16 activations) ----
+static int row_view(const qb200_tensor* t, const char* name, int64_t* rows, int64_t* d, int64_t* pitch) {
+  int st;
+  if ((st = check_tensor(t, name, 1))) return st;
+  if (t->dtype != QB200_BFLOAT16) return fail(QB200_ERR_UNSUPPORTED, "%s: bf16 only", name);
+  const RowMap m = make_rowmap(t);
+  if (!m.contiguous) return fail(QB200_ERR_BAD_STRIDE, "%s: rows must be evenly spaced", name);
+  *rows = rows_of(t); *d = t->shape[t->ndim - 1]; *pitch = t->ndim >= 2 ? m.row_pitch : *d;
+  return 0;
+}
+
+QB200_API int qb200_add_rms_norm(qb200_tensor* sum_res, qb200_tensor* norm_res, const qb200_tensor* a, const qb200_tensor* b,
+                                 const qb200_tensor* weight, float eps, qb200_stream s) {
+  int st;
+  int64_t rows, d, lda, r2, d2, ldb = 0, lds = 0, ldn = 0;
+  if ((st = row_view(a, "a", &rows, &d, &lda))) return st;
+  if (d % 2 != 0 || d > 32768) return fail(QB200_ERR_UNSUPPORTED, "rms_norm: row length must be even and at most 32768");
+  if ((((uintptr_t)a->data) | (uintptr_t)(lda * 2)) & 3) return fail(QB200_ERR_UNSUPPORTED, "rms_norm: rows must be 4-byte aligned");
+  const uint16_t* bp = nullptr; uint16_t* sp = nullptr; uint16_t* np_ = nullptr; const uint16_t* wp = nullptr;
+  if (!is_empty(b)) {
+    if ((st = row_view(b, "b", &r2, &d2, &ldb))) return st;
+    if (r2 != rows || d2 != d || ((((uintptr_t)b->data) | (uintptr_t)(ldb * 2)) & 3)) return fail(QB200_ERR_BAD_SHAPE, "add_rms_norm: a and b must have the same shape");
+    bp = (const uint16_t*)b->data;
+    if (!is_empty(sum_res)) {
+      if ((st = row_view(sum_res, "sum_res", &r2, &d2, &lds))) return st;
+      if (r2 != rows || d2 != d || ((((uintptr_t)sum_res->data) | (uintptr_t)(lds * 2)) & 3)) return fail(QB200_ERR_BAD_SHAPE, "add_rms_norm: sum_res must have a's shape");
+      sp = (uint16_t*)sum_res->data;
+    }
+  } else if (!is_empty(sum_res)) {
+    return fail(QB200_ERR_BAD_ARG, "add_rms_norm: sum_res without b");
+  }
+  if (!is_empty(norm_res)) {
+    if ((st = row_view(norm_res, "norm_res", &r2, &d2, &ldn))) return st;
+    if (r2 != rows || d2 != d || ((((uintptr_t)norm_res->data) | (uintptr_t)(ldn * 2)) & 3)) return fail(QB200_ERR_BAD_SHAPE, "rms_norm: res must have x's shape");
+    if ((st = check_tensor(weight, "weight", 1))) return st;
+    if (weight->dtype != QB200_BFLOAT16 || weight->ndim != 1 || weight->shape[0] != d || (((uintptr_t)weight->data) & 3))
+      return fail(QB200_ERR_BAD_SHAPE, "rms_norm: weight must be bf16 [d]");
+    np_ = (uint16_t*)norm_res->data; wp = (const uint16_t*)weight->data;
+  }
+  if (!sp && !np_) return QB200_OK;
+  const cudaError_t e = launch_rms_norm((const uint16_t*)a->data, bp, wp, sp, np_, rows, (int)d, lda, ldb, lds, ldn, eps, (cudaStream_t)s);
+  if (e != cudaSuccess) return cuda_fail(e, "rms_norm");
+  return QB200_OK;
+}
+
+QB200_API int qb200_rms_norm(qb200_tensor* res, const qb200_tensor* x, const qb200_tensor* weight, float eps, qb200_stream s) {
+  return qb200_add_rms_norm(nullptr, res, x, nullptr, weight, eps, s);
+}
+
+QB200_API int qb200_rope(qb200_tensor* res, const qb200_tensor* x, int dims, bool traditional, qb200_optional_float base,
+                         float scale, const qb200_tensor* offsets, const qb200_tensor* freqs, qb200_stream s) {
+  int st;
+  if ((st = check_tensor(res, "res", 4)) || (st = check_tensor(x, "x", 4)) || (st = check_tensor(offsets, "offsets", 1))) return st;
+  if (traditional) return fail(QB200_ERR_UNSUPPORTED, "rope: the traditional (interleaved) pairing is not served");
+  if (!is_empty(freqs) || !base.has_value) return fail(QB200_ERR_UNSUPPORTED, "rope: a frequency table is not served (give a base)");
+  if (x->ndim != 4 || res->ndim != 4 || x->dtype != QB200_BFLOAT16 || res->dtype != QB200_BFLOAT16)
+    return fail(QB200_ERR_UNSUPPORTED, "rope: x and res must be bf16 [N, heads, 1, D]");
+  const int64_t N = x->shape[0], Hh = x->shape[1], D = x->shape[3];
+  if (x->shape[2] != 1) return fail(QB200_ERR_UNSUPPORTED, "rope: sequence length 1 only (the decode step)");
+  for (int d = 0; d < 4; ++d)
+    if (res->shape[d] != x->shape[d]) return fail(QB200_ERR_BAD_SHAPE, "rope: res must have x's shape");
+  if (dims <= 0 || dims % 2 != 0 || dims > D || D % 2 != 0) return fail(QB200_ERR_BAD_SHAPE, "rope: dims must be even and at most D");
+  if (offsets->dtype != QB200_INT32 || offsets->ndim != 1 || offsets->shape[0] != N || offsets->stride[0] != 1)
+    return fail(QB200_ERR_BAD_SHAPE, "rope: offsets must be int32 [N]");
+  if (N == 0 || Hh == 0) return QB200_OK;
+  const cudaError_t e = launch_rope((const uint16_t*)x->data, (uint16_t*)res->data, (const int32_t*)offsets->data, N, (int)Hh, (int)D,
+                                    dims, base.value, scale, x->stride[0], x->stride[1], res->stride[0], res->stride[1], (cudaStream_t)s);
+  if (e != cudaSuccess) return cuda_fail(e, "rope");
+  return QB200_OK;
+}
+
+QB200_API int qb200_swiglu(qb200_tensor* res, const qb200_tensor* gate, const qb200_tensor* up, qb200_stream s) {
+  int st;
+  int64_t rows, d, ldg, r2, d2, ldu, ldo;
+  if ((st = row_view(gate, "gate", &rows, &d, &ldg)) || (st = row_view(up, "up", &r2, &d2, &ldu))) return st;
+  if (r2 != rows || d2 != d) return fail(QB200_ERR_BAD_SHAPE, "swiglu: gate and up must have the same shape");
+  if ((st = row_view(res, "res", &r2, &d2, &ldo))) return st;
+  if (r2 != rows || d2 != d) return fail(QB200_ERR_BAD_SHAPE, "swiglu: res must have gate's shape");
+  if (d % 2 != 0 || ((((uintptr_t)gate->data) | ((uintptr_t)up->data) | ((uintptr_t)res->data) | (uintptr_t)((ldg | ldu | ldo) * 2)) & 3))
+    return fail(QB200_ERR_UNSUPPORTED, "swiglu: rows must be even and 4-byte aligned");
+  const cudaError_t e = launch_swiglu((const uint16_t*)gate->data, (const uint16_t*)up->data, (uint16_t*)res->data, rows, (int)d, ldg, ldu,
+                                      ldo, (cudaStream_t)s);
+  if (e != cudaSuccess) return cuda_fail(e, "swiglu");
+  return QB200_OK;
+}
+
+QB200_API int qb200_kv_append_seqs(qb200_tensor* const* k_q, qb200_tensor* const* k_scales, qb200_tensor* const* k_biases,
+                                   qb200_tensor* const* v_q, qb200_tensor* const* v_scales, qb200_tensor* const* v_biases,
+                                   const qb200_tensor* dense_k, const qb200_tensor* dense_v, const int64_t* offsets, int num_seqs,
+                                   int bits, int group_size, qb200_stream s) {
+  int gs, nb, st;
+  qb200_optional_int og = {group_size, true}, ob = {bits, true};
+  if ((st = resolve_mode("affine", og, ob, &gs, &nb))) return st;
+  if (nb == 2) return fail(QB200_ERR_UNSUPPORTED, "kv_append_seqs: bits must be 4 or 8");
+  if ((st = check_tensor(dense_k, "dense_k", 4)) || (st = check_tensor(dense_v, "dense_v", 4))) return st;
+  if (dense_k->ndim != 4 || dense_v->ndim != 4 || dense_k->dtype != QB200_BFLOAT16 || dense_v->dtype != QB200_BFLOAT16)
+    return fail(QB200_ERR_UNSUPPORTED, "kv_append_seqs: dense K and V must be bf16 [N, Hkv, 1, D]");
+  const int64_t N = dense_k->shape[0], Hkv = dense_k->shape[1];
+  if (N != num_seqs || dense_v->shape[0] != N || dense_v->shape[1] != Hkv || dense_k->shape[2] != 1 || dense_v->shape[2] != 1)
+    return fail(QB200_ERR_BAD_SHAPE, "kv_append_seqs: one new token per sequence, dense [num_seqs, Hkv, 1, D]");
+  if (num_seqs < 0 || (num_seqs > 0 && (!k_q || !k_scales || !k_biases || !v_q || !v_scales || !v_biases || !offsets)))
+    return fail(QB200_ERR_BAD_ARG, "kv_append_seqs: null list");
+  if (num_seqs == 0) return QB200_OK;
+  if (num_seqs > 4096) return fail(QB200_ERR_UNSUPPORTED, "kv_append_seqs: at most 4096 sequences");
+  const int vpw = 32 / nb;
+  const int64_t D[2] = {dense_k->shape[3], dense_v->shape[3]};
+  if (D[0] % gs != 0 || D[1] % gs != 0) return fail(QB200_ERR_BAD_SHAPE, "kv_append_seqs: head dims must be multiples of group_size");
+  std::vector<uint32_t*> q[2]; std::vector<uint16_t*> sc[2], bi[2]; std::vector<int64_t> qh[2], sbh[2];
+  for (int64_t n = 0; n < N; ++n) {
+    qb200_tensor* const ts[2][3] = {{k_q[n], k_scales[n], k_biases[n]}, {v_q[n], v_scales[n], v_biases[n]}};
+    for (int kv = 0; kv < 2; ++kv) {
+      for (int i = 0; i < 3; ++i) {
+        if ((st = check_tensor(ts[kv][i], "cache", 4))) return st;
+        if (ts[kv][i]->ndim != 4 || ts[kv][i]->shape[0] != 1 || ts[kv][i]->shape[1] != Hkv)
+          return fail(QB200_ERR_BAD_SHAPE, "kv_append_seqs: every cache buffer must be [1, Hkv, cap, last]");
+        if (ts[kv][i]->dtype != (i == 0 ? QB200_UINT32 : QB200_BFLOAT16))
+          return fail(QB200_ERR_BAD_DTYPE, "kv_append_seqs: codes uint32, scales and biases bf16");
+        if (ts[kv][i]->shape[2] != ts[kv][0]->shape[2]) return fail(QB200_ERR_BAD_SHAPE, "kv_append_seqs: the three buffers of a cache disagree on capacity");
+      }
+      if (ts[kv][0]->shape[3] * vpw != D[kv] || ts[kv][1]->shape[3] != D[kv] / gs || ts[kv][2]->shape[3] != D[kv] / gs)
+        return fail(QB200_ERR_BAD_SHAPE, "kv_append_seqs: cache widths do not match the dense rows");
+      if (!same_strides(ts[kv][1], ts[kv][2])) return fail(QB200_ERR_BAD_STRIDE, "kv_append_seqs: scales and biases must have identical strides");
+      if (offsets[n] < 0 || offsets[n] >= ts[kv][0]->shape[2])
+        return fail(QB200_ERR_BAD_SHAPE, "kv_append_seqs: offset %lld outside the capacity %lld of sequence %lld", (long long)offsets[n],
+                    (long long)ts[kv][0]->shape[2], (long long)n);
+      q[kv].push_back((uint32_t*)ts[kv][0]->data + offsets[n] * ts[kv][0]->stride[2]);
+      sc[kv].push_back((uint16_t*)ts[kv][1]->data + offsets[n] * ts[kv][1]->stride[2]);
+      bi[kv].push_back((uint16_t*)ts[kv][2]->data + offsets[n] * ts[kv][2]->stride[2]);
+      qh[kv].push_back(ts[kv][0]->stride[1]);
+      sbh[kv].push_back(ts[kv][1]->stride[1]);
+    }
+  }
+  KvAppendSeqsArgs a;
+  const qb200_tensor* dn[2] = {dense_k, dense_v};
+  for (int kv = 0; kv < 2; ++kv) {
+    a.q[kv] = q[kv].data(); a.s[kv] = sc[kv].data(); a.b[kv] = bi[kv].data();
+    a.q_head[kv] = qh[kv].data(); a.sb_head[kv] = sbh[kv].data();
+    a.dense[kv] = (const uint16_t*)dn[kv]->data; a.dsn[kv] = dn[kv]->stride[0]; a.dsh[kv] = dn[kv]->stride[1]; a.d[kv] = (int)D[kv];
+  }
+  a.n = (int)N; a.heads = (int)Hkv; a.gs = gs; a.bits = nb;
+  const cudaError_t e = launch_kv_append_seqs(a, (cudaStream_t)s);
+  if (e != cudaSuccess) return cuda_fail(e, "kv_append_seqs");
   return QB200_OK;
 }
 

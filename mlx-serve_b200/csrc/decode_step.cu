@@ -1,0 +1,232 @@
+// The small operators of the batched decode step around the quantized projections and the packed-cache attention
+// (forwardBatchedDecode, mlx-serve src/transformer.zig:9562-9924): RMS norm (alone, or after the residual add that
+// precedes it), rotary embedding with one position per sequence, the dense SwiGLU between gate/up and down, and the
+// append of one new token per sequence into per-sequence packed caches.  Each is one launch; rounding points are
+// the reference graph's: every operator output is rounded to the activation dtype.
+#include <cmath>
+#include <cstring>
+
+#include "kernels.h"
+
+namespace qb {
+namespace {
+
+__device__ __forceinline__ float rbf16(float x) { return __uint_as_float((uint32_t)f32_to_bf16_bits(x) << 16); }
+
+// One CTA per row.  sum_out (optional) = a + b rounded to bf16 (mlx_add, src/transformer.zig:9838-9841), and the
+// norm is taken of that sum: y = bf16(w * bf16(x * rsqrt(mean(x^2) + eps))) (mlx_fast_rms_norm).
+__global__ void __launch_bounds__(256) rms_norm_kernel(const uint16_t* a, const uint16_t* b, const uint16_t* w, uint16_t* sum_out,
+                                                       uint16_t* norm_out, int64_t lda, int64_t ldb, int64_t lds, int64_t ldn,
+                                                       int d, float eps) {
+  extern __shared__ float xs[];   // the row in fp32
+  __shared__ float red[8];
+  const int64_t row = blockIdx.x;
+  const uint16_t* ar = a + row * lda;
+  const uint16_t* br = b ? b + row * ldb : nullptr;
+  float acc = 0.f;
+  for (int i = threadIdx.x * 2; i < d; i += blockDim.x * 2) {
+    const uint32_t av = *(const uint32_t*)(ar + i);
+    float x0 = bf16lo(av), x1 = bf16hi(av);
+    if (br) {
+      const uint32_t bv = *(const uint32_t*)(br + i);
+      x0 = rbf16(x0 + bf16lo(bv));
+      x1 = rbf16(x1 + bf16hi(bv));
+      if (sum_out) *(uint32_t*)(sum_out + row * lds + i) = pack_bf16x2(x0, x1);
+    }
+    xs[i] = x0; xs[i + 1] = x1;
+    acc += x0 * x0 + x1 * x1;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
+  const float inv = rsqrtf(tot / (float)d + eps);
+  if (!norm_out) return;
+  for (int i = threadIdx.x * 2; i < d; i += blockDim.x * 2) {
+    const uint32_t wv = *(const uint32_t*)(w + i);
+    const float y0 = bf16lo(wv) * rbf16(xs[i] * inv), y1 = bf16hi(wv) * rbf16(xs[i + 1] * inv);
+    *(uint32_t*)(norm_out + row * ldn + i) = pack_bf16x2(y0, y1);
+  }
+}
+
+// Rotary embedding, non-traditional pairing (i, i + dims/2), one position per sequence (mlx_fast_rope_dynamic).
+// x [n, heads, 1, d] with strides (sn, sh); in place when out == x.  One thread per pair.
+__global__ void __launch_bounds__(256) rope_kernel(const uint16_t* x, uint16_t* out, const int32_t* offsets, int64_t n, int heads,
+                                                   int d, int dims, float log2_base, float scale, int64_t xsn, int64_t xsh,
+                                                   int64_t osn, int64_t osh) {
+  const int half = dims / 2, per_head = d / 2;   // threads per head: the pairs, then the pass-through elements in twos
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n * heads * per_head) return;
+  const int i = (int)(idx % per_head);
+  const int64_t hh = idx / per_head;
+  const int h = (int)(hh % heads);
+  const int64_t s = hh / heads;
+  const uint16_t* xr = x + s * xsn + (int64_t)h * xsh;
+  uint16_t* o = out + s * osn + (int64_t)h * osh;
+  if (i < half) {
+    const float theta = scale * (float)offsets[s] * exp2f(-((float)i / (float)half) * log2_base);
+    float sn, c;
+    sincosf(theta, &sn, &c);
+    const float x1 = bf16_bits_to_f32(xr[i]), x2 = bf16_bits_to_f32(xr[i + half]);
+    o[i] = f32_to_bf16_bits(x1 * c - x2 * sn);
+    o[i + half] = f32_to_bf16_bits(x1 * sn + x2 * c);
+  } else if (out != x || osn != xsn || osh != xsh) {
+    const int e = dims + 2 * (i - half);
+    o[e] = xr[e];
+    o[e + 1] = xr[e + 1];
+  }
+}
+
+// silu(gate) * up with the rounding points of the reference's fused kernel (src/transformer.zig:19842-19851): the
+// sigmoid of the bf16 gate from a table over all bf16 patterns, g * sig rounded, then * up rounded.
+__global__ void __launch_bounds__(256) swiglu_kernel(const uint16_t* gate, const uint16_t* up, uint16_t* out, const uint16_t* sigtab,
+                                                     int64_t rows, int d, int64_t ldg, int64_t ldu, int64_t ldo) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int per_row = d / 2;
+  if (idx >= rows * per_row) return;
+  const int64_t r = idx / per_row;
+  const int i = (int)(idx - r * per_row) * 2;
+  const uint32_t gv = *(const uint32_t*)(gate + r * ldg + i), uv = *(const uint32_t*)(up + r * ldu + i);
+  const float g0 = bf16lo(gv), g1 = bf16hi(gv);
+  const float s0 = bf16_bits_to_f32(sigtab[gv & 0xFFFFu]), s1 = bf16_bits_to_f32(sigtab[gv >> 16]);
+  const float y0 = rbf16(g0 * s0) * bf16lo(uv), y1 = rbf16(g1 * s1) * bf16hi(uv);
+  *(uint32_t*)(out + r * ldo + i) = pack_bf16x2(y0, y1);
+}
+
+// ---- one new token per sequence into per-sequence packed caches (KVCache.updateAffine per slot,
+// src/transformer.zig:9738-9756, :3224-3337): quantise K and V rows and write the triples at each cache's offset ----
+struct AppendSeq {
+  uint32_t* q[2]; uint16_t* s[2]; uint16_t* b[2];   // [K, V]: the token row of head 0
+  int64_t q_head[2], sb_head[2];                    // head strides in elements
+};
+struct AppendTable { AppendSeq s[kMaxSeqPtrs]; };
+struct AppendArgs {
+  const uint16_t* dense[2];       // K, V rows [n, heads, 1, d]
+  int64_t dsn[2], dsh[2];
+  int n, heads, d[2], gs;
+};
+
+template <int BITS>
+__global__ void __launch_bounds__(256) kv_append_seqs_kernel(const __grid_constant__ AppendArgs a, const __grid_constant__ AppendTable tab) {
+  constexpr int VPW = 32 / BITS;
+  // thread -> (which of K / V, sequence, head, packed word); the threads of a group are adjacent lanes
+  const int wpr0 = a.d[0] / VPW, wpr1 = a.d[1] / VPW;
+  const int64_t n0 = (int64_t)a.n * a.heads * wpr0, total = n0 + (int64_t)a.n * a.heads * wpr1;
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = idx < total;
+  if (!live) idx = total - 1;   // keep the warp converged for the shuffles
+  const int kv = idx >= n0 ? 1 : 0;
+  const int64_t li = kv ? idx - n0 : idx;
+  const int wpr = kv ? wpr1 : wpr0;
+  const int wi = (int)(li % wpr);
+  const int64_t rh = li / wpr;
+  const int h = (int)(rh % a.heads);
+  const int s = (int)(rh / a.heads);
+  const uint16_t* xr = a.dense[kv] + (int64_t)s * a.dsn[kv] + (int64_t)h * a.dsh[kv] + wi * VPW;
+  float v[VPW];
+#pragma unroll
+  for (int k = 0; k < VPW; ++k) v[k] = bf16_bits_to_f32(xr[k]);
+  float xmin = v[0], xmax = v[0];
+#pragma unroll
+  for (int k = 1; k < VPW; ++k) { xmin = fminf(xmin, v[k]); xmax = fmaxf(xmax, v[k]); }
+  const int tpg = a.gs / VPW;   // threads per group: a power of two, at most 32
+  for (int off = tpg >> 1; off > 0; off >>= 1) {
+    xmin = fminf(xmin, __shfl_xor_sync(0xffffffffu, xmin, off));
+    xmax = fmaxf(xmax, __shfl_xor_sync(0xffffffffu, xmax, off));
+  }
+  // the affine rule of mlx_quantize as the reference restates it (tests/dsv4_imatrix.py:169-183, codes :264)
+  const float n_bins = (float)((1 << BITS) - 1);
+  const bool mask = fabsf(xmin) > fabsf(xmax);
+  float scale = fmaxf(__fdiv_rn(__fsub_rn(xmax, xmin), n_bins), 1e-7f);
+  scale = mask ? scale : -scale;
+  const float edge = mask ? xmin : xmax;
+  const float q0 = rintf(__fdiv_rn(edge, scale));
+  float bias = 0.0f;
+  if (q0 != 0.0f) { scale = __fdiv_rn(edge, q0); bias = edge; }
+  uint32_t word = 0;
+#pragma unroll
+  for (int k = 0; k < VPW; ++k) {
+    float c = rintf(__fdiv_rn(__fsub_rn(v[k], bias), scale));
+    c = fminf(fmaxf(c, 0.0f), n_bins);
+    word |= ((uint32_t)c) << (k * BITS);
+  }
+  if (!live) return;
+  const AppendSeq& e = tab.s[s];
+  e.q[kv][(int64_t)h * e.q_head[kv] + wi] = word;
+  if ((wi % tpg) == 0) {
+    const int64_t o = (int64_t)h * e.sb_head[kv] + (wi * VPW) / a.gs;
+    e.s[kv][o] = f32_to_bf16_bits(scale);
+    e.b[kv][o] = f32_to_bf16_bits(bias);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_rms_norm(const uint16_t* a, const uint16_t* b, const uint16_t* w, uint16_t* sum_out, uint16_t* norm_out,
+                            int64_t rows, int d, int64_t lda, int64_t ldb, int64_t lds, int64_t ldn, float eps, cudaStream_t st) {
+  if (rows <= 0 || d <= 0) return cudaSuccess;
+  const int threads = d >= 2048 ? 256 : 128;
+  if ((size_t)d * sizeof(float) > 48 * 1024) {   // rows beyond 12288 values: the fp32 copy of a row needs the opt-in shared memory
+    std::lock_guard<std::mutex> lk(setup_mutex());
+    static bool done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !done[dev]) {
+      const cudaError_t e = cudaFuncSetAttribute(rms_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * (int)sizeof(float));
+      if (e != cudaSuccess) return e;
+      if (dev >= 0 && dev < 64) done[dev] = true;
+    }
+  }
+  rms_norm_kernel<<<(unsigned)rows, threads, (size_t)d * sizeof(float), st>>>(a, b, w, sum_out, norm_out, lda, ldb, lds, ldn, d, eps);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rope(const uint16_t* x, uint16_t* out, const int32_t* offsets, int64_t n, int heads, int d, int dims, float base,
+                        float scale, int64_t xsn, int64_t xsh, int64_t osn, int64_t osh, cudaStream_t st) {
+  const int64_t total = n * heads * (d / 2);
+  if (total <= 0) return cudaSuccess;
+  rope_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(x, out, offsets, n, heads, d, dims, log2f(base), scale, xsn, xsh, osn, osh);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_swiglu(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_t rows, int d, int64_t ldg, int64_t ldu,
+                          int64_t ldo, cudaStream_t st) {
+  const int64_t total = rows * (d / 2);
+  if (total <= 0) return cudaSuccess;
+  cudaError_t te;
+  const uint16_t* tab = sigmoid_table(st, &te);
+  if (!tab) return te;
+  swiglu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(gate, up, out, tab, rows, d, ldg, ldu, ldo);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_kv_append_seqs(const KvAppendSeqsArgs& h, cudaStream_t st) {
+  for (int s0 = 0; s0 < h.n; s0 += kMaxSeqPtrs) {
+    const int nb = h.n - s0 < kMaxSeqPtrs ? h.n - s0 : kMaxSeqPtrs;
+    AppendTable tab;
+    std::memset(&tab, 0, sizeof(tab));
+    for (int i = 0; i < nb; ++i)
+      for (int kv = 0; kv < 2; ++kv) {
+        tab.s[i].q[kv] = h.q[kv][s0 + i]; tab.s[i].s[kv] = h.s[kv][s0 + i]; tab.s[i].b[kv] = h.b[kv][s0 + i];
+        tab.s[i].q_head[kv] = h.q_head[kv][s0 + i]; tab.s[i].sb_head[kv] = h.sb_head[kv][s0 + i];
+      }
+    AppendArgs a;
+    for (int kv = 0; kv < 2; ++kv) {
+      a.dense[kv] = h.dense[kv] + (int64_t)s0 * h.dsn[kv];
+      a.dsn[kv] = h.dsn[kv]; a.dsh[kv] = h.dsh[kv]; a.d[kv] = h.d[kv];
+    }
+    a.n = nb; a.heads = h.heads; a.gs = h.gs;
+    const int vpw = 32 / h.bits;
+    const int64_t total = (int64_t)nb * h.heads * (h.d[0] / vpw + h.d[1] / vpw);
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (h.bits == 4) kv_append_seqs_kernel<4><<<blocks, 256, 0, st>>>(a, tab);
+    else kv_append_seqs_kernel<8><<<blocks, 256, 0, st>>>(a, tab);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
+
+}  // namespace qb

@@ -140,6 +140,21 @@ cudaError_t launch_gather_small(const GatherArgs& a, cudaStream_t st);
 bool gather_stream_supported(const GatherArgs& a);   // qmv_stream.cu: persistent streaming kernel, gather form
 cudaError_t launch_gather_stream(const GatherArgs& a, cudaStream_t st);
 
+// ---- decode_step.cu: the small operators of the batched decode step (bf16) ----
+cudaError_t launch_rms_norm(const uint16_t* a, const uint16_t* b, const uint16_t* w, uint16_t* sum_out, uint16_t* norm_out,
+                            int64_t rows, int d, int64_t lda, int64_t ldb, int64_t lds, int64_t ldn, float eps, cudaStream_t st);
+cudaError_t launch_rope(const uint16_t* x, uint16_t* out, const int32_t* offsets, int64_t n, int heads, int d, int dims, float base,
+                        float scale, int64_t xsn, int64_t xsh, int64_t osn, int64_t osh, cudaStream_t st);
+cudaError_t launch_swiglu(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_t rows, int d, int64_t ldg, int64_t ldu,
+                          int64_t ldo, cudaStream_t st);
+struct KvAppendSeqsArgs {     // host side: [K, V] lists over the sequences, token rows already resolved
+  uint32_t* const* q[2]; uint16_t* const* s[2]; uint16_t* const* b[2];
+  const int64_t* q_head[2]; const int64_t* sb_head[2];
+  const uint16_t* dense[2]; int64_t dsn[2], dsh[2];
+  int n, heads, d[2], gs, bits;
+};
+cudaError_t launch_kv_append_seqs(const KvAppendSeqsArgs& a, cudaStream_t st);
+
 // ---- kv_attn.cu ----
 struct KvAttnArgs {
   const void* q; void* out; int q_dtype;

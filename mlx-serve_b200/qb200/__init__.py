@@ -51,6 +51,10 @@ class OptDtype(C.Structure):
     _fields_ = [("value", C.c_int), ("has_value", C.c_bool)]
 
 
+class OptFloat(C.Structure):
+    _fields_ = [("value", C.c_float), ("has_value", C.c_bool)]
+
+
 class Qb200Error(RuntimeError):
     def __init__(self, status: int, msg: str):
         super().__init__(f"qb200 status {status} ({STATUS.get(status, '?')}): {msg}")
@@ -94,6 +98,13 @@ def lib():
         L.qb200_moe_sort_by_expert.argtypes = [TP] * 6 + [C.c_int, C.c_void_p]
         L.qb200_moe_sort_by_expert.restype = C.c_int
         L.qb200_debug_tc_reset.restype = None
+        L.qb200_rms_norm.argtypes = [TP, TP, TP, C.c_float, C.c_void_p]
+        L.qb200_add_rms_norm.argtypes = [TP, TP, TP, TP, TP, C.c_float, C.c_void_p]
+        L.qb200_rope.argtypes = [TP, TP, C.c_int, C.c_bool, OptFloat, C.c_float, TP, TP, C.c_void_p]
+        L.qb200_swiglu.argtypes = [TP, TP, TP, C.c_void_p]
+        L.qb200_kv_append_seqs.argtypes = [C.POINTER(TP)] * 6 + [TP, TP, C.POINTER(C.c_int64), C.c_int, C.c_int, C.c_int, C.c_void_p]
+        for name in ("qb200_rms_norm", "qb200_add_rms_norm", "qb200_rope", "qb200_swiglu", "qb200_kv_append_seqs"):
+            getattr(L, name).restype = C.c_int
         L.qb200_kv_decode_attention_noalloc.argtypes = [TP, TP, TP, TP, TP, TP, TP, TP, C.c_int, C.c_int, C.c_float,
                                                         C.c_char_p, TP, TP, C.c_void_p]
         L.qb200_kv_decode_attention_noalloc.restype = C.c_int
@@ -362,3 +373,58 @@ def moe_sort_by_expert(inds, num_experts, want_offsets=True):
     check(L.qb200_moe_sort_by_expert(C.byref(desc(order)), C.byref(desc(inv)), C.byref(desc(sinds)), C.byref(desc(rows)),
                                      C.byref(desc(offs)), C.byref(desc(inds)), int(num_experts), _stream()))
     return order, inv, sinds, rows, offs
+
+
+def rms_norm(x, weight, eps, out=None):
+    """mlx_fast_rms_norm (src/mlx.zig:319)."""
+    if out is None:
+        out = torch.empty_like(x)
+    check(lib().qb200_rms_norm(C.byref(desc(out)), C.byref(desc(x)), C.byref(desc(weight)), float(eps), _stream()))
+    return out
+
+
+def add_rms_norm(a, b, weight=None, eps=1e-5, sum_out=None, norm_out=None, want_norm=True):
+    """round(a + b) and its RMS norm in one launch (mlx_add + rmsNorm of the decode step).  Returns (sum, norm)."""
+    if sum_out is None:
+        sum_out = torch.empty_like(a)
+    if norm_out is None and want_norm:
+        norm_out = torch.empty_like(a)
+    check(lib().qb200_add_rms_norm(C.byref(desc(sum_out)), C.byref(desc(norm_out)), C.byref(desc(a)), C.byref(desc(b)),
+                                   C.byref(desc(weight if want_norm else None)), float(eps), _stream()))
+    return sum_out, norm_out
+
+
+def rope(x, dims, base, scale, offsets, out=None):
+    """mlx_fast_rope_dynamic, non-traditional (src/mlx.zig:324): x [N, heads, 1, D], offsets int32 [N]; in place when
+    out is x."""
+    if out is None:
+        out = torch.empty_like(x)
+    check(lib().qb200_rope(C.byref(desc(out)), C.byref(desc(x)), int(dims), False, OptFloat(float(base), True), float(scale),
+                           C.byref(desc(offsets)), C.byref(desc(None)), _stream()))
+    return out
+
+
+def swiglu(gate, up, out=None):
+    """fusedSwiGLU of the dense MLP (src/transformer.zig:8220-8243)."""
+    if out is None:
+        out = torch.empty_like(gate)
+    check(lib().qb200_swiglu(C.byref(desc(out)), C.byref(desc(gate)), C.byref(desc(up)), _stream()))
+    return out
+
+
+def kv_append_seqs(k_triples, v_triples, dense_k, dense_v, offsets, bits, group_size):
+    """One new token per sequence into per-sequence packed caches (the per-slot cache update of the batched decode,
+    src/transformer.zig:9738-9756): k_triples[n] / v_triples[n] are the capacity buffers [1, Hkv, cap_n, .]."""
+    n = len(k_triples)
+    TP = C.POINTER(Tensor)
+    keep = []
+
+    def arr(items, packed):
+        ds = [(_packed(t) if packed else desc(t)) for t in items]
+        keep.append(ds)
+        return (TP * n)(*[C.pointer(d) for d in ds])
+    lists = [arr([t[0] for t in k_triples], True), arr([t[1] for t in k_triples], False), arr([t[2] for t in k_triples], False),
+             arr([t[0] for t in v_triples], True), arr([t[1] for t in v_triples], False), arr([t[2] for t in v_triples], False)]
+    offs = (C.c_int64 * n)(*[int(o) for o in offsets])
+    check(lib().qb200_kv_append_seqs(*lists, C.byref(desc(dense_k)), C.byref(desc(dense_v)), offs, n, int(bits), int(group_size),
+                                     _stream()))

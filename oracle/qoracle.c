@@ -32,6 +32,13 @@
  *               stored scale/bias are those values rounded to bf16.
  * Matmul/attention accumulate in fp32 in index order; the weight term is the
  * fp32 value q*s+b (not rounded to bf16).
+ *
+ * The decode step around the kernels (src/transformer.zig:9562-9924) adds two operators whose arithmetic also lives in
+ * MLX (mlx_fast_rms_norm, mlx_fast_rope_dynamic; src/mlx.zig:319-324).  Their restatement here follows MLX's
+ * published definition of the fused operators' fallback graphs and is unpinned against MLX itself:
+ *   rms_norm: y = bf16( w * bf16( x * rsqrt(mean(x^2) + eps) ) ), the mean and the first product in fp32;
+ *   rope (non-traditional): pairs (i, i + dims/2), angle = scale * offset * base^(-2i/dims), rotation in fp32,
+ *             one rounding; elements beyond `dims` pass through.
  */
 #include <math.h>
 #include <stdint.h>
@@ -394,6 +401,48 @@ QO_API void qo_kv_decode_attention(
       const float inv = l > 0.0f ? 1.0f / l : 0.0f;
       for (int64_t e = 0; e < Dv; ++e) o[e] *= inv;
       free(sc);
+    }
+  }
+}
+
+
+/* ---- mlx_fast_rms_norm (src/mlx.zig:319; callers rmsNorm / rmsNormEps, src/transformer.zig:7770-7779) ----
+ * x [rows, d] and w [d] are fp32 carriers of bf16 values when as_bf16; out likewise. */
+QO_API void qo_rms_norm(const float* x, const float* w, int64_t rows, int64_t d, float eps, int as_bf16, float* out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r) {
+    const float* xr = x + r * d;
+    float acc = 0.f;
+    for (int64_t i = 0; i < d; ++i) acc += xr[i] * xr[i];
+    const float inv = 1.0f / sqrtf(acc / (float)d + eps);
+    for (int64_t i = 0; i < d; ++i) {
+      float v = xr[i] * inv;
+      if (as_bf16) v = bf16_to_f32(f32_to_bf16(v));
+      v = w[i] * v;
+      out[r * d + i] = as_bf16 ? bf16_to_f32(f32_to_bf16(v)) : v;
+    }
+  }
+}
+
+/* ---- mlx_fast_rope_dynamic, non-traditional (src/mlx.zig:324; callers src/transformer.zig:9678, :9735) ----
+ * x [n, heads, d] at sequence length 1: row n is rotated by the angle of position offsets[n]. */
+QO_API void qo_rope(const float* x, int64_t n, int64_t heads, int64_t d, int dims, float base, float scale,
+                    const int32_t* offsets, int as_bf16, float* out) {
+  const int half = dims / 2;
+  const float l2 = log2f(base);
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < n * heads; ++r) {
+    const float pos = scale * (float)offsets[r / heads];
+    const float* xr = x + r * d;
+    float* o = out + r * d;
+    for (int64_t i = 0; i < d; ++i) o[i] = xr[i];
+    for (int i = 0; i < half; ++i) {
+      const float theta = pos * exp2f(-((float)i / (float)half) * l2);
+      const float c = cosf(theta), sn = sinf(theta);
+      float a = xr[i] * c - xr[i + half] * sn, b = xr[i] * sn + xr[i + half] * c;
+      if (as_bf16) { a = bf16_to_f32(f32_to_bf16(a)); b = bf16_to_f32(f32_to_bf16(b)); }
+      o[i] = a;
+      o[i + half] = b;
     }
   }
 }

@@ -241,3 +241,23 @@ def kv_decode_attention(q, kq, ks, kb, vq, vs, vb, gs: int, bits: int, scale: fl
         _p(vqs, C.c_int64), _p(vsbs, C.c_int64), C.c_float(scale), _p(lens, C.c_int32), _p(m, C.c_float),
         _p(out, C.c_float))
     return out
+
+
+def rms_norm(x, w, eps: float, as_bf16: bool = True) -> np.ndarray:
+    """mlx_fast_rms_norm restatement: x [..., d], w [d] (fp32 carriers of bf16 values when as_bf16)."""
+    x, w = _c(x, np.float32), _c(w, np.float32)
+    d = x.shape[-1]
+    out = np.empty(x.shape, np.float32)
+    lib().qo_rms_norm(_p(x, C.c_float), _p(w, C.c_float), C.c_int64(x.size // d), C.c_int64(d), C.c_float(eps),
+                      C.c_int(1 if as_bf16 else 0), _p(out, C.c_float))
+    return out
+
+
+def rope(x, dims: int, base: float, scale: float, offsets, as_bf16: bool = True) -> np.ndarray:
+    """mlx_fast_rope_dynamic (non-traditional) at sequence length 1: x [n, heads, d], offsets int32 [n]."""
+    x = _c(x, np.float32)
+    n, heads, d = x.shape
+    out = np.empty(x.shape, np.float32)
+    lib().qo_rope(_p(x, C.c_float), C.c_int64(n), C.c_int64(heads), C.c_int64(d), C.c_int(dims), C.c_float(base),
+                  C.c_float(scale), _p(_c(offsets, np.int32), C.c_int32), C.c_int(1 if as_bf16 else 0), _p(out, C.c_float))
+    return out
