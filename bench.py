@@ -184,7 +184,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the other benchmark configurations (C1, C3, C4, C5, sweep)")
     ap.add_argument("--no-batch", action="store_true", help="seven separate calls per layer instead of four")
-    ap.add_argument("--only", default="", help="comma list of c1,sweep,c3,c4,c5,ep: run just these extra configurations and exit")
+    ap.add_argument("--only", default="", help="comma list of c1,sweep,tick,c3,c4,c5,ep: run just these extra configurations and exit")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -241,7 +241,7 @@ def main():
 
     # ------------------------------------------------------------------ C2 weights and graphs
     layers = []
-    if not only or "sweep" in only or "c1" in only:
+    if not only or "sweep" in only or "c1" in only or "tick" in only:
         for _ in range(L):
             ws = []
             for _, n, k in LLAMA:
@@ -444,6 +444,63 @@ def main():
         res["sharding"] = shard_note
         return res
 
+    def cfg_tick():
+        """A whole decode tick of one Llama-3-8B-shaped layer through the library (forwardBatchedDecode's layer body,
+        src/transformer.zig:9656-9861): norm, q/k/v, rope, cache append, attention over per-sequence 4-bit caches, o,
+        add + norm, gate/up, SwiGLU, down, add -- 13 launches.  8 layers' weights rotate so the weights stream from HBM."""
+        Hd, Hq, Hkv, D, F, NL = 4096, 32, 8, 128, 14336, 8
+        lw = layers[:NL] if len(layers) >= NL else None
+        if lw is None:
+            return {"error": "needs the C2 layer weights"}
+        res = {}
+        wn = (1.0 + 0.1 * torch.randn((Hd,), device=dev, generator=g)).to(torch.bfloat16)
+        for N, T in ((8, 4096), (16, 4096), (32, 1024)):
+            cap = T + 256
+            kt, vt = [], []
+            for n in range(N):      # every sequence owns its cache (one set shared by the 8 layers of the replay)
+                k = torch.randn((1, Hkv, cap, D), device=dev, generator=g).to(torch.bfloat16)
+                kt.append(qb200.quantize(k, 64, 4))
+                k.normal_(generator=g)
+                vt.append(qb200.quantize(k, 64, 4))
+                del k
+            lens = [T - 1 - 7 * n for n in range(N)]
+            kviews = [[t_[:, :, :lens[n] + 1] for t_ in kt[n]] for n in range(N)]
+            vviews = [[t_[:, :, :lens[n] + 1] for t_ in vt[n]] for n in range(N)]
+            offs = torch.tensor(lens, dtype=torch.int32, device=dev)
+            h = torch.randn((N, Hd), device=dev, generator=g).to(torch.bfloat16)
+            qkv = torch.empty((N, (Hq + 2 * Hkv) * D), dtype=torch.bfloat16, device=dev)
+            outs = [qkv[:, :Hq * D], qkv[:, Hq * D:(Hq + Hkv) * D], qkv[:, (Hq + Hkv) * D:]]
+            qk = qkv[:, :(Hq + Hkv) * D].view(N, Hq + Hkv, 1, D)
+            q4, k4, v4 = outs[0].view(N, Hq, 1, D), outs[1].view(N, Hkv, 1, D), outs[2].view(N, Hkv, 1, D)
+            attn = torch.empty((N, Hq, 1, D), dtype=torch.bfloat16, device=dev)
+            ws = torch.empty(int(qb200.lib().qb200_kv_decode_attention_ptrs_workspace_size(N, Hq, Hkv, T, D)), dtype=torch.uint8, device=dev)
+            bufs = {k_: torch.empty((N, n_), dtype=torch.bfloat16, device=dev) for k_, n_ in (("n1", Hd), ("o", Hd), ("h1", Hd), ("ff", Hd), ("g", F), ("u", F), ("act", F), ("d", Hd), ("h2", Hd))}
+
+            def tick():
+                hcur = h
+                for li in range(NL):
+                    wq, wk, wv, wo, wg, wu, wd = lw[li]
+                    qb200.rms_norm(hcur, wn, 1e-5, out=bufs["n1"])
+                    qb200.quantized_matmul_batch(bufs["n1"], [wq, wk, wv], outs, True, GS, BITS)
+                    qb200.rope(qk, D, 500000.0, 1.0, offs, out=qk)
+                    qb200.kv_append_seqs(kt, vt, k4, v4, lens, 4, 64)
+                    qb200.kv_decode_attention_ptrs(q4, kviews, vviews, 4, 64, D ** -0.5, workspace=ws, out=attn)
+                    qb200.quantized_matmul(attn.view(N, Hq * D), *wo, True, GS, BITS, out=bufs["o"])
+                    qb200.add_rms_norm(hcur, bufs["o"], wn, 1e-5, sum_out=bufs["h1"], norm_out=bufs["ff"])
+                    qb200.quantized_matmul_batch(bufs["ff"], [wg, wu], [bufs["g"], bufs["u"]], True, GS, BITS)
+                    qb200.swiglu(bufs["g"], bufs["u"], out=bufs["act"])
+                    qb200.quantized_matmul(bufs["act"], *wd, True, GS, BITS, out=bufs["d"])
+                    qb200.add_rms_norm(bufs["h1"], bufs["d"], want_norm=False, sum_out=bufs["h2"])
+                    hcur = bufs["h2"]
+            gr = capture(tick)
+            ms = time_graph(gr, 20, sync_ranks=False) / 20 / NL
+            kv_bytes = sum(2 * Hkv * (lens[n] + 1) * (D * 4 // 8 + 8) for n in range(N))
+            by = layer_bytes(N) + kv_bytes
+            res[f"N{N}_T{T}"] = {"us_per_layer_tick": ms * 1e3, "launches_per_layer": 13, "tokens_per_s_through_32_layers": N / (32 * ms * 1e-3),
+                                  "bytes_per_layer_tick": by, "GBps": by / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": by / (ms * 1e-3) / 1e9 / hbm_peak}
+            del gr, kt, vt, kviews, vviews
+        return res
+
     def cfg_ep():
         """C3 decode block with the experts sharded over the ranks (all-to-all dispatch and combine through the
         library's own exchange entry); 64 tokens per GPU."""
@@ -454,7 +511,8 @@ def main():
         out = {}
         table = {"c1": ("C1_qmv_1x4096_to_4096", cfg_c1), "sweep": ("C2_sweep", cfg_sweep), "c3": ("C3_routed_experts", cfg_c3),
                  "c4": ("C4_dense_prefill_2048x4096_to_14336", cfg_c4),
-                 "c5": ("C5_decode_attention_batch16", lambda: cfg_c5(16, "16 sequences on one GPU"))}
+                 "c5": ("C5_decode_attention_batch16", lambda: cfg_c5(16, "16 sequences on one GPU")),
+                 "tick": ("decode_layer_tick_llama3_8b", cfg_tick)}
         for nm in names:
             if nm in table and rank == 0:
                 key, fn = table[nm]
@@ -572,7 +630,7 @@ def main():
     e2e_value = world * M * L * R * args.steps / (ms_e2e * 1e-3)
     del gr2, xin2, yout2, sets
 
-    extras = {} if args.no_configs else run_extras(["c1", "sweep", "c3", "c4", "c5"] + (["ep"] if world > 1 else []))
+    extras = {} if args.no_configs else run_extras(["c1", "sweep", "tick", "c3", "c4", "c5"] + (["ep"] if world > 1 else []))
 
     if rank == 0:
         achieved = L * R * layer_bytes(M) / (ms_step * 1e-3) / 1e9

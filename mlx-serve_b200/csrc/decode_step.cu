@@ -179,16 +179,14 @@ cudaError_t launch_rms_norm(const uint16_t* a, const uint16_t* b, const uint16_t
       if (dev >= 0 && dev < 64) done[dev] = true;
     }
   }
-  rms_norm_kernel<<<(unsigned)rows, threads, (size_t)d * sizeof(float), st>>>(a, b, w, sum_out, norm_out, lda, ldb, lds, ldn, d, eps);
-  return cudaGetLastError();
+  return launch_kernel(rms_norm_kernel, dim3((unsigned)rows), dim3(threads), (size_t)d * sizeof(float), st, a, b, w, sum_out, norm_out, lda, ldb, lds, ldn, d, eps);
 }
 
 cudaError_t launch_rope(const uint16_t* x, uint16_t* out, const int32_t* offsets, int64_t n, int heads, int d, int dims, float base,
                         float scale, int64_t xsn, int64_t xsh, int64_t osn, int64_t osh, cudaStream_t st) {
   const int64_t total = n * heads * (d / 2);
   if (total <= 0) return cudaSuccess;
-  rope_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(x, out, offsets, n, heads, d, dims, log2f(base), scale, xsn, xsh, osn, osh);
-  return cudaGetLastError();
+  return launch_kernel(rope_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, x, out, offsets, n, heads, d, dims, log2f(base), scale, xsn, xsh, osn, osh);
 }
 
 cudaError_t launch_swiglu(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_t rows, int d, int64_t ldg, int64_t ldu,
@@ -198,8 +196,7 @@ cudaError_t launch_swiglu(const uint16_t* gate, const uint16_t* up, uint16_t* ou
   cudaError_t te;
   const uint16_t* tab = sigmoid_table(st, &te);
   if (!tab) return te;
-  swiglu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(gate, up, out, tab, rows, d, ldg, ldu, ldo);
-  return cudaGetLastError();
+  return launch_kernel(swiglu_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, gate, up, out, tab, rows, d, ldg, ldu, ldo);
 }
 
 cudaError_t launch_kv_append_seqs(const KvAppendSeqsArgs& h, cudaStream_t st) {
@@ -221,9 +218,8 @@ cudaError_t launch_kv_append_seqs(const KvAppendSeqsArgs& h, cudaStream_t st) {
     const int vpw = 32 / h.bits;
     const int64_t total = (int64_t)nb * h.heads * (h.d[0] / vpw + h.d[1] / vpw);
     const unsigned blocks = (unsigned)((total + 255) / 256);
-    if (h.bits == 4) kv_append_seqs_kernel<4><<<blocks, 256, 0, st>>>(a, tab);
-    else kv_append_seqs_kernel<8><<<blocks, 256, 0, st>>>(a, tab);
-    const cudaError_t e = cudaGetLastError();
+    const cudaError_t e = h.bits == 4 ? launch_kernel(kv_append_seqs_kernel<4>, dim3(blocks), dim3(256), 0, st, a, tab)
+                                      : launch_kernel(kv_append_seqs_kernel<8>, dim3(blocks), dim3(256), 0, st, a, tab);
     if (e != cudaSuccess) return e;
   }
   return cudaSuccess;

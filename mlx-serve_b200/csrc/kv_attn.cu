@@ -280,19 +280,18 @@ cudaError_t launch_kv_attn(const KvAttnArgs& a, cudaStream_t st, const KvSeqTabl
     const int nwarp = 4;
     const size_t smem = (size_t)(p.gqa * a.D + 2 * nwarp * p.gqa + nwarp * p.gqa * a.Dv) * sizeof(float);
     dim3 grid((unsigned)sp.nsplit, (unsigned)a.Hkv, (unsigned)a.B);
+    const dim3 blk(nwarp * 32);
     if (seqs) {
-      if (a.bits == 4) kv_split_generic<4, KvSeqTable><<<grid, nwarp * 32, smem, st>>>(p, *seqs);
-      else kv_split_generic<8, KvSeqTable><<<grid, nwarp * 32, smem, st>>>(p, *seqs);
+      e = a.bits == 4 ? launch_kernel(kv_split_generic<4, KvSeqTable>, grid, blk, smem, st, p, *seqs)
+                      : launch_kernel(kv_split_generic<8, KvSeqTable>, grid, blk, smem, st, p, *seqs);
     } else {
-      if (a.bits == 4) kv_split_generic<4, KvNoTable><<<grid, nwarp * 32, smem, st>>>(p, KvNoTable{});
-      else kv_split_generic<8, KvNoTable><<<grid, nwarp * 32, smem, st>>>(p, KvNoTable{});
+      e = a.bits == 4 ? launch_kernel(kv_split_generic<4, KvNoTable>, grid, blk, smem, st, p, KvNoTable{})
+                      : launch_kernel(kv_split_generic<8, KvNoTable>, grid, blk, smem, st, p, KvNoTable{});
     }
-    e = cudaGetLastError();
   }
   if (e != cudaSuccess) return e;
   dim3 mgrid((unsigned)a.Hq, (unsigned)a.B, 1);
-  kv_merge<<<mgrid, 128, 0, st>>>(p);
-  return cudaGetLastError();
+  return launch_kernel(kv_merge, mgrid, dim3(128), 0, st, p);
 }
 
 }  // namespace qb

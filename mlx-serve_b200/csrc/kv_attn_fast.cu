@@ -546,8 +546,7 @@ cudaError_t launch_fast_inst(const FastK& p, const TAB& tab, dim3 grid, cudaStre
       if (dev >= 0 && dev < 64) done[dev] = true;
     }
   }
-  kv_fast_kernel<BITS, TAB><<<grid, kWarps * 32, smem, st>>>(p, tab);
-  return cudaGetLastError();
+  return launch_kernel(kv_fast_kernel<BITS, TAB>, grid, dim3(kWarps * 32), smem, st, p, tab);
 }
 }  // namespace
 
