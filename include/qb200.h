@@ -243,15 +243,18 @@ QB200_API int qb200_quantize(qb200_tensor* res_q, qb200_tensor* res_scales, qb20
  * decode kernel + merge (src/transformer.zig:5063-5070, :5204-5246) for
  * T_q == 1, and extends them to a batch of sequences with per-sequence
  * lengths, which the reference serves by dequantising, padding and masking
- * (src/transformer.zig:9758-9792, :10216-10249).
- *   q            [B, Hq, 1, D]  bf16 or f32
+ * (src/transformer.zig:9758-9792, :10216-10249).  The verify widths T_q = 2..8 of
+ * qkvAttnVerifyKernel (src/transformer.zig:5464-5588) are served with mask_mode "causal":
+ * query position tq sees the first T - T_q + 1 + tq cache positions (src/transformer.zig:5314-5318);
+ * one launch pair per sequence, workspace sized with T_q in place of B.
+ *   q            [B, Hq, T_q, D]  bf16 or f32
  *   k_q/k_s/k_b  [B, Hkv, T, D*bits/32 | D/gs | D/gs]  strided cache views
  *   v_q/v_s/v_b  [B, Hkv, T, Dv*bits/32 | Dv/gs | Dv/gs]
  *   mask_mode    "" | "causal" (a no-op at T_q == 1) | "array"
  *   mask_arr     additive row broadcastable to [B, 1, 1, T] in q's dtype or f32
  *                ("array" only; empty otherwise)
  *   kv_lens      empty, or int32 [B] on the device: positions >= kv_lens[b] are masked
- *   res          [B, Hq, 1, Dv] in q's dtype
+ *   res          [B, Hq, T_q, Dv] in q's dtype
  *   workspace    device scratch of at least qb200_kv_decode_attention_workspace_size bytes
  */
 QB200_API int qb200_kv_decode_attention(qb200_tensor* res, const qb200_tensor* q, const qb200_tensor* k_q,

@@ -814,7 +814,7 @@ static int parse_kv_mask(KvAttnArgs& a, const qb200_tensor* q, const char* mask_
 }
 
 QB200_API size_t qb200_kv_decode_attention_workspace_size(int64_t B, int64_t Hq, int64_t Hkv, int64_t T, int64_t Dv) {
-  return kv_attn_workspace_bytes(B, Hq, Hkv, T, Dv);
+  return kv_attn_workspace_bytes(B, Hq, Hkv, T, Dv);   // for T_q > 1 pass T_q as the batch
 }
 
 QB200_API int qb200_kv_decode_attention(qb200_tensor* res, const qb200_tensor* q, const qb200_tensor* k_q,
@@ -847,7 +847,10 @@ QB200_API int qb200_kv_decode_attention(qb200_tensor* res, const qb200_tensor* q
   const int vpw = 32 / nb;
   const int64_t Dk = k_q->shape[3] * vpw, Dv = v_q->shape[3] * vpw;
   // Decode width only, as qkvAttnDecodeKernel (mlx-serve src/transformer.zig:5077); wider queries are declined.
-  if (Tq != 1) return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention: T_q=%lld (only decode width 1 is served)", (long long)Tq);
+  // Decode width, or the verify widths 2..8 of qkvAttnVerifyKernel (src/transformer.zig:5464-5588), causal only.
+  if (Tq < 1 || Tq > 8) return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention: T_q=%lld (1..8 are served)", (long long)Tq);
+  if (Tq > 1 && (mask_mode == nullptr || std::strcmp(mask_mode, "causal") != 0 || !is_empty(kv_lens)))
+    return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention: T_q > 1 is served with mask_mode \"causal\" and without kv_lens");
   if (Dk != D) return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: q head dim %lld != K head dim %lld", (long long)D, (long long)Dk);
   if (Hkv <= 0 || Hq % Hkv != 0) return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: Hq %lld not a multiple of Hkv %lld", (long long)Hq, (long long)Hkv);
   if (D % gs != 0 || Dv % gs != 0) return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: head dims must be multiples of group_size");
@@ -862,8 +865,8 @@ QB200_API int qb200_kv_decode_attention(qb200_tensor* res, const qb200_tensor* q
     return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: scales/biases last dim must be D/group_size");
   if (!same_strides(k_scales, k_biases) || !same_strides(v_scales, v_biases))
     return fail(QB200_ERR_BAD_STRIDE, "kv_decode_attention: scales and biases must have identical strides");
-  if (res->shape[0] != B || res->shape[1] != Hq || res->shape[2] != 1 || res->shape[3] != Dv)
-    return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: res must be [B, Hq, 1, Dv]");
+  if (res->shape[0] != B || res->shape[1] != Hq || res->shape[2] != Tq || res->shape[3] != Dv)
+    return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: res must be [B, Hq, T_q, Dv]");
 
   KvAttnArgs a;
   std::memset(&a, 0, sizeof(a));
@@ -887,9 +890,40 @@ QB200_API int qb200_kv_decode_attention(qb200_tensor* res, const qb200_tensor* q
   if (!kv_attn_supported(a))
     return fail(QB200_ERR_UNSUPPORTED, "kv_decode_attention: geometry not served (D=%lld Dv=%lld gs=%d gqa=%lld)",
                 (long long)D, (long long)Dv, gs, (long long)(Hq / Hkv));
-  const size_t need = kv_attn_workspace_bytes(B, Hq, Hkv, T, Dv);
+  const size_t need = kv_attn_workspace_bytes(Tq > 1 ? Tq : B, Hq, Hkv, T, Dv);
   if (need == 0 || workspace == nullptr || workspace_bytes < need)
     return fail(QB200_ERR_WORKSPACE, "kv_decode_attention: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  if (Tq > 1) {
+    // Verify widths: query position tq of sequence b attends to the first T - T_q + 1 + tq cache positions (the
+    // end-aligned causal tail, src/transformer.zig:5314-5318).  Every (b, tq) runs as a sequence of its own over the
+    // same cache view, with that length; the cache is read T_q times, the repeats out of L2.
+    if (T < Tq) return fail(QB200_ERR_BAD_SHAPE, "kv_decode_attention: the cache view must hold at least T_q tokens");
+    const int esz = dtype_size(q->dtype);
+    for (int64_t b = 0; b < B; ++b) {   // one launch per sequence: its T_q query positions as T_q "sequences"
+      KvSeqTable tab;
+      std::memset(&tab, 0, sizeof(tab));
+      for (int64_t tq = 0; tq < Tq; ++tq) {
+        KvSeq& e = tab.s[tq];
+        e.kq = a.kq + b * a.kq_str[0]; e.vq = a.vq + b * a.vq_str[0];
+        e.ks = (const uint16_t*)a.ks + b * a.ksb_str[0]; e.kb = (const uint16_t*)a.kb + b * a.ksb_str[0];
+        e.vs = (const uint16_t*)a.vs + b * a.vsb_str[0]; e.vb = (const uint16_t*)a.vb + b * a.vsb_str[0];
+        for (int d = 0; d < 2; ++d) {
+          e.kq_str[d] = a.kq_str[d + 1]; e.ksb_str[d] = a.ksb_str[d + 1];
+          e.vq_str[d] = a.vq_str[d + 1]; e.vsb_str[d] = a.vsb_str[d + 1];
+        }
+        e.T = T - Tq + 1 + tq;
+      }
+      KvAttnArgs c = a;
+      c.B = Tq;
+      c.q = (const char*)q->data + b * q->stride[0] * esz;
+      c.out = (char*)res->data + b * res->stride[0] * esz;
+      c.q_str[0] = q->stride[2];
+      c.o_str[0] = res->stride[2];
+      const cudaError_t ev = launch_kv_attn(c, (cudaStream_t)s, &tab);
+      if (ev != cudaSuccess) return cuda_fail(ev, "kv_decode_attention");
+    }
+    return QB200_OK;
+  }
   cudaError_t e = launch_kv_attn(a, (cudaStream_t)s);
   if (e != cudaSuccess) return cuda_fail(e, "kv_decode_attention");
   return QB200_OK;

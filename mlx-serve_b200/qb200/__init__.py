@@ -298,16 +298,18 @@ def kv_decode_attention_workspace_size(B, Hq, Hkv, T, Dv) -> int:
 
 def kv_decode_attention(q, k_triple, v_triple, bits, group_size, scale, mask_mode="", mask=None, kv_lens=None,
                         workspace=None, out=None):
-    """Decode attention over packed K/V views; q [B,Hq,1,D] -> [B,Hq,1,Dv] (quantAttention at T_q = 1)."""
+    """Decode attention over packed K/V views; q [B,Hq,T_q,D] -> [B,Hq,T_q,Dv] (quantAttention at T_q = 1; the verify
+    widths T_q = 2..8 with mask_mode "causal")."""
     L = lib()
     kq, ks, kb = k_triple
     vq, vs, vb = v_triple
     B, Hq = q.shape[0], q.shape[1]
     Hkv, T = kq.shape[1], kq.shape[2]
     Dv = vq.shape[3] * 32 // bits
+    Tq = q.shape[2]
     if out is None:
-        out = torch.empty((B, Hq, 1, Dv), dtype=q.dtype, device=q.device)
-    need = kv_decode_attention_workspace_size(B, Hq, Hkv, T, Dv)
+        out = torch.empty((B, Hq, Tq, Dv), dtype=q.dtype, device=q.device)
+    need = kv_decode_attention_workspace_size(Tq if Tq > 1 else B, Hq, Hkv, T, Dv)
     if workspace is None:
         workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
     args = [desc(out), desc(q), _packed(kq), desc(ks), desc(kb), _packed(vq), desc(vs), desc(vb)]

@@ -134,7 +134,11 @@ def test_kv_attention_declines_wide_queries_and_checks_workspace(q):
     fn = q.lib().qb200_kv_decode_attention
     args = lambda r, qq_: [C.byref(r), C.byref(qq_), C.byref(kq), C.byref(ks), C.byref(ks), C.byref(kq), C.byref(ks),
                            C.byref(ks), 4, 64, 0.088, b"", C.byref(e), C.byref(e), None, 0, None]
-    assert fn(*args(res, qq)) == 1  # T_q = 2 declined, like the reference kernel
+    assert fn(*args(res, qq)) == 1  # T_q = 2 without the causal mask mode is declined
+    q9 = _t(q, q.BFLOAT16, [B, Hq, 9, D])
+    a9 = args(_t(q, q.BFLOAT16, [B, Hq, 9, D]), q9)
+    a9[11] = b"causal"
+    assert fn(*a9) == 1              # beyond the verify widths
     q1 = _t(q, q.BFLOAT16, [B, Hq, 1, D])
     r1 = _t(q, q.BFLOAT16, [B, Hq, 1, D])
     assert q.kv_decode_attention_workspace_size(B, Hq, Hkv, T, D) > 0

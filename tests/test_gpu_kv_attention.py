@@ -195,3 +195,26 @@ def test_pointer_form_other_head_dims_and_more_than_32_sequences():
             vtr.append([t[:, :, :lens[b]] for t in dev_triple(*vt)])
         o = qb200.kv_decode_attention_ptrs(torch.from_numpy(q).cuda().view(B, Hq, 1, D), ktr, vtr, bits, 64, D ** -0.5)
         gate_f32(o.cpu().numpy().reshape(B, Hq, D), np.concatenate(refs, 0), f"pointer form D={D} B={B}")
+
+
+@pytest.mark.parametrize("Tq,bits,B,Hq,Hkv,T", [(2, 4, 1, 32, 8, 300), (4, 8, 1, 8, 2, 129), (8, 4, 2, 16, 4, 1000), (3, 4, 1, 12, 2, 64)])
+def test_verify_widths_with_the_causal_tail(Tq, bits, B, Hq, Hkv, T):
+    """qkvAttnVerifyKernel's widths (src/transformer.zig:5464-5588): T_q = 2..8 queries over a cache that already holds
+    them; query position tq sees the first T - T_q + 1 + tq positions (:5314-5318).  Against the oracle row by row."""
+    import qb200
+    rng = np.random.default_rng(Tq * 100 + T)
+    D = 128 if Hq != 12 else 64
+    kt, vt = _cache(rng, B, Hkv, T + 40, D, bits)
+    q = rand_bf16(rng, (B, Hq, Tq, D))
+    dk = [t[:, :, :T] for t in dev_triple(*kt)]
+    dv = [t[:, :, :T] for t in dev_triple(*vt)]
+    out = qb200.kv_decode_attention(torch.from_numpy(q).cuda(), dk, dv, bits, 64, D ** -0.5, mask_mode="causal")
+    assert tuple(out.shape) == (B, Hq, Tq, D)
+    got = out.cpu().numpy()
+    for tq in range(Tq):
+        lens = np.full((B,), T - Tq + 1 + tq, np.int32)
+        ref = qo.kv_decode_attention(np.ascontiguousarray(q[:, :, tq]), *[a[:, :, :T] for a in kt], *[a[:, :, :T] for a in vt],
+                                     64, bits, D ** -0.5, kv_lens=lens)
+        gate_f32(got[:, :, tq], ref, f"verify width {Tq}, position {tq}")
+    with pytest.raises(qb200.Qb200Error):
+        qb200.kv_decode_attention(torch.from_numpy(q).cuda(), dk, dv, bits, 64, D ** -0.5)   # no mask mode: declined
