@@ -343,6 +343,31 @@ QB200_API int qb200_kv_append_seqs(qb200_tensor* const* k_q, qb200_tensor* const
                                    const qb200_tensor* dense_k, const qb200_tensor* dense_v, const int64_t* offsets, int num_seqs,
                                    int bits, int group_size, qb200_stream s);
 
+/* ==== checkpoint -> device loader: MLX-format quantized safetensors (host side; the device layout is the file's) ==== */
+
+/* One opened .safetensors file (memory-mapped).  Quantized linears are stored as <name>.weight (uint32 packed codes),
+ * <name>.scales and <name>.biases, exactly the triples the operators above take. */
+typedef struct qb200_checkpoint qb200_checkpoint;
+QB200_API int qb200_checkpoint_open(qb200_checkpoint** out, const char* path);
+QB200_API void qb200_checkpoint_close(qb200_checkpoint* ck);
+QB200_API int qb200_checkpoint_num_tensors(const qb200_checkpoint* ck);
+QB200_API const char* qb200_checkpoint_tensor_name(const qb200_checkpoint* ck, int i);
+/* Shape and dtype as loaded (desc->data stays NULL; strides are contiguous); *nbytes = bytes to allocate. */
+QB200_API int qb200_checkpoint_tensor_info(const qb200_checkpoint* ck, const char* name, qb200_tensor* desc, size_t* nbytes);
+/* Copies the tensor into caller-allocated device memory, synchronously.  An f16 tensor the narrowing rule covers
+ * arrives as bf16 (f16 -> f32 exactly, then round to nearest even). */
+QB200_API int qb200_checkpoint_load_tensor(const qb200_checkpoint* ck, const char* name, void* device_dst, size_t dst_bytes);
+/* The same bytes into host memory (for hosts that stage their own uploads). */
+QB200_API int qb200_checkpoint_read_tensor(const qb200_checkpoint* ck, const char* name, void* host_dst, size_t cap, size_t* nbytes);
+/* narrowsLoadedF16 (src/model.zig:3030-3061): an f16 tensor named *.scales / *.biases, or any 1-D f16 tensor, is
+ * narrowed to bf16 at load time so that it does not promote bf16 activations. */
+QB200_API bool qb200_narrows_loaded_f16(const char* name, int ndim, int dtype);
+/* affineParamsFromGeometry (src/transformer.zig:16763-16790): bits = w_cols * 32 / in_dim, group = in_dim / s_cols. */
+QB200_API int qb200_affine_params_from_geometry(int64_t w_cols, int64_t s_cols, int64_t in_dim, int* bits, int* group_size);
+/* config.json's top-level "quantization" object (src/model.zig:1480-1505): bits, group_size, mode ("affine" when absent);
+ * QB200_ERR_UNSUPPORTED for a file without one, or for an affine width MLX has no kernels for. */
+QB200_API int qb200_config_quantization(const char* json_text, int* bits, int* group_size, char* mode, size_t mode_cap);
+
 #ifdef __cplusplus
 }
 #endif

@@ -30,13 +30,23 @@ __global__ void __launch_bounds__(kSortWarps * 32) moe_sort_kernel(MoeSortArgs a
   const int64_t per = ((a.n + kSortWarps - 1) / kSortWarps + 31) / 32 * 32;   // slice length, whole 32-entry steps
   const int64_t lo = (int64_t)warp * per, hi = lo + per < a.n ? lo + per : a.n;
   int* mine = cnt + warp * bins;
-  for (int64_t i0 = lo; i0 < hi; i0 += 32) {
-    const int64_t i = i0 + lane;
-    const bool live = i < hi;
-    const int key = live ? load_key(a.inds, a.inds_i64, i, a.E) : -1 - lane;   // dead lanes match nobody
-    const unsigned same = __match_any_sync(0xffffffffu, key);
-    if (live && (same & ((1u << lane) - 1u)) == 0) mine[key] += __popc(same);   // the group's first lane
-    __syncwarp();
+  // (eight 32-entry steps of keys are loaded before any is used: the loop is bound by load latency otherwise)
+  constexpr int kAhead = 8;
+  for (int64_t c0 = lo; c0 < hi; c0 += 32 * kAhead) {
+    int keys[kAhead];
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      const int64_t i = c0 + 32 * u + lane;
+      keys[u] = i < hi ? load_key(a.inds, a.inds_i64, i, a.E) : -1 - lane;   // dead lanes match nobody
+    }
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      if (c0 + 32 * u >= hi) break;
+      const int key = keys[u];
+      const unsigned same = __match_any_sync(0xffffffffu, key);
+      if (key >= 0 && (same & ((1u << lane) - 1u)) == 0) mine[key] += __popc(same);   // the group's first lane
+      __syncwarp();
+    }
   }
   __syncthreads();
   // first position of every (warp, expert): experts in ascending order, inside an expert the warps in order
@@ -72,22 +82,37 @@ __global__ void __launch_bounds__(kSortWarps * 32) moe_sort_kernel(MoeSortArgs a
     for (int w = 0; w < kSortWarps; ++w) cnt[w * bins + e] += base;
   }
   __syncthreads();
-  for (int64_t i0 = lo; i0 < hi; i0 += 32) {
-    const int64_t i = i0 + lane;
-    const bool live = i < hi;
-    const int key = live ? load_key(a.inds, a.inds_i64, i, a.E) : -1 - lane;
-    const unsigned same = __match_any_sync(0xffffffffu, key);
-    const int rank = __popc(same & ((1u << lane) - 1u));
-    int pos = 0;
-    if (live) pos = mine[key] + rank;
-    __syncwarp();
-    if (live && rank == 0) mine[key] += __popc(same);
-    __syncwarp();
-    if (live) {
-      if (a.order) a.order[pos] = (int)i;
-      if (a.inv_order) a.inv_order[i] = pos;
-      if (a.sorted_inds) a.sorted_inds[pos] = a.inds_i64 ? (int)((const long long*)a.inds)[i] : ((const int*)a.inds)[i];
-      if (a.token_rows) a.token_rows[pos] = (int)(i / a.topk);
+  for (int64_t c0 = lo; c0 < hi; c0 += 32 * kAhead) {
+    int keys[kAhead], raw[kAhead];
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      const int64_t i = c0 + 32 * u + lane;
+      raw[u] = 0;
+      keys[u] = -1 - lane;
+      if (i < hi) {
+        raw[u] = a.inds_i64 ? (int)((const long long*)a.inds)[i] : ((const int*)a.inds)[i];
+        keys[u] = load_key(a.inds, a.inds_i64, i, a.E);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      if (c0 + 32 * u >= hi) break;
+      const int64_t i = c0 + 32 * u + lane;
+      const bool live = i < hi;
+      const int key = keys[u];
+      const unsigned same = __match_any_sync(0xffffffffu, key);
+      const int rank = __popc(same & ((1u << lane) - 1u));
+      int pos = 0;
+      if (live) pos = mine[key] + rank;
+      __syncwarp();
+      if (live && rank == 0) mine[key] += __popc(same);
+      __syncwarp();
+      if (live) {
+        if (a.order) a.order[pos] = (int)i;
+        if (a.inv_order) a.inv_order[i] = pos;
+        if (a.sorted_inds) a.sorted_inds[pos] = raw[u];
+        if (a.token_rows) a.token_rows[pos] = (int)(i / a.topk);
+      }
     }
   }
 }

@@ -98,6 +98,22 @@ def lib():
         L.qb200_moe_sort_by_expert.argtypes = [TP] * 6 + [C.c_int, C.c_void_p]
         L.qb200_moe_sort_by_expert.restype = C.c_int
         L.qb200_debug_tc_reset.restype = None
+        L.qb200_checkpoint_open.argtypes = [C.POINTER(C.c_void_p), C.c_char_p]
+        L.qb200_checkpoint_close.argtypes = [C.c_void_p]
+        L.qb200_checkpoint_close.restype = None
+        L.qb200_checkpoint_num_tensors.argtypes = [C.c_void_p]
+        L.qb200_checkpoint_tensor_name.argtypes = [C.c_void_p, C.c_int]
+        L.qb200_checkpoint_tensor_name.restype = C.c_char_p
+        L.qb200_checkpoint_tensor_info.argtypes = [C.c_void_p, C.c_char_p, TP, C.POINTER(C.c_size_t)]
+        L.qb200_checkpoint_load_tensor.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_size_t]
+        L.qb200_checkpoint_read_tensor.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t)]
+        L.qb200_narrows_loaded_f16.argtypes = [C.c_char_p, C.c_int, C.c_int]
+        L.qb200_narrows_loaded_f16.restype = C.c_bool
+        L.qb200_affine_params_from_geometry.argtypes = [C.c_int64, C.c_int64, C.c_int64, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+        L.qb200_config_quantization.argtypes = [C.c_char_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_char_p, C.c_size_t]
+        for name in ("qb200_checkpoint_open", "qb200_checkpoint_num_tensors", "qb200_checkpoint_tensor_info", "qb200_checkpoint_load_tensor",
+                     "qb200_checkpoint_read_tensor", "qb200_affine_params_from_geometry", "qb200_config_quantization"):
+            getattr(L, name).restype = C.c_int
         L.qb200_rms_norm.argtypes = [TP, TP, TP, C.c_float, C.c_void_p]
         L.qb200_add_rms_norm.argtypes = [TP, TP, TP, TP, TP, C.c_float, C.c_void_p]
         L.qb200_rope.argtypes = [TP, TP, C.c_int, C.c_bool, OptFloat, C.c_float, TP, TP, C.c_void_p]
@@ -430,3 +446,56 @@ def kv_append_seqs(k_triples, v_triples, dense_k, dense_v, offsets, bits, group_
     offs = (C.c_int64 * n)(*[int(o) for o in offsets])
     check(lib().qb200_kv_append_seqs(*lists, C.byref(desc(dense_k)), C.byref(desc(dense_v)), offs, n, int(bits), int(group_size),
                                      _stream()))
+
+
+_Q2TORCH = {v: k for k, v in _TORCH2Q.items()}
+_Q2TORCH[UINT32] = torch.int32   # packed codes are carried in int32 tensors
+
+
+class Checkpoint:
+    """One MLX-format .safetensors file: names, shapes, and tensors copied to the device in the layout the operators
+    take (loadWeights' role, src/model.zig; f16 quant scales/biases and 1-D tables arrive as bf16)."""
+
+    def __init__(self, path):
+        self._h = C.c_void_p()
+        check(lib().qb200_checkpoint_open(C.byref(self._h), os.fsencode(path)))
+
+    def close(self):
+        if self._h:
+            lib().qb200_checkpoint_close(self._h)
+            self._h = C.c_void_p()
+
+    def names(self):
+        L = lib()
+        return [L.qb200_checkpoint_tensor_name(self._h, i).decode() for i in range(L.qb200_checkpoint_num_tensors(self._h))]
+
+    def info(self, name):
+        d, n = Tensor(), C.c_size_t()
+        check(lib().qb200_checkpoint_tensor_info(self._h, name.encode(), C.byref(d), C.byref(n)))
+        return d.dtype, [d.shape[i] for i in range(d.ndim)], n.value
+
+    def read(self, name):
+        """Host bytes as they would be uploaded (numpy uint8)."""
+        import numpy as np
+        _, _, n = self.info(name)
+        buf = np.empty(n, np.uint8)
+        check(lib().qb200_checkpoint_read_tensor(self._h, name.encode(), buf.ctypes.data_as(C.c_void_p), n, None))
+        return buf
+
+    def load(self, name, device="cuda"):
+        dt, shape, n = self.info(name)
+        out = torch.empty(shape, dtype=_Q2TORCH[dt], device=device)
+        check(lib().qb200_checkpoint_load_tensor(self._h, name.encode(), C.c_void_p(out.data_ptr()), n))
+        return out
+
+    def load_triple(self, prefix, device="cuda"):
+        """(codes, scales, biases) of the quantized linear `prefix` and its (bits, group_size) from the geometry."""
+        q, s, b = (self.load(f"{prefix}.{k}", device) for k in ("weight", "scales", "biases"))
+        bits, gs = C.c_int(), C.c_int()
+        in_dim = q.shape[-1] * 32 // 4   # a first guess; the geometry is solved against the scale count below
+        for cand in (2, 3, 4, 5, 6, 8):
+            in_dim = q.shape[-1] * 32 // cand
+            if q.shape[-1] * 32 % cand == 0 and in_dim % s.shape[-1] == 0 and in_dim // s.shape[-1] in (32, 64, 128):
+                check(lib().qb200_affine_params_from_geometry(q.shape[-1], s.shape[-1], in_dim, C.byref(bits), C.byref(gs)))
+                break
+        return (q, s, b), bits.value, gs.value
