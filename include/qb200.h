@@ -202,7 +202,9 @@ QB200_API int qb200_moe_route(qb200_tensor* inds, qb200_tensor* norm_scores, con
  *   token_rows   = order / k (:14983-14987), the lhs_indices that stand for the x_rep gather (:14995-15005);
  *   expert_offsets [num_experts + 1]: rows of expert e are [offsets[e], offsets[e+1]) (no counterpart in the
  *                  reference; the expert-parallel exchange cuts the sorted list by it).
- * One launch (a counting sort).  Index values outside [0, num_experts) sort behind every expert; num_experts <= 1024. */
+ * A counting sort: one launch up to 2048 entries, two above (count per slice, then place; the per-slice counts live
+ * in a small array inside the library, so calls that overlap on the GPU from different streams must be serialised).
+ * Index values outside [0, num_experts) sort behind every expert; num_experts <= 1024. */
 QB200_API int qb200_moe_sort_by_expert(qb200_tensor* order, qb200_tensor* inv_order, qb200_tensor* sorted_inds,
                                        qb200_tensor* token_rows, qb200_tensor* expert_offsets, const qb200_tensor* inds,
                                        int num_experts, qb200_stream s);

@@ -488,14 +488,10 @@ class Checkpoint:
         check(lib().qb200_checkpoint_load_tensor(self._h, name.encode(), C.c_void_p(out.data_ptr()), n))
         return out
 
-    def load_triple(self, prefix, device="cuda"):
-        """(codes, scales, biases) of the quantized linear `prefix` and its (bits, group_size) from the geometry."""
+    def load_triple(self, prefix, in_dim, device="cuda"):
+        """(codes, scales, biases) of the quantized linear `prefix` and its (bits, group_size) solved from the geometry
+        and the layer's input width (affineParamsFromGeometry, src/transformer.zig:16763-16790)."""
         q, s, b = (self.load(f"{prefix}.{k}", device) for k in ("weight", "scales", "biases"))
         bits, gs = C.c_int(), C.c_int()
-        in_dim = q.shape[-1] * 32 // 4   # a first guess; the geometry is solved against the scale count below
-        for cand in (2, 3, 4, 5, 6, 8):
-            in_dim = q.shape[-1] * 32 // cand
-            if q.shape[-1] * 32 % cand == 0 and in_dim % s.shape[-1] == 0 and in_dim // s.shape[-1] in (32, 64, 128):
-                check(lib().qb200_affine_params_from_geometry(q.shape[-1], s.shape[-1], in_dim, C.byref(bits), C.byref(gs)))
-                break
+        check(lib().qb200_affine_params_from_geometry(q.shape[-1], s.shape[-1], int(in_dim), C.byref(bits), C.byref(gs)))
         return (q, s, b), bits.value, gs.value

@@ -138,7 +138,7 @@ def test_loaded_triple_feeds_the_operators(tmp_path):
     path, tensors, (q, s, b) = make_checkpoint(tmp_path, rng)
     ck = qb200.Checkpoint(path)
     try:
-        (dq, ds, db), bits, gs = ck.load_triple("model.layers.0.mlp.gate_proj")
+        (dq, ds, db), bits, gs = ck.load_triple("model.layers.0.mlp.gate_proj", 256)
         assert (bits, gs) == (4, 64) and ds.dtype == torch.bfloat16
         x = rand_bf16(rng, (3, 256))
         y = qb200.quantized_matmul(to_dev_bf16(qo.f32_to_bf16(x)), dq, ds, db, True, gs, bits)
