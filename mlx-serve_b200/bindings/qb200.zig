@@ -16,6 +16,7 @@ pub const Tensor = extern struct {
 };
 pub const OptionalInt = extern struct { value: c_int = 0, has_value: bool = false };
 pub const OptionalDtype = extern struct { value: c_int = 0, has_value: bool = false };
+pub const OptionalFloat = extern struct { value: f32 = 0, has_value: bool = false };
 pub const Stream = ?*anyopaque; // cudaStream_t
 
 pub const ErrorHandler = ?*const fn ([*:0]const u8, ?*anyopaque) callconv(.c) void;
@@ -49,6 +50,38 @@ pub extern "c" fn qb200_kv_decode_attention_noalloc(res: *Tensor, q: *const Tens
 pub extern "c" fn qb200_kv_decode_attention_noalloc_max_scratch() usize;
 // replaces steps 2 and 5 of KVCache.updateAffine (src/transformer.zig:3224-3337)
 pub extern "c" fn qb200_kv_append(cache_q: *Tensor, cache_scales: *Tensor, cache_biases: *Tensor, dense: *const Tensor, offset: i64, bits: c_int, group_size: c_int, s: Stream) c_int;
+
+// replaces the argsort chain of moeMLP2 (src/transformer.zig:14961-15006): order, inv_order, sorted_inds, order / k, expert row ranges
+pub extern "c" fn qb200_moe_sort_by_expert(order: ?*Tensor, inv_order: ?*Tensor, sorted_inds: ?*Tensor, token_rows: ?*Tensor, expert_offsets: ?*Tensor, inds: *const Tensor, num_experts: c_int, s: Stream) c_int;
+// replaces the dequantise / pad / concat / mask / SDPA read of forwardBatchedDecode (src/transformer.zig:9742-9792): per-slot cache views in place
+pub extern "c" fn qb200_kv_decode_attention_ptrs(res: *Tensor, q: *const Tensor, k_q: [*]const *const Tensor, k_scales: [*]const *const Tensor, k_biases: [*]const *const Tensor, v_q: [*]const *const Tensor, v_scales: [*]const *const Tensor, v_biases: [*]const *const Tensor, num_seqs: c_int, bits: c_int, group_size: c_int, scale: f32, mask_mode: [*:0]const u8, mask_arr: ?*const Tensor, kv_lens: ?*const Tensor, workspace: ?*anyopaque, workspace_bytes: usize, s: Stream) c_int;
+pub extern "c" fn qb200_kv_decode_attention_ptrs_workspace_size(num_seqs: i64, Hq: i64, Hkv: i64, T_max: i64, Dv: i64) usize;
+// replaces the per-slot cache.update loop of forwardBatchedDecode (src/transformer.zig:9738-9756)
+pub extern "c" fn qb200_kv_append_seqs(k_q: [*]const *Tensor, k_scales: [*]const *Tensor, k_biases: [*]const *Tensor, v_q: [*]const *Tensor, v_scales: [*]const *Tensor, v_biases: [*]const *Tensor, dense_k: *const Tensor, dense_v: *const Tensor, offsets: [*]const i64, num_seqs: c_int, bits: c_int, group_size: c_int, s: Stream) c_int;
+// replace mlx_fast_rms_norm (src/mlx.zig:319), mlx_add + rmsNorm, mlx_fast_rope_dynamic (src/mlx.zig:324), fusedSwiGLU
+pub extern "c" fn qb200_rms_norm(res: *Tensor, x: *const Tensor, weight: *const Tensor, eps: f32, s: Stream) c_int;
+pub extern "c" fn qb200_add_rms_norm(sum_res: ?*Tensor, norm_res: ?*Tensor, a: *const Tensor, b: ?*const Tensor, weight: ?*const Tensor, eps: f32, s: Stream) c_int;
+pub extern "c" fn qb200_rope(res: *Tensor, x: *const Tensor, dims: c_int, traditional: bool, base: OptionalFloat, scale: f32, offsets: *const Tensor, freqs: ?*const Tensor, s: Stream) c_int;
+pub extern "c" fn qb200_swiglu(res: *Tensor, gate: *const Tensor, up: *const Tensor, s: Stream) c_int;
+// checkpoint loader (src/model.zig loadWeights; narrowsLoadedF16 :3030-3061; affineParamsFromGeometry src/transformer.zig:16763-16790)
+pub const Checkpoint = opaque {};
+pub extern "c" fn qb200_checkpoint_open(out: *?*Checkpoint, path: [*:0]const u8) c_int;
+pub extern "c" fn qb200_checkpoint_close(ck: ?*Checkpoint) void;
+pub extern "c" fn qb200_checkpoint_num_tensors(ck: ?*const Checkpoint) c_int;
+pub extern "c" fn qb200_checkpoint_tensor_name(ck: ?*const Checkpoint, i: c_int) ?[*:0]const u8;
+pub extern "c" fn qb200_checkpoint_tensor_info(ck: ?*const Checkpoint, name: [*:0]const u8, desc: *Tensor, nbytes: ?*usize) c_int;
+pub extern "c" fn qb200_checkpoint_load_tensor(ck: ?*const Checkpoint, name: [*:0]const u8, device_dst: ?*anyopaque, dst_bytes: usize) c_int;
+pub extern "c" fn qb200_checkpoint_read_tensor(ck: ?*const Checkpoint, name: [*:0]const u8, host_dst: ?*anyopaque, cap: usize, nbytes: ?*usize) c_int;
+pub extern "c" fn qb200_narrows_loaded_f16(name: [*:0]const u8, ndim: c_int, dtype: c_int) bool;
+pub extern "c" fn qb200_affine_params_from_geometry(w_cols: i64, s_cols: i64, in_dim: i64, bits: *c_int, group_size: *c_int) c_int;
+pub extern "c" fn qb200_config_quantization(json_text: [*:0]const u8, bits: *c_int, group_size: *c_int, mode: ?[*]u8, mode_cap: usize) c_int;
+// status of the bounded waits inside the tensor-core and wide streaming kernels: poll once per step after the stream sync
+pub extern "c" fn qb200_debug_tc_status() c_int;
+pub extern "c" fn qb200_debug_tc_reset() void;
+// expert-parallel routed-expert block (include/qb200_ep.h, libqb200_ep.so: links NCCL)
+pub extern "c" fn qb200_moe_block_ep(res: *Tensor, x: *const Tensor, inds: *const Tensor, scores: *const Tensor, w_gate: *const Tensor, s_gate: *const Tensor, b_gate: *const Tensor, w_up: *const Tensor, s_up: *const Tensor, b_up: *const Tensor, w_down: *const Tensor, s_down: *const Tensor, b_down: *const Tensor, num_experts: c_int, world: c_int, rank: c_int, comm: ?*anyopaque, capacity: i64, group_size: c_int, bits: c_int, overflow: ?*c_int, workspace: ?*anyopaque, workspace_bytes: usize, s: Stream) c_int;
+pub extern "c" fn qb200_moe_block_ep_capacity(T: i64, topk: c_int, world: c_int) i64;
+pub extern "c" fn qb200_moe_block_ep_workspace_size(T: i64, topk: c_int, H: i64, I: i64, num_experts: c_int, world: c_int, capacity: i64) usize;
 
 /// Same convention as mlx.check (src/mlx.zig:547-550): 0 is success.  UNSUPPORTED (1) means
 /// "declined": the caller keeps its existing mlx-c path for that call.

@@ -8,6 +8,9 @@
 //   gatherExpertMm                           src/transformer.zig:20763-20784
 //   gatherExpertGateUpSwiGLU                 src/transformer.zig:15007-15035 with fusedSwiGLU, :19925-19931
 //   KVCacheEntry, KVCache::updateAffine      src/transformer.zig:2777-2858, :3224-3337
+//   moeSortByExpert (argsort chain of moeMLP2) src/transformer.zig:14961-15006
+//   quantAttentionBatched (per-slot caches)  src/transformer.zig:9742-9792, :10165-10249
+//   rmsNorm, addRmsNorm, ropeDynamic, computeGeglu, updateAffineBatched   src/transformer.zig:7770-7779, :9678, :8220-8243, :9738-9756
 //
 // Differences that follow from the eager ABI: arrays are caller-owned device buffers described by `Array`
 // (no refcounted handles), results are allocated by the caller, and every call takes the CUDA stream (as the ABI's `qb200_stream`, a `cudaStream_t`).  A
@@ -19,6 +22,7 @@
 #include <initializer_list>
 #include <stdexcept>
 #include <string>
+#include <vector>
 
 #include "qb200.h"
 
@@ -186,5 +190,68 @@ inline void quantAttention(Array& out, const Array& q, const QuantizedKV& k, con
                                   k.group_size, scale, mask ? "array" : "", mask ? &mask->t : nullptr,
                                   kv_lens ? &kv_lens->t : nullptr, workspace, workspace_bytes, s));
 }
+
+// The sort step of moeMLP2 (src/transformer.zig:14961-15006): order = argsort(flat_inds), inv_order = argsort(order),
+// sorted_inds = flat_inds[order], lhs_idx = order / k, and the row range of every expert.  Any output may be null.
+inline void moeSortByExpert(Array* order, Array* inv_order, Array* sorted_inds, Array* lhs_idx, Array* expert_offsets,
+                            const Array& inds, int num_experts, qb200_stream s) {
+  check(qb200_moe_sort_by_expert(order ? &order->t : nullptr, inv_order ? &inv_order->t : nullptr, sorted_inds ? &sorted_inds->t : nullptr,
+                                 lhs_idx ? &lhs_idx->t : nullptr, expert_offsets ? &expert_offsets->t : nullptr, &inds.t, num_experts, s));
+}
+
+// The KV read of forwardBatchedDecode (src/transformer.zig:9742-9792): every slot owns a B = 1 cache with its own
+// capacity and length.  The reference dequantises, pads to the longest and concatenates; here the packed views are
+// read in place.  `entries[n]` is slot n's cache of this layer (views of its first `offset` tokens are taken here).
+inline size_t quantAttentionBatchedWorkspace(int64_t slots, int64_t Hq, int64_t Hkv, int64_t T_max, int64_t Dv) {
+  return qb200_kv_decode_attention_ptrs_workspace_size(slots, Hq, Hkv, T_max, Dv);
+}
+inline void quantAttentionBatched(Array& out, const Array& q, const KVCacheEntry* const* entries, int slots, float scale,
+                                  void* workspace, size_t workspace_bytes, qb200_stream s) {
+  if (slots < 1 || slots > 4096) throw Error(2, "quantAttentionBatched: 1..4096 slots");
+  std::vector<QuantizedKV> kv(2 * (size_t)slots);
+  std::vector<const qb200_tensor*> p(6 * (size_t)slots);
+  for (int n = 0; n < slots; ++n) {
+    kv[2 * n] = entries[n]->view(entries[n]->keys);
+    kv[2 * n + 1] = entries[n]->view(entries[n]->values);
+    p[0 * slots + n] = &kv[2 * n].q.t; p[1 * slots + n] = &kv[2 * n].scales.t; p[2 * slots + n] = &kv[2 * n].biases.t;
+    p[3 * slots + n] = &kv[2 * n + 1].q.t; p[4 * slots + n] = &kv[2 * n + 1].scales.t; p[5 * slots + n] = &kv[2 * n + 1].biases.t;
+  }
+  check(qb200_kv_decode_attention_ptrs(&out.t, &q.t, &p[0], &p[slots], &p[2 * slots], &p[3 * slots], &p[4 * slots], &p[5 * slots], slots,
+                                       entries[0]->keys.bits, entries[0]->keys.group_size, scale, "", nullptr, nullptr, workspace,
+                                       workspace_bytes, s));
+}
+
+// The per-slot cache update loop of forwardBatchedDecode (src/transformer.zig:9738-9756) as one launch: the new K and V
+// rows [slots, Hkv, 1, D] go to each slot's own cache at its own offset, which then advances.
+inline void updateAffineBatched(KVCacheEntry* const* entries, int slots, const Array& k_new, const Array& v_new, qb200_stream s) {
+  if (slots < 1 || slots > 4096) throw Error(2, "updateAffineBatched: 1..4096 slots");
+  std::vector<qb200_tensor*> p(6 * (size_t)slots);
+  std::vector<int64_t> offs((size_t)slots);
+  for (int n = 0; n < slots; ++n) {
+    KVCacheEntry& e = *entries[n];
+    if (e.offset + 1 > e.capacity()) throw Error(2, "updateAffineBatched: capacity exceeded; grow the cache first");
+    p[0 * slots + n] = &e.keys.q.t; p[1 * slots + n] = &e.keys.scales.t; p[2 * slots + n] = &e.keys.biases.t;
+    p[3 * slots + n] = &e.values.q.t; p[4 * slots + n] = &e.values.scales.t; p[5 * slots + n] = &e.values.biases.t;
+    offs[n] = e.offset;
+  }
+  check(qb200_kv_append_seqs(&p[0], &p[slots], &p[2 * slots], &p[3 * slots], &p[4 * slots], &p[5 * slots], &k_new.t, &v_new.t, offs.data(),
+                             slots, entries[0]->keys.bits, entries[0]->keys.group_size, s));
+  for (int n = 0; n < slots; ++n) entries[n]->offset += 1;
+}
+
+// rmsNorm / rmsNormEps (src/transformer.zig:7770-7779) and the mlx_add that precedes the post-attention and the next
+// layer's input norm (:9836-9843, :9856-9859) fused with it.
+inline void rmsNorm(Array& res, const Array& x, const Array& weight, float eps, qb200_stream s) {
+  check(qb200_rms_norm(&res.t, &x.t, &weight.t, eps, s));
+}
+inline void addRmsNorm(Array& sum, Array* normed, const Array& a, const Array& b, const Array* weight, float eps, qb200_stream s) {
+  check(qb200_add_rms_norm(&sum.t, normed ? &normed->t : nullptr, &a.t, &b.t, weight ? &weight->t : nullptr, eps, s));
+}
+// mlx_fast_rope_dynamic as forwardBatchedDecode calls it (src/transformer.zig:9678, :9735): one position per slot.
+inline void ropeDynamic(Array& res, const Array& x, int dims, float base, float scale, const Array& offsets, qb200_stream s) {
+  check(qb200_rope(&res.t, &x.t, dims, false, qb200_optional_float{base, true}, scale, &offsets.t, nullptr, s));
+}
+// computeGeglu with the silu activation (src/transformer.zig:8220-8243): the reference's bit-exact fused SwiGLU.
+inline void computeGeglu(Array& res, const Array& gate, const Array& up, qb200_stream s) { check(qb200_swiglu(&res.t, &gate.t, &up.t, s)); }
 
 }  // namespace qb200h
