@@ -11,6 +11,8 @@
 //   moeSortByExpert (argsort chain of moeMLP2) src/transformer.zig:14961-15006
 //   quantAttentionBatched (per-slot caches)  src/transformer.zig:9742-9792, :10165-10249
 //   rmsNorm, addRmsNorm, ropeDynamic, computeGeglu, updateAffineBatched   src/transformer.zig:7770-7779, :9678, :8220-8243, :9738-9756
+//   Checkpoint (safetensors triples, f16 narrowing, geometry)   src/model.zig:3030-3061, :3241-3256; src/transformer.zig:16763-16790
+//   moeBlockEp (moeMLP2 over several GPUs; define QB200_HOST_WITH_EP and link libqb200_ep)   src/transformer.zig:14945-15140
 //
 // Differences that follow from the eager ABI: arrays are caller-owned device buffers described by `Array`
 // (no refcounted handles), results are allocated by the caller, and every call takes the CUDA stream (as the ABI's `qb200_stream`, a `cudaStream_t`).  A
@@ -253,5 +255,63 @@ inline void ropeDynamic(Array& res, const Array& x, int dims, float base, float 
 }
 // computeGeglu with the silu activation (src/transformer.zig:8220-8243): the reference's bit-exact fused SwiGLU.
 inline void computeGeglu(Array& res, const Array& gate, const Array& up, qb200_stream s) { check(qb200_swiglu(&res.t, &gate.t, &up.t, s)); }
+
+// One opened .safetensors file.  `loadTriple` is what the reference's loader does per quantized linear
+// (src/model.zig:3241-3256 narrows f16 scales and biases to bf16; src/transformer.zig:16763-16790 solves bits and
+// group size from the packed geometry): the three tensors go to caller-allocated device memory and the QWeight
+// describes them.
+class Checkpoint {
+ public:
+  explicit Checkpoint(const std::string& path) { check(qb200_checkpoint_open(&ck_, path.c_str())); }
+  ~Checkpoint() { qb200_checkpoint_close(ck_); }
+  Checkpoint(const Checkpoint&) = delete;
+  Checkpoint& operator=(const Checkpoint&) = delete;
+  int size() const { return qb200_checkpoint_num_tensors(ck_); }
+  std::string name(int i) const { const char* n = qb200_checkpoint_tensor_name(ck_, i); return n ? n : ""; }
+  // shape and dtype as loaded (data stays null) and the bytes to allocate
+  Array info(const std::string& name, size_t* nbytes) const {
+    Array a;
+    check(qb200_checkpoint_tensor_info(ck_, name.c_str(), &a.t, nbytes));
+    return a;
+  }
+  void load(const std::string& name, void* device_dst, size_t bytes) const {
+    check(qb200_checkpoint_load_tensor(ck_, name.c_str(), device_dst, bytes));
+  }
+  // <prefix>.weight / .scales / .biases into the three buffers (sizes from info()); in_dim is the layer's input width
+  QWeight loadTriple(const std::string& prefix, int64_t in_dim, void* q, void* scales, void* biases) const {
+    QWeight w;
+    size_t nq = 0, ns = 0, nb = 0;
+    w.q = info(prefix + ".weight", &nq);
+    w.scales = info(prefix + ".scales", &ns);
+    w.biases = info(prefix + ".biases", &nb);
+    check(qb200_affine_params_from_geometry(w.q.dim(-1), w.scales.dim(-1), in_dim, &w.bits, &w.group_size));
+    load(prefix + ".weight", q, nq);
+    load(prefix + ".scales", scales, ns);
+    load(prefix + ".biases", biases, nb);
+    w.q.t.data = q;
+    w.scales.t.data = scales;
+    w.biases.t.data = biases;
+    return w;
+  }
+
+ private:
+  qb200_checkpoint* ck_ = nullptr;
+};
+
+#ifdef QB200_HOST_WITH_EP
+}  // namespace qb200h
+#include "qb200_ep.h"
+namespace qb200h {
+// moeMLP2 (src/transformer.zig:14945-15140) with the experts spread over `world` GPUs: this rank's tokens x [T, H]
+// with their routing (inds, scores [T, k]), this rank's slice of the three expert banks, an NCCL communicator made
+// with qb200_ep_comm_create.  `overflow` (device int, may be null) counts routed rows beyond the per-peer capacity.
+inline void moeBlockEp(Array& res, const Array& x, const Array& inds, const Array& scores, const QWeight& gate,
+                       const QWeight& up, const QWeight& down, int num_experts, int world, int rank, void* comm,
+                       int64_t capacity, int* overflow, void* workspace, size_t workspace_bytes, qb200_stream s) {
+  check(qb200_moe_block_ep(&res.t, &x.t, &inds.t, &scores.t, &gate.q.t, &gate.scales.t, &gate.biases.t, &up.q.t,
+                           &up.scales.t, &up.biases.t, &down.q.t, &down.scales.t, &down.biases.t, num_experts, world,
+                           rank, comm, capacity, gate.group_size, gate.bits, overflow, workspace, workspace_bytes, s));
+}
+#endif
 
 }  // namespace qb200h
