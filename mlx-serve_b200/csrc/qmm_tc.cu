@@ -12,7 +12,7 @@
 //
 // Persistent, warp-specialised CTAs (one per SM) walk the output tiles of
 // 256 tokens x BN weight rows (BN chosen per problem so that the last wave of
-// tiles is full), K in steps of 64 through a 3- or 4-stage ring.  Two tile
+// tiles is full), K in steps of 64 through a 3- or 4-stage ring (and a ring of packed codes beside it).  Two tile
 // forms: BN <= 128 with two accumulator sets in tensor memory (the epilogue of
 // tile i overlaps the main loop of tile i+1; used below 257 tokens and by the
 // grouped form), and BN <= 208 with one set (fewer shared-memory operand bytes
@@ -39,6 +39,12 @@
 //                path that the tensor core's operand reads share.
 //   warp 22    : the single-thread tcgen05.mma issuer (M=128, N=BN, K=16 x4 per
 //                stage and accumulator) and its tcgen05.commit arrivals.
+//   warp 23    : the issuer's scout.  The issuing thread is held for as long as its MMAs execute, so
+//                whatever else it executes adds to the k-block time, and a poll of an mbarrier costs it
+//                ~130 cycles even when the phase is already complete (measured: 4 MMAs of N <= 128 per
+//                k-block issue in 256 cycles, with the two polls and the commit in 624).  The scout polls
+//                the two "stage full" barriers of the next k-block while the issuer is busy and the
+//                two meet at a named barrier, which costs the issuer a few cycles.
 // Every mbarrier wait is bounded: on expiry the kernel records an error code,
 // every role leaves its loops, the CTA frees its tensor memory and returns.
 #include <cuda.h>
@@ -51,10 +57,13 @@ namespace qb {
 namespace {
 
 constexpr int BM = 256, BN_MAX = 128, BK = 64;
-// ring depth: the grouped (routed-expert) form gives one stage's room to its row-offset tables
-// (few-token form, at most 128 tokens: stages hold one 128-row box of x, so six of them fit where four did --
-// the k-loop is bound by the round trip of a stage there, not by any unit's throughput)
+// ring depth: the grouped (routed-expert) form gives one stage's room to its row-offset tables; the few-token form
+// (at most 128 tokens) holds one x box per stage, so six of them fit where four did
 __host__ __device__ constexpr int stages_of(bool grouped, bool wide = false, bool half = false) { return half ? 6 : ((grouped || wide) ? 3 : 4); }
+// Buffers of the packed-code ring (each holds 128 bytes of every weight row of the tile: four k-blocks at 4 bits,
+// two at 8).  Two are enough: trading pipeline stages for a ring of five or six buffers was measured and changed
+// nothing at few tokens (the refills are not what the k-loop waits for).
+__host__ __device__ constexpr int raw_bufs_of(bool grouped, bool wide = false, bool half = false) { return 2; }
 // The wide form multiplies one B tile of up to 208 weight rows per stage against both token halves: fewer
 // operand bytes per MAC through shared memory (the resource that bounds this kernel), at the price of a
 // single accumulator set in tensor memory (2 x 256 columns), i.e. an epilogue that is not overlapped.
@@ -66,27 +75,14 @@ constexpr int kDequantWarps = 8 * kDequantGroups, kEpiWarps = 4;
 constexpr int kDequantThreads = 256;                 // threads that fill one stage: two per weight row
 constexpr int kEpiWarp0 = kDequantWarps;            // warps 16..19: warp % 4 = TMEM lane quarter
 constexpr int kTmaWarp = kEpiWarp0 + kEpiWarps, kWTmaWarp = kTmaWarp + 1, kMmaWarp = kWTmaWarp + 1;
-constexpr int kThreads = (kMmaWarp + 1) * 32;
+constexpr int kScoutWarp = kMmaWarp + 1;            // waits on the stage barriers on the issuer's behalf (below)
+constexpr int kThreads = (kScoutWarp + 1) * 32;
 constexpr int A_STAGE_BYTES = BM * BK * 2;   // two 128-row boxes
 constexpr int B_STAGE_BYTES = BN_MAX * BK * 2;
 constexpr int RAW_BYTES = BN_MAX * 128;      // one super-block of packed codes: 128 bytes of every weight row
 constexpr uint32_t kSpinLimit = 1u << 24;
 
-__device__ int g_tc_error = 0;
-
-// Optional cycle accounting of the roles (a build with -DQB_TC_PROFILE; not part of the library build).
-#ifdef QB_TC_PROFILE
-__device__ long long g_tc_prof[256][16];
-#define PROF_DECL long long pt0 = 0, pacc[6] = {0, 0, 0, 0, 0, 0}
-#define PROF_T0() pt0 = clock64()
-#define PROF_ADD(i) do { const long long t_ = clock64(); pacc[i] += t_ - pt0; pt0 = t_; } while (0)
-#define PROF_OUT(base) do { for (int i_ = 0; i_ < 6; ++i_) g_tc_prof[blockIdx.x][(base) + i_] = pacc[i_]; } while (0)
-#else
-#define PROF_DECL
-#define PROF_T0()
-#define PROF_ADD(i)
-#define PROF_OUT(base)
-#endif  // 0 = ok; otherwise the code of the wait that expired
+__device__ int g_tc_error = 0;   // 0 = ok; otherwise the code of the wait that expired
 
 struct TcK {
   const uint32_t* w; const uint16_t* s; const uint16_t* b; uint16_t* y;
@@ -155,6 +151,24 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity
   }
   return false;
 }
+// Wait of the dequant warps: they run several stages ahead of the tensor core, so a poll that fails is followed
+// by a short sleep -- sixteen warps polling in a tight loop take issue slots from the one thread that issues MMAs.
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    __nanosleep(40);
+  }
+  return false;
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                ::"r"(dst), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
@@ -207,6 +221,13 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar, uint32_t issue) {
       "setp.ne.b32 q, %1, 0;\n\t"
       "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
       ::"r"(smem_u32(bar)), "r"(issue) : "memory");
+}
+__device__ __forceinline__ void umma_commit_addr(uint32_t bar_smem, uint32_t issue) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(bar_smem), "r"(issue) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -272,6 +293,89 @@ __device__ __forceinline__ void dequant_half(const uint32_t* codes, uint32_t sb2
   }
 }
 
+// Tile t -> coordinates.  Dense: token block t % tiles_m (fastest, so that CTAs running side by side share
+// a weight tile through L2), weight block t / tiles_m.  Grouped: the expert whose tile range holds t, then
+// the same order inside the expert (s_off: first routed row of every expert, s_tcum: prefix of their tile counts).
+template <bool GROUPED>
+__device__ __forceinline__ TileCoord tile_coords(const TcK& p, int BN, const int* s_off, const int* s_tcum, int tile) {
+  TileCoord c;
+  if constexpr (GROUPED) {
+    int a = 0, b = p.E;   // s_tcum[a] <= tile < s_tcum[b]
+    while (b - a > 1) {
+      const int m = (a + b) >> 1;
+      if (s_tcum[m] <= tile) a = m; else b = m;
+    }
+    const int local = tile - s_tcum[a];
+    const int rows = s_off[a + 1] - s_off[a], tm = (rows + BM - 1) / BM;
+    const int nb = local / tm, mb = local - nb * tm;
+    c.row0 = s_off[a] + mb * BM;
+    c.row_end = s_off[a + 1];
+    c.n0 = nb * BN;
+    c.nend = (c.n0 + BN) < p.N ? (c.n0 + BN) : p.N;
+    c.wrow0 = a * p.N + c.n0;
+    c.wrow_last = a * p.N + p.N - 1;
+  } else {
+    c.row0 = (tile % p.tiles_m) * BM;
+    c.row_end = p.M;
+    c.n0 = (tile / p.tiles_m) * BN;
+    c.nend = (c.n0 + BN) < p.N ? (c.n0 + BN) : p.N;
+    c.wrow0 = c.n0;
+    c.wrow_last = p.N - 1;
+  }
+  return c;
+}
+
+// The MMA issuer's walk over this CTA's tiles and k-blocks, kept out of line: as part of the kernel's one big
+// function its loop was compiled into something three times slower than the same loop on its own (4 MMAs issued in
+// ~700 cycles against ~260).  Every lane of the warp runs it; `lead` marks the lane that issues.
+struct IssuerArgs {
+  uint32_t tmem_base, a_smem, b_smem, empty_smem, acc_full_smem;
+  int tile0, ntiles, tstride, nkb, BN;
+  const int* s_off; const int* s_tcum;
+};
+template <bool GROUPED, bool WIDE, bool HALF>
+__device__ __noinline__ void issuer_walk(const TcK& p, const IssuerArgs a, uint32_t lead) {
+  constexpr int STAGES = stages_of(GROUPED, WIDE, HALF);
+  constexpr int A_STAGE = HALF ? A_STAGE_BYTES / 2 : A_STAGE_BYTES;
+  constexpr int B_STAGE = bn_max_of(WIDE, GROUPED) * BK * 2;
+  constexpr int HALF_COLS = WIDE ? 256 : 128;
+  const uint32_t idesc = make_idesc(a.BN);
+  const uint64_t adesc0 = make_desc(a.a_smem), bdesc0 = make_desc(a.b_smem);
+  int it = 0, ti = 0;
+  for (int tile = a.tile0; tile < a.ntiles; tile += a.tstride, ++ti) {
+    const TileCoord tc = tile_coords<GROUPED>(p, a.BN, a.s_off, a.s_tcum, tile);
+    const bool two_halves = tc.row0 + 128 < tc.row_end;  // the second 128 token rows hold real tokens
+    // dense form: two accumulator sets used alternately; wide form: one set, reused by every tile
+    const int buf = WIDE ? 0 : ti & 1;
+    const uint32_t d0 = a.tmem_base + buf * 256;   // (buf is 0 in the wide form)
+    for (int kb = 0; kb < a.nkb; ++kb, ++it) {
+      const int st = it % STAGES;
+      // the scout has seen both "full" barriers of this stage (and, before a tile's first k-block, that the
+      // epilogue has drained the accumulator set)
+      asm volatile("bar.sync 1, 64;" ::: "memory");
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // descriptors of the stage: the start-address field counts 16-byte units, so a K step of
+      // 16 values (32 bytes) adds 2 and the second 128-row box of x adds 16 KiB / 16
+      const uint64_t ad0 = adesc0 + (uint64_t)(st * (A_STAGE >> 4)), bd0 = bdesc0 + (uint64_t)(st * (B_STAGE >> 4));
+      // A tile without a second token half keeps two partial sums over K, in the columns the second
+      // half would use (odd K steps go there; the epilogue adds them).
+#pragma unroll
+      for (int k16 = 0; k16 < BK / 16; ++k16) {
+        if (two_halves) {
+          const uint32_t accum = (kb > 0 || k16 > 0) ? 1u : 0u;
+          umma(d0, ad0 + 2 * k16, bd0 + 2 * k16, idesc, accum, lead);
+          umma(d0 + HALF_COLS, ad0 + ((128 * BK * 2) >> 4) + 2 * k16, bd0 + 2 * k16, idesc, accum, lead);
+        } else {
+          const uint32_t accum = (kb > 0 || k16 > 1) ? 1u : 0u;
+          umma(d0 + (k16 & 1) * HALF_COLS, ad0 + 2 * k16, bd0 + 2 * k16, idesc, accum, lead);
+        }
+      }
+      umma_commit_addr(a.empty_smem + (uint32_t)st * 8u, lead);  // frees this stage (A and B) once the MMAs above have read it
+    }
+    umma_commit_addr(a.acc_full_smem + (uint32_t)buf * 8u, lead);
+  }
+}
+
 template <int BITS, bool GROUPED, bool WIDE, bool HALF = false>
 __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, TcK p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -284,12 +388,13 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
   constexpr int HALF_COLS = WIDE ? 256 : 128;      // tensor-memory columns between the two token halves
   unsigned char* a_tiles = smem;                                   // [STAGES][2][128 x 64 bf16]
   unsigned char* b_tiles = smem + STAGES * A_STAGE;                // [STAGES][BN x 64 bf16]
-  unsigned char* raw = b_tiles + STAGES * B_STAGE;                 // [2][BN x 128 B of packed codes]
-  uint64_t* bars = (uint64_t*)(raw + 2 * RAW_B);
+  constexpr int RAW_BUFS = raw_bufs_of(GROUPED, WIDE, HALF);
+  unsigned char* raw = b_tiles + STAGES * B_STAGE;                 // [RAW_BUFS][BN x 128 B of packed codes]
+  uint64_t* bars = (uint64_t*)(raw + RAW_BUFS * RAW_B);
   uint64_t* full_a = bars, *full_b = bars + STAGES, *empty = bars + 2 * STAGES;
   uint64_t* acc_full = bars + 3 * STAGES, *acc_empty = bars + 3 * STAGES + 2;
-  uint64_t* raw_full = bars + 3 * STAGES + 4, *raw_empty = bars + 3 * STAGES + 6;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 3 * STAGES + 8);
+  uint64_t* raw_full = bars + 3 * STAGES + 4, *raw_empty = raw_full + RAW_BUFS;
+  uint32_t* tmem_slot = (uint32_t*)(raw_empty + RAW_BUFS);
   volatile int& s_fail = *(volatile int*)(tmem_slot + 1);
   // grouped form: first routed row of every expert and the prefix of their tile counts
   int* s_off = (int*)(tmem_slot + 4);               // [E + 1]
@@ -307,9 +412,9 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
   constexpr int KPS = 128 * 8 / (BK * BITS);  // k-blocks per 128-byte super-block of codes (4 or 2)
 
   if (tid == 0) {
-    for (int i = 0; i < STAGES; ++i) { mbar_init(&full_a[i], 1); mbar_init(&full_b[i], kDequantThreads); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&full_a[i], 1); mbar_init(&full_b[i], kDequantWarps / kDequantGroups); mbar_init(&empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], kEpiWarps * 32); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], kDequantWarps * 32); }
+    for (int i = 0; i < RAW_BUFS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], kDequantWarps); }
     s_fail = (WIDE && (smem_u32(smem) & 1023u) != 0) ? 8 : 0;   // misaligned window: every role leaves at once
     if (s_fail) atomicExch(&g_tc_error, 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -361,33 +466,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
   // Tile t -> coordinates.  Dense: token block t % tiles_m (fastest, so that CTAs running side by side share
   // a weight tile through L2), weight block t / tiles_m.  Grouped: the expert whose tile range holds t, then
   // the same order inside the expert.
-  auto coords = [&](int tile) {
-    TileCoord c;
-    if constexpr (GROUPED) {
-      int a = 0, b = p.E;   // s_tcum[a] <= tile < s_tcum[b]
-      while (b - a > 1) {
-        const int m = (a + b) >> 1;
-        if (s_tcum[m] <= tile) a = m; else b = m;
-      }
-      const int local = tile - s_tcum[a];
-      const int rows = s_off[a + 1] - s_off[a], tm = (rows + BM - 1) / BM;
-      const int nb = local / tm, mb = local - nb * tm;
-      c.row0 = s_off[a] + mb * BM;
-      c.row_end = s_off[a + 1];
-      c.n0 = nb * BN;
-      c.nend = (c.n0 + BN) < p.N ? (c.n0 + BN) : p.N;
-      c.wrow0 = a * p.N + c.n0;
-      c.wrow_last = a * p.N + p.N - 1;
-    } else {
-      c.row0 = (tile % p.tiles_m) * BM;
-      c.row_end = p.M;
-      c.n0 = (tile / p.tiles_m) * BN;
-      c.nend = (c.n0 + BN) < p.N ? (c.n0 + BN) : p.N;
-      c.wrow0 = c.n0;
-      c.wrow_last = p.N - 1;
-    }
-    return c;
-  };
+  auto coords = [&](int tile) { return tile_coords<GROUPED>(p, BN, s_off, s_tcum, tile); };
   if (warp == kTmaWarp) {
     if (lane == 0) {
       // ---------------- TMA producer (one thread) ----------------
@@ -415,8 +494,8 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       for (int tile = tile0; tile < ntiles && !fail && !s_fail; tile += tstride) {
         const int n0 = coords(tile).wrow0;
         for (int sbl = 0; sbl < sb_per_tile; ++sbl, ++sbk) {
-          const int buf = sbk & 1;
-          if (sbk >= 2 && !mbar_wait_relaxed(&raw_empty[buf], ((sbk >> 1) - 1) & 1)) { fail = 7; break; }
+          const int buf = sbk % RAW_BUFS;
+          if (sbk >= RAW_BUFS && !mbar_wait_relaxed(&raw_empty[buf], ((sbk / RAW_BUFS) - 1) & 1)) { fail = 7; break; }
           mbar_expect_tx(&raw_full[buf], (uint32_t)BN * 128u);
           tma_load_2d(smem_u32(raw + buf * RAW_B), &wmap, &raw_full[buf], (kb0 / KPS + sbl) * 32, n0);
         }
@@ -426,55 +505,34 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
   } else if (warp == kMmaWarp) {
     {
       // ---------------- MMA issuer (the whole warp walks the loop, lane 0 issues) ----------------
-      const uint32_t lead = lane == 0 ? 1u : 0u;
-      const uint32_t idesc = make_idesc(BN);
-      const uint64_t adesc0 = make_desc(smem_u32(a_tiles)), bdesc0 = make_desc(smem_u32(b_tiles));
-      int it = 0, fail = 0, ti = 0;
-      PROF_DECL;
-      PROF_T0();
-      for (int tile = tile0; tile < ntiles && !fail && !s_fail; tile += tstride, ++ti) {
-        const TileCoord tc = coords(tile);
-        const bool two_halves = tc.row0 + 128 < tc.row_end;  // the second 128 token rows hold real tokens
-        // dense form: two accumulator sets used alternately; wide form: one set, reused by every tile
-        const int buf = WIDE ? 0 : ti & 1;
-        const int use = WIDE ? ti : ti >> 1;     // how many times this set was used before
-        if (use >= 1 && !mbar_wait_relaxed(&acc_empty[buf], (use - 1) & 1)) { fail = 6; break; }
-        PROF_ADD(0);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t d0 = tmem_base + buf * 256;   // (buf is 0 in the wide form)
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int st = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&full_a[st], ph)) { fail = 1; break; }
-          PROF_ADD(1);
-          if (!mbar_wait(&full_b[st], ph)) { fail = 2; break; }
-          PROF_ADD(2);
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          // descriptors of the stage: the start-address field counts 16-byte units, so a K step of
-          // 16 values (32 bytes) adds 2 and the second 128-row box of x adds 16 KiB / 16
-          const uint64_t ad0 = adesc0 + (uint64_t)(st * (A_STAGE >> 4)), bd0 = bdesc0 + (uint64_t)(st * (B_STAGE >> 4));
-          // A tile without a second token half keeps two partial sums over K, in the columns the second
-          // half would use (odd K steps go there; the epilogue adds them): consecutive MMAs into ONE
-          // accumulator wait ~100 cycles on each other, two independent chains hide that.
-#pragma unroll
-          for (int k16 = 0; k16 < BK / 16; ++k16) {
-            if (two_halves) {
-              const uint32_t accum = (kb > 0 || k16 > 0) ? 1u : 0u;
-              umma(d0, ad0 + 2 * k16, bd0 + 2 * k16, idesc, accum, lead);
-              umma(d0 + HALF_COLS, ad0 + ((128 * BK * 2) >> 4) + 2 * k16, bd0 + 2 * k16, idesc, accum, lead);
-            } else {
-              const uint32_t accum = (kb > 0 || k16 > 1) ? 1u : 0u;
-              umma(d0 + (k16 & 1) * HALF_COLS, ad0 + 2 * k16, bd0 + 2 * k16, idesc, accum, lead);
-            }
-          }
-          umma_commit(&empty[st], lead);  // frees this stage (A and B) once the MMAs above have read it
-          PROF_ADD(3);
-        }
-        if (fail) break;
-        umma_commit(&acc_full[buf], lead);
+      // The issuer waits on nothing but its scout: the two walk the same (tile, k-block) sequence and meet at named
+      // barrier 1 once per k-block, whatever happens.  When a wait of the scout runs out it records the failure and
+      // stops waiting; the issuer then multiplies stale stages into an accumulator nobody trusts (the status word
+      // says so) and every role still reaches the end of the kernel.
+      IssuerArgs ia;
+      ia.tmem_base = tmem_base; ia.a_smem = smem_u32(a_tiles); ia.b_smem = smem_u32(b_tiles);
+      ia.empty_smem = smem_u32(empty); ia.acc_full_smem = smem_u32(acc_full);
+      ia.tile0 = tile0; ia.ntiles = ntiles; ia.tstride = tstride; ia.nkb = nkb; ia.BN = BN;
+      ia.s_off = s_off; ia.s_tcum = s_tcum;
+      issuer_walk<GROUPED, WIDE, HALF>(p, ia, lane == 0 ? 1u : 0u);
+    }
+  } else if (warp == kScoutWarp) {
+    // ---------------- the issuer's scout: the same walk, one meeting per k-block ----------------
+    int it = 0, ti = 0, fail = 0;
+    for (int tile = tile0; tile < ntiles; tile += tstride, ++ti) {
+      const int buf = WIDE ? 0 : ti & 1;
+      const int use = WIDE ? ti : ti >> 1;     // how many times this accumulator set was used before
+      if (!fail && s_fail) fail = 9;           // another role gave up
+      if (!fail && use >= 1 && !mbar_wait_relaxed(&acc_empty[buf], (use - 1) & 1)) fail = 6;
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int st = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!fail && s_fail) fail = 9;
+        if (!fail && !mbar_wait(&full_a[st], ph)) fail = 1;
+        if (!fail && !mbar_wait(&full_b[st], ph)) fail = 2;
+        if (fail && fail != 9 && !s_fail && lane == 0) { s_fail = fail; atomicExch(&g_tc_error, fail); }
+        asm volatile("bar.sync 1, 64;" ::: "memory");
       }
-      if (lane == 0) PROF_OUT(0);
-      if (fail && lane == 0) { s_fail = fail; atomicExch(&g_tc_error, fail); }
     }
   } else if (warp < kDequantWarps) {
     // ---------------- dequant producers: two threads per weight row, two groups ----------------
@@ -495,10 +553,16 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       const int n = tc.wrow0 + r;
       return n < tc.wrow_last ? n : tc.wrow_last;
     };
+    // (the row is looked up once per tile: coords() divides, and searches in the grouped form)
+    int f_row = ntl > 0 ? row_of(0) : 0, c_row = f_row;
     auto prefetch_window = [&]() {
-      if (f_kb >= nkb) { f_kb = 0; ++f_tl; }
+      if (f_kb >= nkb) {
+        f_kb = 0;
+        ++f_tl;
+        if (f_tl < ntl) f_row = row_of(f_tl);
+      }
       if (active && f_tl < ntl) {
-        const int64_t off = (int64_t)row_of(f_tl) * p.lds + ((kb0 + f_kb) >> p.gshift);
+        const int64_t off = (int64_t)f_row * p.lds + ((kb0 + f_kb) >> p.gshift);
         s_nxt = __ldg((const uint4*)(p.s + off));
         b_nxt = __ldg((const uint4*)(p.b + off));
       }
@@ -506,12 +570,17 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
     };
     if (p.sb_vec) prefetch_window();
     bool ok = true;
-    PROF_DECL;
-    PROF_T0();
+    // (tile, k-block) of iteration `it`, stepped without dividing: nkb is even, so a group keeps its k-block parity
+    int tl = 0, kb = grp - kDequantGroups;
     for (int it = grp; it < total_it; it += kDequantGroups) {
       const int st = it % STAGES;
-      const int tl = it / nkb, kb = it - tl * nkb;
-      const int sbk = it / KPS, kbl = it % KPS, buf = sbk & 1;   // nkb is a multiple of KPS
+      kb += kDequantGroups;
+      if (kb >= nkb) {
+        kb -= nkb;
+        ++tl;
+        if (!p.sb_vec) c_row = row_of(tl);
+      }
+      const int sbk = it / KPS, kbl = it % KPS, buf = sbk % RAW_BUFS;   // nkb is a multiple of KPS
       uint32_t sv2, bv2;
       if (p.sb_vec) {
         if ((kb & (WL - 1)) == grp) {   // this group's first k-block of a window
@@ -523,16 +592,15 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
         const uint32_t bw = e < 4 ? (e < 2 ? b_cur.x : b_cur.y) : (e < 6 ? b_cur.z : b_cur.w);
         sv2 = (e & 1) ? __byte_perm(sw, sw, 0x3232) : __byte_perm(sw, sw, 0x1010);
         bv2 = (e & 1) ? __byte_perm(bw, bw, 0x3232) : __byte_perm(bw, bw, 0x1010);
-      } else {
-        const int64_t off = (int64_t)row_of(tl) * p.lds + ((kb0 + kb) >> p.gshift);
+      }
+      else {
+        const int64_t off = (int64_t)c_row * p.lds + ((kb0 + kb) >> p.gshift);
         const uint32_t sv = active ? __ldg(p.s + off) : 0u, bv = active ? __ldg(p.b + off) : 0u;
         sv2 = sv | (sv << 16);
         bv2 = bv | (bv << 16);
       }
-      PROF_ADD(0);
-      ok = mbar_wait(&raw_full[buf], (sbk >> 1) & 1);
+      ok = mbar_wait_backoff(&raw_full[buf], (sbk / RAW_BUFS) & 1);
       if (!ok || s_fail) { ok = false; break; }
-      PROF_ADD(1);
       constexpr int NH = WIDE ? 2 : 1;   // halves of the k-block this thread converts
       uint32_t c[NH][WPH];
       if (active) {
@@ -546,25 +614,26 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
             c[hh][4 * i] = v.x; c[hh][4 * i + 1] = v.y; c[hh][4 * i + 2] = v.z; c[hh][4 * i + 3] = v.w;
           }
       }
-      if (it >= STAGES) ok = mbar_wait(&empty[st], ((it / STAGES) - 1) & 1);
+      if (it >= STAGES) ok = mbar_wait_backoff(&empty[st], ((it / STAGES) - 1) & 1);
       if (!ok || s_fail) { ok = false; break; }
-      PROF_ADD(2);
-      if (active) {
+      if (active)
+      {
 #pragma unroll
         for (int hh = 0; hh < NH; ++hh) dequant_half<BITS>(c[hh], sv2, bv2, b_tiles + st * B_STAGE, r, h + hh);
       }
-      PROF_ADD(3);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> async proxy (UMMA)
-      PROF_ADD(4);
-      mbar_arrive(&full_b[st]);
-      // Release the codes buffer only now that the loaded words have been consumed: the arrival is not
-      // ordered behind a shared-memory load whose result no instruction has waited for yet, and the
-      // TMA refill must not overtake this thread's last read.
-      if (kbl + kDequantGroups >= KPS) mbar_arrive(&raw_empty[buf]);
+      // One arrival per warp: every lane has written its part of the stage and made it visible to the async
+      // proxy above; the warp barrier orders those behind lane 0's arrival.  (256 threads arriving one by one on
+      // the same barrier word kept the stage from completing for several hundred cycles.)
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&full_b[st]);
+        // Release the codes buffer only now that the loaded words have been consumed: the arrival is not
+        // ordered behind a shared-memory load whose result no instruction has waited for yet, and the
+        // TMA refill must not overtake the warp's last read.
+        if (kbl + kDequantGroups >= KPS) mbar_arrive(&raw_empty[buf]);
+      }
     }
-#ifdef QB_TC_PROFILE
-    if (lane == 0 && wg == 0) { PROF_ADD(5); PROF_OUT(grp == 0 ? 4 : 10); }
-#endif
     if (!ok && !s_fail) { s_fail = 4; atomicExch(&g_tc_error, 4); }
   } else {
     // ---------------- epilogue: TMEM -> registers -> bf16 rows of y ----------------
@@ -739,16 +808,20 @@ EncodeFn get_encode() {
   return fn;
 }
 
-constexpr size_t smem_bytes_tc(bool grouped, bool wide, bool half = false) {
+constexpr size_t pipe_bytes_tc(bool grouped, bool wide, bool half = false) {   // stages + code ring
   return (size_t)stages_of(grouped, wide, half) * ((half ? A_STAGE_BYTES / 2 : A_STAGE_BYTES) + bn_max_of(wide, grouped) * BK * 2) +
-         (size_t)2 * bn_max_of(wide, grouped) * 128 + (3 * stages_of(grouped, wide, half) + 8) * 8 + 16 + (grouped ? (size_t)2 * (kMaxGroupExperts + 1) * 4 : 0) +
-         (wide ? 0 : 1024);
+         (size_t)raw_bufs_of(grouped, wide, half) * bn_max_of(wide, grouped) * 128;
+}
+constexpr size_t smem_bytes_tc(bool grouped, bool wide, bool half = false) {
+  return pipe_bytes_tc(grouped, wide, half) + (3 * stages_of(grouped, wide, half) + 4 + 2 * raw_bufs_of(grouped, wide, half)) * 8 + 16 +
+         (grouped ? (size_t)2 * (kMaxGroupExperts + 1) * 4 : 0) + (wide ? 0 : 1024);
 }
 static_assert(smem_bytes_tc(false, true) <= 227 * 1024 && smem_bytes_tc(true, true) <= 227 * 1024, "wide form does not fit in shared memory");
 static_assert(smem_bytes_tc(false, false) <= 227 * 1024 && smem_bytes_tc(true, false) <= 227 * 1024, "shared memory");
 static_assert(smem_bytes_tc(false, false, true) <= 227 * 1024, "few-token form does not fit in shared memory");
 
-constexpr size_t STAGES_DENSE_BYTES = (size_t)stages_of(false) * (A_STAGE_BYTES + B_STAGE_BYTES) + 2 * RAW_BYTES;  // pipeline buffers reused by the exchange
+// pipeline buffers reused by the split-K exchange (either few-token form)
+constexpr size_t STAGES_DENSE_BYTES = pipe_bytes_tc(false, false) < pipe_bytes_tc(false, false, true) ? pipe_bytes_tc(false, false) : pipe_bytes_tc(false, false, true);
 
 
 // Weight rows per tile: the candidate whose tile count fills the last wave best.  Time per tile ~ rows + 40:
@@ -894,7 +967,7 @@ cudaError_t launch_tc(const TcLaunch& a, bool grouped, cudaStream_t st) {
   // the time is the number of k-blocks a CTA walks (plus ~6 k-block times for the exchange), whatever the tile
   // width, so K is cut in 4 or 2 and the tile is made just wide enough for tiles x ranks to fit the SMs.
   p.ksplit = 1;
-  const bool half = !grouped && !wide && a.M <= 128;   // no tile has a second token half: six stages of one x box
+  const bool half = !grouped && !wide && a.M <= 128;   // no tile has a second token half: stages of one x box
   if (!grouped && !wide && a.M <= 256) {
     const int gshift = a.gs == 128 ? 1 : 0;
     const int nkb_all = (int)(a.K / BK);
@@ -994,11 +1067,6 @@ cudaError_t launch_gather_tc(const GatherArgs& a, cudaStream_t st) {
   return launch_tc(l, true, st);
 }
 
-#ifdef QB_TC_PROFILE
-extern "C" __attribute__((visibility("default"))) void qb200_debug_tc_profile(long long* out) {
-  cudaMemcpyFromSymbol(out, g_tc_prof, sizeof(long long) * 256 * 16);
-}
-#endif
 
 void qmm_tc_error_reset() {
   const int zero = 0;

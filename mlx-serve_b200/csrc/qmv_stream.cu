@@ -61,17 +61,6 @@ __host__ __device__ constexpr int kc_for(int nt) { return nt <= 2 ? 4096 : 1024;
 
 constexpr int kMaxMat = 4;          // weight matrices served by one launch (same activations)
 
-// Optional timeline of one launch (a build with -DQB_STREAM_PROFILE; not part of the library build):
-// nanosecond timestamps of thread 0 of every CTA at the phase boundaries
-// (0 start, 5 shared memory carved up, 6 producer set up, 7 first stage issued, 1 ring filled,
-// 2 previous grid complete, 8 activations converted, 3 staged for every CTA of the cluster, 4 end).
-#ifdef QB_STREAM_PROFILE
-__device__ unsigned long long g_stream_tl[512][12];
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define TL(i) do { if (threadIdx.x == 0 && blockIdx.x < 512) g_stream_tl[blockIdx.x][i] = gtime(); } while (0)
-#else
-#define TL(i)
-#endif
 
 struct StreamK {
   const void* x;
@@ -122,8 +111,6 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
   const bool split = !M1 && p.ksplit > 1;
   const int crank = M1 ? 0 : (int)cluster_rank();
   const int ggrp = (split ? (int)blockIdx.x / p.ksplit : (int)blockIdx.x) * kGroups + grp;  // global group id
-  TL(0);
-
   // ---- shared memory carve-up ----
   const int kc = p.kc;
   unsigned char* sp = smem;
@@ -144,8 +131,6 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
   const int k_lo = split ? crank * p.upc * CK : 0;                 // first K value of this CTA's range
   const int k_cta = split ? (p.K - k_lo < p.upc * CK ? (p.K - k_lo > 0 ? p.K - k_lo : 0) : p.upc * CK) : p.K;
   const int ut = k_cta / CK, upk = split ? (ut > 0 ? ut : 1) : kc / CK;
-
-  TL(5);
   // ---- producer: this warp's stream of (pass, local tile, K unit) items ----
   // A lane copies 16 bytes of four rows of a stage (rows lane/8 + 4r) and one scale or bias entry.  The source
   // pointers move by constants from unit to unit and from a tile to the group's next tile; only a change of
@@ -229,20 +214,16 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
   }
 
   setup();
-  TL(6);
 #pragma unroll
   for (int i = 0; i < kStages - 1; ++i) {
     if (prod_valid()) issue();
     cp_async_commit();
-    if (i == 0) TL(7);
   }
 
   // Let the next grid in the stream begin launching, then wait for the previous grid to complete (and
   // its writes to be visible) before reading activations or writing outputs.
-  TL(1);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  TL(2);
   if constexpr (!M1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 
   uint32_t c_off = 0;   // byte offset of the stage the next unit is read from
@@ -403,10 +384,7 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
       };
       if (p.x_f32) stage_all(std::true_type{}); else stage_all(std::false_type{});
     }
-    if (pass == 0) TL(8);
     if constexpr (M1) __syncthreads(); else cluster_sync_all();
-    if (pass == 0) TL(3);
-
     const int upt = (ut - pass * upk) < upk ? (ut - pass * upk) : upk;
     const int ntl_rounds = split ? p.ntl_max : ntl;   // K-split: the same number of rounds in every group and CTA
     for (int tl0 = 0; tl0 < ntl_rounds; tl0 += RT) {
@@ -579,14 +557,8 @@ __global__ void __launch_bounds__(kWarpsPerGroup * groups_for(M1) * 32, M1 ? 2 :
     }
   }
   cp_async_wait<0>();
-  TL(4);
 }
 
-#ifdef QB_STREAM_PROFILE
-extern "C" __attribute__((visibility("default"))) void qb200_debug_stream_timeline(unsigned long long* out) {
-  cudaMemcpyFromSymbol(out, g_stream_tl, sizeof(unsigned long long) * 512 * 12);
-}
-#endif
 
 
 // Grid, K passes and shared-memory footprint of one instantiation; false when it does not fit.
