@@ -18,12 +18,12 @@
 // grouped form), and BN <= 208 with one set (fewer shared-memory operand bytes
 // per MAC -- the resource that bounds this kernel -- at the price of an
 // epilogue that is not overlapped; used for wide prefill).  Roles:
-//   warps 0-15 : dequantisers in two groups of 8 warps that take alternate
-//                k-blocks (a warp's per-k-block latency -- barrier wait, byte
-//                shuffles, proxy fence -- is what bounds this role, so two
-//                k-blocks are always being converted side by side).  Two threads
-//                per weight row: packed codes -> exact bf16 integers (byte
-//                shuffles) -> one bf16 FMA with the group's scale and bias ->
+//   warps 0-15 : dequantisers in groups that take k-blocks in turn (four groups of four warps
+//                for tiles of up to 128 weight rows, two of eight for the wide form): a group's
+//                per-k-block latency -- two barrier polls, scale selection, proxy fence, arrival
+//                -- is several times its arithmetic, so several k-blocks are always being
+//                converted side by side.  One thread per weight row: packed codes -> exact bf16
+//                integers (byte shuffles) -> one bf16 FMA with the group's scale and bias ->
 //                the K-major SWIZZLE_128B operand row.  The packed codes come
 //                from a shared-memory ring that TMA fills (below); scales and
 //                biases are fetched eight k-groups at a time, one window ahead.
@@ -57,9 +57,13 @@ namespace qb {
 namespace {
 
 constexpr int BM = 256, BN_MAX = 128, BK = 64;
-// ring depth: the grouped (routed-expert) form gives one stage's room to its row-offset tables; the few-token form
-// (at most 128 tokens) holds one x box per stage, so six of them fit where four did
-__host__ __device__ constexpr int stages_of(bool grouped, bool wide = false, bool half = false) { return half ? 6 : ((grouped || wide) ? 3 : 4); }
+// ring depth: the grouped (routed-expert) form gives one stage's room to its row-offset tables.  The few-token form
+// (at most 128 tokens, no second token half) puts TWO k-blocks into a stage -- the stage's second x box holds the
+// next 64 columns of K instead of the next 128 tokens, and B has two sub-tiles, one per dequant group: what a
+// k-block costs there is the hand-over of a stage between the roles (~800 cycles with nothing to compute), not any
+// role's work, so it is paid half as often.
+__host__ __device__ constexpr int stages_of(bool grouped, bool wide = false, bool half = false) { return half ? 3 : ((grouped || wide) ? 3 : 4); }
+__host__ __device__ constexpr int kb_per_stage_of(bool half) { return half ? 2 : 1; }
 // Buffers of the packed-code ring (each holds 128 bytes of every weight row of the tile: four k-blocks at 4 bits,
 // two at 8).  Two are enough: trading pipeline stages for a ring of five or six buffers was measured and changed
 // nothing at few tokens (the refills are not what the k-loop waits for).
@@ -70,9 +74,16 @@ __host__ __device__ constexpr int raw_bufs_of(bool grouped, bool wide = false, b
 constexpr int BN_WIDE = 208, BN_WIDE_GROUPED = 192;   // the grouped form keeps 8 KiB for its tables
 __host__ __device__ constexpr int bn_max_of(bool wide, bool grouped = false) { return wide ? (grouped ? BN_WIDE_GROUPED : BN_WIDE) : BN_MAX; }
 constexpr int kMaxGroupExperts = 1024;
-constexpr int kDequantGroups = 2;                   // group g converts the k-blocks with (index % 2) == g
-constexpr int kDequantWarps = 8 * kDequantGroups, kEpiWarps = 4;
-constexpr int kDequantThreads = 256;                 // threads that fill one stage: two per weight row
+// The sixteen dequant warps work in groups; group g converts the k-blocks with (index % groups) == g, one thread per
+// weight row (both halves of the row's 64 codes).  What a group spends per k-block is mostly not arithmetic -- two
+// barrier polls of ~130 cycles each, the scale selection, the proxy fence, the arrival: ~1500 cycles around ~400 of
+// conversion -- and the k-loop of a few-token tile ran at exactly (that sum) / groups.  Tiles of up to 128 weight
+// rows therefore use four groups of four warps; the wide form needs eight warps to cover its 208 rows.  A group must
+// not step further than the stage ring holds (groups <= stages x k-blocks per stage): its wait on a stage's "empty"
+// barrier names a phase by parity, and a group that is two completions ahead of the barrier reads the previous
+// round's completion as its own.  The grouped form has three one-k-block stages and so keeps two groups.
+__host__ __device__ constexpr int dq_groups_of(bool wide, bool grouped) { return (wide || grouped) ? 2 : 4; }
+constexpr int kDequantWarps = 16, kEpiWarps = 4;
 constexpr int kEpiWarp0 = kDequantWarps;            // warps 16..19: warp % 4 = TMEM lane quarter
 constexpr int kTmaWarp = kEpiWarp0 + kEpiWarps, kWTmaWarp = kTmaWarp + 1, kMmaWarp = kWTmaWarp + 1;
 constexpr int kScoutWarp = kMmaWarp + 1;            // waits on the stage barriers on the issuer's behalf (below)
@@ -336,8 +347,9 @@ struct IssuerArgs {
 template <bool GROUPED, bool WIDE, bool HALF>
 __device__ __noinline__ void issuer_walk(const TcK& p, const IssuerArgs a, uint32_t lead) {
   constexpr int STAGES = stages_of(GROUPED, WIDE, HALF);
-  constexpr int A_STAGE = HALF ? A_STAGE_BYTES / 2 : A_STAGE_BYTES;
-  constexpr int B_STAGE = bn_max_of(WIDE, GROUPED) * BK * 2;
+  constexpr int KPST = kb_per_stage_of(HALF);          // k-blocks per stage
+  constexpr int A_STAGE = A_STAGE_BYTES;               // two x boxes: two token halves, or (few-token form) two k-blocks
+  constexpr int B_SUB = bn_max_of(WIDE, GROUPED) * BK * 2, B_STAGE = KPST * B_SUB;
   constexpr int HALF_COLS = WIDE ? 256 : 128;
   const uint32_t idesc = make_idesc(a.BN);
   const uint64_t adesc0 = make_desc(a.a_smem), bdesc0 = make_desc(a.b_smem);
@@ -348,26 +360,30 @@ __device__ __noinline__ void issuer_walk(const TcK& p, const IssuerArgs a, uint3
     // dense form: two accumulator sets used alternately; wide form: one set, reused by every tile
     const int buf = WIDE ? 0 : ti & 1;
     const uint32_t d0 = a.tmem_base + buf * 256;   // (buf is 0 in the wide form)
-    for (int kb = 0; kb < a.nkb; ++kb, ++it) {
+    for (int kb = 0; kb < a.nkb; kb += KPST, ++it) {   // `it` counts stages
       const int st = it % STAGES;
       // the scout has seen both "full" barriers of this stage (and, before a tile's first k-block, that the
       // epilogue has drained the accumulator set)
       asm volatile("bar.sync 1, 64;" ::: "memory");
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // descriptors of the stage: the start-address field counts 16-byte units, so a K step of
-      // 16 values (32 bytes) adds 2 and the second 128-row box of x adds 16 KiB / 16
+      // 16 values (32 bytes) adds 2 and the stage's second x box adds 16 KiB / 16
       const uint64_t ad0 = adesc0 + (uint64_t)(st * (A_STAGE >> 4)), bd0 = bdesc0 + (uint64_t)(st * (B_STAGE >> 4));
       // A tile without a second token half keeps two partial sums over K, in the columns the second
       // half would use (odd K steps go there; the epilogue adds them).
 #pragma unroll
-      for (int k16 = 0; k16 < BK / 16; ++k16) {
-        if (two_halves) {
-          const uint32_t accum = (kb > 0 || k16 > 0) ? 1u : 0u;
-          umma(d0, ad0 + 2 * k16, bd0 + 2 * k16, idesc, accum, lead);
-          umma(d0 + HALF_COLS, ad0 + ((128 * BK * 2) >> 4) + 2 * k16, bd0 + 2 * k16, idesc, accum, lead);
-        } else {
-          const uint32_t accum = (kb > 0 || k16 > 1) ? 1u : 0u;
-          umma(d0 + (k16 & 1) * HALF_COLS, ad0 + 2 * k16, bd0 + 2 * k16, idesc, accum, lead);
+      for (int sub = 0; sub < KPST; ++sub) {
+#pragma unroll
+        for (int k16 = 0; k16 < BK / 16; ++k16) {
+          if (!HALF && two_halves) {
+            const uint32_t accum = (kb > 0 || k16 > 0) ? 1u : 0u;
+            umma(d0, ad0 + 2 * k16, bd0 + 2 * k16, idesc, accum, lead);
+            umma(d0 + HALF_COLS, ad0 + ((128 * BK * 2) >> 4) + 2 * k16, bd0 + 2 * k16, idesc, accum, lead);
+          } else {
+            const uint32_t accum = (kb > 0 || sub > 0 || k16 > 1) ? 1u : 0u;
+            umma(d0 + (k16 & 1) * HALF_COLS, ad0 + sub * ((128 * BK * 2) >> 4) + 2 * k16, bd0 + sub * (B_SUB >> 4) + 2 * k16, idesc,
+                 accum, lead);
+          }
         }
       }
       umma_commit_addr(a.empty_smem + (uint32_t)st * 8u, lead);  // frees this stage (A and B) once the MMAs above have read it
@@ -383,8 +399,11 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
   // static shared memory, so its dynamic window starts aligned; that is verified below.
   unsigned char* smem = WIDE ? smem_raw : (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int STAGES = stages_of(GROUPED, WIDE, HALF);
-  constexpr int A_STAGE = HALF ? A_STAGE_BYTES / 2 : A_STAGE_BYTES;   // HALF: no tile has a second token half
-  constexpr int B_STAGE = bn_max_of(WIDE, GROUPED) * BK * 2, RAW_B = bn_max_of(WIDE, GROUPED) * 128;
+  constexpr int KPST = kb_per_stage_of(HALF);          // k-blocks per stage (2 in the few-token form)
+  constexpr int DQG = dq_groups_of(WIDE, GROUPED);     // dequant groups, kDequantWarps / DQG warps each
+  static_assert(DQG <= STAGES * KPST, "a dequant group would run more than one ring round ahead of its barrier");
+  constexpr int A_STAGE = A_STAGE_BYTES;               // two x boxes: two token halves, or (few-token form) two k-blocks
+  constexpr int B_SUB = bn_max_of(WIDE, GROUPED) * BK * 2, B_STAGE = KPST * B_SUB, RAW_B = bn_max_of(WIDE, GROUPED) * 128;
   constexpr int HALF_COLS = WIDE ? 256 : 128;      // tensor-memory columns between the two token halves
   unsigned char* a_tiles = smem;                                   // [STAGES][2][128 x 64 bf16]
   unsigned char* b_tiles = smem + STAGES * A_STAGE;                // [STAGES][BN x 64 bf16]
@@ -412,11 +431,11 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
   constexpr int KPS = 128 * 8 / (BK * BITS);  // k-blocks per 128-byte super-block of codes (4 or 2)
 
   if (tid == 0) {
-    for (int i = 0; i < STAGES; ++i) { mbar_init(&full_a[i], 1); mbar_init(&full_b[i], kDequantWarps / kDequantGroups); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&full_a[i], 1); mbar_init(&full_b[i], KPST * kDequantWarps / DQG); mbar_init(&empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], kEpiWarps * 32); }
-    for (int i = 0; i < RAW_BUFS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], kDequantWarps); }
+    for (int i = 0; i < RAW_BUFS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], (kDequantWarps / DQG) * (DQG < KPS ? DQG : KPS)); }
     s_fail = (WIDE && (smem_u32(smem) & 1023u) != 0) ? 8 : 0;   // misaligned window: every role leaves at once
-    if (s_fail) atomicExch(&g_tc_error, 8);
+    if (s_fail) atomicCAS(&g_tc_error, 0, 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kMmaWarp) {  // tensor memory: 512 columns = two sets of two 128x128 fp32 accumulators
@@ -475,16 +494,22 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
         const TileCoord tc = coords(tile);
         const int m0 = tc.row0;
         const bool two = m0 + 128 < tc.row_end;   // the second 128-row box holds real tokens (else it is not multiplied)
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        for (int kb = 0; kb < nkb; kb += KPST, ++it) {   // `it` counts stages
           const int st = it % STAGES;
           if (it >= STAGES && !mbar_wait_relaxed(&empty[st], ((it / STAGES) - 1) & 1)) { fail = 3; break; }
-          mbar_expect_tx(&full_a[st], two ? A_STAGE_BYTES : A_STAGE_BYTES / 2);
           const uint32_t dst = smem_u32(a_tiles + st * A_STAGE);
-          tma_load_2d(dst, &xmap, &full_a[st], (kb0 + kb) * BK, m0);
-          if (two) tma_load_2d(dst + 128 * BK * 2, &xmap, &full_a[st], (kb0 + kb) * BK, m0 + 128);
+          if constexpr (HALF) {   // the second box is the next k-block of the same 128 tokens
+            mbar_expect_tx(&full_a[st], A_STAGE_BYTES);
+            tma_load_2d(dst, &xmap, &full_a[st], (kb0 + kb) * BK, m0);
+            tma_load_2d(dst + 128 * BK * 2, &xmap, &full_a[st], (kb0 + kb + 1) * BK, m0);
+          } else {
+            mbar_expect_tx(&full_a[st], two ? A_STAGE_BYTES : A_STAGE_BYTES / 2);
+            tma_load_2d(dst, &xmap, &full_a[st], (kb0 + kb) * BK, m0);
+            if (two) tma_load_2d(dst + 128 * BK * 2, &xmap, &full_a[st], (kb0 + kb) * BK, m0 + 128);
+          }
         }
       }
-      if (fail) { s_fail = fail; atomicExch(&g_tc_error, fail); }
+      if (fail) { s_fail = fail; atomicCAS(&g_tc_error, 0, fail); }
     }
   } else if (warp == kWTmaWarp) {
     if (lane == 0) {
@@ -500,7 +525,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
           tma_load_2d(smem_u32(raw + buf * RAW_B), &wmap, &raw_full[buf], (kb0 / KPS + sbl) * 32, n0);
         }
       }
-      if (fail) { s_fail = fail; atomicExch(&g_tc_error, fail); }
+      if (fail) { s_fail = fail; atomicCAS(&g_tc_error, 0, fail); }
     }
   } else if (warp == kMmaWarp) {
     {
@@ -524,21 +549,23 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       const int use = WIDE ? ti : ti >> 1;     // how many times this accumulator set was used before
       if (!fail && s_fail) fail = 9;           // another role gave up
       if (!fail && use >= 1 && !mbar_wait_relaxed(&acc_empty[buf], (use - 1) & 1)) fail = 6;
-      for (int kb = 0; kb < nkb; ++kb, ++it) {
+      for (int kb = 0; kb < nkb; kb += KPST, ++it) {   // `it` counts stages
         const int st = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
         if (!fail && s_fail) fail = 9;
         if (!fail && !mbar_wait(&full_a[st], ph)) fail = 1;
         if (!fail && !mbar_wait(&full_b[st], ph)) fail = 2;
-        if (fail && fail != 9 && !s_fail && lane == 0) { s_fail = fail; atomicExch(&g_tc_error, fail); }
+        if (fail && fail != 9 && !s_fail && lane == 0) { s_fail = fail; atomicCAS(&g_tc_error, 0, fail); }
         asm volatile("bar.sync 1, 64;" ::: "memory");
       }
     }
   } else if (warp < kDequantWarps) {
-    // ---------------- dequant producers: two threads per weight row, two groups ----------------
-    const int grp = warp >> 3, wg = warp & 7;
-    // dense form: two threads per weight row (h = half of the 64-wide k-block); wide form: one thread per row
-    const int r = WIDE ? wg * 32 + lane : (wg & 3) * 32 + lane, h = WIDE ? 0 : wg >> 2;
+    // ---------------- dequant producers: DQG groups, one thread per weight row ----------------
+    constexpr int WPG = kDequantWarps / DQG;   // warps per group
+    constexpr int TPR = (WPG * 32) / bn_max_of(WIDE, GROUPED);   // threads per weight row: 1, or 2 (a half of the k-block each)
+    static_assert(TPR == 1 || TPR == 2, "dequant thread layout");
+    const int grp = warp / WPG, wg = warp % WPG;
+    const int r = (wg % (WPG / TPR)) * 32 + lane, h = wg / (WPG / TPR);
     const bool active = r < BN;
     const int ntl = ntiles > tile0 ? (ntiles - tile0 + tstride - 1) / tstride : 0;  // tiles of this CTA
     const int total_it = ntl * nkb;
@@ -570,11 +597,11 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
     };
     if (p.sb_vec) prefetch_window();
     bool ok = true;
-    // (tile, k-block) of iteration `it`, stepped without dividing: nkb is even, so a group keeps its k-block parity
-    int tl = 0, kb = grp - kDequantGroups;
-    for (int it = grp; it < total_it; it += kDequantGroups) {
-      const int st = it % STAGES;
-      kb += kDequantGroups;
+    // (tile, k-block) of iteration `it`, stepped without dividing (nkb is a multiple of four)
+    int tl = 0, kb = grp - DQG;
+    for (int it = grp; it < total_it; it += DQG) {   // `it` counts k-blocks
+      const int sit = it / KPST, st = sit % STAGES;   // stage iteration and stage (few-token form: group g fills sub-tile g)
+      kb += DQG;
       if (kb >= nkb) {
         kb -= nkb;
         ++tl;
@@ -601,7 +628,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       }
       ok = mbar_wait_backoff(&raw_full[buf], (sbk / RAW_BUFS) & 1);
       if (!ok || s_fail) { ok = false; break; }
-      constexpr int NH = WIDE ? 2 : 1;   // halves of the k-block this thread converts
+      constexpr int NH = 2 / TPR;   // halves of the k-block this thread converts
       uint32_t c[NH][WPH];
       if (active) {
         const unsigned char* rrow = raw + buf * RAW_B + r * 128;
@@ -614,12 +641,12 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
             c[hh][4 * i] = v.x; c[hh][4 * i + 1] = v.y; c[hh][4 * i + 2] = v.z; c[hh][4 * i + 3] = v.w;
           }
       }
-      if (it >= STAGES) ok = mbar_wait_backoff(&empty[st], ((it / STAGES) - 1) & 1);
+      if (sit >= STAGES) ok = mbar_wait_backoff(&empty[st], ((sit / STAGES) - 1) & 1);
       if (!ok || s_fail) { ok = false; break; }
       if (active)
       {
 #pragma unroll
-        for (int hh = 0; hh < NH; ++hh) dequant_half<BITS>(c[hh], sv2, bv2, b_tiles + st * B_STAGE, r, h + hh);
+        for (int hh = 0; hh < NH; ++hh) dequant_half<BITS>(c[hh], sv2, bv2, b_tiles + st * B_STAGE + (it % KPST) * B_SUB, r, h + hh);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> async proxy (UMMA)
       // One arrival per warp: every lane has written its part of the stage and made it visible to the async
@@ -631,10 +658,10 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
         // Release the codes buffer only now that the loaded words have been consumed: the arrival is not
         // ordered behind a shared-memory load whose result no instruction has waited for yet, and the
         // TMA refill must not overtake the warp's last read.
-        if (kbl + kDequantGroups >= KPS) mbar_arrive(&raw_empty[buf]);
+        if (kbl + DQG >= KPS) mbar_arrive(&raw_empty[buf]);
       }
     }
-    if (!ok && !s_fail) { s_fail = 4; atomicExch(&g_tc_error, 4); }
+    if (!ok && !s_fail) { s_fail = 4; atomicCAS(&g_tc_error, 0, 4); }
   } else {
     // ---------------- epilogue: TMEM -> registers -> bf16 rows of y ----------------
     const int q = warp & 3;   // TMEM lane quarter this warp may read
@@ -690,7 +717,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(&acc_empty[buf]);  // this accumulator set may be overwritten
     }
-    if (!ok && !s_fail) { s_fail = 5; atomicExch(&g_tc_error, 5); }
+    if (!ok && !s_fail) { s_fail = 5; atomicCAS(&g_tc_error, 0, 5); }
   }
   if constexpr (CAN_SPLIT) {
     if (S > 1) {
@@ -809,7 +836,7 @@ EncodeFn get_encode() {
 }
 
 constexpr size_t pipe_bytes_tc(bool grouped, bool wide, bool half = false) {   // stages + code ring
-  return (size_t)stages_of(grouped, wide, half) * ((half ? A_STAGE_BYTES / 2 : A_STAGE_BYTES) + bn_max_of(wide, grouped) * BK * 2) +
+  return (size_t)stages_of(grouped, wide, half) * (A_STAGE_BYTES + kb_per_stage_of(half) * bn_max_of(wide, grouped) * BK * 2) +
          (size_t)raw_bufs_of(grouped, wide, half) * bn_max_of(wide, grouped) * 128;
 }
 constexpr size_t smem_bytes_tc(bool grouped, bool wide, bool half = false) {
