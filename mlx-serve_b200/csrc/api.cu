@@ -362,9 +362,15 @@ QB200_API int qb200_quantized_matmul_batch(qb200_tensor* const* res, const qb200
       wide = wide && !empty[i] && takes_wide(a[i]) && a[i].K == a[0].K;
       fuse = fuse && !empty[i] && a[i].M <= 8 && qmv_stream_supported(a[i]) && a[i].K == a[0].K;
     }
+    // beyond the streaming kernels' widths, up to 256 tokens: one launch of the tensor-core kernel over all matrices
+    bool tc = n > 1 && !wide && !fuse;
+    for (int i = 0; i < n && tc; ++i) tc = !empty[i] && a[i].M > wide_max_tokens() && a[i].M > 8;
+    tc = tc && qmm_tc_multi_supported(a, n);
     cudaError_t e = cudaSuccess;
     if (wide) {
       e = launch_qmv_wide_multi(a, n, (cudaStream_t)s);
+    } else if (tc) {
+      e = launch_qmm_tc_multi(a, n, (cudaStream_t)s);
     } else if (fuse) {
       e = launch_qmv_stream_multi(a, n, (cudaStream_t)s);
     } else {

@@ -119,6 +119,8 @@ void qmv_wide_error_reset();
 // ---- qmm_tc.cu : prefill widths on tcgen05 (dequantise into the swizzled smem operand, TMEM accumulate) ----
 bool qmm_tc_supported(const QmmArgs& a);
 cudaError_t launch_qmm_tc(const QmmArgs& a, cudaStream_t st);
+bool qmm_tc_multi_supported(const QmmArgs* a, int count);   // several matrices, same activations, one launch (<= 256 tokens)
+cudaError_t launch_qmm_tc_multi(const QmmArgs* a, int count, cudaStream_t st);
 void qmm_tc_error_reset();
 int qmm_tc_error_code();  // 0, or the code of a bounded wait that expired in the last failing launch
 struct GatherArgs;

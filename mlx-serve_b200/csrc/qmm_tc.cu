@@ -95,10 +95,16 @@ constexpr uint32_t kSpinLimit = 1u << 24;
 
 __device__ int g_tc_error = 0;   // 0 = ok; otherwise the code of the wait that expired
 
+constexpr int kMaxTcMat = 4;   // weight matrices multiplied against the same activations by one launch (dense forms)
+struct TcMaps { CUtensorMap m[kMaxTcMat]; };   // their packed codes as tensor maps
 struct TcK {
-  const uint32_t* w; const uint16_t* s; const uint16_t* b; uint16_t* y;
-  int M, N, K;
-  int64_t ldw, lds, ldy;
+  // per matrix (the grouped form has one: the banks seen as a matrix of E * N rows)
+  const uint16_t* sv[kMaxTcMat]; const uint16_t* bv[kMaxTcMat]; uint16_t* yv[kMaxTcMat];
+  int Nv[kMaxTcMat];
+  int64_t ldsv[kMaxTcMat], ldyv[kMaxTcMat];
+  int tstart[kMaxTcMat + 1];   // first tile of each matrix in the launch-wide tile numbering
+  int nmat;
+  int M, N, K;                 // N: rows of matrix 0 (the grouped form: of ONE expert's matrix)
   int gshift;   // scale column = (k / 64) >> gshift
   int BN;       // weight rows per tile (multiple of 16, <= 128)
   int tiles_m, ntiles;
@@ -111,7 +117,11 @@ struct TcK {
   int ksplit;
 };
 
+// Kernel parameters are indexed with constant subscripts only (a dynamic subscript would force a local copy).
+#define TC_SEL4(arr, i) ((i) == 0 ? (arr)[0] : ((i) == 1 ? (arr)[1] : ((i) == 2 ? (arr)[2] : (arr)[3])))
+
 struct TileCoord {
+  int mi;                // matrix of the tile (0 in the grouped form)
   int row0, row_end;     // token rows [row0, min(row0 + 256, row_end)) of x / y
   int n0, nend;          // output columns [n0, nend) of y
   int wrow0, wrow_last;  // first weight row of the tile in the (stacked) weight matrix; last row that may be read
@@ -319,6 +329,7 @@ __device__ __forceinline__ TileCoord tile_coords(const TcK& p, int BN, const int
     const int local = tile - s_tcum[a];
     const int rows = s_off[a + 1] - s_off[a], tm = (rows + BM - 1) / BM;
     const int nb = local / tm, mb = local - nb * tm;
+    c.mi = 0;
     c.row0 = s_off[a] + mb * BM;
     c.row_end = s_off[a + 1];
     c.n0 = nb * BN;
@@ -326,12 +337,18 @@ __device__ __forceinline__ TileCoord tile_coords(const TcK& p, int BN, const int
     c.wrow0 = a * p.N + c.n0;
     c.wrow_last = a * p.N + p.N - 1;
   } else {
-    c.row0 = (tile % p.tiles_m) * BM;
+    int mi = 0;
+    if (p.nmat > 1 && tile >= p.tstart[1]) mi = 1;
+    if (p.nmat > 2 && tile >= p.tstart[2]) mi = 2;
+    if (p.nmat > 3 && tile >= p.tstart[3]) mi = 3;
+    const int t = tile - TC_SEL4(p.tstart, mi), Nm = TC_SEL4(p.Nv, mi);
+    c.mi = mi;
+    c.row0 = (t % p.tiles_m) * BM;
     c.row_end = p.M;
-    c.n0 = (tile / p.tiles_m) * BN;
-    c.nend = (c.n0 + BN) < p.N ? (c.n0 + BN) : p.N;
+    c.n0 = (t / p.tiles_m) * BN;
+    c.nend = (c.n0 + BN) < Nm ? (c.n0 + BN) : Nm;
     c.wrow0 = c.n0;
-    c.wrow_last = p.N - 1;
+    c.wrow_last = Nm - 1;
   }
   return c;
 }
@@ -393,7 +410,7 @@ __device__ __noinline__ void issuer_walk(const TcK& p, const IssuerArgs a, uint3
 }
 
 template <int BITS, bool GROUPED, bool WIDE, bool HALF = false>
-__global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, TcK p) {
+__global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ TcMaps wmaps, TcK p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // 1024-byte alignment for the swizzled tiles.  The wide form has no room for the slack: the kernel has no
   // static shared memory, so its dynamic window starts aligned; that is verified below.
@@ -517,12 +534,14 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       const int sb_per_tile = nkb / KPS;
       int sbk = 0, fail = 0;
       for (int tile = tile0; tile < ntiles && !fail && !s_fail; tile += tstride) {
-        const int n0 = coords(tile).wrow0;
+        const TileCoord tcw = coords(tile);
+        const int n0 = tcw.wrow0;
+        const CUtensorMap* wmap = &wmaps.m[tcw.mi];
         for (int sbl = 0; sbl < sb_per_tile; ++sbl, ++sbk) {
           const int buf = sbk % RAW_BUFS;
           if (sbk >= RAW_BUFS && !mbar_wait_relaxed(&raw_empty[buf], ((sbk / RAW_BUFS) - 1) & 1)) { fail = 7; break; }
           mbar_expect_tx(&raw_full[buf], (uint32_t)BN * 128u);
-          tma_load_2d(smem_u32(raw + buf * RAW_B), &wmap, &raw_full[buf], (kb0 / KPS + sbl) * 32, n0);
+          tma_load_2d(smem_u32(raw + buf * RAW_B), wmap, &raw_full[buf], (kb0 / KPS + sbl) * 32, n0);
         }
       }
       if (fail) { s_fail = fail; atomicCAS(&g_tc_error, 0, fail); }
@@ -574,24 +593,30 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
     const int WL = 8 << p.gshift;
     uint4 s_cur = make_uint4(0, 0, 0, 0), b_cur = s_cur, s_nxt = s_cur, b_nxt = s_cur;
     int f_tl = 0, f_kb = 0;
-    auto row_of = [&](int tl) {
+    // this thread's row of scales and of biases in tile `tl` (looked up once per tile: coords() divides, and
+    // searches in the grouped form)
+    auto row_ptrs = [&](int tl, const uint16_t*& sp, const uint16_t*& bp) {
       const int tile = tile0 + tl * tstride;
       const TileCoord tc = coords(tile);
-      const int n = tc.wrow0 + r;
-      return n < tc.wrow_last ? n : tc.wrow_last;
+      int n = tc.wrow0 + r;
+      n = n < tc.wrow_last ? n : tc.wrow_last;
+      const int64_t off = (int64_t)n * TC_SEL4(p.ldsv, tc.mi);
+      sp = TC_SEL4(p.sv, tc.mi) + off;
+      bp = TC_SEL4(p.bv, tc.mi) + off;
     };
-    // (the row is looked up once per tile: coords() divides, and searches in the grouped form)
-    int f_row = ntl > 0 ? row_of(0) : 0, c_row = f_row;
+    const uint16_t* f_sp = nullptr; const uint16_t* f_bp = nullptr;   // prefetch cursor's row
+    const uint16_t* c_sp = nullptr; const uint16_t* c_bp = nullptr;   // current tile's row (scalar path)
+    if (ntl > 0) { row_ptrs(0, f_sp, f_bp); c_sp = f_sp; c_bp = f_bp; }
     auto prefetch_window = [&]() {
       if (f_kb >= nkb) {
         f_kb = 0;
         ++f_tl;
-        if (f_tl < ntl) f_row = row_of(f_tl);
+        if (f_tl < ntl) row_ptrs(f_tl, f_sp, f_bp);
       }
       if (active && f_tl < ntl) {
-        const int64_t off = (int64_t)f_row * p.lds + ((kb0 + f_kb) >> p.gshift);
-        s_nxt = __ldg((const uint4*)(p.s + off));
-        b_nxt = __ldg((const uint4*)(p.b + off));
+        const int off = (kb0 + f_kb) >> p.gshift;
+        s_nxt = __ldg((const uint4*)(f_sp + off));
+        b_nxt = __ldg((const uint4*)(f_bp + off));
       }
       f_kb += WL;
     };
@@ -605,7 +630,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       if (kb >= nkb) {
         kb -= nkb;
         ++tl;
-        if (!p.sb_vec) c_row = row_of(tl);
+        if (!p.sb_vec) row_ptrs(tl, c_sp, c_bp);
       }
       const int sbk = it / KPS, kbl = it % KPS, buf = sbk % RAW_BUFS;   // nkb is a multiple of KPS
       uint32_t sv2, bv2;
@@ -621,8 +646,8 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
         bv2 = (e & 1) ? __byte_perm(bw, bw, 0x3232) : __byte_perm(bw, bw, 0x1010);
       }
       else {
-        const int64_t off = (int64_t)c_row * p.lds + ((kb0 + kb) >> p.gshift);
-        const uint32_t sv = active ? __ldg(p.s + off) : 0u, bv = active ? __ldg(p.b + off) : 0u;
+        const int off = (kb0 + kb) >> p.gshift;
+        const uint32_t sv = active ? __ldg(c_sp + off) : 0u, bv = active ? __ldg(c_bp + off) : 0u;
         sv2 = sv | (sv << 16);
         bv2 = bv | (bv << 16);
       }
@@ -693,7 +718,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
             for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(w[j]));
           }
           if (m < mend) {
-            uint16_t* yrow = p.y + (int64_t)m * p.ldy + n0 + c0;
+            uint16_t* yrow = TC_SEL4(p.yv, tc.mi) + (int64_t)m * TC_SEL4(p.ldyv, tc.mi) + n0 + c0;
             const int nvalid = nend - (n0 + c0);   // columns of this chunk inside the matrix and the tile
             const bool aligned = (((uintptr_t)yrow) & 15) == 0;
 #pragma unroll
@@ -785,7 +810,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
               }
             }
             if (m < tc.row_end) {
-              uint16_t* yrow = p.y + (int64_t)m * p.ldy + tc.n0 + c0;
+              uint16_t* yrow = TC_SEL4(p.yv, tc.mi) + (int64_t)m * TC_SEL4(p.ldyv, tc.mi) + tc.n0 + c0;
               const int nvalid = tc.nend - (tc.n0 + c0);
               const bool aligned = (((uintptr_t)yrow) & 15) == 0;
 #pragma unroll
@@ -854,12 +879,17 @@ constexpr size_t STAGES_DENSE_BYTES = pipe_bytes_tc(false, false) < pipe_bytes_t
 // Weight rows per tile: the candidate whose tile count fills the last wave best.  Time per tile ~ rows + 40:
 // the activation traffic of a k-block through shared memory does not shrink with the tile, so narrow tiles
 // only pay when they put otherwise idle SMs to work (few weight rows, long K, few tokens).
-int pick_bn(int64_t M, int64_t N, int nsm, int bn_max = BN_MAX) {
+int64_t count_tiles(const int64_t* N, int nmat, int bn) {   // weight-row blocks of all matrices (tiles never straddle two)
+  int64_t t = 0;
+  for (int i = 0; i < nmat; ++i) t += (N[i] + bn - 1) / bn;
+  return t;
+}
+int pick_bn(int64_t M, const int64_t* N, int nmat, int nsm, int bn_max = BN_MAX) {
   const int64_t tiles_m = (M + BM - 1) / BM;
   int best = bn_max;
   int64_t best_cost = -1;
   for (int bn = bn_max; bn >= 32; bn -= 16) {
-    const int64_t tiles = tiles_m * ((N + bn - 1) / bn);
+    const int64_t tiles = tiles_m * count_tiles(N, nmat, bn);
     const int64_t waves = (tiles + nsm - 1) / nsm;
     const int64_t cost = waves * (bn + 40);
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
@@ -895,7 +925,7 @@ struct TcLaunch {
 };
 
 template <int BITS, bool GROUPED, bool WIDE, bool HALF = false>
-cudaError_t launch_tc_inst(const CUtensorMap& xmap, const CUtensorMap& wmap, const TcK& p, dim3 grid, cudaStream_t st,
+cudaError_t launch_tc_inst(const CUtensorMap& xmap, const TcMaps& wmap, const TcK& p, dim3 grid, cudaStream_t st,
                            int cluster = 1) {
   static bool done[64] = {};
   int dev = 0;
@@ -957,7 +987,14 @@ int split_capacity(int cluster) {
   return cached[dev][cluster] > 0 ? cached[dev][cluster] : 0;
 }
 
-cudaError_t launch_tc(const TcLaunch& a, bool grouped, cudaStream_t st) {
+// `nmat` matrices against the same activations (dense forms; every entry shares x, M, K, bits and group size with
+// the first; the grouped form takes one).
+cudaError_t launch_tc(const TcLaunch* av, int nmat, bool grouped, cudaStream_t st) {
+  const TcLaunch& a = av[0];
+  int64_t Nv[kMaxTcMat];
+  for (int i = 0; i < nmat; ++i) Nv[i] = av[i].N;
+  int64_t Ntot = 0, Nmin = a.N;
+  for (int i = 0; i < nmat; ++i) { Ntot += Nv[i]; Nmin = Nv[i] < Nmin ? Nv[i] : Nmin; }
   EncodeFn enc = get_encode();
   if (!enc) return cudaErrorNotSupported;
   CUtensorMap map;
@@ -974,7 +1011,7 @@ cudaError_t launch_tc(const TcLaunch& a, bool grouped, cudaStream_t st) {
   // Wide tiles when both 128-token halves of a tile are in use and there are enough weight rows to fill the GPU
   // with them; the grouped form does not know its tile count on the host and takes full-width dense tiles.
   // (grouped: many rows per expert on average, so that most tiles have both halves)
-  const bool wide = grouped ? (a.M >= 192 * (int64_t)a.E && a.N >= 256) : (a.M > 256 && a.N >= 1024);
+  const bool wide = grouped ? (a.M >= 192 * (int64_t)a.E && a.N >= 256) : (a.M > 256 && Nmin >= 1024);
   if (grouped) {
     // tile width with the best product of (rows used / rows multiplied) and the width's own efficiency
     // (time per tile ~ width + 40, as in pick_bn)
@@ -988,7 +1025,7 @@ cudaError_t launch_tc(const TcLaunch& a, bool grouped, cudaStream_t st) {
     }
     p.BN = a.N >= 64 ? best : (int)((a.N + 15) / 16 * 16);
   } else {
-    p.BN = pick_bn(a.M, a.N, nsm, bn_max_of(wide));
+    p.BN = pick_bn(a.M, Nv, nmat, nsm, bn_max_of(wide));
   }
   // Split-K over a cluster when a few-token problem has too few tiles to occupy the GPU: with one tile per CTA
   // the time is the number of k-blocks a CTA walks (plus ~6 k-block times for the exchange), whatever the tile
@@ -998,39 +1035,48 @@ cudaError_t launch_tc(const TcLaunch& a, bool grouped, cudaStream_t st) {
   if (!grouped && !wide && a.M <= 256) {
     const int gshift = a.gs == 128 ? 1 : 0;
     const int nkb_all = (int)(a.K / BK);
-    const int64_t plain_tiles = (a.N + p.BN - 1) / p.BN;
+    const int64_t plain_tiles = count_tiles(Nv, nmat, p.BN);
     const int64_t plain_cost = ((plain_tiles + nsm - 1) / nsm) * nkb_all;
     for (int sp = 4; sp >= 2; sp >>= 1) {
       if (nkb_all % (sp * (8 << gshift)) != 0 || nkb_all / sp < 8) continue;   // whole scale windows per rank
       const int cap = a.bits == 4 ? split_capacity<4>(sp) : split_capacity<8>(sp);   // resident CTAs in clusters of sp
       const int max_tiles = cap / sp;
       if (max_tiles < 1) continue;
-      int bn = (int)((a.N + max_tiles - 1) / max_tiles);
+      int bn = (int)((Ntot + max_tiles - 1) / max_tiles);
       bn = (bn + 15) / 16 * 16;
       if (bn < 32) bn = 32;
-      if (bn > BN_MAX || (a.N + bn - 1) / bn > max_tiles) continue;
+      while (bn <= BN_MAX && count_tiles(Nv, nmat, bn) > max_tiles) bn += 16;   // (tiles do not straddle matrices)
+      if (bn > BN_MAX) continue;
       if ((size_t)(sp - 1) * (a.M > 128 ? 256 : 128) * ((bn + 31) / 32 * 32 * 4 + 16) > (size_t)STAGES_DENSE_BYTES) continue;   // exchange buffer
       if (nkb_all / sp + 6 < plain_cost) { p.ksplit = sp; p.BN = bn; break; }
     }
   }
   // packed codes as a [rows][K * bits / 32] array of 32-bit words: 128 bytes of BN rows per copy
-  CUtensorMap wmap;
-  {
-    const cuuint64_t wdims[2] = {(cuuint64_t)(a.K * a.bits / 32), (cuuint64_t)a.wrows};
-    const cuuint64_t wstrides[1] = {(cuuint64_t)a.ldw * 4};
+  TcMaps wmap;
+  for (int i = 0; i < kMaxTcMat; ++i) {
+    const TcLaunch& m = av[i < nmat ? i : 0];
+    const cuuint64_t wdims[2] = {(cuuint64_t)(m.K * m.bits / 32), (cuuint64_t)m.wrows};
+    const cuuint64_t wstrides[1] = {(cuuint64_t)m.ldw * 4};
     const cuuint32_t wbox[2] = {32, (cuuint32_t)p.BN};
-    r = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)a.w, wdims, wstrides, wbox, estr,
+    r = enc(&wmap.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)m.w, wdims, wstrides, wbox, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
   }
-  p.w = a.w; p.s = a.s; p.b = a.b; p.y = a.y;
+  p.nmat = nmat;
   p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
-  p.ldw = a.ldw; p.lds = a.lds; p.ldy = a.ldy;
   p.gshift = a.gs == 128 ? 1 : 0;
-  p.sb_vec = (a.lds % 8 == 0) && ((((uintptr_t)p.s) | ((uintptr_t)p.b)) & 15) == 0 && (a.K % (512 << p.gshift)) == 0;
   p.tiles_m = (int)((a.M + BM - 1) / BM);
-  p.ntiles = p.tiles_m * (int)((a.N + p.BN - 1) / p.BN);   // dense form; the grouped form counts on the device
+  p.sb_vec = (a.K % (512 << p.gshift)) == 0;
+  p.tstart[0] = 0;
+  for (int i = 0; i < kMaxTcMat; ++i) {
+    const TcLaunch& m = av[i < nmat ? i : 0];
+    p.sv[i] = m.s; p.bv[i] = m.b; p.yv[i] = m.y;
+    p.Nv[i] = (int)m.N; p.ldsv[i] = m.lds; p.ldyv[i] = m.ldy;
+    p.tstart[i + 1] = p.tstart[i] + (i < nmat ? p.tiles_m * (int)((m.N + p.BN - 1) / p.BN) : 0);
+    if (i < nmat && !((m.lds % 8 == 0) && ((((uintptr_t)m.s) | ((uintptr_t)m.b)) & 15) == 0)) p.sb_vec = 0;
+  }
+  p.ntiles = p.tstart[nmat];   // dense forms; the grouped form counts on the device
   p.rhs = a.rhs; p.rhs_i64 = a.rhs_i64; p.E = a.E;
   dim3 grid((unsigned)((!grouped && p.ntiles < nsm) ? p.ntiles : nsm), 1, 1);
   if (p.ksplit > 1) {
@@ -1059,7 +1105,35 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, cudaStream_t st) {
   l.y = (uint16_t*)a.y + a.yb.offset(0); l.ldy = a.ldy;
   l.bits = a.bits; l.gs = a.gs;
   l.rhs = nullptr; l.rhs_i64 = 0; l.E = 0;
-  return launch_tc(l, false, st);
+  return launch_tc(&l, 1, false, st);
+}
+
+// `count` (<= 4) matrices against the same activations in one launch: every entry has passed qmm_tc_supported
+// and shares x, M, K, bits and group size with the first.  Few-token forms only (M <= 256): that is where a
+// launch is short enough for its fixed part and its partly filled wave to matter.
+bool qmm_tc_multi_supported(const QmmArgs* a, int count) {
+  if (count < 2 || count > kMaxTcMat || a[0].M > 256) return false;
+  for (int i = 0; i < count; ++i) {
+    if (!qmm_tc_supported(a[i])) return false;
+    if (a[i].x != a[0].x || a[i].M != a[0].M || a[i].K != a[0].K || a[i].bits != a[0].bits || a[i].gs != a[0].gs ||
+        a[i].ldx != a[0].ldx || a[i].xb.offset(0) != a[0].xb.offset(0))
+      return false;
+  }
+  return true;
+}
+cudaError_t launch_qmm_tc_multi(const QmmArgs* a, int count, cudaStream_t st) {
+  TcLaunch l[kMaxTcMat];
+  for (int i = 0; i < count; ++i) {
+    l[i].x = (const char*)a[i].x + a[i].xb.offset(0) * 2; l[i].M = a[i].M; l[i].K = a[i].K; l[i].ldx = a[i].ldx;
+    l[i].w = a[i].w + a[i].wb.offset(0);
+    l[i].s = (const uint16_t*)a[i].s + a[i].sb.offset(0);
+    l[i].b = (const uint16_t*)a[i].b + a[i].sb.offset(0);
+    l[i].wrows = a[i].N; l[i].N = a[i].N; l[i].ldw = a[i].ldw; l[i].lds = a[i].lds;
+    l[i].y = (uint16_t*)a[i].y + a[i].yb.offset(0); l[i].ldy = a[i].ldy;
+    l[i].bits = a[i].bits; l[i].gs = a[i].gs;
+    l[i].rhs = nullptr; l[i].rhs_i64 = 0; l[i].E = 0;
+  }
+  return launch_tc(l, count, false, st);
 }
 
 // gather_qmm with the rows sorted by expert (the reference's prefill MoE path: x [I, 1, K] already gathered,
@@ -1091,7 +1165,7 @@ cudaError_t launch_gather_tc(const GatherArgs& a, cudaStream_t st) {
   l.y = (uint16_t*)a.y; l.ldy = a.N;
   l.bits = a.bits; l.gs = a.gs;
   l.rhs = a.rhs; l.rhs_i64 = a.rhs_dtype == QB200_INT64; l.E = (int)a.E;
-  return launch_tc(l, true, st);
+  return launch_tc(&l, 1, true, st);
 }
 
 

@@ -194,6 +194,33 @@ def test_batch_entry_matches_single_calls(M):
     for a, b in zip(single, outs):
         assert torch.equal(a.view(torch.int16), b.view(torch.int16))
 
+@pytest.mark.parametrize("bits,gs", [(4, 64), (8, 64), (4, 128)])
+@pytest.mark.parametrize("M,K,Ns", [(128, 4096, (4096, 1024, 1024)), (200, 1024, (1000, 520)), (100, 768, (256, 48, 640, 1008)),
+                                    (65, 14336, (512, 512)), (128, 2048, (7168, 7168))])
+def test_batch_entry_beyond_64_tokens_one_tensor_core_launch(bits, gs, M, K, Ns):
+    """Several matrices on one input above the streaming kernels' widths (q, k, v and gate, up at 65..256 tokens): one
+    launch of the tensor-core kernel walks the tiles of all of them, with K split over a cluster where the tiles are
+    few.  Every output against the oracle of that route (weight term rounded to bf16 once), and against the single
+    calls within the order-of-summation noise of fp32 partial sums."""
+    import qb200
+    if K % gs:
+        pytest.skip("K not a multiple of the group size")
+    rng = np.random.default_rng(M + K + bits + gs + len(Ns))
+    xh = qo.f32_to_bf16(rand_bf16(rng, (M, K)))
+    x = to_dev_bf16(xh)
+    host = [make_weight(rng, (n, K), gs, bits) for n in Ns]
+    triples = [dev_triple(*t) for t in host]
+    outs = [torch.full((M, n), float("nan"), dtype=torch.bfloat16, device="cuda") for n in Ns]
+    qb200.quantized_matmul_batch(x, triples, outs, True, gs, bits)
+    assert qb200.lib().qb200_debug_tc_status() == 0
+    for (q, s, b), t, o in zip(host, triples, outs):
+        assert not torch.isnan(o).any()
+        ref = qo.qmm(qo.bf16_to_f32(xh), q, s, b, gs, bits, True, bf16_weights=True)
+        gate_bf16(o.float().cpu().numpy(), ref, f"batched tensor-core launch N={q.shape[0]}")
+        one = qb200.quantized_matmul(x, *t, True, gs, bits)
+        d = (o.float() - one.float()).abs().max().item()
+        assert d <= 2.0 ** -6 * max(1.0, one.float().abs().max().item()), d
+
 
 @pytest.mark.parametrize("bits,gs", [(4, 64), (8, 64), (4, 128)])
 @pytest.mark.parametrize("M,N,K", [(512, 1024, 4096), (300, 1000, 1024), (17, 128, 64), (2048, 256, 2048),
