@@ -304,15 +304,16 @@ static int prepare_qmm(qb200_tensor* res, const qb200_tensor* x, const qb200_ten
   return QB200_OK;
 }
 
-// Routing by token count.  Up to 8 tokens: the narrow streaming kernel (one launch).  9 .. 64 (bf16 activations): the
-// wide streaming kernel, which reads every packed word once for up to 64 tokens per pass (measured on the C2 layer:
-// 172 us at 64 tokens against 235 us for the tensor-core kernel; at 128 tokens the tensor-core kernel wins, 238 us
-// against 341).  Above that the tensor-core kernel.  QB200_WIDE_MAX_TOKENS in the environment moves the upper limit (0 turns the wide kernel off; a
-// diagnostic for measuring the crossover, read once).
+// Routing by token count.  Up to 8 tokens: the narrow streaming kernel (one launch).  9 .. 32 (bf16 activations): the
+// wide streaming kernel, which reads every packed word once for up to 64 tokens per pass.  Above that the
+// tensor-core kernel, whose time does not depend on the token count up to 128 (measured on the C2 layer through the
+// batch entry: 110 us at 32 tokens and 170 us at 64 on the wide kernel, 140 / 143 / 149 us at 32 / 64 / 128 on the
+// tensor-core kernel).  QB200_WIDE_MAX_TOKENS in the environment moves the upper limit (0 turns the wide kernel off,
+// 64 is the most it serves; a diagnostic for measuring the crossover, read once).
 static int64_t wide_max_tokens() {
   static const int64_t v = [] {
     const char* e = getenv("QB200_WIDE_MAX_TOKENS");
-    return e ? (int64_t)atoll(e) : (int64_t)64;
+    return e ? (int64_t)atoll(e) : (int64_t)32;
   }();
   return v;
 }

@@ -40,10 +40,11 @@ def _run(x32, q, s, b, gs, bits, transpose=True, tag=None):
 def _tensor_core_route(M, K, bits, gs):
     """The dispatch rule of qb200_quantized_matmul for bf16 activations: from 9 tokens a kernel that rounds the weight
     term to bf16 once, as the reference's dense route does -- the wide streaming kernel (4/8 bits at group 64, 4 bits
-    at group 128, K a multiple of 256 up to 16384) or the tcgen05 kernel (K a multiple of 256, 4/8 bits, group
-    64/128); up to 8 tokens, and for other formats, the fp32 weight term."""
+    at group 128, K a multiple of 256 up to 16384; 9..32 tokens) or the tcgen05 kernel (K a multiple of 256, 4/8 bits,
+    group 64/128; from 33 tokens, and where the wide kernel does not serve); up to 8 tokens, and for other formats,
+    the fp32 weight term."""
     tc_ok = K % 256 == 0 and bits in (4, 8) and gs in (64, 128)
-    return tc_ok and M > 8 and (M > 64 or K <= 16384 or (bits, gs) == (8, 128))
+    return tc_ok and M > 8 and (M > 32 or K <= 16384 or (bits, gs) == (8, 128))
 
 
 def test_config1_qmv_4096x4096():
@@ -72,11 +73,42 @@ def test_config2_llama_projections(proj, M):
                                    (31, 640, 4096), (16, 14336, 4096), (12, 256, 256), (40, 1000, 2048), (64, 640, 4096),
                                    (57, 4096, 1024), (33, 16, 512)])
 def test_nine_to_sixty_four_tokens(bits, gs, M, N, K):
-    """9..64 tokens: the wide streaming kernel reads the weights once per pass (16-, 32- and 64-token forms, ragged token
-    counts and row counts, K from one ring stage to the longest projection, work cut over the CTAs inside tile blocks)."""
+    """9..32 tokens: the wide streaming kernel reads the weights once per pass (16- and 32-token forms, ragged token
+    counts and row counts, K from one ring stage to the longest projection, work cut over the CTAs inside tile blocks);
+    33..64 tokens take the tensor-core kernel."""
     rng = np.random.default_rng(M * 7 + N + K + bits)
     q, s, b = make_weight(rng, (N, K), gs, bits)
     _run(rand_bf16(rng, (M, K)), q, s, b, gs, bits)
+
+
+_WIDE64_CHILD = r"""
+import sys, numpy as np, torch
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[2]); sys.path.insert(0, sys.argv[3])
+from oracle import qoracle as qo
+import qb200
+from util import make_weight, rand_bf16, dev_triple, to_dev_bf16, gate_bf16
+for (M, N, K, bits, gs) in [(64, 640, 4096, 4, 64), (40, 1000, 2048, 8, 64), (57, 4096, 1024, 4, 128), (33, 16, 512, 4, 64)]:
+    rng = np.random.default_rng(M + N + K)
+    q, s, b = make_weight(rng, (N, K), gs, bits)
+    xh = qo.f32_to_bf16(rand_bf16(rng, (M, K)))
+    y = qb200.quantized_matmul(to_dev_bf16(xh), *dev_triple(q, s, b), True, gs, bits)
+    ref = qo.qmm(qo.bf16_to_f32(xh), q, s, b, gs, bits, True, bf16_weights=True)
+    gate_bf16(y.float().cpu().numpy(), ref, f"64-token form {M}x{N}x{K}")
+assert qb200.lib().qb200_debug_tc_status() == 0
+print("ok")
+"""
+
+
+def test_wide_kernel_64_token_form_behind_the_environment_switch():
+    """QB200_WIDE_MAX_TOKENS=64 (read once per process, hence a child process) sends 33..64 tokens to the wide streaming
+    kernel's 64-token form, which the default routing no longer reaches."""
+    import os, subprocess, sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    root = os.path.dirname(here)
+    env = dict(os.environ, QB200_WIDE_MAX_TOKENS="64")
+    out = subprocess.run([sys.executable, "-c", _WIDE64_CHILD, root, os.path.join(root, "mlx-serve_b200"), here],
+                         env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and out.stdout.strip().endswith("ok"), out.stdout[-2000:] + out.stderr[-2000:]
 
 
 def test_config2_m128():
