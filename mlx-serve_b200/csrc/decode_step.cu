@@ -15,26 +15,48 @@ __device__ __forceinline__ float rbf16(float x) { return __uint_as_float((uint32
 
 // One CTA per row.  sum_out (optional) = a + b rounded to bf16 (mlx_add, src/transformer.zig:9838-9841), and the
 // norm is taken of that sum: y = bf16(w * bf16(x * rsqrt(mean(x^2) + eps))) (mlx_fast_rms_norm).
-__global__ void __launch_bounds__(256) rms_norm_kernel(const uint16_t* a, const uint16_t* b, const uint16_t* w, uint16_t* sum_out,
-                                                       uint16_t* norm_out, int64_t lda, int64_t ldb, int64_t lds, int64_t ldn,
-                                                       int d, float eps) {
+// VEC: eight values per thread and step through 128-bit loads, the weight row fetched before the reduction (rows of a
+// few thousand values are one step for a CTA of up to 1024 threads: every load of the row is in flight at once);
+// otherwise two values per step (any alignment of even d).
+template <bool VEC>
+__global__ void __launch_bounds__(1024) rms_norm_kernel(const uint16_t* a, const uint16_t* b, const uint16_t* w, uint16_t* sum_out,
+                                                        uint16_t* norm_out, int64_t lda, int64_t ldb, int64_t lds, int64_t ldn,
+                                                        int d, float eps) {
   extern __shared__ float xs[];   // the row in fp32
-  __shared__ float red[8];
+  __shared__ float red[32];
   const int64_t row = blockIdx.x;
   const uint16_t* ar = a + row * lda;
   const uint16_t* br = b ? b + row * ldb : nullptr;
+  constexpr int V = VEC ? 8 : 2;
   float acc = 0.f;
-  for (int i = threadIdx.x * 2; i < d; i += blockDim.x * 2) {
-    const uint32_t av = *(const uint32_t*)(ar + i);
-    float x0 = bf16lo(av), x1 = bf16hi(av);
-    if (br) {
-      const uint32_t bv = *(const uint32_t*)(br + i);
-      x0 = rbf16(x0 + bf16lo(bv));
-      x1 = rbf16(x1 + bf16hi(bv));
-      if (sum_out) *(uint32_t*)(sum_out + row * lds + i) = pack_bf16x2(x0, x1);
+  uint4 wv0 = make_uint4(0u, 0u, 0u, 0u);   // VEC: the weights of this thread's first step
+  if (VEC && norm_out && (int)threadIdx.x * V < d) wv0 = *(const uint4*)(w + threadIdx.x * V);
+  for (int i = threadIdx.x * V; i < d; i += blockDim.x * V) {
+    uint32_t av[V / 2], bv[V / 2];
+    if constexpr (VEC) {
+      const uint4 t = *(const uint4*)(ar + i);
+      av[0] = t.x; av[1] = t.y; av[2] = t.z; av[3] = t.w;
+      if (br) { const uint4 u = *(const uint4*)(br + i); bv[0] = u.x; bv[1] = u.y; bv[2] = u.z; bv[3] = u.w; }
+    } else {
+      av[0] = *(const uint32_t*)(ar + i);
+      if (br) bv[0] = *(const uint32_t*)(br + i);
     }
-    xs[i] = x0; xs[i + 1] = x1;
-    acc += x0 * x0 + x1 * x1;
+    uint32_t sv[V / 2];
+#pragma unroll
+    for (int j = 0; j < V / 2; ++j) {
+      float x0 = bf16lo(av[j]), x1 = bf16hi(av[j]);
+      if (br) {
+        x0 = rbf16(x0 + bf16lo(bv[j]));
+        x1 = rbf16(x1 + bf16hi(bv[j]));
+        sv[j] = pack_bf16x2(x0, x1);
+      }
+      xs[i + 2 * j] = x0; xs[i + 2 * j + 1] = x1;
+      acc += x0 * x0 + x1 * x1;
+    }
+    if (br && sum_out) {
+      if constexpr (VEC) *(uint4*)(sum_out + row * lds + i) = make_uint4(sv[0], sv[1], sv[2], sv[3]);
+      else *(uint32_t*)(sum_out + row * lds + i) = sv[0];
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -44,10 +66,19 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const uint16_t* a, const 
   for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
   const float inv = rsqrtf(tot / (float)d + eps);
   if (!norm_out) return;
-  for (int i = threadIdx.x * 2; i < d; i += blockDim.x * 2) {
-    const uint32_t wv = *(const uint32_t*)(w + i);
-    const float y0 = bf16lo(wv) * rbf16(xs[i] * inv), y1 = bf16hi(wv) * rbf16(xs[i + 1] * inv);
-    *(uint32_t*)(norm_out + row * ldn + i) = pack_bf16x2(y0, y1);
+  for (int i = threadIdx.x * V; i < d; i += blockDim.x * V) {
+    uint32_t wv[V / 2], ov[V / 2];
+    if constexpr (VEC) {
+      const uint4 t = i == (int)threadIdx.x * V ? wv0 : *(const uint4*)(w + i);
+      wv[0] = t.x; wv[1] = t.y; wv[2] = t.z; wv[3] = t.w;
+    } else {
+      wv[0] = *(const uint32_t*)(w + i);
+    }
+#pragma unroll
+    for (int j = 0; j < V / 2; ++j)
+      ov[j] = pack_bf16x2(bf16lo(wv[j]) * rbf16(xs[i + 2 * j] * inv), bf16hi(wv[j]) * rbf16(xs[i + 2 * j + 1] * inv));
+    if constexpr (VEC) *(uint4*)(norm_out + row * ldn + i) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+    else *(uint32_t*)(norm_out + row * ldn + i) = ov[0];
   }
 }
 
@@ -167,19 +198,29 @@ __global__ void __launch_bounds__(256) kv_append_seqs_kernel(const __grid_consta
 cudaError_t launch_rms_norm(const uint16_t* a, const uint16_t* b, const uint16_t* w, uint16_t* sum_out, uint16_t* norm_out,
                             int64_t rows, int d, int64_t lda, int64_t ldb, int64_t lds, int64_t ldn, float eps, cudaStream_t st) {
   if (rows <= 0 || d <= 0) return cudaSuccess;
-  const int threads = d >= 2048 ? 256 : 128;
+  // 128-bit form when every row of every operand is 16-byte aligned; a CTA of up to 1024 threads, one step per row
+  // where the row is short enough
+  auto al16 = [](const void* p, int64_t ld) { return p == nullptr || (((uintptr_t)p & 15) == 0 && (ld * 2) % 16 == 0); };
+  const bool vec = d % 8 == 0 && al16(a, lda) && al16(b, ldb) && al16(w, 0) && al16(sum_out, lds) && al16(norm_out, ldn);
+  const int per = vec ? 8 : 2;
+  int threads = (d + per - 1) / per;
+  threads = (threads + 31) / 32 * 32;
+  threads = threads > 1024 ? 1024 : (threads < 64 ? 64 : threads);
   if ((size_t)d * sizeof(float) > 48 * 1024) {   // rows beyond 12288 values: the fp32 copy of a row needs the opt-in shared memory
     std::lock_guard<std::mutex> lk(setup_mutex());
     static bool done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !done[dev]) {
-      const cudaError_t e = cudaFuncSetAttribute(rms_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * (int)sizeof(float));
+      cudaError_t e = cudaFuncSetAttribute(rms_norm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * (int)sizeof(float));
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(rms_norm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * (int)sizeof(float));
       if (e != cudaSuccess) return e;
       if (dev >= 0 && dev < 64) done[dev] = true;
     }
   }
-  return launch_kernel(rms_norm_kernel, dim3((unsigned)rows), dim3(threads), (size_t)d * sizeof(float), st, a, b, w, sum_out, norm_out, lda, ldb, lds, ldn, d, eps);
+  if (vec)
+    return launch_kernel(rms_norm_kernel<true>, dim3((unsigned)rows), dim3(threads), (size_t)d * sizeof(float), st, a, b, w, sum_out, norm_out, lda, ldb, lds, ldn, d, eps);
+  return launch_kernel(rms_norm_kernel<false>, dim3((unsigned)rows), dim3(threads), (size_t)d * sizeof(float), st, a, b, w, sum_out, norm_out, lda, ldb, lds, ldn, d, eps);
 }
 
 cudaError_t launch_rope(const uint16_t* x, uint16_t* out, const int32_t* offsets, int64_t n, int heads, int d, int dims, float base,
