@@ -503,11 +503,6 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
   // a weight tile through L2), weight block t / tiles_m.  Grouped: the expert whose tile range holds t, then
   // the same order inside the expert.
   auto coords = [&](int tile) { return tile_coords<GROUPED>(p, BN, s_off, s_tcum, tile); };
-  // Registers follow the work: the four control warps (one warp group) give theirs back, the sixteen dequant warps
-  // and the epilogue warps take more (16 x 32 x 96 + 4 x 32 x 88 + 4 x 32 x 40 = 64 Ki registers).  Every group
-  // returns to the kernel's own count before the common tail.
-  if (warp >= kTmaWarp) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
   if (warp == kTmaWarp) {
     if (lane == 0) {
       // ---------------- TMA producer (one thread) ----------------
@@ -583,10 +578,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
         asm volatile("bar.sync 1, 64;" ::: "memory");
       }
     }
-  }
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 80;");
   } else if (warp < kDequantWarps) {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 96;");
     // ---------------- dequant producers: DQG groups, one thread per weight row ----------------
     constexpr int WPG = kDequantWarps / DQG;   // warps per group
     constexpr int TPR = (WPG * 32) / bn_max_of(WIDE, GROUPED);   // threads per weight row: 1, or 2 (a half of the k-block each)
@@ -695,9 +687,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       }
     }
     if (!ok && !s_fail) { s_fail = 4; atomicCAS(&g_tc_error, 0, 4); }
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 88;");
     // ---------------- epilogue: TMEM -> registers -> bf16 rows of y ----------------
     const int q = warp & 3;   // TMEM lane quarter this warp may read
     int ti = 0;
@@ -753,7 +743,6 @@ __global__ void __launch_bounds__(kThreads, 1) qmm_tc_kernel(const __grid_consta
       mbar_arrive(&acc_empty[buf]);  // this accumulator set may be overwritten
     }
     if (!ok && !s_fail) { s_fail = 5; atomicCAS(&g_tc_error, 0, 5); }
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
   }
   if constexpr (CAN_SPLIT) {
     if (S > 1) {
