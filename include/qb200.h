@@ -370,6 +370,27 @@ QB200_API int qb200_affine_params_from_geometry(int64_t w_cols, int64_t s_cols, 
  * QB200_ERR_UNSUPPORTED for a file without one, or for an affine width MLX has no kernels for. */
 QB200_API int qb200_config_quantization(const char* json_text, int* bits, int* group_size, char* mode, size_t mode_cap);
 
+/* ==== Chunked persistence of the quantized KV cache: the chunk files of mlx-serve's SSD tier for its prefix cache
+ * (src/kv_disk_cache.zig:1-48).  One safetensors file per position range, holding for every layer with a cache the
+ * token slice of its six capacity buffers under "l{i}.k", "l{i}.v", "l{i}.ks", "l{i}.kb", "l{i}.vs", "l{i}.vb"
+ * (:1062-1074), each [1, Hkv, positions, cols].  The index around the chunks (meta.json, tokens.bin, prefix lookup,
+ * eviction) stays with the host. ==== */
+/* One layer's capacity buffers [1, Hkv, cap, cols] as qb200_kv_append takes them; k_q.data == NULL: the layer keeps no
+ * KV cache (it is left out of a chunk, and skipped when one is restored). */
+typedef struct qb200_kv_layer {
+  qb200_tensor k_q, k_scales, k_biases, v_q, v_scales, v_biases;
+} qb200_kv_layer;
+/* Writes positions [pos0, pos1) of every layer to `path` (under a temporary name, then renamed).  Synchronous:
+ * returns after the copies on `s` and the write are done. */
+QB200_API int qb200_kv_chunk_save(const char* path, const qb200_kv_layer* layers, int n_layers, int64_t pos0, int64_t pos1,
+                                  qb200_stream s);
+/* restoreKvInto for one chunk (src/kv_disk_cache.zig:320-440): the first `need` stored positions of every layer in
+ * the file go to positions [pos0, pos0 + need) of the cache's buffers.  A chunk holding more positions than `need` is
+ * sliced down; fewer positions, a missing key of a present layer, another rank, geometry or dtype: QB200_ERR_BAD_SHAPE
+ * (a corrupt chunk -- nothing of the file is trusted then; the caller resets the cache and prefills).  Synchronous. */
+QB200_API int qb200_kv_chunk_restore(const char* path, const qb200_kv_layer* layers, int n_layers, int64_t pos0, int64_t need,
+                                     qb200_stream s);
+
 #ifdef __cplusplus
 }
 #endif

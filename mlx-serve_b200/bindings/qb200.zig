@@ -89,3 +89,9 @@ pub fn check(ret: c_int) !void {
     if (ret == 1) return error.Qb200Declined;
     if (ret != 0) return error.Qb200Error;
 }
+
+// chunk files of the quantized KV cache: the slice writes and reads of kv_disk_cache.zig (appendCommit's chunk write,
+// src/kv_disk_cache.zig:1062-1074; restoreKvInto, :320-440).  k_q.data == null: the layer keeps no KV cache.
+pub const KvLayer = extern struct { k_q: Tensor, k_scales: Tensor, k_biases: Tensor, v_q: Tensor, v_scales: Tensor, v_biases: Tensor };
+pub extern "c" fn qb200_kv_chunk_save(path: [*:0]const u8, layers: [*]const KvLayer, n_layers: c_int, pos0: i64, pos1: i64, s: Stream) c_int;
+pub extern "c" fn qb200_kv_chunk_restore(path: [*:0]const u8, layers: [*]const KvLayer, n_layers: c_int, pos0: i64, need: i64, s: Stream) c_int;

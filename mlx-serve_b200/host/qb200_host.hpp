@@ -11,6 +11,7 @@
 //   moeSortByExpert (argsort chain of moeMLP2) src/transformer.zig:14961-15006
 //   quantAttentionBatched (per-slot caches)  src/transformer.zig:9742-9792, :10165-10249
 //   rmsNorm, addRmsNorm, ropeDynamic, computeGeglu, updateAffineBatched   src/transformer.zig:7770-7779, :9678, :8220-8243, :9738-9756
+//   saveChunk / restoreChunk (chunk files of the prefix cache's SSD tier)   src/kv_disk_cache.zig:320-440, :1062-1074
 //   Checkpoint (safetensors triples, f16 narrowing, geometry)   src/model.zig:3030-3061, :3241-3256; src/transformer.zig:16763-16790
 //   moeBlockEp (moeMLP2 over several GPUs; define QB200_HOST_WITH_EP and link libqb200_ep)   src/transformer.zig:14945-15140
 //
@@ -297,6 +298,28 @@ class Checkpoint {
  private:
   qb200_checkpoint* ck_ = nullptr;
 };
+
+// The chunk files of kv_disk_cache.zig's SSD tier (src/kv_disk_cache.zig:1-48): positions [pos0, pos1) of every
+// layer's six buffers as "l{i}.k" ... "l{i}.vb" in one safetensors file; an entry whose buffers are empty stands for
+// a layer without a KV cache.  restoreChunk slices an over-long chunk down to `need` positions and throws on a
+// corrupt one (the caller then resets the cache and prefills, as DiskTier's callers do).
+inline std::vector<qb200_kv_layer> chunkLayers(const KVCacheEntry* const* entries, int n) {
+  std::vector<qb200_kv_layer> v((size_t)n);
+  for (int i = 0; i < n; ++i) {
+    if (!entries[i]) { v[(size_t)i] = qb200_kv_layer{}; continue; }
+    const KVCacheEntry& e = *entries[i];
+    v[(size_t)i] = qb200_kv_layer{e.keys.q.t, e.keys.scales.t, e.keys.biases.t, e.values.q.t, e.values.scales.t, e.values.biases.t};
+  }
+  return v;
+}
+inline void saveChunk(const std::string& path, const KVCacheEntry* const* entries, int n, int64_t pos0, int64_t pos1, qb200_stream s) {
+  const std::vector<qb200_kv_layer> v = chunkLayers(entries, n);
+  check(qb200_kv_chunk_save(path.c_str(), v.data(), n, pos0, pos1, s));
+}
+inline void restoreChunk(const std::string& path, KVCacheEntry* const* entries, int n, int64_t pos0, int64_t need, qb200_stream s) {
+  const std::vector<qb200_kv_layer> v = chunkLayers(entries, n);
+  check(qb200_kv_chunk_restore(path.c_str(), v.data(), n, pos0, need, s));
+}
 
 #ifdef QB200_HOST_WITH_EP
 }  // namespace qb200h

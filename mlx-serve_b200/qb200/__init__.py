@@ -98,6 +98,8 @@ def lib():
         L.qb200_moe_sort_by_expert.argtypes = [TP] * 6 + [C.c_int, C.c_void_p]
         L.qb200_moe_sort_by_expert.restype = C.c_int
         L.qb200_debug_tc_reset.restype = None
+        L.qb200_kv_chunk_save.argtypes = [C.c_char_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p]
+        L.qb200_kv_chunk_restore.argtypes = [C.c_char_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p]
         L.qb200_checkpoint_open.argtypes = [C.POINTER(C.c_void_p), C.c_char_p]
         L.qb200_checkpoint_close.argtypes = [C.c_void_p]
         L.qb200_checkpoint_close.restype = None
@@ -450,6 +452,35 @@ def kv_append_seqs(k_triples, v_triples, dense_k, dense_v, offsets, bits, group_
 
 _Q2TORCH = {v: k for k, v in _TORCH2Q.items()}
 _Q2TORCH[UINT32] = torch.int32   # packed codes are carried in int32 tensors
+
+class KvLayer(C.Structure):
+    _fields_ = [(n, Tensor) for n in ("k_q", "k_scales", "k_biases", "v_q", "v_scales", "v_biases")]
+
+
+def _kv_layers(layers):
+    """layers: per layer either None (no KV cache) or (k_triple, v_triple) of capacity buffers [1, Hkv, cap, cols]."""
+    arr = (KvLayer * len(layers))()
+    for i, l in enumerate(layers):
+        if l is None:
+            continue
+        (kq, ks, kb), (vq, vs, vb) = l
+        arr[i].k_q, arr[i].k_scales, arr[i].k_biases = _packed(kq), desc(ks), desc(kb)
+        arr[i].v_q, arr[i].v_scales, arr[i].v_biases = _packed(vq), desc(vs), desc(vb)
+    return arr
+
+
+def kv_chunk_save(path, layers, pos0, pos1):
+    """Positions [pos0, pos1) of every layer's six buffers as one chunk file of the prefix cache's SSD tier
+    (src/kv_disk_cache.zig:1062-1074)."""
+    arr = _kv_layers(layers)
+    check(lib().qb200_kv_chunk_save(str(path).encode(), arr, len(layers), int(pos0), int(pos1), _stream()))
+
+
+def kv_chunk_restore(path, layers, pos0, need):
+    """The first ``need`` positions stored in a chunk file into positions [pos0, pos0 + need) of the cache
+    (restoreKvInto, src/kv_disk_cache.zig:320-440)."""
+    arr = _kv_layers(layers)
+    check(lib().qb200_kv_chunk_restore(str(path).encode(), arr, len(layers), int(pos0), int(need), _stream()))
 
 
 class Checkpoint:

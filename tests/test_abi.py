@@ -160,3 +160,22 @@ def test_kv_attention_refuses_an_empty_cache_view_before_any_launch(q):
     assert q.lib().qb200_kv_decode_attention(*common, C.c_void_p(0x1000), 1 << 20, None) == 2
     assert q.lib().qb200_kv_decode_attention_noalloc(*common, None) == 2
     assert b"no tokens" in q.lib().qb200_last_error()
+
+
+def test_kv_chunk_entries_validate_before_any_copy(q, tmp_path):
+    """Argument checks of the chunk save / restore entries run on the host: no path, an empty position range, a
+    buffer that is not [1, Hkv, cap, cols], positions beyond the capacity, a file that does not exist."""
+    L = q.lib()
+    layers = (q.KvLayer * 1)()
+    for name, dt, cols in (("k_q", q.UINT32, 16), ("k_scales", q.BFLOAT16, 2), ("k_biases", q.BFLOAT16, 2),
+                           ("v_q", q.UINT32, 16), ("v_scales", q.BFLOAT16, 2), ("v_biases", q.BFLOAT16, 2)):
+        setattr(layers[0], name, _t(q, dt, [1, 2, 64, cols]))
+    path = str(tmp_path / "c.safetensors").encode()
+    assert L.qb200_kv_chunk_save(None, layers, 1, 0, 8, None) == 5
+    assert L.qb200_kv_chunk_save(path, layers, 1, 8, 8, None) == 2
+    assert L.qb200_kv_chunk_save(path, layers, 1, 0, 65, None) == 2      # beyond the capacity
+    layers[0].k_scales = _t(q, q.BFLOAT16, [2, 64, 2])
+    assert L.qb200_kv_chunk_save(path, layers, 1, 0, 8, None) == 2      # not a 4-D capacity buffer
+    assert L.qb200_kv_chunk_restore(path, layers, 1, 0, 0, None) == 2
+    assert L.qb200_kv_chunk_restore(path, layers, 1, 0, 8, None) != 0                 # no such file
+    assert not os.path.exists(path.decode())
