@@ -344,6 +344,16 @@ QB200_API int qb200_kv_append_seqs(qb200_tensor* const* k_q, qb200_tensor* const
                                    qb200_tensor* const* v_q, qb200_tensor* const* v_scales, qb200_tensor* const* v_biases,
                                    const qb200_tensor* dense_k, const qb200_tensor* dense_v, const int64_t* offsets, int num_seqs,
                                    int bits, int group_size, qb200_stream s);
+/* The two steps before the attention of a batched decode tick as one launch: mlx_fast_rope_dynamic on the queries and
+ * on the new keys (src/transformer.zig:9678, :9735; non-traditional pairing, position offsets[n] for sequence n), then
+ * the cache update above with the rotated keys.  q [num_seqs, Hq, 1, D] is rotated in place; dense_k is read only (its
+ * rotated values go to the cache, rounded to bf16 first, so the cache holds exactly what qb200_rope followed by
+ * qb200_kv_append_seqs would have written).  dims / 2 must be a multiple of the values per packed word. */
+QB200_API int qb200_rope_kv_append_seqs(qb200_tensor* q, int dims, float base, float scale, qb200_tensor* const* k_q,
+                                        qb200_tensor* const* k_scales, qb200_tensor* const* k_biases, qb200_tensor* const* v_q,
+                                        qb200_tensor* const* v_scales, qb200_tensor* const* v_biases, const qb200_tensor* dense_k,
+                                        const qb200_tensor* dense_v, const int64_t* offsets, int num_seqs, int bits, int group_size,
+                                        qb200_stream s);
 
 /* ==== checkpoint -> device loader: MLX-format quantized safetensors (host side; the device layout is the file's) ==== */
 

@@ -95,3 +95,6 @@ pub fn check(ret: c_int) !void {
 pub const KvLayer = extern struct { k_q: Tensor, k_scales: Tensor, k_biases: Tensor, v_q: Tensor, v_scales: Tensor, v_biases: Tensor };
 pub extern "c" fn qb200_kv_chunk_save(path: [*:0]const u8, layers: [*]const KvLayer, n_layers: c_int, pos0: i64, pos1: i64, s: Stream) c_int;
 pub extern "c" fn qb200_kv_chunk_restore(path: [*:0]const u8, layers: [*]const KvLayer, n_layers: c_int, pos0: i64, need: i64, s: Stream) c_int;
+
+// mlx_fast_rope_dynamic on q and k followed by the per-slot updateAffine (src/transformer.zig:9678, :9735, :9738-9756): one launch
+pub extern "c" fn qb200_rope_kv_append_seqs(q: *Tensor, dims: c_int, base: f32, scale: f32, k_q: [*]const *Tensor, k_scales: [*]const *Tensor, k_biases: [*]const *Tensor, v_q: [*]const *Tensor, v_scales: [*]const *Tensor, v_biases: [*]const *Tensor, dense_k: *const Tensor, dense_v: *const Tensor, offsets: [*]const i64, num_seqs: c_int, bits: c_int, group_size: c_int, s: Stream) c_int;

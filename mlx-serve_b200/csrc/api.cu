@@ -1133,10 +1133,12 @@ QB200_API int qb200_swiglu(qb200_tensor* res, const qb200_tensor* gate, const qb
   return QB200_OK;
 }
 
-QB200_API int qb200_kv_append_seqs(qb200_tensor* const* k_q, qb200_tensor* const* k_scales, qb200_tensor* const* k_biases,
-                                   qb200_tensor* const* v_q, qb200_tensor* const* v_scales, qb200_tensor* const* v_biases,
-                                   const qb200_tensor* dense_k, const qb200_tensor* dense_v, const int64_t* offsets, int num_seqs,
-                                   int bits, int group_size, qb200_stream s) {
+// q_rope != NULL: the rope form (K rotated on its way into the cache, the queries in place, both at position offsets[n])
+static int kv_append_seqs_impl(qb200_tensor* q_rope, int rope_dims, float rope_base, float rope_scale,
+                               qb200_tensor* const* k_q, qb200_tensor* const* k_scales, qb200_tensor* const* k_biases,
+                               qb200_tensor* const* v_q, qb200_tensor* const* v_scales, qb200_tensor* const* v_biases,
+                               const qb200_tensor* dense_k, const qb200_tensor* dense_v, const int64_t* offsets, int num_seqs,
+                               int bits, int group_size, qb200_stream s) {
   int gs, nb, st;
   qb200_optional_int og = {group_size, true}, ob = {bits, true};
   if ((st = resolve_mode("affine", og, ob, &gs, &nb))) return st;
@@ -1187,9 +1189,43 @@ QB200_API int qb200_kv_append_seqs(qb200_tensor* const* k_q, qb200_tensor* const
     a.dense[kv] = (const uint16_t*)dn[kv]->data; a.dsn[kv] = dn[kv]->stride[0]; a.dsh[kv] = dn[kv]->stride[1]; a.d[kv] = (int)D[kv];
   }
   a.n = (int)N; a.heads = (int)Hkv; a.gs = gs; a.bits = nb;
+  std::vector<int> pos;
+  if (q_rope) {
+    if ((st = check_tensor(q_rope, "q", 4))) return st;
+    if (q_rope->ndim != 4 || q_rope->dtype != QB200_BFLOAT16 || q_rope->shape[0] != N || q_rope->shape[2] != 1 || q_rope->shape[3] != D[0] ||
+        q_rope->stride[3] != 1 || dense_k->stride[3] != 1)
+      return fail(QB200_ERR_BAD_SHAPE, "rope_kv_append_seqs: q must be bf16 [num_seqs, Hq, 1, D] with K's head dim, rows contiguous");
+    if (rope_dims <= 0 || rope_dims % 2 != 0 || rope_dims > D[0] || (rope_dims / 2) % vpw != 0 || !(rope_base > 0.f))
+      return fail(QB200_ERR_UNSUPPORTED, "rope_kv_append_seqs: dims must be even, at most D, with dims / 2 a multiple of the values per packed word");
+    for (int64_t n = 0; n < N; ++n) {
+      if (offsets[n] > 0x7fffffff) return fail(QB200_ERR_BAD_SHAPE, "rope_kv_append_seqs: position out of range");
+      pos.push_back((int)offsets[n]);
+    }
+    a.pos = pos.data();
+    a.rq = (uint16_t*)q_rope->data; a.qsn = q_rope->stride[0]; a.qsh = q_rope->stride[1]; a.q_heads = (int)q_rope->shape[1];
+    a.rope_dims = rope_dims; a.rope_base = rope_base; a.rope_scale = rope_scale;
+  }
   const cudaError_t e = launch_kv_append_seqs(a, (cudaStream_t)s);
   if (e != cudaSuccess) return cuda_fail(e, "kv_append_seqs");
   return QB200_OK;
+}
+
+QB200_API int qb200_kv_append_seqs(qb200_tensor* const* k_q, qb200_tensor* const* k_scales, qb200_tensor* const* k_biases,
+                                   qb200_tensor* const* v_q, qb200_tensor* const* v_scales, qb200_tensor* const* v_biases,
+                                   const qb200_tensor* dense_k, const qb200_tensor* dense_v, const int64_t* offsets, int num_seqs,
+                                   int bits, int group_size, qb200_stream s) {
+  return kv_append_seqs_impl(nullptr, 0, 0.f, 1.f, k_q, k_scales, k_biases, v_q, v_scales, v_biases, dense_k, dense_v, offsets, num_seqs, bits,
+                             group_size, s);
+}
+
+QB200_API int qb200_rope_kv_append_seqs(qb200_tensor* q, int dims, float base, float scale, qb200_tensor* const* k_q,
+                                        qb200_tensor* const* k_scales, qb200_tensor* const* k_biases, qb200_tensor* const* v_q,
+                                        qb200_tensor* const* v_scales, qb200_tensor* const* v_biases, const qb200_tensor* dense_k,
+                                        const qb200_tensor* dense_v, const int64_t* offsets, int num_seqs, int bits, int group_size,
+                                        qb200_stream s) {
+  if (!q) return fail(QB200_ERR_BAD_ARG, "rope_kv_append_seqs: q is required");
+  return kv_append_seqs_impl(q, dims, base, scale, k_q, k_scales, k_biases, v_q, v_scales, v_biases, dense_k, dense_v, offsets, num_seqs, bits,
+                             group_size, s);
 }
 
 }  // extern "C"

@@ -82,6 +82,15 @@ __global__ void __launch_bounds__(1024) rms_norm_kernel(const uint16_t* a, const
   }
 }
 
+// The rotation of one pair: angle = scale * position * base^(-i / half); products and sums as separate fp32 operations
+// (no contraction), so that every kernel that rotates gives the same bits.
+__device__ __forceinline__ void rope_sincos(int pos, int i, int half, float log2_base, float scale, float* sn, float* c) {
+  const float theta = __fmul_rn(__fmul_rn(scale, (float)pos), exp2f(__fmul_rn(-__fdiv_rn((float)i, (float)half), log2_base)));
+  sincosf(theta, sn, c);
+}
+__device__ __forceinline__ float rope_lo(float x1, float x2, float sn, float c) { return __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn)); }
+__device__ __forceinline__ float rope_hi(float x1, float x2, float sn, float c) { return __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, c)); }
+
 // Rotary embedding, non-traditional pairing (i, i + dims/2), one position per sequence (mlx_fast_rope_dynamic).
 // x [n, heads, 1, d] with strides (sn, sh); in place when out == x.  One thread per pair.
 __global__ void __launch_bounds__(256) rope_kernel(const uint16_t* x, uint16_t* out, const int32_t* offsets, int64_t n, int heads,
@@ -97,12 +106,11 @@ __global__ void __launch_bounds__(256) rope_kernel(const uint16_t* x, uint16_t* 
   const uint16_t* xr = x + s * xsn + (int64_t)h * xsh;
   uint16_t* o = out + s * osn + (int64_t)h * osh;
   if (i < half) {
-    const float theta = scale * (float)offsets[s] * exp2f(-((float)i / (float)half) * log2_base);
     float sn, c;
-    sincosf(theta, &sn, &c);
+    rope_sincos(offsets[s], i, half, log2_base, scale, &sn, &c);
     const float x1 = bf16_bits_to_f32(xr[i]), x2 = bf16_bits_to_f32(xr[i + half]);
-    o[i] = f32_to_bf16_bits(x1 * c - x2 * sn);
-    o[i + half] = f32_to_bf16_bits(x1 * sn + x2 * c);
+    o[i] = f32_to_bf16_bits(rope_lo(x1, x2, sn, c));
+    o[i + half] = f32_to_bf16_bits(rope_hi(x1, x2, sn, c));
   } else if (out != x || osn != xsn || osh != xsh) {
     const int e = dims + 2 * (i - half);
     o[e] = xr[e];
@@ -131,21 +139,46 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const uint16_t* gate, const
 struct AppendSeq {
   uint32_t* q[2]; uint16_t* s[2]; uint16_t* b[2];   // [K, V]: the token row of head 0
   int64_t q_head[2], sb_head[2];                    // head strides in elements
+  int pos;                                          // position of the new token (the rotary angle's factor)
 };
 struct AppendTable { AppendSeq s[kMaxSeqPtrs]; };
 struct AppendArgs {
   const uint16_t* dense[2];       // K, V rows [n, heads, 1, d]
   int64_t dsn[2], dsh[2];
   int n, heads, d[2], gs;
+  // ROPE form: the rotary embedding of K happens on the way into the cache, and the same launch rotates the
+  // queries [n, q_heads, 1, d[0]] in place (mlx_fast_rope_dynamic on q and k, then updateAffine: one launch for both)
+  uint16_t* rq; int64_t qsn, qsh; int q_heads;
+  int dims; float log2_base, scale;
 };
 
-template <int BITS>
+template <int BITS, bool ROPE>
 __global__ void __launch_bounds__(256) kv_append_seqs_kernel(const __grid_constant__ AppendArgs a, const __grid_constant__ AppendTable tab) {
   constexpr int VPW = 32 / BITS;
   // thread -> (which of K / V, sequence, head, packed word); the threads of a group are adjacent lanes
   const int wpr0 = a.d[0] / VPW, wpr1 = a.d[1] / VPW;
   const int64_t n0 = (int64_t)a.n * a.heads * wpr0, total = n0 + (int64_t)a.n * a.heads * wpr1;
   int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if constexpr (ROPE) {
+    // the blocks behind the quantiser's rotate the queries: one thread per pair (whole blocks, so no warp is mixed)
+    const int64_t qblk0 = (total + blockDim.x - 1) / blockDim.x;
+    if ((int64_t)blockIdx.x >= qblk0) {
+      const int half = a.dims / 2, per_head = a.d[0] / 2;
+      const int64_t qi = ((int64_t)blockIdx.x - qblk0) * blockDim.x + threadIdx.x;
+      if (qi >= (int64_t)a.n * a.q_heads * per_head) return;
+      const int i = (int)(qi % per_head);
+      const int64_t hh = qi / per_head;
+      const int h = (int)(hh % a.q_heads), sq = (int)(hh / a.q_heads);
+      if (i >= half) return;   // pass-through elements stay where they are (in place)
+      uint16_t* xr = a.rq + (int64_t)sq * a.qsn + (int64_t)h * a.qsh;
+      float sn, c;
+      rope_sincos(tab.s[sq].pos, i, half, a.log2_base, a.scale, &sn, &c);
+      const float x1 = bf16_bits_to_f32(xr[i]), x2 = bf16_bits_to_f32(xr[i + half]);
+      xr[i] = f32_to_bf16_bits(rope_lo(x1, x2, sn, c));
+      xr[i + half] = f32_to_bf16_bits(rope_hi(x1, x2, sn, c));
+      return;
+    }
+  }
   const bool live = idx < total;
   if (!live) idx = total - 1;   // keep the warp converged for the shuffles
   const int kv = idx >= n0 ? 1 : 0;
@@ -159,6 +192,23 @@ __global__ void __launch_bounds__(256) kv_append_seqs_kernel(const __grid_consta
   float v[VPW];
 #pragma unroll
   for (int k = 0; k < VPW; ++k) v[k] = bf16_bits_to_f32(xr[k]);
+  if constexpr (ROPE) {
+    // K: this word's values rotated with their partners half a rotary width away (a word lies on one side of the
+    // pairing: dims / 2 is a multiple of the values per word), rounded to bf16 as the separate rope would store them
+    const int e0 = wi * VPW, half = a.dims / 2;
+    if (kv == 0 && e0 < a.dims) {
+      const bool low = e0 < half;
+      const uint16_t* pr = low ? xr + half : xr - half;
+#pragma unroll
+      for (int k = 0; k < VPW; ++k) {
+        const float other = bf16_bits_to_f32(pr[k]);
+        float sn, c;
+        rope_sincos(tab.s[s].pos, (low ? e0 : e0 - half) + k, half, a.log2_base, a.scale, &sn, &c);
+        const float r = low ? rope_lo(v[k], other, sn, c) : rope_hi(other, v[k], sn, c);
+        v[k] = bf16_bits_to_f32(f32_to_bf16_bits(r));
+      }
+    }
+  }
   float xmin = v[0], xmax = v[0];
 #pragma unroll
   for (int k = 1; k < VPW; ++k) { xmin = fminf(xmin, v[k]); xmax = fmaxf(xmax, v[k]); }
@@ -249,6 +299,7 @@ cudaError_t launch_kv_append_seqs(const KvAppendSeqsArgs& h, cudaStream_t st) {
       for (int kv = 0; kv < 2; ++kv) {
         tab.s[i].q[kv] = h.q[kv][s0 + i]; tab.s[i].s[kv] = h.s[kv][s0 + i]; tab.s[i].b[kv] = h.b[kv][s0 + i];
         tab.s[i].q_head[kv] = h.q_head[kv][s0 + i]; tab.s[i].sb_head[kv] = h.sb_head[kv][s0 + i];
+        tab.s[i].pos = h.pos ? h.pos[s0 + i] : 0;
       }
     AppendArgs a;
     for (int kv = 0; kv < 2; ++kv) {
@@ -256,11 +307,20 @@ cudaError_t launch_kv_append_seqs(const KvAppendSeqsArgs& h, cudaStream_t st) {
       a.dsn[kv] = h.dsn[kv]; a.dsh[kv] = h.dsh[kv]; a.d[kv] = h.d[kv];
     }
     a.n = nb; a.heads = h.heads; a.gs = h.gs;
+    a.rq = h.rq ? h.rq + (int64_t)s0 * h.qsn : nullptr; a.qsn = h.qsn; a.qsh = h.qsh; a.q_heads = h.q_heads;
+    a.dims = h.rope_dims; a.log2_base = h.rope_dims > 0 ? log2f(h.rope_base) : 0.f; a.scale = h.rope_scale;
     const int vpw = 32 / h.bits;
     const int64_t total = (int64_t)nb * h.heads * (h.d[0] / vpw + h.d[1] / vpw);
-    const unsigned blocks = (unsigned)((total + 255) / 256);
-    const cudaError_t e = h.bits == 4 ? launch_kernel(kv_append_seqs_kernel<4>, dim3(blocks), dim3(256), 0, st, a, tab)
-                                      : launch_kernel(kv_append_seqs_kernel<8>, dim3(blocks), dim3(256), 0, st, a, tab);
+    unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaError_t e;
+    if (h.rope_dims > 0) {
+      blocks += (unsigned)(((int64_t)nb * h.q_heads * (h.d[0] / 2) + 255) / 256);   // the blocks that rotate the queries
+      e = h.bits == 4 ? launch_kernel(kv_append_seqs_kernel<4, true>, dim3(blocks), dim3(256), 0, st, a, tab)
+                      : launch_kernel(kv_append_seqs_kernel<8, true>, dim3(blocks), dim3(256), 0, st, a, tab);
+    } else {
+      e = h.bits == 4 ? launch_kernel(kv_append_seqs_kernel<4, false>, dim3(blocks), dim3(256), 0, st, a, tab)
+                      : launch_kernel(kv_append_seqs_kernel<8, false>, dim3(blocks), dim3(256), 0, st, a, tab);
+    }
     if (e != cudaSuccess) return e;
   }
   return cudaSuccess;

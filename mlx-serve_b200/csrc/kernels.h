@@ -168,6 +168,11 @@ struct KvAppendSeqsArgs {     // host side: [K, V] lists over the sequences, tok
   const int64_t* q_head[2]; const int64_t* sb_head[2];
   const uint16_t* dense[2]; int64_t dsn[2], dsh[2];
   int n, heads, d[2], gs, bits;
+  // rope form (rope_dims > 0): K is rotated on its way into the cache and the queries rq [n, q_heads, 1, d[0]] in place,
+  // each sequence at position pos[i]
+  const int* pos = nullptr;
+  uint16_t* rq = nullptr; int64_t qsn = 0, qsh = 0; int q_heads = 0;
+  int rope_dims = 0; float rope_base = 0.f, rope_scale = 1.f;
 };
 cudaError_t launch_kv_append_seqs(const KvAppendSeqsArgs& a, cudaStream_t st);
 

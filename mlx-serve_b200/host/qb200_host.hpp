@@ -242,6 +242,26 @@ inline void updateAffineBatched(KVCacheEntry* const* entries, int slots, const A
   for (int n = 0; n < slots; ++n) entries[n]->offset += 1;
 }
 
+// The same with the rotary embedding of the decode step folded in (mlx_fast_rope_dynamic on q and k, src/transformer.zig:9678,
+// :9735, then the per-slot update): q [slots, Hq, 1, D] is rotated in place, k_new on its way into the caches, every
+// slot at its own offset.
+inline void ropeUpdateAffineBatched(Array& q, int dims, float base, float scale, KVCacheEntry* const* entries, int slots,
+                                    const Array& k_new, const Array& v_new, qb200_stream s) {
+  if (slots < 1 || slots > 4096) throw Error(2, "ropeUpdateAffineBatched: 1..4096 slots");
+  std::vector<qb200_tensor*> p(6 * (size_t)slots);
+  std::vector<int64_t> offs((size_t)slots);
+  for (int n = 0; n < slots; ++n) {
+    KVCacheEntry& e = *entries[n];
+    if (e.offset + 1 > e.capacity()) throw Error(2, "ropeUpdateAffineBatched: capacity exceeded; grow the cache first");
+    p[0 * slots + n] = &e.keys.q.t; p[1 * slots + n] = &e.keys.scales.t; p[2 * slots + n] = &e.keys.biases.t;
+    p[3 * slots + n] = &e.values.q.t; p[4 * slots + n] = &e.values.scales.t; p[5 * slots + n] = &e.values.biases.t;
+    offs[n] = e.offset;
+  }
+  check(qb200_rope_kv_append_seqs(&q.t, dims, base, scale, &p[0], &p[slots], &p[2 * slots], &p[3 * slots], &p[4 * slots], &p[5 * slots],
+                                  &k_new.t, &v_new.t, offs.data(), slots, entries[0]->keys.bits, entries[0]->keys.group_size, s));
+  for (int n = 0; n < slots; ++n) entries[n]->offset += 1;
+}
+
 // rmsNorm / rmsNormEps (src/transformer.zig:7770-7779) and the mlx_add that precedes the post-attention and the next
 // layer's input norm (:9836-9843, :9856-9859) fused with it.
 inline void rmsNorm(Array& res, const Array& x, const Array& weight, float eps, qb200_stream s) {

@@ -121,6 +121,8 @@ def lib():
         L.qb200_rope.argtypes = [TP, TP, C.c_int, C.c_bool, OptFloat, C.c_float, TP, TP, C.c_void_p]
         L.qb200_swiglu.argtypes = [TP, TP, TP, C.c_void_p]
         L.qb200_kv_append_seqs.argtypes = [C.POINTER(TP)] * 6 + [TP, TP, C.POINTER(C.c_int64), C.c_int, C.c_int, C.c_int, C.c_void_p]
+        L.qb200_rope_kv_append_seqs.argtypes = [TP, C.c_int, C.c_float, C.c_float] + L.qb200_kv_append_seqs.argtypes
+        L.qb200_rope_kv_append_seqs.restype = C.c_int
         for name in ("qb200_rms_norm", "qb200_add_rms_norm", "qb200_rope", "qb200_swiglu", "qb200_kv_append_seqs"):
             getattr(L, name).restype = C.c_int
         L.qb200_kv_decode_attention_noalloc.argtypes = [TP, TP, TP, TP, TP, TP, TP, TP, C.c_int, C.c_int, C.c_float,
@@ -432,9 +434,11 @@ def swiglu(gate, up, out=None):
     return out
 
 
-def kv_append_seqs(k_triples, v_triples, dense_k, dense_v, offsets, bits, group_size):
+def kv_append_seqs(k_triples, v_triples, dense_k, dense_v, offsets, bits, group_size, rope_q=None, rope_dims=0, rope_base=10000.0,
+                   rope_scale=1.0):
     """One new token per sequence into per-sequence packed caches (the per-slot cache update of the batched decode,
-    src/transformer.zig:9738-9756): k_triples[n] / v_triples[n] are the capacity buffers [1, Hkv, cap_n, .]."""
+    src/transformer.zig:9738-9756): k_triples[n] / v_triples[n] are the capacity buffers [1, Hkv, cap_n, .].
+    With ``rope_q`` the same launch rotates the queries in place and the keys on their way into the cache."""
     n = len(k_triples)
     TP = C.POINTER(Tensor)
     keep = []
@@ -446,6 +450,11 @@ def kv_append_seqs(k_triples, v_triples, dense_k, dense_v, offsets, bits, group_
     lists = [arr([t[0] for t in k_triples], True), arr([t[1] for t in k_triples], False), arr([t[2] for t in k_triples], False),
              arr([t[0] for t in v_triples], True), arr([t[1] for t in v_triples], False), arr([t[2] for t in v_triples], False)]
     offs = (C.c_int64 * n)(*[int(o) for o in offsets])
+    if rope_q is not None:
+        check(lib().qb200_rope_kv_append_seqs(C.byref(desc(rope_q)), int(rope_dims), C.c_float(rope_base), C.c_float(rope_scale), *lists,
+                                              C.byref(desc(dense_k)), C.byref(desc(dense_v)), offs, n, int(bits), int(group_size),
+                                              _stream()))
+        return
     check(lib().qb200_kv_append_seqs(*lists, C.byref(desc(dense_k)), C.byref(desc(dense_v)), offs, n, int(bits), int(group_size),
                                      _stream()))
 

@@ -109,6 +109,46 @@ def test_kv_append_into_per_sequence_caches(bits):
             untouched[0, :, offs[n]] = 7
             assert bool((untouched == 7).all())
 
+@pytest.mark.parametrize("bits,D,dims", [(4, 128, 128), (8, 128, 128), (4, 128, 64), (8, 64, 64)])
+def test_rope_fused_into_the_cache_update_equals_the_two_calls(bits, D, dims):
+    """qb200_rope_kv_append_seqs: the queries rotated in place and the keys on their way into the cache, one launch --
+    bit for bit what qb200_rope on q and k followed by qb200_kv_append_seqs writes (the dense k stays as it was)."""
+    import qb200
+    rng = np.random.default_rng(bits + D + dims)
+    N, Hq, Hkv = 6, 8, 2
+    qkv = _dev(rand_bf16(rng, (N, Hq + 2 * Hkv, D)))          # one fused-projection buffer, as the decode step has it
+    q4, k4, v4 = qkv[:, :Hq].unsqueeze(2), qkv[:, Hq:Hq + Hkv].unsqueeze(2), qkv[:, Hq + Hkv:].unsqueeze(2)
+    caps = [256 * int(c) for c in rng.integers(1, 3, N)]
+    offs = [int(rng.integers(0, c)) for c in caps]
+    offs[0], offs[1] = 0, caps[1] - 1
+
+    def fresh():
+        kt, vt = [], []
+        for n in range(N):
+            mk = lambda last, dt: torch.full((1, Hkv, caps[n], last), 7, dtype=dt, device="cuda")
+            kt.append([mk(D * bits // 32, torch.int32), mk(D // 64, torch.bfloat16), mk(D // 64, torch.bfloat16)])
+            vt.append([mk(D * bits // 32, torch.int32), mk(D // 64, torch.bfloat16), mk(D // 64, torch.bfloat16)])
+        return kt, vt
+    # the two calls
+    two = qkv.clone()
+    tq, tk, tv = two[:, :Hq].unsqueeze(2), two[:, Hq:Hq + Hkv].unsqueeze(2), two[:, Hq + Hkv:].unsqueeze(2)
+    pos = torch.tensor(offs, dtype=torch.int32, device="cuda")
+    qk = two[:, :Hq + Hkv].unsqueeze(2)
+    qb200.rope(qk, dims, 500000.0, 1.0, pos, out=qk)
+    kt2, vt2 = fresh()
+    qb200.kv_append_seqs(kt2, vt2, tk, tv, offs, bits, 64)
+    # one call
+    one = qkv.clone()
+    oq, ok_, ov = one[:, :Hq].unsqueeze(2), one[:, Hq:Hq + Hkv].unsqueeze(2), one[:, Hq + Hkv:].unsqueeze(2)
+    kt1, vt1 = fresh()
+    qb200.kv_append_seqs(kt1, vt1, ok_, ov, offs, bits, 64, rope_q=oq, rope_dims=dims, rope_base=500000.0)
+    torch.cuda.synchronize()
+    assert torch.equal(oq.view(torch.int16), tq.view(torch.int16)), "queries"
+    assert torch.equal(ok_.view(torch.int16), qkv[:, Hq:Hq + Hkv].unsqueeze(2).view(torch.int16)), "the dense keys are read only"
+    for a, b in zip(kt1 + vt1, kt2 + vt2):
+        for x, y in zip(a, b):
+            assert torch.equal(x.view(torch.int16) if x.dtype == torch.bfloat16 else x, y.view(torch.int16) if y.dtype == torch.bfloat16 else y)
+
 
 def test_one_layer_tick_against_the_oracle_chain():
     """A Llama-shaped layer tick (hidden 1024, 8 query / 2 KV heads of 128, MLP 2816, 4-bit g64 weights, 4-bit packed
