@@ -336,6 +336,16 @@ QB200_API int qb200_rope(qb200_tensor* res, const qb200_tensor* x, int dims, boo
  * of the reference's kernel (src/transformer.zig:19842-19851).  The first call on a device uploads the 128 KiB sigmoid
  * table (call once before capturing a graph). */
 QB200_API int qb200_swiglu(qb200_tensor* res, const qb200_tensor* gate, const qb200_tensor* up, qb200_stream s);
+/* The rotation of the TurboQuant cache schemes (src/kv_quant.zig:164-403; quantizeTurbo = rotate then mlx_quantize,
+ * dequantizeTurbo = mlx_dequantize then rotate): res = x @ R along the last axis, R = diag(sg) H diag(sg) / sqrt(D) with H
+ * the Sylvester Hadamard matrix and sg the +-1 vector of the reference's generator seeded with `seed` (TurboState uses
+ * 0x9E37 ^ layer for K and 0x85EB ^ layer for V).  R is symmetric and orthogonal, so the same call rotates back.
+ * bf16, D a power of two in [32, 1024] (the reference refuses other head dims); res may be x.  Computed as a fast
+ * Walsh-Hadamard transform in fp32, scaled by bf16(1 / sqrt(D)) -- the magnitude of every entry of the reference's bf16
+ * matrix -- and rounded once; the reference's mlx_matmul sums the same products in another order. */
+QB200_API int qb200_turbo_rotate(qb200_tensor* res, const qb200_tensor* x, uint64_t seed, qb200_stream s);
+/* The sign vector itself (bit e set = -1), for hosts that build R as a matrix. */
+QB200_API int qb200_turbo_signs(uint64_t seed, int n, uint32_t* bits);
 /* One new token per sequence into per-sequence packed caches: the per-slot KVCache.update loop of the batched decode
  * (src/transformer.zig:9738-9756; updateAffine, :3224-3337) as one launch for K and V of every sequence.
  * k_q[n] ... v_biases[n]: the capacity buffers [1, Hkv, cap_n, last] of sequence n; dense_k / dense_v

@@ -98,3 +98,8 @@ pub extern "c" fn qb200_kv_chunk_restore(path: [*:0]const u8, layers: [*]const K
 
 // mlx_fast_rope_dynamic on q and k followed by the per-slot updateAffine (src/transformer.zig:9678, :9735, :9738-9756): one launch
 pub extern "c" fn qb200_rope_kv_append_seqs(q: *Tensor, dims: c_int, base: f32, scale: f32, k_q: [*]const *Tensor, k_scales: [*]const *Tensor, k_biases: [*]const *Tensor, v_q: [*]const *Tensor, v_scales: [*]const *Tensor, v_biases: [*]const *Tensor, dense_k: *const Tensor, dense_v: *const Tensor, offsets: [*]const i64, num_seqs: c_int, bits: c_int, group_size: c_int, s: Stream) c_int;
+
+// rotateLastDim of the TurboQuant schemes (src/kv_quant.zig:362-372; quantizeTurbo / dequantizeTurbo around it): res = x @ R with
+// TurboState's Hadamard rotation of the given seed (0x9E37 ^ layer for K, 0x85EB ^ layer for V) instead of an mlx_matmul by the [D, D] matrix
+pub extern "c" fn qb200_turbo_rotate(res: *Tensor, x: *const Tensor, seed: u64, s: Stream) c_int;
+pub extern "c" fn qb200_turbo_signs(seed: u64, n: c_int, bits: [*]u32) c_int;

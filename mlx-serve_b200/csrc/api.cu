@@ -1118,6 +1118,39 @@ QB200_API int qb200_rope(qb200_tensor* res, const qb200_tensor* x, int dims, boo
   return QB200_OK;
 }
 
+
+// The +-1 vector of TurboState's cloneWithSignFlip (src/kv_quant.zig:318-330): a 64-bit LCG stepped once per entry,
+// bit 33 of the state picks the sign; bit e of the result set = -1.
+static void turbo_sign_bits(uint64_t seed, int n, uint32_t* bits) {
+  for (int i = 0; i < (n + 31) / 32; ++i) bits[i] = 0u;
+  uint64_t st = seed * 6364136223846793005ull;
+  for (int e = 0; e < n; ++e) {
+    st = st * 6364136223846793005ull + 1442695040888963407ull;
+    if ((st >> 33) & 1ull) bits[e >> 5] |= 1u << (e & 31);
+  }
+}
+
+QB200_API int qb200_turbo_signs(uint64_t seed, int n, uint32_t* bits) {
+  if (!bits || n <= 0 || n > 4096) return fail(QB200_ERR_BAD_ARG, "turbo_signs: 1..4096 entries");
+  turbo_sign_bits(seed, n, bits);
+  return QB200_OK;
+}
+
+QB200_API int qb200_turbo_rotate(qb200_tensor* res, const qb200_tensor* x, uint64_t seed, qb200_stream s) {
+  int st;
+  int64_t rows, d, ldx, r2, d2, ldo;
+  if ((st = row_view(x, "x", &rows, &d, &ldx)) || (st = row_view(res, "res", &r2, &d2, &ldo))) return st;
+  if (r2 != rows || d2 != d) return fail(QB200_ERR_BAD_SHAPE, "turbo_rotate: res must have x's shape");
+  if (d < 32 || d > 1024 || (d & (d - 1)) != 0)
+    return fail(QB200_ERR_UNSUPPORTED, "turbo_rotate: the last axis must be a power of two between 32 and 1024 (the reference refuses other head dims too)");
+  if (rows == 0) return QB200_OK;
+  uint32_t bits[32];
+  turbo_sign_bits(seed, (int)d, bits);
+  const cudaError_t e = launch_turbo_rotate((const uint16_t*)x->data, (uint16_t*)res->data, rows, (int)d, ldx, ldo, bits, (cudaStream_t)s);
+  if (e != cudaSuccess) return cuda_fail(e, "turbo_rotate");
+  return QB200_OK;
+}
+
 QB200_API int qb200_swiglu(qb200_tensor* res, const qb200_tensor* gate, const qb200_tensor* up, qb200_stream s) {
   int st;
   int64_t rows, d, ldg, r2, d2, ldu, ldo;

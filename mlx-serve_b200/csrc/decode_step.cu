@@ -243,6 +243,55 @@ __global__ void __launch_bounds__(256) kv_append_seqs_kernel(const __grid_consta
   }
 }
 
+
+// ---- the rotation of the TurboQuant cache schemes (src/kv_quant.zig:164-403): out = x @ R along the last axis with
+// R = diag(sg) H diag(sg) / sqrt(D), H the Sylvester Hadamard matrix and sg a +-1 vector -- symmetric and orthogonal, so
+// the same call rotates back.  The reference multiplies by the [D, D] bf16 matrix; every entry of it is +-r with
+// r = bf16(1 / sqrt(D)), so the product is r * sg[e] * sum_j H[e][j] * sg[j] * x[j]: a fast Walsh-Hadamard transform,
+// D log2 D additions per row instead of D^2 multiply-adds.  One warp per row, element e = j * 32 + lane: the low five
+// bits of e are the lane (shuffles), the rest stay in the lane's registers. ----
+struct TurboSigns { uint32_t bits[32]; };   // bit e of the vector: 1 = -1 (D <= 1024)
+
+template <int PER>   // values per lane: D / 32
+__global__ void __launch_bounds__(256) turbo_rotate_kernel(const uint16_t* x, uint16_t* out, int64_t rows, int64_t ldx, int64_t ldo,
+                                                           float r, const __grid_constant__ TurboSigns sg) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const uint16_t* xr = x + row * ldx;
+  float v[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const float f = bf16_bits_to_f32(xr[j * 32 + lane]);
+    v[j] = ((sg.bits[j] >> lane) & 1u) ? -f : f;
+  }
+#pragma unroll
+  for (int m = 1; m < 32; m <<= 1) {   // bits of the lane
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const float o = __shfl_xor_sync(0xffffffffu, v[j], m);
+      v[j] = (lane & m) ? __fsub_rn(o, v[j]) : __fadd_rn(v[j], o);
+    }
+  }
+#pragma unroll
+  for (int m = 1; m < PER; m <<= 1) {   // bits of the register index
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      if ((j & m) == 0) {
+        const float a = v[j], b = v[j | m];
+        v[j] = __fadd_rn(a, b);
+        v[j | m] = __fsub_rn(a, b);
+      }
+    }
+  }
+  uint16_t* orow = out + row * ldo;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const float y = __fmul_rn(v[j], r);
+    orow[j * 32 + lane] = f32_to_bf16_bits(((sg.bits[j] >> lane) & 1u) ? -y : y);
+  }
+}
+
 }  // namespace
 
 cudaError_t launch_rms_norm(const uint16_t* a, const uint16_t* b, const uint16_t* w, uint16_t* sum_out, uint16_t* norm_out,
@@ -324,6 +373,33 @@ cudaError_t launch_kv_append_seqs(const KvAppendSeqsArgs& h, cudaStream_t st) {
     if (e != cudaSuccess) return e;
   }
   return cudaSuccess;
+}
+
+// signs: bit e set = -1, the vector of TurboState's cloneWithSignFlip (src/kv_quant.zig:318-330)
+cudaError_t launch_turbo_rotate(const uint16_t* x, uint16_t* out, int64_t rows, int d, int64_t ldx, int64_t ldo, const uint32_t* signs,
+                                cudaStream_t st) {
+  if (rows <= 0) return cudaSuccess;
+  TurboSigns sg;
+  std::memset(&sg, 0, sizeof(sg));
+  for (int i = 0; i < d / 32; ++i) sg.bits[i] = signs[i];
+  // r = bf16(1 / sqrt(d)): the magnitude of every entry of the reference's bf16 matrix
+  float r = 1.0f / std::sqrt((float)d);
+  {
+    uint32_t u;
+    std::memcpy(&u, &r, 4);
+    u = (u + 0x7FFFu + ((u >> 16) & 1u)) & 0xFFFF0000u;   // round to nearest even at bf16 precision
+    std::memcpy(&r, &u, 4);
+  }
+  const dim3 grid((unsigned)((rows + 7) / 8)), block(256);
+  switch (d / 32) {
+    case 1: return launch_kernel(turbo_rotate_kernel<1>, grid, block, 0, st, x, out, rows, ldx, ldo, r, sg);
+    case 2: return launch_kernel(turbo_rotate_kernel<2>, grid, block, 0, st, x, out, rows, ldx, ldo, r, sg);
+    case 4: return launch_kernel(turbo_rotate_kernel<4>, grid, block, 0, st, x, out, rows, ldx, ldo, r, sg);
+    case 8: return launch_kernel(turbo_rotate_kernel<8>, grid, block, 0, st, x, out, rows, ldx, ldo, r, sg);
+    case 16: return launch_kernel(turbo_rotate_kernel<16>, grid, block, 0, st, x, out, rows, ldx, ldo, r, sg);
+    case 32: return launch_kernel(turbo_rotate_kernel<32>, grid, block, 0, st, x, out, rows, ldx, ldo, r, sg);
+    default: return cudaErrorInvalidValue;
+  }
 }
 
 }  // namespace qb

@@ -161,6 +161,8 @@ cudaError_t launch_rms_norm(const uint16_t* a, const uint16_t* b, const uint16_t
                             int64_t rows, int d, int64_t lda, int64_t ldb, int64_t lds, int64_t ldn, float eps, cudaStream_t st);
 cudaError_t launch_rope(const uint16_t* x, uint16_t* out, const int32_t* offsets, int64_t n, int heads, int d, int dims, float base,
                         float scale, int64_t xsn, int64_t xsh, int64_t osn, int64_t osh, cudaStream_t st);
+cudaError_t launch_turbo_rotate(const uint16_t* x, uint16_t* out, int64_t rows, int d, int64_t ldx, int64_t ldo, const uint32_t* signs,
+                                cudaStream_t st);
 cudaError_t launch_swiglu(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_t rows, int d, int64_t ldg, int64_t ldu,
                           int64_t ldo, cudaStream_t st);
 struct KvAppendSeqsArgs {     // host side: [K, V] lists over the sequences, token rows already resolved

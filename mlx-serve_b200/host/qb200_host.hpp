@@ -11,6 +11,7 @@
 //   moeSortByExpert (argsort chain of moeMLP2) src/transformer.zig:14961-15006
 //   quantAttentionBatched (per-slot caches)  src/transformer.zig:9742-9792, :10165-10249
 //   rmsNorm, addRmsNorm, ropeDynamic, computeGeglu, updateAffineBatched   src/transformer.zig:7770-7779, :9678, :8220-8243, :9738-9756
+//   rotateLastDim, quantizeTurbo, dequantizeTurbo   src/kv_quant.zig:362-403
 //   saveChunk / restoreChunk (chunk files of the prefix cache's SSD tier)   src/kv_disk_cache.zig:320-440, :1062-1074
 //   Checkpoint (safetensors triples, f16 narrowing, geometry)   src/model.zig:3030-3061, :3241-3256; src/transformer.zig:16763-16790
 //   moeBlockEp (moeMLP2 over several GPUs; define QB200_HOST_WITH_EP and link libqb200_ep)   src/transformer.zig:14945-15140
@@ -318,6 +319,18 @@ class Checkpoint {
  private:
   qb200_checkpoint* ck_ = nullptr;
 };
+
+// The TurboQuant cache schemes (src/kv_quant.zig:164-403): a Hadamard rotation of the last axis before the affine
+// quantiser and after the dequantiser; `seed` names the rotation (TurboState: 0x9E37 ^ layer for K, 0x85EB ^ layer for V).
+inline void rotateLastDim(Array& res, const Array& x, uint64_t seed, qb200_stream s) { check(qb200_turbo_rotate(&res.t, &x.t, seed, s)); }
+inline void quantizeTurbo(QuantizedKV& out, Array& rotated_scratch, const Array& x, uint64_t seed, qb200_stream s) {
+  rotateLastDim(rotated_scratch, x, seed, s);
+  quantizeAffine(out, rotated_scratch, s);
+}
+inline void dequantizeTurbo(Array& res, const QuantizedKV& kv, uint64_t seed, qb200_stream s) {
+  dequantizeAffine(res, kv, s);
+  rotateLastDim(res, res, seed, s);   // R is its own inverse
+}
 
 // The chunk files of kv_disk_cache.zig's SSD tier (src/kv_disk_cache.zig:1-48): positions [pos0, pos1) of every
 // layer's six buffers as "l{i}.k" ... "l{i}.vb" in one safetensors file; an entry whose buffers are empty stands for

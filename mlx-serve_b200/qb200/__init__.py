@@ -120,6 +120,10 @@ def lib():
         L.qb200_add_rms_norm.argtypes = [TP, TP, TP, TP, TP, C.c_float, C.c_void_p]
         L.qb200_rope.argtypes = [TP, TP, C.c_int, C.c_bool, OptFloat, C.c_float, TP, TP, C.c_void_p]
         L.qb200_swiglu.argtypes = [TP, TP, TP, C.c_void_p]
+        L.qb200_turbo_rotate.argtypes = [TP, TP, C.c_uint64, C.c_void_p]
+        L.qb200_turbo_rotate.restype = C.c_int
+        L.qb200_turbo_signs.argtypes = [C.c_uint64, C.c_int, C.POINTER(C.c_uint32)]
+        L.qb200_turbo_signs.restype = C.c_int
         L.qb200_kv_append_seqs.argtypes = [C.POINTER(TP)] * 6 + [TP, TP, C.POINTER(C.c_int64), C.c_int, C.c_int, C.c_int, C.c_void_p]
         L.qb200_rope_kv_append_seqs.argtypes = [TP, C.c_int, C.c_float, C.c_float] + L.qb200_kv_append_seqs.argtypes
         L.qb200_rope_kv_append_seqs.restype = C.c_int
@@ -424,6 +428,22 @@ def rope(x, dims, base, scale, offsets, out=None):
     check(lib().qb200_rope(C.byref(desc(out)), C.byref(desc(x)), int(dims), False, OptFloat(float(base), True), float(scale),
                            C.byref(desc(offsets)), C.byref(desc(None)), _stream()))
     return out
+
+
+def turbo_rotate(x, seed, out=None):
+    """x @ R along the last axis, R the Hadamard rotation of the TurboQuant schemes (src/kv_quant.zig:164-403;
+    seed 0x9E37 ^ layer for K, 0x85EB ^ layer for V).  R is its own inverse."""
+    if out is None:
+        out = torch.empty_like(x)
+    check(lib().qb200_turbo_rotate(C.byref(desc(out)), C.byref(desc(x)), int(seed), _stream()))
+    return out
+
+
+def turbo_signs(seed, n):
+    """The rotation's sign vector as a 0/1 array (1 = -1)."""
+    bits = (C.c_uint32 * ((n + 31) // 32))()
+    check(lib().qb200_turbo_signs(int(seed), int(n), bits))
+    return [(bits[e >> 5] >> (e & 31)) & 1 for e in range(n)]
 
 
 def swiglu(gate, up, out=None):

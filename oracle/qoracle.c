@@ -446,3 +446,42 @@ QO_API void qo_rope(const float* x, int64_t n, int64_t heads, int64_t d, int dim
     }
   }
 }
+
+/* ---- the rotation of the TurboQuant cache schemes (src/kv_quant.zig:164-403) ----
+ * R as TurboState builds it: the Sylvester Hadamard matrix H[N][N] (buildHadamardArray, :284-313) divided by sqrt(N) in
+ * fp32 and cast to bf16, then rows and columns multiplied by the +-1 vector of cloneWithSignFlip (:318-360: a 64-bit
+ * LCG, bit 33 of the state after every step picks the sign).  out = x @ R with fp32 accumulation in index order and one
+ * rounding to bf16 (rotateLastDim is an mlx_matmul on bf16 operands; its summation order is MLX's and is not pinned).
+ * signs (optional, N bytes): 1 where the vector is -1. */
+QO_API void qo_turbo_rotate(const float* x, int64_t rows, int n, uint64_t seed, float* out, unsigned char* signs_out) {
+  float* R = (float*)malloc((size_t)n * n * sizeof(float));
+  float* sg = (float*)malloc((size_t)n * sizeof(float));
+  R[0] = 1.0f;
+  for (int size = 1; size < n; size *= 2)
+    for (int r = 0; r < size; ++r)
+      for (int c = 0; c < size; ++c) {
+        const float tl = R[(size_t)r * n + c];
+        R[(size_t)r * n + (c + size)] = tl;
+        R[(size_t)(r + size) * n + c] = tl;
+        R[(size_t)(r + size) * n + (c + size)] = -tl;
+      }
+  const float inv = 1.0f / sqrtf((float)n);
+  uint64_t st = seed * 6364136223846793005ull;
+  for (int e = 0; e < n; ++e) {
+    st = st * 6364136223846793005ull + 1442695040888963407ull;
+    sg[e] = ((st >> 33) & 1ull) == 0 ? 1.0f : -1.0f;
+    if (signs_out) signs_out[e] = sg[e] < 0.0f;
+  }
+  for (int r = 0; r < n; ++r)
+    for (int c = 0; c < n; ++c)
+      R[(size_t)r * n + c] = bf16_to_f32(f32_to_bf16(R[(size_t)r * n + c] * inv)) * sg[r] * sg[c];
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < rows; ++i)
+    for (int c = 0; c < n; ++c) {
+      float acc = 0.0f;
+      for (int j = 0; j < n; ++j) acc += x[i * n + j] * R[(size_t)j * n + c];
+      out[i * n + c] = bf16_to_f32(f32_to_bf16(acc));
+    }
+  free(R);
+  free(sg);
+}

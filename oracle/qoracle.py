@@ -261,3 +261,14 @@ def rope(x, dims: int, base: float, scale: float, offsets, as_bf16: bool = True)
     lib().qo_rope(_p(x, C.c_float), C.c_int64(n), C.c_int64(heads), C.c_int64(d), C.c_int(dims), C.c_float(base),
                   C.c_float(scale), _p(_c(offsets, np.int32), C.c_int32), C.c_int(1 if as_bf16 else 0), _p(out, C.c_float))
     return out
+
+
+def turbo_rotate(x, seed: int, want_signs: bool = False):
+    """x @ R along the last axis with TurboState's rotation R (src/kv_quant.zig:164-360); fp32 carriers of bf16 values."""
+    x = _c(x, np.float32)
+    n = x.shape[-1]
+    out = np.empty(x.shape, np.float32)
+    signs = np.zeros(n, np.uint8)
+    lib().qo_turbo_rotate(_p(x, C.c_float), C.c_int64(x.size // n), C.c_int(n), C.c_uint64(seed), _p(out, C.c_float),
+                          signs.ctypes.data_as(C.POINTER(C.c_ubyte)))
+    return (out, signs) if want_signs else out
