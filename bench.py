@@ -184,7 +184,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the other benchmark configurations (C1, C3, C4, C5, sweep)")
     ap.add_argument("--no-batch", action="store_true", help="seven separate calls per layer instead of four")
-    ap.add_argument("--only", default="", help="comma list of c1,sweep,tick,c3,c4,c5,ep: run just these extra configurations and exit")
+    ap.add_argument("--only", default="", help="comma list of c1,sweep,tick,c3,c4,c5,a7,ep: run just these extra configurations and exit")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -444,6 +444,34 @@ def main():
         res["sharding"] = shard_note
         return res
 
+    def cfg_a7():
+        """attn @ V of the composed quantized attention: quantized_matmul(transpose_w=false) of the probabilities
+        [16, 8, 4, T] with the packed value cache [16, 8, T, 128] (16 sequences, 8 kv heads, GQA 4)."""
+        res = {}
+        seqs, Hkv, gq, D = 16, 8, 4, 128
+        for T in (4096, 4099, 32768):      # 4099: a probability row pitch that rules the vector loads out
+            for bits in (4, 8):
+                ncache = 8 if T < 32768 else 1   # rotate caches so every call streams from HBM (126 MB L2)
+                caches = []
+                for _ in range(ncache):
+                    v = torch.randn((seqs, Hkv, T, D), device=dev, generator=g).to(torch.bfloat16)
+                    caches.append(qb200.quantize(v, 64, bits))
+                    del v
+                pr = torch.softmax(torch.randn((seqs, Hkv, gq, T), device=dev, generator=g), dim=-1).to(torch.bfloat16)
+                out = torch.empty((seqs, Hkv, gq, D), dtype=torch.bfloat16, device=dev)
+                reps = 8
+
+                def run():
+                    for i in range(reps):
+                        qb200.quantized_matmul(pr, *caches[i % ncache], False, 64, bits, out=out)
+                gr = capture(run)
+                ms = time_graph(gr, 20, sync_ranks=False) / 20 / reps
+                by = seqs * Hkv * T * (D * bits // 8 + (D // 64) * 4) + seqs * Hkv * gq * (T + D) * 2
+                res[f"T{T}_{bits}bit"] = {"us_per_call": ms * 1e3, "bytes": by, "GBps": by / (ms * 1e-3) / 1e9,
+                                          "frac_of_hbm_peak": by / (ms * 1e-3) / 1e9 / hbm_peak}
+                del caches, gr
+        return res
+
     def cfg_tick():
         """A whole decode tick of one Llama-3-8B-shaped layer through the library (forwardBatchedDecode's layer body,
         src/transformer.zig:9656-9861): q/k/v, rope + cache append, attention over per-sequence 4-bit caches (two launches), o,
@@ -516,7 +544,8 @@ def main():
         table = {"c1": ("C1_qmv_1x4096_to_4096", cfg_c1), "sweep": ("C2_sweep", cfg_sweep), "c3": ("C3_routed_experts", cfg_c3),
                  "c4": ("C4_dense_prefill_2048x4096_to_14336", cfg_c4),
                  "c5": ("C5_decode_attention_batch16", lambda: cfg_c5(16, "16 sequences on one GPU")),
-                 "tick": ("decode_layer_tick_llama3_8b", cfg_tick)}
+                 "tick": ("decode_layer_tick_llama3_8b", cfg_tick),
+                 "a7": ("attn_times_V_transpose_false_batch16", cfg_a7)}
         for nm in names:
             if nm in table and rank == 0:
                 key, fn = table[nm]
@@ -634,7 +663,7 @@ def main():
     e2e_value = world * M * L * R * args.steps / (ms_e2e * 1e-3)
     del gr2, xin2, yout2, sets
 
-    extras = {} if args.no_configs else run_extras(["c1", "sweep", "tick", "c3", "c4", "c5"] + (["ep"] if world > 1 else []))
+    extras = {} if args.no_configs else run_extras(["c1", "sweep", "tick", "c3", "c4", "c5", "a7"] + (["ep"] if world > 1 else []))
 
     if rank == 0:
         achieved = L * R * layer_bytes(M) / (ms_step * 1e-3) / 1e9

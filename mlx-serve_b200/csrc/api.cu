@@ -320,6 +320,7 @@ static int64_t wide_max_tokens() {
 static bool takes_wide(const QmmArgs& a) { return a.M > 8 && a.M <= wide_max_tokens() && qmv_wide_supported(a); }
 
 static cudaError_t dispatch_qmm(const QmmArgs& a, cudaStream_t s) {
+  if (!a.transpose) return qmv_rows_supported(a) ? launch_qmv_rows(a, s) : launch_qmm_generic(a, s);
   if (takes_wide(a)) return launch_qmv_wide(a, s);
   if (a.M > wide_max_tokens() && a.M > 8 && qmm_tc_supported(a)) return launch_qmm_tc(a, s);
   if (a.M > 8 && !qmv_stream_supported(a) && qmm_tc_supported(a)) return launch_qmm_tc(a, s);

@@ -100,6 +100,10 @@ struct QmmArgs {
 };
 cudaError_t launch_qmm_generic(const QmmArgs& a, cudaStream_t st);
 
+// ---- qmv_rows.cu : transpose=false at attention widths (attn @ V over the packed value cache), one pass over W ----
+bool qmv_rows_supported(const QmmArgs& a);
+cudaError_t launch_qmv_rows(const QmmArgs& a, cudaStream_t st);
+
 // ---- qmv_mma.cu : small-M weight-streaming kernels (tensor-core dots, HBM-bound) ----
 bool qmv_mma_supported(const QmmArgs& a);
 cudaError_t launch_qmv_mma(const QmmArgs& a, cudaStream_t st);

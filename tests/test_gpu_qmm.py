@@ -155,6 +155,48 @@ def test_batch_broadcast_and_transpose_false_attention_shapes(transpose):
     _run(x, q[:1], s[:1], b[:1], 64, 8, transpose)
 
 
+# attn @ V of the composed quantized attention (src/kv_quant.zig:657-674): x [B, Hkv, g*Tq, T], W the packed value cache
+# [B, Hkv, T, D*bits/32] quantised along D.  The shapes below take the row-streaming tensor-core kernel (one or more 64- /
+# 32-wide column blocks, 4 or 8 bits); the last two stay on the generic kernel (2 bits; a width the blocks do not tile).
+@pytest.mark.parametrize("batch,M,T,D,bits,gs", [
+    ((4, 8), 4, 4096, 128, 4, 64),      # decode over a 4K cache, GQA 4: K split over a cluster
+    ((2, 8), 4, 4099, 128, 4, 64),      # an odd row pitch of the probabilities: scalar activation loads, partial last tile
+    ((2, 2), 4, 1000, 128, 8, 64),      # T not a multiple of the 16-row tile
+    ((3,), 1, 17, 64, 4, 64),           # one token, one column block, two tiles
+    ((1,), 8, 1, 128, 4, 64),           # a single cached position
+    ((2,), 12, 300, 128, 4, 128),       # two token tiles, group 128 = two column blocks per scale
+    ((2,), 16, 333, 256, 8, 32),        # 8 column blocks of 32, one scale each
+    ((1, 2), 32, 200, 64, 8, 64),       # four token tiles (verify widths), two blocks per scale
+    ((2,), 5, 77, 512, 4, 64),          # the widest row the kernel takes
+    ((1,), 4, 32768, 128, 4, 64),       # one long sequence: 8 CTAs of a cluster, 256 tiles each
+    ((2,), 3, 50, 128, 2, 64),          # generic kernel
+    ((2,), 3, 50, 192, 4, 64),          # generic kernel (three column blocks)
+])
+def test_transpose_false_value_cache_shapes(batch, M, T, D, bits, gs):
+    rng = np.random.default_rng(T * 7 + D + bits + M)
+    kv = rand_bf16(rng, batch + (T, D))
+    q, s, b = qo.quantize(kv, gs, bits)
+    x = rand_bf16(rng, batch + (M, T), 0.3)
+    tag = "attn @ V, T=%d D=%d %d-bit" % (T, D, bits) if T in (4096, 32768) else None
+    _run(x, q, s, b, gs, bits, False, tag=tag)
+
+
+def test_transpose_false_over_a_strided_cache_view():
+    """The value cache is a slice [:, :, :T] of capacity buffers, the probabilities a slice of a wider score block: batch
+    strides that differ from the dense ones, and an activation pitch that rules the vector loads out."""
+    import qb200
+    rng = np.random.default_rng(77)
+    B, H, cap, T, D, g = 2, 3, 160, 100, 128, 4
+    kv = rand_bf16(rng, (B, H, cap, D))
+    q, s, b = qo.quantize(kv, 64, 4)
+    dq, ds, db = dev_triple(q, s, b)
+    xw = rand_bf16(rng, (B, H, g, cap + 3), 0.3)
+    dx = to_dev_bf16(qo.f32_to_bf16(xw))
+    y = qb200.quantized_matmul(dx[..., 1:T + 1], dq[:, :, :T], ds[:, :, :T], db[:, :, :T], False, 64, 4)
+    ref = qo.qmm_batched(xw[..., 1:T + 1], q[:, :, :T], s[:, :, :T], b[:, :, :T], 64, 4, False)
+    gate_bf16(y.float().cpu().numpy(), ref, "strided value cache")
+
+
 @pytest.mark.parametrize("M", [1, 8])
 def test_fp32_activations_just_below_a_power_of_two(M):
     """fp32 activations whose group maximum rounds up to 2^14 on the 15-bit fixed-point grid (the staging clamps them
