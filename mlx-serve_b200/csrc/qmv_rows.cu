@@ -345,7 +345,8 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) qmv_rows_kernel(Row
 #pragma unroll
     for (int u = 0; u < kDepth; ++u) {
       if (i < n) {
-        if (i + kDepth - 1 < n) load_any<NT, XT>(p, a, first + (i + kDepth - 1) * rstep, lane, ring[(u + kDepth - 1) % kDepth]);
+        if (i + kDepth - 1 < nfast) load_full<NT, XT>(a, first + (i + kDepth - 1) * rstep, p.x_vec != 0, ring[(u + kDepth - 1) % kDepth]);
+        else if (i + kDepth - 1 < n) load_any<NT, XT>(p, a, first + (i + kDepth - 1) * rstep, lane, ring[(u + kDepth - 1) % kDepth]);
         const int fj = i + kCodeStages - 1;
         tile_math<BITS, NT, XT>(p, a, ring[u], stage, fj < n ? first + fj * rstep : -1, false, sbx + (u & 1) * 32, lane, acc, bacc);
         stage = stage == kCodeStages - 1 ? 0 : stage + 1;
