@@ -30,7 +30,9 @@
 //    instruction) into a ring of shared-memory stages private to the warp, several tiles ahead;
 //    a warp only ever waits on its own copies (cp.async.wait_group + __syncwarp), so there is no
 //    cross-warp protocol that could hang.  Scales, biases and activations (a quarter of the bytes)
-//    come through a short ring of registers.
+//    come through a short ring of registers.  (Sending those through the cp.async ring as well, as
+//    4-byte pieces around elements that are only 2-byte aligned, was built and measured: 10 % slower
+//    at long T -- four more copy instructions per tile in a kernel bound by instruction issue.)
 //  * One CTA = 8 warps on one batch element.  A warp owns one block of 8 packed words of the row
 //    (64 outputs at 4 bits, 32 at 8) and every (8 / blocks)-th 16-row tile of the CTA's range of K;
 //    the warps add their sums in shared memory in a fixed order.  K is split over the CTAs of a
