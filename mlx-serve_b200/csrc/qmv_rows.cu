@@ -26,11 +26,15 @@
 //  * (x s) is split into two bf16 values, hi + lo, and each MMA is issued for both: the product
 //    keeps 16 significant bits of x s, so that fp32 activations stay far inside the stated
 //    tolerance and the 128-fold constant cancels (what is left of it is 2^-18 of |x s| per term).
+//    With bf16 activations the split is exact and costs two packed instructions per pair
+//    (hi = rn(x s), lo = fma(x, s, -hi)), and the bias term rides on the tensor cores too: the sum
+//    of hi + lo against an A operand of ones and the sum of x * bias against an A operand whose rows
+//    all hold the biases, both taken from the packed words as loaded -- no fp32 unpacking at all.
 //  * The packed codes travel by cp.async (16 bytes per lane, one tile of 16 rows x 32 bytes per
 //    instruction) into a ring of shared-memory stages private to the warp, several tiles ahead;
 //    a warp only ever waits on its own copies (cp.async.wait_group + __syncwarp), so there is no
 //    cross-warp protocol that could hang.  Scales, biases and activations (a quarter of the bytes)
-//    come through a short ring of registers.  (Sending those through the cp.async ring as well, as
+//    come through a ring of registers.  (Sending those through the cp.async ring as well, as
 //    4-byte pieces around elements that are only 2-byte aligned, was built and measured: 10 % slower
 //    at long T -- four more copy instructions per tile in a kernel bound by instruction issue.)
 //  * One CTA = 8 warps on one batch element.  A warp owns one block of 8 packed words of the row
@@ -38,6 +42,8 @@
 //    the warps add their sums in shared memory in a fixed order.  K is split over the CTAs of a
 //    thread-block cluster (up to 8), whose rank 0 adds the partial sums through distributed shared
 //    memory, in rank order, and stores: no global scratch, no atomics, a reproducible sum.
+#include <type_traits>
+
 #include "kernels.h"
 #include "stream_ptx.cuh"
 
@@ -76,6 +82,25 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
   return v;
 }
 
+// packed bf16 pair arithmetic, correctly rounded
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+// The bias term sum_k x (bias - C s) of a warp's tiles.  With bf16 activations it is two more accumulators of the
+// tensor cores, in the token layout of the main ones (TC); otherwise one fp32 sum per token tile, held by the four
+// threads that hold the token's activations.
+template <int NT, bool TC> struct BiasAcc;
+template <int NT> struct BiasAcc<NT, false> { float b[NT]; };
+template <int NT> struct BiasAcc<NT, true> { float s[NT][4]; float b[NT][4]; };
+
 // Dynamic shared memory of a CTA: the partial-sum tile [8 * nt][N + 1] (fp32), the per-warp bias sums [warps][8 * nt], the
 // scale / bias hand-over [warps][64] (bf16), then, 16-byte aligned, the code rings.
 __host__ __device__ inline size_t code_ring_offset(int nt, int N) {
@@ -103,9 +128,9 @@ __device__ __forceinline__ uint4 ldg_pin_u4(const void* p) {
 
 // What a thread loads into registers for one 16-row tile (the packed codes go to shared memory instead, by cp.async).
 // A ring of kDepth of these lives in registers, so that the loads of the next kDepth - 1 tiles are in flight while one
-// tile is computed (3 registers per tile at up to 8 bf16 tokens).  Measured on the 16 x 8 x 4 x T attention shape: ring
-// depths 3, 4 and 6 (and code rings of 6, 8 and 10 stages, two or three CTAs per SM) all land within 10 % of one
-// another -- the kernel is bound by instruction issue (about 130 instructions per 512 bytes of codes), not by latency.
+// tile is computed (3 registers per tile at up to 8 bf16 tokens).  The depth matters: with seven code tiles per warp in
+// flight the memory system's queues are long, and a scale or an activation requested only two tiles ahead arrives late
+// (measured on the 16 x 8 x 4 x 32768 attention shape: 142 us at depth 3, 127 at 6, 124 at 8).
 //   sb: lanes 0-15 hold the scale of row `lane`, lanes 16-31 the bias of row `lane - 16` (bf16 bits)
 //   x : activations of token g (per token tile) at rows 4t .. 4t + 3: two packed words for 16-bit types, four floats
 template <int NT, int XW>
@@ -113,7 +138,7 @@ struct TileRegs {
   uint32_t sb;
   uint32_t x[NT][XW];
 };
-constexpr int kDepth = 3;
+constexpr int kDepth = 8;
 static_assert(kDepth <= kCodeStages, "the code ring is at least as deep as the register ring");
 
 template <typename XT> struct XRaw;   // four consecutive activations, as loaded / as fp32
@@ -219,7 +244,7 @@ __device__ __forceinline__ void load_any(const RowsK& p, const Walk<NT>& a, int 
 template <int BITS, int NT, typename XT>
 __device__ __forceinline__ void tile_math(const RowsK& p, const Walk<NT>& a, const TileRegs<NT, XRaw<XT>::W>& r, int stage,
                                           int fetch_ti, bool fetch_full, uint16_t* sbx, int lane, float (&acc)[NT][4][4],
-                                          float (&bacc)[NT]) {
+                                          BiasAcc<NT, std::is_same<XT, __nv_bfloat16>::value>& ba) {
   constexpr float kMagic = BITS == 4 ? 128.f : 128.f * 17.f;
   const int t = lane & 3;
   sbx[lane] = (uint16_t)r.sb;
@@ -238,22 +263,41 @@ __device__ __forceinline__ void tile_math(const RowsK& p, const Walk<NT>& a, con
     else if (fetch_ti >= 0) fetch_codes<NT>(p, a, fetch_ti, fill, lane);
     cp_async_commit();
   }
-  const float sc[4] = {bf16lo(sraw.x), bf16hi(sraw.x), bf16lo(sraw.y), bf16hi(sraw.y)};
-  const float bi[4] = {bf16lo(braw.x), bf16hi(braw.x), bf16lo(braw.y), bf16hi(braw.y)};
   uint32_t bh[NT][2], bl[NT][2];
+  if constexpr (std::is_same<XT, __nv_bfloat16>::value) {
+    // bf16 activations times bf16 scales: the product has 16 significant bits, hi = rn(x s) is one packed multiply
+    // and lo = x s - hi (exact, then exactly representable) one packed fused multiply-add.  The bias term rides on
+    // the tensor cores as well: sum_k (hi + lo) against an A operand of ones, sum_k x bias against an A operand
+    // whose 16 rows all hold the biases -- both straight from the packed words as they were loaded.
+    const uint32_t ones[4] = {0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u};
+    const uint32_t brow[4] = {braw.x, braw.x, braw.y, braw.y};
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    float xv[4], v[4];
-    XRaw<XT>::f32(r.x[nt], xv);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      v[i] = xv[i] * sc[i];
-      bacc[nt] = fmaf(xv[i], fmaf(-kMagic, sc[i], bi[i]), bacc[nt]);
+    for (int nt = 0; nt < NT; ++nt) {
+      bh[nt][0] = mul_bf16x2(r.x[nt][0], sraw.x);
+      bh[nt][1] = mul_bf16x2(r.x[nt][1], sraw.y);
+      bl[nt][0] = fma_bf16x2(r.x[nt][0], sraw.x, bh[nt][0] ^ 0x80008000u);
+      bl[nt][1] = fma_bf16x2(r.x[nt][1], sraw.y, bh[nt][1] ^ 0x80008000u);
+      mma_bf16_16816(ba.s[nt], ones, bh[nt][0], bh[nt][1]);
+      mma_bf16_16816(ba.s[nt], ones, bl[nt][0], bl[nt][1]);
+      mma_bf16_16816(ba.b[nt], brow, r.x[nt][0], r.x[nt][1]);
     }
-    bh[nt][0] = pack2(v[0], v[1]);
-    bh[nt][1] = pack2(v[2], v[3]);
-    bl[nt][0] = pack2(v[0] - bf16lo(bh[nt][0]), v[1] - bf16hi(bh[nt][0]));
-    bl[nt][1] = pack2(v[2] - bf16lo(bh[nt][1]), v[3] - bf16hi(bh[nt][1]));
+  } else {
+    const float sc[4] = {bf16lo(sraw.x), bf16hi(sraw.x), bf16lo(sraw.y), bf16hi(sraw.y)};
+    const float bi[4] = {bf16lo(braw.x), bf16hi(braw.x), bf16lo(braw.y), bf16hi(braw.y)};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      float xv[4], v[4];
+      XRaw<XT>::f32(r.x[nt], xv);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[i] = xv[i] * sc[i];
+        ba.b[nt] = fmaf(xv[i], fmaf(-kMagic, sc[i], bi[i]), ba.b[nt]);
+      }
+      bh[nt][0] = pack2(v[0], v[1]);
+      bh[nt][1] = pack2(v[2], v[3]);
+      bl[nt][0] = pack2(v[0] - bf16lo(bh[nt][0]), v[1] - bf16hi(bh[nt][0]));
+      bl[nt][1] = pack2(v[2] - bf16lo(bh[nt][1]), v[3] - bf16hi(bh[nt][1]));
+    }
   }
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -305,11 +349,18 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) qmv_rows_kernel(Row
       a.x[nt] = xb + ((int64_t)(nt * 8 + g < p.M ? nt * 8 + g : 0) * p.ldx + 4 * t) * sizeof(XT);
   }
 
+  constexpr bool TCB = std::is_same<XT, __nv_bfloat16>::value;   // bias term on the tensor cores
+  constexpr float kMagic = BITS == 4 ? 128.f : 128.f * 17.f;
   float acc[NT][4][4];
-  float bacc[NT];
+  BiasAcc<NT, TCB> bacc;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
-    bacc[nt] = 0.f;
+    if constexpr (TCB) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) bacc.s[nt][e] = bacc.b[nt][e] = 0.f;
+    } else {
+      bacc.b[nt] = 0.f;
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j)
 #pragma unroll
@@ -359,20 +410,29 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) qmv_rows_kernel(Row
   cp_async_wait<0>();
 
   // ---- the warp's bias sums: over the four threads of a token, then to the threads that hold the token's outputs ----
+  if constexpr (!TCB) {
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    float v = bacc[nt];
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    if (t == 0) sbias[warp * 8 * NT + nt * 8 + g] = v;
+    for (int nt = 0; nt < NT; ++nt) {
+      float v = bacc.b[nt];
+      v += __shfl_xor_sync(0xffffffffu, v, 1);
+      v += __shfl_xor_sync(0xffffffffu, v, 2);
+      if (t == 0) sbias[warp * 8 * NT + nt * 8 + g] = v;
+    }
+    __syncwarp();
   }
-  __syncwarp();
   // ---- the warps of one column block add their sums into the CTA's tile, one warp per round ----
   for (int r = 0; r < rstep; ++r) {
     if (rsub == r) {
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        const float b0 = sbias[warp * 8 * NT + nt * 8 + 2 * t], b1 = sbias[warp * 8 * NT + nt * 8 + 2 * t + 1];
+        float b0, b1;   // bias sums of tokens 2t and 2t + 1 of this token tile
+        if constexpr (TCB) {
+          b0 = fmaf(-kMagic, bacc.s[nt][0], bacc.b[nt][0]);
+          b1 = fmaf(-kMagic, bacc.s[nt][1], bacc.b[nt][1]);
+        } else {
+          b0 = sbias[warp * 8 * NT + nt * 8 + 2 * t];
+          b1 = sbias[warp * 8 * NT + nt * 8 + 2 * t + 1];
+        }
         float* row0 = fin + (size_t)(nt * 8 + 2 * t) * pitch + cb * NL;
         float* row1 = row0 + pitch;
 #pragma unroll
