@@ -20,7 +20,7 @@
 //    MMA j simply takes byte j of the four words: its low nibbles are A row g, its high nibbles
 //    A row g + 8.  No transposition through shared memory.
 //  * A nibble c becomes the bf16 value 128 + c by OR-ing it into the mantissa of 0x4300 (one
-//    PRMT, one shift and two LOP3 per eight codes); the 128 is taken out again in fp32 through
+//    PRMT, one shift and two LOP3 per four codes); the 128 is taken out again in fp32 through
 //    the bias term, sum_k x (bias - 128 s).  An 8-bit code is its two nibbles: the high-nibble
 //    rows of the accumulator count 16-fold in the epilogue (and the constant is 128 * 17).
 //  * (x s) is split into two bf16 values, hi + lo, and each MMA is issued for both: the product
