@@ -184,7 +184,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the other benchmark configurations (C1, C3, C4, C5, sweep)")
     ap.add_argument("--no-batch", action="store_true", help="seven separate calls per layer instead of four")
-    ap.add_argument("--only", default="", help="comma list of c1,sweep,tick,c3,c4,c5,a7,ep: run just these extra configurations and exit")
+    ap.add_argument("--only", default="", help="comma list of c1,sweep,tick,c3,c4,c5,a7,qk,ep: run just these extra configurations and exit")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -444,12 +444,13 @@ def main():
         res["sharding"] = shard_note
         return res
 
-    def cfg_a7():
-        """attn @ V of the composed quantized attention: quantized_matmul(transpose_w=false) of the probabilities
-        [16, 8, 4, T] with the packed value cache [16, 8, T, 128] (16 sequences, 8 kv heads, GQA 4)."""
+    def cfg_attn_products(transpose):
+        """The two products of the composed quantized attention as standalone operators, 16 sequences x 8 kv heads, GQA 4,
+        D = 128: q @ K^T (transpose_w=true: queries [16, 8, 4, 128] with the packed key cache [16, 8, T, 128]) and
+        attn @ V (transpose_w=false: probabilities [16, 8, 4, T] with the packed value cache)."""
         res = {}
         seqs, Hkv, gq, D = 16, 8, 4, 128
-        for T in (4096, 4099, 32768):      # 4099: a probability row pitch that rules the vector loads out
+        for T in (4096, 4099, 32768):      # 4099: a cache length that rules vector loads of the probabilities out
             for bits in (4, 8):
                 ncache = 8 if T < 32768 else 1   # rotate caches so every call streams from HBM (126 MB L2)
                 caches = []
@@ -457,13 +458,17 @@ def main():
                     v = torch.randn((seqs, Hkv, T, D), device=dev, generator=g).to(torch.bfloat16)
                     caches.append(qb200.quantize(v, 64, bits))
                     del v
-                pr = torch.softmax(torch.randn((seqs, Hkv, gq, T), device=dev, generator=g), dim=-1).to(torch.bfloat16)
-                out = torch.empty((seqs, Hkv, gq, D), dtype=torch.bfloat16, device=dev)
+                if transpose:
+                    xin = torch.randn((seqs, Hkv, gq, D), device=dev, generator=g).to(torch.bfloat16)
+                    out = torch.empty((seqs, Hkv, gq, T), dtype=torch.bfloat16, device=dev)
+                else:
+                    xin = torch.softmax(torch.randn((seqs, Hkv, gq, T), device=dev, generator=g), dim=-1).to(torch.bfloat16)
+                    out = torch.empty((seqs, Hkv, gq, D), dtype=torch.bfloat16, device=dev)
                 reps = 8
 
                 def run():
                     for i in range(reps):
-                        qb200.quantized_matmul(pr, *caches[i % ncache], False, 64, bits, out=out)
+                        qb200.quantized_matmul(xin, *caches[i % ncache], transpose, 64, bits, out=out)
                 gr = capture(run)
                 ms = time_graph(gr, 20, sync_ranks=False) / 20 / reps
                 by = seqs * Hkv * T * (D * bits // 8 + (D // 64) * 4) + seqs * Hkv * gq * (T + D) * 2
@@ -545,7 +550,8 @@ def main():
                  "c4": ("C4_dense_prefill_2048x4096_to_14336", cfg_c4),
                  "c5": ("C5_decode_attention_batch16", lambda: cfg_c5(16, "16 sequences on one GPU")),
                  "tick": ("decode_layer_tick_llama3_8b", cfg_tick),
-                 "a7": ("attn_times_V_transpose_false_batch16", cfg_a7)}
+                 "a7": ("attn_times_V_transpose_false_batch16", lambda: cfg_attn_products(False)),
+                 "qk": ("q_times_Kt_transpose_true_batch16", lambda: cfg_attn_products(True))}
         for nm in names:
             if nm in table and rank == 0:
                 key, fn = table[nm]
@@ -663,7 +669,7 @@ def main():
     e2e_value = world * M * L * R * args.steps / (ms_e2e * 1e-3)
     del gr2, xin2, yout2, sets
 
-    extras = {} if args.no_configs else run_extras(["c1", "sweep", "tick", "c3", "c4", "c5", "a7"] + (["ep"] if world > 1 else []))
+    extras = {} if args.no_configs else run_extras(["c1", "sweep", "tick", "c3", "c4", "c5", "a7", "qk"] + (["ep"] if world > 1 else []))
 
     if rank == 0:
         achieved = L * R * layer_bytes(M) / (ms_step * 1e-3) / 1e9

@@ -321,6 +321,7 @@ static bool takes_wide(const QmmArgs& a) { return a.M > 8 && a.M <= wide_max_tok
 
 static cudaError_t dispatch_qmm(const QmmArgs& a, cudaStream_t s) {
   if (!a.transpose) return qmv_rows_supported(a) ? launch_qmv_rows(a, s) : launch_qmm_generic(a, s);
+  if (a.nbatch > 1 && qmv_shortk_supported(a)) return launch_qmv_shortk(a, s);   // one W per batch element, short K: q @ K^T
   if (takes_wide(a)) return launch_qmv_wide(a, s);
   if (a.M > wide_max_tokens() && a.M > 8 && qmm_tc_supported(a)) return launch_qmm_tc(a, s);
   if (a.M > 8 && !qmv_stream_supported(a) && qmm_tc_supported(a)) return launch_qmm_tc(a, s);

@@ -104,6 +104,10 @@ cudaError_t launch_qmm_generic(const QmmArgs& a, cudaStream_t st);
 bool qmv_rows_supported(const QmmArgs& a);
 cudaError_t launch_qmv_rows(const QmmArgs& a, cudaStream_t st);
 
+// ---- qmv_shortk.cu : batched transpose=true with a short contraction (q @ K^T over the packed key cache) ----
+bool qmv_shortk_supported(const QmmArgs& a);
+cudaError_t launch_qmv_shortk(const QmmArgs& a, cudaStream_t st);
+
 // ---- qmv_mma.cu : small-M weight-streaming kernels (tensor-core dots, HBM-bound) ----
 bool qmv_mma_supported(const QmmArgs& a);
 cudaError_t launch_qmv_mma(const QmmArgs& a, cudaStream_t st);

@@ -1,0 +1,360 @@
+// Batched quantized matmul with a short contraction and many weight rows, at attention widths:
+//   y[b, m, n] = sum_k x[b, m, k] * (s[b, n, G(k)] * q[b, n, k] + bias[b, n, G(k)]),   m <= 8, K = 64 / 128 / 256,
+// W [N, K] quantised along K in groups of 64, N long, one W per batch element.
+//
+// Replaces mlx_quantized_matmul(transpose=true) as quantAttention calls it for q @ K^T
+// (mlx-serve src/kv_quant.zig:528-533; pinned by the reference test at :968-1036): x is the query
+// block [B, Hkv, g*Tq, D], W the packed key cache [B, Hkv, T, D*bits/32], so the contraction is one
+// head dimension, N = T is the cache length and the batch B*Hkv is large.  One pass over the packed
+// cache, nothing shared between the rows: every warp owns 16-row tiles of one batch element, no
+// reduction across warps or CTAs.
+//
+//  * Tensor cores with the roles swapped: the codes are the 16-row A operand of
+//    mma.sync.m16n8k16 (bf16, fp32 accumulate), the activations the 8-column B operand.  A packed
+//    word holds 8 (4-bit) or 4 (8-bit) consecutive k of one row, and the position of a k inside the
+//    64-wide group is free as long as B follows; so a register of A is simply
+//    (word >> 4 i) & 0x000F000F -- nibbles i and i + 4 side by side -- OR-ed into the mantissa of
+//    two bf16 128.0: one shift and one LOP3 per two codes, no byte permutation.  The activations are
+//    arranged once per CTA into the matching B fragments and stay in registers.
+//  * An 8-bit code is its two nibbles on two accumulators (the high one counts 16-fold).
+//  * Per 64-wide group the accumulator holds sum (128 + q) x; the group's scale and bias are applied
+//    in fp32:  y += s * acc + (bias - C s) * sum_k x  with C = 128 (4-bit) or 128 * 17.  The weight
+//    term q s + bias is never rounded.
+//  * Activations that are not bf16 are split into two bf16 values, hi + lo, and every MMA is issued
+//    for both (16 significant bits of x).
+//  * Codes, scales and biases travel by cp.async into a ring of shared-memory stages private to the
+//    warp; a warp only ever waits on its own copies (cp.async.wait_group + __syncwarp).
+#include <type_traits>
+
+#include "kernels.h"
+#include "stream_ptx.cuh"
+
+namespace qb {
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kStages = 4;          // tiles per warp in the ring (three in flight)
+constexpr int kRowPad = 32;         // bytes added to a row of codes in a stage: fragment reads of rows g, g + 1, .. miss each other's banks
+
+struct ShortK {
+  const void* x; const uint32_t* w; const uint16_t* s; const uint16_t* b; void* y;
+  int M, K;
+  int64_t N;
+  int64_t ldx, ldw, lds, ldy;    // row pitches in elements
+  int tiles;                     // 16-row tiles of N
+  int tiles_per_cta;
+  int sb_vec;                    // a batch element's scales and biases start on 4 bytes
+  BatchMap xb, wb, sb, yb;
+};
+
+template <int BITS, int NG> struct Geo {
+  static constexpr int kRowBytes = NG * 64 * BITS / 8;              // packed codes of one row
+  static constexpr int kPitch = kRowBytes + kRowPad;                // a row in a stage
+  static constexpr int kCodeBytes = 16 * kPitch;
+  static constexpr int kSbRow = NG * 2;                             // bytes of a row's scales (= of its biases)
+  static constexpr int kSbBytes = 2 * 16 * kSbRow;                  // scales of 16 rows, then their biases
+  static constexpr int kStageBytes = (kCodeBytes + kSbBytes + 15) / 16 * 16;
+  static constexpr int kCodePieces = 16 * kRowBytes / 16;           // 16-byte pieces of a tile's codes
+  static constexpr int kSbWords = 16 * kSbRow / 4;                  // 4-byte pieces of a tile's scales (= biases)
+  static constexpr int kWordsPerThread = BITS == 4 ? 2 : 4;         // packed words of one row and group a thread expands
+};
+
+__device__ __forceinline__ void cp_async16_if(uint32_t dst, const void* src, bool in) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(in ? 16 : 0));
+}
+__device__ __forceinline__ uint2 lds_u2(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint4 lds_u4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *(const uint32_t*)&h;
+}
+
+// The k (inside its 64-wide group) that slot `e` (0..3: a0.lo, a0.hi, a2.lo, a2.hi) of MMA `mm` of the group takes
+// from thread t.  4 bits: word 2t + mm / 2 of the group, nibbles (2p, 2p + 4) and (2p + 1, 2p + 5) with p = mm % 2.
+// 8 bits: word 4t + mm, bytes (0, 2) and (1, 3).
+template <int BITS>
+__device__ __forceinline__ int k_of_slot(int t, int mm, int e) {
+  if (BITS == 4) {
+    const int word = 2 * t + (mm >> 1), p = mm & 1;
+    return 8 * word + 2 * p + (e >> 1) + 4 * (e & 1);
+  }
+  return 4 * (4 * t + mm) + (e >> 1) + 2 * (e & 1);
+}
+
+template <int BITS, int NG, typename XT>
+__global__ void __launch_bounds__(kThreads, 2) qmv_shortk_kernel(ShortK p) {
+  using G = Geo<BITS, NG>;
+  constexpr bool SPLIT = !std::is_same<XT, __nv_bfloat16>::value;   // activations as hi + lo
+  constexpr int NP = SPLIT ? 2 : 1;
+  constexpr float kMagic = BITS == 4 ? 128.f : 128.f * 17.f;
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int64_t bz = blockIdx.y;
+  __shared__ int64_t boff[4];
+  if (tid < 4) boff[tid] = (tid == 0 ? p.xb : (tid == 1 ? p.wb : (tid == 2 ? p.sb : p.yb))).offset(bz);
+  __syncthreads();
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + (uint32_t)warp * kStages * G::kStageBytes;
+
+  // ---- what this lane copies for every tile ----
+  const uint32_t* wbase = p.w + boff[1];
+  const uint16_t* sbase = p.s + boff[2];
+  const uint16_t* bbase = p.b + boff[2];
+  auto fetch = [&](int tile, int stage) {
+    const int64_t n0 = (int64_t)tile * 16;
+    const uint32_t dst = ring + (uint32_t)stage * G::kStageBytes;
+#pragma unroll
+    for (int c = 0; c < (G::kCodePieces + 31) / 32; ++c) {
+      const int piece = lane + 32 * c;
+      if (G::kCodePieces % 32 == 0 || piece < G::kCodePieces) {
+        const int row = piece / (G::kRowBytes / 16), col = piece % (G::kRowBytes / 16);
+        const bool in = n0 + row < p.N;
+        cp_async16_if(dst + row * G::kPitch + col * 16, in ? (const void*)(wbase + (n0 + row) * p.ldw + col * 4) : (const void*)p.w, in);
+      }
+    }
+    // scales of the 16 rows, then their biases: the rows are contiguous (lds == NG), 32 * NG bytes each way, copied as
+    // 4-byte pieces (a batch element's scales start on 4 bytes whenever its row count times NG is even)
+    if (n0 + 16 <= p.N && p.sb_vec) {
+#pragma unroll
+      for (int c = 0; c < (2 * G::kSbWords + 31) / 32; ++c) {
+        const int piece = lane + 32 * c;
+        if ((2 * G::kSbWords) % 32 == 0 || piece < 2 * G::kSbWords) {
+          const int which = piece / G::kSbWords, word = piece % G::kSbWords;
+          cp_async4(dst + G::kCodeBytes + which * 16 * G::kSbRow + word * 4, (which ? bbase : sbase) + n0 * NG + word * 2);
+        }
+      }
+    } else {
+      // the matrix's last, partial tile (or scales that start on an odd element): entry by entry, so that nothing
+      // behind the last row is read; the plain stores are ordered before the reads of this stage by the __syncwarp
+      // that precedes them
+      for (int idx = lane; idx < 2 * 16 * NG; idx += 32) {
+        const int which = idx / (16 * NG), r = (idx % (16 * NG)) / NG;
+        const uint16_t v = n0 + r < p.N ? (which ? bbase : sbase)[n0 * NG + idx % (16 * NG)] : (uint16_t)0;
+        asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst + G::kCodeBytes + which * 16 * G::kSbRow + (idx % (16 * NG)) * 2), "h"(v) : "memory");
+      }
+    }
+  };
+
+  const int t0 = blockIdx.x * p.tiles_per_cta;
+  const int t1 = min(p.tiles, t0 + p.tiles_per_cta);
+  const int first = t0 + warp;
+  const int n = first < t1 ? (t1 - first + kWarps - 1) / kWarps : 0;
+#pragma unroll 1
+  for (int d = 0; d < kStages - 1; ++d) {
+    if (d < n) fetch(first + d * kWarps, d);
+    cp_async_commit();
+  }
+  // ---- the activations of token g in B-fragment order and the per-group sums of tokens 2t and 2t + 1: the same
+  // for every warp, so warp 0 builds them (while the others' first tiles are already on their way) and hands them
+  // over through shared memory ----
+  constexpr int kFragWords = NP * NG * 8 + NG * 2;
+  __shared__ uint32_t xs[kFragWords][32];
+  uint32_t bf[NP][NG][4][2];
+  float sx[NG][2];
+  if (warp == 0) {
+    const char* xb = (const char*)p.x + boff[0] * sizeof(XT);
+    const int tok = g < p.M ? g : 0;   // a token beyond M repeats token 0: its results are never stored
+#pragma unroll
+    for (int gi = 0; gi < NG; ++gi) {
+      float part = 0.f;
+#pragma unroll
+      for (int mm = 0; mm < 4; ++mm) {
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = IO<XT>::load(xb, (int64_t)tok * p.ldx + 64 * gi + k_of_slot<BITS>(t, mm, e));
+        part += (v[0] + v[1]) + (v[2] + v[3]);
+        const uint32_t h0 = pack2(v[0], v[1]), h1 = pack2(v[2], v[3]);
+        xs[(gi * 4 + mm) * 2 + 0][lane] = h0;
+        xs[(gi * 4 + mm) * 2 + 1][lane] = h1;
+        if constexpr (SPLIT) {
+          xs[NG * 8 + (gi * 4 + mm) * 2 + 0][lane] = pack2(v[0] - bf16lo(h0), v[1] - bf16hi(h0));
+          xs[NG * 8 + (gi * 4 + mm) * 2 + 1][lane] = pack2(v[2] - bf16lo(h1), v[3] - bf16hi(h1));
+        }
+      }
+      part += __shfl_xor_sync(0xffffffffu, part, 1);
+      part += __shfl_xor_sync(0xffffffffu, part, 2);            // token g, the whole group
+      xs[NP * NG * 8 + gi * 2 + 0][lane] = __float_as_uint(__shfl_sync(0xffffffffu, part, (2 * t) * 4));   // this thread's accumulator columns
+      xs[NP * NG * 8 + gi * 2 + 1][lane] = __float_as_uint(__shfl_sync(0xffffffffu, part, (2 * t + 1) * 4));
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int pl = 0; pl < NP; ++pl)
+#pragma unroll
+    for (int gi = 0; gi < NG; ++gi)
+#pragma unroll
+      for (int mm = 0; mm < 4; ++mm) {
+        bf[pl][gi][mm][0] = xs[pl * NG * 8 + (gi * 4 + mm) * 2 + 0][lane];
+        bf[pl][gi][mm][1] = xs[pl * NG * 8 + (gi * 4 + mm) * 2 + 1][lane];
+      }
+#pragma unroll
+  for (int gi = 0; gi < NG; ++gi) {
+    sx[gi][0] = __uint_as_float(xs[NP * NG * 8 + gi * 2 + 0][lane]);
+    sx[gi][1] = __uint_as_float(xs[NP * NG * 8 + gi * 2 + 1][lane]);
+  }
+
+  char* yb = (char*)p.y + boff[3] * sizeof(XT);
+  int stage = 0;
+#pragma unroll 1
+  for (int i = 0; i < n; ++i) {
+    cp_async_wait<kStages - 2>();   // this lane's pieces of tile i have landed ...
+    __syncwarp();                   // ... and so have every other lane's; every lane is done with the stage read last
+    if (i + kStages - 1 < n) fetch(first + (i + kStages - 1) * kWarps, stage == 0 ? kStages - 1 : stage - 1);
+    cp_async_commit();
+    const uint32_t st = ring + (uint32_t)stage * G::kStageBytes;
+    float y[4] = {0.f, 0.f, 0.f, 0.f};   // rows g, g (tokens 2t, 2t + 1), rows g + 8, g + 8
+#pragma unroll
+    for (int gi = 0; gi < NG; ++gi) {
+      // packed words of rows g and g + 8 in this group: words 2t, 2t + 1 (4-bit) or 4t .. 4t + 3 (8-bit)
+      uint32_t wq[2][G::kWordsPerThread];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t at = st + (uint32_t)(g + 8 * h) * G::kPitch + gi * (64 * BITS / 8) + t * (4 * G::kWordsPerThread);
+        if (BITS == 4) {
+          const uint2 q = lds_u2(at);
+          wq[h][0] = q.x; wq[h][1] = q.y;
+        } else {
+          const uint4 q = lds_u4(at);
+          wq[h][0] = q.x; wq[h][1] = q.y; wq[h][2] = q.z; wq[h][3] = q.w;
+        }
+      }
+      float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};   // low nibbles (all of a 4-bit code) / high nibbles
+#pragma unroll
+      for (int mm = 0; mm < 4; ++mm) {
+        uint32_t a[4], ah[4];
+        if (BITS == 4) {
+          const int wd = mm >> 1, sh = 8 * (mm & 1);   // nibbles (2p, 2p + 4) and (2p + 1, 2p + 5): shifts 8p and 8p + 4
+          a[0] = lop3_and_or(wq[0][wd] >> sh, 0x000F000Fu, 0x43004300u);
+          a[1] = lop3_and_or(wq[1][wd] >> sh, 0x000F000Fu, 0x43004300u);
+          a[2] = lop3_and_or(wq[0][wd] >> (sh + 4), 0x000F000Fu, 0x43004300u);
+          a[3] = lop3_and_or(wq[1][wd] >> (sh + 4), 0x000F000Fu, 0x43004300u);
+        } else {
+          a[0] = lop3_and_or(wq[0][mm], 0x000F000Fu, 0x43004300u);          // bytes 0 and 2, low nibbles
+          a[1] = lop3_and_or(wq[1][mm], 0x000F000Fu, 0x43004300u);
+          a[2] = lop3_and_or(wq[0][mm] >> 8, 0x000F000Fu, 0x43004300u);     // bytes 1 and 3
+          a[3] = lop3_and_or(wq[1][mm] >> 8, 0x000F000Fu, 0x43004300u);
+          ah[0] = lop3_and_or(wq[0][mm] >> 4, 0x000F000Fu, 0x43004300u);    // the high nibbles
+          ah[1] = lop3_and_or(wq[1][mm] >> 4, 0x000F000Fu, 0x43004300u);
+          ah[2] = lop3_and_or(wq[0][mm] >> 12, 0x000F000Fu, 0x43004300u);
+          ah[3] = lop3_and_or(wq[1][mm] >> 12, 0x000F000Fu, 0x43004300u);
+        }
+#pragma unroll
+        for (int pl = 0; pl < NP; ++pl) {
+          mma_bf16_16816(d0, a, bf[pl][gi][mm][0], bf[pl][gi][mm][1]);
+          if (BITS == 8) mma_bf16_16816(d1, ah, bf[pl][gi][mm][0], bf[pl][gi][mm][1]);
+        }
+      }
+      // the group's scale and bias of rows g and g + 8
+      const uint32_t sat = st + G::kCodeBytes + 2 * gi;
+      float sc[2], bi[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint16_t sv, bv;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sv) : "r"(sat + (uint32_t)(g + 8 * h) * G::kSbRow));
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(bv) : "r"(sat + 16 * G::kSbRow + (uint32_t)(g + 8 * h) * G::kSbRow));
+        sc[h] = bf16_bits_to_f32(sv);
+        bi[h] = fmaf(-kMagic, sc[h], bf16_bits_to_f32(bv));
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1, col = e & 1;
+        const float acc = BITS == 4 ? d0[e] : fmaf(16.f, d1[e], d0[e]);
+        y[e] = fmaf(sc[h], acc, fmaf(bi[h], sx[gi][col], y[e]));
+      }
+    }
+    const int64_t n0 = (int64_t)(first + i * kWarps) * 16;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int64_t nn = n0 + g + 8 * (e >> 1);
+      const int m = 2 * t + (e & 1);
+      if (nn < p.N && m < p.M) IO<XT>::store(yb, (int64_t)m * p.ldy + nn, y[e]);
+    }
+    stage = stage == kStages - 1 ? 0 : stage + 1;
+  }
+  cp_async_wait<0>();
+}
+
+template <int BITS, int NG, typename XT>
+cudaError_t launch_inst(const ShortK& p, int ctas_per_batch, int64_t nbatch, cudaStream_t st) {
+  using G = Geo<BITS, NG>;
+  const size_t smem = (size_t)kWarps * kStages * G::kStageBytes;
+  {
+    std::lock_guard<std::mutex> lk(setup_mutex());
+    static bool done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !done[dev]) {
+      const cudaError_t e = cudaFuncSetAttribute(qmv_shortk_kernel<BITS, NG, XT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      if (dev >= 0 && dev < 64) done[dev] = true;
+    }
+  }
+  return launch_kernel(qmv_shortk_kernel<BITS, NG, XT>, dim3((unsigned)ctas_per_batch, (unsigned)nbatch, 1), dim3(kThreads), smem, st, p);
+}
+
+template <int BITS, int NG>
+cudaError_t launch_x(const ShortK& p, int x_dtype, int ctas, int64_t nbatch, cudaStream_t st) {
+  switch (x_dtype) {
+    case QB200_BFLOAT16: return launch_inst<BITS, NG, __nv_bfloat16>(p, ctas, nbatch, st);
+    case QB200_FLOAT32: return launch_inst<BITS, NG, float>(p, ctas, nbatch, st);
+    case QB200_FLOAT16: return launch_inst<BITS, NG, __half>(p, ctas, nbatch, st);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+template <int BITS>
+cudaError_t launch_bits(const ShortK& p, int x_dtype, int ctas, int64_t nbatch, cudaStream_t st) {
+  switch (p.K / 64) {
+    case 1: return launch_x<BITS, 1>(p, x_dtype, ctas, nbatch, st);
+    case 2: return launch_x<BITS, 2>(p, x_dtype, ctas, nbatch, st);
+    case 4: return launch_x<BITS, 4>(p, x_dtype, ctas, nbatch, st);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+bool strides_multiple_of(const BatchMap& m, int64_t q) {
+  for (int d = 0; d < m.nd; ++d)
+    if (m.stride[d] % q) return false;
+  return true;
+}
+
+}  // namespace
+
+bool qmv_shortk_supported(const QmmArgs& a) {
+  if (!a.transpose || (a.bits != 4 && a.bits != 8) || a.gs != 64) return false;
+  if (a.K != 64 && a.K != 128 && a.K != 256) return false;
+  if (a.M < 1 || a.M > 8 || a.N < 1 || a.N > ((int64_t)1 << 30) || a.nbatch < 2 || a.nbatch > 65535) return false;
+  const int64_t ng = a.K / 64;
+  // 16-byte pieces of codes by cp.async: rows start on 16 bytes; a row's scales follow the previous row's (lds == groups)
+  if ((uintptr_t)a.w % 16 || a.ldw % 4 || !strides_multiple_of(a.wb, 4)) return false;
+  if (a.lds != ng) return false;
+  return true;
+}
+
+cudaError_t launch_qmv_shortk(const QmmArgs& a, cudaStream_t st) {
+  if (!qmv_shortk_supported(a)) return cudaErrorInvalidValue;
+  ShortK p;
+  p.x = a.x; p.w = a.w; p.s = (const uint16_t*)a.s; p.b = (const uint16_t*)a.b; p.y = a.y;
+  p.M = (int)a.M; p.K = (int)a.K; p.N = a.N;
+  p.ldx = a.ldx; p.ldw = a.ldw; p.lds = a.lds; p.ldy = a.ldy;
+  p.tiles = (int)((a.N + 15) / 16);
+  // tiles per CTA: at least 8 per warp (the ring's fill and the activation set-up are paid once per CTA), fewer only
+  // when that would leave SMs without a CTA
+  int per_warp = 16;
+  while (per_warp > 2 && a.nbatch * ((p.tiles + kWarps * per_warp - 1) / (kWarps * per_warp)) < 2LL * sm_count()) per_warp /= 2;
+  p.tiles_per_cta = kWarps * per_warp;
+  const int ctas = (p.tiles + p.tiles_per_cta - 1) / p.tiles_per_cta;
+  p.sb_vec = (uintptr_t)a.s % 4 == 0 && (uintptr_t)a.b % 4 == 0 && strides_multiple_of(a.sb, 2);
+  p.xb = a.xb; p.wb = a.wb; p.sb = a.sb; p.yb = a.yb;
+  return a.bits == 4 ? launch_bits<4>(p, a.x_dtype, ctas, a.nbatch, st) : launch_bits<8>(p, a.x_dtype, ctas, a.nbatch, st);
+}
+
+}  // namespace qb

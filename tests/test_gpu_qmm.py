@@ -181,6 +181,45 @@ def test_transpose_false_value_cache_shapes(batch, M, T, D, bits, gs):
     _run(x, q, s, b, gs, bits, False, tag=tag)
 
 
+# q @ K^T of the composed quantized attention (src/kv_quant.zig:528-533): x [B, Hkv, g*Tq, D], W the packed key cache
+# [B, Hkv, T, D*bits/32], one W per batch element, a contraction of one head dimension.  The shapes below take the
+# batched short-contraction tensor-core kernel; the last two stay on the generic kernel (group 32; 9 rows).
+@pytest.mark.parametrize("batch,M,T,D,bits,gs", [
+    ((4, 8), 4, 4096, 128, 4, 64),      # decode over a 4K cache, GQA 4
+    ((2, 2), 4, 1000, 128, 8, 64),      # T not a multiple of the 16-row tile: the partial last tile
+    ((3,), 1, 17, 64, 4, 64),           # one query row, one group, two tiles
+    ((2,), 8, 1, 128, 4, 64),           # a single cached position, eight rows
+    ((2,), 5, 333, 256, 4, 64),         # four groups
+    ((1, 2), 3, 200, 64, 8, 64),        # 8-bit, one group
+    ((2,), 2, 77, 256, 8, 64),          # 8-bit, four groups
+    ((2,), 4, 40000, 128, 4, 64),       # a long cache: many CTAs per batch element
+    ((2,), 3, 50, 128, 8, 32),          # generic kernel (group 32)
+    ((2,), 9, 50, 128, 4, 64),          # generic kernel (more than 8 rows)
+])
+def test_transpose_true_key_cache_shapes(batch, M, T, D, bits, gs):
+    rng = np.random.default_rng(T * 5 + D + bits + M)
+    kv = rand_bf16(rng, batch + (T, D))
+    q, s, b = qo.quantize(kv, gs, bits)
+    x = rand_bf16(rng, batch + (M, D), 0.3)
+    tag = "q @ K^T, T=%d D=%d %d-bit" % (T, D, bits) if T == 4096 else None
+    _run(x, q, s, b, gs, bits, True, tag=tag)
+
+
+def test_transpose_true_over_a_strided_cache_view():
+    """The key cache as a slice [:, :, :T] of capacity buffers and the queries as a slice of a wider block."""
+    import qb200
+    rng = np.random.default_rng(78)
+    B, H, cap, T, D, g = 2, 3, 160, 100, 128, 4
+    kv = rand_bf16(rng, (B, H, cap, D))
+    q, s, b = qo.quantize(kv, 64, 4)
+    dq, ds, db = dev_triple(q, s, b)
+    xw = rand_bf16(rng, (B, H, g, D + 8), 0.3)
+    dx = to_dev_bf16(qo.f32_to_bf16(xw))
+    y = qb200.quantized_matmul(dx[..., 3:D + 3], dq[:, :, :T], ds[:, :, :T], db[:, :, :T], True, 64, 4)
+    ref = qo.qmm_batched(xw[..., 3:D + 3], q[:, :, :T], s[:, :, :T], b[:, :, :T], 64, 4, True)
+    gate_bf16(y.float().cpu().numpy(), ref, "strided key cache")
+
+
 def test_transpose_false_over_a_strided_cache_view():
     """The value cache is a slice [:, :, :T] of capacity buffers, the probabilities a slice of a wider score block: batch
     strides that differ from the dense ones, and an activation pitch that rules the vector loads out."""
