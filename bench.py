@@ -479,8 +479,9 @@ def main():
 
     def cfg_tick():
         """A whole decode tick of one Llama-3-8B-shaped layer through the library (forwardBatchedDecode's layer body,
-        src/transformer.zig:9656-9861): q/k/v, rope + cache append, attention over per-sequence 4-bit caches (two launches), o,
-        add + norm, gate/up, SwiGLU, down, add + the next layer's input norm -- 11 launches (plus one norm before the
+        src/transformer.zig:9656-9861): q/k/v, rope + cache append, attention over per-sequence 4-bit caches (one launch: the splits of a
+        sequence merge inside a thread-block cluster), o, add + norm, gate/up, SwiGLU, down, add + the next layer's input
+        norm -- 10 launches (plus one norm before the
         first layer).  8 layers' weights rotate so the weights stream from HBM."""
         Hd, Hq, Hkv, D, F, NL = 4096, 32, 8, 128, 14336, 8
         lw = layers[:NL] if len(layers) >= NL else None
@@ -533,7 +534,7 @@ def main():
             ms = time_graph(gr, 20, sync_ranks=False) / 20 / NL
             kv_bytes = sum(2 * Hkv * (lens[n] + 1) * (D * 4 // 8 + 8) for n in range(N))
             by = layer_bytes(N) + kv_bytes
-            res[f"N{N}_T{T}"] = {"us_per_layer_tick": ms * 1e3, "launches_per_layer": 11, "tokens_per_s_through_32_layers": N / (32 * ms * 1e-3),
+            res[f"N{N}_T{T}"] = {"us_per_layer_tick": ms * 1e3, "launches_per_layer": 10, "tokens_per_s_through_32_layers": N / (32 * ms * 1e-3),
                                   "bytes_per_layer_tick": by, "GBps": by / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": by / (ms * 1e-3) / 1e9 / hbm_peak}
             del gr, kt, vt, kviews, vviews
         return res

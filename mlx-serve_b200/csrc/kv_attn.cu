@@ -243,7 +243,8 @@ __global__ void kv_merge(KvK p) {
 }  // namespace
 
 cudaError_t launch_kv_fast(const KvAttnArgs& a, int nsplit, int64_t tps, float* pm, float* pl, float* po,
-                           cudaStream_t st, const KvSeqTable* seqs);
+                           cudaStream_t st, const KvSeqTable* seqs, bool fused);
+constexpr int kMaxFusedSplits = 8;   // the portable cluster size
 
 size_t kv_attn_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t T, int64_t Dv) {
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || T <= 0 || Dv <= 0) return 0;
@@ -275,7 +276,14 @@ cudaError_t launch_kv_attn(const KvAttnArgs& a, cudaStream_t st, const KvSeqTabl
   p.part_o = ws + 2 * a.B * a.Hq * sp.nsplit;
   cudaError_t e;
   if (kv_fast_supported(a, seqs)) {
-    e = launch_kv_fast(a, sp.nsplit, sp.tokens_per_split, p.part_m, p.part_l, p.part_o, st, seqs);
+    // Up to 8 splits per (sequence, kv head) run as one thread-block cluster whose rank 0 merges the partial results
+    // through distributed shared memory and writes the output: no partials in global memory, no merge launch.
+    if (sp.nsplit <= kMaxFusedSplits) {
+      e = launch_kv_fast(a, sp.nsplit, sp.tokens_per_split, p.part_m, p.part_l, p.part_o, st, seqs, true);
+      if (e == cudaSuccess) return e;
+      (void)cudaGetLastError();   // a cluster this launch could not place: fall back to partials and the merge kernel
+    }
+    e = launch_kv_fast(a, sp.nsplit, sp.tokens_per_split, p.part_m, p.part_l, p.part_o, st, seqs, false);
   } else {
     const int nwarp = 4;
     const size_t smem = (size_t)(p.gqa * a.D + 2 * nwarp * p.gqa + nwarp * p.gqa * a.Dv) * sizeof(float);

@@ -56,6 +56,7 @@ struct FastK {
   int nsplit;
   int64_t tps;  // tokens per split, multiple of 128
   int gqa;
+  int fused;    // the splits of a (sequence, kv head) are the CTAs of one cluster: rank 0 merges them and writes the output
   float* part_m; float* part_l; float* part_o;
 };
 
@@ -480,6 +481,11 @@ __global__ void __launch_bounds__(kWarps * 32, BITS == 4 ? 2 : 1) kv_fast_kernel
     wo[(warp * 4 + t) * kD + e_hi] = O[2 * i + 1] + ob[grp];
   }
   __syncthreads();
+  // this CTA's split: (M, L, O) per head, either to the workspace (a merge kernel follows) or, when the splits of
+  // this (sequence, kv head) form a cluster, to shared memory, where rank 0 reads them through distributed shared memory
+  float* cm = wo + kWarps * 4 * kD;   // [4] running maxima (log2 domain), [4] sums, [4][128] outputs of this CTA
+  float* cl = cm + 4;
+  float* co = cl + 4;
   for (int i = tid; i < p.gqa * kD; i += kWarps * 32) {
     const int h = i / kD, e = i - h * kD;
     float M = kNegBig;
@@ -492,9 +498,38 @@ __global__ void __launch_bounds__(kWarps * 32, BITS == 4 ? 2 : 1) kv_fast_kernel
       L += wl[w * 4 + h] * scl;
       Ov += wo[(w * 4 + h) * kD + e] * scl;
     }
-    const int64_t pi = (b * a.Hq + hk * p.gqa + h) * p.nsplit + split;
-    p.part_o[pi * kD + e] = Ov;
-    if (e == 0) { p.part_m[pi] = M * 0.6931471805599453f; p.part_l[pi] = L; }  // natural-log domain for the merge
+    if (p.fused) {
+      co[i] = Ov;
+      if (e == 0) { cm[h] = M; cl[h] = L; }
+    } else {
+      const int64_t pi = (b * a.Hq + hk * p.gqa + h) * p.nsplit + split;
+      p.part_o[pi * kD + e] = Ov;
+      if (e == 0) { p.part_m[pi] = M * 0.6931471805599453f; p.part_l[pi] = L; }  // natural-log domain for the merge
+    }
+  }
+  if (p.fused) {
+    // out = (sum_r o_r w_r) / (sum_r l_r w_r), w_r = 2^(m_r - max m)  (src/transformer.zig:5194-5203), r over the cluster
+    if (p.nsplit > 1) cluster_sync_all(); else __syncthreads();
+    if (split == 0) {   // the cluster spans the grid's x dimension: its rank is the split index
+      const uint32_t cm_s = (uint32_t)__cvta_generic_to_shared(cm), cl_s = (uint32_t)__cvta_generic_to_shared(cl),
+                     co_s = (uint32_t)__cvta_generic_to_shared(co);
+      for (int i = tid; i < p.gqa * kD; i += kWarps * 32) {
+        const int h = i / kD, e = i - h * kD;
+        float M = kNegBig;
+        for (int r = 0; r < p.nsplit; ++r) M = fmaxf(M, ld_cluster_f32(map_to_rank(cm_s + 4u * h, (uint32_t)r)));
+        float L = 0.f, Ov = 0.f;
+        for (int r = 0; r < p.nsplit; ++r) {
+          const float wgt = ex2(ld_cluster_f32(map_to_rank(cm_s + 4u * h, (uint32_t)r)) - M);
+          L += ld_cluster_f32(map_to_rank(cl_s + 4u * h, (uint32_t)r)) * wgt;
+          Ov += ld_cluster_f32(map_to_rank(co_s + 4u * i, (uint32_t)r)) * wgt;
+        }
+        const float v = Ov * (L > 0.f ? 1.f / L : 0.f);
+        const int64_t off = b * a.o_str[0] + (int64_t)(hk * p.gqa + h) * a.o_str[1] + e;
+        if (a.q_dtype == QB200_FLOAT32) ((float*)a.out)[off] = v;
+        else ((uint16_t*)a.out)[off] = f32_to_bf16_bits(v);
+      }
+    }
+    if (p.nsplit > 1) cluster_sync_all();   // the other ranks' shared memory stays alive until rank 0 has read it
   }
 }
 
@@ -546,14 +581,28 @@ cudaError_t launch_fast_inst(const FastK& p, const TAB& tab, dim3 grid, cudaStre
       if (dev >= 0 && dev < 64) done[dev] = true;
     }
   }
+  if (p.fused && p.nsplit > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kWarps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)p.nsplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kv_fast_kernel<BITS, TAB>, p, tab);
+  }
   return launch_kernel(kv_fast_kernel<BITS, TAB>, grid, dim3(kWarps * 32), smem, st, p, tab);
 }
 }  // namespace
 
 cudaError_t launch_kv_fast(const KvAttnArgs& a, int nsplit, int64_t tps, float* pm, float* pl, float* po,
-                           cudaStream_t st, const KvSeqTable* seqs) {
+                           cudaStream_t st, const KvSeqTable* seqs, bool fused) {
   FastK p;
   p.a = a; p.nsplit = nsplit; p.tps = tps; p.gqa = (int)(a.Hq / a.Hkv);
+  p.fused = fused ? 1 : 0;
   p.part_m = pm; p.part_l = pl; p.part_o = po;
   const dim3 grid((unsigned)nsplit, (unsigned)a.Hkv, (unsigned)a.B);
   if (seqs) return a.bits == 4 ? launch_fast_inst<4, KvSeqTable>(p, *seqs, grid, st) : launch_fast_inst<8, KvSeqTable>(p, *seqs, grid, st);

@@ -76,11 +76,6 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *(const uint32_t*)&h;
 }
 
-__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
-  return v;
-}
 
 // packed bf16 pair arithmetic, correctly rounded
 __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
