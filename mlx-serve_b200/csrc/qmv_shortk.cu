@@ -1,5 +1,5 @@
 // Batched quantized matmul with a short contraction and many weight rows, at attention widths:
-//   y[b, m, n] = sum_k x[b, m, k] * (s[b, n, G(k)] * q[b, n, k] + bias[b, n, G(k)]),   m <= 8, K = 64 / 128 / 256,
+//   y[b, m, n] = sum_k x[b, m, k] * (s[b, n, G(k)] * q[b, n, k] + bias[b, n, G(k)]),   m <= 32, K = 64 / 128 / 256,
 // W [N, K] quantised along K in groups of 64, N long, one W per batch element.
 //
 // Replaces mlx_quantized_matmul(transpose=true) as quantAttention calls it for q @ K^T
@@ -90,8 +90,8 @@ __device__ __forceinline__ int k_of_slot(int t, int mm, int e) {
   return 4 * (4 * t + mm) + (e >> 1) + 2 * (e & 1);
 }
 
-template <int BITS, int NG, typename XT>
-__global__ void __launch_bounds__(kThreads, 2) qmv_shortk_kernel(ShortK p) {
+template <int BITS, int NG, int NT, typename XT>
+__global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) qmv_shortk_kernel(ShortK p) {
   using G = Geo<BITS, NG>;
   constexpr bool SPLIT = !std::is_same<XT, __nv_bfloat16>::value;   // activations as hi + lo
   constexpr int NP = SPLIT ? 2 : 1;
@@ -155,50 +155,56 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_shortk_kernel(ShortK p) {
   // ---- the activations of token g in B-fragment order and the per-group sums of tokens 2t and 2t + 1: the same
   // for every warp, so warp 0 builds them (while the others' first tiles are already on their way) and hands them
   // over through shared memory ----
-  constexpr int kFragWords = NP * NG * 8 + NG * 2;
-  __shared__ uint32_t xs[kFragWords][32];
-  uint32_t bf[NP][NG][4][2];
-  float sx[NG][2];
+  constexpr int kFragWords = NP * NG * 8 + NG * 2;   // per token tile
+  __shared__ uint32_t xs[NT * kFragWords][32];
+  uint32_t bf[NT][NP][NG][4][2];
+  float sx[NT][NG][2];
   if (warp == 0) {
     const char* xb = (const char*)p.x + boff[0] * sizeof(XT);
-    const int tok = g < p.M ? g : 0;   // a token beyond M repeats token 0: its results are never stored
 #pragma unroll
-    for (int gi = 0; gi < NG; ++gi) {
-      float part = 0.f;
+    for (int nt = 0; nt < NT; ++nt) {
+      const int tok = nt * 8 + g < p.M ? nt * 8 + g : 0;   // a token beyond M repeats token 0: its results are never stored
 #pragma unroll
-      for (int mm = 0; mm < 4; ++mm) {
-        float v[4];
+      for (int gi = 0; gi < NG; ++gi) {
+        float part = 0.f;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) v[e] = IO<XT>::load(xb, (int64_t)tok * p.ldx + 64 * gi + k_of_slot<BITS>(t, mm, e));
-        part += (v[0] + v[1]) + (v[2] + v[3]);
-        const uint32_t h0 = pack2(v[0], v[1]), h1 = pack2(v[2], v[3]);
-        xs[(gi * 4 + mm) * 2 + 0][lane] = h0;
-        xs[(gi * 4 + mm) * 2 + 1][lane] = h1;
-        if constexpr (SPLIT) {
-          xs[NG * 8 + (gi * 4 + mm) * 2 + 0][lane] = pack2(v[0] - bf16lo(h0), v[1] - bf16hi(h0));
-          xs[NG * 8 + (gi * 4 + mm) * 2 + 1][lane] = pack2(v[2] - bf16lo(h1), v[3] - bf16hi(h1));
+        for (int mm = 0; mm < 4; ++mm) {
+          float v[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[e] = IO<XT>::load(xb, (int64_t)tok * p.ldx + 64 * gi + k_of_slot<BITS>(t, mm, e));
+          part += (v[0] + v[1]) + (v[2] + v[3]);
+          const uint32_t h0 = pack2(v[0], v[1]), h1 = pack2(v[2], v[3]);
+          xs[nt * kFragWords + (gi * 4 + mm) * 2 + 0][lane] = h0;
+          xs[nt * kFragWords + (gi * 4 + mm) * 2 + 1][lane] = h1;
+          if constexpr (SPLIT) {
+            xs[nt * kFragWords + NG * 8 + (gi * 4 + mm) * 2 + 0][lane] = pack2(v[0] - bf16lo(h0), v[1] - bf16hi(h0));
+            xs[nt * kFragWords + NG * 8 + (gi * 4 + mm) * 2 + 1][lane] = pack2(v[2] - bf16lo(h1), v[3] - bf16hi(h1));
+          }
         }
+        part += __shfl_xor_sync(0xffffffffu, part, 1);
+        part += __shfl_xor_sync(0xffffffffu, part, 2);            // token nt * 8 + g, the whole group
+        xs[nt * kFragWords + NP * NG * 8 + gi * 2 + 0][lane] = __float_as_uint(__shfl_sync(0xffffffffu, part, (2 * t) * 4));   // this thread's accumulator columns
+        xs[nt * kFragWords + NP * NG * 8 + gi * 2 + 1][lane] = __float_as_uint(__shfl_sync(0xffffffffu, part, (2 * t + 1) * 4));
       }
-      part += __shfl_xor_sync(0xffffffffu, part, 1);
-      part += __shfl_xor_sync(0xffffffffu, part, 2);            // token g, the whole group
-      xs[NP * NG * 8 + gi * 2 + 0][lane] = __float_as_uint(__shfl_sync(0xffffffffu, part, (2 * t) * 4));   // this thread's accumulator columns
-      xs[NP * NG * 8 + gi * 2 + 1][lane] = __float_as_uint(__shfl_sync(0xffffffffu, part, (2 * t + 1) * 4));
     }
   }
   __syncthreads();
 #pragma unroll
-  for (int pl = 0; pl < NP; ++pl)
+  for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
-    for (int gi = 0; gi < NG; ++gi)
+    for (int pl = 0; pl < NP; ++pl)
 #pragma unroll
-      for (int mm = 0; mm < 4; ++mm) {
-        bf[pl][gi][mm][0] = xs[pl * NG * 8 + (gi * 4 + mm) * 2 + 0][lane];
-        bf[pl][gi][mm][1] = xs[pl * NG * 8 + (gi * 4 + mm) * 2 + 1][lane];
-      }
+      for (int gi = 0; gi < NG; ++gi)
 #pragma unroll
-  for (int gi = 0; gi < NG; ++gi) {
-    sx[gi][0] = __uint_as_float(xs[NP * NG * 8 + gi * 2 + 0][lane]);
-    sx[gi][1] = __uint_as_float(xs[NP * NG * 8 + gi * 2 + 1][lane]);
+        for (int mm = 0; mm < 4; ++mm) {
+          bf[nt][pl][gi][mm][0] = xs[nt * kFragWords + pl * NG * 8 + (gi * 4 + mm) * 2 + 0][lane];
+          bf[nt][pl][gi][mm][1] = xs[nt * kFragWords + pl * NG * 8 + (gi * 4 + mm) * 2 + 1][lane];
+        }
+#pragma unroll
+    for (int gi = 0; gi < NG; ++gi) {
+      sx[nt][gi][0] = __uint_as_float(xs[nt * kFragWords + NP * NG * 8 + gi * 2 + 0][lane]);
+      sx[nt][gi][1] = __uint_as_float(xs[nt * kFragWords + NP * NG * 8 + gi * 2 + 1][lane]);
+    }
   }
 
   char* yb = (char*)p.y + boff[3] * sizeof(XT);
@@ -210,7 +216,11 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_shortk_kernel(ShortK p) {
     if (i + kStages - 1 < n) fetch(first + (i + kStages - 1) * kWarps, stage == 0 ? kStages - 1 : stage - 1);
     cp_async_commit();
     const uint32_t st = ring + (uint32_t)stage * G::kStageBytes;
-    float y[4] = {0.f, 0.f, 0.f, 0.f};   // rows g, g (tokens 2t, 2t + 1), rows g + 8, g + 8
+    float y[NT][4];   // per token tile: rows g, g (tokens 2t, 2t + 1), rows g + 8, g + 8
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) y[nt][e] = 0.f;
 #pragma unroll
     for (int gi = 0; gi < NG; ++gi) {
       // packed words of rows g and g + 8 in this group: words 2t, 2t + 1 (4-bit) or 4t .. 4t + 3 (8-bit)
@@ -226,7 +236,11 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_shortk_kernel(ShortK p) {
           wq[h][0] = q.x; wq[h][1] = q.y; wq[h][2] = q.z; wq[h][3] = q.w;
         }
       }
-      float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};   // low nibbles (all of a 4-bit code) / high nibbles
+      float d0[NT][4], d1[NT][4];   // low nibbles (all of a 4-bit code) / high nibbles
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) d0[nt][e] = d1[nt][e] = 0.f;
 #pragma unroll
       for (int mm = 0; mm < 4; ++mm) {
         uint32_t a[4], ah[4];
@@ -247,10 +261,12 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_shortk_kernel(ShortK p) {
           ah[3] = lop3_and_or(wq[1][mm] >> 12, 0x000F000Fu, 0x43004300u);
         }
 #pragma unroll
-        for (int pl = 0; pl < NP; ++pl) {
-          mma_bf16_16816(d0, a, bf[pl][gi][mm][0], bf[pl][gi][mm][1]);
-          if (BITS == 8) mma_bf16_16816(d1, ah, bf[pl][gi][mm][0], bf[pl][gi][mm][1]);
-        }
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int pl = 0; pl < NP; ++pl) {
+            mma_bf16_16816(d0[nt], a, bf[nt][pl][gi][mm][0], bf[nt][pl][gi][mm][1]);
+            if (BITS == 8) mma_bf16_16816(d1[nt], ah, bf[nt][pl][gi][mm][0], bf[nt][pl][gi][mm][1]);
+          }
       }
       // the group's scale and bias of rows g and g + 8
       const uint32_t sat = st + G::kCodeBytes + 2 * gi;
@@ -264,25 +280,29 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_shortk_kernel(ShortK p) {
         bi[h] = fmaf(-kMagic, sc[h], bf16_bits_to_f32(bv));
       }
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int h = e >> 1, col = e & 1;
-        const float acc = BITS == 4 ? d0[e] : fmaf(16.f, d1[e], d0[e]);
-        y[e] = fmaf(sc[h], acc, fmaf(bi[h], sx[gi][col], y[e]));
-      }
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h = e >> 1, col = e & 1;
+          const float acc = BITS == 4 ? d0[nt][e] : fmaf(16.f, d1[nt][e], d0[nt][e]);
+          y[nt][e] = fmaf(sc[h], acc, fmaf(bi[h], sx[nt][gi][col], y[nt][e]));
+        }
     }
     const int64_t n0 = (int64_t)(first + i * kWarps) * 16;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int64_t nn = n0 + g + 8 * (e >> 1);
-      const int m = 2 * t + (e & 1);
-      if (nn < p.N && m < p.M) IO<XT>::store(yb, (int64_t)m * p.ldy + nn, y[e]);
-    }
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int64_t nn = n0 + g + 8 * (e >> 1);
+        const int m = nt * 8 + 2 * t + (e & 1);
+        if (nn < p.N && m < p.M) IO<XT>::store(yb, (int64_t)m * p.ldy + nn, y[nt][e]);
+      }
     stage = stage == kStages - 1 ? 0 : stage + 1;
   }
   cp_async_wait<0>();
 }
 
-template <int BITS, int NG, typename XT>
+template <int BITS, int NG, int NT, typename XT>
 cudaError_t launch_inst(const ShortK& p, int ctas_per_batch, int64_t nbatch, cudaStream_t st) {
   using G = Geo<BITS, NG>;
   const size_t smem = (size_t)kWarps * kStages * G::kStageBytes;
@@ -292,20 +312,38 @@ cudaError_t launch_inst(const ShortK& p, int ctas_per_batch, int64_t nbatch, cud
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !done[dev]) {
-      const cudaError_t e = cudaFuncSetAttribute(qmv_shortk_kernel<BITS, NG, XT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      const cudaError_t e = cudaFuncSetAttribute(qmv_shortk_kernel<BITS, NG, NT, XT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return e;
       if (dev >= 0 && dev < 64) done[dev] = true;
     }
   }
-  return launch_kernel(qmv_shortk_kernel<BITS, NG, XT>, dim3((unsigned)ctas_per_batch, (unsigned)nbatch, 1), dim3(kThreads), smem, st, p);
+  return launch_kernel(qmv_shortk_kernel<BITS, NG, NT, XT>, dim3((unsigned)ctas_per_batch, (unsigned)nbatch, 1), dim3(kThreads), smem, st, p);
+}
+
+// Token tiles of 8: fragments of all of them stay in registers, so their number is limited by NT * groups * (2 when the
+// activations are split) <= 8 (64 registers of fragments).
+constexpr bool inst_ok(int ng, int nt, bool split) { return nt * ng * (split ? 2 : 1) <= 8; }
+
+template <int BITS, int NG, typename XT>
+cudaError_t launch_nt(const ShortK& p, int ctas, int64_t nbatch, cudaStream_t st) {
+  constexpr bool SPLIT = !std::is_same<XT, __nv_bfloat16>::value;
+  const int nt = (p.M + 7) / 8;
+  if (nt == 1) return launch_inst<BITS, NG, 1, XT>(p, ctas, nbatch, st);
+  if constexpr (inst_ok(NG, 2, SPLIT)) {
+    if (nt == 2) return launch_inst<BITS, NG, 2, XT>(p, ctas, nbatch, st);
+  }
+  if constexpr (inst_ok(NG, 4, SPLIT)) {
+    if (nt <= 4) return launch_inst<BITS, NG, 4, XT>(p, ctas, nbatch, st);
+  }
+  return cudaErrorInvalidValue;
 }
 
 template <int BITS, int NG>
 cudaError_t launch_x(const ShortK& p, int x_dtype, int ctas, int64_t nbatch, cudaStream_t st) {
   switch (x_dtype) {
-    case QB200_BFLOAT16: return launch_inst<BITS, NG, __nv_bfloat16>(p, ctas, nbatch, st);
-    case QB200_FLOAT32: return launch_inst<BITS, NG, float>(p, ctas, nbatch, st);
-    case QB200_FLOAT16: return launch_inst<BITS, NG, __half>(p, ctas, nbatch, st);
+    case QB200_BFLOAT16: return launch_nt<BITS, NG, __nv_bfloat16>(p, ctas, nbatch, st);
+    case QB200_FLOAT32: return launch_nt<BITS, NG, float>(p, ctas, nbatch, st);
+    case QB200_FLOAT16: return launch_nt<BITS, NG, __half>(p, ctas, nbatch, st);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -331,7 +369,11 @@ bool strides_multiple_of(const BatchMap& m, int64_t q) {
 bool qmv_shortk_supported(const QmmArgs& a) {
   if (!a.transpose || (a.bits != 4 && a.bits != 8) || a.gs != 64) return false;
   if (a.K != 64 && a.K != 128 && a.K != 256) return false;
-  if (a.M < 1 || a.M > 8 || a.N < 1 || a.N > ((int64_t)1 << 30) || a.nbatch < 2 || a.nbatch > 65535) return false;
+  if (a.M < 1 || a.M > 32 || a.N < 1 || a.N > ((int64_t)1 << 30) || a.nbatch < 2 || a.nbatch > 65535) return false;
+  {
+    const int nt = a.M <= 8 ? 1 : (a.M <= 16 ? 2 : 4);
+    if (!inst_ok((int)(a.K / 64), nt, a.x_dtype != QB200_BFLOAT16)) return false;
+  }
   const int64_t ng = a.K / 64;
   // 16-byte pieces of codes by cp.async: rows start on 16 bytes; a row's scales follow the previous row's (lds == groups)
   if ((uintptr_t)a.w % 16 || a.ldw % 4 || !strides_multiple_of(a.wb, 4)) return false;

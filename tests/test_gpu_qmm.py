@@ -183,7 +183,9 @@ def test_transpose_false_value_cache_shapes(batch, M, T, D, bits, gs):
 
 # q @ K^T of the composed quantized attention (src/kv_quant.zig:528-533): x [B, Hkv, g*Tq, D], W the packed key cache
 # [B, Hkv, T, D*bits/32], one W per batch element, a contraction of one head dimension.  The shapes below take the
-# batched short-contraction tensor-core kernel; the last two stay on the generic kernel (group 32; 9 rows).
+# batched short-contraction tensor-core kernel (up to 32 rows); the last two stay on the generic kernel (group 32; fp32
+# activations of 20 rows at four groups, whose fragments would not fit the registers -- the bf16 half of the same case
+# still takes the kernel).
 @pytest.mark.parametrize("batch,M,T,D,bits,gs", [
     ((4, 8), 4, 4096, 128, 4, 64),      # decode over a 4K cache, GQA 4
     ((2, 2), 4, 1000, 128, 8, 64),      # T not a multiple of the 16-row tile: the partial last tile
@@ -194,7 +196,10 @@ def test_transpose_false_value_cache_shapes(batch, M, T, D, bits, gs):
     ((2,), 2, 77, 256, 8, 64),          # 8-bit, four groups
     ((2,), 4, 40000, 128, 4, 64),       # a long cache: many CTAs per batch element
     ((2,), 3, 50, 128, 8, 32),          # generic kernel (group 32)
-    ((2,), 9, 50, 128, 4, 64),          # generic kernel (more than 8 rows)
+    ((2,), 9, 50, 128, 4, 64),          # two token tiles
+    ((2, 2), 16, 300, 128, 8, 64),      # two token tiles, 8-bit
+    ((2,), 32, 130, 128, 4, 64),        # four token tiles (verify widths)
+    ((2,), 20, 90, 256, 4, 64),         # four groups: bf16 activations take the kernel, fp32 the generic one
 ])
 def test_transpose_true_key_cache_shapes(batch, M, T, D, bits, gs):
     rng = np.random.default_rng(T * 5 + D + bits + M)
