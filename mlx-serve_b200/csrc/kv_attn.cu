@@ -11,6 +11,8 @@
 
 #include <type_traits>
 
+#include <cstdlib>
+
 #include "kernels.h"
 
 namespace qb {
@@ -262,6 +264,16 @@ bool kv_attn_supported(const KvAttnArgs& a) {
   return true;
 }
 
+// QB200_KV_FUSED_MERGE=0 in the environment keeps the partials-plus-merge-kernel path for every split count (a
+// diagnostic for measuring the two against each other on one GPU; read once).
+static bool fused_merge_enabled() {
+  static const bool v = [] {
+    const char* e = getenv("QB200_KV_FUSED_MERGE");
+    return !(e && e[0] == '0');
+  }();
+  return v;
+}
+
 cudaError_t launch_kv_attn(const KvAttnArgs& a, cudaStream_t st, const KvSeqTable* seqs) {
   KvK p;
   p.a = a;
@@ -278,7 +290,10 @@ cudaError_t launch_kv_attn(const KvAttnArgs& a, cudaStream_t st, const KvSeqTabl
   if (kv_fast_supported(a, seqs)) {
     // Up to 8 splits per (sequence, kv head) run as one thread-block cluster whose rank 0 merges the partial results
     // through distributed shared memory and writes the output: no partials in global memory, no merge launch.
-    if (sp.nsplit <= kMaxFusedSplits) {
+    // Measured against the merge kernel on one GPU (16 sequences, 8 kv heads): 4-bit caches 23.4 against 24.0 us at
+    // 4096 tokens and 132.8 against 134.0 us at 32768; 8-bit caches, whose CTAs fill an SM alone, 33.0 against 31.8 us
+    // at 4096 tokens -- so only the 4-bit kernel takes the cluster form.
+    if (sp.nsplit <= kMaxFusedSplits && a.bits == 4 && fused_merge_enabled()) {
       e = launch_kv_fast(a, sp.nsplit, sp.tokens_per_split, p.part_m, p.part_l, p.part_o, st, seqs, true);
       if (e == cudaSuccess) return e;
       (void)cudaGetLastError();   // a cluster this launch could not place: fall back to partials and the merge kernel
