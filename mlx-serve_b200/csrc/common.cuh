@@ -58,6 +58,12 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16);
 }
 
+// two fp32 -> packed bf16 (round to nearest even), `lo` in the low half: one conversion instruction
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *(const uint32_t*)&h;
+}
+
 template <typename T> struct IO;
 template <> struct IO<float> {
   __device__ static __forceinline__ float load(const void* p, int64_t i) { return ((const float*)p)[i]; }

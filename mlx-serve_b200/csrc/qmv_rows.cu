@@ -70,11 +70,6 @@ struct RowsK {
   BatchMap xb, wb, sb, yb;
 };
 
-// two fp32 -> packed bf16 (round to nearest even), `lo` in the low half: one conversion instruction
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-  return *(const uint32_t*)&h;
-}
 
 
 // packed bf16 pair arithmetic, correctly rounded

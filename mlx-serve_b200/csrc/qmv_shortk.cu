@@ -73,10 +73,6 @@ __device__ __forceinline__ uint4 lds_u4(uint32_t addr) {
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-  return *(const uint32_t*)&h;
-}
 
 // The k (inside its 64-wide group) that slot `e` (0..3: a0.lo, a0.hi, a2.lo, a2.hi) of MMA `mm` of the group takes
 // from thread t.  4 bits: word 2t + mm / 2 of the group, nibbles (2p, 2p + 4) and (2p + 1, 2p + 5) with p = mm % 2.
