@@ -384,8 +384,8 @@ cudaError_t launch_qmv_shortk(const QmmArgs& a, cudaStream_t st) {
   p.M = (int)a.M; p.K = (int)a.K; p.N = a.N;
   p.ldx = a.ldx; p.ldw = a.ldw; p.lds = a.lds; p.ldy = a.ldy;
   p.tiles = (int)((a.N + 15) / 16);
-  // tiles per CTA: at least 8 per warp (the ring's fill and the activation set-up are paid once per CTA), fewer only
-  // when that would leave SMs without a CTA
+  // tiles per CTA: 16 per warp (the ring's fill and the activation set-up are paid once per CTA), halved down to 2 while
+  // the grid would have fewer than two CTAs per SM
   int per_warp = 16;
   while (per_warp > 2 && a.nbatch * ((p.tiles + kWarps * per_warp - 1) / (kWarps * per_warp)) < 2LL * sm_count()) per_warp /= 2;
   p.tiles_per_cta = kWarps * per_warp;
