@@ -225,6 +225,28 @@ def test_transpose_true_over_a_strided_cache_view():
     gate_bf16(y.float().cpu().numpy(), ref, "strided key cache")
 
 
+def test_non_finite_activations_reach_the_output_of_the_attention_products():
+    """An Inf or a NaN in a row of the activations makes that row's outputs non-finite and leaves the other rows
+    bit for bit as they were, for both products of the composed attention (q @ K^T and attn @ V)."""
+    import qb200
+    rng = np.random.default_rng(405)
+    B, T, D, M = 3, 200, 128, 6
+    kv = rand_bf16(rng, (B, T, D))
+    q, s, b = qo.quantize(kv, 64, 4)
+    dq, ds, db = dev_triple(q, s, b)
+    for transpose, width in ((True, D), (False, T)):
+        x = rand_bf16(rng, (B, M, width), 0.3)
+        clean = qb200.quantized_matmul(to_dev_bf16(qo.f32_to_bf16(x)), dq, ds, db, transpose, 64, 4).float().cpu().numpy()
+        x[1, 0, 5] = np.inf
+        x[1, M - 1, width - 3] = np.nan
+        for dev_x in (to_dev_bf16(qo.f32_to_bf16(x)), torch.from_numpy(x).cuda()):
+            y = qb200.quantized_matmul(dev_x, dq, ds, db, transpose, 64, 4).float().cpu().numpy()
+            assert not np.isfinite(y[1, 0]).any() and not np.isfinite(y[1, M - 1]).any()
+            assert np.isfinite(y[1, 1:M - 1]).all() and np.isfinite(y[0]).all() and np.isfinite(y[2]).all()
+        y16 = qb200.quantized_matmul(to_dev_bf16(qo.f32_to_bf16(x)), dq, ds, db, transpose, 64, 4).float().cpu().numpy()
+        assert np.array_equal(y16[1, 1:M - 1], clean[1, 1:M - 1]) and np.array_equal(y16[0], clean[0])
+
+
 def test_transpose_false_over_a_strided_cache_view():
     """The value cache is a slice [:, :, :T] of capacity buffers, the probabilities a slice of a wider score block: batch
     strides that differ from the dense ones, and an activation pitch that rules the vector loads out."""
