@@ -86,6 +86,45 @@ __device__ __forceinline__ int k_of_slot(int t, int mm, int e) {
   return 4 * (4 * t + mm) + (e >> 1) + 2 * (e & 1);
 }
 
+// The codes, scales and biases of 16-row tile `tile` of the batch element into stage `stage` of the warp's ring.
+template <int BITS, int NG>
+__device__ __forceinline__ void fetch_tile(const ShortK& p, const uint32_t* wbase, const uint16_t* sbase, const uint16_t* bbase,
+                                           uint32_t ring, int tile, int stage, int lane) {
+  using G = Geo<BITS, NG>;
+      const int64_t n0 = (int64_t)tile * 16;
+      const uint32_t dst = ring + (uint32_t)stage * G::kStageBytes;
+  #pragma unroll
+      for (int c = 0; c < (G::kCodePieces + 31) / 32; ++c) {
+        const int piece = lane + 32 * c;
+        if (G::kCodePieces % 32 == 0 || piece < G::kCodePieces) {
+          const int row = piece / (G::kRowBytes / 16), col = piece % (G::kRowBytes / 16);
+          const bool in = n0 + row < p.N;
+          cp_async16_if(dst + row * G::kPitch + col * 16, in ? (const void*)(wbase + (n0 + row) * p.ldw + col * 4) : (const void*)p.w, in);
+        }
+      }
+      // scales of the 16 rows, then their biases: the rows are contiguous (lds == NG), 32 * NG bytes each way, copied as
+      // 4-byte pieces (a batch element's scales start on 4 bytes whenever its row count times NG is even)
+      if (n0 + 16 <= p.N && p.sb_vec) {
+  #pragma unroll
+        for (int c = 0; c < (2 * G::kSbWords + 31) / 32; ++c) {
+          const int piece = lane + 32 * c;
+          if ((2 * G::kSbWords) % 32 == 0 || piece < 2 * G::kSbWords) {
+            const int which = piece / G::kSbWords, word = piece % G::kSbWords;
+            cp_async4(dst + G::kCodeBytes + which * 16 * G::kSbRow + word * 4, (which ? bbase : sbase) + n0 * NG + word * 2);
+          }
+        }
+      } else {
+        // the matrix's last, partial tile (or scales that start on an odd element): entry by entry, so that nothing
+        // behind the last row is read; the plain stores are ordered before the reads of this stage by the __syncwarp
+        // that precedes them
+        for (int idx = lane; idx < 2 * 16 * NG; idx += 32) {
+          const int which = idx / (16 * NG), r = (idx % (16 * NG)) / NG;
+          const uint16_t v = n0 + r < p.N ? (which ? bbase : sbase)[n0 * NG + idx % (16 * NG)] : (uint16_t)0;
+          asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst + G::kCodeBytes + which * 16 * G::kSbRow + (idx % (16 * NG)) * 2), "h"(v) : "memory");
+        }
+      }
+}
+
 template <int BITS, int NG, int NT, typename XT>
 __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) qmv_shortk_kernel(ShortK p) {
   using G = Geo<BITS, NG>;
@@ -104,40 +143,7 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) qmv_shortk_kernel(S
   const uint32_t* wbase = p.w + boff[1];
   const uint16_t* sbase = p.s + boff[2];
   const uint16_t* bbase = p.b + boff[2];
-  auto fetch = [&](int tile, int stage) {
-    const int64_t n0 = (int64_t)tile * 16;
-    const uint32_t dst = ring + (uint32_t)stage * G::kStageBytes;
-#pragma unroll
-    for (int c = 0; c < (G::kCodePieces + 31) / 32; ++c) {
-      const int piece = lane + 32 * c;
-      if (G::kCodePieces % 32 == 0 || piece < G::kCodePieces) {
-        const int row = piece / (G::kRowBytes / 16), col = piece % (G::kRowBytes / 16);
-        const bool in = n0 + row < p.N;
-        cp_async16_if(dst + row * G::kPitch + col * 16, in ? (const void*)(wbase + (n0 + row) * p.ldw + col * 4) : (const void*)p.w, in);
-      }
-    }
-    // scales of the 16 rows, then their biases: the rows are contiguous (lds == NG), 32 * NG bytes each way, copied as
-    // 4-byte pieces (a batch element's scales start on 4 bytes whenever its row count times NG is even)
-    if (n0 + 16 <= p.N && p.sb_vec) {
-#pragma unroll
-      for (int c = 0; c < (2 * G::kSbWords + 31) / 32; ++c) {
-        const int piece = lane + 32 * c;
-        if ((2 * G::kSbWords) % 32 == 0 || piece < 2 * G::kSbWords) {
-          const int which = piece / G::kSbWords, word = piece % G::kSbWords;
-          cp_async4(dst + G::kCodeBytes + which * 16 * G::kSbRow + word * 4, (which ? bbase : sbase) + n0 * NG + word * 2);
-        }
-      }
-    } else {
-      // the matrix's last, partial tile (or scales that start on an odd element): entry by entry, so that nothing
-      // behind the last row is read; the plain stores are ordered before the reads of this stage by the __syncwarp
-      // that precedes them
-      for (int idx = lane; idx < 2 * 16 * NG; idx += 32) {
-        const int which = idx / (16 * NG), r = (idx % (16 * NG)) / NG;
-        const uint16_t v = n0 + r < p.N ? (which ? bbase : sbase)[n0 * NG + idx % (16 * NG)] : (uint16_t)0;
-        asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst + G::kCodeBytes + which * 16 * G::kSbRow + (idx % (16 * NG)) * 2), "h"(v) : "memory");
-      }
-    }
-  };
+  auto fetch = [&](int tile, int stage) { fetch_tile<BITS, NG>(p, wbase, sbase, bbase, ring, tile, stage, lane); };
 
   const int t0 = blockIdx.x * p.tiles_per_cta;
   const int t1 = min(p.tiles, t0 + p.tiles_per_cta);
@@ -298,6 +304,201 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) qmv_shortk_kernel(S
   cp_async_wait<0>();
 }
 
+// ---- up to 8 rows: integer tensor cores ----
+// The same kernel with the codes as the u8 A operand of mma.sync.m16n8k32 (s32 accumulate): a packed word is the
+// thread's eight k of one MMA as it stands -- 4 bits: its even nibbles (word & 0x0F0F0F0F) and its odd ones; 8 bits: two
+// words untouched -- and the activations are 15-bit fixed point, v = rn(x 2^(14 - e)) with one power-of-two scale per
+// (token, 64-wide group), split into a signed high and a 7-bit low plane that sit in two columns of the n8 tile (four
+// tokens per tile).  sum_k q v is exact in s32; per group  y += (s 2^(e - 14)) (128 d_hi + d_lo) + bias 2^(e - 14) sum v.
+// A NaN or an Inf in a group makes its scale NaN, so the row's outputs come out non-finite.
+template <int BITS, int NG, int NT, typename XT>
+__global__ void __launch_bounds__(kThreads, 2) qmv_shortk_i8_kernel(ShortK p) {
+  using G = Geo<BITS, NG>;
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int64_t bz = blockIdx.y;
+  __shared__ int64_t boff[4];
+  if (tid < 4) boff[tid] = (tid == 0 ? p.xb : (tid == 1 ? p.wb : (tid == 2 ? p.sb : p.yb))).offset(bz);
+  __syncthreads();
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + (uint32_t)warp * kStages * G::kStageBytes;
+  const uint32_t* wbase = p.w + boff[1];
+  const uint16_t* sbase = p.s + boff[2];
+  const uint16_t* bbase = p.b + boff[2];
+  auto fetch = [&](int tile, int stage) { fetch_tile<BITS, NG>(p, wbase, sbase, bbase, ring, tile, stage, lane); };
+
+  const int t0 = blockIdx.x * p.tiles_per_cta;
+  const int t1 = min(p.tiles, t0 + p.tiles_per_cta);
+  const int first = t0 + warp;
+  const int n = first < t1 ? (t1 - first + kWarps - 1) / kWarps : 0;
+#pragma unroll 1
+  for (int d = 0; d < kStages - 1; ++d) {
+    if (d < n) fetch(first + d * kWarps, d);
+    cp_async_commit();
+  }
+
+  // ---- the activations as B fragments, built by warp 0 and handed over through shared memory.  Lane (g, t) of a
+  // token tile holds plane g % 2 of token g / 2 at the eight k of its word: 64 gi + 8 (2t + mm) + (4 bits: even k in
+  // b0, odd in b1; 8 bits: k + 0..3 in b0, k + 4..7 in b1) ----
+  constexpr int kFragWords = NG * 4 + NG * 2;   // per token tile: [gi][mm][2] fragments, then (scale, scale * sum v) by token
+  __shared__ uint32_t xs[NT * kFragWords][32];
+  if (warp == 0) {
+    const char* xb = (const char*)p.x + boff[0] * sizeof(XT);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int tk = nt * 4 + (g >> 1);
+      const int tok = tk < p.M ? tk : 0;   // a token beyond M repeats token 0: its results are never stored
+#pragma unroll
+      for (int gi = 0; gi < NG; ++gi) {
+        float f[2][8];
+        float mx = 0.f;
+#pragma unroll
+        for (int mm = 0; mm < 2; ++mm)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int k = 64 * gi + 8 * (2 * t + mm) + (BITS == 4 ? 2 * (j & 3) + (j >> 2) : j);
+            f[mm][j] = IO<XT>::load(xb, (int64_t)tok * p.ldx + k);
+            mx = fmax_nan(mx, fabsf(f[mm][j]));
+          }
+        mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        int e = (int)((__float_as_uint(mx) >> 23) & 0xFF) - 127 + 1;   // mx < 2^e
+        e = e < -100 ? -100 : (e > 110 ? 110 : e);
+        const float up = __uint_as_float((uint32_t)(127 + 14 - e) << 23);
+        const float down = poison_if(nonfinite(mx), __uint_as_float((uint32_t)(127 + e - 14) << 23));
+        int isum = 0;
+#pragma unroll
+        for (int mm = 0; mm < 2; ++mm) {
+          uint32_t reg[2] = {0u, 0u};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float r = fmaf(f[mm][j], up, 12582912.f);   // 1.5 * 2^23 + v: the low 16 bits are v in two's complement
+            if (sizeof(XT) == 4) r = fminf(r, 12599295.f);   // fp32 inputs may round up to 2^14: v <= 16383
+            const int v = (int)(int16_t)(__float_as_uint(r) & 0xFFFFu);
+            isum += v;
+            const uint32_t byte = (g & 1) ? (uint32_t)(v & 127) : (uint32_t)((v >> 7) & 0xFF);
+            reg[j >> 2] |= byte << (8 * (j & 3));
+          }
+          xs[nt * kFragWords + (gi * 2 + mm) * 2 + 0][lane] = reg[0];
+          xs[nt * kFragWords + (gi * 2 + mm) * 2 + 1][lane] = reg[1];
+        }
+        isum += __shfl_xor_sync(0xffffffffu, isum, 1);
+        isum += __shfl_xor_sync(0xffffffffu, isum, 2);
+        if ((g & 1) == 0 && t == 0) {   // one lane per token: the scale and scale * sum v, read back by token index
+          xs[nt * kFragWords + NG * 4 + gi * 2 + 0][g >> 1] = __float_as_uint(down);
+          xs[nt * kFragWords + NG * 4 + gi * 2 + 1][g >> 1] = __float_as_uint(down * (float)isum);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  uint32_t bfr[NT][NG][2][2];
+  float dn[NT][NG], ds[NT][NG];   // of token nt * 4 + t: this thread's accumulator columns
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int gi = 0; gi < NG; ++gi) {
+#pragma unroll
+      for (int mm = 0; mm < 2; ++mm) {
+        bfr[nt][gi][mm][0] = xs[nt * kFragWords + (gi * 2 + mm) * 2 + 0][lane];
+        bfr[nt][gi][mm][1] = xs[nt * kFragWords + (gi * 2 + mm) * 2 + 1][lane];
+      }
+      dn[nt][gi] = __uint_as_float(xs[nt * kFragWords + NG * 4 + gi * 2 + 0][t]);
+      ds[nt][gi] = __uint_as_float(xs[nt * kFragWords + NG * 4 + gi * 2 + 1][t]);
+    }
+
+  char* yb = (char*)p.y + boff[3] * sizeof(XT);
+  int stage = 0;
+#pragma unroll 1
+  for (int i = 0; i < n; ++i) {
+    cp_async_wait<kStages - 2>();   // this lane's pieces of tile i have landed ...
+    __syncwarp();                   // ... and so have every other lane's; every lane is done with the stage read last
+    if (i + kStages - 1 < n) fetch(first + (i + kStages - 1) * kWarps, stage == 0 ? kStages - 1 : stage - 1);
+    cp_async_commit();
+    const uint32_t st = ring + (uint32_t)stage * G::kStageBytes;
+    float y[NT][2];   // rows g and g + 8 of token nt * 4 + t
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) y[nt][0] = y[nt][1] = 0.f;
+#pragma unroll
+    for (int gi = 0; gi < NG; ++gi) {
+      uint32_t wq[2][G::kWordsPerThread];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t at = st + (uint32_t)(g + 8 * h) * G::kPitch + gi * (64 * BITS / 8) + t * (4 * G::kWordsPerThread);
+        if (BITS == 4) {
+          const uint2 q = lds_u2(at);
+          wq[h][0] = q.x; wq[h][1] = q.y;
+        } else {
+          const uint4 q = lds_u4(at);
+          wq[h][0] = q.x; wq[h][1] = q.y; wq[h][2] = q.z; wq[h][3] = q.w;
+        }
+      }
+      int d[NT][4];
+#pragma unroll
+      for (int mm = 0; mm < 2; ++mm) {
+        uint32_t a0, a1, a2, a3;
+        if (BITS == 4) {
+          a0 = wq[0][mm] & 0x0F0F0F0Fu; a2 = (wq[0][mm] >> 4) & 0x0F0F0F0Fu;
+          a1 = wq[1][mm] & 0x0F0F0F0Fu; a3 = (wq[1][mm] >> 4) & 0x0F0F0F0Fu;
+        } else {
+          a0 = wq[0][2 * mm]; a2 = wq[0][2 * mm + 1];
+          a1 = wq[1][2 * mm]; a3 = wq[1][2 * mm + 1];
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          if (mm == 0) mma_u8s8_z(d[nt], a0, a1, a2, a3, bfr[nt][gi][0][0], bfr[nt][gi][0][1]);
+          else mma_u8s8(d[nt], a0, a1, a2, a3, bfr[nt][gi][1][0], bfr[nt][gi][1][1]);
+        }
+      }
+      const uint32_t sat = st + G::kCodeBytes + 2 * gi;
+      float sc[2], bi[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint16_t sv, bv;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sv) : "r"(sat + (uint32_t)(g + 8 * h) * G::kSbRow));
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(bv) : "r"(sat + 16 * G::kSbRow + (uint32_t)(g + 8 * h) * G::kSbRow));
+        sc[h] = bf16_bits_to_f32(sv);
+        bi[h] = bf16_bits_to_f32(bv);
+      }
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int v = 128 * d[nt][2 * h] + d[nt][2 * h + 1];   // columns 2t, 2t + 1: the two planes of token t
+          y[nt][h] = fmaf(sc[h] * dn[nt][gi], (float)v, fmaf(bi[h], ds[nt][gi], y[nt][h]));
+        }
+    }
+    const int64_t n0 = (int64_t)(first + i * kWarps) * 16;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int64_t nn = n0 + g + 8 * h;
+        const int m = nt * 4 + t;
+        if (nn < p.N && m < p.M) IO<XT>::store(yb, (int64_t)m * p.ldy + nn, y[nt][h]);
+      }
+    stage = stage == kStages - 1 ? 0 : stage + 1;
+  }
+  cp_async_wait<0>();
+}
+
+template <int BITS, int NG, int NT, typename XT>
+cudaError_t launch_i8_inst(const ShortK& p, int ctas_per_batch, int64_t nbatch, cudaStream_t st) {
+  using G = Geo<BITS, NG>;
+  const size_t smem = (size_t)kWarps * kStages * G::kStageBytes;
+  {
+    std::lock_guard<std::mutex> lk(setup_mutex());
+    static bool done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !done[dev]) {
+      const cudaError_t e = cudaFuncSetAttribute(qmv_shortk_i8_kernel<BITS, NG, NT, XT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      if (dev >= 0 && dev < 64) done[dev] = true;
+    }
+  }
+  return launch_kernel(qmv_shortk_i8_kernel<BITS, NG, NT, XT>, dim3((unsigned)ctas_per_batch, (unsigned)nbatch, 1), dim3(kThreads), smem, st, p);
+}
+
 template <int BITS, int NG, int NT, typename XT>
 cudaError_t launch_inst(const ShortK& p, int ctas_per_batch, int64_t nbatch, cudaStream_t st) {
   using G = Geo<BITS, NG>;
@@ -323,6 +524,8 @@ constexpr bool inst_ok(int ng, int nt, bool split) { return nt * ng * (split ? 2
 template <int BITS, int NG, typename XT>
 cudaError_t launch_nt(const ShortK& p, int ctas, int64_t nbatch, cudaStream_t st) {
   constexpr bool SPLIT = !std::is_same<XT, __nv_bfloat16>::value;
+  if (p.M <= 4) return launch_i8_inst<BITS, NG, 1, XT>(p, ctas, nbatch, st);   // up to 8 rows: the integer tensor-core form
+  if (p.M <= 8) return launch_i8_inst<BITS, NG, 2, XT>(p, ctas, nbatch, st);
   const int nt = (p.M + 7) / 8;
   if (nt == 1) return launch_inst<BITS, NG, 1, XT>(p, ctas, nbatch, st);
   if constexpr (inst_ok(NG, 2, SPLIT)) {
