@@ -341,22 +341,42 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_shortk_i8_kernel(ShortK p) {
   // b0, odd in b1; 8 bits: k + 0..3 in b0, k + 4..7 in b1) ----
   constexpr int kFragWords = NG * 4 + NG * 2;   // per token tile: [gi][mm][2] fragments, then (scale, scale * sum v) by token
   __shared__ uint32_t xs[NT * kFragWords][32];
-  if (warp == 0) {
+  {
     const char* xb = (const char*)p.x + boff[0] * sizeof(XT);
+    // 16 consecutive k of a token row as two 16-byte loads where the rows allow it (16-bit activations)
+    const bool vec = sizeof(XT) == 2 && (((uintptr_t)xb | (uintptr_t)(p.ldx * 2)) & 15) == 0;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const int tk = nt * 4 + (g >> 1);
       const int tok = tk < p.M ? tk : 0;   // a token beyond M repeats token 0: its results are never stored
 #pragma unroll
       for (int gi = 0; gi < NG; ++gi) {
+        if (warp != (nt * NG + gi) % kWarps) continue;   // one warp per (token tile, group): they work side by side
         float f[2][8];
         float mx = 0.f;
+        float lin[16];   // x[tok][64 gi + 16 t + 0..15]
+        if (vec) {
+          const uint4* src = (const uint4*)(xb + ((int64_t)tok * p.ldx + 64 * gi + 16 * t) * 2);
+          const uint4 q0 = src[0], q1 = src[1];
+          const uint32_t wds[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (std::is_same<XT, __half>::value) {
+              const float2 h2 = __half22float2(*(const __half2*)&wds[j]);
+              lin[2 * j] = h2.x; lin[2 * j + 1] = h2.y;
+            } else {
+              lin[2 * j] = bf16lo(wds[j]); lin[2 * j + 1] = bf16hi(wds[j]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) lin[j] = IO<XT>::load(xb, (int64_t)tok * p.ldx + 64 * gi + 16 * t + j);
+        }
 #pragma unroll
         for (int mm = 0; mm < 2; ++mm)
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const int k = 64 * gi + 8 * (2 * t + mm) + (BITS == 4 ? 2 * (j & 3) + (j >> 2) : j);
-            f[mm][j] = IO<XT>::load(xb, (int64_t)tok * p.ldx + k);
+            f[mm][j] = lin[8 * mm + (BITS == 4 ? 2 * (j & 3) + (j >> 2) : j)];
             mx = fmax_nan(mx, fabsf(f[mm][j]));
           }
         mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
