@@ -611,8 +611,11 @@ cudaError_t launch_qmv_shortk(const QmmArgs& a, cudaStream_t st) {
   // the grid would have fewer than two CTAs per SM
   int per_warp = 16;
   while (per_warp > 2 && a.nbatch * ((p.tiles + kWarps * per_warp - 1) / (kWarps * per_warp)) < 2LL * sm_count()) per_warp /= 2;
-  p.tiles_per_cta = kWarps * per_warp;
-  const int ctas = (p.tiles + p.tiles_per_cta - 1) / p.tiles_per_cta;
+  // the nearest whole number of CTAs, each with an equal share (a cache length just past a multiple of the share must
+  // not add a CTA of one tile)
+  const int target = kWarps * per_warp;
+  const int ctas = p.tiles < target ? 1 : (p.tiles + target / 2) / target;
+  p.tiles_per_cta = (p.tiles + ctas - 1) / ctas;
   p.sb_vec = (uintptr_t)a.s % 4 == 0 && (uintptr_t)a.b % 4 == 0 && strides_multiple_of(a.sb, 2);
   p.xb = a.xb; p.wb = a.wb; p.sb = a.sb; p.yb = a.yb;
   return a.bits == 4 ? launch_bits<4>(p, a.x_dtype, ctas, a.nbatch, st) : launch_bits<8>(p, a.x_dtype, ctas, a.nbatch, st);
